@@ -1,0 +1,210 @@
+"""TEST INFRASTRUCTURE - NOT PRODUCT CODE.
+
+numpy front-end of the plain-C oracle (oracle/exb_oracle.c).  Every function takes and
+returns dense NCHW arrays like the reference's tensors; helpers at the bottom convert to
+the NHWC layouts the CUDA kernels use.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+ACT_NONE, ACT_RELU, ACT_RELU6_QUIRK, ACT_SIGMOID, ACT_MISH = 0, 1, 3, 4, 5
+ACT_RELU6, ACT_SILU = 103, 104
+
+
+def build(force=False):
+    """Compile oracle/exb_oracle.c into oracle/libexb_oracle.so (gcc, a second or two)."""
+    so = os.path.join(_HERE, "libexb_oracle.so")
+    src = os.path.join(_HERE, "exb_oracle.c")
+    hdr = os.path.join(_HERE, "exb_oracle.h")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < max(os.path.getmtime(src), os.path.getmtime(hdr)):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
+    return so
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(build())
+        _LIB.exbo_float32_to_int8.restype = C.c_int8
+        _LIB.exbo_float32_to_int8.argtypes = [C.c_float]
+        _LIB.exbo_conv_out_dim.restype = C.c_int
+        _LIB.exbo_pool_out_dim.restype = C.c_int
+    return _LIB
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _pads(pad):
+    """pad: int or (top, bottom, left, right)."""
+    if isinstance(pad, int):
+        return pad, pad, pad, pad
+    return tuple(pad)
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+def conv_out_dim(i, pa, pb, k, s):
+    return (i + pa + pb - k) // s + 1
+
+
+def conv2d_f32(x, w, bias=None, stride=1, pad=0, group=1, act=0):
+    x, w = _f32(x), _f32(w)
+    N, Cc, H, W = x.shape
+    Cout, _, kh, kw = w.shape
+    sh, sw = _pair(stride)
+    pt, pb, pl, pr = _pads(pad)
+    OH, OW = conv_out_dim(H, pt, pb, kh, sh), conv_out_dim(W, pl, pr, kw, sw)
+    y = np.empty((N, Cout, OH, OW), np.float32)
+    b = _f32(bias) if bias is not None else None
+    lib().exbo_conv2d_f32(_p(x), _p(w), _p(b), _p(y), N, Cc, H, W, Cout, kh, kw, sh, sw,
+                          pt, pb, pl, pr, group, act)
+    return y
+
+
+def float32_to_int8(v):
+    return int(lib().exbo_float32_to_int8(float(v)))
+
+
+def quantize_f32_i8(x, scales):
+    x = _f32(x)
+    N, Cc, H, W = x.shape
+    s = _f32(np.atleast_1d(scales))
+    q = np.empty(x.shape, np.int8)
+    lib().exbo_quantize_f32_i8(_p(x), _p(q), N, Cc, H * W, _p(s), int(s.size))
+    return q
+
+
+def requantize_rne(v, scale):
+    v = _f32(v)
+    q = np.empty(v.shape, np.int8)
+    lib().exbo_requantize_rne_f32_i8(_p(v), _p(q), C.c_int64(v.size), C.c_float(scale))
+    return q
+
+
+def conv2d_i8_acc(xq, wq, stride=1, pad=0, group=1):
+    xq = np.ascontiguousarray(xq, np.int8)
+    wq = np.ascontiguousarray(wq, np.int8)
+    N, Cc, H, W = xq.shape
+    Cout, _, kh, kw = wq.shape
+    sh, sw = _pair(stride)
+    pt, pb, pl, pr = _pads(pad)
+    OH, OW = conv_out_dim(H, pt, pb, kh, sh), conv_out_dim(W, pl, pr, kw, sw)
+    acc = np.empty((N, Cout, OH, OW), np.int32)
+    lib().exbo_conv2d_i8_acc(_p(xq), _p(wq), _p(acc), N, Cc, H, W, Cout, kh, kw, sh, sw,
+                             pt, pb, pl, pr, group)
+    return acc
+
+
+def dequant_scales(ws, fs, cout):
+    ws, fs = _f32(np.atleast_1d(ws)), _f32(np.atleast_1d(fs))
+    out = np.empty(cout, np.float32)
+    lib().exbo_dequant_scales(_p(ws), int(ws.size), _p(fs), int(fs.size), _p(out), cout)
+    return out
+
+
+def dequantize(acc, scale, bias=None):
+    acc = np.ascontiguousarray(acc, np.int32)
+    N, Cc, H, W = acc.shape
+    y = np.empty(acc.shape, np.float32)
+    b = _f32(bias) if bias is not None else None
+    lib().exbo_dequantize_i32_f32(_p(acc), _p(_f32(scale)), _p(b), _p(y), N, Cc, H * W)
+    return y
+
+
+def activation(y, act):
+    y = _f32(y).copy()
+    lib().exbo_activation_f32(_p(y), C.c_int64(y.size), act)
+    return y
+
+
+def conv2d_i8(x, wq, bias, ws, fs, stride=1, pad=0, group=1, act=0):
+    x = _f32(x)
+    wq = np.ascontiguousarray(wq, np.int8)
+    N, Cc, H, W = x.shape
+    Cout, _, kh, kw = wq.shape
+    sh, sw = _pair(stride)
+    pt, pb, pl, pr = _pads(pad)
+    OH, OW = conv_out_dim(H, pt, pb, kh, sh), conv_out_dim(W, pl, pr, kw, sw)
+    y = np.empty((N, Cout, OH, OW), np.float32)
+    ws, fs = _f32(np.atleast_1d(ws)), _f32(np.atleast_1d(fs))
+    b = _f32(bias) if bias is not None else None
+    lib().exbo_conv2d_i8(_p(x), _p(wq), _p(b), _p(ws), int(ws.size), _p(fs), int(fs.size), _p(y),
+                         N, Cc, H, W, Cout, kh, kw, sh, sw, pt, pb, pl, pr, group, act)
+    return y
+
+
+def dwconv2d_f32(x, w, bias=None, stride=1, pad=0, act=0):
+    x, w = _f32(x), _f32(w)
+    N, Cc, H, W = x.shape
+    kh, kw = w.shape[-2:]
+    sh, sw = _pair(stride)
+    pt, pb, pl, pr = _pads(pad)
+    OH, OW = conv_out_dim(H, pt, pb, kh, sh), conv_out_dim(W, pl, pr, kw, sw)
+    y = np.empty((N, Cc, OH, OW), np.float32)
+    b = _f32(bias) if bias is not None else None
+    lib().exbo_dwconv2d_f32(_p(x), _p(w), _p(b), _p(y), N, Cc, H, W, kh, kw, sh, sw,
+                            pt, pb, pl, pr, act)
+    return y
+
+
+def pool2d_f32(x, type=0, kernel=2, stride=2, pad=0, global_pool=False, pad_mode=1,
+               count_include_pad=0):
+    x = _f32(x)
+    N, Cc, H, W = x.shape
+    kh, kw = _pair(kernel)
+    sh, sw = _pair(stride)
+    pt, pb, pl, pr = _pads(pad)
+    if global_pool:
+        kh, kw, sh, sw, pt, pb, pl, pr = H, W, 1, 1, 0, 0, 0, 0
+    PH = lib().exbo_pool_out_dim(H, pt, pb, kh, sh, pad_mode)
+    PW = lib().exbo_pool_out_dim(W, pl, pr, kw, sw, pad_mode)
+    y = np.empty((N, Cc, PH, PW), np.float32)
+    lib().exbo_pool2d_f32(_p(x), _p(y), N, Cc, H, W, type, kh, kw, sh, sw, pt, pb, pl, pr,
+                          int(global_pool), pad_mode, count_include_pad)
+    return y
+
+
+def eltwise_f32(xs, type=1, coeffs=None):
+    xs = [_f32(a) for a in xs]
+    arr = (C.c_void_p * len(xs))(*[a.ctypes.data for a in xs])
+    cf = _f32(coeffs) if coeffs is not None else None
+    y = np.empty(xs[0].shape, np.float32)
+    lib().exbo_eltwise_f32(arr, len(xs), _p(cf), type, _p(y), C.c_int64(y.size))
+    return y
+
+
+def binaryop_f32(a, b, op=0):
+    a, b = _f32(a), _f32(b)
+    y = np.empty(a.shape, np.float32)
+    lib().exbo_binaryop_f32(_p(a), _p(b), _p(y), C.c_int64(y.size), op)
+    return y
+
+
+def relu_f32(x):
+    x = _f32(x)
+    y = np.empty(x.shape, np.float32)
+    lib().exbo_relu_f32(_p(x), _p(y), C.c_int64(y.size))
+    return y
+
+
+# ---- layout helpers -------------------------------------------------------------------
+def nchw_to_nhwc(a):
+    return np.ascontiguousarray(np.transpose(a, (0, 2, 3, 1)))
+
+
+def nhwc_to_nchw(a):
+    return np.ascontiguousarray(np.transpose(a, (0, 3, 1, 2)))
