@@ -1,0 +1,377 @@
+"""ctypes binding of the C ABI (include/excalibur_b200.h) plus thin helpers that take torch
+tensors for device memory.  torch is plumbing here (allocation, streams); every computation
+goes through libexcalibur_b200.so, and importing this module fails loudly if the library has
+not been built.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_PKG, "lib", "libexcalibur_b200.so")
+
+EXB_OK, EXB_ERR_BAD_ARG, EXB_ERR_UNSUPPORTED, EXB_ERR_CUDA, EXB_ERR_TIMEOUT, EXB_ERR_NOMEM = 0, -1, -2, -3, -4, -5
+EXB_F16, EXB_I8, EXB_F32, EXB_I32 = 0, 1, 2, 3
+ACT_NONE, ACT_RELU, ACT_RELU6_QUIRK, ACT_SIGMOID, ACT_RELU6, ACT_SILU = 0, 1, 3, 4, 103, 104
+
+EXPORTED_SYMBOLS = [
+    "exb_ctx_create", "exb_ctx_destroy", "exb_last_error_string", "exb_version", "exb_ctx_sm_count",
+    "exb_ctx_sync_check", "exb_nchw_f32_to_nhwc", "exb_nhwc_to_nchw_f32", "exb_conv_out_dims",
+    "exb_conv_weights_pack_f16", "exb_conv_weights_pack_i8", "exb_conv_weights_destroy",
+    "exb_conv2d_fwd", "exb_conv2d_uses_tensor_cores", "exb_dw_weights_pack", "exb_dw_weights_destroy",
+    "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_eltwise_fwd", "exb_binaryop_fwd",
+    "exb_binaryop_scalar_fwd", "exb_relu_fwd", "exb_activation_fwd", "exb_quantize_fwd",
+    "exb_dequantize_fwd",
+]
+
+
+class ConvDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "N", "H", "W", "Cin", "Cout", "cin_stride", "cout_stride", "kh", "kw", "stride_h", "stride_w",
+        "pad_t", "pad_b", "pad_l", "pad_r", "dilation", "group", "in_dtype", "out_dtype", "out2_dtype",
+        "res_dtype", "act")] + [("out_scale", C.c_float), ("out2_scale", C.c_float), ("impl", C.c_int32)]
+
+
+class DwConvDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "N", "H", "W", "C", "c_stride", "kh", "kw", "stride_h", "stride_w", "pad_t", "pad_b", "pad_l",
+        "pad_r", "in_dtype", "out_dtype", "act")] + [("in_scale", C.c_float), ("out_scale", C.c_float)]
+
+
+class PoolDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "N", "H", "W", "C", "c_stride", "type", "kh", "kw", "stride_h", "stride_w", "pad_t", "pad_b",
+        "pad_l", "pad_r", "global_pool", "pad_mode", "count_include_pad", "dtype", "out2_dtype")] + \
+        [("out2_scale", C.c_float)]
+
+
+class ExbError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("excalibur_b200 error %d: %s" % (code, msg))
+        self.code = code
+
+
+_LIB = None
+
+
+def lib():
+    """Load the shared library (raises if it has not been built: there is no fallback)."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(SO_PATH):
+            raise ImportError("%s is missing: run `python -m excalibur_b200.build`" % SO_PATH)
+        L = C.CDLL(SO_PATH)
+        L.exb_last_error_string.restype = C.c_char_p
+        L.exb_version.restype = C.c_char_p
+        vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
+        L.exb_ctx_create.argtypes = [i32, C.POINTER(vp)]
+        L.exb_ctx_destroy.argtypes = [vp]
+        L.exb_ctx_sm_count.argtypes = [vp, C.POINTER(i32)]
+        L.exb_ctx_sync_check.argtypes = [vp, vp]
+        L.exb_nchw_f32_to_nhwc.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
+        L.exb_nhwc_to_nchw_f32.argtypes = [vp, vp, i32, vp, i32, i32, i32, i32, i32, f32, vp]
+        L.exb_conv_out_dims.argtypes = [C.POINTER(ConvDesc), C.POINTER(i32), C.POINTER(i32)]
+        L.exb_conv2d_uses_tensor_cores.argtypes = [C.POINTER(ConvDesc)]
+        L.exb_conv_weights_pack_f16.argtypes = [vp, C.POINTER(ConvDesc), vp, vp, C.POINTER(vp)]
+        L.exb_conv_weights_pack_i8.argtypes = [vp, C.POINTER(ConvDesc), vp, vp, vp, i32, f32, C.POINTER(vp)]
+        L.exb_conv_weights_destroy.argtypes = [vp]
+        L.exb_conv2d_fwd.argtypes = [vp, C.POINTER(ConvDesc), vp, vp, vp, vp, vp, vp]
+        L.exb_dw_weights_pack.argtypes = [vp, C.POINTER(DwConvDesc), vp, vp, C.POINTER(vp)]
+        L.exb_dw_weights_destroy.argtypes = [vp]
+        L.exb_dwconv2d_fwd.argtypes = [vp, C.POINTER(DwConvDesc), vp, vp, vp, vp]
+        L.exb_pool_out_dims.argtypes = [C.POINTER(PoolDesc), C.POINTER(i32), C.POINTER(i32)]
+        L.exb_pool2d_fwd.argtypes = [vp, C.POINTER(PoolDesc), vp, vp, vp, vp]
+        L.exb_eltwise_fwd.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(f32), vp, i64, i32, vp]
+        L.exb_binaryop_fwd.argtypes = [vp, i32, vp, vp, vp, i64, i32, vp]
+        L.exb_binaryop_scalar_fwd.argtypes = [vp, i32, vp, f32, vp, i64, i32, vp]
+        L.exb_relu_fwd.argtypes = [vp, vp, vp, i64, i32, vp]
+        L.exb_activation_fwd.argtypes = [vp, i32, vp, vp, i64, i32, vp]
+        L.exb_quantize_fwd.argtypes = [vp, vp, i32, vp, i64, f32, i32, vp]
+        L.exb_dequantize_fwd.argtypes = [vp, vp, vp, i32, i64, f32, vp]
+        _LIB = L
+    return _LIB
+
+
+def check(rc):
+    if rc != 0:
+        raise ExbError(rc, lib().exb_last_error_string().decode())
+
+
+def last_error():
+    return lib().exb_last_error_string().decode()
+
+
+# ---- torch plumbing ---------------------------------------------------------------------------
+def _torch():
+    import torch
+    return torch
+
+
+def torch_dtype(dt):
+    t = _torch()
+    return {EXB_F16: t.float16, EXB_I8: t.int8, EXB_F32: t.float32, EXB_I32: t.int32}[dt]
+
+
+def exb_dtype_of(tensor):
+    t = _torch()
+    return {t.float16: EXB_F16, t.int8: EXB_I8, t.float32: EXB_F32, t.int32: EXB_I32}[tensor.dtype]
+
+
+def ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def cur_stream():
+    return C.c_void_p(_torch().cuda.current_stream().cuda_stream)
+
+
+def _np_ptr(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+class Context:
+    """exb_ctx for one device."""
+
+    def __init__(self, device=0):
+        self._h = C.c_void_p()
+        self.device = device
+        check(lib().exb_ctx_create(device, C.byref(self._h)))
+
+    @property
+    def handle(self):
+        return self._h
+
+    def sm_count(self):
+        n = C.c_int()
+        check(lib().exb_ctx_sm_count(self._h, C.byref(n)))
+        return n.value
+
+    def sync_check(self):
+        check(lib().exb_ctx_sync_check(self._h, cur_stream()))
+
+    def close(self):
+        if self._h:
+            lib().exb_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def make_conv_desc(N, H, W, Cin, Cout, k, stride=1, pad=0, in_dtype=EXB_F16, out_dtype=EXB_F16,
+                   out2_dtype=-1, res=False, act=ACT_NONE, out_scale=1.0, out2_scale=1.0,
+                   cin_stride=0, cout_stride=0, group=1, impl=0):
+    kh, kw = (k, k) if isinstance(k, int) else k
+    sh, sw = (stride, stride) if isinstance(stride, int) else stride
+    pt, pb, pl, pr = (pad,) * 4 if isinstance(pad, int) else pad
+    return ConvDesc(N, H, W, Cin, Cout, cin_stride, cout_stride, kh, kw, sh, sw, pt, pb, pl, pr, 1, group,
+                    in_dtype, out_dtype, out2_dtype, EXB_F16 if res else -1, act, out_scale, out2_scale, impl)
+
+
+class ConvWeights:
+    """Packed device-resident convolution weights (exb_conv_weights)."""
+
+    def __init__(self, ctx, desc, w_oihw, bias=None, wscale=None, act_scale=None):
+        self._h = C.c_void_p()
+        bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        if desc.in_dtype == EXB_I8:
+            w = np.ascontiguousarray(w_oihw, np.int8)
+            ws = np.ascontiguousarray(np.atleast_1d(wscale), np.float32)
+            check(lib().exb_conv_weights_pack_i8(ctx.handle, C.byref(desc), _np_ptr(w), _np_ptr(bias),
+                                                 _np_ptr(ws), int(ws.size), float(act_scale), C.byref(self._h)))
+        else:
+            w = np.ascontiguousarray(w_oihw, np.float32)
+            check(lib().exb_conv_weights_pack_f16(ctx.handle, C.byref(desc), _np_ptr(w), _np_ptr(bias),
+                                                  C.byref(self._h)))
+
+    @property
+    def handle(self):
+        return self._h
+
+    def close(self):
+        if self._h:
+            lib().exb_conv_weights_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def conv_out_dims(desc):
+    oh, ow = C.c_int(), C.c_int()
+    check(lib().exb_conv_out_dims(C.byref(desc), C.byref(oh), C.byref(ow)))
+    return oh.value, ow.value
+
+
+def conv2d(ctx, desc, x, weights, residual=None, y=None, y2=None):
+    """x: NHWC torch tensor on the context's device.  Returns (y, y2)."""
+    t = _torch()
+    oh, ow = conv_out_dims(desc)
+    cs = desc.cout_stride or desc.Cout
+    if y is None:
+        y = t.empty((desc.N, oh, ow, cs), dtype=torch_dtype(desc.out_dtype), device=x.device)
+    if desc.out2_dtype != -1 and y2 is None:
+        y2 = t.empty((desc.N, oh, ow, cs), dtype=torch_dtype(desc.out2_dtype), device=x.device)
+    check(lib().exb_conv2d_fwd(ctx.handle, C.byref(desc), ptr(x), weights.handle, ptr(residual), ptr(y),
+                               ptr(y2), cur_stream()))
+    return y, y2
+
+
+class DwWeights:
+    def __init__(self, ctx, desc, w, bias=None):
+        self._h = C.c_void_p()
+        w = np.ascontiguousarray(w, np.float32)
+        bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        check(lib().exb_dw_weights_pack(ctx.handle, C.byref(desc), _np_ptr(w), _np_ptr(bias), C.byref(self._h)))
+
+    @property
+    def handle(self):
+        return self._h
+
+    def close(self):
+        if self._h:
+            lib().exb_dw_weights_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def make_dw_desc(N, H, W, Cc, k=3, stride=1, pad=1, in_dtype=EXB_F16, out_dtype=EXB_F16, act=ACT_NONE,
+                 in_scale=1.0, out_scale=1.0, c_stride=0):
+    kh, kw = (k, k) if isinstance(k, int) else k
+    sh, sw = (stride, stride) if isinstance(stride, int) else stride
+    pt, pb, pl, pr = (pad,) * 4 if isinstance(pad, int) else pad
+    return DwConvDesc(N, H, W, Cc, c_stride, kh, kw, sh, sw, pt, pb, pl, pr, in_dtype, out_dtype, act,
+                      in_scale, out_scale)
+
+
+def dwconv2d(ctx, desc, x, weights, y=None):
+    t = _torch()
+    oh = (desc.H + desc.pad_t + desc.pad_b - desc.kh) // desc.stride_h + 1
+    ow = (desc.W + desc.pad_l + desc.pad_r - desc.kw) // desc.stride_w + 1
+    cs = desc.c_stride or desc.C
+    if y is None:
+        y = t.empty((desc.N, oh, ow, cs), dtype=torch_dtype(desc.out_dtype), device=x.device)
+    check(lib().exb_dwconv2d_fwd(ctx.handle, C.byref(desc), ptr(x), weights.handle, ptr(y), cur_stream()))
+    return y
+
+
+def make_pool_desc(N, H, W, Cc, type=0, k=2, stride=2, pad=0, global_pool=False, pad_mode=1,
+                   count_include_pad=0, dtype=EXB_F16, out2_dtype=-1, out2_scale=1.0, c_stride=0):
+    kh, kw = (k, k) if isinstance(k, int) else k
+    sh, sw = (stride, stride) if isinstance(stride, int) else stride
+    pt, pb, pl, pr = (pad,) * 4 if isinstance(pad, int) else pad
+    return PoolDesc(N, H, W, Cc, c_stride, type, kh, kw, sh, sw, pt, pb, pl, pr, int(global_pool), pad_mode,
+                    count_include_pad, dtype, out2_dtype, out2_scale)
+
+
+def pool_out_dims(desc):
+    ph, pw = C.c_int(), C.c_int()
+    check(lib().exb_pool_out_dims(C.byref(desc), C.byref(ph), C.byref(pw)))
+    return ph.value, pw.value
+
+
+def pool2d(ctx, desc, x, y=None, y2=None):
+    t = _torch()
+    ph, pw = pool_out_dims(desc)
+    cs = desc.c_stride or desc.C
+    if y is None:
+        y = t.empty((desc.N, ph, pw, cs), dtype=x.dtype, device=x.device)
+    if desc.out2_dtype != -1 and y2 is None:
+        y2 = t.empty((desc.N, ph, pw, cs), dtype=t.int8, device=x.device)
+    check(lib().exb_pool2d_fwd(ctx.handle, C.byref(desc), ptr(x), ptr(y), ptr(y2), cur_stream()))
+    return y, y2
+
+
+def eltwise(ctx, xs, type=1, coeffs=None, y=None):
+    t = _torch()
+    if y is None:
+        y = t.empty_like(xs[0])
+    arr = (C.c_void_p * len(xs))(*[x.data_ptr() for x in xs])
+    cf = None if coeffs is None else (C.c_float * len(xs))(*[float(c) for c in coeffs])
+    check(lib().exb_eltwise_fwd(ctx.handle, type, len(xs), arr, cf, ptr(y), xs[0].numel(), exb_dtype_of(xs[0]),
+                                cur_stream()))
+    return y
+
+
+def binaryop(ctx, a, b, op=0, y=None):
+    t = _torch()
+    if y is None:
+        y = t.empty_like(a)
+    check(lib().exb_binaryop_fwd(ctx.handle, op, ptr(a), ptr(b), ptr(y), a.numel(), exb_dtype_of(a), cur_stream()))
+    return y
+
+
+def binaryop_scalar(ctx, a, scalar, op=0, y=None):
+    t = _torch()
+    if y is None:
+        y = t.empty_like(a)
+    check(lib().exb_binaryop_scalar_fwd(ctx.handle, op, ptr(a), float(scalar), ptr(y), a.numel(), exb_dtype_of(a),
+                                        cur_stream()))
+    return y
+
+
+def relu(ctx, x, y=None):
+    t = _torch()
+    if y is None:
+        y = t.empty_like(x)
+    check(lib().exb_relu_fwd(ctx.handle, ptr(x), ptr(y), x.numel(), exb_dtype_of(x), cur_stream()))
+    return y
+
+
+def activation(ctx, x, act, y=None):
+    t = _torch()
+    if y is None:
+        y = t.empty_like(x)
+    check(lib().exb_activation_fwd(ctx.handle, act, ptr(x), ptr(y), x.numel(), exb_dtype_of(x), cur_stream()))
+    return y
+
+
+def quantize(ctx, x, scale, rounding=0, q=None):
+    t = _torch()
+    if q is None:
+        q = t.empty(x.shape, dtype=t.int8, device=x.device)
+    check(lib().exb_quantize_fwd(ctx.handle, ptr(x), exb_dtype_of(x), ptr(q), x.numel(), float(scale), rounding,
+                                 cur_stream()))
+    return q
+
+
+def dequantize(ctx, q, scale, out_dtype=EXB_F16, y=None):
+    t = _torch()
+    if y is None:
+        y = t.empty(q.shape, dtype=torch_dtype(out_dtype), device=q.device)
+    check(lib().exb_dequantize_fwd(ctx.handle, ptr(q), ptr(y), out_dtype, q.numel(), float(scale), cur_stream()))
+    return y
+
+
+def nchw_f32_to_nhwc(ctx, x, dtype=EXB_F16, c_stride=0, scale=1.0, rounding=0, y=None):
+    t = _torch()
+    N, Cc, H, W = x.shape
+    cs = c_stride or Cc
+    if y is None:
+        y = t.empty((N, H, W, cs), dtype=torch_dtype(dtype), device=x.device)
+    check(lib().exb_nchw_f32_to_nhwc(ctx.handle, ptr(x), ptr(y), dtype, N, Cc, H, W, cs, float(scale), rounding,
+                                     cur_stream()))
+    return y
+
+
+def nhwc_to_nchw_f32(ctx, x, Cc=None, scale=1.0, y=None):
+    t = _torch()
+    N, H, W, cs = x.shape
+    Cc = Cc or cs
+    if y is None:
+        y = t.empty((N, Cc, H, W), dtype=t.float32, device=x.device)
+    check(lib().exb_nhwc_to_nchw_f32(ctx.handle, ptr(x), exb_dtype_of(x), ptr(y), N, Cc, H, W, cs, float(scale),
+                                     cur_stream()))
+    return y

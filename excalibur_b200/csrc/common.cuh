@@ -1,0 +1,98 @@
+// Shared declarations of the C-ABI implementation: context, error reporting, launch helpers
+// and the scalar conversion rules every kernel uses.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/excalibur_b200.h"
+
+struct exb_ctx {
+    int device;
+    int sm_count;
+    int smem_optin;          // max dynamic shared memory per block (opt-in)
+    int* d_error;            // device error word written by kernels whose bounded waits ran out
+    int* h_error;            // pinned host mirror
+};
+
+namespace exb {
+
+// Record a message for exb_last_error_string() and return `code`.
+int fail(int code, const char* fmt, ...);
+
+#define EXB_CUDA_TRY(expr)                                                                  \
+    do {                                                                                    \
+        cudaError_t e__ = (expr);                                                           \
+        if (e__ != cudaSuccess)                                                             \
+            return ::exb::fail(EXB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                \
+                               cudaGetErrorString(e__), __FILE__, __LINE__);                \
+    } while (0)
+
+#define EXB_REQUIRE(cond, ...)                                                              \
+    do {                                                                                    \
+        if (!(cond)) return ::exb::fail(EXB_ERR_BAD_ARG, __VA_ARGS__);                      \
+    } while (0)
+
+inline int after_launch(const char* what) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess)
+        return fail(EXB_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+    return EXB_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline size_t dtype_size(int dt) {
+    switch (dt) {
+    case EXB_F16: return 2;
+    case EXB_I8: return 1;
+    case EXB_F32: return 4;
+    case EXB_I32: return 4;
+    default: return 0;
+    }
+}
+
+// ---- device-side scalar rules -------------------------------------------------------------
+// Quantise, half away from zero then truncate and saturate: the reference's float32_to_int8.
+__device__ __forceinline__ int quant_half_away(float v) {
+    float t = v >= 0.f ? v + 0.5f : v - 0.5f;
+    t = fminf(fmaxf(t, -128.f), 127.f);
+    return (int)t;  // truncation toward zero
+}
+// Quantise, round half to even, saturate.
+__device__ __forceinline__ int quant_rne(float v) {
+    float t = rintf(v);
+    t = fminf(fmaxf(t, -128.f), 127.f);
+    return (int)t;
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    switch (act) {
+    case EXB_ACT_NONE: return v;
+    case EXB_ACT_RELU: return v >= 0.f ? v : 0.f;
+    case EXB_ACT_RELU6_QUIRK: return (v >= 0.f && v <= 6.f) ? v : 0.f;
+    case EXB_ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
+    case EXB_ACT_RELU6: return fminf(fmaxf(v, 0.f), 6.f);
+    case EXB_ACT_SILU: return v / (1.f + __expf(-v));
+    default: return v;
+    }
+}
+
+inline bool act_supported(int act) {
+    return act == EXB_ACT_NONE || act == EXB_ACT_RELU || act == EXB_ACT_RELU6_QUIRK ||
+           act == EXB_ACT_SIGMOID || act == EXB_ACT_RELU6 || act == EXB_ACT_SILU;
+}
+
+// Grid for a bandwidth-bound grid-stride kernel: enough CTAs to fill every SM a few times
+// over, a multiple of the SM count, never more than the work needs.
+inline int stream_grid(const exb_ctx* ctx, int64_t work_items, int threads, int ctas_per_sm = 8) {
+    int64_t need = (work_items + threads - 1) / threads;
+    int64_t cap = (int64_t)ctx->sm_count * ctas_per_sm;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+}  // namespace exb

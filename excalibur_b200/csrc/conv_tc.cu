@@ -1,0 +1,429 @@
+// Implicit-GEMM convolution on the 5th-generation tensor cores (sm_100a).
+//
+// GEMM view: M = output pixels, N = output channels, K = kh*kw*Cin.  No im2col buffer exists:
+// for every kernel tap (r,s) and channel block the A operand is a TMA tiled load of a shifted
+// TW x TH x TN box of NHWC pixels (out-of-bounds rows and columns are zero-filled by the TMA
+// unit, which is the convolution's zero padding), landing in shared memory as 128 K-major rows
+// in the hardware swizzle; the B operand is a 2-D TMA load of the packed weight matrix
+// [Cout][kh][kw][Cin].  Stride-2 layers read one of four "parity" views of the input (every
+// second row / column, offset by 0 or 1) so that a box is still a dense rectangle.
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0   TMA producer (one lane)           - fills a ring of shared-memory stages
+//   warp 1   MMA issuer (one lane) + TMEM owner - tcgen05.mma, fp32 / int32 accumulators in TMEM,
+//                                                 two accumulator buffers so the epilogue of
+//                                                 tile i overlaps the main loop of tile i+1
+//   warps 2-5 epilogue                          - tcgen05.ld, scale/bias, residual, activation,
+//                                                 requantise, 16-byte NHWC stores
+// All mbarrier waits are bounded; when one runs out the kernel raises the context's error
+// word, every role leaves its loop, TMEM is freed and the launch returns normally.
+#include "conv_common.cuh"
+#include "ptx_sm100.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace exb {
+namespace {
+
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 192;
+constexpr int kTileM = 128;
+constexpr uint32_t kMaxSpins = 1u << 21;  // tens of milliseconds at least; a legitimate wait is microseconds
+
+struct ConvTcParams {
+    CUtensorMap tmA[4];
+    CUtensorMap tmB;
+    int N, OH, OW;
+    int TW, TH, TN;
+    int tiles_w, tiles_h, tiles_nb;  // M tiles per dimension
+    int n_tiles;                     // N (cout) tiles
+    int BN;
+    int kh, kw, stride, pad_t, pad_l;
+    int cin_pad;      // channels per tap in the packed weights (= physical input channels)
+    int cblks;        // K blocks per tap
+    int kb_elems;     // channels per K block
+    int kb_bytes;     // 32 / 64 / 128
+    int stages;
+    int a_bytes, b_bytes;   // shared-memory bytes per stage
+    int a_tx_bytes;         // bytes one A box delivers
+    int tmem_cols;
+    uint32_t idesc;
+    int has_res;
+    EpiParams e;
+    int* error;
+};
+
+struct TileCoord {
+    int ow0, oh0, n0, ntile;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const ConvTcParams& p, int t) {
+    TileCoord c;
+    c.ntile = t % p.n_tiles;
+    int m = t / p.n_tiles;
+    c.ow0 = (m % p.tiles_w) * p.TW;
+    m /= p.tiles_w;
+    c.oh0 = (m % p.tiles_h) * p.TH;
+    c.n0 = (m / p.tiles_h) * p.TN;
+    return c;
+}
+
+template <bool kInt8>
+__global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_constant__ ConvTcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t tfull_bar[2];
+    __shared__ __align__(8) uint64_t tempty_bar[2];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_flag;
+
+    // Operand ring, 1024-byte aligned (the widest swizzle atom).
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + (size_t)p.stages * p.a_bytes;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.n_tiles;
+    const int k_iters = p.kh * p.kw * p.cblks;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&tfull_bar[i], 1);
+            ptx::mbar_init(&tempty_bar[i], 4);
+        }
+        ptx::fence_mbar_init();
+        ptx::tma_prefetch_desc(&p.tmA[0]);
+        ptx::tma_prefetch_desc(&p.tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(&tmem_base_smem, (uint32_t)p.tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_smem;
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer --------------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = decode_tile(p, t);
+                for (int r = 0; r < p.kh && ok; ++r) {
+                    for (int s = 0; s < p.kw && ok; ++s) {
+                        int map = 0, cw, ch;
+                        if (p.stride == 1) {
+                            cw = tc.ow0 + s - p.pad_l;
+                            ch = tc.oh0 + r - p.pad_t;
+                        } else {
+                            const int dw = s - p.pad_l, dh = r - p.pad_t;
+                            const int pw = dw & 1, ph = dh & 1;
+                            cw = tc.ow0 + ((dw - pw) >> 1);
+                            ch = tc.oh0 + ((dh - ph) >> 1);
+                            map = ph * 2 + pw;
+                        }
+                        const int kbase = (r * p.kw + s) * p.cin_pad;
+                        for (int cb = 0; cb < p.cblks; ++cb) {
+                            if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, &abort_flag, kMaxSpins)) {
+                                ok = false;
+                                break;
+                            }
+                            ptx::mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(p.a_tx_bytes + p.b_bytes));
+                            ptx::tma_load_4d(smem_a + (size_t)stage * p.a_bytes, &p.tmA[map], &full_bar[stage],
+                                             cb * p.kb_elems, cw, ch, tc.n0);
+                            ptx::tma_load_2d(smem_b + (size_t)stage * p.b_bytes, &p.tmB, &full_bar[stage],
+                                             kbase + cb * p.kb_elems, tc.ntile * p.BN);
+                            if (++stage == p.stages) {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                atomicExch(p.error, 1);
+                // Give copies already in flight time to land before this CTA's shared memory
+                // can be handed to another CTA.
+                for (int i = 0; i < 2000; ++i) __nanosleep(100);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ----------------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            const int ksteps = p.kb_bytes / 32;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                if (!ptx::mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, &abort_flag, kMaxSpins)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
+                uint32_t accumulate = 0;
+                for (int it = 0; it < k_iters; ++it) {
+                    if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, &abort_flag, kMaxSpins)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = ptx::smem_u32(smem_a + (size_t)stage * p.a_bytes);
+                    const uint32_t b_addr = ptx::smem_u32(smem_b + (size_t)stage * p.b_bytes);
+                    for (int k = 0; k < ksteps; ++k) {
+                        const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, (uint32_t)p.kb_bytes);
+                        const uint64_t bdesc = ptx::make_smem_desc(b_addr + k * 32, (uint32_t)p.kb_bytes);
+                        ptx::tc_mma<kInt8>(d_tmem, adesc, bdesc, p.idesc, accumulate);
+                        accumulate = 1;
+                    }
+                    ptx::tc_commit(&empty_bar[stage]);  // stage is free once these MMAs retire
+                    if (++stage == p.stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                ptx::tc_commit(&tfull_bar[acc]);  // accumulator complete
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+            if (!ok) atomicExch(p.error, 2);
+        }
+    } else {
+        // ------------------------------- epilogue ------------------------------------------
+        const int q = warp & 3;            // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;     // row of the M tile == TMEM lane
+        const int tw = row % p.TW;
+        const int th = (row / p.TW) % p.TH;
+        const int tn = row / (p.TW * p.TH);
+        const bool row_in_box = row < p.TW * p.TH * p.TN;
+        const bool vec_ok = (p.e.cout_stride & 15) == 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            const TileCoord tc = decode_tile(p, t);
+            if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_phase, &abort_flag, kMaxSpins)) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            const int ow = tc.ow0 + tw, oh = tc.oh0 + th, n = tc.n0 + tn;
+            const bool valid = row_in_box && ow < p.OW && oh < p.OH && n < p.N;
+            const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.BN);
+            for (int chunk = 0; chunk < p.BN / 16; ++chunk) {
+                uint32_t raw[16];
+                ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
+                ptx::tmem_ld_wait();
+                const int c0 = tc.ntile * p.BN + chunk * 16;
+                if (!valid || c0 >= p.e.cout_stride) continue;
+                const int64_t off = pix * p.e.cout_stride + c0;
+                if (vec_ok) {
+                    float v[16];
+                    const float4* sc = reinterpret_cast<const float4*>(p.e.scale + c0);
+                    const float4* bi = reinterpret_cast<const float4*>(p.e.bias + c0);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float4 s4 = __ldg(sc + i), b4 = __ldg(bi + i);
+                        v[4 * i + 0] = epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x);
+                        v[4 * i + 1] = epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y);
+                        v[4 * i + 2] = epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z);
+                        v[4 * i + 3] = epi_value<kInt8>(raw[4 * i + 3], s4.w, b4.w);
+                    }
+                    if (p.has_res) {
+                        const uint4* rp = reinterpret_cast<const uint4*>(p.e.residual + off);
+                        uint4 rr[2] = {__ldg(rp), __ldg(rp + 1)};
+                        const __half2* h = reinterpret_cast<const __half2*>(rr);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 f = __half22float2(h[i]);
+                            v[2 * i] += f.x;
+                            v[2 * i + 1] += f.y;
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = apply_act(v[i], p.e.act);
+                    epi_store_vec16(p.e.y, p.e.out_dtype, off, v, p.e.out_scale, raw);
+                    if (p.e.out2_dtype >= 0) epi_store_vec16(p.e.y2, p.e.out2_dtype, off, v, p.e.out2_scale, raw);
+                } else {
+                    for (int i = 0; i < 16 && c0 + i < p.e.cout_stride; ++i) {
+                        float v = epi_value<kInt8>(raw[i], __ldg(p.e.scale + c0 + i), __ldg(p.e.bias + c0 + i));
+                        if (p.has_res) v += __half2float(p.e.residual[off + i]);
+                        v = apply_act(v, p.e.act);
+                        epi_store_scalar(p.e.y, p.e.out_dtype, off + i, v, p.e.out_scale, raw[i]);
+                        if (p.e.out2_dtype >= 0)
+                            epi_store_scalar(p.e.y2, p.e.out2_dtype, off + i, v, p.e.out2_scale, raw[i]);
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+        if (!ok && lane == 0) atomicExch(p.error, 3);
+    }
+
+    // ------------------------------- teardown -----------------------------------------------
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }
+    return fn;
+}
+
+CUtensorMapSwizzle swizzle_for(int kb_bytes) {
+    return kb_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                           : (kb_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+int round_up(int a, int b) { return (a + b - 1) / b * b; }
+
+// Pick the pixel box (TW x TH x TN <= 128 rows) that wastes the fewest MMA rows; ties go to
+// the widest box (longest contiguous runs for the TMA unit), then the tallest.
+void choose_tile(int N, int OH, int OW, int& TW, int& TH, int& TN) {
+    double best = -1.0;
+    TW = 1; TH = 1; TN = 1;
+    for (int tw = 1; tw <= OW && tw <= kTileM; ++tw)
+        for (int th = 1; th <= OH && tw * th <= kTileM; ++th) {
+            int tn = kTileM / (tw * th);
+            if (tn > N) tn = N;
+            if (tn < 1) continue;
+            const int64_t tiles = (int64_t)((OW + tw - 1) / tw) * ((OH + th - 1) / th) * ((N + tn - 1) / tn);
+            const double eff = (double)OW * OH * N / ((double)tiles * kTileM);
+            const bool better = eff > best + 1e-9 ||
+                                (eff > best - 1e-9 && (tw > TW || (tw == TW && th > TH)));
+            if (better) {
+                best = eff;
+                TW = tw; TH = th; TN = tn;
+            }
+        }
+}
+
+}  // namespace
+
+bool conv_tc_eligible(const ConvGeom& g) {
+    const int es = g.in_dtype == EXB_I8 ? 1 : 2;
+    if (g.group != 1) return false;
+    if (g.sh != g.sw || (g.sh != 1 && g.sh != 2)) return false;
+    if ((g.cin_stride * es) % 32 != 0) return false;       // K block of at least 32 bytes
+    if (g.N < 1 || g.OH < 1 || g.OW < 1) return false;
+    if (g.out_dtype == EXB_I32 && g.in_dtype != EXB_I8) return false;
+    return true;
+}
+
+int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_conv_weights* w,
+                   const void* residual, void* y, void* y2, cudaStream_t st) {
+    auto encode = get_encode_fn();
+    if (!encode) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const bool int8 = g.in_dtype == EXB_I8;
+    const int es = int8 ? 1 : 2;
+    ConvTcParams p;
+    memset(&p, 0, sizeof(p));
+    p.N = g.N; p.OH = g.OH; p.OW = g.OW;
+    choose_tile(g.N, g.OH, g.OW, p.TW, p.TH, p.TN);
+    p.tiles_w = (g.OW + p.TW - 1) / p.TW;
+    p.tiles_h = (g.OH + p.TH - 1) / p.TH;
+    p.tiles_nb = (g.N + p.TN - 1) / p.TN;
+    p.n_tiles = (w->cout_pad + 255) / 256;
+    p.BN = round_up((w->cout_pad + p.n_tiles - 1) / p.n_tiles, 16);
+    p.kh = g.kh; p.kw = g.kw; p.stride = g.sh; p.pad_t = g.pt; p.pad_l = g.pl;
+    p.cin_pad = g.cin_stride;
+    const int row_bytes = g.cin_stride * es;
+    p.kb_bytes = row_bytes % 128 == 0 ? 128 : (row_bytes % 64 == 0 ? 64 : 32);
+    p.kb_elems = p.kb_bytes / es;
+    p.cblks = row_bytes / p.kb_bytes;
+    p.a_bytes = kTileM * p.kb_bytes;
+    p.b_bytes = p.BN * p.kb_bytes;
+    p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
+    const int budget = ctx->smem_optin - 2048;  // static barriers + alignment slack
+    int stages = budget / (p.a_bytes + p.b_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return fail(EXB_ERR_UNSUPPORTED, "conv tile does not fit shared memory (BN=%d)", p.BN);
+    p.stages = stages;
+    int cols = 32;
+    while (cols < 2 * p.BN) cols *= 2;
+    p.tmem_cols = cols;
+    p.idesc = ptx::make_idesc(int8, kTileM, (uint32_t)p.BN);
+    p.has_res = g.has_res;
+    p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.residual = static_cast<const __half*>(residual);
+    p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;
+    p.e.out_scale = g.out_scale; p.e.out2_scale = g.out2_scale; p.e.cout_stride = g.cout_stride;
+    p.error = ctx->d_error;
+
+    const CUtensorMapDataType dt = int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapSwizzle sw = swizzle_for(p.kb_bytes);
+    // A: one view per input parity (only view 0 for stride 1).
+    const int nviews = g.sh == 1 ? 1 : 4;
+    for (int v = 0; v < nviews; ++v) {
+        const int ph = v >> 1, pw = v & 1;
+        const int st_ = g.sh;
+        // rows / columns of this view: indices ph, ph+st, ... < H
+        const int vh = (g.H - ph + st_ - 1) / st_;
+        const int vw = (g.W - pw + st_ - 1) / st_;
+        if (vh <= 0 || vw <= 0) {
+            // view is empty (1-pixel-wide input): reuse view 0's descriptor slot with zero-size
+            // semantics by pointing at a valid 1x1 view; its taps never contribute because the
+            // corresponding coordinates are out of range.  Keep it simple: refuse.
+            return fail(EXB_ERR_UNSUPPORTED, "stride-2 convolution needs H and W of at least 2");
+        }
+        cuuint64_t dims[4] = {(cuuint64_t)g.cin_stride, (cuuint64_t)vw, (cuuint64_t)vh, (cuuint64_t)g.N};
+        cuuint64_t strides[3] = {(cuuint64_t)st_ * g.cin_stride * es, (cuuint64_t)st_ * g.W * g.cin_stride * es,
+                                 (cuuint64_t)g.H * g.W * g.cin_stride * es};
+        cuuint32_t box[4] = {(cuuint32_t)p.kb_elems, (cuuint32_t)p.TW, (cuuint32_t)p.TH, (cuuint32_t)p.TN};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        void* base = const_cast<char*>(static_cast<const char*>(x)) + ((size_t)ph * g.W + pw) * g.cin_stride * es;
+        CUresult r = encode(&p.tmA[v], dt, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(A view %d) failed with %d", v, (int)r);
+    }
+    {
+        const int K = g.kh * g.kw * w->cin_pad;
+        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)w->cout_pad};
+        cuuint64_t strides[1] = {(cuuint64_t)K * es};
+        cuuint32_t box[2] = {(cuuint32_t)p.kb_elems, (cuuint32_t)p.BN};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = encode(&p.tmB, dt, 2, w->d_w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed with %d", (int)r);
+    }
+
+    const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.n_tiles;
+    const int grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
+    const size_t smem = (size_t)p.stages * (p.a_bytes + p.b_bytes) + 1024;
+    auto kern = int8 ? conv_tc_kernel<true> : conv_tc_kernel<false>;
+    EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, kThreads, smem, st>>>(p);
+    return after_launch("conv_tc_kernel");
+}
+
+}  // namespace exb

@@ -1,0 +1,108 @@
+// API-edge converts between the reference's NCHW fp32 tensors and the NHWC fp16 / int8
+// buffers the kernels use.  Both directions go through a shared-memory transpose tile so
+// that global reads and writes are both coalesced (reads along W, writes along C or back).
+#include "common.cuh"
+
+namespace exb {
+namespace {
+
+constexpr int kTile = 32;  // 32 (hw) x 32 (c) transpose tile, 32x8 threads
+
+template <typename Out> __device__ __forceinline__ Out cvt_out(float v, float scale, int rounding);
+template <> __device__ __forceinline__ __half cvt_out<__half>(float v, float, int) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ int8_t cvt_out<int8_t>(float v, float scale, int rounding) {
+    return (int8_t)(rounding ? quant_rne(v * scale) : quant_half_away(v * scale));
+}
+template <> __device__ __forceinline__ float cvt_out<float>(float v, float, int) { return v; }
+
+// x: [N][C][HW] fp32  ->  y: [N][HW][c_stride] Out, channels >= C written as zero.
+template <typename Out>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float* __restrict__ x, Out* __restrict__ y,
+                                                           int C, int HW, int c_stride, float scale, int rounding) {
+    __shared__ float tile[kTile][kTile + 1];
+    const int n = blockIdx.z;
+    const int hw0 = blockIdx.x * kTile, c0 = blockIdx.y * kTile;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    for (int j = ty; j < kTile; j += 8) {
+        int c = c0 + j, hw = hw0 + tx;
+        tile[j][tx] = (c < C && hw < HW) ? x[((int64_t)n * C + c) * HW + hw] : 0.f;
+    }
+    __syncthreads();
+    for (int j = ty; j < kTile; j += 8) {
+        int hw = hw0 + j, c = c0 + tx;
+        if (hw < HW && c < c_stride)
+            y[((int64_t)n * HW + hw) * c_stride + c] = cvt_out<Out>(tile[tx][j], scale, rounding);
+    }
+}
+
+template <typename In> __device__ __forceinline__ float cvt_in(In v, float scale);
+template <> __device__ __forceinline__ float cvt_in<__half>(__half v, float) { return __half2float(v); }
+template <> __device__ __forceinline__ float cvt_in<int8_t>(int8_t v, float scale) { return (float)v * scale; }
+template <> __device__ __forceinline__ float cvt_in<float>(float v, float) { return v; }
+
+// x: [N][HW][c_stride] In  ->  y: [N][C][HW] fp32.
+template <typename In>
+__global__ void __launch_bounds__(256) nhwc_to_nchw_kernel(const In* __restrict__ x, float* __restrict__ y,
+                                                           int C, int HW, int c_stride, float scale) {
+    __shared__ float tile[kTile][kTile + 1];
+    const int n = blockIdx.z;
+    const int hw0 = blockIdx.x * kTile, c0 = blockIdx.y * kTile;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    for (int j = ty; j < kTile; j += 8) {
+        int hw = hw0 + j, c = c0 + tx;
+        tile[j][tx] = (hw < HW && c < C) ? cvt_in<In>(x[((int64_t)n * HW + hw) * c_stride + c], scale) : 0.f;
+    }
+    __syncthreads();
+    for (int j = ty; j < kTile; j += 8) {
+        int c = c0 + j, hw = hw0 + tx;
+        if (c < C && hw < HW) y[((int64_t)n * C + c) * HW + hw] = tile[tx][j];
+    }
+}
+
+int check_dims(const exb_ctx* ctx, const void* a, const void* b, int N, int C, int H, int W, int c_stride) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(N >= 0 && C > 0 && H > 0 && W > 0, "bad tensor shape %dx%dx%dx%d", N, C, H, W);
+    EXB_REQUIRE(c_stride >= C, "c_stride %d < C %d", c_stride, C);
+    EXB_REQUIRE(N == 0 || (a && b), "null buffer");
+    EXB_REQUIRE(N <= 65535, "batch %d exceeds the grid limit of this kernel", N);
+    return EXB_OK;
+}
+
+}  // namespace
+}  // namespace exb
+
+using namespace exb;
+
+extern "C" int exb_nchw_f32_to_nhwc(exb_ctx* ctx, const float* x, void* y, int dtype, int N, int C, int H,
+                                    int W, int c_stride, float scale, int rounding, void* stream) {
+    if (c_stride == 0) c_stride = C;
+    if (int rc = check_dims(ctx, x, y, N, C, H, W, c_stride)) return rc;
+    if (N == 0) return EXB_OK;
+    const int HW = H * W;
+    dim3 grid((HW + kTile - 1) / kTile, (c_stride + kTile - 1) / kTile, N), block(kTile, 8);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+    case EXB_F16: nchw_to_nhwc_kernel<__half><<<grid, block, 0, st>>>(x, static_cast<__half*>(y), C, HW, c_stride, scale, rounding); break;
+    case EXB_I8: nchw_to_nhwc_kernel<int8_t><<<grid, block, 0, st>>>(x, static_cast<int8_t*>(y), C, HW, c_stride, scale, rounding); break;
+    case EXB_F32: nchw_to_nhwc_kernel<float><<<grid, block, 0, st>>>(x, static_cast<float*>(y), C, HW, c_stride, scale, rounding); break;
+    default: return fail(EXB_ERR_UNSUPPORTED, "exb_nchw_f32_to_nhwc: dtype %d", dtype);
+    }
+    return after_launch("nchw_to_nhwc_kernel");
+}
+
+extern "C" int exb_nhwc_to_nchw_f32(exb_ctx* ctx, const void* x, int dtype, float* y, int N, int C, int H,
+                                    int W, int c_stride, float scale, void* stream) {
+    if (c_stride == 0) c_stride = C;
+    if (int rc = check_dims(ctx, x, y, N, C, H, W, c_stride)) return rc;
+    if (N == 0) return EXB_OK;
+    const int HW = H * W;
+    dim3 grid((HW + kTile - 1) / kTile, (C + kTile - 1) / kTile, N), block(kTile, 8);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+    case EXB_F16: nhwc_to_nchw_kernel<__half><<<grid, block, 0, st>>>(static_cast<const __half*>(x), y, C, HW, c_stride, scale); break;
+    case EXB_I8: nhwc_to_nchw_kernel<int8_t><<<grid, block, 0, st>>>(static_cast<const int8_t*>(x), y, C, HW, c_stride, scale); break;
+    case EXB_F32: nhwc_to_nchw_kernel<float><<<grid, block, 0, st>>>(static_cast<const float*>(x), y, C, HW, c_stride, scale); break;
+    default: return fail(EXB_ERR_UNSUPPORTED, "exb_nhwc_to_nchw_f32: dtype %d", dtype);
+    }
+    return after_launch("nhwc_to_nchw_kernel");
+}

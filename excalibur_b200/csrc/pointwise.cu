@@ -1,0 +1,315 @@
+// Bandwidth-bound element-wise kernels: n-ary eltwise, binary op, ReLU / activation,
+// quantise / dequantise.  One pass each, 128-bit loads and stores, grid-stride over 16-byte
+// vectors with a scalar tail.  Math is fp32 whatever the storage type.
+#include "common.cuh"
+
+namespace exb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxEltwiseInputs = 8;
+
+template <typename T> struct Vec;  // 16 bytes of T
+template <> struct Vec<__half> {
+    static constexpr int N = 8;
+    __device__ static void load(const __half* p, float (&v)[8]) {
+        uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    __device__ static void store(__half* p, const float (&v)[8]) {
+        uint4 r;
+        __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float (&v)[4]) {
+        float4 r = *reinterpret_cast<const float4*>(p);
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    __device__ static void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+__device__ __forceinline__ float ldf(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ void stf(__half* p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+
+// ---- generic unary / binary map ---------------------------------------------------------
+template <typename T, typename F>
+__global__ void __launch_bounds__(kThreads) map1_kernel(const T* x, T* y, int64_t count, F f) {
+    constexpr int V = Vec<T>::N;
+    const int64_t nvec = count / V;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        float v[V];
+        Vec<T>::load(x + i * V, v);
+#pragma unroll
+        for (int k = 0; k < V; ++k) v[k] = f(v[k]);
+        Vec<T>::store(y + i * V, v);
+    }
+    for (int64_t i = nvec * V + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+        stf(y + i, f(ldf(x + i)));
+}
+
+template <typename T, typename F>
+__global__ void __launch_bounds__(kThreads) map2_kernel(const T* a, const T* b, T* y,
+                                                        int64_t count, F f) {
+    constexpr int V = Vec<T>::N;
+    const int64_t nvec = count / V;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        float va[V], vb[V];
+        Vec<T>::load(a + i * V, va);
+        Vec<T>::load(b + i * V, vb);
+#pragma unroll
+        for (int k = 0; k < V; ++k) va[k] = f(va[k], vb[k]);
+        Vec<T>::store(y + i * V, va);
+    }
+    for (int64_t i = nvec * V + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+        stf(y + i, f(ldf(a + i), ldf(b + i)));
+}
+
+struct EltwiseArgs {
+    const void* x[kMaxEltwiseInputs];
+    float coeff[kMaxEltwiseInputs];
+    int n_in;
+    int type;  // 0 PROD, 1 SUM, 2 MAX
+};
+
+__device__ __forceinline__ float eltwise_combine(int type, float acc, float v, float c) {
+    // SUM follows the reference order: y = 0, then y = c_k * x_k + y for each input.
+    return type == 1 ? fmaf(c, v, acc) : (type == 2 ? fmaxf(acc, v) : acc * v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) eltwise_kernel(EltwiseArgs args, T* y, int64_t count) {
+    constexpr int V = Vec<T>::N;
+    const int64_t nvec = count / V;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        float acc[V], v[V];
+        Vec<T>::load(static_cast<const T*>(args.x[0]) + i * V, acc);
+        if (args.type == 1) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[k] = fmaf(args.coeff[0], acc[k], 0.f);
+        }
+        for (int j = 1; j < args.n_in; ++j) {
+            Vec<T>::load(static_cast<const T*>(args.x[j]) + i * V, v);
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[k] = eltwise_combine(args.type, acc[k], v[k], args.coeff[j]);
+        }
+        Vec<T>::store(y + i * V, acc);
+    }
+    for (int64_t i = nvec * V + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float acc = ldf(static_cast<const T*>(args.x[0]) + i);
+        if (args.type == 1) acc = fmaf(args.coeff[0], acc, 0.f);
+        for (int j = 1; j < args.n_in; ++j)
+            acc = eltwise_combine(args.type, acc, ldf(static_cast<const T*>(args.x[j]) + i), args.coeff[j]);
+        stf(y + i, acc);
+    }
+}
+
+// ---- quantise / dequantise ---------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads) quantize_kernel(const T* x, int8_t* q, int64_t count,
+                                                            float scale, int rounding) {
+    // 16 outputs (16 bytes) per thread step.
+    const int64_t nvec = count / 16;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    constexpr int V = Vec<T>::N;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        alignas(16) int8_t out[16];
+#pragma unroll
+        for (int c = 0; c < 16 / V; ++c) {
+            float v[V];
+            Vec<T>::load(x + i * 16 + c * V, v);
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                out[c * V + k] = (int8_t)(rounding ? quant_rne(v[k] * scale) : quant_half_away(v[k] * scale));
+        }
+        *reinterpret_cast<uint4*>(q + i * 16) = *reinterpret_cast<const uint4*>(out);
+    }
+    for (int64_t i = nvec * 16 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float v = ldf(x + i) * scale;
+        q[i] = (int8_t)(rounding ? quant_rne(v) : quant_half_away(v));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) dequantize_kernel(const int8_t* q, T* y, int64_t count,
+                                                              float scale) {
+    const int64_t nvec = count / 16;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    constexpr int V = Vec<T>::N;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        alignas(16) int8_t in[16];
+        *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(q + i * 16);
+#pragma unroll
+        for (int c = 0; c < 16 / V; ++c) {
+            float v[V];
+#pragma unroll
+            for (int k = 0; k < V; ++k) v[k] = (float)in[c * V + k] * scale;
+            Vec<T>::store(y + i * 16 + c * V, v);
+        }
+    }
+    for (int64_t i = nvec * 16 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+        stf(y + i, (float)q[i] * scale);
+}
+
+struct ActFn {
+    int act;
+    __device__ float operator()(float v) const { return apply_act(v, act); }
+};
+struct ReluFn {
+    __device__ float operator()(float v) const { return v >= 0.f ? v : 0.f; }
+};
+struct BinFn {
+    int op;
+    __device__ float operator()(float a, float b) const {
+        return op == 0 ? a + b : (op == 1 ? a - b : (op == 2 ? a * b : a / b));
+    }
+};
+struct BinScalarFn {
+    int op;
+    float s;
+    __device__ float operator()(float a) const {
+        return op == 0 ? a + s : (op == 1 ? a - s : (op == 2 ? a * s : a / s));
+    }
+};
+
+int check_common(const exb_ctx* ctx, int64_t count, int dtype) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(count >= 0, "negative element count");
+    if (dtype != EXB_F16 && dtype != EXB_F32)
+        return fail(EXB_ERR_UNSUPPORTED, "element-wise ops support EXB_F16 and EXB_F32, got dtype %d", dtype);
+    return EXB_OK;
+}
+
+template <typename F>
+int launch_map1(exb_ctx* ctx, const void* x, void* y, int64_t count, int dtype, void* stream, F f,
+                const char* name) {
+    if (int rc = check_common(ctx, count, dtype)) return rc;
+    if (count == 0) return EXB_OK;
+    EXB_REQUIRE(x && y, "%s: null buffer", name);
+    EXB_REQUIRE(aligned16(x) && aligned16(y), "%s: buffers must be 16-byte aligned", name);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == EXB_F16) {
+        int grid = stream_grid(ctx, count / 8 + 1, kThreads);
+        map1_kernel<__half, F><<<grid, kThreads, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), count, f);
+    } else {
+        int grid = stream_grid(ctx, count / 4 + 1, kThreads);
+        map1_kernel<float, F><<<grid, kThreads, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), count, f);
+    }
+    return after_launch(name);
+}
+
+}  // namespace
+}  // namespace exb
+
+using namespace exb;
+
+extern "C" int exb_relu_fwd(exb_ctx* ctx, const void* x, void* y, int64_t count, int dtype, void* stream) {
+    return launch_map1(ctx, x, y, count, dtype, stream, ReluFn{}, "exb_relu_fwd");
+}
+
+extern "C" int exb_activation_fwd(exb_ctx* ctx, int act, const void* x, void* y, int64_t count,
+                                  int dtype, void* stream) {
+    if (!act_supported(act)) return fail(EXB_ERR_UNSUPPORTED, "activation type %d is not implemented", act);
+    return launch_map1(ctx, x, y, count, dtype, stream, ActFn{act}, "exb_activation_fwd");
+}
+
+extern "C" int exb_binaryop_scalar_fwd(exb_ctx* ctx, int op, const void* a, float scalar, void* y,
+                                       int64_t count, int dtype, void* stream) {
+    if (op < 0 || op > 3) return fail(EXB_ERR_UNSUPPORTED, "binary op %d is not implemented", op);
+    return launch_map1(ctx, a, y, count, dtype, stream, BinScalarFn{op, scalar}, "exb_binaryop_scalar_fwd");
+}
+
+extern "C" int exb_binaryop_fwd(exb_ctx* ctx, int op, const void* a, const void* b, void* y,
+                                int64_t count, int dtype, void* stream) {
+    if (int rc = check_common(ctx, count, dtype)) return rc;
+    if (op < 0 || op > 3) return fail(EXB_ERR_UNSUPPORTED, "binary op %d is not implemented", op);
+    if (count == 0) return EXB_OK;
+    EXB_REQUIRE(a && b && y, "exb_binaryop_fwd: null buffer");
+    EXB_REQUIRE(aligned16(a) && aligned16(b) && aligned16(y), "exb_binaryop_fwd: buffers must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == EXB_F16) {
+        int grid = stream_grid(ctx, count / 8 + 1, kThreads);
+        map2_kernel<__half, BinFn><<<grid, kThreads, 0, st>>>(static_cast<const __half*>(a), static_cast<const __half*>(b),
+                                                              static_cast<__half*>(y), count, BinFn{op});
+    } else {
+        int grid = stream_grid(ctx, count / 4 + 1, kThreads);
+        map2_kernel<float, BinFn><<<grid, kThreads, 0, st>>>(static_cast<const float*>(a), static_cast<const float*>(b),
+                                                             static_cast<float*>(y), count, BinFn{op});
+    }
+    return after_launch("exb_binaryop_fwd");
+}
+
+extern "C" int exb_eltwise_fwd(exb_ctx* ctx, int type, int n_in, const void* const* xs,
+                               const float* coeffs, void* y, int64_t count, int dtype, void* stream) {
+    if (int rc = check_common(ctx, count, dtype)) return rc;
+    if (type < 0 || type > 2) return fail(EXB_ERR_UNSUPPORTED, "eltwise type %d is not implemented", type);
+    EXB_REQUIRE(n_in >= 2, "eltwise needs at least 2 inputs, got %d", n_in);
+    if (n_in > kMaxEltwiseInputs)
+        return fail(EXB_ERR_UNSUPPORTED, "eltwise supports at most %d inputs, got %d", kMaxEltwiseInputs, n_in);
+    EXB_REQUIRE(xs && y, "exb_eltwise_fwd: null buffer");
+    if (count == 0) return EXB_OK;
+    EltwiseArgs args;
+    args.n_in = n_in;
+    args.type = type;
+    for (int i = 0; i < n_in; ++i) {
+        EXB_REQUIRE(xs[i] && aligned16(xs[i]), "exb_eltwise_fwd: input %d null or not 16-byte aligned", i);
+        args.x[i] = xs[i];
+        args.coeff[i] = coeffs ? coeffs[i] : 1.0f;
+    }
+    EXB_REQUIRE(aligned16(y), "exb_eltwise_fwd: output must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == EXB_F16) {
+        int grid = stream_grid(ctx, count / 8 + 1, kThreads);
+        eltwise_kernel<__half><<<grid, kThreads, 0, st>>>(args, static_cast<__half*>(y), count);
+    } else {
+        int grid = stream_grid(ctx, count / 4 + 1, kThreads);
+        eltwise_kernel<float><<<grid, kThreads, 0, st>>>(args, static_cast<float*>(y), count);
+    }
+    return after_launch("exb_eltwise_fwd");
+}
+
+extern "C" int exb_quantize_fwd(exb_ctx* ctx, const void* x, int in_dtype, int8_t* q, int64_t count,
+                                float scale, int rounding, void* stream) {
+    if (int rc = check_common(ctx, count, in_dtype)) return rc;
+    if (count == 0) return EXB_OK;
+    EXB_REQUIRE(x && q, "exb_quantize_fwd: null buffer");
+    EXB_REQUIRE(aligned16(x) && aligned16(q), "exb_quantize_fwd: buffers must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = stream_grid(ctx, count / 16 + 1, kThreads);
+    if (in_dtype == EXB_F16)
+        quantize_kernel<__half><<<grid, kThreads, 0, st>>>(static_cast<const __half*>(x), q, count, scale, rounding);
+    else
+        quantize_kernel<float><<<grid, kThreads, 0, st>>>(static_cast<const float*>(x), q, count, scale, rounding);
+    return after_launch("exb_quantize_fwd");
+}
+
+extern "C" int exb_dequantize_fwd(exb_ctx* ctx, const int8_t* q, void* y, int out_dtype, int64_t count,
+                                  float scale, void* stream) {
+    if (int rc = check_common(ctx, count, out_dtype)) return rc;
+    if (count == 0) return EXB_OK;
+    EXB_REQUIRE(q && y, "exb_dequantize_fwd: null buffer");
+    EXB_REQUIRE(aligned16(q) && aligned16(y), "exb_dequantize_fwd: buffers must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = stream_grid(ctx, count / 16 + 1, kThreads);
+    if (out_dtype == EXB_F16)
+        dequantize_kernel<__half><<<grid, kThreads, 0, st>>>(q, static_cast<__half*>(y), count, scale);
+    else
+        dequantize_kernel<float><<<grid, kThreads, 0, st>>>(q, static_cast<float*>(y), count, scale);
+    return after_launch("exb_dequantize_fwd");
+}

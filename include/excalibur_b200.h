@@ -1,0 +1,250 @@
+/*
+ * excalibur_b200 - C ABI of the B200 (sm_100a) CNN forward hot path.
+ *
+ * One shared library (libexcalibur_b200.so), extern "C", plain pointers and sizes only.
+ * Every entry point returns an int status (0 = ok, negative = error, see exb_status); none
+ * aborts the process.  Device buffers are owned by the caller, activations are dense NHWC
+ * (channels innermost) in fp16 or int8, `stream` is a cudaStream_t passed as void* (NULL =
+ * the legacy default stream, which is what the reference uses everywhere).
+ *
+ * Each function names the reference interface it stands in for (paths are relative to the
+ * reference project's root).  The C++ classes in excalibur_b200/csrc/host/ mirror
+ * glasssix::excalibur::operation<Dtype> on top of this ABI.
+ */
+#ifndef EXCALIBUR_B200_H_
+#define EXCALIBUR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define EXB_API __attribute__((visibility("default")))
+#else
+#define EXB_API
+#endif
+
+typedef enum exb_status {
+    EXB_OK = 0,
+    EXB_ERR_BAD_ARG = -1,      /* null pointer, non-positive size, misaligned buffer ... */
+    EXB_ERR_UNSUPPORTED = -2,  /* valid request this build has no kernel for */
+    EXB_ERR_CUDA = -3,         /* a CUDA runtime / driver call failed */
+    EXB_ERR_TIMEOUT = -4,      /* a bounded device-side wait ran out (kernel error word set) */
+    EXB_ERR_NOMEM = -5
+} exb_status;
+
+typedef enum exb_dtype {
+    EXB_F16 = 0,  /* IEEE half, the reference's `unsigned short` tensors */
+    EXB_I8 = 1,   /* signed char */
+    EXB_F32 = 2,
+    EXB_I32 = 3   /* raw int32 accumulators (parity / debugging output of the int8 conv) */
+} exb_dtype;
+
+/* 0..5: conv key 9 of the reference (src/Excalibur/operation_general_conv.cpp:127-272);
+ * 103/104 are activations the reference expresses as separate ops (Clip 0..6; Sigmoid+Mul). */
+typedef enum exb_act {
+    EXB_ACT_NONE = 0,
+    EXB_ACT_RELU = 1,
+    EXB_ACT_RELU6_QUIRK = 3, /* reference behaviour: x > 6 -> 0 */
+    EXB_ACT_SIGMOID = 4,
+    EXB_ACT_RELU6 = 103,
+    EXB_ACT_SILU = 104
+} exb_act;
+
+typedef struct exb_ctx exb_ctx;                   /* per-device context */
+typedef struct exb_conv_weights exb_conv_weights; /* packed, device-resident conv weights */
+typedef struct exb_dw_weights exb_dw_weights;     /* packed depthwise weights */
+
+/* ---------------------------------------------------------------------------------------
+ * Context.  Stands in for the per-pipeline device selection + cublasCreate of the reference
+ * (src/Excalibur/pipeline.cpp:37-48); binds AFTER selecting the device.
+ * ------------------------------------------------------------------------------------- */
+EXB_API int exb_ctx_create(int device, exb_ctx** out);
+EXB_API int exb_ctx_destroy(exb_ctx* ctx);
+/* Message of the last failing call on this thread (never NULL). */
+EXB_API const char* exb_last_error_string(void);
+/* Library version string, e.g. "0.1.0". (pipeline<Dtype>::version, include/Excalibur/pipeline.hpp:41) */
+EXB_API const char* exb_version(void);
+/* Number of SMs of the context's device (grid sizing of persistent kernels). */
+EXB_API int exb_ctx_sm_count(const exb_ctx* ctx, int* out);
+/* Wait for `stream` and report what the kernels launched on it left behind: EXB_OK,
+ * EXB_ERR_CUDA (sticky CUDA error) or EXB_ERR_TIMEOUT when a kernel's bounded device-side wait
+ * ran out (the error word is cleared by this call).  The reference has no counterpart: its
+ * kernels run on the legacy stream and errors surface as CHECK failures that terminate the
+ * process (include/Primitives/logger.hpp:101-118). */
+EXB_API int exb_ctx_sync_check(exb_ctx* ctx, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Layout / precision converts at the API edge.  The reference keeps NCHW fp32 tensors
+ * between ops (include/Primitives/tensor.hpp:15-173) and converts NHWC->NCHW on the CPU
+ * (src/Primitives/tensor.cpp:334-377); these kernels move between that edge format and the
+ * NHWC fp16 / int8 layout the kernels use.  c_stride >= C is the physical channel count of
+ * the NHWC buffer (padding channels are written as zero / ignored on read).
+ * For EXB_I8, q = sat8(round(x * scale)) with rounding 0 = half away from zero (reference
+ * float32_to_int8, src/Primitives/simd_types.cpp:140-152) or 1 = half to even.
+ * ------------------------------------------------------------------------------------- */
+EXB_API int exb_nchw_f32_to_nhwc(exb_ctx* ctx, const float* x_nchw, void* y_nhwc, int dtype,
+                                 int N, int C, int H, int W, int c_stride, float scale,
+                                 int rounding, void* stream);
+EXB_API int exb_nhwc_to_nchw_f32(exb_ctx* ctx, const void* x_nhwc, int dtype, float* y_nchw,
+                                 int N, int C, int H, int W, int c_stride, float scale,
+                                 void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Dense convolution forward.  Stands in for operation_convolution::forward_{cpu,gpu}_{f32,
+ * f16,i8} (src/Excalibur/operation_convolution.cpp:251-409, src/Excalibur/cuda/
+ * operation_convolution.cu:118-262,338-394,484-549): implicit GEMM on the tensor cores, with
+ * what the reference runs as separate passes fused into the epilogue:
+ *   v  = acc * scale[c] + bias[c]      (int8: scale[c] = 1/(wscale[c]*act_scale), exactly the
+ *                                       reference's dequantize scale; fp16: scale = 1)
+ *   v += residual                      (the Eltwise/BinaryOp add that follows in ResNet graphs)
+ *   v  = act(v)                        (conv key 9, or the ReLU op that follows)
+ *   y  = convert(v)                    (fp16 / fp32, or int8 q = sat8(rne(v*out_scale)), i.e.
+ *                                       the NEXT int8 conv's input quantisation)
+ *   y2 = optional second copy in another dtype (e.g. fp16 skip + int8 for the next conv)
+ * ------------------------------------------------------------------------------------- */
+typedef struct exb_conv_desc {
+    int32_t N, H, W;        /* input batch / height / width */
+    int32_t Cin, Cout;      /* logical channels */
+    int32_t cin_stride;     /* physical channels of x (NHWC), 0 => Cin; >= Cin */
+    int32_t cout_stride;    /* physical channels of y / y2 / residual, 0 => Cout */
+    int32_t kh, kw;
+    int32_t stride_h, stride_w;
+    int32_t pad_t, pad_b, pad_l, pad_r;
+    int32_t dilation;       /* only 1 is supported (the reference's forward ignores it too) */
+    int32_t group;          /* 1 for the tensor-core path; other values use the direct kernel */
+    int32_t in_dtype;       /* EXB_F16 or EXB_I8 */
+    int32_t out_dtype;      /* EXB_F16, EXB_I8, EXB_F32 or (int8 input only) EXB_I32 */
+    int32_t out2_dtype;     /* -1 = no second output, else EXB_F16 or EXB_I8 */
+    int32_t res_dtype;      /* -1 = no residual, else EXB_F16 */
+    int32_t act;            /* exb_act */
+    float out_scale;        /* multiplier used when out_dtype == EXB_I8 */
+    float out2_scale;       /* multiplier used when out2_dtype == EXB_I8 */
+    int32_t impl;           /* 0 = auto (tensor cores when eligible), 1 = force direct kernel */
+} exb_conv_desc;
+
+/* Output spatial size: (in + pad_a + pad_b - k) / stride + 1
+ * (src/Excalibur/operation_convolution.cpp:270-273). */
+EXB_API int exb_conv_out_dims(const exb_conv_desc* d, int* OH, int* OW);
+
+/* Weight pre-transform, the analogue of the reference's *_tr_kernel repacks done once in
+ * init_weights (src/Excalibur/operation_convolution.cpp:88-98,412-467,873-971).  Inputs are
+ * HOST pointers in the reference's on-disk layout: OIHW weights [Cout][Cin/group][kh][kw],
+ * bias[Cout] or NULL.  fp16 variant converts fp32 -> fp16 (round to nearest even).
+ * int8 variant also takes the per-output-channel weight scale table (n_wscale == Cout or 1)
+ * and the activation scale of this conv's input, and forms the dequantise multiplier
+ * 1.0f / (wscale * act_scale) (0 when |wscale| <= 1e-6) in fp32 on the host exactly as
+ * src/Excalibur/operation_convolution.cpp:397-404 does. */
+EXB_API int exb_conv_weights_pack_f16(exb_ctx* ctx, const exb_conv_desc* d, const float* w_oihw,
+                                      const float* bias, exb_conv_weights** out);
+EXB_API int exb_conv_weights_pack_i8(exb_ctx* ctx, const exb_conv_desc* d, const int8_t* w_oihw,
+                                     const float* bias, const float* wscale, int n_wscale,
+                                     float act_scale, exb_conv_weights** out);
+EXB_API int exb_conv_weights_destroy(exb_conv_weights* w);
+
+/* x: NHWC in_dtype [N][H][W][cin_stride]; y (and y2, residual): NHWC [N][OH][OW][cout_stride].
+ * residual / y2 may be NULL when the descriptor says so.  All device pointers, 16-byte aligned. */
+EXB_API int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* x,
+                           const exb_conv_weights* w, const void* residual, void* y, void* y2,
+                           void* stream);
+/* Which kernel exb_conv2d_fwd would run for this descriptor: 1 = tcgen05 implicit GEMM,
+ * 0 = direct kernel; negative = error. */
+EXB_API int exb_conv2d_uses_tensor_cores(const exb_conv_desc* d);
+
+/* ---------------------------------------------------------------------------------------
+ * Depthwise convolution forward.  Stands in for operation_convolutiondepthwise::forward_*
+ * (src/Excalibur/operation_convolutiondepthwise.cpp:18-222, src/Excalibur/cuda/
+ * operation_convolutiondepthwise.cu:12-93,146-229).  fp32 math on fp16 or int8 activations;
+ * the reference's int8 variant likewise dequantises the WEIGHTS once and computes in fp32
+ * (operation_convolutiondepthwise.cpp:184-222).  in_scale multiplies int8 inputs back to real
+ * values (1/act_scale); out_scale is the consumer's quantisation multiplier.
+ * ------------------------------------------------------------------------------------- */
+typedef struct exb_dwconv_desc {
+    int32_t N, H, W, C;
+    int32_t c_stride;       /* physical channels of x and y, 0 => C */
+    int32_t kh, kw, stride_h, stride_w;
+    int32_t pad_t, pad_b, pad_l, pad_r;
+    int32_t in_dtype;       /* EXB_F16 or EXB_I8 */
+    int32_t out_dtype;      /* EXB_F16 or EXB_I8 */
+    int32_t act;
+    float in_scale;         /* int8 input: real = q * in_scale */
+    float out_scale;        /* int8 output: q = sat8(rne(v * out_scale)) */
+} exb_dwconv_desc;
+
+/* w: HOST fp32 [C][kh][kw] (the reference's OIHW with Cin/group == 1), bias[C] or NULL. */
+EXB_API int exb_dw_weights_pack(exb_ctx* ctx, const exb_dwconv_desc* d, const float* w,
+                                const float* bias, exb_dw_weights** out);
+EXB_API int exb_dw_weights_destroy(exb_dw_weights* w);
+EXB_API int exb_dwconv2d_fwd(exb_ctx* ctx, const exb_dwconv_desc* d, const void* x,
+                             const exb_dw_weights* w, void* y, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Pooling forward.  Stands in for operation_pooling::forward_* (src/Excalibur/
+ * operation_pooling.cpp:80-309, src/Excalibur/cuda/operation_pooling.cu:15-171,276-434) with
+ * the CPU path's rules: max ignores padding; average divides by the window clipped to
+ * H+pad_bottom / W+pad_right, or by the valid tap count when count_include_pad == 0;
+ * pad_mode 0 = ceil, 1 = floor output size; global_pool pools the whole map.
+ * A second, int8 copy of the result (q = sat8(rne(v*out2_scale))) can be written at once.
+ * ------------------------------------------------------------------------------------- */
+typedef struct exb_pool_desc {
+    int32_t N, H, W, C;
+    int32_t c_stride;       /* physical channels, 0 => C */
+    int32_t type;           /* 0 max, 1 average */
+    int32_t kh, kw, stride_h, stride_w;
+    int32_t pad_t, pad_b, pad_l, pad_r;
+    int32_t global_pool;
+    int32_t pad_mode;
+    int32_t count_include_pad;
+    int32_t dtype;          /* EXB_F16, EXB_I8 (max only) or EXB_F32: x and y */
+    int32_t out2_dtype;     /* -1 or EXB_I8 */
+    float out2_scale;
+} exb_pool_desc;
+
+EXB_API int exb_pool_out_dims(const exb_pool_desc* d, int* PH, int* PW);
+EXB_API int exb_pool2d_fwd(exb_ctx* ctx, const exb_pool_desc* d, const void* x, void* y,
+                           void* y2, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Element-wise ops on `count` contiguous elements of dtype EXB_F16 or EXB_F32.
+ * exb_eltwise_fwd   - operation_eltwise (src/Excalibur/operation_eltwise.cpp:42-94,
+ *                     cuda/operation_eltwise.cu:29-163): type 0 PROD, 1 SUM with coeffs
+ *                     (NULL => all 1), 2 MAX over n_in >= 2 inputs, ONE pass.
+ * exb_binaryop_fwd  - operation_binaryop equal-shape path (src/Excalibur/
+ *                     operation_binaryop.cpp:74-84, cuda/operation_binaryop.cu:94-102):
+ *                     op 0 add, 1 sub, 2 mul, 3 div.
+ * exb_binaryop_scalar_fwd - its with_scalar mode (operation_binaryop.cpp:389-409).
+ * exb_relu_fwd      - operation_relu (src/Excalibur/operation_relu.cpp:31-81,
+ *                     cuda/operation_relu.cu:13-73).
+ * exb_activation_fwd - the conv suffix activation as a standalone pass
+ *                     (operation_general_conv.cpp:127-272).
+ * ------------------------------------------------------------------------------------- */
+EXB_API int exb_eltwise_fwd(exb_ctx* ctx, int type, int n_in, const void* const* xs,
+                            const float* coeffs, void* y, int64_t count, int dtype,
+                            void* stream);
+EXB_API int exb_binaryop_fwd(exb_ctx* ctx, int op, const void* a, const void* b, void* y,
+                             int64_t count, int dtype, void* stream);
+EXB_API int exb_binaryop_scalar_fwd(exb_ctx* ctx, int op, const void* a, float scalar, void* y,
+                                    int64_t count, int dtype, void* stream);
+EXB_API int exb_relu_fwd(exb_ctx* ctx, const void* x, void* y, int64_t count, int dtype,
+                         void* stream);
+EXB_API int exb_activation_fwd(exb_ctx* ctx, int act, const void* x, void* y, int64_t count,
+                               int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Quantise / dequantise passes.  Stand in for quantize_float32_to_int8 /
+ * dequantize_int32_to_float32 (src/Excalibur/operation_general_conv.cpp:584-941) and the
+ * GPU quant kernels (src/Excalibur/cuda/operation_convolution.cu:449-481).  Per-tensor scale.
+ * rounding 0 = half away from zero (reference), 1 = half to even.
+ * ------------------------------------------------------------------------------------- */
+EXB_API int exb_quantize_fwd(exb_ctx* ctx, const void* x, int in_dtype, int8_t* q,
+                             int64_t count, float scale, int rounding, void* stream);
+EXB_API int exb_dequantize_fwd(exb_ctx* ctx, const int8_t* q, void* y, int out_dtype,
+                               int64_t count, float scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXCALIBUR_B200_H_ */

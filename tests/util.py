@@ -1,0 +1,56 @@
+"""Helpers shared by the parity tests: seeded data and NCHW/NHWC plumbing."""
+import numpy as np
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+def to_nhwc(a, c_stride=None):
+    """NCHW numpy -> NHWC numpy, optionally zero-padding the channel dimension."""
+    a = np.ascontiguousarray(np.transpose(a, (0, 2, 3, 1)))
+    if c_stride and c_stride > a.shape[3]:
+        pad = np.zeros(a.shape[:3] + (c_stride - a.shape[3],), a.dtype)
+        a = np.concatenate([a, pad], axis=3)
+    return np.ascontiguousarray(a)
+
+
+def to_nchw(a, C=None):
+    a = np.transpose(a, (0, 3, 1, 2))
+    if C is not None:
+        a = a[:, :C]
+    return np.ascontiguousarray(a)
+
+
+def dev(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+def f16_round(a):
+    """Round fp32 data to fp16 and back, so the oracle sees exactly what the kernel sees."""
+    return np.asarray(a, np.float32).astype(np.float16).astype(np.float32)
+
+
+def assert_close_f16(y, ref, rel=1e-2, what=""):
+    """fp16 parity bar: |y - ref| <= rel*|ref| + 1e-3*max|ref| (the 1e-2 relative tolerance
+    against the fp32 reference, with an absolute floor for values that cancel to ~0)."""
+    y = np.asarray(y, np.float32)
+    ref = np.asarray(ref, np.float32)
+    assert y.shape == ref.shape, (y.shape, ref.shape)
+    tol = rel * np.abs(ref) + 1e-3 * max(float(np.abs(ref).max()), 1e-6)
+    bad = np.abs(y - ref) > tol
+    assert not bad.any(), "%s: %d of %d elements off, worst abs err %g" % (
+        what, int(bad.sum()), bad.size, float(np.abs(y - ref).max()))
+
+
+def quant_weights(w):
+    """Symmetric per-output-channel int8 weights, reference convention ws = 127/max|w|."""
+    cout = w.shape[0]
+    ws = (127.0 / np.abs(w).reshape(cout, -1).max(axis=1)).astype(np.float32)
+    wq = np.clip(np.rint(w * ws[:, None, None, None]), -127, 127).astype(np.int8)
+    return wq, ws
