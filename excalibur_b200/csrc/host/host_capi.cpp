@@ -1,0 +1,186 @@
+// C entry points of the host layer (include/excalibur_b200_host.h).
+#include "../../../include/excalibur_b200_host.h"
+
+#include <cstring>
+#include <sstream>
+
+#include "ops.hpp"
+#include "pipeline.hpp"
+
+using namespace glasssix;
+using namespace glasssix::excalibur;
+
+namespace {
+thread_local std::string g_err = "no error";
+
+void throwing_handler(const std::string& msg) { throw fatal_error(msg); }
+
+struct fatal_guard {
+    fatal_handler_t prev;
+    fatal_guard() : prev(get_fatal_handler()) { set_fatal_handler(throwing_handler); }
+    ~fatal_guard() { set_fatal_handler(prev); }
+};
+
+template <typename F>
+int guarded(F f) {
+    fatal_guard g;
+    try {
+        return f();
+    } catch (const fatal_error& e) {
+        g_err = e.what();
+        return EXB_HOST_FATAL;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return EXB_HOST_FATAL;
+    }
+}
+
+struct host_pipeline {
+    std::unique_ptr<pipeline<float>> net;
+    pipeline<float>::result_map outputs;
+    std::vector<std::string> names;
+};
+
+int copy_out(const std::shared_ptr<memory::tensor<float>>& t, float* out, int64_t cap, int* shape4) {
+    if (!t) {
+        g_err = "no such feature map (or it was fused away)";
+        return EXB_ERR_BAD_ARG;
+    }
+    auto shp = t->data_shape();
+    for (int i = 0; i < 4; ++i) shape4[i] = shp[i];
+    if (!out) return EXB_OK;
+    if ((int64_t)t->count() > cap) {
+        g_err = "output buffer too small";
+        return EXB_ERR_BAD_ARG;
+    }
+    std::memcpy(out, t->cpu_data(), sizeof(float) * (size_t)t->count());
+    return EXB_OK;
+}
+}  // namespace
+
+extern "C" const char* exb_host_last_error(void) { return g_err.c_str(); }
+
+extern "C" int exb_host_registered(const char* class_name) {
+    return operation_reflector<float>::instance().has(class_name) ? 1 : 0;
+}
+
+extern "C" int exb_host_pipeline_create(const char* phai_text, const char* racy_path, int device, void** out) {
+    return guarded([&]() {
+        set_log_quiet(true);
+        std::vector<std::string> lines;
+        std::istringstream ss(phai_text);
+        std::string l;
+        while (std::getline(ss, l)) {
+            while (!l.empty() && (l.back() == '\r' || l.back() == ' ')) l.pop_back();
+            lines.push_back(l);
+        }
+        auto* h = new host_pipeline;
+        h->net.reset(new pipeline<float>(lines, racy_path ? racy_path : "", device));
+        *out = h;
+        return (int)EXB_OK;
+    });
+}
+
+extern "C" int exb_host_pipeline_destroy(void* p) {
+    return guarded([&]() {
+        delete static_cast<host_pipeline*>(p);
+        return (int)EXB_OK;
+    });
+}
+
+extern "C" int exb_host_pipeline_set_option(void* p, const char* key, int value) {
+    auto* h = static_cast<host_pipeline*>(p);
+    const std::string k = key;
+    if (k == "fusion") h->net->set_fusion(value != 0);
+    else if (k == "cuda_graph") h->net->set_cuda_graph(value != 0);
+    else if (k == "profile") value ? h->net->enable_profiler() : h->net->disable_profiler();
+    else {
+        g_err = "unknown option " + k;
+        return EXB_ERR_BAD_ARG;
+    }
+    return EXB_OK;
+}
+
+extern "C" int exb_host_pipeline_forward(void* p, const float* input, int N, int C, int H, int W) {
+    return guarded([&]() {
+        auto* h = static_cast<host_pipeline*>(p);
+        // a tensor that borrows the caller's host memory
+        auto t = std::shared_ptr<memory::tensor<float>>(
+            new memory::tensor<float>(std::vector<int>{N, C, H, W}, 0, memory::NCHW, nullptr));
+        t->data()->set_external_cpu_data(const_cast<float*>(input));
+        h->outputs = h->net->forward(t);
+        h->names.clear();
+        for (auto& n : h->net->output_names()) h->names.push_back(n);
+        return (int)EXB_OK;
+    });
+}
+
+extern "C" int exb_host_pipeline_num_outputs(void* p) { return (int)static_cast<host_pipeline*>(p)->names.size(); }
+
+extern "C" int exb_host_pipeline_output_name(void* p, int i, char* buf, int cap) {
+    auto* h = static_cast<host_pipeline*>(p);
+    if (i < 0 || i >= (int)h->names.size() || cap <= 0) return EXB_ERR_BAD_ARG;
+    std::strncpy(buf, h->names[i].c_str(), cap - 1);
+    buf[cap - 1] = 0;
+    return EXB_OK;
+}
+
+extern "C" int exb_host_pipeline_get(void* p, const char* name, float* out, int64_t cap, int* shape4) {
+    return guarded([&]() {
+        auto* h = static_cast<host_pipeline*>(p);
+        auto it = h->outputs.find(name);
+        if (it != h->outputs.end()) return copy_out(it->second, out, cap, shape4);
+        return copy_out(h->net->get_featmap(name), out, cap, shape4);
+    });
+}
+
+extern "C" int exb_host_pipeline_stats(void* p, int* launches, double* device_ms) {
+    auto* h = static_cast<host_pipeline*>(p);
+    if (launches) *launches = h->net->launches_last_forward();
+    if (device_ms) *device_ms = h->net->device_ms_last_forward();
+    return EXB_OK;
+}
+
+extern "C" int exb_host_pipeline_dump_profile(void* p, const char* path) {
+    return static_cast<host_pipeline*>(p)->net->dump_profile(path) ? EXB_OK : EXB_ERR_BAD_ARG;
+}
+
+extern "C" int exb_host_op_run(const char* type, const char* params, const char* racy_path, int device, int n_in,
+                               const float* const* inputs, const int* shapes, float* out, int64_t cap,
+                               int* out_shape4) {
+    return guarded([&]() {
+        set_log_quiet(true);
+        CUDA_CHECK(cudaSetDevice(device));
+        std::vector<std::string> ins, outs{"out"};
+        for (int i = 0; i < n_in; ++i) ins.push_back("in" + std::to_string(i));
+        operation_param prm(type, std::string(type) + "_0", n_in, 1, ins, outs, false, false, false, false, device,
+                            params ? params : "");
+        auto op = operation_reflector<float>::instance().create_object(prm);
+        if (racy_path && racy_path[0]) {
+            FILE* fp = fopen(racy_path, "rb");
+            if (!fp) LOG(FATAL) << "Cannot open " << racy_path;
+            op->init_weights(fp);
+            fclose(fp);
+        } else {
+            op->init_weights();
+        }
+        exb_ctx* ctx = nullptr;
+        exb_check(exb_ctx_create(device, &ctx), "exb_ctx_create");
+        std::vector<std::shared_ptr<memory::tensor<float>>> bottoms, tops(1);
+        for (int i = 0; i < n_in; ++i) {
+            std::vector<int> shp(shapes + 4 * i, shapes + 4 * i + 4);
+            auto t = std::shared_ptr<memory::tensor<float>>(new memory::tensor<float>(shp, device, memory::NCHW, nullptr));
+            t->copy_from(inputs[i], sizeof(float) * (size_t)t->count());
+            bottoms.push_back(t);
+        }
+        op->forward_gpu(ctx, bottoms, tops);
+        int rc = exb_ctx_sync_check(ctx, nullptr);
+        if (rc == EXB_OK) rc = copy_out(tops[0], out, cap, out_shape4);
+        else g_err = exb_last_error_string();
+        tops.clear();
+        bottoms.clear();
+        op.reset();
+        exb_ctx_destroy(ctx);
+        return rc;
+    });
+}

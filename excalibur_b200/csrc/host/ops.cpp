@@ -1,0 +1,746 @@
+// Operation classes of the CNN forward hot path on top of the C ABI.  Each class keeps the
+// reference's parameter keys, weight-file reading order and tensor semantics (fp32 NCHW tensors
+// between ops for operation<float>; int8 only inside the convolution), and runs its arithmetic
+// through libexcalibur_b200's kernels on the legacy default stream, like the reference's GPU path.
+#include "ops.hpp"
+
+#include <cmath>
+#include <random>
+
+namespace glasssix {
+namespace excalibur {
+
+void exb_check(int rc, const char* what) {
+    if (rc != EXB_OK) LOG(FATAL) << what << " failed (" << rc << "): " << exb_last_error_string();
+}
+
+device_scratch::~device_scratch() {
+    if (ptr_) cudaFree(ptr_);
+}
+void* device_scratch::get(size_t bytes, int device) {
+    if (bytes > cap_) {
+        if (ptr_) cudaFree(ptr_);
+        ptr_ = nullptr;
+        CUDA_CHECK(cudaSetDevice(device));
+        CUDA_CHECK(cudaMalloc(&ptr_, bytes));
+        cap_ = bytes;
+    }
+    return ptr_;
+}
+
+namespace {
+int round_up(int a, int b) { return (a + b - 1) / b * b; }
+
+template <typename T>
+std::shared_ptr<memory::tensor<T>> make_tensor(const std::vector<int>& shape, int device, memory::orderType order,
+                                               memory::pool_allocator<T>* alloc = nullptr) {
+    return std::shared_ptr<memory::tensor<T>>(new memory::tensor<T>(shape, device, order, alloc));
+}
+
+void read_or_die(void* dst, size_t bytes, FILE* fp, const char* what) {
+    if (bytes && fread(dst, 1, bytes, fp) != bytes) LOG(FATAL) << "weight file ended while reading " << what;
+}
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// general conv: parameter parsing
+// ---------------------------------------------------------------------------------------------
+template <typename Dtype>
+operation_general_conv<Dtype>::operation_general_conv(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        const int v = std::atoi(kv.second.c_str());
+        switch (kv.first) {
+        case 0: output_channel_ = v; break;
+        case 1: kernel_size_w_ = kernel_size_h_ = v; break;
+        case 2: dilation_w_ = dilation_h_ = v; break;
+        case 3: stride_w_ = stride_h_ = v; break;
+        case 4: pad_left_ = pad_right_ = pad_top_ = pad_bottom_ = v; break;
+        case 5: bias_term_ = v != 0; break;
+        case 6: weight_data_size_ = v; break;
+        case 7: group_ = v; break;
+        case 8:
+            int8_scale_term_ = v != 0;
+            this->params_.set_int8_quantization(int8_scale_term_);
+            break;
+        case 9: activation_type_ = v; break;
+        case 10: NOT_IMPLEMENTED; break;
+        case 11: kernel_size_h_ = v; break;
+        case 12: dilation_h_ = v; break;
+        case 13: stride_h_ = v; break;
+        case 14: pad_top_ = v; break;
+        case 15: pad_right_ = v; break;
+        case 16: pad_bottom_ = v; break;
+        case 17: impl_type_ = v; break;
+        case 18: case 19: case 20: case 21: break;  // output padding / dims: deconvolution only
+        case -23330: break;
+        default: LOG(FATAL) << "Un-supported Convolution Attribution " << kv.first;
+        }
+    }
+    CHECK_GT(output_channel_, 0);
+    CHECK_GT(group_, 0);
+    CHECK_EQ(output_channel_ % group_, 0);
+    CHECK(kernel_size_h_ > 0 && kernel_size_w_ > 0) << "convolution kernel size missing";
+    const int per_group = (output_channel_ / group_) * kernel_size_h_ * kernel_size_w_;
+    if (weight_data_size_ > 0) {
+        CHECK_EQ(weight_data_size_ % (per_group * group_), 0) << "weight_data_size does not match the kernel shape";
+        input_channel_ = weight_data_size_ / (per_group * group_) * group_;
+    }
+}
+INSTANCE_CLASS(operation_general_conv);
+
+// ---------------------------------------------------------------------------------------------
+// dense convolution
+// ---------------------------------------------------------------------------------------------
+template <typename Dtype>
+operation_convolution<Dtype>::operation_convolution(const operation_param& param)
+    : operation_general_conv<Dtype>(param) {}
+
+template <typename Dtype>
+operation_convolution<Dtype>::~operation_convolution() {
+    for (auto& e : packed_) exb_conv_weights_destroy(e.w);
+}
+
+// .racy record: int32 tag; tag 0: fp32 OIHW weights (+ bias); tag 871224: int8 weights padded to
+// a multiple of 4 bytes (+ fp32 bias), per-output-channel weight scales, one activation scale.
+template <typename Dtype>
+int operation_convolution<Dtype>::init_weights(FILE* fp) {
+    int tag = 0;
+    read_or_die(&tag, sizeof(int), fp, "the quantize tag");
+    const int dev = this->params_.device_;
+    int mem = 0;
+    if (tag == 0) {
+        this->weights_f32_.push_back(make_tensor<float>({this->weight_data_size_}, dev, memory::NCHW));
+        read_or_die(this->weights_f32_[0]->mutable_cpu_data(), sizeof(float) * this->weight_data_size_, fp, "weights");
+        mem += this->weight_data_size_ * sizeof(float);
+        if (this->bias_term_) {
+            this->weights_f32_.push_back(make_tensor<float>({this->output_channel_}, dev, memory::NCHW));
+            read_or_die(this->weights_f32_[1]->mutable_cpu_data(), sizeof(float) * this->output_channel_, fp, "bias");
+            mem += this->output_channel_ * sizeof(float);
+        }
+    } else if (tag == 871224) {
+        const size_t aligned = ((size_t)this->weight_data_size_ + 3) & ~(size_t)3;
+        this->weights_i8_.push_back(make_tensor<signed char>({(int)aligned}, dev, memory::NCHW));
+        read_or_die(this->weights_i8_[0]->mutable_cpu_data(), aligned, fp, "int8 weights");
+        mem += (int)aligned;
+        if (this->bias_term_) {
+            this->weights_f32_.push_back(make_tensor<float>({1}, dev, memory::NCHW));   // slot 0 unused, as in the reference
+            this->weights_f32_.push_back(make_tensor<float>({this->output_channel_}, dev, memory::NCHW));
+            read_or_die(this->weights_f32_[1]->mutable_cpu_data(), sizeof(float) * this->output_channel_, fp, "bias");
+            mem += this->output_channel_ * sizeof(float);
+        }
+        this->weights_scaletable_i8_ = make_tensor<float>({this->output_channel_}, dev, memory::NCHW);
+        read_or_die(this->weights_scaletable_i8_->mutable_cpu_data(), sizeof(float) * this->output_channel_, fp, "weight scales");
+        this->featmap_scaletable_i8_ = make_tensor<float>({1}, dev, memory::NCHW);
+        read_or_die(this->featmap_scaletable_i8_->mutable_cpu_data(), sizeof(float), fp, "activation scale");
+        mem += (this->output_channel_ + 1) * sizeof(float);
+        this->params_.set_int8_quantization(true);
+    } else {
+        NOT_IMPLEMENTED << " (weight record tag " << tag << ")";
+    }
+    return mem;
+}
+
+// Seeded dummy weights: N(0, 0.3) fp32, U[-128,127] int8, from a default-seeded engine.
+template <typename Dtype>
+int operation_convolution<Dtype>::init_weights() {
+    std::default_random_engine e;
+    std::normal_distribution<float> n(0, 0.3);
+    std::uniform_int_distribution<int> u(-128, 127);
+    const int dev = this->params_.device_;
+    int mem = 0;
+    if (!this->params_.int8_quantization_) {
+        this->weights_f32_.push_back(make_tensor<float>({this->weight_data_size_}, dev, memory::NCHW));
+        float* w = this->weights_f32_[0]->mutable_cpu_data();
+        for (int i = 0; i < this->weight_data_size_; ++i) w[i] = n(e);
+        mem += this->weight_data_size_ * sizeof(float);
+        if (this->bias_term_) {
+            this->weights_f32_.push_back(make_tensor<float>({this->output_channel_}, dev, memory::NCHW));
+            float* b = this->weights_f32_[1]->mutable_cpu_data();
+            for (int i = 0; i < this->output_channel_; ++i) b[i] = n(e);
+            mem += this->output_channel_ * sizeof(float);
+        }
+    } else {
+        const size_t aligned = ((size_t)this->weight_data_size_ + 3) & ~(size_t)3;
+        this->weights_i8_.push_back(make_tensor<signed char>({(int)aligned}, dev, memory::NCHW));
+        signed char* w = this->weights_i8_[0]->mutable_cpu_data();
+        for (size_t i = 0; i < aligned; ++i) w[i] = (signed char)u(e);
+        mem += (int)aligned;
+        if (this->bias_term_) {
+            this->weights_f32_.push_back(make_tensor<float>({1}, dev, memory::NCHW));
+            this->weights_f32_.push_back(make_tensor<float>({this->output_channel_}, dev, memory::NCHW));
+            float* b = this->weights_f32_[1]->mutable_cpu_data();
+            for (int i = 0; i < this->output_channel_; ++i) b[i] = n(e);
+            mem += this->output_channel_ * sizeof(float);
+        }
+        this->weights_scaletable_i8_ = make_tensor<float>({this->output_channel_}, dev, memory::NCHW);
+        float* s = this->weights_scaletable_i8_->mutable_cpu_data();
+        for (int i = 0; i < this->output_channel_; ++i) s[i] = n(e);
+        this->featmap_scaletable_i8_ = make_tensor<float>({1}, dev, memory::NCHW);
+        this->featmap_scaletable_i8_->mutable_cpu_data()[0] = n(e);
+        mem += (this->output_channel_ + 1) * sizeof(float);
+    }
+    return mem;
+}
+
+template <typename Dtype>
+float operation_convolution<Dtype>::act_scale() const {
+    CHECK(this->featmap_scaletable_i8_ != nullptr) << "convolution has no activation scale";
+    if (this->featmap_scaletable_i8_->count() != 1)
+        NOT_IMPLEMENTED << " (per-channel activation scales)";
+    return this->featmap_scaletable_i8_->cpu_data()[0];
+}
+
+template <typename Dtype>
+int operation_convolution<Dtype>::exb_activation() const {
+    switch (this->activation_type_) {
+    case 0: return EXB_ACT_NONE;
+    case 1: return EXB_ACT_RELU;
+    case 3: return EXB_ACT_RELU6_QUIRK;
+    case 4: return EXB_ACT_SIGMOID;
+    default: NOT_IMPLEMENTED << " (convolution activation type " << this->activation_type_ << ")";
+    }
+    return EXB_ACT_NONE;
+}
+
+template <typename Dtype>
+exb_conv_desc operation_convolution<Dtype>::base_desc(int N, int H, int W) const {
+    exb_conv_desc d;
+    std::memset(&d, 0, sizeof(d));
+    d.N = N; d.H = H; d.W = W;
+    d.Cin = this->input_channel_; d.Cout = this->output_channel_;
+    d.kh = this->kernel_size_h_; d.kw = this->kernel_size_w_;
+    d.stride_h = this->stride_h_; d.stride_w = this->stride_w_;
+    d.pad_t = this->pad_top_; d.pad_b = this->pad_bottom_; d.pad_l = this->pad_left_; d.pad_r = this->pad_right_;
+    d.dilation = 1;   // the reference's forward ignores keys 2/12 as well
+    d.group = this->group_;
+    d.in_dtype = is_int8() ? EXB_I8 : EXB_F16;
+    d.out_dtype = EXB_F16; d.out2_dtype = -1; d.res_dtype = -1;
+    d.act = EXB_ACT_NONE; d.out_scale = 1.f; d.out2_scale = 1.f; d.impl = 0;
+    return d;
+}
+
+template <typename Dtype>
+exb_conv_weights* operation_convolution<Dtype>::packed(exb_ctx* ctx, const exb_conv_desc& d) {
+    const int cin_stride = d.cin_stride ? d.cin_stride : d.Cin;
+    const int cout_stride = d.cout_stride ? d.cout_stride : d.Cout;
+    for (auto& e : packed_)
+        if (e.in_dtype == d.in_dtype && e.cin_stride == cin_stride && e.cout_stride == cout_stride) return e.w;
+    exb_conv_weights* w = nullptr;
+    const float* bias = this->bias_term_ ? this->weights_f32_[1]->cpu_data() : nullptr;
+    if (d.in_dtype == EXB_I8) {
+        CHECK(is_int8()) << "int8 convolution requested but the weights are fp32";
+        exb_check(exb_conv_weights_pack_i8(ctx, &d, this->weights_i8_[0]->cpu_data(), bias,
+                                           this->weights_scaletable_i8_->cpu_data(),
+                                           this->weights_scaletable_i8_->count(), act_scale(), &w),
+                  "exb_conv_weights_pack_i8");
+    } else {
+        CHECK(!is_int8()) << "fp16 convolution requested but the weights are int8";
+        exb_check(exb_conv_weights_pack_f16(ctx, &d, this->weights_f32_[0]->cpu_data(), bias, &w),
+                  "exb_conv_weights_pack_f16");
+    }
+    packed_.push_back({d.in_dtype, cin_stride, cout_stride, w});
+    return w;
+}
+
+// Stand-alone op semantics of the reference: fp32 NCHW tensor in, fp32 NCHW tensor out.  int8:
+// quantise the input with the conv's activation scale (half away from zero), int8 x int8 -> int32
+// on the tensor cores, y = acc * 1/(ws*fs) + bias, activation - the reference's forward_cpu_i8
+// (src/Excalibur/operation_convolution.cpp:332-409).  fp32: fp16 operands, fp32 accumulation.
+template <typename Dtype>
+void operation_convolution<Dtype>::forward_nchw_f32(exb_ctx* h, const f32_list& bottoms, f32_list& tops, bool int8) {
+    CHECK_EQ(bottoms.size(), (size_t)1);
+    CHECK_EQ(tops.size(), (size_t)1);
+    CHECK(h != nullptr) << "null context";
+    if (bottoms[0]->order() == memory::NHWC) bottoms[0]->convert_order();
+    const int N = bottoms[0]->num(), C = bottoms[0]->channels(), H = bottoms[0]->height(), W = bottoms[0]->width();
+    CHECK_EQ(C, this->input_channel_) << "input channels do not match the weights";
+    const int dev = this->params_.device_;
+    exb_conv_desc d = base_desc(N, H, W);
+    d.in_dtype = int8 ? EXB_I8 : EXB_F16;
+    d.cin_stride = this->group_ == 1 ? round_up(C, int8 ? 32 : 16) : C;
+    d.out_dtype = EXB_F32;
+    d.act = exb_activation();
+    int OH = 0, OW = 0;
+    exb_check(exb_conv_out_dims(&d, &OH, &OW), "exb_conv_out_dims");
+    tops[0] = make_tensor<float>({N, this->output_channel_, OH, OW}, dev, memory::NCHW, bottoms[0]->allocator());
+    if (N == 0) return;
+    const size_t es = int8 ? 1 : 2;
+    void* xin = scratch_in_.get((size_t)N * H * W * d.cin_stride * es, dev);
+    void* yout = scratch_out_.get((size_t)N * OH * OW * this->output_channel_ * sizeof(float), dev);
+    exb_check(exb_nchw_f32_to_nhwc(h, bottoms[0]->gpu_data(), xin, d.in_dtype, N, C, H, W, d.cin_stride,
+                                   int8 ? act_scale() : 1.f, 0, nullptr),
+              "exb_nchw_f32_to_nhwc");
+    exb_check(exb_conv2d_fwd(h, &d, xin, packed(h, d), nullptr, yout, nullptr, nullptr), "exb_conv2d_fwd");
+    exb_check(exb_nhwc_to_nchw_f32(h, yout, EXB_F32, tops[0]->mutable_gpu_data(), N, this->output_channel_, OH, OW,
+                                   this->output_channel_, 1.f, nullptr),
+              "exb_nhwc_to_nchw_f32");
+}
+
+template <typename Dtype>
+void operation_convolution<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    forward_nchw_f32(h, bottoms, tops, false);
+}
+template <typename Dtype>
+void operation_convolution<Dtype>::forward_gpu_i8(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    forward_nchw_f32(h, bottoms, tops, true);
+}
+
+// fp16 tensors: NHWC, channels already padded by the caller to a multiple of 16 when the tensor
+// cores are wanted; no layout conversion at all.
+template <typename Dtype>
+void operation_convolution<Dtype>::forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops) {
+    CHECK_EQ(bottoms.size(), (size_t)1);
+    CHECK_EQ(tops.size(), (size_t)1);
+    if (bottoms[0]->order() != memory::NHWC) NOT_IMPLEMENTED << " (fp16 tensors must be NHWC)";
+    const int N = bottoms[0]->num(), C = bottoms[0]->channels(), H = bottoms[0]->height(), W = bottoms[0]->width();
+    CHECK_EQ(C, this->input_channel_);
+    exb_conv_desc d = base_desc(N, H, W);
+    d.in_dtype = EXB_F16;
+    d.out_dtype = EXB_F16;
+    d.act = exb_activation();
+    int OH = 0, OW = 0;
+    exb_check(exb_conv_out_dims(&d, &OH, &OW), "exb_conv_out_dims");
+    tops[0] = make_tensor<unsigned short>({N, OH, OW, this->output_channel_}, this->params_.device_, memory::NHWC,
+                                          bottoms[0]->allocator());
+    if (N == 0) return;
+    exb_check(exb_conv2d_fwd(h, &d, bottoms[0]->gpu_data(), packed(h, d), nullptr, tops[0]->mutable_gpu_data(),
+                             nullptr, nullptr),
+              "exb_conv2d_fwd");
+}
+INSTANCE_CLASS(operation_convolution);
+REGISTE(operation_convolution);
+
+// ---------------------------------------------------------------------------------------------
+// depthwise convolution
+// ---------------------------------------------------------------------------------------------
+template <typename Dtype>
+operation_convolutiondepthwise<Dtype>::operation_convolutiondepthwise(const operation_param& param)
+    : operation_convolution<Dtype>(param) {}
+
+template <typename Dtype>
+operation_convolutiondepthwise<Dtype>::~operation_convolutiondepthwise() {
+    if (dw_w_) exb_dw_weights_destroy(dw_w_);
+}
+
+template <typename Dtype>
+const float* operation_convolutiondepthwise<Dtype>::dw_weights_f32() {
+    if (!this->is_int8()) return this->weights_f32_[0]->cpu_data();
+    if (dequantized_.empty()) {
+        // w = q * (scale <= 1e-6 ? 0 : 1/scale), per output channel
+        const int per = this->weight_data_size_ / this->output_channel_;
+        dequantized_.resize((size_t)this->weight_data_size_);
+        const signed char* q = this->weights_i8_[0]->cpu_data();
+        const float* s = this->weights_scaletable_i8_->cpu_data();
+        for (int c = 0; c < this->output_channel_; ++c) {
+            const float inv = s[c] <= 1e-6 ? 0.f : 1.f / s[c];
+            for (int i = 0; i < per; ++i) dequantized_[(size_t)c * per + i] = q[(size_t)c * per + i] * inv;
+        }
+    }
+    return dequantized_.data();
+}
+
+template <typename Dtype>
+exb_dwconv_desc operation_convolutiondepthwise<Dtype>::dw_desc(int N, int H, int W, int c_stride) const {
+    exb_dwconv_desc d;
+    std::memset(&d, 0, sizeof(d));
+    d.N = N; d.H = H; d.W = W; d.C = this->output_channel_; d.c_stride = c_stride;
+    d.kh = this->kernel_size_h_; d.kw = this->kernel_size_w_;
+    d.stride_h = this->stride_h_; d.stride_w = this->stride_w_;
+    d.pad_t = this->pad_top_; d.pad_b = this->pad_bottom_; d.pad_l = this->pad_left_; d.pad_r = this->pad_right_;
+    d.in_dtype = EXB_F16; d.out_dtype = EXB_F16; d.act = this->exb_activation();
+    d.in_scale = 1.f; d.out_scale = 1.f;
+    return d;
+}
+
+template <typename Dtype>
+exb_dw_weights* operation_convolutiondepthwise<Dtype>::dw_packed(exb_ctx* ctx, const exb_dwconv_desc& d) {
+    const int cs = d.c_stride ? d.c_stride : d.C;
+    if (dw_w_ && dw_cs_ == cs) return dw_w_;
+    if (dw_w_) exb_dw_weights_destroy(dw_w_);
+    dw_w_ = nullptr;
+    const float* bias = this->bias_term_ ? this->weights_f32_[1]->cpu_data() : nullptr;
+    exb_check(exb_dw_weights_pack(ctx, &d, dw_weights_f32(), bias, &dw_w_), "exb_dw_weights_pack");
+    dw_cs_ = cs;
+    return dw_w_;
+}
+
+template <typename Dtype>
+void operation_convolutiondepthwise<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), (size_t)1);
+    CHECK_EQ(tops.size(), (size_t)1);
+    CHECK_EQ(this->output_channel_, this->group_);
+    if (bottoms[0]->order() == memory::NHWC) bottoms[0]->convert_order();
+    const int N = bottoms[0]->num(), C = bottoms[0]->channels(), H = bottoms[0]->height(), W = bottoms[0]->width();
+    CHECK_EQ(C, this->output_channel_);
+    const int dev = this->params_.device_;
+    const int cs = round_up(C, 8);
+    exb_dwconv_desc d = dw_desc(N, H, W, cs);
+    const int OH = (H + d.pad_t + d.pad_b - d.kh) / d.stride_h + 1, OW = (W + d.pad_l + d.pad_r - d.kw) / d.stride_w + 1;
+    tops[0] = make_tensor<float>({N, C, OH, OW}, dev, memory::NCHW, bottoms[0]->allocator());
+    if (N == 0) return;
+    void* xin = this->scratch_in_.get((size_t)N * H * W * cs * 2, dev);
+    void* yout = this->scratch_out_.get((size_t)N * OH * OW * cs * 2, dev);
+    exb_check(exb_nchw_f32_to_nhwc(h, bottoms[0]->gpu_data(), xin, EXB_F16, N, C, H, W, cs, 1.f, 0, nullptr),
+              "exb_nchw_f32_to_nhwc");
+    exb_check(exb_dwconv2d_fwd(h, &d, xin, dw_packed(h, d), yout, nullptr), "exb_dwconv2d_fwd");
+    exb_check(exb_nhwc_to_nchw_f32(h, yout, EXB_F16, tops[0]->mutable_gpu_data(), N, C, OH, OW, cs, 1.f, nullptr),
+              "exb_nhwc_to_nchw_f32");
+}
+// int8 depthwise = dequantised weights, float activations (the reference does the same).
+template <typename Dtype>
+void operation_convolutiondepthwise<Dtype>::forward_gpu_i8(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    forward_gpu_f32(h, bottoms, tops);
+}
+template <typename Dtype>
+void operation_convolutiondepthwise<Dtype>::forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops) {
+    CHECK_EQ(bottoms.size(), (size_t)1);
+    CHECK_EQ(tops.size(), (size_t)1);
+    if (bottoms[0]->order() != memory::NHWC) NOT_IMPLEMENTED << " (fp16 tensors must be NHWC)";
+    const int N = bottoms[0]->num(), C = bottoms[0]->channels(), H = bottoms[0]->height(), W = bottoms[0]->width();
+    exb_dwconv_desc d = dw_desc(N, H, W, C);
+    const int OH = (H + d.pad_t + d.pad_b - d.kh) / d.stride_h + 1, OW = (W + d.pad_l + d.pad_r - d.kw) / d.stride_w + 1;
+    tops[0] = make_tensor<unsigned short>({N, OH, OW, C}, this->params_.device_, memory::NHWC, bottoms[0]->allocator());
+    if (N == 0) return;
+    exb_check(exb_dwconv2d_fwd(h, &d, bottoms[0]->gpu_data(), dw_packed(h, d), tops[0]->mutable_gpu_data(), nullptr),
+              "exb_dwconv2d_fwd");
+}
+INSTANCE_CLASS(operation_convolutiondepthwise);
+REGISTE(operation_convolutiondepthwise);
+
+// ---------------------------------------------------------------------------------------------
+// pooling
+// ---------------------------------------------------------------------------------------------
+template <typename Dtype>
+operation_pooling<Dtype>::operation_pooling(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        const int v = std::atoi(kv.second.c_str());
+        switch (kv.first) {
+        case 0: type_ = v; break;
+        case 1: kernel_size_w_ = kernel_size_h_ = v; break;
+        case 2: stride_w_ = stride_h_ = v; break;
+        case 3: pad_left_ = pad_right_ = pad_top_ = pad_bottom_ = v; break;
+        case 4: global_pooling_ = v != 0; break;
+        case 5: pad_mode_ = v; break;
+        case 6: avgpool_count_include_pad_ = v; break;
+        case 11: kernel_size_h_ = v; break;
+        case 12: stride_h_ = v; break;
+        case 13: pad_top_ = v; break;
+        case 14: pad_right_ = v; break;
+        case 15: pad_bottom_ = v; break;
+        case -23330: break;
+        default: LOG(FATAL) << "Un-supported Pooling Attribution " << kv.first;
+        }
+    }
+}
+
+template <typename Dtype>
+exb_pool_desc operation_pooling<Dtype>::desc(int N, int H, int W, int C, int c_stride, int dtype) const {
+    exb_pool_desc d;
+    std::memset(&d, 0, sizeof(d));
+    if (type_ != MAX && type_ != AVE) LOG(FATAL) << "Unknown pooling method.";
+    if (pad_mode_ != 0 && pad_mode_ != 1) NOT_IMPLEMENTED;
+    d.N = N; d.H = H; d.W = W; d.C = C; d.c_stride = c_stride; d.type = type_;
+    d.kh = kernel_size_h_; d.kw = kernel_size_w_; d.stride_h = stride_h_; d.stride_w = stride_w_;
+    d.pad_t = pad_top_; d.pad_b = pad_bottom_; d.pad_l = pad_left_; d.pad_r = pad_right_;
+    d.global_pool = global_pooling_; d.pad_mode = pad_mode_; d.count_include_pad = avgpool_count_include_pad_;
+    d.dtype = dtype; d.out2_dtype = -1; d.out2_scale = 1.f;
+    return d;
+}
+
+template <typename Dtype>
+void operation_pooling<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), tops.size());
+    for (size_t i = 0; i < bottoms.size(); ++i) {
+        const auto& b = bottoms[i];
+        const int N = b->num(), C = b->channels(), H = b->height(), W = b->width();
+        const int dev = b->device();
+        if (b->order() == memory::NHWC && C % 4 == 0) {   // native layout, no conversion
+            exb_pool_desc d = desc(N, H, W, C, C, EXB_F32);
+            int PH, PW;
+            exb_check(exb_pool_out_dims(&d, &PH, &PW), "exb_pool_out_dims");
+            tops[i] = make_tensor<float>({N, PH, PW, C}, dev, memory::NHWC, b->allocator());
+            if (N) exb_check(exb_pool2d_fwd(h, &d, b->gpu_data(), tops[i]->mutable_gpu_data(), nullptr, nullptr), "exb_pool2d_fwd");
+            continue;
+        }
+        if (b->order() == memory::NHWC) b->convert_order();
+        const int cs = round_up(C, 4);
+        exb_pool_desc d = desc(N, H, W, C, cs, EXB_F32);
+        int PH, PW;
+        exb_check(exb_pool_out_dims(&d, &PH, &PW), "exb_pool_out_dims");
+        tops[i] = make_tensor<float>({N, C, PH, PW}, dev, memory::NCHW, b->allocator());
+        if (N == 0) continue;
+        void* xin = scratch_in_.get((size_t)N * H * W * cs * 4, dev);
+        void* yout = scratch_out_.get((size_t)N * PH * PW * cs * 4, dev);
+        exb_check(exb_nchw_f32_to_nhwc(h, b->gpu_data(), xin, EXB_F32, N, C, H, W, cs, 1.f, 0, nullptr), "exb_nchw_f32_to_nhwc");
+        exb_check(exb_pool2d_fwd(h, &d, xin, yout, nullptr, nullptr), "exb_pool2d_fwd");
+        exb_check(exb_nhwc_to_nchw_f32(h, yout, EXB_F32, tops[i]->mutable_gpu_data(), N, C, PH, PW, cs, 1.f, nullptr),
+                  "exb_nhwc_to_nchw_f32");
+    }
+}
+
+template <typename Dtype>
+void operation_pooling<Dtype>::forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops) {
+    CHECK_EQ(bottoms.size(), tops.size());
+    for (size_t i = 0; i < bottoms.size(); ++i) {
+        const auto& b = bottoms[i];
+        if (b->order() != memory::NHWC) NOT_IMPLEMENTED << " (fp16 tensors must be NHWC)";
+        const int N = b->num(), C = b->channels(), H = b->height(), W = b->width();
+        exb_pool_desc d = desc(N, H, W, C, C, EXB_F16);
+        int PH, PW;
+        exb_check(exb_pool_out_dims(&d, &PH, &PW), "exb_pool_out_dims");
+        tops[i] = make_tensor<unsigned short>({N, PH, PW, C}, b->device(), memory::NHWC, b->allocator());
+        if (N) exb_check(exb_pool2d_fwd(h, &d, b->gpu_data(), tops[i]->mutable_gpu_data(), nullptr, nullptr), "exb_pool2d_fwd");
+    }
+}
+INSTANCE_CLASS(operation_pooling);
+REGISTE(operation_pooling);
+
+// ---------------------------------------------------------------------------------------------
+// eltwise / binaryop / relu / clip / sigmoid (layout-agnostic element-wise passes)
+// ---------------------------------------------------------------------------------------------
+template <typename Dtype>
+operation_eltwise<Dtype>::operation_eltwise(const operation_param& param) : operation<Dtype>(param) {
+    coeffs_ = std::vector<float>(param.input_count_, 1.0f);
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        if (kv.first == 0) {
+            type_ = std::atoi(kv.second.c_str());
+        } else if (kv.first == -23301) {
+            // "<n>,c1,c2,...": the reference reads entries 1..n-1 (so n-1 coefficients; the
+            // rest keep their default 1.0) - src/Excalibur/operation_eltwise.cpp:22-30.
+            auto parts = split_string(kv.second, ",");
+            CHECK_EQ(type_, (int)SUM);
+            const int n = parts.empty() ? 0 : std::atoi(parts[0].c_str());
+            for (int j = 1; j < n && j < (int)parts.size() && j - 1 < (int)coeffs_.size(); ++j)
+                coeffs_[j - 1] = (float)std::atof(parts[j].c_str());
+        } else if (kv.first != -23330) {
+            LOG(FATAL) << "Un-supported Eltwise Attribution " << kv.first;
+        }
+    }
+}
+
+template <typename T, typename L>
+static void eltwise_run(exb_ctx* h, int type, const std::vector<float>& coeffs, const L& bottoms, L& tops, int dtype) {
+    CHECK_GE(bottoms.size(), (size_t)2);
+    for (size_t i = 1; i < bottoms.size(); ++i) CHECK(bottoms[i]->data_shape() == bottoms[0]->data_shape());
+    CHECK_EQ(tops.size(), (size_t)1);
+    if (type < 0 || type > 2) LOG(FATAL) << "Unknown elementwise operation.";
+    tops[0] = make_tensor<T>(bottoms[0]->data_shape(), bottoms[0]->device(), bottoms[0]->order(), bottoms[0]->allocator());
+    std::vector<const void*> xs;
+    for (auto& b : bottoms) xs.push_back(b->gpu_data());
+    std::vector<float> cf(bottoms.size(), 1.f);
+    for (size_t i = 0; i < cf.size() && i < coeffs.size(); ++i) cf[i] = coeffs[i];
+    exb_check(exb_eltwise_fwd(h, type, (int)xs.size(), xs.data(), cf.data(), tops[0]->mutable_gpu_data(),
+                              tops[0]->count(), dtype, nullptr),
+              "exb_eltwise_fwd");
+}
+template <typename Dtype>
+void operation_eltwise<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    eltwise_run<float>(h, type_, coeffs_, bottoms, tops, EXB_F32);
+}
+template <typename Dtype>
+void operation_eltwise<Dtype>::forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops) {
+    eltwise_run<unsigned short>(h, type_, coeffs_, bottoms, tops, EXB_F16);
+}
+INSTANCE_CLASS(operation_eltwise);
+REGISTE(operation_eltwise);
+
+template <typename Dtype>
+operation_binaryop<Dtype>::operation_binaryop(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        switch (kv.first) {
+        case 0: op_type_ = std::atoi(kv.second.c_str()); break;
+        case 1: with_scalar_ = std::atoi(kv.second.c_str()); break;
+        case 2: coef_ = (float)std::atof(kv.second.c_str()); break;
+        default: LOG(FATAL) << "Un-supported BinaryOp Attribution " << kv.first;
+        }
+    }
+}
+template <typename T, typename L>
+static void binaryop_run(exb_ctx* h, int op, int with_scalar, float coef, const L& bottoms, L& tops, int dtype) {
+    CHECK_GE(bottoms.size(), (size_t)1);
+    CHECK_EQ(tops.size(), (size_t)1);
+    if (op < 0 || op > 3) NOT_IMPLEMENTED << " (binary op type " << op << ")";
+    tops[0] = make_tensor<T>(bottoms[0]->data_shape(), bottoms[0]->device(), bottoms[0]->order(), bottoms[0]->allocator());
+    if (with_scalar) {
+        exb_check(exb_binaryop_scalar_fwd(h, op, bottoms[0]->gpu_data(), coef, tops[0]->mutable_gpu_data(),
+                                          tops[0]->count(), dtype, nullptr),
+                  "exb_binaryop_scalar_fwd");
+        return;
+    }
+    CHECK_GE(bottoms.size(), (size_t)2);
+    if (bottoms[0]->data_shape() != bottoms[1]->data_shape())
+        NOT_IMPLEMENTED << " (broadcasting binary op: only equal shapes are on the hot path)";
+    exb_check(exb_binaryop_fwd(h, op, bottoms[0]->gpu_data(), bottoms[1]->gpu_data(), tops[0]->mutable_gpu_data(),
+                               tops[0]->count(), dtype, nullptr),
+              "exb_binaryop_fwd");
+}
+template <typename Dtype>
+void operation_binaryop<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    binaryop_run<float>(h, op_type_, with_scalar_, coef_, bottoms, tops, EXB_F32);
+}
+template <typename Dtype>
+void operation_binaryop<Dtype>::forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops) {
+    binaryop_run<unsigned short>(h, op_type_, with_scalar_, coef_, bottoms, tops, EXB_F16);
+}
+INSTANCE_CLASS(operation_binaryop);
+REGISTE(operation_binaryop);
+
+template <typename Dtype>
+operation_relu<Dtype>::operation_relu(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        if (kv.first == 0) slope_ = (float)std::atof(kv.second.c_str());
+        else if (kv.first != -23330) LOG(FATAL) << "Un-supported ReLU Attribution " << kv.first;
+    }
+    this->params_.inplace_ = true;   // flagged in place, yet a new top is allocated (as the reference does)
+}
+template <typename T, typename L>
+static void act_run(exb_ctx* h, int act, const L& bottoms, L& tops, int dtype) {
+    CHECK_EQ(bottoms.size(), tops.size());
+    for (size_t i = 0; i < bottoms.size(); ++i) {
+        tops[i] = make_tensor<T>(bottoms[i]->data_shape(), bottoms[i]->device(), bottoms[i]->order(), bottoms[i]->allocator());
+        int rc = act == EXB_ACT_RELU
+                     ? exb_relu_fwd(h, bottoms[i]->gpu_data(), tops[i]->mutable_gpu_data(), tops[i]->count(), dtype, nullptr)
+                     : exb_activation_fwd(h, act, bottoms[i]->gpu_data(), tops[i]->mutable_gpu_data(), tops[i]->count(), dtype, nullptr);
+        exb_check(rc, "activation kernel");
+    }
+}
+template <typename Dtype>
+void operation_relu<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    act_run<float>(h, EXB_ACT_RELU, bottoms, tops, EXB_F32);
+}
+template <typename Dtype>
+void operation_relu<Dtype>::forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops) {
+    act_run<unsigned short>(h, EXB_ACT_RELU, bottoms, tops, EXB_F16);
+}
+INSTANCE_CLASS(operation_relu);
+REGISTE(operation_relu);
+
+INSTANCE_CLASS(operation_split);
+REGISTE(operation_split);
+
+template <typename Dtype>
+operation_clip<Dtype>::operation_clip(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        if (kv.first == 0) min_ = std::stof(kv.second);
+        else if (kv.first == 1) max_ = std::stof(kv.second);
+        else if (kv.first != -23330) LOG(FATAL) << "Un-supported Clip Attribution " << kv.first;
+    }
+}
+template <typename Dtype>
+void operation_clip<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    if (!is_relu6()) NOT_IMPLEMENTED << " (Clip is implemented for the ReLU6 range 0..6 only)";
+    act_run<float>(h, EXB_ACT_RELU6, bottoms, tops, EXB_F32);
+}
+INSTANCE_CLASS(operation_clip);
+REGISTE(operation_clip);
+
+template <typename Dtype>
+void operation_sigmoid<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    act_run<float>(h, EXB_ACT_SIGMOID, bottoms, tops, EXB_F32);
+}
+INSTANCE_CLASS(operation_sigmoid);
+REGISTE(operation_sigmoid);
+
+// ---------------------------------------------------------------------------------------------
+// inner product
+// ---------------------------------------------------------------------------------------------
+template <typename Dtype>
+operation_innerproduct<Dtype>::operation_innerproduct(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        const int v = std::atoi(kv.second.c_str());
+        switch (kv.first) {
+        case 0: num_output_ = v; break;
+        case 1: bias_term_ = v != 0; break;
+        case 2: weight_data_size_ = v; break;
+        case 8:
+            int8_scale_term_ = v != 0;
+            this->params_.set_int8_quantization(int8_scale_term_);
+            break;
+        case 9: activation_type_ = v; break;
+        case 10: case -23330: break;
+        default: LOG(FATAL) << "Un-supported InnerProduct Attribution " << kv.first;
+        }
+    }
+    CHECK_GT(num_output_, 0);
+}
+template <typename Dtype>
+operation_innerproduct<Dtype>::~operation_innerproduct() {
+    if (w_) exb_conv_weights_destroy(w_);
+}
+template <typename Dtype>
+int operation_innerproduct<Dtype>::init_weights(FILE* fp) {
+    int tag = 0;
+    read_or_die(&tag, sizeof(int), fp, "the quantize tag");
+    if (tag != 0) NOT_IMPLEMENTED << " (int8 InnerProduct: the reference has only an ARM implementation)";
+    const int dev = this->params_.device_;
+    this->weights_f32_.push_back(make_tensor<float>({weight_data_size_}, dev, memory::NCHW));
+    read_or_die(this->weights_f32_[0]->mutable_cpu_data(), sizeof(float) * weight_data_size_, fp, "weights");
+    int mem = weight_data_size_ * sizeof(float);
+    if (bias_term_) {
+        this->weights_f32_.push_back(make_tensor<float>({num_output_}, dev, memory::NCHW));
+        read_or_die(this->weights_f32_[1]->mutable_cpu_data(), sizeof(float) * num_output_, fp, "bias");
+        mem += num_output_ * sizeof(float);
+    }
+    return mem;
+}
+template <typename Dtype>
+int operation_innerproduct<Dtype>::init_weights() {
+    std::default_random_engine e;
+    std::normal_distribution<float> n(0, 0.3);
+    const int dev = this->params_.device_;
+    this->weights_f32_.push_back(make_tensor<float>({weight_data_size_}, dev, memory::NCHW));
+    float* w = this->weights_f32_[0]->mutable_cpu_data();
+    for (int i = 0; i < weight_data_size_; ++i) w[i] = n(e);
+    if (bias_term_) {
+        this->weights_f32_.push_back(make_tensor<float>({num_output_}, dev, memory::NCHW));
+        float* b = this->weights_f32_[1]->mutable_cpu_data();
+        for (int i = 0; i < num_output_; ++i) b[i] = n(e);
+    }
+    return (weight_data_size_ + (bias_term_ ? num_output_ : 0)) * (int)sizeof(float);
+}
+template <typename Dtype>
+exb_conv_desc operation_innerproduct<Dtype>::fc_desc(int N, int cin_stride) const {
+    exb_conv_desc d;
+    std::memset(&d, 0, sizeof(d));
+    d.N = N; d.H = 1; d.W = 1; d.Cin = in_features(); d.Cout = num_output_; d.cin_stride = cin_stride;
+    d.kh = d.kw = 1; d.stride_h = d.stride_w = 1; d.dilation = 1; d.group = 1;
+    d.in_dtype = EXB_F16; d.out_dtype = EXB_F32; d.out2_dtype = -1; d.res_dtype = -1;
+    d.act = activation_type_ == 1 ? EXB_ACT_RELU : (activation_type_ == 4 ? EXB_ACT_SIGMOID : EXB_ACT_NONE);
+    d.out_scale = d.out2_scale = 1.f;
+    return d;
+}
+template <typename Dtype>
+exb_conv_weights* operation_innerproduct<Dtype>::packed(exb_ctx* ctx, const exb_conv_desc& d) {
+    if (w_ && w_cin_stride_ == d.cin_stride) return w_;
+    if (w_) exb_conv_weights_destroy(w_);
+    w_ = nullptr;
+    const float* bias = bias_term_ ? this->weights_f32_[1]->cpu_data() : nullptr;
+    exb_check(exb_conv_weights_pack_f16(ctx, &d, this->weights_f32_[0]->cpu_data(), bias, &w_), "exb_conv_weights_pack_f16");
+    w_cin_stride_ = d.cin_stride;
+    return w_;
+}
+// bottoms[0]: {N, C, H, W} fp32 NCHW, flattened to N x (C*H*W) like the reference.
+template <typename Dtype>
+void operation_innerproduct<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), (size_t)1);
+    CHECK_EQ(tops.size(), (size_t)1);
+    if (bottoms[0]->order() == memory::NHWC) bottoms[0]->convert_order();
+    const int N = bottoms[0]->num(), K = bottoms[0]->count(1, 4);
+    CHECK_EQ(K, in_features()) << "flattened input size does not match the weights";
+    const int dev = this->params_.device_;
+    const int ks = round_up(K, 16);
+    exb_conv_desc d = fc_desc(N, ks);
+    tops[0] = make_tensor<float>({N, num_output_, 1, 1}, dev, memory::NCHW, bottoms[0]->allocator());
+    if (N == 0) return;
+    void* xin = scratch_in_.get((size_t)N * ks * 2, dev);
+    // {N, K, 1, 1} NCHW -> NHWC fp16 with padded channels
+    exb_check(exb_nchw_f32_to_nhwc(h, bottoms[0]->gpu_data(), xin, EXB_F16, N, K, 1, 1, ks, 1.f, 0, nullptr),
+              "exb_nchw_f32_to_nhwc");
+    exb_check(exb_conv2d_fwd(h, &d, xin, packed(h, d), nullptr, tops[0]->mutable_gpu_data(), nullptr, nullptr),
+              "exb_conv2d_fwd");
+}
+INSTANCE_CLASS(operation_innerproduct);
+REGISTE(operation_innerproduct);
+
+}  // namespace excalibur
+}  // namespace glasssix

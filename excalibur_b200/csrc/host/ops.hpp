@@ -1,0 +1,228 @@
+// The operation classes on the CNN forward hot path, registered under the reference's keys
+// (operation_convolution, operation_convolutiondepthwise, operation_pooling, operation_eltwise,
+// operation_binaryop, operation_relu) plus the glue ops the benchmark graphs need
+// (operation_split, operation_innerproduct, operation_input, operation_clip, operation_sigmoid).
+// Constructors parse the same integer-keyed "k=v" lists; unknown keys are fatal; key -23330 is
+// ignored (reference src/Excalibur/operation_general_conv.cpp:9-124, operation_pooling.cpp:10-77,
+// operation_eltwise.cpp:11-40, operation_binaryop.cpp:369-391, operation_relu.cpp:9-28).
+#pragma once
+#include "operation.hpp"
+
+namespace glasssix {
+namespace excalibur {
+
+// Raises LOG(FATAL) with the library's error string when a C-ABI call fails.
+void exb_check(int rc, const char* what);
+
+// Scratch device buffer that grows on demand (an op instance is not re-entrant, like the
+// reference's member scratch tensors, include/Excalibur/operation_convolution.hpp:102-141).
+class device_scratch {
+public:
+    ~device_scratch();
+    void* get(size_t bytes, int device);
+private:
+    void* ptr_ = nullptr;
+    size_t cap_ = 0;
+};
+
+template <typename Dtype>
+class operation_general_conv : public operation<Dtype> {
+public:
+    explicit operation_general_conv(const operation_param& param);
+    virtual const char* type() const { return this->params_.type_.c_str(); }
+
+    int output_channel_ = 0, kernel_size_w_ = 0, kernel_size_h_ = 0, dilation_w_ = 1, dilation_h_ = 1;
+    int stride_w_ = 1, stride_h_ = 1, group_ = 1, pad_left_ = 0, pad_right_ = 0, pad_top_ = 0, pad_bottom_ = 0;
+    bool int8_scale_term_ = false, bias_term_ = false;
+    int weight_data_size_ = 0, activation_type_ = 0, impl_type_ = 0;
+    int input_channel_ = 0;   // known after init_weights: weight_data_size / (Cout/group * kh * kw) * ... 
+};
+
+template <typename Dtype>
+class operation_convolution : public operation_general_conv<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    typedef typename operation<Dtype>::f16_list f16_list;
+    explicit operation_convolution(const operation_param& param);
+    virtual ~operation_convolution();
+    virtual int init_weights();
+    virtual int init_weights(FILE* fp);
+
+    // --- used by the fused executor ---------------------------------------------------------
+    bool is_int8() const { return !this->weights_i8_.empty(); }
+    int in_channels() const { return this->input_channel_; }
+    float act_scale() const;                  // the conv's input quantisation multiplier (int8)
+    // Packed weights for a given input layout; cached per (in_dtype, cin_stride, cout_stride).
+    exb_conv_weights* packed(exb_ctx* ctx, const exb_conv_desc& d);
+    // Descriptor skeleton for an input of N x H x W (dtypes / fusion fields left to the caller).
+    exb_conv_desc base_desc(int N, int H, int W) const;
+    // Drop the fp32 host weights that only a CPU path would read (keeps bias and scales).
+    int exb_activation() const;               // key 9 mapped to exb_act (fatal if unsupported)
+
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    virtual void forward_gpu_i8(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
+    void forward_nchw_f32(exb_ctx* h, const f32_list& bottoms, f32_list& tops, bool int8);
+
+    struct packed_entry { int in_dtype, cin_stride, cout_stride; exb_conv_weights* w; };
+    std::vector<packed_entry> packed_;
+    device_scratch scratch_in_, scratch_out_;
+};
+
+template <typename Dtype>
+class operation_convolutiondepthwise : public operation_convolution<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    typedef typename operation<Dtype>::f16_list f16_list;
+    explicit operation_convolutiondepthwise(const operation_param& param);
+    virtual ~operation_convolutiondepthwise();
+    exb_dwconv_desc dw_desc(int N, int H, int W, int c_stride) const;
+    exb_dw_weights* dw_packed(exb_ctx* ctx, const exb_dwconv_desc& d);
+    // fp32 [C][kh][kw] weights; int8 files are dequantised once, like the reference
+    // (src/Excalibur/operation_convolutiondepthwise.cpp:184-222).
+    const float* dw_weights_f32();
+
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    virtual void forward_gpu_i8(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
+    exb_dw_weights* dw_w_ = nullptr;
+    int dw_cs_ = 0;
+    std::vector<float> dequantized_;
+};
+
+template <typename Dtype>
+class operation_pooling : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    typedef typename operation<Dtype>::f16_list f16_list;
+    enum pooling_type { MAX = 0, AVE = 1 };
+    explicit operation_pooling(const operation_param& param);
+    virtual const char* type() const { return "Pooling"; }
+    exb_pool_desc desc(int N, int H, int W, int C, int c_stride, int dtype) const;
+
+    int type_ = MAX, kernel_size_w_ = 0, kernel_size_h_ = 0, stride_w_ = 1, stride_h_ = 1;
+    int pad_left_ = 0, pad_right_ = 0, pad_top_ = 0, pad_bottom_ = 0;
+    bool global_pooling_ = false;
+    int pad_mode_ = 1, avgpool_count_include_pad_ = 0;
+
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
+    device_scratch scratch_in_, scratch_out_;
+};
+
+template <typename Dtype>
+class operation_eltwise : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    typedef typename operation<Dtype>::f16_list f16_list;
+    enum eltwise_type { PROD = 0, SUM = 1, MAX = 2 };
+    explicit operation_eltwise(const operation_param& param);
+    virtual const char* type() const { return "Eltwise"; }
+    int type_ = SUM;
+    std::vector<float> coeffs_;
+
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
+};
+
+template <typename Dtype>
+class operation_binaryop : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    typedef typename operation<Dtype>::f16_list f16_list;
+    explicit operation_binaryop(const operation_param& param);
+    virtual const char* type() const { return "BinaryOp"; }
+    int op_type_ = 0;
+    int with_scalar_ = 0;
+    float coef_ = 0.f;
+
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
+};
+
+template <typename Dtype>
+class operation_relu : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    typedef typename operation<Dtype>::f16_list f16_list;
+    explicit operation_relu(const operation_param& param);
+    virtual const char* type() const { return "ReLU"; }
+    float slope_ = 0.f;   // parsed, unused (as in the reference)
+
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
+};
+
+// ---- glue ops around the hot path -----------------------------------------------------------
+template <typename Dtype>
+class operation_split : public operation<Dtype> {   // aliases its input to every output
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    typedef typename operation<Dtype>::f16_list f16_list;
+    explicit operation_split(const operation_param& param) : operation<Dtype>(param) {}
+    virtual const char* type() const { return "Split"; }
+protected:
+    virtual void forward_gpu_f32(exb_ctx*&, const f32_list& bottoms, f32_list& tops) {
+        CHECK_EQ(bottoms.size(), (size_t)1);
+        for (auto& t : tops) t = bottoms[0];
+    }
+    virtual void forward_gpu_f16(exb_ctx*&, const f16_list& bottoms, f16_list& tops) {
+        CHECK_EQ(bottoms.size(), (size_t)1);
+        for (auto& t : tops) t = bottoms[0];
+    }
+};
+
+template <typename Dtype>
+class operation_clip : public operation<Dtype> {    // keys 0 = min, 1 = max
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_clip(const operation_param& param);
+    virtual const char* type() const { return "Clip"; }
+    float min_ = -3.402823466e+38f, max_ = 3.402823466e+38f;
+    bool is_relu6() const { return min_ == 0.f && max_ == 6.f; }
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
+template <typename Dtype>
+class operation_sigmoid : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_sigmoid(const operation_param& param) : operation<Dtype>(param) {}
+    virtual const char* type() const { return "Sigmoid"; }
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
+// Fully connected layer: keys 0 num_output, 1 bias_term, 2 weight_data_size, 8 int8, 9 activation
+// (reference src/Excalibur/operation_innerproduct.cpp:35-120).  Runs as a 1x1 convolution on a
+// 1x1 map through the tensor-core kernel in fp16.
+template <typename Dtype>
+class operation_innerproduct : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_innerproduct(const operation_param& param);
+    virtual ~operation_innerproduct();
+    virtual const char* type() const { return "InnerProduct"; }
+    virtual int init_weights();
+    virtual int init_weights(FILE* fp);
+    int num_output_ = 0, weight_data_size_ = 0, activation_type_ = 0;
+    bool bias_term_ = false, int8_scale_term_ = false;
+    int in_features() const { return num_output_ ? weight_data_size_ / num_output_ : 0; }
+    exb_conv_desc fc_desc(int N, int cin_stride) const;
+    exb_conv_weights* packed(exb_ctx* ctx, const exb_conv_desc& d);
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    exb_conv_weights* w_ = nullptr;
+    int w_cin_stride_ = 0;
+    device_scratch scratch_in_, scratch_out_;
+};
+
+}  // namespace excalibur
+}  // namespace glasssix

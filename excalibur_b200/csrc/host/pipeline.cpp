@@ -1,0 +1,914 @@
+// pipeline<Dtype>: .phai parser, .racy loader, sequential executor (reference
+// src/Excalibur/pipeline.cpp:35-194,234-404,422-451) and, for pipeline<float> on a GPU, the fused
+// NHWC plan that is the fast path of this library.
+#include "pipeline.hpp"
+
+#include <cuda_fp16.h>
+
+#include <fstream>
+#include <functional>
+#include <set>
+
+#include "ops.hpp"
+
+namespace glasssix {
+namespace excalibur {
+
+namespace {
+
+int round_up(int a, int b) { return (a + b - 1) / b * b; }
+
+std::vector<std::string> read_lines(std::string_view path) {
+    std::ifstream in{std::string(path)};
+    if (!in) LOG(FATAL) << "Cannot open " << path;
+    std::vector<std::string> lines;
+    std::string l;
+    while (std::getline(in, l)) {
+        while (!l.empty() && (l.back() == '\r' || l.back() == '\n')) l.pop_back();
+        lines.push_back(l);
+    }
+    return lines;
+}
+
+struct trace_event {
+    std::string name;
+    float begin_ms, end_ms;
+};
+
+// ------------------------------------------------------------------------------------------
+// Fused plan (float pipelines on a GPU)
+// ------------------------------------------------------------------------------------------
+struct dev_buf {
+    void* p = nullptr;
+    size_t bytes = 0;
+    ~dev_buf() { if (p) cudaFree(p); }
+    void* ensure(size_t n, int device) {
+        if (n > bytes) {
+            if (p) cudaFree(p);
+            p = nullptr;
+            CUDA_CHECK(cudaSetDevice(device));
+            CUDA_CHECK(cudaMalloc(&p, n ? n : 16));
+            bytes = n;
+        }
+        return p;
+    }
+};
+
+struct fmap_info {
+    std::string name;
+    int root = -1;                 // featmap this one aliases (Split), or itself
+    int N = 0, C = 0, H = 0, W = 0;
+    int cs = 0;                    // physical channels of the NHWC device forms
+    bool need_f16 = false, need_i8 = false, need_f32 = false;
+    float i8_scale = 0.f;          // multiplier of the int8 form
+    std::vector<float> extra_i8_scales;   // further int8 consumers with other scales
+    std::shared_ptr<dev_buf> f16, i8, f32;
+    std::vector<std::shared_ptr<dev_buf>> extra_i8;
+    bool produced = false;
+};
+
+struct plan_step {
+    std::string name;
+    std::function<void(cudaStream_t)> run;
+    int launches = 1;
+};
+
+class fused_plan {
+public:
+    typedef operation<float> op_t;
+    fused_plan(const std::vector<operation_param>& params, const std::vector<std::shared_ptr<op_t>>& ops,
+               const std::vector<std::string>& inputs, const std::vector<std::string>& outputs, int device)
+        : params_(params), ops_(ops), inputs_(inputs), outputs_(outputs), device_(device) {}
+    ~fused_plan() {
+        if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+        if (stream_) cudaStreamDestroy(stream_);
+        if (ev0_) cudaEventDestroy(ev0_);
+        if (ev1_) cudaEventDestroy(ev1_);
+        if (ctx_) exb_ctx_destroy(ctx_);
+    }
+
+    // Why the graph cannot be fused, or "" when it can.
+    std::string unsupported_reason() const {
+        static const std::set<std::string> ok = {"convolution", "convolutiondepthwise", "pooling", "eltwise", "binaryop",
+                                                  "relu", "split", "innerproduct", "clip", "sigmoid"};
+        for (const auto& p : params_) {
+            std::string t = p.type_;
+            std::transform(t.begin(), t.end(), t.begin(), ::tolower);
+            if (!ok.count(t)) return "operation type " + p.type_ + " has no fused implementation";
+        }
+        if (inputs_.size() != 1) return "fused plan needs exactly one input feature map";
+        return "";
+    }
+
+    void build(int N, int C, int H, int W);
+    bool built_for(int N, int C, int H, int W) const { return built_ && N == N_ && C == C_ && H == H_ && W == W_; }
+    void run(const float* host_input, bool use_graph, bool profile, std::vector<trace_event>* trace);
+    std::shared_ptr<memory::tensor<float>> fetch(const std::string& name);
+    int launches() const { return launches_; }
+    double device_ms() const { return device_ms_; }
+    exb_ctx* ctx() { return ctx_; }
+
+private:
+    int fid(const std::string& n) {
+        auto it = index_.find(n);
+        if (it != index_.end()) return it->second;
+        fmap_info f;
+        f.name = n;
+        f.root = (int)fmaps_.size();
+        index_[n] = f.root;
+        fmaps_.push_back(f);
+        return f.root;
+    }
+    int root(int f) const {
+        while (fmaps_[f].root != f) f = fmaps_[f].root;
+        return f;
+    }
+    static std::string lower_type(const operation_param& p) {
+        std::string t = p.type_;
+        std::transform(t.begin(), t.end(), t.begin(), ::tolower);
+        return t;
+    }
+    void add_step(const std::string& name, std::function<void(cudaStream_t)> fn, int launches = 1) {
+        steps_.push_back({name, fn, launches});
+    }
+    void* form_f16(fmap_info& f) {
+        if (!f.f16) f.f16 = std::make_shared<dev_buf>();
+        return f.f16->ensure((size_t)f.N * f.H * f.W * f.cs * 2, device_);
+    }
+    void* form_i8(fmap_info& f) {
+        if (!f.i8) f.i8 = std::make_shared<dev_buf>();
+        return f.i8->ensure((size_t)f.N * f.H * f.W * f.cs, device_);
+    }
+    void* form_f32(fmap_info& f) {
+        if (!f.f32) f.f32 = std::make_shared<dev_buf>();
+        return f.f32->ensure((size_t)f.N * f.H * f.W * f.C * 4, device_);
+    }
+    void set_shape(fmap_info& f, int N, int C, int H, int W) {
+        f.N = N; f.C = C; f.H = H; f.W = W;
+        f.cs = round_up(C, (f.need_i8 || C > 16) ? 32 : 16);
+    }
+    // After a producer wrote f's primary forms: emit quantise passes for what it could not fuse.
+    void finish_forms(fmap_info& f, bool wrote_i8);
+    const void* int8_form_for(fmap_info& f, float scale);
+
+    const std::vector<operation_param>& params_;
+    const std::vector<std::shared_ptr<op_t>>& ops_;
+    std::vector<std::string> inputs_, outputs_;
+    int device_;
+    exb_ctx* ctx_ = nullptr;
+    cudaStream_t stream_ = nullptr;
+    cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+    cudaGraphExec_t graph_exec_ = nullptr;
+    bool built_ = false;
+    int N_ = 0, C_ = 0, H_ = 0, W_ = 0;
+    std::vector<fmap_info> fmaps_;
+    std::unordered_map<std::string, int> index_;
+    std::vector<plan_step> steps_;
+    dev_buf staging_in_;
+    int launches_ = 0;
+    double device_ms_ = 0.0;
+    bool warmed_ = false;
+
+public:
+    // results of the last run, by output feature map name
+    std::unordered_map<std::string, std::shared_ptr<memory::tensor<float>>> host_out_;
+};
+
+void fused_plan::finish_forms(fmap_info& f, bool wrote_i8) {
+    f.produced = true;
+    exb_ctx* ctx = ctx_;
+    if (f.need_i8 && !wrote_i8) {
+        CHECK(f.need_f16) << "internal: int8 form requested without a source";
+        void* src = form_f16(f);
+        void* dst = form_i8(f);
+        const int64_t count = (int64_t)f.N * f.H * f.W * f.cs;
+        const float s = f.i8_scale;
+        add_step("quantize " + f.name, [=](cudaStream_t st) {
+            exb_check(exb_quantize_fwd(ctx, src, EXB_F16, static_cast<int8_t*>(dst), count, s, 1, st), "exb_quantize_fwd");
+        });
+    }
+    f.extra_i8.clear();
+    for (float s : f.extra_i8_scales) {
+        auto b = std::make_shared<dev_buf>();
+        void* dst = b->ensure((size_t)f.N * f.H * f.W * f.cs, device_);
+        f.extra_i8.push_back(b);
+        void* src = form_f16(f);
+        const int64_t count = (int64_t)f.N * f.H * f.W * f.cs;
+        add_step("quantize " + f.name, [=](cudaStream_t st) {
+            exb_check(exb_quantize_fwd(ctx, src, EXB_F16, static_cast<int8_t*>(dst), count, s, 1, st), "exb_quantize_fwd");
+        });
+    }
+}
+
+const void* fused_plan::int8_form_for(fmap_info& f, float scale) {
+    if (f.i8 && f.i8_scale == scale) return f.i8->p;
+    for (size_t i = 0; i < f.extra_i8_scales.size(); ++i)
+        if (f.extra_i8_scales[i] == scale) return f.extra_i8[i]->p;
+    LOG(FATAL) << "internal: no int8 form of " << f.name << " with scale " << scale;
+    return nullptr;
+}
+
+void fused_plan::build(int N, int C, int H, int W) {
+    CUDA_CHECK(cudaSetDevice(device_));
+    if (!ctx_) exb_check(exb_ctx_create(device_, &ctx_), "exb_ctx_create");
+    if (!stream_) CUDA_CHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    if (!ev0_) {
+        CUDA_CHECK(cudaEventCreate(&ev0_));
+        CUDA_CHECK(cudaEventCreate(&ev1_));
+    }
+    if (graph_exec_) {
+        cudaGraphExecDestroy(graph_exec_);
+        graph_exec_ = nullptr;
+    }
+    steps_.clear();
+    fmaps_.clear();
+    index_.clear();
+    warmed_ = false;
+    const size_t n_ops = ops_.size();
+
+    // ---- 1. feature maps, Split aliases, consumers ------------------------------------------
+    std::vector<std::vector<int>> in_ids(n_ops), out_ids(n_ops);
+    for (size_t i = 0; i < n_ops; ++i) {
+        for (const auto& n : params_[i].input_featmaps_) in_ids[i].push_back(fid(n));
+        for (const auto& n : params_[i].output_featmaps_) out_ids[i].push_back(fid(n));
+    }
+    for (size_t i = 0; i < n_ops; ++i)
+        if (lower_type(params_[i]) == "split")
+            for (int o : out_ids[i]) fmaps_[o].root = root(in_ids[i][0]);
+    std::vector<std::vector<int>> consumers(fmaps_.size());   // by root id -> op indices
+    for (size_t i = 0; i < n_ops; ++i) {
+        if (lower_type(params_[i]) == "split") continue;
+        for (int f : in_ids[i]) consumers[root(f)].push_back((int)i);
+    }
+    std::set<int> output_roots;
+    for (const auto& n : outputs_) output_roots.insert(root(fid(n)));
+
+    // ---- 2. fusion groups -------------------------------------------------------------------
+    struct group {
+        int conv = -1;          // leading op
+        int residual = -1;      // root featmap added in the epilogue
+        int act = EXB_ACT_NONE;
+        int out = -1;           // root featmap the group finally produces
+        int exec_at = -1;       // index of the last absorbed op
+    };
+    std::vector<int> absorbed(n_ops, 0);
+    std::vector<group> groups(n_ops);
+    auto sole_consumer = [&](int f) -> int {
+        if (output_roots.count(f)) return -1;
+        return consumers[f].size() == 1 ? consumers[f][0] : -1;
+    };
+    auto act_of_op = [&](int j) -> int {
+        const std::string t = lower_type(params_[j]);
+        if (t == "relu") return EXB_ACT_RELU;
+        if (t == "sigmoid") return EXB_ACT_SIGMOID;
+        if (t == "clip") {
+            auto* c = dynamic_cast<operation_clip<float>*>(ops_[j].get());
+            if (c && c->is_relu6()) return EXB_ACT_RELU6;
+        }
+        return -1;
+    };
+    auto is_plain_add = [&](int j) -> bool {
+        const std::string t = lower_type(params_[j]);
+        if (in_ids[j].size() != 2) return false;
+        if (t == "binaryop") {
+            auto* b = dynamic_cast<operation_binaryop<float>*>(ops_[j].get());
+            return b && b->op_type_ == 0 && !b->with_scalar_;
+        }
+        if (t == "eltwise") {
+            auto* e = dynamic_cast<operation_eltwise<float>*>(ops_[j].get());
+            return e && e->type_ == 1 && e->coeffs_.size() >= 2 && e->coeffs_[0] == 1.f && e->coeffs_[1] == 1.f;
+        }
+        return false;
+    };
+    for (size_t i = 0; i < n_ops; ++i) {
+        const std::string t = lower_type(params_[i]);
+        if (absorbed[i] || (t != "convolution" && t != "convolutiondepthwise")) continue;
+        auto* conv = dynamic_cast<operation_convolution<float>*>(ops_[i].get());
+        group g;
+        g.conv = (int)i;
+        g.act = conv->exb_activation();
+        g.out = root(out_ids[i][0]);
+        g.exec_at = (int)i;
+        int j;
+        if (g.act == EXB_ACT_NONE && (j = sole_consumer(g.out)) >= 0 && !absorbed[j] && act_of_op(j) > 0) {
+            g.act = act_of_op(j);
+            absorbed[j] = 1;
+            g.out = root(out_ids[j][0]);
+            g.exec_at = j;
+        } else if (t == "convolution" && g.act == EXB_ACT_NONE && (j = sole_consumer(g.out)) >= 0 && !absorbed[j] &&
+                   is_plain_add(j)) {
+            const int a = root(in_ids[j][0]), b = root(in_ids[j][1]);
+            g.residual = a == g.out ? b : a;
+            absorbed[j] = 1;
+            g.out = root(out_ids[j][0]);
+            g.exec_at = j;
+            int k;
+            if ((k = sole_consumer(g.out)) >= 0 && !absorbed[k] && act_of_op(k) > 0) {
+                g.act = act_of_op(k);
+                absorbed[k] = 1;
+                g.out = root(out_ids[k][0]);
+                g.exec_at = k;
+            }
+        }
+        groups[i] = g;
+    }
+    // Which op index triggers which group (a group runs where its last op stood).
+    std::vector<int> run_group_at(n_ops, -1);
+    for (size_t i = 0; i < n_ops; ++i)
+        if (groups[i].conv >= 0) run_group_at[groups[i].exec_at] = (int)i;
+
+    // ---- 3. forms every feature map must exist in -------------------------------------------
+    auto want_i8 = [&](int f, float scale) {
+        fmap_info& m = fmaps_[f];
+        if (!m.need_i8) {
+            m.need_i8 = true;
+            m.i8_scale = scale;
+        } else if (m.i8_scale != scale &&
+                   std::find(m.extra_i8_scales.begin(), m.extra_i8_scales.end(), scale) == m.extra_i8_scales.end()) {
+            m.extra_i8_scales.push_back(scale);
+            m.need_f16 = true;
+        }
+    };
+    for (size_t i = 0; i < n_ops; ++i) {
+        const std::string t = lower_type(params_[i]);
+        if (t == "split") continue;
+        if (absorbed[i]) {
+            // an absorbed add reads its residual operand as fp16
+            continue;
+        }
+        if (t == "convolution") {
+            auto* conv = dynamic_cast<operation_convolution<float>*>(ops_[i].get());
+            const int f = root(in_ids[i][0]);
+            if (conv->is_int8() && conv->group_ == 1) want_i8(f, conv->act_scale());
+            else fmaps_[f].need_f16 = true;
+            if (groups[i].residual >= 0) fmaps_[groups[i].residual].need_f16 = true;
+        } else {
+            for (int f : in_ids[i]) fmaps_[root(f)].need_f16 = true;
+        }
+    }
+    for (int f : output_roots) {
+        // InnerProduct writes fp32 directly; everything else is converted from fp16.
+        fmaps_[f].need_f16 = true;
+    }
+    for (auto& m : fmaps_)
+        if (m.need_i8 && m.extra_i8_scales.size()) m.need_f16 = true;
+
+    // ---- 4. steps in execution order ---------------------------------------------------------
+    exb_ctx* ctx = ctx_;
+    {
+        fmap_info& in = fmaps_[root(fid(inputs_[0]))];
+        set_shape(in, N, C, H, W);
+        float* stage = static_cast<float*>(staging_in_.ensure((size_t)N * C * H * W * 4, device_));
+        const bool direct_i8 = in.need_i8 && !in.need_f16;
+        void* dst = direct_i8 ? form_i8(in) : form_f16(in);
+        const int cs = in.cs;
+        const float s = in.i8_scale;
+        add_step("ingest " + in.name, [=](cudaStream_t st) {
+            exb_check(exb_nchw_f32_to_nhwc(ctx, stage, dst, direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs,
+                                           direct_i8 ? s : 1.f, 1, st),
+                      "exb_nchw_f32_to_nhwc");
+        });
+        finish_forms(in, direct_i8);
+    }
+
+    auto run_conv_group = [&](const group& g) {
+        const int i = g.conv;
+        const std::string t = lower_type(params_[i]);
+        fmap_info& x = fmaps_[root(in_ids[i][0])];
+        fmap_info& y = fmaps_[g.out];
+        CHECK(x.produced) << "feature map " << x.name << " is consumed before it is produced";
+        if (t == "convolutiondepthwise") {
+            auto* dw = dynamic_cast<operation_convolutiondepthwise<float>*>(ops_[i].get());
+            CHECK_EQ(dw->output_channel_, dw->group_);
+            CHECK_EQ(x.C, dw->output_channel_);
+            exb_dwconv_desc d = dw->dw_desc(x.N, x.H, x.W, x.cs);
+            d.act = g.act;
+            const int OH = (x.H + d.pad_t + d.pad_b - d.kh) / d.stride_h + 1;
+            const int OW = (x.W + d.pad_l + d.pad_r - d.kw) / d.stride_w + 1;
+            y.need_f16 = true;
+            set_shape(y, x.N, x.C, OH, OW);
+            y.cs = x.cs;
+            const void* xin = form_f16(x);
+            void* yo = form_f16(y);
+            exb_dw_weights* w = dw->dw_packed(ctx, d);
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_dwconv2d_fwd(ctx, &d, xin, w, yo, st), "exb_dwconv2d_fwd");
+            });
+            finish_forms(y, false);
+            return;
+        }
+        auto* conv = dynamic_cast<operation_convolution<float>*>(ops_[i].get());
+        CHECK_EQ(x.C, conv->in_channels()) << params_[i].name_ << ": input channels do not match the weights";
+        const bool int8 = conv->is_int8() && conv->group_ == 1;
+        exb_conv_desc d = conv->base_desc(x.N, x.H, x.W);
+        d.in_dtype = int8 ? EXB_I8 : EXB_F16;
+        d.cin_stride = conv->group_ == 1 ? x.cs : x.C;
+        d.act = g.act;
+        int OH, OW;
+        exb_check(exb_conv_out_dims(&d, &OH, &OW), "exb_conv_out_dims");
+        set_shape(y, x.N, conv->output_channel_, OH, OW);
+        if (conv->group_ != 1) CHECK_EQ(x.cs, x.C) << "grouped convolution needs unpadded channels";
+        d.cout_stride = y.cs;
+        const void* xin = int8 ? int8_form_for(x, conv->act_scale()) : form_f16(x);
+        const void* res = nullptr;
+        if (g.residual >= 0) {
+            fmap_info& r = fmaps_[g.residual];
+            CHECK(r.produced) << "residual " << r.name << " is not available when " << params_[i].name_ << " runs";
+            CHECK(r.N == y.N && r.C == y.C && r.H == y.H && r.W == y.W && r.cs == y.cs) << "residual shape mismatch";
+            res = form_f16(r);
+            d.res_dtype = EXB_F16;
+        }
+        void* y1 = nullptr;
+        void* y2 = nullptr;
+        bool wrote_i8 = false;
+        if (y.need_f16 || !y.need_i8) {
+            y.need_f16 = true;
+            d.out_dtype = EXB_F16;
+            y1 = form_f16(y);
+            if (y.need_i8) {
+                d.out2_dtype = EXB_I8;
+                d.out2_scale = y.i8_scale;
+                y2 = form_i8(y);
+                wrote_i8 = true;
+            }
+        } else {
+            d.out_dtype = EXB_I8;
+            d.out_scale = y.i8_scale;
+            y1 = form_i8(y);
+            wrote_i8 = true;
+        }
+        exb_conv_weights* w = conv->packed(ctx, d);
+        add_step(params_[i].name_, [=](cudaStream_t st) {
+            exb_check(exb_conv2d_fwd(ctx, &d, xin, w, res, y1, y2, st), "exb_conv2d_fwd");
+        });
+        finish_forms(y, wrote_i8);
+    };
+
+    for (size_t i = 0; i < n_ops; ++i) {
+        const std::string t = lower_type(params_[i]);
+        if (run_group_at[i] >= 0) {
+            run_conv_group(groups[run_group_at[i]]);
+            continue;
+        }
+        if (absorbed[i] || t == "split" || t == "convolution" || t == "convolutiondepthwise") continue;
+        fmap_info& x = fmaps_[root(in_ids[i][0])];
+        fmap_info& y = fmaps_[root(out_ids[i][0])];
+        CHECK(x.produced) << "feature map " << x.name << " is consumed before it is produced";
+        if (t == "pooling") {
+            auto* pool = dynamic_cast<operation_pooling<float>*>(ops_[i].get());
+            exb_pool_desc d = pool->desc(x.N, x.H, x.W, x.C, x.cs, EXB_F16);
+            int PH, PW;
+            exb_check(exb_pool_out_dims(&d, &PH, &PW), "exb_pool_out_dims");
+            y.need_f16 = true;
+            set_shape(y, x.N, x.C, PH, PW);
+            y.cs = x.cs;
+            const void* xin = form_f16(x);
+            void* y1 = form_f16(y);
+            void* y2 = nullptr;
+            const bool fuse_q = y.need_i8 && d.type == 0;   // max commutes with the monotone quantiser
+            if (fuse_q) {
+                d.out2_dtype = EXB_I8;
+                d.out2_scale = y.i8_scale;
+                y2 = form_i8(y);
+            }
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_pool2d_fwd(ctx, &d, xin, y1, y2, st), "exb_pool2d_fwd");
+            });
+            finish_forms(y, fuse_q);
+        } else if (t == "innerproduct") {
+            auto* fc = dynamic_cast<operation_innerproduct<float>*>(ops_[i].get());
+            if (x.H != 1 || x.W != 1) NOT_IMPLEMENTED << " (fused InnerProduct needs a 1x1 input map; call set_fusion(false))";
+            CHECK_EQ(x.C, fc->in_features());
+            exb_conv_desc d = fc->fc_desc(x.N, x.cs);
+            y.N = x.N; y.C = fc->num_output_; y.H = 1; y.W = 1; y.cs = y.C;
+            y.need_f32 = true;
+            const void* xin = form_f16(x);
+            void* yo = form_f32(y);
+            exb_conv_weights* w = fc->packed(ctx, d);
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_conv2d_fwd(ctx, &d, xin, w, nullptr, yo, nullptr, st), "exb_conv2d_fwd");
+            });
+            y.produced = true;
+            if (!output_roots.count(root(out_ids[i][0])) || consumers[root(out_ids[i][0])].size())
+                NOT_IMPLEMENTED << " (fused plan: InnerProduct must be a pipeline output)";
+        } else {
+            // element-wise ops on the fp16 form
+            y.need_f16 = true;
+            set_shape(y, x.N, x.C, x.H, x.W);
+            y.cs = x.cs;
+            const int64_t count = (int64_t)x.N * x.H * x.W * x.cs;
+            void* yo = form_f16(y);
+            if (t == "relu" || t == "clip" || t == "sigmoid") {
+                const int act = act_of_op((int)i);
+                if (act < 0) NOT_IMPLEMENTED << " (" << params_[i].type_ << " parameters)";
+                const void* xin = form_f16(x);
+                add_step(params_[i].name_, [=](cudaStream_t st) {
+                    exb_check(exb_activation_fwd(ctx, act, xin, yo, count, EXB_F16, st), "exb_activation_fwd");
+                });
+            } else if (t == "binaryop") {
+                auto* b = dynamic_cast<operation_binaryop<float>*>(ops_[i].get());
+                const void* a = form_f16(x);
+                const int op = b->op_type_;
+                if (b->with_scalar_) {
+                    const float s = b->coef_;
+                    add_step(params_[i].name_, [=](cudaStream_t st) {
+                        exb_check(exb_binaryop_scalar_fwd(ctx, op, a, s, yo, count, EXB_F16, st), "exb_binaryop_scalar_fwd");
+                    });
+                } else {
+                    fmap_info& x2 = fmaps_[root(in_ids[i][1])];
+                    CHECK(x2.produced && x2.N == x.N && x2.C == x.C && x2.H == x.H && x2.W == x.W) << "BinaryOp operands differ in shape";
+                    const void* bb = form_f16(x2);
+                    add_step(params_[i].name_, [=](cudaStream_t st) {
+                        exb_check(exb_binaryop_fwd(ctx, op, a, bb, yo, count, EXB_F16, st), "exb_binaryop_fwd");
+                    });
+                }
+            } else if (t == "eltwise") {
+                auto* e = dynamic_cast<operation_eltwise<float>*>(ops_[i].get());
+                auto xs = std::make_shared<std::vector<const void*>>();
+                auto cf = std::make_shared<std::vector<float>>();
+                for (size_t k = 0; k < in_ids[i].size(); ++k) {
+                    fmap_info& xi = fmaps_[root(in_ids[i][k])];
+                    CHECK(xi.produced && xi.C == x.C && xi.H == x.H && xi.W == x.W) << "Eltwise operands differ in shape";
+                    xs->push_back(form_f16(xi));
+                    cf->push_back(k < e->coeffs_.size() ? e->coeffs_[k] : 1.f);
+                }
+                const int type = e->type_;
+                add_step(params_[i].name_, [=](cudaStream_t st) {
+                    exb_check(exb_eltwise_fwd(ctx, type, (int)xs->size(), xs->data(), cf->data(), yo, count, EXB_F16, st),
+                              "exb_eltwise_fwd");
+                });
+            } else {
+                LOG(FATAL) << "fused plan: unexpected operation type " << params_[i].type_;
+            }
+            finish_forms(y, false);
+        }
+    }
+
+    // ---- 5. outputs: fp32 NCHW on the device, then one D2H each -------------------------------
+    host_out_.clear();
+    for (const auto& name : outputs_) {
+        fmap_info& f = fmaps_[root(fid(name))];
+        CHECK(f.produced) << "output " << name << " is never produced";
+        auto t = std::shared_ptr<memory::tensor<float>>(
+            new memory::tensor<float>(std::vector<int>{f.N, f.C, f.H, f.W}, device_, memory::NCHW, nullptr));
+        host_out_[name] = t;
+        if (f.need_f32 && f.f32 && f.H == 1 && f.W == 1) continue;   // already fp32 [N][C]
+        const void* src = form_f16(f);
+        float* dst = static_cast<float*>(form_f32(f));
+        const int n = f.N, c = f.C, h = f.H, w = f.W, cs = f.cs;
+        add_step("emit " + name, [=](cudaStream_t st) {
+            exb_check(exb_nhwc_to_nchw_f32(ctx, src, EXB_F16, dst, n, c, h, w, cs, 1.f, st), "exb_nhwc_to_nchw_f32");
+        });
+    }
+    N_ = N; C_ = C; H_ = H; W_ = W;
+    built_ = true;
+}
+
+void fused_plan::run(const float* host_input, bool use_graph, bool profile, std::vector<trace_event>* trace) {
+    CUDA_CHECK(cudaSetDevice(device_));
+    const size_t in_bytes = (size_t)N_ * C_ * H_ * W_ * 4;
+    CUDA_CHECK(cudaMemcpyAsync(staging_in_.p, host_input, in_bytes, cudaMemcpyHostToDevice, stream_));
+    launches_ = 0;
+    for (auto& s : steps_) launches_ += s.launches;
+    if (profile) {
+        // per-step device times; never replayed from the graph so every step can be bracketed
+        std::vector<cudaEvent_t> evs(steps_.size() + 1);
+        for (auto& e : evs) CUDA_CHECK(cudaEventCreate(&e));
+        CUDA_CHECK(cudaEventRecord(evs[0], stream_));
+        for (size_t i = 0; i < steps_.size(); ++i) {
+            steps_[i].run(stream_);
+            CUDA_CHECK(cudaEventRecord(evs[i + 1], stream_));
+        }
+        CUDA_CHECK(cudaStreamSynchronize(stream_));
+        if (trace) {
+            trace->clear();
+            for (size_t i = 0; i < steps_.size(); ++i) {
+                float b = 0, e = 0;
+                cudaEventElapsedTime(&b, evs[0], evs[i]);
+                cudaEventElapsedTime(&e, evs[0], evs[i + 1]);
+                trace->push_back({steps_[i].name, b, e});
+            }
+        }
+        float total = 0;
+        cudaEventElapsedTime(&total, evs[0], evs.back());
+        device_ms_ = total;
+        for (auto& e : evs) cudaEventDestroy(e);
+    } else {
+        CUDA_CHECK(cudaEventRecord(ev0_, stream_));
+        if (use_graph && warmed_) {   // the first forward runs eagerly, the second one captures
+            if (!graph_exec_) {
+                cudaGraph_t graph = nullptr;
+                CUDA_CHECK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+                for (auto& s : steps_) s.run(stream_);
+                CUDA_CHECK(cudaStreamEndCapture(stream_, &graph));
+                CUDA_CHECK(cudaGraphInstantiate(&graph_exec_, graph, 0));
+                cudaGraphDestroy(graph);
+            }
+            CUDA_CHECK(cudaGraphLaunch(graph_exec_, stream_));
+        } else {
+            for (auto& s : steps_) s.run(stream_);
+            warmed_ = true;
+        }
+        CUDA_CHECK(cudaEventRecord(ev1_, stream_));
+    }
+    for (auto& kv : host_out_) {
+        fmap_info& f = fmaps_[root(index_[kv.first])];
+        CUDA_CHECK(cudaMemcpyAsync(kv.second->mutable_cpu_data(), f.f32->p, (size_t)f.N * f.C * f.H * f.W * 4,
+                                   cudaMemcpyDeviceToHost, stream_));
+    }
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+    if (!profile) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, ev0_, ev1_);
+        device_ms_ = ms;
+    }
+    exb_check(exb_ctx_sync_check(ctx_, stream_), "fused forward");
+}
+
+std::shared_ptr<memory::tensor<float>> fused_plan::fetch(const std::string& name) {
+    auto it = index_.find(name);
+    if (it == index_.end()) return nullptr;
+    fmap_info& f = fmaps_[root(it->second)];
+    if (!f.produced) {
+        LOG(WARNING) << "feature map " << name << " was fused into its consumer and is not materialised; "
+                        "call set_fusion(false) to inspect it";
+        return nullptr;
+    }
+    auto t = std::shared_ptr<memory::tensor<float>>(
+        new memory::tensor<float>(std::vector<int>{f.N, f.C, f.H, f.W}, device_, memory::NCHW, nullptr));
+    if (f.f32 && f.need_f32 && !f.f16) {
+        CUDA_CHECK(cudaMemcpy(t->mutable_cpu_data(), f.f32->p, (size_t)t->count() * 4, cudaMemcpyDeviceToHost));
+        return t;
+    }
+    const void* src = f.f16 ? f.f16->p : (f.i8 ? f.i8->p : nullptr);
+    if (!src) return nullptr;
+    const int dt = f.f16 ? EXB_F16 : EXB_I8;
+    const float scale = f.f16 ? 1.f : 1.f / f.i8_scale;
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+    exb_check(exb_nhwc_to_nchw_f32(ctx_, src, dt, t->mutable_gpu_data(), f.N, f.C, f.H, f.W, f.cs, scale, nullptr),
+              "exb_nhwc_to_nchw_f32");
+    CUDA_CHECK(cudaDeviceSynchronize());
+    t->cpu_data();
+    return t;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+// impl
+// ------------------------------------------------------------------------------------------
+template <typename Dtype>
+class pipeline<Dtype>::impl {
+public:
+    impl() {}
+    impl(std::string_view param_file, std::string_view model_file, int device)
+        : impl(read_lines(param_file), model_file, device) {}
+    impl(const std::vector<std::string>& lines, std::string_view model_file, int device) {
+        device_ = device;
+        if (device >= 0) CUDA_CHECK(cudaSetDevice(device));   // select the device BEFORE creating any handle
+        if (lines.empty()) LOG(FATAL) << "Incorrect param file.";
+        auto head = split_string(lines[0], " ");
+        if (head.empty() || (head[0] != "glsv1" && head[0] != "7767517")) LOG(FATAL) << "Incorrect param file version.";
+        if (head.size() > 1) name_ = head[1];
+        for (size_t i = 2; i < lines.size(); ++i) {   // line 1 (op / feature map counts) is not used
+            std::vector<std::string> tok;
+            for (auto& s : split_string(lines[i], " "))
+                if (!s.empty()) tok.push_back(s);
+            if (tok.empty()) continue;
+            if (tok.size() < 4) LOG(FATAL) << "malformed operation line: " << lines[i];
+            operation_param p;
+            p.type_ = tok[0];
+            p.name_ = tok[1];
+            p.device_ = device_;
+            p.input_count_ = std::atoi(tok[2].c_str());
+            p.output_count_ = std::atoi(tok[3].c_str());
+            const int n_in = p.input_count_ > 0 ? p.input_count_ : 0, n_out = p.output_count_ > 0 ? p.output_count_ : 0;
+            if ((int)tok.size() < 4 + n_in + n_out) LOG(FATAL) << "operation line lists fewer feature maps than it declares: " << lines[i];
+            for (int j = 0; j < n_out; ++j) p.output_featmaps_.push_back(tok[4 + n_in + j]);
+            for (size_t j = 4 + n_in + n_out; j < tok.size(); ++j) p.specific_params_ += tok[j] + " ";
+            if (p.input_count_ <= 0) {
+                p.input_count_ = 1;   // an op without inputs takes the implicit "<name>_input"
+                p.input_featmaps_ = {p.name_ + "_input"};
+            } else {
+                for (int j = 0; j < n_in; ++j) p.input_featmaps_.push_back(tok[4 + j]);
+            }
+            op_params_.push_back(p);
+        }
+        for (auto& p : op_params_) operations_.push_back(operation_reflector<Dtype>::instance().create_object(p));
+        if (model_file.empty()) {
+            LOG(WARNING) << "THIS PIPELINE IS LOADED WITH DUMMY DATA.";
+            for (auto& op : operations_) weights_mem_cost_ += op->init_weights();
+        } else {
+            FILE* fp = fopen(std::string(model_file).c_str(), "rb");
+            if (!fp) LOG(FATAL) << "Cannot open " << model_file;
+            for (auto& op : operations_) weights_mem_cost_ += op->init_weights(fp);
+            CHECK_EQ(fclose(fp), 0) << "Cannot close " << model_file;
+        }
+        // feature map table; inputs = consumed but never produced, outputs = produced but never consumed
+        std::set<std::string> produced, consumed;
+        for (auto& p : op_params_) {
+            for (auto& n : p.output_featmaps_) produced.insert(n);
+            for (auto& n : p.input_featmaps_) consumed.insert(n);
+        }
+        for (auto& p : op_params_) {
+            for (auto& n : p.input_featmaps_) {
+                index_of(n);
+                if (!produced.count(n) && std::find(input_names_.begin(), input_names_.end(), n) == input_names_.end())
+                    input_names_.push_back(n);
+            }
+            for (auto& n : p.output_featmaps_) {
+                index_of(n);
+                if (!consumed.count(n)) output_names_.push_back(n);
+            }
+        }
+        featmaps_.resize(featmap_index_.size());
+        if (input_names_.empty()) LOG(FATAL) << "the graph has no input feature map";
+    }
+    ~impl() {
+        plan_.reset();
+        if (ctx_) exb_ctx_destroy(ctx_);
+    }
+
+    result_map forward(const std::shared_ptr<memory::tensor<Dtype>>& input) {
+        if (device_ >= 0) return forward_gpu(input);
+        return forward_cpu(input);
+    }
+    result_map forward_cpu(const std::shared_ptr<memory::tensor<Dtype>>&) {
+        NO_CPU;
+        return {};
+    }
+    result_map forward_gpu(const std::shared_ptr<memory::tensor<Dtype>>& input);
+    std::shared_ptr<memory::tensor<Dtype>> get_featmap(std::string_view name);
+
+    int index_of(const std::string& n) {
+        auto it = featmap_index_.find(n);
+        if (it != featmap_index_.end()) return it->second;
+        int id = (int)featmap_index_.size();
+        featmap_index_[n] = id;
+        return id;
+    }
+    result_map forward_unfused(const std::shared_ptr<memory::tensor<Dtype>>& input);
+
+    std::string name_;
+    int device_ = -1;
+    std::vector<operation_param> op_params_;
+    std::vector<std::shared_ptr<operation<Dtype>>> operations_;
+    std::unordered_map<std::string, int> featmap_index_;
+    std::vector<std::shared_ptr<memory::tensor<Dtype>>> featmaps_;
+    std::vector<std::string> input_names_, output_names_;
+    int weights_mem_cost_ = 0;
+    bool profile_ = false, fusion_ = true, graph_ = true;
+    bool used_fused_ = false;
+    exb_ctx* ctx_ = nullptr;
+    std::unique_ptr<fused_plan> plan_;
+    std::vector<trace_event> trace_;
+    int launches_ = 0;
+    double device_ms_ = 0.0;
+};
+
+// Op-by-op execution in file order with the reference's tensor semantics.
+template <typename Dtype>
+typename pipeline<Dtype>::result_map pipeline<Dtype>::impl::forward_unfused(
+    const std::shared_ptr<memory::tensor<Dtype>>& input) {
+    if (!ctx_) exb_check(exb_ctx_create(device_, &ctx_), "exb_ctx_create");
+    featmaps_[featmap_index_[input_names_[0]]] = input;
+    trace_.clear();
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (profile_) {
+        CUDA_CHECK(cudaEventCreate(&e0));
+        CUDA_CHECK(cudaEventCreate(&e1));
+    }
+    float t_acc = 0.f;
+    for (size_t i = 0; i < operations_.size(); ++i) {
+        const auto& p = op_params_[i];
+        std::vector<std::shared_ptr<memory::tensor<Dtype>>> in(p.input_featmaps_.size()), out(p.output_featmaps_.size());
+        for (size_t j = 0; j < in.size(); ++j) {
+            in[j] = featmaps_[featmap_index_[p.input_featmaps_[j]]];
+            if (!in[j]) LOG(FATAL) << "feature map " << p.input_featmaps_[j] << " is not available for " << p.name_;
+        }
+        if (profile_) CUDA_CHECK(cudaEventRecord(e0, nullptr));
+        operations_[i]->forward_gpu(ctx_, in, out);
+        if (profile_) {
+            CUDA_CHECK(cudaEventRecord(e1, nullptr));
+            CUDA_CHECK(cudaEventSynchronize(e1));
+            float ms = 0;
+            cudaEventElapsedTime(&ms, e0, e1);
+            trace_.push_back({p.name_, t_acc, t_acc + ms});
+            t_acc += ms;
+        }
+        for (size_t j = 0; j < out.size(); ++j) featmaps_[featmap_index_[p.output_featmaps_[j]]] = out[j];
+    }
+    if (profile_) {
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+    }
+    exb_check(exb_ctx_sync_check(ctx_, nullptr), "forward");
+    result_map results;
+    for (auto& n : output_names_) {
+        results[n] = featmaps_[featmap_index_[n]];
+        if (results[n]) results[n]->cpu_data();   // bring the result to the host, as a caller of the reference would read it
+    }
+    launches_ = -1;
+    return results;
+}
+
+template <typename Dtype>
+typename pipeline<Dtype>::result_map pipeline<Dtype>::impl::forward_gpu(
+    const std::shared_ptr<memory::tensor<Dtype>>& input) {
+    if (device_ < 0) NO_GPU;
+    CHECK(input != nullptr && !input->empty()) << "empty input tensor";
+    used_fused_ = false;
+    return forward_unfused(input);
+}
+
+template <>
+pipeline<float>::result_map pipeline<float>::impl::forward_gpu(const std::shared_ptr<memory::tensor<float>>& input) {
+    if (device_ < 0) NO_GPU;
+    CHECK(input != nullptr && !input->empty()) << "empty input tensor";
+    if (fusion_) {
+        if (!plan_) plan_.reset(new fused_plan(op_params_, operations_, input_names_, output_names_, device_));
+        const std::string why = plan_->unsupported_reason();
+        if (why.empty()) {
+            if (input->order() == memory::NHWC) input->convert_order();
+            const int N = input->num(), C = input->channels(), H = input->height(), W = input->width();
+            if (!plan_->built_for(N, C, H, W)) plan_->build(N, C, H, W);
+            plan_->run(input->cpu_data(), graph_, profile_, &trace_);
+            launches_ = plan_->launches();
+            device_ms_ = plan_->device_ms();
+            used_fused_ = true;
+            return plan_->host_out_;
+        }
+        LOG(WARNING) << "running op by op: " << why;
+    }
+    used_fused_ = false;
+    return forward_unfused(input);
+}
+
+template <typename Dtype>
+std::shared_ptr<memory::tensor<Dtype>> pipeline<Dtype>::impl::get_featmap(std::string_view name) {
+    auto it = featmap_index_.find(std::string(name));
+    if (it == featmap_index_.end()) return nullptr;
+    return featmaps_[it->second];
+}
+template <>
+std::shared_ptr<memory::tensor<float>> pipeline<float>::impl::get_featmap(std::string_view name) {
+    if (used_fused_ && plan_) return plan_->fetch(std::string(name));
+    auto it = featmap_index_.find(std::string(name));
+    if (it == featmap_index_.end()) return nullptr;
+    return featmaps_[it->second];
+}
+
+// ------------------------------------------------------------------------------------------
+// public wrappers
+// ------------------------------------------------------------------------------------------
+template <typename Dtype> pipeline<Dtype>::pipeline() : impl_{new impl} {}
+template <typename Dtype>
+pipeline<Dtype>::pipeline(std::string_view param_file, std::string_view model_file, int device)
+    : impl_{new impl{param_file, model_file, device}} {}
+template <typename Dtype>
+pipeline<Dtype>::pipeline(std::string_view param_file, int device) : impl_{new impl{param_file, std::string_view{}, device}} {}
+template <typename Dtype>
+pipeline<Dtype>::pipeline(const std::vector<std::string>& lines, std::string_view model_file, int device)
+    : impl_{new impl{lines, model_file, device}} {}
+template <typename Dtype> pipeline<Dtype>::~pipeline() { delete impl_; }
+
+template <typename Dtype>
+typename pipeline<Dtype>::result_map pipeline<Dtype>::forward(const std::shared_ptr<memory::tensor<Dtype>>& t) { return impl_->forward(t); }
+template <typename Dtype>
+typename pipeline<Dtype>::result_map pipeline<Dtype>::forward_cpu(const std::shared_ptr<memory::tensor<Dtype>>& t) { return impl_->forward_cpu(t); }
+template <typename Dtype>
+typename pipeline<Dtype>::result_map pipeline<Dtype>::forward_gpu(const std::shared_ptr<memory::tensor<Dtype>>& t) { return impl_->forward_gpu(t); }
+template <typename Dtype>
+std::shared_ptr<memory::tensor<Dtype>> pipeline<Dtype>::get_featmap(std::string_view n) { return impl_->get_featmap(n); }
+template <typename Dtype> void pipeline<Dtype>::enable_profiler() { impl_->profile_ = true; }
+template <typename Dtype> void pipeline<Dtype>::disable_profiler() { impl_->profile_ = false; }
+template <typename Dtype> void pipeline<Dtype>::set_fusion(bool on) { impl_->fusion_ = on; }
+template <typename Dtype> void pipeline<Dtype>::set_cuda_graph(bool on) { impl_->graph_ = on; }
+template <typename Dtype> int pipeline<Dtype>::launches_last_forward() const { return impl_->launches_; }
+template <typename Dtype> double pipeline<Dtype>::device_ms_last_forward() const { return impl_->device_ms_; }
+template <typename Dtype> std::vector<std::string> pipeline<Dtype>::input_names() const { return impl_->input_names_; }
+template <typename Dtype> std::vector<std::string> pipeline<Dtype>::output_names() const { return impl_->output_names_; }
+template <typename Dtype> std::string pipeline<Dtype>::version() { return exb_version(); }
+
+template <typename Dtype>
+bool pipeline<Dtype>::dump_profile(std::string_view path) {
+    std::ofstream out{std::string(path)};
+    if (!out) return false;
+    out << "{\"traceEvents\":[";
+    bool first = true;
+    for (auto& e : impl_->trace_) {
+        for (int k = 0; k < 2; ++k) {
+            if (!first) out << ",";
+            first = false;
+            out << "{\"name\":\"" << e.name << "\",\"cat\":\"op\",\"ph\":\"" << (k ? "E" : "B") << "\",\"pid\":0,\"tid\":0,\"ts\":"
+                << (double)(k ? e.end_ms : e.begin_ms) * 1000.0 << "}";
+        }
+    }
+    out << "]}";
+    return true;
+}
+
+INSTANCE_CLASS(pipeline);
+
+}  // namespace excalibur
+}  // namespace glasssix

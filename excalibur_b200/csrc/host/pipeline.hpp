@@ -1,0 +1,56 @@
+// Graph executor with the reference's public interface (include/Excalibur/pipeline.hpp:18-45):
+// parse a .phai description, create operations through the reflector, load .racy weights in
+// file order, run forward.  pipeline<float> on a GPU device additionally builds a FUSED plan
+// (Conv + ReLU, Conv + residual add + ReLU, requantisation to the next int8 conv's scale, NHWC
+// fp16/int8 tensors between kernels, CUDA-graph replay); set_fusion(false) runs op by op with
+// the reference's tensor semantics instead.
+#pragma once
+#include <string>
+#include <string_view>
+#include <unordered_map>
+#include <vector>
+
+#include "operation.hpp"
+
+namespace glasssix {
+namespace excalibur {
+
+template <typename Dtype>
+class EXB_HOST_API pipeline {
+public:
+    class impl;
+    typedef std::unordered_map<std::string, std::shared_ptr<memory::tensor<Dtype>>> result_map;
+
+    explicit pipeline();
+    explicit pipeline(std::string_view param_file, std::string_view model_file, int device = -1);
+    explicit pipeline(std::string_view param_file, int device = -1);
+    explicit pipeline(const std::vector<std::string>& hardcode_params, std::string_view model_file, int device = -1);
+    ~pipeline();
+
+    result_map forward(const std::shared_ptr<memory::tensor<Dtype>>& input_tensor);
+    result_map forward_cpu(const std::shared_ptr<memory::tensor<Dtype>>& input_tensor);
+    result_map forward_gpu(const std::shared_ptr<memory::tensor<Dtype>>& input_tensor);
+    std::shared_ptr<memory::tensor<Dtype>> get_featmap(std::string_view featmap_name);
+
+    void enable_profiler();
+    void disable_profiler();
+    // chrome://tracing JSON of the last profiled forward ("B"/"E" events per op, device time).
+    bool dump_profile(std::string_view path);
+
+    // Extras of this implementation.
+    void set_fusion(bool on);            // default on for pipeline<float> on a GPU
+    void set_cuda_graph(bool on);        // replay the fused plan as a CUDA graph (default on)
+    int launches_last_forward() const;   // kernels launched by the last forward
+    double device_ms_last_forward() const;   // device time of the last forward's kernels (events)
+    std::vector<std::string> input_names() const;
+    std::vector<std::string> output_names() const;
+
+    static std::string version();
+
+private:
+    impl* impl_;
+    DISABLE_COPY_AND_ASSIGN(pipeline);
+};
+
+}  // namespace excalibur
+}  // namespace glasssix

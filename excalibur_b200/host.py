@@ -1,0 +1,152 @@
+"""ctypes binding of the C++ host layer (include/excalibur_b200_host.h): pipeline<float> and single
+operations created through the operation reflector, driven with numpy / pinned torch buffers."""
+import ctypes as C
+import os
+import tempfile
+
+import numpy as np
+
+from . import capi
+
+EXB_HOST_FATAL = -100
+HOST_SYMBOLS = [
+    "exb_host_last_error", "exb_host_registered", "exb_host_pipeline_create", "exb_host_pipeline_destroy",
+    "exb_host_pipeline_set_option", "exb_host_pipeline_forward", "exb_host_pipeline_num_outputs",
+    "exb_host_pipeline_output_name", "exb_host_pipeline_get", "exb_host_pipeline_stats",
+    "exb_host_pipeline_dump_profile", "exb_host_op_run",
+]
+_READY = False
+
+
+class HostError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("excalibur_b200 host error %d: %s" % (code, msg))
+        self.code = code
+
+
+def lib():
+    global _READY
+    L = capi.lib()
+    if not _READY:
+        vp, i32 = C.c_void_p, C.c_int
+        L.exb_host_last_error.restype = C.c_char_p
+        L.exb_host_registered.argtypes = [C.c_char_p]
+        L.exb_host_pipeline_create.argtypes = [C.c_char_p, C.c_char_p, i32, C.POINTER(vp)]
+        L.exb_host_pipeline_destroy.argtypes = [vp]
+        L.exb_host_pipeline_set_option.argtypes = [vp, C.c_char_p, i32]
+        L.exb_host_pipeline_forward.argtypes = [vp, vp, i32, i32, i32, i32]
+        L.exb_host_pipeline_num_outputs.argtypes = [vp]
+        L.exb_host_pipeline_output_name.argtypes = [vp, i32, C.c_char_p, i32]
+        L.exb_host_pipeline_get.argtypes = [vp, C.c_char_p, vp, C.c_int64, vp]
+        L.exb_host_pipeline_stats.argtypes = [vp, C.POINTER(i32), C.POINTER(C.c_double)]
+        L.exb_host_pipeline_dump_profile.argtypes = [vp, C.c_char_p]
+        L.exb_host_op_run.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, i32, i32, C.POINTER(vp), vp, vp,
+                                      C.c_int64, vp]
+        _READY = True
+    return L
+
+
+def _check(rc):
+    if rc == EXB_HOST_FATAL:
+        raise HostError(rc, lib().exb_host_last_error().decode())
+    if rc != 0:
+        msg = lib().exb_host_last_error().decode()
+        raise HostError(rc, msg if msg != "no error" else capi.last_error())
+
+
+def registered(class_name):
+    return bool(lib().exb_host_registered(class_name.encode()))
+
+
+class Pipeline:
+    """glasssix::excalibur::pipeline<float> on a GPU device."""
+
+    def __init__(self, phai_text, racy_bytes=b"", device=0, fusion=True, cuda_graph=True):
+        self._h = C.c_void_p()
+        self._tmp = None
+        path = b""
+        if racy_bytes:
+            self._tmp = tempfile.NamedTemporaryFile(suffix=".racy", delete=False)
+            self._tmp.write(racy_bytes)
+            self._tmp.close()
+            path = self._tmp.name.encode()
+        _check(lib().exb_host_pipeline_create(phai_text.encode(), path, device, C.byref(self._h)))
+        self.set_option("fusion", int(fusion))
+        self.set_option("cuda_graph", int(cuda_graph))
+
+    def set_option(self, key, value):
+        _check(lib().exb_host_pipeline_set_option(self._h, key.encode(), int(value)))
+
+    def forward_ptr(self, host_ptr, N, Cc, H, W):
+        """forward() on caller-owned host memory (fp32 NCHW); returns nothing, see get()."""
+        _check(lib().exb_host_pipeline_forward(self._h, C.c_void_p(host_ptr), N, Cc, H, W))
+
+    def forward(self, x_nchw):
+        x = np.ascontiguousarray(x_nchw, np.float32)
+        self._keep = x
+        self.forward_ptr(x.ctypes.data, *x.shape)
+        return {n: self.get(n) for n in self.output_names()}
+
+    def output_names(self):
+        buf = C.create_string_buffer(256)
+        names = []
+        for i in range(lib().exb_host_pipeline_num_outputs(self._h)):
+            _check(lib().exb_host_pipeline_output_name(self._h, i, buf, 256))
+            names.append(buf.value.decode())
+        return names
+
+    def get(self, name, out=None):
+        shp = (C.c_int * 4)()
+        _check(lib().exb_host_pipeline_get(self._h, name.encode(), None, 0, shp))
+        if out is None:
+            out = np.empty(tuple(shp), np.float32)
+        _check(lib().exb_host_pipeline_get(self._h, name.encode(), out.ctypes.data, out.size, shp))
+        return out
+
+    def stats(self):
+        n, ms = C.c_int(), C.c_double()
+        lib().exb_host_pipeline_stats(self._h, C.byref(n), C.byref(ms))
+        return n.value, ms.value
+
+    def dump_profile(self, path):
+        _check(lib().exb_host_pipeline_dump_profile(self._h, path.encode()))
+
+    def close(self):
+        if self._h:
+            lib().exb_host_pipeline_destroy(self._h)
+            self._h = C.c_void_p()
+        if self._tmp is not None:
+            os.unlink(self._tmp.name)
+            self._tmp = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def run_op(type_, params, inputs, racy_bytes=None, device=0):
+    """Create one operation through the reflector and run its forward_gpu on fp32 NCHW arrays."""
+    ins = [np.ascontiguousarray(a, np.float32) for a in inputs]
+    ptrs = (C.c_void_p * len(ins))(*[a.ctypes.data for a in ins])
+    shapes = np.array([list(a.shape) for a in ins], np.int32)
+    tmp = None
+    path = b""
+    if racy_bytes:
+        tmp = tempfile.NamedTemporaryFile(suffix=".racy", delete=False)
+        tmp.write(racy_bytes)
+        tmp.close()
+        path = tmp.name.encode()
+    try:
+        shp = (C.c_int * 4)()
+        # the output shape is only known after running, so run into a generous buffer
+        cap = max(int(a.size) for a in ins) * 64 + 1024
+        out = np.empty(cap, np.float32)
+        _check(lib().exb_host_op_run(type_.encode(), params.encode(), path, device, len(ins), ptrs,
+                                     shapes.ctypes.data, out.ctypes.data, cap, shp))
+        n = int(np.prod(tuple(shp)))
+        return out[:n].reshape(tuple(shp)).copy()
+    finally:
+        if tmp is not None:
+            os.unlink(tmp.name)

@@ -1,0 +1,65 @@
+/*
+ * excalibur_b200 - C entry points of the C++ host layer (excalibur_b200/csrc/host/), for
+ * harnesses that cannot include C++ headers (the Python tests and the benchmark).
+ *
+ * The host layer mirrors the reference's operation plug-in API and graph executor:
+ *   glasssix::excalibur::operation<Dtype>, operation_reflector<Dtype>, REGISTE(...)
+ *       (reference include/Excalibur/operation.hpp:109-374, operation_reflector.hpp:16-93)
+ *   glasssix::excalibur::pipeline<Dtype>
+ *       (reference include/Excalibur/pipeline.hpp:18-45)
+ * C++ users include excalibur_b200/csrc/host/pipeline.hpp directly; these functions wrap
+ * pipeline<float> and single operations created through the reflector.  LOG(FATAL) / CHECK
+ * failures inside the host layer (which terminate the process in the reference,
+ * include/Primitives/logger.hpp:101-118) are turned into the status EXB_HOST_FATAL here and the
+ * message is kept for exb_host_last_error().
+ */
+#ifndef EXCALIBUR_B200_HOST_H_
+#define EXCALIBUR_B200_HOST_H_
+
+#include <stdint.h>
+
+#include "excalibur_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EXB_HOST_FATAL (-100)
+
+EXB_API const char* exb_host_last_error(void);
+
+/* 1 when an operation class is registered under `class_name` (e.g. "operation_convolution")
+ * for pipeline<float>; mirrors operation_reflector<float>::create_object's key lookup. */
+EXB_API int exb_host_registered(const char* class_name);
+
+/* pipeline<float>(lines of a .phai file, .racy path or "" for seeded dummy weights, device)
+ * - reference include/Excalibur/pipeline.hpp:26. */
+EXB_API int exb_host_pipeline_create(const char* phai_text, const char* racy_path, int device,
+                                     void** out);
+EXB_API int exb_host_pipeline_destroy(void* p);
+/* key: "fusion" (fused NHWC plan, default 1), "cuda_graph" (default 1), "profile" (0/1 =
+ * disable_profiler / enable_profiler, reference pipeline.hpp:38-39). */
+EXB_API int exb_host_pipeline_set_option(void* p, const char* key, int value);
+/* forward(): `input` is HOST memory, fp32 NCHW; it is wrapped, not copied (page-locked memory
+ * makes the upload asynchronous).  The call returns when the outputs are back on the host. */
+EXB_API int exb_host_pipeline_forward(void* p, const float* input, int N, int C, int H, int W);
+EXB_API int exb_host_pipeline_num_outputs(void* p);
+EXB_API int exb_host_pipeline_output_name(void* p, int i, char* buf, int cap);
+/* Output or any feature map by name (pipeline::get_featmap, pipeline.hpp:32).  out == NULL
+ * returns only the shape; the data is fp32 NCHW. */
+EXB_API int exb_host_pipeline_get(void* p, const char* name, float* out, int64_t cap, int* shape4);
+/* Kernels launched by the last forward (-1 when run op by op) and their device time in ms. */
+EXB_API int exb_host_pipeline_stats(void* p, int* launches, double* device_ms);
+EXB_API int exb_host_pipeline_dump_profile(void* p, const char* path);
+
+/* One operation through the reflector, the way pipeline does it: create_object(param),
+ * init_weights(FILE*) from `racy_path` (or init_weights() when NULL/""), forward_gpu on fp32
+ * NCHW host arrays.  shapes = 4 ints per input.  out == NULL returns only the shape. */
+EXB_API int exb_host_op_run(const char* type, const char* params, const char* racy_path, int device,
+                            int n_in, const float* const* inputs, const int* shapes, float* out,
+                            int64_t cap, int* out_shape4);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXCALIBUR_B200_HOST_H_ */

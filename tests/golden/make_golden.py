@@ -1,0 +1,147 @@
+"""Generate tests/golden/reference_vectors.npz from the UNMODIFIED reference CPU library.
+
+Run in a container that has the reference tree (it cannot travel to the GPU box):
+
+    make -C oracle ref            # builds oracle/_ref/libexcalibur_ref.so from the reference sources
+    python tests/golden/make_golden.py
+
+Every case stores its inputs, weights and the reference's output, so the fixture pins the oracle
+(oracle/exb_oracle.c) and, through it, the CUDA kernels, without the reference being present.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from excalibur_b200 import models  # noqa: E402
+from excalibur_b200.modelfile import GraphBuilder  # noqa: E402
+from oracle import ref_lib  # noqa: E402
+
+
+def run(g, x, names=("out",)):
+    p = ref_lib.RefPipeline(g.phai_text(), g.racy_bytes())
+    p.forward(x)
+    outs = [p.featmap(n) for n in names]
+    p.close()
+    return outs
+
+
+def main():
+    assert ref_lib.available(), "build oracle/_ref first: make -C oracle ref"
+    r = np.random.default_rng(20240607)
+    out = {}
+
+    def conv_case(tag, N, Cin, H, W, Cout, k, stride, pad, act, int8):
+        x = r.uniform(-1, 1, (N, Cin, H, W)).astype(np.float32)
+        w = (r.standard_normal((Cout, Cin, k, k)) * np.sqrt(2.0 / (Cin * k * k))).astype(np.float32)
+        b = (r.standard_normal(Cout) * 0.05).astype(np.float32)
+        g = GraphBuilder()
+        i8 = None
+        if int8:
+            wq, ws = models.quantize_weights(w)
+            fs = np.float32(127.0 / np.abs(x).max())
+            i8 = (wq, ws, fs)
+            out[tag + "_wq"], out[tag + "_ws"], out[tag + "_fs"] = wq, ws, fs
+        g.conv("c", "in", "out", w, b, stride, pad, act=act, int8=i8)
+        (y,) = run(g, x)
+        out[tag + "_x"], out[tag + "_w"], out[tag + "_b"], out[tag + "_y"] = x, w, b, y
+        out[tag + "_cfg"] = np.array([stride, pad, act], np.int32)
+
+    # fp32: Winograd path (3x3 s1, Cout < 128), packed im2col path (everything else)
+    conv_case("conv_f32_wino", 2, 16, 12, 13, 32, 3, 1, 1, 1, False)
+    conv_case("conv_f32_im2col_s2", 2, 8, 15, 15, 24, 3, 2, 1, 0, False)
+    conv_case("conv_f32_stem", 1, 3, 32, 32, 16, 7, 2, 3, 1, False)
+    conv_case("conv_f32_1x1", 2, 32, 7, 7, 136, 1, 1, 0, 0, False)
+    # int8: Winograd path handles batches; the im2col path only computes image 0, so batch 1
+    conv_case("conv_i8_wino", 2, 32, 10, 10, 64, 3, 1, 1, 1, True)
+    conv_case("conv_i8_im2col_s2", 1, 32, 12, 12, 64, 3, 2, 1, 1, True)
+    conv_case("conv_i8_im2col_wide", 1, 64, 7, 7, 128, 3, 1, 1, 0, True)
+    conv_case("conv_i8_1x1_s2", 1, 32, 8, 8, 64, 1, 2, 0, 0, True)
+
+    # depthwise 3x3 s1 / s2
+    for tag, stride in (("dw_s1", 1), ("dw_s2", 2)):
+        x = r.uniform(-1, 1, (2, 24, 14, 14)).astype(np.float32)
+        w = (r.standard_normal((24, 1, 3, 3)) * 0.3).astype(np.float32)
+        b = (r.standard_normal(24) * 0.1).astype(np.float32)
+        g = GraphBuilder()
+        g.dwconv("d", "in", "out", w, b, stride, 1, act=1)
+        (y,) = run(g, x)
+        out[tag + "_x"], out[tag + "_w"], out[tag + "_b"], out[tag + "_y"] = x, w, b, y
+
+    # pooling
+    x = r.standard_normal((2, 8, 13, 13)).astype(np.float32)
+    out["pool_x"] = x
+    for tag, kw in (("pool_max_3s2p1", dict(type_=0, kernel=3, stride=2, pad=1)),
+                    ("pool_max_5s1p2", dict(type_=0, kernel=5, stride=1, pad=2)),
+                    ("pool_max_ceil", dict(type_=0, kernel=2, stride=2, pad=0, pad_mode=0)),
+                    ("pool_avg_excl", dict(type_=1, kernel=3, stride=2, pad=1, count_include_pad=0)),
+                    ("pool_avg_incl", dict(type_=1, kernel=3, stride=2, pad=1, count_include_pad=1)),
+                    ("pool_gap", dict(type_=1, global_pool=True))):
+        g = GraphBuilder()
+        g.pool("p", "in", "out", **kw)
+        (out[tag + "_y"],) = run(g, x)
+
+    # eltwise / binaryop / relu.  The graph input is fanned out through Split and convolutions so
+    # that the ops see distinct tensors.
+    x = r.standard_normal((2, 6, 9, 9)).astype(np.float32)
+    out["elt_x"] = x
+    g = GraphBuilder()
+    g.split("s", "in", ["a", "b", "c"])
+    g.relu("r", "a", "ra")
+    g.binaryop("m", "b", "c", "bb", op=2)           # x*x
+    g.eltwise("sum", ["ra", "bb", "a"], "esum", 1, coeffs=[0.5, -1.25])   # third coefficient stays 1
+    g.eltwise("prod", ["ra", "bb"], "eprod", 0)
+    g.eltwise("max", ["ra", "bb", "a"], "emax", 2)
+    g.binaryop("add", "esum", "eprod", "out", op=0)
+    p = ref_lib.RefPipeline(g.phai_text(), g.racy_bytes())
+    p.forward(x)
+    for n in ("ra", "bb", "esum", "eprod", "emax", "out"):
+        out["elt_" + n] = p.featmap(n)
+    p.close()
+
+    # ResNet-18-style net at 64x64, batch 2: fp32 and int8 (image-at-a-time because of the
+    # reference's int8 batch quirk), calibration on 4 seeded images through the fp32 reference.
+    seed = 2
+    x = np.random.default_rng(2000).uniform(0, 1, (2, 3, 64, 64)).astype(np.float32)
+    g32, info = models.resnet18(seed)
+    p32 = ref_lib.RefPipeline(g32.phai_text(), g32.racy_bytes())
+    out["resnet_x"] = x
+    out["resnet_f32_logits"] = p32.forward(x)["logits"].reshape(2, -1)
+    out["resnet_f32_s1b1_out"] = p32.featmap("s1b1_out")
+    calib = np.random.default_rng(2007).uniform(0, 1, (4, 3, 64, 64)).astype(np.float32)
+    scales = models.calibrate(_RefAdapter(p32), info["conv_inputs"], calib)
+    p32.close()
+    names = sorted(scales)
+    out["resnet_scale_names"] = np.array(names)
+    out["resnet_scales"] = np.array([scales[n] for n in names], np.float32)
+    g8, _ = models.resnet18(seed, act_scales=scales)
+    p8 = ref_lib.RefPipeline(g8.phai_text(), g8.racy_bytes())
+    logits, s1 = [], []
+    for i in range(2):
+        logits.append(p8.forward(x[i:i + 1])["logits"].reshape(1, -1))
+        s1.append(p8.featmap("s1b1_out"))
+    p8.close()
+    out["resnet_i8_logits"] = np.concatenate(logits)
+    out["resnet_i8_s1b1_out"] = np.concatenate(s1)
+
+    path = os.path.join(ROOT, "tests", "golden", "reference_vectors.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
+
+
+class _RefAdapter:
+    def __init__(self, p):
+        self.p = p
+
+    def forward(self, x):
+        return self.p.forward(x)
+
+    def get(self, name):
+        return self.p.featmap(name)
+
+
+if __name__ == "__main__":
+    main()

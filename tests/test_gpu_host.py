@@ -1,0 +1,160 @@
+"""The C++ host layer (operation classes created through the reflector, pipeline<float>) against
+the reference's own outputs (golden vectors) and the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+
+from excalibur_b200 import models
+from excalibur_b200.modelfile import GraphBuilder
+from oracle import exb_oracle as O
+from tests.util import assert_close_f16, f16_round
+
+pytestmark = pytest.mark.gpu
+G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.npz"))
+
+
+def _host():
+    from excalibur_b200 import host
+    return host
+
+
+def _conv_line_and_blob(w, b, stride, pad, act, int8=None, dw=False):
+    g = GraphBuilder()
+    if dw:
+        g.dwconv("c", "in", "out", w, b, stride, pad, act=act)
+    else:
+        g.conv("c", "in", "out", w, b, stride, pad, act=act, int8=int8)
+    params = g.lines[0].split(" ", 6)[6]
+    return params, g.racy_bytes()
+
+
+@pytest.mark.parametrize("tag", ["conv_i8_wino", "conv_i8_im2col_s2", "conv_i8_im2col_wide", "conv_i8_1x1_s2"])
+def test_operation_convolution_int8_matches_reference_bit_for_bit(tag):
+    """operation_convolution::forward_gpu_i8 on fp32 NCHW tensors == the reference's forward_cpu_i8."""
+    stride, pad, act = [int(v) for v in G[tag + "_cfg"]]
+    params, blob = _conv_line_and_blob(G[tag + "_w"], G[tag + "_b"], stride, pad, act,
+                                       int8=(G[tag + "_wq"], G[tag + "_ws"], G[tag + "_fs"]))
+    y = _host().run_op("Convolution", params, [G[tag + "_x"]], blob)
+    np.testing.assert_array_equal(y, G[tag + "_y"])
+
+
+def test_operation_convolution_int8_batch_is_computed_for_every_image():
+    """The reference's packed int8 path only computes image 0 of a batch; this one computes all."""
+    tag = "conv_i8_im2col_wide"
+    stride, pad, act = [int(v) for v in G[tag + "_cfg"]]
+    x = np.concatenate([G[tag + "_x"], G[tag + "_x"][:, ::-1].copy(), G[tag + "_x"] * 0.5])
+    params, blob = _conv_line_and_blob(G[tag + "_w"], G[tag + "_b"], stride, pad, act,
+                                       int8=(G[tag + "_wq"], G[tag + "_ws"], G[tag + "_fs"]))
+    y = _host().run_op("Convolution", params, [x], blob)
+    ref = O.conv2d_i8(x, G[tag + "_wq"], G[tag + "_b"], G[tag + "_ws"], G[tag + "_fs"], stride, pad, act=act)
+    np.testing.assert_array_equal(y, ref)
+    np.testing.assert_array_equal(y[:1], G[tag + "_y"])
+
+
+@pytest.mark.parametrize("tag", ["conv_f32_wino", "conv_f32_im2col_s2", "conv_f32_stem", "conv_f32_1x1"])
+def test_operation_convolution_fp16_compute_within_1e2_of_reference_fp32(tag):
+    stride, pad, act = [int(v) for v in G[tag + "_cfg"]]
+    params, blob = _conv_line_and_blob(G[tag + "_w"], G[tag + "_b"], stride, pad, act)
+    y = _host().run_op("Convolution", params, [G[tag + "_x"]], blob)
+    assert_close_f16(y, G[tag + "_y"], what=tag)
+
+
+@pytest.mark.parametrize("tag,stride", [("dw_s1", 1), ("dw_s2", 2)])
+def test_operation_convolutiondepthwise(tag, stride):
+    params, blob = _conv_line_and_blob(G[tag + "_w"], G[tag + "_b"], stride, 1, 1, dw=True)
+    y = _host().run_op("ConvolutionDepthWise", params, [G[tag + "_x"]], blob)
+    assert_close_f16(y, G[tag + "_y"], what=tag)
+
+
+@pytest.mark.parametrize("tag,params", [
+    ("pool_max_3s2p1", "0=0 1=3 2=2 3=1"), ("pool_max_5s1p2", "0=0 1=5 2=1 3=2"),
+    ("pool_max_ceil", "0=0 1=2 2=2 3=0 5=0"), ("pool_avg_excl", "0=1 1=3 2=2 3=1 6=0"),
+    ("pool_avg_incl", "0=1 1=3 2=2 3=1 6=1"), ("pool_gap", "0=1 4=1"),
+])
+def test_operation_pooling(tag, params):
+    y = _host().run_op("Pooling", params, [G["pool_x"]])
+    assert y.shape == G[tag + "_y"].shape
+    if params.startswith("0=0"):
+        np.testing.assert_array_equal(y, G[tag + "_y"])
+    else:
+        np.testing.assert_allclose(y, G[tag + "_y"], rtol=1e-6, atol=1e-6)
+
+
+def test_operation_eltwise_binaryop_relu():
+    h = _host()
+    x = G["elt_x"]
+    np.testing.assert_array_equal(h.run_op("ReLU", "", [x]), G["elt_ra"])
+    np.testing.assert_array_equal(h.run_op("BinaryOp", "0=2", [x, x]), G["elt_bb"])
+    np.testing.assert_allclose(h.run_op("Eltwise", "0=1 -23301=3,0.5,-1.25", [G["elt_ra"], G["elt_bb"], x]),
+                               G["elt_esum"], rtol=1e-6, atol=1e-6)
+    np.testing.assert_array_equal(h.run_op("Eltwise", "0=0", [G["elt_ra"], G["elt_bb"]]), G["elt_eprod"])
+    np.testing.assert_array_equal(h.run_op("Eltwise", "0=2", [G["elt_ra"], G["elt_bb"], x]), G["elt_emax"])
+    np.testing.assert_array_equal(h.run_op("BinaryOp", "0=0", [G["elt_esum"], G["elt_eprod"]]), G["elt_out"])
+
+
+def test_fatal_errors_become_status_codes():
+    h = _host()
+    with pytest.raises(h.HostError) as e:
+        h.run_op("Pooling", "0=0 1=3 99=1", [G["pool_x"]])
+    assert "Un-supported Pooling Attribution" in str(e.value)
+    with pytest.raises(h.HostError) as e:
+        h.run_op("NoSuchOp", "", [G["pool_x"]])
+    assert "Un-suppoted operation type" in str(e.value)
+    with pytest.raises(h.HostError):
+        h.run_op("Eltwise", "0=1", [G["elt_x"], G["elt_x"][:, :3]])   # shape mismatch CHECK
+
+
+def _rel(a, b):
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-12))
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_resnet18_fp(fusion):
+    h = _host()
+    g, _ = models.resnet18(2)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    x = G["resnet_x"]
+    for _ in range(3):     # eager, capture, replay
+        out = p.forward(x)["logits"].reshape(2, -1)
+    ref = G["resnet_f32_logits"]
+    assert _rel(out, ref) < 1e-2, _rel(out, ref)
+    assert (out.argmax(1) == ref.argmax(1)).all()
+    s1 = p.get("s1b1_out")
+    assert_close_f16(s1, G["resnet_f32_s1b1_out"], rel=2e-2, what="s1b1_out")
+    launches, ms = p.stats()
+    assert (launches > 0) == fusion
+    p.close()
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_resnet18_int8(fusion):
+    h = _host()
+    scales = {str(n): np.float32(s) for n, s in zip(G["resnet_scale_names"], G["resnet_scales"])}
+    g, _ = models.resnet18(2, act_scales=scales)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    x = G["resnet_x"]
+    for _ in range(3):
+        out = p.forward(x)["logits"].reshape(2, -1)
+    ref = G["resnet_i8_logits"]
+    r = _rel(out, ref)
+    assert r < 3e-2, r
+    assert (out.argmax(1) == ref.argmax(1)).all()
+    # first block output: int8 steps of the reference's own quantisation grid
+    s1 = p.get("s1b1_out")
+    ref1 = G["resnet_i8_s1b1_out"]
+    assert _rel(s1, ref1) < 2e-2, _rel(s1, ref1)
+    p.close()
+
+
+def test_calibration_with_own_pipeline_matches_reference_scales():
+    """Max-abs calibration through this library's fp16 pipeline reproduces the scales the fp32
+    reference gives (to fp16 accuracy), so a GPU-only deployment can calibrate itself."""
+    h = _host()
+    g, info = models.resnet18(2)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=False)
+    calib = np.random.default_rng(2007).uniform(0, 1, (4, 3, 64, 64)).astype(np.float32)
+    scales = models.calibrate(p, info["conv_inputs"], calib)
+    p.close()
+    for n, s in zip(G["resnet_scale_names"], G["resnet_scales"]):
+        assert abs(scales[str(n)] / s - 1.0) < 1e-2, (n, scales[str(n)], s)

@@ -1,0 +1,47 @@
+"""The .phai / .racy writers produce what the reference's parser and init_weights expect."""
+import struct
+
+import numpy as np
+
+from excalibur_b200 import models
+from excalibur_b200.modelfile import GraphBuilder, RACY_TAG_F32, RACY_TAG_I8
+
+
+def test_phai_lines_and_racy_records():
+    g = GraphBuilder("t")
+    w = np.arange(2 * 3 * 3 * 3, dtype=np.float32).reshape(2, 3, 3, 3)
+    b = np.array([1.0, 2.0], np.float32)
+    g.conv("c1", "in", "a", w, b, 2, 1, act=1)
+    wq = np.ones((4, 2, 1, 1), np.int8)
+    g.conv("c2", "a", "b", None, None, 1, 0, int8=(wq, np.full(4, 3.0, np.float32), 5.0))
+    g.pool("p", "b", "c", 0, 3, 2, 1)
+    text = g.phai_text().splitlines()
+    assert text[0].startswith("glsv1") and text[1] == "3 4"
+    assert text[2] == "Convolution c1 1 1 in a 0=2 1=3 11=3 2=1 12=1 3=2 13=2 4=1 14=1 15=1 16=1 5=1 6=54 9=1"
+    assert "8=1" in text[3] and "5=0" in text[3] and "6=8" in text[3]
+    blob = g.racy_bytes()
+    assert struct.unpack_from("<i", blob, 0)[0] == RACY_TAG_F32
+    off = 4 + 54 * 4 + 2 * 4
+    assert struct.unpack_from("<i", blob, off)[0] == RACY_TAG_I8
+    off += 4 + 8            # 8 int8 weights, already a multiple of 4
+    assert struct.unpack_from("<4f", blob, off) == (3.0, 3.0, 3.0, 3.0)
+    assert struct.unpack_from("<f", blob, off + 16)[0] == 5.0
+    assert len(blob) == off + 20
+
+
+def test_int8_weight_padding_to_four_bytes():
+    g = GraphBuilder()
+    wq = np.ones((1, 3, 1, 1), np.int8)
+    g.conv("c", "in", "out", None, None, int8=(wq, np.ones(1, np.float32), 1.0))
+    assert len(g.racy_bytes()) == 4 + 4 + 4 + 4   # tag, 3 weights + 1 pad, 1 weight scale, 1 act scale
+
+
+def test_resnet18_builder_counts():
+    g, info = models.resnet18(2)
+    convs = [l for l in g.lines if l.startswith("Convolution")]
+    assert len(convs) == 1 + 16 + 3
+    assert len(info["conv_inputs"]) == 19
+    macs = models.resnet18_macs()
+    assert macs["total"] == 1814073344 and macs["conv3x3"] == 1676279808
+    wq, ws = models.quantize_weights(np.array([[[[0.5]], [[-2.0]]]], np.float32))
+    assert ws[0] == np.float32(63.5) and list(wq.reshape(-1)) == [32, -127]
