@@ -145,6 +145,32 @@ extern "C" int exb_host_pipeline_dump_profile(void* p, const char* path) {
     return static_cast<host_pipeline*>(p)->net->dump_profile(path) ? EXB_OK : EXB_ERR_BAD_ARG;
 }
 
+extern "C" int exb_host_pipeline_run_resident(void* p, int iters, double* ms) {
+    return guarded([&]() {
+        auto* h = static_cast<host_pipeline*>(p);
+        const double t = h->net->run_resident(iters);
+        if (t < 0) {
+            g_err = "run_resident needs a previous fused forward";
+            return (int)EXB_ERR_BAD_ARG;
+        }
+        if (ms) *ms = t;
+        return (int)EXB_OK;
+    });
+}
+
+extern "C" int exb_host_pipeline_trace_size(void* p) { return static_cast<host_pipeline*>(p)->net->trace_size(); }
+
+extern "C" int exb_host_pipeline_trace_entry(void* p, int i, char* name, int cap, double* begin_ms, double* end_ms) {
+    std::string n;
+    double b = 0, e = 0;
+    if (!static_cast<host_pipeline*>(p)->net->trace_entry(i, n, b, e) || cap <= 0) return EXB_ERR_BAD_ARG;
+    std::strncpy(name, n.c_str(), cap - 1);
+    name[cap - 1] = 0;
+    if (begin_ms) *begin_ms = b;
+    if (end_ms) *end_ms = e;
+    return EXB_OK;
+}
+
 extern "C" int exb_host_op_run(const char* type, const char* params, const char* racy_path, int device, int n_in,
                                const float* const* inputs, const int* shapes, float* out, int64_t cap,
                                int* out_shape4) {

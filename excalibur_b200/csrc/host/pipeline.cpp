@@ -104,6 +104,7 @@ public:
     bool built_for(int N, int C, int H, int W) const { return built_ && N == N_ && C == C_ && H == H_ && W == W_; }
     void run(const float* host_input, bool use_graph, bool profile, std::vector<trace_event>* trace);
     std::shared_ptr<memory::tensor<float>> fetch(const std::string& name);
+    double run_resident(int iters, bool use_graph);
     int launches() const { return launches_; }
     double device_ms() const { return device_ms_; }
     exb_ctx* ctx() { return ctx_; }
@@ -625,6 +626,34 @@ void fused_plan::run(const float* host_input, bool use_graph, bool profile, std:
     exb_check(exb_ctx_sync_check(ctx_, stream_), "fused forward");
 }
 
+double fused_plan::run_resident(int iters, bool use_graph) {
+    if (!built_) return -1.0;
+    CUDA_CHECK(cudaSetDevice(device_));
+    if (use_graph && !graph_exec_) {
+        cudaGraph_t graph = nullptr;
+        for (auto& s : steps_) s.run(stream_);   // make sure every kernel has run eagerly once
+        CUDA_CHECK(cudaStreamSynchronize(stream_));
+        CUDA_CHECK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+        for (auto& s : steps_) s.run(stream_);
+        CUDA_CHECK(cudaStreamEndCapture(stream_, &graph));
+        CUDA_CHECK(cudaGraphInstantiate(&graph_exec_, graph, 0));
+        cudaGraphDestroy(graph);
+        warmed_ = true;
+    }
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+    CUDA_CHECK(cudaEventRecord(ev0_, stream_));
+    for (int i = 0; i < iters; ++i) {
+        if (use_graph) CUDA_CHECK(cudaGraphLaunch(graph_exec_, stream_));
+        else for (auto& s : steps_) s.run(stream_);
+    }
+    CUDA_CHECK(cudaEventRecord(ev1_, stream_));
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+    float ms = 0;
+    cudaEventElapsedTime(&ms, ev0_, ev1_);
+    exb_check(exb_ctx_sync_check(ctx_, stream_), "resident run");
+    return ms;
+}
+
 std::shared_ptr<memory::tensor<float>> fused_plan::fetch(const std::string& name) {
     auto it = index_.find(name);
     if (it == index_.end()) return nullptr;
@@ -885,6 +914,19 @@ template <typename Dtype> void pipeline<Dtype>::disable_profiler() { impl_->prof
 template <typename Dtype> void pipeline<Dtype>::set_fusion(bool on) { impl_->fusion_ = on; }
 template <typename Dtype> void pipeline<Dtype>::set_cuda_graph(bool on) { impl_->graph_ = on; }
 template <typename Dtype> int pipeline<Dtype>::launches_last_forward() const { return impl_->launches_; }
+template <typename Dtype> double pipeline<Dtype>::run_resident(int iters) {
+    if (!impl_->plan_ || !impl_->used_fused_) return -1.0;
+    return impl_->plan_->run_resident(iters, impl_->graph_);
+}
+template <typename Dtype> int pipeline<Dtype>::trace_size() const { return (int)impl_->trace_.size(); }
+template <typename Dtype>
+bool pipeline<Dtype>::trace_entry(int i, std::string& name, double& b, double& e) const {
+    if (i < 0 || i >= (int)impl_->trace_.size()) return false;
+    name = impl_->trace_[i].name;
+    b = impl_->trace_[i].begin_ms;
+    e = impl_->trace_[i].end_ms;
+    return true;
+}
 template <typename Dtype> double pipeline<Dtype>::device_ms_last_forward() const { return impl_->device_ms_; }
 template <typename Dtype> std::vector<std::string> pipeline<Dtype>::input_names() const { return impl_->input_names_; }
 template <typename Dtype> std::vector<std::string> pipeline<Dtype>::output_names() const { return impl_->output_names_; }

@@ -40,6 +40,13 @@ public:
     // Extras of this implementation.
     void set_fusion(bool on);            // default on for pipeline<float> on a GPU
     void set_cuda_graph(bool on);        // replay the fused plan as a CUDA graph (default on)
+    // Re-run the fused plan `iters` times on the input already resident on the device (the last
+    // forward's), no host<->device copies; returns the device time in ms between CUDA events on the
+    // plan's stream, or a negative value when there is no fused plan yet.
+    double run_resident(int iters);
+    // Per-kernel device times of the last profiled forward.
+    int trace_size() const;
+    bool trace_entry(int i, std::string& name, double& begin_ms, double& end_ms) const;
     int launches_last_forward() const;   // kernels launched by the last forward
     double device_ms_last_forward() const;   // device time of the last forward's kernels (events)
     std::vector<std::string> input_names() const;

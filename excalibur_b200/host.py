@@ -13,7 +13,8 @@ HOST_SYMBOLS = [
     "exb_host_last_error", "exb_host_registered", "exb_host_pipeline_create", "exb_host_pipeline_destroy",
     "exb_host_pipeline_set_option", "exb_host_pipeline_forward", "exb_host_pipeline_num_outputs",
     "exb_host_pipeline_output_name", "exb_host_pipeline_get", "exb_host_pipeline_stats",
-    "exb_host_pipeline_dump_profile", "exb_host_op_run",
+    "exb_host_pipeline_dump_profile", "exb_host_pipeline_run_resident", "exb_host_pipeline_trace_size",
+    "exb_host_pipeline_trace_entry", "exb_host_op_run",
 ]
 _READY = False
 
@@ -40,6 +41,10 @@ def lib():
         L.exb_host_pipeline_get.argtypes = [vp, C.c_char_p, vp, C.c_int64, vp]
         L.exb_host_pipeline_stats.argtypes = [vp, C.POINTER(i32), C.POINTER(C.c_double)]
         L.exb_host_pipeline_dump_profile.argtypes = [vp, C.c_char_p]
+        L.exb_host_pipeline_run_resident.argtypes = [vp, i32, C.POINTER(C.c_double)]
+        L.exb_host_pipeline_trace_size.argtypes = [vp]
+        L.exb_host_pipeline_trace_entry.argtypes = [vp, i32, C.c_char_p, i32, C.POINTER(C.c_double),
+                                                    C.POINTER(C.c_double)]
         L.exb_host_op_run.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, i32, i32, C.POINTER(vp), vp, vp,
                                       C.c_int64, vp]
         _READY = True
@@ -107,6 +112,22 @@ class Pipeline:
         n, ms = C.c_int(), C.c_double()
         lib().exb_host_pipeline_stats(self._h, C.byref(n), C.byref(ms))
         return n.value, ms.value
+
+    def run_resident(self, iters):
+        """Device time (ms) of `iters` back-to-back runs of the fused plan on the resident input."""
+        ms = C.c_double()
+        _check(lib().exb_host_pipeline_run_resident(self._h, iters, C.byref(ms)))
+        return ms.value
+
+    def trace(self):
+        """[(kernel/op name, begin_ms, end_ms)] of the last forward run with option profile=1."""
+        out = []
+        buf = C.create_string_buffer(256)
+        b, e = C.c_double(), C.c_double()
+        for i in range(lib().exb_host_pipeline_trace_size(self._h)):
+            _check(lib().exb_host_pipeline_trace_entry(self._h, i, buf, 256, C.byref(b), C.byref(e)))
+            out.append((buf.value.decode(), b.value, e.value))
+        return out
 
     def dump_profile(self, path):
         _check(lib().exb_host_pipeline_dump_profile(self._h, path.encode()))

@@ -51,6 +51,13 @@ EXB_API int exb_host_pipeline_get(void* p, const char* name, float* out, int64_t
 /* Kernels launched by the last forward (-1 when run op by op) and their device time in ms. */
 EXB_API int exb_host_pipeline_stats(void* p, int* launches, double* device_ms);
 EXB_API int exb_host_pipeline_dump_profile(void* p, const char* path);
+/* Re-run the fused plan `iters` times on the input the last forward left on the device: no
+ * host<->device copies, device time between CUDA events on the plan's stream in *ms. */
+EXB_API int exb_host_pipeline_run_resident(void* p, int iters, double* ms);
+/* Per-kernel device times of the last forward run with the profiler enabled. */
+EXB_API int exb_host_pipeline_trace_size(void* p);
+EXB_API int exb_host_pipeline_trace_entry(void* p, int i, char* name, int cap, double* begin_ms,
+                                          double* end_ms);
 
 /* One operation through the reflector, the way pipeline does it: create_object(param),
  * init_weights(FILE*) from `racy_path` (or init_weights() when NULL/""), forward_gpu on fp32
