@@ -54,11 +54,31 @@ __device__ __forceinline__ void epi_store_scalar(void* y, int dtype, int64_t off
     }
 }
 
+// Four floats -> four int8 (round half to even, saturate), packed little-endian in 32 bits.
+__device__ __forceinline__ uint32_t quant_pack4(float a, float b, float c, float d, float qscale) {
+    const int q0 = __float2int_rn(a * qscale), q1 = __float2int_rn(b * qscale);
+    const int q2 = __float2int_rn(c * qscale), q3 = __float2int_rn(d * qscale);
+    uint32_t r;
+    // cvt.pack.sat.s8.s32.b32 d, a, b, c:  d = (c << 16) | (sat8(a) << 8) | sat8(b)
+    asm("{\n\t.reg .b32 t;\n\t"
+        "cvt.pack.sat.s8.s32.b32 t, %4, %3, 0;\n\t"
+        "cvt.pack.sat.s8.s32.b32 %0, %2, %1, t;\n\t}"
+        : "=r"(r)
+        : "r"(q0), "r"(q1), "r"(q2), "r"(q3));
+    return r;
+}
+
 // 16 consecutive channels starting at element offset `off` (16-byte aligned for every dtype).
 __device__ __forceinline__ void epi_store_vec16(void* y, int dtype, int64_t off, const float (&v)[16],
                                                 float qscale, const uint32_t (&raw)[16]) {
-    switch (dtype) {
-    case EXB_F16: {
+    if (dtype == EXB_I8) {
+        uint4 o;
+        o.x = quant_pack4(v[0], v[1], v[2], v[3], qscale);
+        o.y = quant_pack4(v[4], v[5], v[6], v[7], qscale);
+        o.z = quant_pack4(v[8], v[9], v[10], v[11], qscale);
+        o.w = quant_pack4(v[12], v[13], v[14], v[15], qscale);
+        *reinterpret_cast<uint4*>(static_cast<int8_t*>(y) + off) = o;
+    } else if (dtype == EXB_F16) {
         uint4 o[2];
         __half2* h = reinterpret_cast<__half2*>(o);
 #pragma unroll
@@ -66,33 +86,25 @@ __device__ __forceinline__ void epi_store_vec16(void* y, int dtype, int64_t off,
         uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(y) + off);
         dst[0] = o[0];
         dst[1] = o[1];
-        break;
-    }
-    case EXB_I8: {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            int q0 = quant_rne(v[4 * i] * qscale), q1 = quant_rne(v[4 * i + 1] * qscale);
-            int q2 = quant_rne(v[4 * i + 2] * qscale), q3 = quant_rne(v[4 * i + 3] * qscale);
-            w[i] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-                   ((uint32_t)(q3 & 0xff) << 24);
-        }
-        *reinterpret_cast<uint4*>(static_cast<int8_t*>(y) + off) = make_uint4(w[0], w[1], w[2], w[3]);
-        break;
-    }
-    case EXB_F32: {
+    } else if (dtype == EXB_F32) {
         float4* dst = reinterpret_cast<float4*>(static_cast<float*>(y) + off);
 #pragma unroll
         for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        break;
-    }
-    case EXB_I32: {
+    } else {
         uint4* dst = reinterpret_cast<uint4*>(static_cast<int32_t*>(y) + off);
 #pragma unroll
         for (int i = 0; i < 4; ++i) dst[i] = make_uint4(raw[4 * i], raw[4 * i + 1], raw[4 * i + 2], raw[4 * i + 3]);
-        break;
     }
-    default: break;
+}
+
+// Activation over a register vector with the selector hoisted out of the element loop.
+__device__ __forceinline__ void act_vec16(float (&v)[16], int act) {
+    if (act == EXB_ACT_RELU) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+    } else if (act != EXB_ACT_NONE) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = apply_act(v[i], act);
     }
 }
 

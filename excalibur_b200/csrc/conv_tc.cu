@@ -8,13 +8,14 @@
 // [Cout][kh][kw][Cin].  Stride-2 layers read one of four "parity" views of the input (every
 // second row / column, offset by 0 or 1) so that a box is still a dense rectangle.
 //
-// One persistent CTA per SM, 6 warps:
+// One persistent CTA per SM, 10 warps:
 //   warp 0   TMA producer (one lane)           - fills a ring of shared-memory stages
 //   warp 1   MMA issuer (one lane) + TMEM owner - tcgen05.mma, fp32 / int32 accumulators in TMEM,
 //                                                 two accumulator buffers so the epilogue of
 //                                                 tile i overlaps the main loop of tile i+1
-//   warps 2-5 epilogue                          - tcgen05.ld, scale/bias, residual, activation,
-//                                                 requantise, 16-byte NHWC stores
+//   warps 2-9 epilogue                          - tcgen05.ld, scale/bias, residual, activation,
+//                                                 requantise, 16-byte NHWC stores; two warps per
+//                                                 TMEM lane quarter, alternating 16-column chunks
 // All mbarrier waits are bounded; when one runs out the kernel raises the context's error
 // word, every role leaves its loop, TMEM is freed and the launch returns normally.
 #include "conv_common.cuh"
@@ -26,7 +27,8 @@ namespace exb {
 namespace {
 
 constexpr int kMaxStages = 8;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kEpiWarps = 8;
 constexpr int kTileM = 128;
 constexpr uint32_t kMaxSpins = 1u << 21;  // tens of milliseconds at least; a legitimate wait is microseconds
 
@@ -47,6 +49,7 @@ struct ConvTcParams {
     int a_bytes, b_bytes;   // shared-memory bytes per stage
     int a_tx_bytes;         // bytes one A box delivers
     int tmem_cols;
+    int cout_pad;     // entries of the scale / bias arrays
     uint32_t idesc;
     int has_res;
     EpiParams e;
@@ -82,6 +85,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + (size_t)p.stages * p.a_bytes;
+    // Per-output-channel scale and bias of every N tile, staged once per CTA.
+    float* s_scale = reinterpret_cast<float*>(smem_b + (size_t)p.stages * p.b_bytes);
+    float* s_bias = s_scale + p.n_tiles * p.BN;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -96,7 +102,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
         }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(&tfull_bar[i], 1);
-            ptx::mbar_init(&tempty_bar[i], 4);
+            ptx::mbar_init(&tempty_bar[i], kEpiWarps);
         }
         ptx::fence_mbar_init();
         ptx::tma_prefetch_desc(&p.tmA[0]);
@@ -105,6 +111,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
     if (warp == 1) {
         ptx::tmem_alloc(&tmem_base_smem, (uint32_t)p.tmem_cols);
         ptx::tmem_relinquish();
+    }
+    for (int c = threadIdx.x; c < p.n_tiles * p.BN; c += kThreads) {
+        const bool in = c < p.cout_pad;
+        s_scale[c] = in ? p.e.scale[c] : 0.f;
+        s_bias[c] = in ? p.e.bias[c] : 0.f;
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
@@ -204,13 +215,15 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
         }
     } else {
         // ------------------------------- epilogue ------------------------------------------
-        const int q = warp & 3;            // TMEM lane quarter this warp may read
-        const int row = q * 32 + lane;     // row of the M tile == TMEM lane
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;       // which of the two warps of the quarter
+        const int row = q * 32 + lane;          // row of the M tile == TMEM lane
         const int tw = row % p.TW;
         const int th = (row / p.TW) % p.TH;
         const int tn = row / (p.TW * p.TH);
         const bool row_in_box = row < p.TW * p.TH * p.TN;
         const bool vec_ok = (p.e.cout_stride & 15) == 0;
+        const int n_chunks = p.BN / 16;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -225,28 +238,31 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
             const bool valid = row_in_box && ow < p.OW && oh < p.OH && n < p.N;
             const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.BN);
-            for (int chunk = 0; chunk < p.BN / 16; ++chunk) {
+            for (int chunk = half; chunk < n_chunks; chunk += 2) {
                 uint32_t raw[16];
                 ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
                 ptx::tmem_ld_wait();
-                const int c0 = tc.ntile * p.BN + chunk * 16;
-                if (!valid || c0 >= p.e.cout_stride) continue;
-                const int64_t off = pix * p.e.cout_stride + c0;
-                if (vec_ok) {
-                    float v[16];
-                    const float4* sc = reinterpret_cast<const float4*>(p.e.scale + c0);
-                    const float4* bi = reinterpret_cast<const float4*>(p.e.bias + c0);
+                const int cl = tc.ntile * p.BN + chunk * 16;   // first channel of the chunk
+                if (!valid || cl >= p.e.cout_stride) continue;
+                const int64_t off = pix * p.e.cout_stride + cl;
+                float v[16];
+                {
+                    const float4* sc = reinterpret_cast<const float4*>(s_scale + cl);
+                    const float4* bi = reinterpret_cast<const float4*>(s_bias + cl);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const float4 s4 = __ldg(sc + i), b4 = __ldg(bi + i);
+                        const float4 s4 = sc[i], b4 = bi[i];
                         v[4 * i + 0] = epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x);
                         v[4 * i + 1] = epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y);
                         v[4 * i + 2] = epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z);
                         v[4 * i + 3] = epi_value<kInt8>(raw[4 * i + 3], s4.w, b4.w);
                     }
+                }
+                if (vec_ok) {
                     if (p.has_res) {
                         const uint4* rp = reinterpret_cast<const uint4*>(p.e.residual + off);
-                        uint4 rr[2] = {__ldg(rp), __ldg(rp + 1)};
+                        const uint4 r0 = __ldg(rp), r1 = __ldg(rp + 1);
+                        const uint4 rr[2] = {r0, r1};
                         const __half2* h = reinterpret_cast<const __half2*>(rr);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
@@ -255,18 +271,22 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
                             v[2 * i + 1] += f.y;
                         }
                     }
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = apply_act(v[i], p.e.act);
+                    act_vec16(v, p.e.act);
                     epi_store_vec16(p.e.y, p.e.out_dtype, off, v, p.e.out_scale, raw);
                     if (p.e.out2_dtype >= 0) epi_store_vec16(p.e.y2, p.e.out2_dtype, off, v, p.e.out2_scale, raw);
                 } else {
-                    for (int i = 0; i < 16 && c0 + i < p.e.cout_stride; ++i) {
-                        float v = epi_value<kInt8>(raw[i], __ldg(p.e.scale + c0 + i), __ldg(p.e.bias + c0 + i));
-                        if (p.has_res) v += __half2float(p.e.residual[off + i]);
-                        v = apply_act(v, p.e.act);
-                        epi_store_scalar(p.e.y, p.e.out_dtype, off + i, v, p.e.out_scale, raw[i]);
-                        if (p.e.out2_dtype >= 0)
-                            epi_store_scalar(p.e.y2, p.e.out2_dtype, off + i, v, p.e.out2_scale, raw[i]);
+                    // ragged channel count: element-wise stores, statically indexed so the
+                    // accumulators stay in registers
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        if (cl + i < p.e.cout_stride) {
+                            float u = v[i];
+                            if (p.has_res) u += __half2float(p.e.residual[off + i]);
+                            u = apply_act(u, p.e.act);
+                            epi_store_scalar(p.e.y, p.e.out_dtype, off + i, u, p.e.out_scale, raw[i]);
+                            if (p.e.out2_dtype >= 0)
+                                epi_store_scalar(p.e.y2, p.e.out2_dtype, off + i, u, p.e.out2_scale, raw[i]);
+                        }
                     }
                 }
             }
@@ -365,7 +385,8 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.a_bytes = kTileM * p.kb_bytes;
     p.b_bytes = p.BN * p.kb_bytes;
     p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
-    const int budget = ctx->smem_optin - 2048;  // static barriers + alignment slack
+    const int epi_bytes = 2 * p.n_tiles * p.BN * (int)sizeof(float);
+    const int budget = ctx->smem_optin - 2048 - epi_bytes;  // static barriers + alignment slack + scale/bias
     int stages = budget / (p.a_bytes + p.b_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return fail(EXB_ERR_UNSUPPORTED, "conv tile does not fit shared memory (BN=%d)", p.BN);
@@ -374,6 +395,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     while (cols < 2 * p.BN) cols *= 2;
     p.tmem_cols = cols;
     p.idesc = ptx::make_idesc(int8, kTileM, (uint32_t)p.BN);
+    p.cout_pad = w->cout_pad;
     p.has_res = g.has_res;
     p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.residual = static_cast<const __half*>(residual);
     p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;
@@ -419,7 +441,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
 
     const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.n_tiles;
     const int grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
-    const size_t smem = (size_t)p.stages * (p.a_bytes + p.b_bytes) + 1024;
+    const size_t smem = (size_t)p.stages * (p.a_bytes + p.b_bytes) + 1024 + epi_bytes;
     auto kern = int8 ? conv_tc_kernel<true> : conv_tc_kernel<false>;
     EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, kThreads, smem, st>>>(p);
