@@ -8,14 +8,15 @@
 // [Cout][kh][kw][Cin].  Stride-2 layers read one of four "parity" views of the input (every
 // second row / column, offset by 0 or 1) so that a box is still a dense rectangle.
 //
-// One persistent CTA per SM, 10 warps:
+// One persistent CTA per SM, 20 warps:
 //   warp 0   TMA producer (one lane)           - fills a ring of shared-memory stages
 //   warp 1   MMA issuer (one lane) + TMEM owner - tcgen05.mma, fp32 / int32 accumulators in TMEM,
-//                                                 two accumulator buffers so the epilogue of
-//                                                 tile i overlaps the main loop of tile i+1
-//   warps 2-9 epilogue                          - tcgen05.ld, scale/bias, residual, activation,
-//                                                 requantise, 16-byte NHWC stores; two warps per
-//                                                 TMEM lane quarter, alternating 16-column chunks
+//                                                 NB = 2 or 4 accumulator buffers so epilogues
+//                                                 overlap the main loops of the following tiles
+//   warps 4-19 epilogue, in NB groups           - tile i goes to group i % NB: tcgen05.ld,
+//                                                 scale/bias, residual, activation, requantise,
+//                                                 16-byte NHWC stores
+//   (warps 2-3 only help with set-up)
 // All mbarrier waits are bounded; when one runs out the kernel raises the context's error
 // word, every role leaves its loop, TMEM is freed and the launch returns normally.
 #include "conv_common.cuh"
@@ -27,8 +28,10 @@ namespace exb {
 namespace {
 
 constexpr int kMaxStages = 8;
-constexpr int kThreads = 320;
-constexpr int kEpiWarps = 8;
+constexpr int kThreads = 640;
+constexpr int kEpiWarps = 16;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kMaxAccBufs = 4;
 constexpr int kTileM = 128;
 constexpr uint32_t kMaxSpins = 1u << 21;  // tens of milliseconds at least; a legitimate wait is microseconds
 
@@ -49,11 +52,13 @@ struct ConvTcParams {
     int a_bytes, b_bytes;   // shared-memory bytes per stage
     int a_tx_bytes;         // bytes one A box delivers
     int tmem_cols;
+    int acc_bufs;     // accumulator buffers in TMEM (2 or 4)
     int cout_pad;     // entries of the scale / bias arrays
     uint32_t idesc;
     int has_res;
     EpiParams e;
     int* error;
+    int kgroup;       // K blocks per pipeline stage (one mbarrier round trip per stage)
 };
 
 struct TileCoord {
@@ -76,18 +81,20 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
-    __shared__ __align__(8) uint64_t tfull_bar[2];
-    __shared__ __align__(8) uint64_t tempty_bar[2];
+    __shared__ __align__(8) uint64_t tfull_bar[kMaxAccBufs];
+    __shared__ __align__(8) uint64_t tempty_bar[kMaxAccBufs];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
 
     // Operand ring, 1024-byte aligned (the widest swizzle atom).
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;
-    uint8_t* smem_b = smem + (size_t)p.stages * p.a_bytes;
+    uint8_t* smem_b = smem + (size_t)p.stages * p.kgroup * p.a_bytes;
     // Per-output-channel scale and bias of every N tile, staged once per CTA.
-    float* s_scale = reinterpret_cast<float*>(smem_b + (size_t)p.stages * p.b_bytes);
+    float* s_scale = reinterpret_cast<float*>(smem_b + (size_t)p.stages * p.kgroup * p.b_bytes);
     float* s_bias = s_scale + p.n_tiles * p.BN;
+    // Per K iteration (tap, channel block): TMA coordinates that do not depend on the tile.
+    int4* k_tab = reinterpret_cast<int4*>(s_bias + p.n_tiles * p.BN);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -100,9 +107,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
             ptx::mbar_init(&full_bar[s], 1);
             ptx::mbar_init(&empty_bar[s], 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < p.acc_bufs; ++i) {
             ptx::mbar_init(&tfull_bar[i], 1);
-            ptx::mbar_init(&tempty_bar[i], kEpiWarps);
+            ptx::mbar_init(&tempty_bar[i], kEpiWarps / p.acc_bufs);
         }
         ptx::fence_mbar_init();
         ptx::tma_prefetch_desc(&p.tmA[0]);
@@ -111,6 +118,22 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
     if (warp == 1) {
         ptx::tmem_alloc(&tmem_base_smem, (uint32_t)p.tmem_cols);
         ptx::tmem_relinquish();
+    }
+    for (int it = threadIdx.x; it < k_iters; it += kThreads) {
+        const int tap = it / p.cblks, cb = it - tap * p.cblks;
+        const int r = tap / p.kw, sx = tap - r * p.kw;
+        int view = 0, dw, dh;
+        if (p.stride == 1) {
+            dw = sx - p.pad_l;
+            dh = r - p.pad_t;
+        } else {
+            const int ow_ = sx - p.pad_l, oh_ = r - p.pad_t;
+            const int pw = ow_ & 1, ph = oh_ & 1;
+            dw = (ow_ - pw) >> 1;
+            dh = (oh_ - ph) >> 1;
+            view = ph * 2 + pw;
+        }
+        k_tab[it] = make_int4(cb * p.kb_elems, dw, dh, (tap * p.cin_pad + cb * p.kb_elems) | (view << 28));
     }
     for (int c = threadIdx.x; c < p.n_tiles * p.BN; c += kThreads) {
         const bool in = c < p.cout_pad;
@@ -124,46 +147,48 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
 
     if (warp == 0) {
         // ------------------------------- TMA producer --------------------------------------
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
+        // A pipeline stage holds `kgroup` K blocks.  Lane g issues the two loads of block g, so a
+        // whole stage costs one pass through this loop body: a single thread retires only one
+        // instruction every few cycles, which is what bounds small-K layers otherwise.
+        const int G = p.kgroup;
+        int stage = 0;
+        uint32_t phase = 0;
+        int ok = 1;
+        const uint32_t a_base = ptx::smem_u32(smem_a) + (uint32_t)(lane * p.a_bytes);
+        const uint32_t b_base = ptx::smem_u32(smem_b) + (uint32_t)(lane * p.b_bytes);
+        const uint32_t a_stage = (uint32_t)(G * p.a_bytes), b_stage = (uint32_t)(G * p.b_bytes);
+        const uint32_t full0 = ptx::smem_u32(&full_bar[0]), empty0 = ptx::smem_u32(&empty_bar[0]);
+        const uint64_t mapA0 = reinterpret_cast<uint64_t>(&p.tmA[0]);
+        const uint64_t mapB = reinterpret_cast<uint64_t>(&p.tmB);
+        const uint32_t tx = (uint32_t)(p.a_tx_bytes + p.b_bytes);
+        if (lane < G) {
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
-                for (int r = 0; r < p.kh && ok; ++r) {
-                    for (int s = 0; s < p.kw && ok; ++s) {
-                        int map = 0, cw, ch;
-                        if (p.stride == 1) {
-                            cw = tc.ow0 + s - p.pad_l;
-                            ch = tc.oh0 + r - p.pad_t;
-                        } else {
-                            const int dw = s - p.pad_l, dh = r - p.pad_t;
-                            const int pw = dw & 1, ph = dh & 1;
-                            cw = tc.ow0 + ((dw - pw) >> 1);
-                            ch = tc.oh0 + ((dh - ph) >> 1);
-                            map = ph * 2 + pw;
-                        }
-                        const int kbase = (r * p.kw + s) * p.cin_pad;
-                        for (int cb = 0; cb < p.cblks; ++cb) {
-                            if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, &abort_flag, kMaxSpins)) {
-                                ok = false;
-                                break;
-                            }
-                            ptx::mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(p.a_tx_bytes + p.b_bytes));
-                            ptx::tma_load_4d(smem_a + (size_t)stage * p.a_bytes, &p.tmA[map], &full_bar[stage],
-                                             cb * p.kb_elems, cw, ch, tc.n0);
-                            ptx::tma_load_2d(smem_b + (size_t)stage * p.b_bytes, &p.tmB, &full_bar[stage],
-                                             kbase + cb * p.kb_elems, tc.ntile * p.BN);
-                            if (++stage == p.stages) {
-                                stage = 0;
-                                phase ^= 1u;
-                            }
-                        }
+                const int ncoord = tc.ntile * p.BN;
+                for (int it0 = 0; it0 < k_iters; it0 += G) {
+                    const int nb = min(G, k_iters - it0);
+                    const bool mine = lane < nb;
+                    int4 e = make_int4(0, 0, 0, 0);   // x: A channel coord, y: dw, z: dh, w: B k coord | view << 28
+                    if (mine) e = k_tab[it0 + lane];
+                    if (!ptx::mbar_wait_bounded_u32(empty0 + stage * 8, phase ^ 1u, &abort_flag, kMaxSpins)) {
+                        ok = 0;
+                        break;
+                    }
+                    const uint32_t fb = full0 + stage * 8;
+                    if (lane == 0) ptx::mbar_arrive_expect_tx_u32(fb, tx * (uint32_t)nb);
+                    if (mine) {
+                        ptx::tma_load_4d_u32(a_base + stage * a_stage, mapA0 + ((uint32_t)e.w >> 28) * sizeof(CUtensorMap), fb,
+                                             e.x, tc.ow0 + e.y, tc.oh0 + e.z, tc.n0);
+                        ptx::tma_load_2d_u32(b_base + stage * b_stage, mapB, fb, e.w & 0x0fffffff, ncoord);
+                    }
+                    if (++stage == p.stages) {
+                        stage = 0;
+                        phase ^= 1u;
                     }
                 }
             }
             if (!ok) {
-                atomicExch(p.error, 1);
+                if (lane == 0) atomicExch(p.error, 1);
                 // Give copies already in flight time to land before this CTA's shared memory
                 // can be handed to another CTA.
                 for (int i = 0; i < 2000; ++i) __nanosleep(100);
@@ -172,51 +197,79 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ----------------------------------------
         if (lane == 0) {
+            const int G = p.kgroup;
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
             const int ksteps = p.kb_bytes / 32;
+            const uint32_t full0 = ptx::smem_u32(&full_bar[0]), empty0 = ptx::smem_u32(&empty_bar[0]);
+            const uint32_t tfull0 = ptx::smem_u32(&tfull_bar[0]), tempty0 = ptx::smem_u32(&tempty_bar[0]);
+            // descriptor halves: low = (address >> 4) | LBO(=1) << 16, high = SBO | version | swizzle
+            const uint64_t d0 = ptx::make_smem_desc(ptx::smem_u32(smem_a), (uint32_t)p.kb_bytes);
+            const uint32_t desc_hi = (uint32_t)(d0 >> 32);
+            const uint32_t a_lo0 = (uint32_t)d0;
+            const uint32_t b_lo0 = (uint32_t)ptx::make_smem_desc(ptx::smem_u32(smem_b), (uint32_t)p.kb_bytes);
+            const uint32_t a_blk = (uint32_t)p.a_bytes >> 4, b_blk = (uint32_t)p.b_bytes >> 4;
+            const uint32_t a_stage = a_blk * G, b_stage = b_blk * G;
+            const uint32_t idesc = p.idesc;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                if (!ptx::mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, &abort_flag, kMaxSpins)) {
+                if (!ptx::mbar_wait_bounded_u32(tempty0 + acc * 8, acc_phase ^ 1u, &abort_flag, kMaxSpins)) {
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
                 uint32_t accumulate = 0;
-                for (int it = 0; it < k_iters; ++it) {
-                    if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, &abort_flag, kMaxSpins)) {
+                for (int it0 = 0; it0 < k_iters; it0 += G) {
+                    const int nb = min(G, k_iters - it0);
+                    if (!ptx::mbar_wait_bounded_u32(full0 + stage * 8, phase, &abort_flag, kMaxSpins)) {
                         ok = false;
                         break;
                     }
-                    ptx::tc_fence_after_sync();
-                    const uint32_t a_addr = ptx::smem_u32(smem_a + (size_t)stage * p.a_bytes);
-                    const uint32_t b_addr = ptx::smem_u32(smem_b + (size_t)stage * p.b_bytes);
-                    for (int k = 0; k < ksteps; ++k) {
-                        const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, (uint32_t)p.kb_bytes);
-                        const uint64_t bdesc = ptx::make_smem_desc(b_addr + k * 32, (uint32_t)p.kb_bytes);
-                        ptx::tc_mma<kInt8>(d_tmem, adesc, bdesc, p.idesc, accumulate);
+                    uint32_t a_lo = a_lo0 + stage * a_stage, b_lo = b_lo0 + stage * b_stage;
+                    for (int g = 0; g < nb; ++g) {
+                        if (ksteps == 4) {
+                            ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
+                            ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo + 2, b_lo + 2, desc_hi, idesc, 1);
+                            ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo + 4, b_lo + 4, desc_hi, idesc, 1);
+                            ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo + 6, b_lo + 6, desc_hi, idesc, 1);
+                        } else if (ksteps == 2) {
+                            ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
+                            ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo + 2, b_lo + 2, desc_hi, idesc, 1);
+                        } else {
+                            ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
+                        }
                         accumulate = 1;
+                        a_lo += a_blk;
+                        b_lo += b_blk;
                     }
-                    ptx::tc_commit(&empty_bar[stage]);  // stage is free once these MMAs retire
+                    ptx::tc_commit_u32(empty0 + stage * 8);   // stage is free once these MMAs retire
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                ptx::tc_commit(&tfull_bar[acc]);  // accumulator complete
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
+                ptx::tc_commit_u32(tfull0 + acc * 8);   // accumulator complete
+                if (++acc == p.acc_bufs) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
             }
             if (!ok) atomicExch(p.error, 2);
         }
-    } else {
+    } else if (warp >= kFirstEpiWarp) {
         // ------------------------------- epilogue ------------------------------------------
-        const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        const int half = (warp - 2) >> 2;       // which of the two warps of the quarter
+        // Tile i of this CTA's sequence is accumulated in buffer i % NB and drained by group
+        // i % NB.  A group has 16/NB warps: one (NB = 4) or two (NB = 2) per TMEM lane quarter,
+        // in the second case splitting the 16-column chunks between them.
+        const int e = warp - kFirstEpiWarp;
+        const int q = e & 3;                    // TMEM lane quarter (== warp % 4)
+        const int nsub = kEpiWarps / 4 / p.acc_bufs;
+        const int grp = (e >> 2) % p.acc_bufs;
+        const int sub = (e >> 2) / p.acc_bufs;
         const int row = q * 32 + lane;          // row of the M tile == TMEM lane
         const int tw = row % p.TW;
         const int th = (row / p.TW) % p.TH;
@@ -224,21 +277,20 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
         const bool row_in_box = row < p.TW * p.TH * p.TN;
         const bool vec_ok = (p.e.cout_stride & 15) == 0;
         const int n_chunks = p.BN / 16;
-        int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * p.BN);
+        for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles && ok; t += p.acc_bufs * gridDim.x) {
             const TileCoord tc = decode_tile(p, t);
-            if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_phase, &abort_flag, kMaxSpins)) {
+            const int ow = tc.ow0 + tw, oh = tc.oh0 + th, n = tc.n0 + tn;
+            const bool valid = row_in_box && ow < p.OW && oh < p.OH && n < p.N;
+            const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
+            if (!ptx::mbar_wait_bounded_warp(&tfull_bar[grp], acc_phase, &abort_flag, kMaxSpins)) {
                 ok = false;
                 break;
             }
             ptx::tc_fence_after_sync();
-            const int ow = tc.ow0 + tw, oh = tc.oh0 + th, n = tc.n0 + tn;
-            const bool valid = row_in_box && ow < p.OW && oh < p.OH && n < p.N;
-            const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.BN);
-            for (int chunk = half; chunk < n_chunks; chunk += 2) {
+            for (int chunk = sub; chunk < n_chunks; chunk += nsub) {
                 uint32_t raw[16];
                 ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
                 ptx::tmem_ld_wait();
@@ -292,9 +344,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1u;
+            if (lane == 0) ptx::mbar_arrive(&tempty_bar[grp]);
+            acc_phase ^= 1u;
         }
         if (!ok && lane == 0) atomicExch(p.error, 3);
     }
@@ -385,14 +436,32 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.a_bytes = kTileM * p.kb_bytes;
     p.b_bytes = p.BN * p.kb_bytes;
     p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
-    const int epi_bytes = 2 * p.n_tiles * p.BN * (int)sizeof(float);
-    const int budget = ctx->smem_optin - 2048 - epi_bytes;  // static barriers + alignment slack + scale/bias
-    int stages = budget / (p.a_bytes + p.b_bytes);
+    const int k_iters = g.kh * g.kw * p.cblks;
+    if ((int64_t)g.kh * g.kw * w->cin_pad >= (1 << 28)) return fail(EXB_ERR_UNSUPPORTED, "reduction dimension too large");
+    const int epi_bytes = 2 * p.n_tiles * p.BN * (int)sizeof(float) + k_iters * (int)sizeof(int4);
+    const int budget = ctx->smem_optin - 2048 - epi_bytes;  // static barriers + alignment slack + tables
+    const int blk_bytes = p.a_bytes + p.b_bytes;
+    // K blocks per stage: aim at ~48 KB stages (one mbarrier round trip each), keep >= 3 stages,
+    // prefer a group size that divides the K loop.
+    int gmax = (48 * 1024) / blk_bytes;
+    if (gmax < 1) gmax = 1;
+    if (gmax > 16) gmax = 16;
+    if (gmax > k_iters) gmax = k_iters;
+    int G = gmax;
+    for (int gcand = gmax; gcand >= (gmax + 1) / 2 && gcand >= 1; --gcand)
+        if (k_iters % gcand == 0) {
+            G = gcand;
+            break;
+        }
+    while (G > 1 && budget / (G * blk_bytes) < 3) --G;
+    p.kgroup = G;
+    int stages = budget / (G * blk_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return fail(EXB_ERR_UNSUPPORTED, "conv tile does not fit shared memory (BN=%d)", p.BN);
     p.stages = stages;
+    p.acc_bufs = p.BN <= 128 ? 4 : 2;
     int cols = 32;
-    while (cols < 2 * p.BN) cols *= 2;
+    while (cols < p.acc_bufs * p.BN) cols *= 2;
     p.tmem_cols = cols;
     p.idesc = ptx::make_idesc(int8, kTileM, (uint32_t)p.BN);
     p.cout_pad = w->cout_pad;
@@ -441,7 +510,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
 
     const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.n_tiles;
     const int grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
-    const size_t smem = (size_t)p.stages * (p.a_bytes + p.b_bytes) + 1024 + epi_bytes;
+    const size_t smem = (size_t)p.stages * p.kgroup * (p.a_bytes + p.b_bytes) + 1024 + epi_bytes;
     auto kern = int8 ? conv_tc_kernel<true> : conv_tc_kernel<false>;
     EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, kThreads, smem, st>>>(p);
