@@ -17,7 +17,7 @@ ACT_NONE, ACT_RELU, ACT_RELU6_QUIRK, ACT_SIGMOID, ACT_RELU6, ACT_SILU = 0, 1, 3,
 
 EXPORTED_SYMBOLS = [
     "exb_ctx_create", "exb_ctx_destroy", "exb_last_error_string", "exb_version", "exb_ctx_sm_count",
-    "exb_ctx_sync_check", "exb_nchw_f32_to_nhwc", "exb_nhwc_to_nchw_f32", "exb_conv_out_dims",
+    "exb_ctx_sync_check", "exb_nchw_f32_to_nhwc", "exb_nchw_f32_to_nhwc_padded", "exb_nhwc_to_nchw_f32", "exb_conv_out_dims",
     "exb_conv_weights_pack_f16", "exb_conv_weights_pack_i8", "exb_conv_weights_destroy",
     "exb_conv2d_fwd", "exb_conv2d_uses_tensor_cores", "exb_dw_weights_pack", "exb_dw_weights_destroy",
     "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_eltwise_fwd", "exb_binaryop_fwd",
@@ -30,7 +30,8 @@ class ConvDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "N", "H", "W", "Cin", "Cout", "cin_stride", "cout_stride", "kh", "kw", "stride_h", "stride_w",
         "pad_t", "pad_b", "pad_l", "pad_r", "dilation", "group", "in_dtype", "out_dtype", "out2_dtype",
-        "res_dtype", "act")] + [("out_scale", C.c_float), ("out2_scale", C.c_float), ("impl", C.c_int32)]
+        "res_dtype", "act")] + [("out_scale", C.c_float), ("out2_scale", C.c_float), ("impl", C.c_int32),
+                                      ("x_w_pitch", C.c_int32), ("x_w_pad", C.c_int32)]
 
 
 class DwConvDesc(C.Structure):
@@ -70,6 +71,7 @@ def lib():
         L.exb_ctx_sm_count.argtypes = [vp, C.POINTER(i32)]
         L.exb_ctx_sync_check.argtypes = [vp, vp]
         L.exb_nchw_f32_to_nhwc.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
+        L.exb_nchw_f32_to_nhwc_padded.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, i32, vp]
         L.exb_nhwc_to_nchw_f32.argtypes = [vp, vp, i32, vp, i32, i32, i32, i32, i32, f32, vp]
         L.exb_conv_out_dims.argtypes = [C.POINTER(ConvDesc), C.POINTER(i32), C.POINTER(i32)]
         L.exb_conv2d_uses_tensor_cores.argtypes = [C.POINTER(ConvDesc)]
@@ -164,12 +166,12 @@ class Context:
 
 def make_conv_desc(N, H, W, Cin, Cout, k, stride=1, pad=0, in_dtype=EXB_F16, out_dtype=EXB_F16,
                    out2_dtype=-1, res=False, act=ACT_NONE, out_scale=1.0, out2_scale=1.0,
-                   cin_stride=0, cout_stride=0, group=1, impl=0):
+                   cin_stride=0, cout_stride=0, group=1, impl=0, x_w_pitch=0, x_w_pad=0):
     kh, kw = (k, k) if isinstance(k, int) else k
     sh, sw = (stride, stride) if isinstance(stride, int) else stride
     pt, pb, pl, pr = (pad,) * 4 if isinstance(pad, int) else pad
     return ConvDesc(N, H, W, Cin, Cout, cin_stride, cout_stride, kh, kw, sh, sw, pt, pb, pl, pr, 1, group,
-                    in_dtype, out_dtype, out2_dtype, EXB_F16 if res else -1, act, out_scale, out2_scale, impl)
+                    in_dtype, out_dtype, out2_dtype, EXB_F16 if res else -1, act, out_scale, out2_scale, impl, x_w_pitch, x_w_pad)
 
 
 class ConvWeights:
@@ -363,6 +365,17 @@ def nchw_f32_to_nhwc(ctx, x, dtype=EXB_F16, c_stride=0, scale=1.0, rounding=0, y
         y = t.empty((N, H, W, cs), dtype=torch_dtype(dtype), device=x.device)
     check(lib().exb_nchw_f32_to_nhwc(ctx.handle, ptr(x), ptr(y), dtype, N, Cc, H, W, cs, float(scale), rounding,
                                      cur_stream()))
+    return y
+
+
+def nchw_f32_to_nhwc_padded(ctx, x, dtype=EXB_F16, c_stride=4, w_pad=4, w_pitch=0, scale=1.0, rounding=0, y=None):
+    t = _torch()
+    N, Cc, H, W = x.shape
+    w_pitch = w_pitch or (W + 2 * w_pad)
+    if y is None:
+        y = t.empty((N, H, w_pitch, c_stride), dtype=torch_dtype(dtype), device=x.device)
+    check(lib().exb_nchw_f32_to_nhwc_padded(ctx.handle, ptr(x), ptr(y), dtype, N, Cc, H, W, c_stride, w_pad, w_pitch,
+                                            float(scale), rounding, cur_stream()))
     return y
 
 

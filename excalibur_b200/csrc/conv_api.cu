@@ -43,6 +43,10 @@ int resolve(const exb_conv_desc* d, ConvGeom& g) {
     g.in_dtype = d->in_dtype; g.out_dtype = d->out_dtype; g.out2_dtype = d->out2_dtype;
     g.has_res = d->res_dtype != -1;
     g.act = d->act; g.out_scale = d->out_scale; g.out2_scale = d->out2_scale;
+    EXB_REQUIRE(d->x_w_pad >= 0 && (d->x_w_pitch == 0 || d->x_w_pitch >= d->W + d->x_w_pad),
+                "bad input row padding (x_w_pad %d, x_w_pitch %d, W %d)", d->x_w_pad, d->x_w_pitch, d->W);
+    g.w_pitch = d->x_w_pitch ? d->x_w_pitch : d->W;
+    g.w_pad = d->x_w_pitch ? d->x_w_pad : 0;
     return EXB_OK;
 }
 
@@ -52,11 +56,11 @@ uint16_t f32_to_f16_bits(float f) {
 
 int pack_common(exb_ctx* ctx, const ConvGeom& g, int dtype, const void* hw, size_t wbytes,
                 const std::vector<float>& scale, const std::vector<float>& bias, int cout_pad, int cin_pad,
-                exb_conv_weights** out) {
+                int kw_pack, int s_shift, exb_conv_weights** out) {
     exb_conv_weights* w = new exb_conv_weights();
     memset(w, 0, sizeof(*w));
     w->dtype = dtype; w->Cout = g.Cout; w->Cin = g.Cin; w->kh = g.kh; w->kw = g.kw; w->group = g.group;
-    w->cout_pad = cout_pad; w->cin_pad = cin_pad; w->device = ctx->device;
+    w->cout_pad = cout_pad; w->cin_pad = cin_pad; w->kw_pack = kw_pack; w->s_shift = s_shift; w->device = ctx->device;
     cudaError_t e = cudaSetDevice(ctx->device);
     if (e == cudaSuccess) e = cudaMalloc(&w->d_w, wbytes);
     if (e == cudaSuccess) e = cudaMalloc(&w->d_scale, sizeof(float) * cout_pad);
@@ -72,14 +76,15 @@ int pack_common(exb_ctx* ctx, const ConvGeom& g, int dtype, const void* hw, size
     return EXB_OK;
 }
 
-// OIHW [Cout][cin_g][kh][kw] -> [cout_pad][kh][kw][cin_pad] (zero filled)
+// OIHW [Cout][cin_g][kh][kw] -> [cout_pad][kh][kw_pack][cin_pad] (zero filled), tap s at column s + s_shift
 template <typename TSrc, typename TDst, typename F>
-void repack(const TSrc* src, std::vector<TDst>& dst, const ConvGeom& g, int cin_g, int cin_pad, F cvt) {
+void repack(const TSrc* src, std::vector<TDst>& dst, const ConvGeom& g, int cin_g, int cin_pad, int kw_pack,
+            int s_shift, F cvt) {
     for (int o = 0; o < g.Cout; ++o)
         for (int c = 0; c < cin_g; ++c)
             for (int r = 0; r < g.kh; ++r)
                 for (int s = 0; s < g.kw; ++s)
-                    dst[(((size_t)o * g.kh + r) * g.kw + s) * cin_pad + c] =
+                    dst[(((size_t)o * g.kh + r) * kw_pack + s + s_shift) * cin_pad + c] =
                         cvt(src[(((size_t)o * cin_g + c) * g.kh + r) * g.kw + s]);
 }
 
@@ -113,14 +118,16 @@ extern "C" int exb_conv_weights_pack_f16(exb_ctx* ctx, const exb_conv_desc* d, c
     const int cin_g = g.Cin / g.group;
     const int cin_pad = g.group == 1 ? g.cin_stride : cin_g;
     const int cout_pad = (g.cout_stride + 15) / 16 * 16;  // covers the padding channels of y too
-    std::vector<uint16_t> packed((size_t)cout_pad * g.kh * g.kw * cin_pad, 0);
-    repack(w_oihw, packed, g, cin_g, cin_pad, f32_to_f16_bits);
+    const FoldPlan fold = conv_fold_plan(g);
+    const int kw_pack = fold.on ? fold.F : g.kw, s_shift = fold.on ? fold.shift : 0;
+    std::vector<uint16_t> packed((size_t)cout_pad * g.kh * kw_pack * cin_pad, 0);
+    repack(w_oihw, packed, g, cin_g, cin_pad, kw_pack, s_shift, f32_to_f16_bits);
     std::vector<float> scale(cout_pad, 0.f), b(cout_pad, 0.f);
     for (int o = 0; o < g.Cout; ++o) {
         scale[o] = 1.0f;
         if (bias) b[o] = bias[o];
     }
-    return pack_common(ctx, g, EXB_F16, packed.data(), packed.size() * 2, scale, b, cout_pad, cin_pad, out);
+    return pack_common(ctx, g, EXB_F16, packed.data(), packed.size() * 2, scale, b, cout_pad, cin_pad, kw_pack, s_shift, out);
 }
 
 extern "C" int exb_conv_weights_pack_i8(exb_ctx* ctx, const exb_conv_desc* d, const int8_t* w_oihw,
@@ -135,8 +142,10 @@ extern "C" int exb_conv_weights_pack_i8(exb_ctx* ctx, const exb_conv_desc* d, co
     const int cin_g = g.Cin / g.group;
     const int cin_pad = g.group == 1 ? g.cin_stride : cin_g;
     const int cout_pad = (g.cout_stride + 15) / 16 * 16;  // covers the padding channels of y too
-    std::vector<int8_t> packed((size_t)cout_pad * g.kh * g.kw * cin_pad, 0);
-    repack(w_oihw, packed, g, cin_g, cin_pad, [](int8_t v) { return v; });
+    const FoldPlan fold = conv_fold_plan(g);
+    const int kw_pack = fold.on ? fold.F : g.kw, s_shift = fold.on ? fold.shift : 0;
+    std::vector<int8_t> packed((size_t)cout_pad * g.kh * kw_pack * cin_pad, 0);
+    repack(w_oihw, packed, g, cin_g, cin_pad, kw_pack, s_shift, [](int8_t v) { return v; });
     std::vector<float> scale(cout_pad, 0.f), b(cout_pad, 0.f);
     for (int o = 0; o < g.Cout; ++o) {
         const float ws = n_wscale == 1 ? wscale[0] : wscale[o];
@@ -144,7 +153,7 @@ extern "C" int exb_conv_weights_pack_i8(exb_ctx* ctx, const exb_conv_desc* d, co
         scale[o] = (fabsf(ws) <= 1e-6) ? 0.f : (1.0f / (ws * act_scale));
         if (bias) b[o] = bias[o];
     }
-    return pack_common(ctx, g, EXB_I8, packed.data(), packed.size(), scale, b, cout_pad, cin_pad, out);
+    return pack_common(ctx, g, EXB_I8, packed.data(), packed.size(), scale, b, cout_pad, cin_pad, kw_pack, s_shift, out);
 }
 
 extern "C" int exb_conv_weights_destroy(exb_conv_weights* w) {
@@ -165,6 +174,11 @@ extern "C" int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* 
     EXB_REQUIRE(w->dtype == g.in_dtype && w->Cout == g.Cout && w->Cin == g.Cin && w->kh == g.kh && w->kw == g.kw &&
                     w->group == g.group && w->cin_pad == cin_pad,
                 "exb_conv2d_fwd: packed weights do not match the descriptor");
+    {
+        const FoldPlan fold = conv_fold_plan(g);
+        EXB_REQUIRE(w->kw_pack == (fold.on ? fold.F : g.kw) && w->s_shift == (fold.on ? fold.shift : 0),
+                    "exb_conv2d_fwd: weights were packed for a different input row layout");
+    }
     EXB_REQUIRE(w->device == ctx->device, "exb_conv2d_fwd: weights live on device %d, context on %d", w->device, ctx->device);
     if (g.N == 0) return EXB_OK;
     EXB_REQUIRE(x && y && aligned16(x) && aligned16(y), "exb_conv2d_fwd: null or misaligned x / y");

@@ -9,7 +9,9 @@ struct exb_conv_weights {
     int Cout, Cin, kh, kw, group;
     int cout_pad;     // rows of the packed matrix (Cout rounded up to 16)
     int cin_pad;      // channels per tap in the packed matrix (== x's physical channel count / group)
-    void* d_w;        // [cout_pad][kh][kw][cin_pad], K-major rows
+    int kw_pack;      // taps per kernel row in the packed matrix: kw, or the fold width F (>= kw)
+    int s_shift;      // column of tap s = 0 inside a packed kernel row (0 unless folded)
+    void* d_w;        // [cout_pad][kh][kw_pack][cin_pad], K-major rows
     float* d_scale;   // [cout_pad] epilogue multiplier (fp16: 1; int8: 1/(wscale*act_scale))
     float* d_bias;    // [cout_pad] zeros when the layer has no bias
     int device;
@@ -23,7 +25,40 @@ struct ConvGeom {
     int kh, kw, sh, sw, pt, pl, OH, OW, group;
     int in_dtype, out_dtype, out2_dtype, has_res, act;
     float out_scale, out2_scale;
+    int w_pitch, w_pad;   // physical pixels per input row and zero pixels left of pixel 0 (dense: W, 0)
 };
+
+// "Folded" K layout for convolutions with very few input channels (a stem): one K row of an
+// output pixel is the contiguous run of F input pixels x cin_stride channels that covers all kw
+// taps of one kernel row, so a kernel row is one K block instead of kw tiny ones.  It needs
+// physically zero-padded input rows, a W stride that keeps TMA's 16-byte alignment, and weights
+// packed [Cout][kh][F][cin_stride] with the taps placed at column `shift`.
+struct FoldPlan {
+    bool on;
+    int F;          // input pixels per K row
+    int shift;      // extra zero-weight columns on the left (pl_eff - pad_l)
+    int pl_eff;     // left reach of a K row in pixels (>= pad_l)
+    int kb_bytes;   // bytes of a K row: 32, 64 or 128
+};
+inline FoldPlan conv_fold_plan(const ConvGeom& g) {
+    FoldPlan f = {false, 0, 0, 0, 0};
+    const int px = g.cin_stride * (g.in_dtype == EXB_I8 ? 1 : 2);
+    if (g.w_pad <= 0 || g.group != 1 || px >= 32) return f;
+    if ((g.sw * px) % 16 != 0 || g.sh != g.sw || (g.sh != 1 && g.sh != 2)) return f;
+    int pl_eff = g.pl;
+    while (pl_eff <= g.w_pad && ((g.w_pad - pl_eff) * px) % 16 != 0) ++pl_eff;
+    if (pl_eff > g.w_pad) return f;
+    const int shift = pl_eff - g.pl;
+    for (int kb = 32; kb <= 128; kb *= 2) {
+        if (kb % px) continue;
+        const int F = kb / px;
+        if (F < g.kw + shift) continue;
+        if ((g.OW - 1) * g.sw - pl_eff + F + g.w_pad > g.w_pitch) return f;   // right padding too short
+        f.on = true; f.F = F; f.shift = shift; f.pl_eff = pl_eff; f.kb_bytes = kb;
+        return f;
+    }
+    return f;
+}
 
 struct EpiParams {
     const float* scale;

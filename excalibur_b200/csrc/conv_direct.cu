@@ -15,6 +15,8 @@ struct DirectParams {
     int cin_g;    // input channels per group actually multiplied
     int cout_g;   // output channels per group
     int w_cin;    // channels per tap in the packed weight rows
+    int kw_pack, s_shift;   // packed taps per kernel row / column of tap 0
+    int w_pitch, w_pad;     // physical input row pitch and left padding (pixels)
     int has_res;
     EpiParams e;
 };
@@ -42,8 +44,8 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const void* __restrict
             for (int s = 0; s < p.kw; ++s) {
                 const int iw = ow * p.sw - p.pl + s;
                 if (iw < 0 || iw >= p.W) continue;
-                const T* xp = x + (((int64_t)n * p.H + ih) * p.W + iw) * p.cin_stride + g * p.cin_g;
-                const T* wp = w + (((int64_t)co * p.kh + r) * p.kw + s) * p.w_cin;
+                const T* xp = x + (((int64_t)n * p.H + ih) * p.w_pitch + iw + p.w_pad) * p.cin_stride + g * p.cin_g;
+                const T* wp = w + (((int64_t)co * p.kh + r) * p.kw_pack + s + p.s_shift) * p.w_cin;
                 for (int c = 0; c < p.cin_g; ++c) {
                     if (kInt8) iacc += (int)xp[c] * (int)wp[c];
                     else facc = fmaf(__half2float(xp[c]), __half2float(wp[c]), facc);
@@ -83,6 +85,8 @@ int conv_direct_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb
     p.cin_g = g.Cin / g.group;
     p.cout_g = g.Cout / g.group;
     p.w_cin = w->cin_pad;
+    p.kw_pack = w->kw_pack; p.s_shift = w->s_shift;
+    p.w_pitch = g.w_pitch; p.w_pad = g.w_pad;
     p.has_res = g.has_res;
     p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.residual = static_cast<const __half*>(residual);
     p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;

@@ -59,6 +59,7 @@ struct ConvTcParams {
     EpiParams e;
     int* error;
     int kgroup;       // K blocks per pipeline stage (one mbarrier round trip per stage)
+    int fold;         // folded K layout (see FoldPlan): one K block per kernel row
 };
 
 struct TileCoord {
@@ -99,7 +100,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.n_tiles;
-    const int k_iters = p.kh * p.kw * p.cblks;
+    const int k_iters = p.fold ? p.kh : p.kh * p.kw * p.cblks;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -120,6 +121,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
         ptx::tmem_relinquish();
     }
     for (int it = threadIdx.x; it < k_iters; it += kThreads) {
+        if (p.fold) {   // one K block per kernel row: the box starts at the output column itself
+            const int oh_ = it - p.pad_t;
+            const int ph = p.stride == 2 ? (oh_ & 1) : 0;
+            k_tab[it] = make_int4(0, 0, p.stride == 2 ? ((oh_ - ph) >> 1) : oh_, (it * p.kb_elems) | ((ph * 2) << 28));
+            continue;
+        }
         const int tap = it / p.cblks, cb = it - tap * p.cblks;
         const int r = tap / p.kw, sx = tap - r * p.kw;
         int view = 0, dw, dh;
@@ -406,7 +413,7 @@ bool conv_tc_eligible(const ConvGeom& g) {
     const int es = g.in_dtype == EXB_I8 ? 1 : 2;
     if (g.group != 1) return false;
     if (g.sh != g.sw || (g.sh != 1 && g.sh != 2)) return false;
-    if ((g.cin_stride * es) % 32 != 0) return false;       // K block of at least 32 bytes
+    if ((g.cin_stride * es) % 32 != 0 && !conv_fold_plan(g).on) return false;   // K block of at least 32 bytes
     if (g.N < 1 || g.OH < 1 || g.OW < 1) return false;
     if (g.out_dtype == EXB_I32 && g.in_dtype != EXB_I8) return false;
     return true;
@@ -430,14 +437,22 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.kh = g.kh; p.kw = g.kw; p.stride = g.sh; p.pad_t = g.pt; p.pad_l = g.pl;
     p.cin_pad = g.cin_stride;
     const int row_bytes = g.cin_stride * es;
-    p.kb_bytes = row_bytes % 128 == 0 ? 128 : (row_bytes % 64 == 0 ? 64 : 32);
-    p.kb_elems = p.kb_bytes / es;
-    p.cblks = row_bytes / p.kb_bytes;
+    const FoldPlan fold = conv_fold_plan(g);
+    p.fold = fold.on ? 1 : 0;
+    if (fold.on) {
+        p.kb_bytes = fold.kb_bytes;
+        p.kb_elems = p.kb_bytes / es;
+        p.cblks = 1;
+    } else {
+        p.kb_bytes = row_bytes % 128 == 0 ? 128 : (row_bytes % 64 == 0 ? 64 : 32);
+        p.kb_elems = p.kb_bytes / es;
+        p.cblks = row_bytes / p.kb_bytes;
+    }
     p.a_bytes = kTileM * p.kb_bytes;
     p.b_bytes = p.BN * p.kb_bytes;
     p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
-    const int k_iters = g.kh * g.kw * p.cblks;
-    if ((int64_t)g.kh * g.kw * w->cin_pad >= (1 << 28)) return fail(EXB_ERR_UNSUPPORTED, "reduction dimension too large");
+    const int k_iters = fold.on ? g.kh : g.kh * g.kw * p.cblks;
+    if ((int64_t)g.kh * w->kw_pack * w->cin_pad >= (1 << 28)) return fail(EXB_ERR_UNSUPPORTED, "reduction dimension too large");
     const int epi_bytes = 2 * p.n_tiles * p.BN * (int)sizeof(float) + k_iters * (int)sizeof(int4);
     const int budget = ctx->smem_optin - 2048 - epi_bytes;  // static barriers + alignment slack + tables
     const int blk_bytes = p.a_bytes + p.b_bytes;
@@ -473,32 +488,44 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
 
     const CUtensorMapDataType dt = int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUtensorMapSwizzle sw = swizzle_for(p.kb_bytes);
-    // A: one view per input parity (only view 0 for stride 1).
+    // A: one view per input parity (only view 0 for stride 1).  Rows may be physically padded.
+    const size_t px_bytes = (size_t)g.cin_stride * es;
+    const size_t row_pitch = (size_t)g.w_pitch * px_bytes;
     const int nviews = g.sh == 1 ? 1 : 4;
     for (int v = 0; v < nviews; ++v) {
         const int ph = v >> 1, pw = v & 1;
         const int st_ = g.sh;
+        if (fold.on && pw) continue;   // the folded layout walks W inside the K row
         // rows / columns of this view: indices ph, ph+st, ... < H
         const int vh = (g.H - ph + st_ - 1) / st_;
         const int vw = (g.W - pw + st_ - 1) / st_;
-        if (vh <= 0 || vw <= 0) {
-            // view is empty (1-pixel-wide input): reuse view 0's descriptor slot with zero-size
-            // semantics by pointing at a valid 1x1 view; its taps never contribute because the
-            // corresponding coordinates are out of range.  Keep it simple: refuse.
-            return fail(EXB_ERR_UNSUPPORTED, "stride-2 convolution needs H and W of at least 2");
+        if (vh <= 0 || vw <= 0) return fail(EXB_ERR_UNSUPPORTED, "stride-2 convolution needs H and W of at least 2");
+        CUresult r;
+        if (fold.on) {
+            // dim0: F pixels x cin_stride channels (one K row), dim1: output columns, stepping
+            // stride_w pixels (windows of neighbouring columns overlap), dim2: rows of this parity.
+            cuuint64_t dims[4] = {(cuuint64_t)p.kb_elems, (cuuint64_t)g.OW, (cuuint64_t)vh, (cuuint64_t)g.N};
+            cuuint64_t strides[3] = {(cuuint64_t)g.sw * px_bytes, (cuuint64_t)st_ * row_pitch, (cuuint64_t)g.H * row_pitch};
+            cuuint32_t box[4] = {(cuuint32_t)p.kb_elems, (cuuint32_t)p.TW, (cuuint32_t)p.TH, (cuuint32_t)p.TN};
+            cuuint32_t estr[4] = {1, 1, 1, 1};
+            void* base = const_cast<char*>(static_cast<const char*>(x)) + (size_t)ph * row_pitch +
+                         (size_t)(g.w_pad - fold.pl_eff) * px_bytes;
+            r = encode(&p.tmA[v], dt, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        } else {
+            cuuint64_t dims[4] = {(cuuint64_t)g.cin_stride, (cuuint64_t)vw, (cuuint64_t)vh, (cuuint64_t)g.N};
+            cuuint64_t strides[3] = {(cuuint64_t)st_ * px_bytes, (cuuint64_t)st_ * row_pitch, (cuuint64_t)g.H * row_pitch};
+            cuuint32_t box[4] = {(cuuint32_t)p.kb_elems, (cuuint32_t)p.TW, (cuuint32_t)p.TH, (cuuint32_t)p.TN};
+            cuuint32_t estr[4] = {1, 1, 1, 1};
+            void* base = const_cast<char*>(static_cast<const char*>(x)) + (size_t)ph * row_pitch +
+                         (size_t)(pw + g.w_pad) * px_bytes;
+            r = encode(&p.tmA[v], dt, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         }
-        cuuint64_t dims[4] = {(cuuint64_t)g.cin_stride, (cuuint64_t)vw, (cuuint64_t)vh, (cuuint64_t)g.N};
-        cuuint64_t strides[3] = {(cuuint64_t)st_ * g.cin_stride * es, (cuuint64_t)st_ * g.W * g.cin_stride * es,
-                                 (cuuint64_t)g.H * g.W * g.cin_stride * es};
-        cuuint32_t box[4] = {(cuuint32_t)p.kb_elems, (cuuint32_t)p.TW, (cuuint32_t)p.TH, (cuuint32_t)p.TN};
-        cuuint32_t estr[4] = {1, 1, 1, 1};
-        void* base = const_cast<char*>(static_cast<const char*>(x)) + ((size_t)ph * g.W + pw) * g.cin_stride * es;
-        CUresult r = encode(&p.tmA[v], dt, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(A view %d) failed with %d", v, (int)r);
     }
     {
-        const int K = g.kh * g.kw * w->cin_pad;
+        const int K = g.kh * w->kw_pack * w->cin_pad;
         cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)w->cout_pad};
         cuuint64_t strides[1] = {(cuuint64_t)K * es};
         cuuint32_t box[2] = {(cuuint32_t)p.kb_elems, (cuuint32_t)p.BN};

@@ -224,7 +224,9 @@ exb_conv_weights* operation_convolution<Dtype>::packed(exb_ctx* ctx, const exb_c
     const int cin_stride = d.cin_stride ? d.cin_stride : d.Cin;
     const int cout_stride = d.cout_stride ? d.cout_stride : d.Cout;
     for (auto& e : packed_)
-        if (e.in_dtype == d.in_dtype && e.cin_stride == cin_stride && e.cout_stride == cout_stride) return e.w;
+        if (e.in_dtype == d.in_dtype && e.cin_stride == cin_stride && e.cout_stride == cout_stride &&
+            e.w_pitch == d.x_w_pitch && e.w_pad == d.x_w_pad)
+            return e.w;
     exb_conv_weights* w = nullptr;
     const float* bias = this->bias_term_ ? this->weights_f32_[1]->cpu_data() : nullptr;
     if (d.in_dtype == EXB_I8) {
@@ -238,7 +240,7 @@ exb_conv_weights* operation_convolution<Dtype>::packed(exb_ctx* ctx, const exb_c
         exb_check(exb_conv_weights_pack_f16(ctx, &d, this->weights_f32_[0]->cpu_data(), bias, &w),
                   "exb_conv_weights_pack_f16");
     }
-    packed_.push_back({d.in_dtype, cin_stride, cout_stride, w});
+    packed_.push_back({d.in_dtype, cin_stride, cout_stride, d.x_w_pitch, d.x_w_pad, w});
     return w;
 }
 

@@ -65,7 +65,7 @@ protected:
     virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
     void forward_nchw_f32(exb_ctx* h, const f32_list& bottoms, f32_list& tops, bool int8);
 
-    struct packed_entry { int in_dtype, cin_stride, cout_stride; exb_conv_weights* w; };
+    struct packed_entry { int in_dtype, cin_stride, cout_stride, w_pitch, w_pad; exb_conv_weights* w; };
     std::vector<packed_entry> packed_;
     device_scratch scratch_in_, scratch_out_;
 };

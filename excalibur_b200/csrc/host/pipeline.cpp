@@ -59,6 +59,7 @@ struct fmap_info {
     int root = -1;                 // featmap this one aliases (Split), or itself
     int N = 0, C = 0, H = 0, W = 0;
     int cs = 0;                    // physical channels of the NHWC device forms
+    int w_pitch = 0, w_pad = 0;    // physically zero-padded rows (network input feeding a stem conv); 0 = dense
     bool need_f16 = false, need_i8 = false, need_f32 = false;
     float i8_scale = 0.f;          // multiplier of the int8 form
     std::vector<float> extra_i8_scales;   // further int8 consumers with other scales
@@ -134,7 +135,7 @@ private:
     }
     void* form_f16(fmap_info& f) {
         if (!f.f16) f.f16 = std::make_shared<dev_buf>();
-        return f.f16->ensure((size_t)f.N * f.H * f.W * f.cs * 2, device_);
+        return f.f16->ensure((size_t)f.N * f.H * (f.w_pitch ? f.w_pitch : f.W) * f.cs * 2, device_);
     }
     void* form_i8(fmap_info& f) {
         if (!f.i8) f.i8 = std::make_shared<dev_buf>();
@@ -357,18 +358,46 @@ void fused_plan::build(int N, int C, int H, int W) {
     // ---- 4. steps in execution order ---------------------------------------------------------
     exb_ctx* ctx = ctx_;
     {
-        fmap_info& in = fmaps_[root(fid(inputs_[0]))];
+        const int in_id = root(fid(inputs_[0]));
+        fmap_info& in = fmaps_[in_id];
         set_shape(in, N, C, H, W);
         float* stage = static_cast<float*>(staging_in_.ensure((size_t)N * C * H * W * 4, device_));
+        // A few-channel image that feeds one fp16 convolution is stored as NHWC4 rows with zero
+        // padding along W when that lets the tensor-core kernel fold the kw taps into K.
+        bool padded = false;
+        if (C <= 4 && in.need_f16 && !in.need_i8 && consumers[in_id].size() == 1 &&
+            lower_type(params_[consumers[in_id][0]]) == "convolution") {
+            auto* conv = dynamic_cast<operation_convolution<float>*>(ops_[consumers[in_id][0]].get());
+            if (conv && !conv->is_int8() && conv->group_ == 1 && conv->in_channels() == C) {
+                exb_conv_desc d = conv->base_desc(N, H, W);
+                d.in_dtype = EXB_F16;
+                d.cin_stride = 4;
+                d.x_w_pad = 4;
+                d.x_w_pitch = round_up(W + 4 + 8, 8);
+                if (exb_conv2d_uses_tensor_cores(&d) == 1) {
+                    padded = true;
+                    in.cs = 4;
+                    in.w_pad = d.x_w_pad;
+                    in.w_pitch = d.x_w_pitch;
+                }
+            }
+        }
         const bool direct_i8 = in.need_i8 && !in.need_f16;
         void* dst = direct_i8 ? form_i8(in) : form_f16(in);
-        const int cs = in.cs;
+        const int cs = in.cs, w_pad = in.w_pad, w_pitch = in.w_pitch;
         const float s = in.i8_scale;
-        add_step("ingest " + in.name, [=](cudaStream_t st) {
-            exb_check(exb_nchw_f32_to_nhwc(ctx, stage, dst, direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs,
-                                           direct_i8 ? s : 1.f, 1, st),
-                      "exb_nchw_f32_to_nhwc");
-        });
+        if (padded) {
+            add_step("ingest " + in.name, [=](cudaStream_t st) {
+                exb_check(exb_nchw_f32_to_nhwc_padded(ctx, stage, dst, EXB_F16, N, C, H, W, cs, w_pad, w_pitch, 1.f, 1, st),
+                          "exb_nchw_f32_to_nhwc_padded");
+            });
+        } else {
+            add_step("ingest " + in.name, [=](cudaStream_t st) {
+                exb_check(exb_nchw_f32_to_nhwc(ctx, stage, dst, direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs,
+                                               direct_i8 ? s : 1.f, 1, st),
+                          "exb_nchw_f32_to_nhwc");
+            });
+        }
         finish_forms(in, direct_i8);
     }
 
@@ -404,6 +433,8 @@ void fused_plan::build(int N, int C, int H, int W) {
         exb_conv_desc d = conv->base_desc(x.N, x.H, x.W);
         d.in_dtype = int8 ? EXB_I8 : EXB_F16;
         d.cin_stride = conv->group_ == 1 ? x.cs : x.C;
+        d.x_w_pitch = x.w_pitch;
+        d.x_w_pad = x.w_pad;
         d.act = g.act;
         int OH, OW;
         exb_check(exb_conv_out_dims(&d, &OH, &OW), "exb_conv_out_dims");
@@ -658,6 +689,10 @@ std::shared_ptr<memory::tensor<float>> fused_plan::fetch(const std::string& name
     auto it = index_.find(name);
     if (it == index_.end()) return nullptr;
     fmap_info& f = fmaps_[root(it->second)];
+    if (f.w_pitch) {
+        LOG(WARNING) << "feature map " << name << " is kept in a padded row layout and is not exported";
+        return nullptr;
+    }
     if (!f.produced) {
         LOG(WARNING) << "feature map " << name << " was fused into its consumer and is not materialised; "
                         "call set_fusion(false) to inspect it";

@@ -59,6 +59,38 @@ __global__ void __launch_bounds__(256) nhwc_to_nchw_kernel(const In* __restrict_
     }
 }
 
+// Few-channel images (C <= 8): one thread per output pixel slot.  Reads are coalesced along W in
+// each of the C planes, the write is one 8- or 16-byte vector per pixel; padding pixels and
+// channels are written as zero.
+template <typename Out, int CS>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_padded_kernel(const float* __restrict__ x, Out* __restrict__ y,
+                                                                  int N, int C, int H, int W, int w_pad, int w_pitch,
+                                                                  float scale, int rounding) {
+    const int64_t total = (int64_t)N * H * w_pitch;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int wp = (int)(i % w_pitch);
+        const int64_t nh = i / w_pitch;
+        const int h = (int)(nh % H);
+        const int n = (int)(nh / H);
+        const int w = wp - w_pad;
+        alignas(16) Out v[CS];
+#pragma unroll
+        for (int c = 0; c < CS; ++c) {
+            float f = 0.f;
+            if (c < C && w >= 0 && w < W) f = x[(((int64_t)n * C + c) * H + h) * W + w];
+            v[c] = cvt_out<Out>(f, scale, rounding);
+        }
+        Out* dst = y + i * CS;
+        if (sizeof(Out) * CS == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(v);
+        else if (sizeof(Out) * CS == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(v);
+        else if (sizeof(Out) * CS == 4) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(v);
+        else {
+#pragma unroll
+            for (int c = 0; c < CS; ++c) dst[c] = v[c];
+        }
+    }
+}
+
 int check_dims(const exb_ctx* ctx, const void* a, const void* b, int N, int C, int H, int W, int c_stride) {
     EXB_REQUIRE(ctx != nullptr, "null context");
     EXB_REQUIRE(N >= 0 && C > 0 && H > 0 && W > 0, "bad tensor shape %dx%dx%dx%d", N, C, H, W);
@@ -105,4 +137,23 @@ extern "C" int exb_nhwc_to_nchw_f32(exb_ctx* ctx, const void* x, int dtype, floa
     default: return fail(EXB_ERR_UNSUPPORTED, "exb_nhwc_to_nchw_f32: dtype %d", dtype);
     }
     return after_launch("nhwc_to_nchw_kernel");
+}
+
+extern "C" int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x, void* y, int dtype, int N, int C, int H,
+                                           int W, int c_stride, int w_pad, int w_pitch, float scale, int rounding,
+                                           void* stream) {
+    if (c_stride == 0) c_stride = C;
+    if (int rc = check_dims(ctx, x, y, N, C, H, W, c_stride)) return rc;
+    EXB_REQUIRE(w_pad >= 0 && w_pitch >= W + w_pad, "bad row padding (w_pad %d, w_pitch %d, W %d)", w_pad, w_pitch, W);
+    if (c_stride != 4 && c_stride != 8)
+        return fail(EXB_ERR_UNSUPPORTED, "padded ingest supports c_stride 4 or 8, got %d", c_stride);
+    if (N == 0) return EXB_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = stream_grid(ctx, (int64_t)N * H * w_pitch, 256, 16);
+#define EXB_LAUNCH(T, CS) nchw_to_nhwc_padded_kernel<T, CS><<<grid, 256, 0, st>>>(x, static_cast<T*>(y), N, C, H, W, w_pad, w_pitch, scale, rounding)
+    if (dtype == EXB_F16) { if (c_stride == 4) EXB_LAUNCH(__half, 4); else EXB_LAUNCH(__half, 8); }
+    else if (dtype == EXB_I8) { if (c_stride == 4) EXB_LAUNCH(int8_t, 4); else EXB_LAUNCH(int8_t, 8); }
+    else return fail(EXB_ERR_UNSUPPORTED, "padded ingest supports EXB_F16 and EXB_I8 output");
+#undef EXB_LAUNCH
+    return after_launch("nchw_to_nhwc_padded_kernel");
 }

@@ -89,6 +89,12 @@ EXB_API int exb_ctx_sync_check(exb_ctx* ctx, void* stream);
 EXB_API int exb_nchw_f32_to_nhwc(exb_ctx* ctx, const float* x_nchw, void* y_nhwc, int dtype,
                                  int N, int C, int H, int W, int c_stride, float scale,
                                  int rounding, void* stream);
+/* Same conversion into rows that are physically zero-padded along W: y is
+ * [N][H][w_pitch][c_stride], pixel 0 of each row at index w_pad; padding pixels and channels are
+ * written as zero.  For images with up to 8 channels (the network input). */
+EXB_API int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x_nchw, void* y_nhwc, int dtype,
+                                        int N, int C, int H, int W, int c_stride, int w_pad,
+                                        int w_pitch, float scale, int rounding, void* stream);
 EXB_API int exb_nhwc_to_nchw_f32(exb_ctx* ctx, const void* x_nhwc, int dtype, float* y_nchw,
                                  int N, int C, int H, int W, int c_stride, float scale,
                                  void* stream);
@@ -124,6 +130,12 @@ typedef struct exb_conv_desc {
     float out_scale;        /* multiplier used when out_dtype == EXB_I8 */
     float out2_scale;       /* multiplier used when out2_dtype == EXB_I8 */
     int32_t impl;           /* 0 = auto (tensor cores when eligible), 1 = force direct kernel */
+    /* Optional physically padded input rows: x is [N][H][x_w_pitch][cin_stride] and pixel 0 of a
+     * row sits x_w_pad pixels in; the padding pixels hold zeros (exb_nchw_f32_to_nhwc_padded
+     * writes this layout).  0 / 0 = dense rows.  With few input channels (a stem conv) this lets
+     * the tensor-core kernel take kw taps x cin channels as ONE contiguous K row per output pixel. */
+    int32_t x_w_pitch;
+    int32_t x_w_pad;
 } exb_conv_desc;
 
 /* Output spatial size: (in + pad_a + pad_b - k) / stride + 1

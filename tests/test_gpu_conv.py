@@ -232,3 +232,37 @@ def test_conv_empty_batch_and_errors(ctx):
     bad = capi.make_conv_desc(1, 2, 2, 64, 64, 3, 1, 0, capi.EXB_I8, capi.EXB_I32)   # window > input
     assert capi.lib().exb_conv2d_fwd(ctx.handle, bad, None, wp.handle, None, None, None, None) == capi.EXB_ERR_BAD_ARG
     assert "window" in capi.last_error()
+
+
+STEM_CASES = [
+    # N, H, W, Cout, k, stride, pad, w_pad
+    (2, 64, 64, 64, 7, 2, 3, 4),      # ResNet stem
+    (3, 37, 41, 32, 3, 2, 1, 4),      # MobileNet stem, odd sizes
+    (2, 48, 40, 32, 6, 2, 2, 4),      # YOLOv5 stem
+    (1, 224, 224, 64, 7, 2, 3, 4),
+]
+
+
+@pytest.mark.parametrize("impl", [0, 1], ids=["tc", "direct"])
+@pytest.mark.parametrize("case", STEM_CASES)
+def test_stem_conv_folded_rows(ctx, case, impl):
+    """3-channel stem: fp32 NCHW image -> padded NHWC4 fp16 rows -> conv with kw taps folded into K."""
+    capi = _capi()
+    N, H, W, Cout, k, stride, pad, w_pad = case
+    r = rng(sum(case))
+    x = r.uniform(0, 1, (N, 3, H, W)).astype(np.float32)
+    w = f16_round(r.standard_normal((Cout, 3, k, k)) * np.sqrt(2.0 / (3 * k * k)))
+    b = (r.standard_normal(Cout) * 0.01).astype(np.float32)
+    ref = O.conv2d_f32(f16_round(x), w, b, stride, pad, act=1)
+    w_pitch = (W + w_pad + 8 + 7) // 8 * 8
+    xp = capi.nchw_f32_to_nhwc_padded(ctx, dev(x), capi.EXB_F16, 4, w_pad, w_pitch)
+    xh = host(xp).astype(np.float32)
+    np.testing.assert_array_equal(xh[:, :, w_pad:w_pad + W, :3], f16_round(np.transpose(x, (0, 2, 3, 1))))
+    assert not xh[:, :, :w_pad].any() and not xh[:, :, w_pad + W:].any() and not xh[..., 3].any()
+    d = capi.make_conv_desc(N, H, W, 3, Cout, k, stride, pad, capi.EXB_F16, capi.EXB_F32, act=1, cin_stride=4,
+                            impl=impl, x_w_pitch=w_pitch, x_w_pad=w_pad)
+    assert capi.lib().exb_conv2d_uses_tensor_cores(d) == (1 if impl == 0 else 0)
+    wp = capi.ConvWeights(ctx, d, w, b)
+    y, _ = capi.conv2d(ctx, d, xp, wp)
+    ctx.sync_check()
+    np.testing.assert_allclose(to_nchw(host(y)), ref, rtol=1e-4, atol=1e-4)
