@@ -304,11 +304,8 @@ def run_gpu_arm(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     def max_over_ranks(v):
-        if dist is None:
-            return v
-        t = torch.tensor([v], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        from excalibur_b200 import sharding
+        return sharding.max_over_ranks(v, dist, "cuda")
 
     g8, scales = build_int8_net_gpu(local_rank)
     pipe = host.Pipeline(g8.phai_text(), g8.racy_bytes(), local_rank, fusion=True, cuda_graph=True)
