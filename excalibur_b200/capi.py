@@ -20,7 +20,7 @@ EXPORTED_SYMBOLS = [
     "exb_ctx_sync_check", "exb_nchw_f32_to_nhwc", "exb_nchw_f32_to_nhwc_padded", "exb_nhwc_to_nchw_f32", "exb_conv_out_dims",
     "exb_conv_weights_pack_f16", "exb_conv_weights_pack_i8", "exb_conv_weights_destroy",
     "exb_conv2d_fwd", "exb_conv2d_uses_tensor_cores", "exb_dw_weights_pack", "exb_dw_weights_destroy",
-    "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_eltwise_fwd", "exb_binaryop_fwd",
+    "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_pool2d_nchw_f32_static", "exb_eltwise_fwd", "exb_binaryop_fwd",
     "exb_binaryop_scalar_fwd", "exb_relu_fwd", "exb_activation_fwd", "exb_quantize_fwd",
     "exb_dequantize_fwd",
 ]
@@ -84,6 +84,7 @@ def lib():
         L.exb_dwconv2d_fwd.argtypes = [vp, C.POINTER(DwConvDesc), vp, vp, vp, vp]
         L.exb_pool_out_dims.argtypes = [C.POINTER(PoolDesc), C.POINTER(i32), C.POINTER(i32)]
         L.exb_pool2d_fwd.argtypes = [vp, C.POINTER(PoolDesc), vp, vp, vp, vp]
+        L.exb_pool2d_nchw_f32_static.argtypes = [i32, C.POINTER(PoolDesc), vp, vp, vp]
         L.exb_eltwise_fwd.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(f32), vp, i64, i32, vp]
         L.exb_binaryop_fwd.argtypes = [vp, i32, vp, vp, vp, i64, i32, vp]
         L.exb_binaryop_scalar_fwd.argtypes = [vp, i32, vp, f32, vp, i64, i32, vp]

@@ -219,6 +219,27 @@ EXB_API int exb_pool_out_dims(const exb_pool_desc* d, int* PH, int* PW);
 EXB_API int exb_pool2d_fwd(exb_ctx* ctx, const exb_pool_desc* d, const void* x, void* y,
                            void* y2, void* stream);
 
+/* Pooling of an fp32 NCHW tensor (the reference's own tensor layout) WITHOUT ANY ALLOCATION.
+ * This entry point has no counterpart in the reference.  It is meant for callers that must not
+ * allocate at the point where they run inference: hosts that hand out all device memory at
+ * start-up and forbid cudaMalloc afterwards (hard real-time or safety-reviewed loops), and
+ * plug-ins living inside an application whose allocator may not be entered from the inference
+ * thread.  It needs no exb_ctx.
+ *
+ * d->dtype must be EXB_F32 and d->out2_dtype -1; d->c_stride is ignored.  x_nchw is
+ * [N][C][H][W], y_nchw [N][C][PH][PW] (exb_pool_out_dims), both device pointers owned by the
+ * caller.  The two NHWC intermediates the kernels need are kept in a 16 MiB buffer that is part
+ * of the library image on every GPU that loads it (it stays resident until the process exits):
+ *   (N*H*W + N*PH*PW) * round_up(C,4) * 4 bytes, each part rounded up to 256, must fit in
+ *   16 MiB; larger tensors are refused with EXB_ERR_NOMEM and a message, nothing is launched.
+ * The first call on a device looks up the buffer's device address (a query, not an allocation);
+ * make that first call before starting a stream capture.  All calls on a device share the
+ * buffer: calls whose kernels may overlap on the GPU (different streams, or different threads)
+ * race with each other - serialise them.  The buffer keeps the previous call's data; the entry
+ * point overwrites every byte it later reads, so no clearing is needed between calls. */
+EXB_API int exb_pool2d_nchw_f32_static(int device, const exb_pool_desc* d, const float* x_nchw,
+                                       float* y_nchw, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Element-wise ops on `count` contiguous elements of dtype EXB_F16 or EXB_F32.
  * exb_eltwise_fwd   - operation_eltwise (src/Excalibur/operation_eltwise.cpp:42-94,
