@@ -41,7 +41,8 @@ def _deps_mtime():
 
 
 def _compile(src, obj, verbose):
-    cmd = [nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
+    extra = os.environ.get("EXB_NVCC_EXTRA", "").split()   # e.g. -DEXB_CONV_EXPERIMENTS for kernel experiments
+    cmd = [nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))

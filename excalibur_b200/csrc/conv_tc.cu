@@ -28,8 +28,6 @@ namespace exb {
 namespace {
 
 constexpr int kMaxStages = 8;
-constexpr int kThreads = 640;
-constexpr int kEpiWarps = 16;
 constexpr int kFirstEpiWarp = 4;
 constexpr int kMaxAccBufs = 4;
 constexpr int kTileM = 128;
@@ -60,6 +58,8 @@ struct ConvTcParams {
     int* error;
     int kgroup;       // K blocks per pipeline stage (one mbarrier round trip per stage)
     int fold;         // folded K layout (see FoldPlan): one K block per kernel row
+    int b_resident;   // the whole weight slice stays in shared memory for the life of the CTA
+    int b_region;     // bytes of the B region in shared memory (ring or resident copy)
 };
 
 struct TileCoord {
@@ -77,13 +77,25 @@ __device__ __forceinline__ TileCoord decode_tile(const ConvTcParams& p, int t) {
     return c;
 }
 
-template <bool kInt8>
-__global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_constant__ ConvTcParams p) {
+// kDbg is 0 in the product; builds with -DEXB_CONV_EXPERIMENTS can switch single parts of the
+// kernel off (1: epilogue math and stores, 2: TMA loads, 4: MMAs, 8: TMEM loads) to see which
+// part bounds a layer.  The results are wrong in those modes by construction.
+//
+// kEpiWarps = 16: one CTA per SM (all of shared memory and TMEM, 2-4 accumulator buffers).
+// kEpiWarps = 8:  two CTAs per SM for layers with narrow N tiles, whose cost is the issue rate of
+//                 the single MMA-issuing thread rather than tensor throughput: two CTAs give two
+//                 issuers (and two producers) per SM; each takes half the shared memory and at
+//                 most 256 TMEM columns.
+template <bool kInt8, int kDbg, int kEpiWarps>
+__global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps == 8 ? 2 : 1)
+    conv_tc_kernel(const __grid_constant__ ConvTcParams p) {
+    constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
     __shared__ __align__(8) uint64_t tfull_bar[kMaxAccBufs];
     __shared__ __align__(8) uint64_t tempty_bar[kMaxAccBufs];
+    __shared__ __align__(8) uint64_t bres_bar;
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
 
@@ -92,7 +104,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + (size_t)p.stages * p.kgroup * p.a_bytes;
     // Per-output-channel scale and bias of every N tile, staged once per CTA.
-    float* s_scale = reinterpret_cast<float*>(smem_b + (size_t)p.stages * p.kgroup * p.b_bytes);
+    float* s_scale = reinterpret_cast<float*>(smem_b + (size_t)p.b_region);
     float* s_bias = s_scale + p.n_tiles * p.BN;
     // Per K iteration (tap, channel block): TMA coordinates that do not depend on the tile.
     int4* k_tab = reinterpret_cast<int4*>(s_bias + p.n_tiles * p.BN);
@@ -112,6 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
             ptx::mbar_init(&tfull_bar[i], 1);
             ptx::mbar_init(&tempty_bar[i], kEpiWarps / p.acc_bufs);
         }
+        ptx::mbar_init(&bres_bar, 1);
         ptx::fence_mbar_init();
         ptx::tma_prefetch_desc(&p.tmA[0]);
         ptx::tma_prefetch_desc(&p.tmB);
@@ -167,7 +180,16 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
         const uint32_t full0 = ptx::smem_u32(&full_bar[0]), empty0 = ptx::smem_u32(&empty_bar[0]);
         const uint64_t mapA0 = reinterpret_cast<uint64_t>(&p.tmA[0]);
         const uint64_t mapB = reinterpret_cast<uint64_t>(&p.tmB);
-        const uint32_t tx = (uint32_t)(p.a_tx_bytes + p.b_bytes);
+        const bool bres = p.b_resident != 0;
+        const uint32_t tx = (uint32_t)(p.a_tx_bytes + (bres ? 0 : p.b_bytes));
+        if (bres && lane == 0) {
+            // Weights stay resident: the slice [BN x K] is loaded once (n_tiles == 1 here).
+            const uint32_t rb = ptx::smem_u32(&bres_bar);
+            ptx::mbar_arrive_expect_tx_u32(rb, (uint32_t)(k_iters * p.b_bytes));
+            for (int it = 0; it < k_iters; ++it)
+                ptx::tma_load_2d_u32(ptx::smem_u32(smem_b) + (uint32_t)(it * p.b_bytes), mapB, rb,
+                                     k_tab[it].w & 0x0fffffff, 0);
+        }
         if (lane < G) {
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
@@ -182,11 +204,15 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
                         break;
                     }
                     const uint32_t fb = full0 + stage * 8;
+                    if (kDbg & 2) {
+                        if (lane == 0) ptx::mbar_arrive_u32(fb);
+                    } else {
                     if (lane == 0) ptx::mbar_arrive_expect_tx_u32(fb, tx * (uint32_t)nb);
                     if (mine) {
                         ptx::tma_load_4d_u32(a_base + stage * a_stage, mapA0 + ((uint32_t)e.w >> 28) * sizeof(CUtensorMap), fb,
                                              e.x, tc.ow0 + e.y, tc.oh0 + e.z, tc.n0);
-                        ptx::tma_load_2d_u32(b_base + stage * b_stage, mapB, fb, e.w & 0x0fffffff, ncoord);
+                        if (!bres) ptx::tma_load_2d_u32(b_base + stage * b_stage, mapB, fb, e.w & 0x0fffffff, ncoord);
+                    }
                     }
                     if (++stage == p.stages) {
                         stage = 0;
@@ -219,8 +245,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
             const uint32_t a_lo0 = (uint32_t)d0;
             const uint32_t b_lo0 = (uint32_t)ptx::make_smem_desc(ptx::smem_u32(smem_b), (uint32_t)p.kb_bytes);
             const uint32_t a_blk = (uint32_t)p.a_bytes >> 4, b_blk = (uint32_t)p.b_bytes >> 4;
-            const uint32_t a_stage = a_blk * G, b_stage = b_blk * G;
+            const bool bres = p.b_resident != 0;
+            const uint32_t a_stage = a_blk * G, b_stage = bres ? 0u : b_blk * G;
             const uint32_t idesc = p.idesc;
+            if (bres && !ptx::mbar_wait_bounded(&bres_bar, 0, &abort_flag, kMaxSpins)) ok = false;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 if (!ptx::mbar_wait_bounded_u32(tempty0 + acc * 8, acc_phase ^ 1u, &abort_flag, kMaxSpins)) {
                     ok = false;
@@ -235,8 +263,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
                         ok = false;
                         break;
                     }
-                    uint32_t a_lo = a_lo0 + stage * a_stage, b_lo = b_lo0 + stage * b_stage;
-                    for (int g = 0; g < nb; ++g) {
+                    uint32_t a_lo = a_lo0 + stage * a_stage;
+                    uint32_t b_lo = b_lo0 + (bres ? (uint32_t)it0 * b_blk : stage * b_stage);
+                    for (int g = 0; g < nb && !(kDbg & 4); ++g) {
                         if (ksteps == 4) {
                             ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
                             ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo + 2, b_lo + 2, desc_hi, idesc, 1);
@@ -299,10 +328,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const __grid_const
             ptx::tc_fence_after_sync();
             for (int chunk = sub; chunk < n_chunks; chunk += nsub) {
                 uint32_t raw[16];
+                if (kDbg & 8) continue;
                 ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
                 ptx::tmem_ld_wait();
                 const int cl = tc.ntile * p.BN + chunk * 16;   // first channel of the chunk
-                if (!valid || cl >= p.e.cout_stride) continue;
+                if (!valid || cl >= p.e.cout_stride || (kDbg & 1)) continue;
                 const int64_t off = pix * p.e.cout_stride + cl;
                 float v[16];
                 {
@@ -434,6 +464,11 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.tiles_nb = (g.N + p.TN - 1) / p.TN;
     p.n_tiles = (w->cout_pad + 255) / 256;
     p.BN = round_up((w->cout_pad + p.n_tiles - 1) / p.n_tiles, 16);
+    // Two CTAs per SM when the N tile is narrow (see the kernel's comment).
+    bool two = p.BN <= 128;
+#ifdef EXB_CONV_EXPERIMENTS
+    if (const char* e = getenv("EXB_CONV_ONE_CTA")) two = two && atoi(e) == 0;
+#endif
     p.kh = g.kh; p.kw = g.kw; p.stride = g.sh; p.pad_t = g.pt; p.pad_l = g.pl;
     p.cin_pad = g.cin_stride;
     const int row_bytes = g.cin_stride * es;
@@ -451,11 +486,20 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.a_bytes = kTileM * p.kb_bytes;
     p.b_bytes = p.BN * p.kb_bytes;
     p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
+    const int ctas_per_sm = two ? 2 : 1;
     const int k_iters = fold.on ? g.kh : g.kh * g.kw * p.cblks;
     if ((int64_t)g.kh * w->kw_pack * w->cin_pad >= (1 << 28)) return fail(EXB_ERR_UNSUPPORTED, "reduction dimension too large");
     const int epi_bytes = 2 * p.n_tiles * p.BN * (int)sizeof(float) + k_iters * (int)sizeof(int4);
-    const int budget = ctx->smem_optin - 2048 - epi_bytes;  // static barriers + alignment slack + tables
-    const int blk_bytes = p.a_bytes + p.b_bytes;
+    // static barriers + alignment slack + tables; two resident CTAs share the SM's 228 KB
+    // (1 KB of which is reserved per CTA)
+    int budget = (two ? (228 * 1024 / 2 - 1024) : ctx->smem_optin) - 2048 - epi_bytes;
+    // Keep the weights in shared memory for the whole kernel when the slice fits beside a useful
+    // operand ring: it removes the weight re-read per tile from the L2 -> SM traffic that bounds
+    // this kernel.
+    const int b_all = k_iters * p.b_bytes;
+    p.b_resident = (p.n_tiles == 1 && b_all <= 150 * 1024 && budget - b_all >= 4 * p.a_bytes) ? 1 : 0;
+    if (p.b_resident) budget -= b_all;
+    const int blk_bytes = p.a_bytes + (p.b_resident ? 0 : p.b_bytes);
     // K blocks per stage: aim at ~48 KB stages (one mbarrier round trip each), keep >= 3 stages,
     // prefer a group size that divides the K loop.
     int gmax = (48 * 1024) / blk_bytes;
@@ -473,8 +517,9 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     int stages = budget / (G * blk_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return fail(EXB_ERR_UNSUPPORTED, "conv tile does not fit shared memory (BN=%d)", p.BN);
+    p.b_region = p.b_resident ? b_all : stages * G * p.b_bytes;
     p.stages = stages;
-    p.acc_bufs = p.BN <= 128 ? 4 : 2;
+    p.acc_bufs = two ? 2 : (p.BN <= 128 ? 4 : 2);
     int cols = 32;
     while (cols < p.acc_bufs * p.BN) cols *= 2;
     p.tmem_cols = cols;
@@ -536,11 +581,28 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     }
 
     const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.n_tiles;
-    const int grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
-    const size_t smem = (size_t)p.stages * p.kgroup * (p.a_bytes + p.b_bytes) + 1024 + epi_bytes;
-    auto kern = int8 ? conv_tc_kernel<true> : conv_tc_kernel<false>;
+    const int max_ctas = ctx->sm_count * ctas_per_sm;
+    const int grid = total_tiles < max_ctas ? total_tiles : max_ctas;
+    const size_t smem = (size_t)p.stages * p.kgroup * p.a_bytes + p.b_region + 1024 + epi_bytes;
+    auto kern = int8 ? (two ? conv_tc_kernel<true, 0, 8> : conv_tc_kernel<true, 0, 16>)
+                     : (two ? conv_tc_kernel<false, 0, 8> : conv_tc_kernel<false, 0, 16>);
+#ifdef EXB_CONV_EXPERIMENTS
+    if (const char* e = getenv("EXB_CONV_DBG")) {
+        switch (atoi(e)) {
+        case 1: kern = int8 ? (two ? conv_tc_kernel<true, 1, 8> : conv_tc_kernel<true, 1, 16>) : (two ? conv_tc_kernel<false, 1, 8> : conv_tc_kernel<false, 1, 16>); break;
+        case 2: kern = int8 ? (two ? conv_tc_kernel<true, 2, 8> : conv_tc_kernel<true, 2, 16>) : (two ? conv_tc_kernel<false, 2, 8> : conv_tc_kernel<false, 2, 16>); break;
+        case 4: kern = int8 ? (two ? conv_tc_kernel<true, 4, 8> : conv_tc_kernel<true, 4, 16>) : (two ? conv_tc_kernel<false, 4, 8> : conv_tc_kernel<false, 4, 16>); break;
+        case 6: kern = int8 ? (two ? conv_tc_kernel<true, 6, 8> : conv_tc_kernel<true, 6, 16>) : (two ? conv_tc_kernel<false, 6, 8> : conv_tc_kernel<false, 6, 16>); break;
+        case 8: kern = int8 ? (two ? conv_tc_kernel<true, 8, 8> : conv_tc_kernel<true, 8, 16>) : (two ? conv_tc_kernel<false, 8, 8> : conv_tc_kernel<false, 8, 16>); break;
+        case 10: kern = int8 ? (two ? conv_tc_kernel<true, 10, 8> : conv_tc_kernel<true, 10, 16>) : (two ? conv_tc_kernel<false, 10, 8> : conv_tc_kernel<false, 10, 16>); break;
+        case 12: kern = int8 ? (two ? conv_tc_kernel<true, 12, 8> : conv_tc_kernel<true, 12, 16>) : (two ? conv_tc_kernel<false, 12, 8> : conv_tc_kernel<false, 12, 16>); break;
+        case 14: kern = int8 ? (two ? conv_tc_kernel<true, 14, 8> : conv_tc_kernel<true, 14, 16>) : (two ? conv_tc_kernel<false, 14, 8> : conv_tc_kernel<false, 14, 16>); break;
+        default: break;
+        }
+    }
+#endif
     EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kThreads, smem, st>>>(p);
+    kern<<<grid, (kFirstEpiWarp + (two ? 8 : 16)) * 32, smem, st>>>(p);
     return after_launch("conv_tc_kernel");
 }
 
