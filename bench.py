@@ -97,9 +97,10 @@ def resnet_layers(batch):
     L = {}
     widths = (64, 128, 256, 512)
     h = IMG // 2
-    L["ingest data"] = dict(kind="layout", flops=0, bytes=batch * 3 * IMG * IMG * 4 + batch * IMG * IMG * 16 * 2)
+    pitch = (IMG + 4 + 8 + 7) // 8 * 8      # NHWC4 fp16 rows, zero-padded along W for the folded-K stem
+    L["ingest data"] = dict(kind="layout", flops=0, bytes=batch * 3 * IMG * IMG * 4 + batch * IMG * pitch * 4 * 2)
     L["stem"] = dict(kind="conv_f16", flops=2 * batch * h * h * 64 * 3 * 49,
-                     bytes=batch * IMG * IMG * 16 * 2 + batch * h * h * 64 * 2 + 64 * 49 * 16 * 2)
+                     bytes=batch * IMG * pitch * 4 * 2 + batch * h * h * 64 * 2 + 64 * 7 * 8 * 4 * 2)
     L["pool1"] = dict(kind="pool", flops=0, bytes=batch * h * h * 64 * 2 + batch * (h // 2) ** 2 * 64 * 3)
     h //= 2
     cin = 64

@@ -103,6 +103,18 @@ __device__ __forceinline__ uint32_t quant_pack4(float a, float b, float c, float
     return r;
 }
 
+// 256-bit global accesses (sm_100): one instruction per 32-byte pixel segment instead of two.
+__device__ __forceinline__ void st_global_256(void* p, const uint32_t (&o)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                 "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                 : "memory");
+}
+__device__ __forceinline__ void ld_global_nc_256(const void* p, uint32_t (&o)[8]) {
+    asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7])
+                 : "l"(p));
+}
+
 // 16 consecutive channels starting at element offset `off` (16-byte aligned for every dtype).
 __device__ __forceinline__ void epi_store_vec16(void* y, int dtype, int64_t off, const float (&v)[16],
                                                 float qscale, const uint32_t (&raw)[16]) {
@@ -114,13 +126,11 @@ __device__ __forceinline__ void epi_store_vec16(void* y, int dtype, int64_t off,
         o.w = quant_pack4(v[12], v[13], v[14], v[15], qscale);
         *reinterpret_cast<uint4*>(static_cast<int8_t*>(y) + off) = o;
     } else if (dtype == EXB_F16) {
-        uint4 o[2];
+        uint32_t o[8];
         __half2* h = reinterpret_cast<__half2*>(o);
 #pragma unroll
         for (int i = 0; i < 8; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(y) + off);
-        dst[0] = o[0];
-        dst[1] = o[1];
+        st_global_256(static_cast<__half*>(y) + off, o);   // 32 bytes, 32-byte aligned
     } else if (dtype == EXB_F32) {
         float4* dst = reinterpret_cast<float4*>(static_cast<float*>(y) + off);
 #pragma unroll

@@ -321,15 +321,30 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const int ow = tc.ow0 + tw, oh = tc.oh0 + th, n = tc.n0 + tn;
             const bool valid = row_in_box && ow < p.OW && oh < p.OH && n < p.N;
             const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
+            // This warp's chunks of 16 channels.  The residual of a chunk is requested one chunk
+            // ahead (the first one before the accumulator is even ready), because with so few
+            // epilogue warps an exposed global-memory latency per chunk is what the epilogue costs.
+            const int per = (n_chunks + nsub - 1) / nsub;
+            const int c_begin = sub * per, c_end = min(n_chunks, (sub + 1) * per);
+            const bool do_res = p.has_res && vec_ok && valid && !(kDbg & 16);
+            const __half* res_row = p.e.residual + pix * p.e.cout_stride + tc.ntile * p.BN;
+            uint32_t rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (do_res && c_begin < c_end && tc.ntile * p.BN + c_begin * 16 < p.e.cout_stride)
+                ld_global_nc_256(res_row + c_begin * 16, rn);
             if (!ptx::mbar_wait_bounded_warp(&tfull_bar[grp], acc_phase, &abort_flag, kMaxSpins)) {
                 ok = false;
                 break;
             }
             ptx::tc_fence_after_sync();
-            for (int chunk = sub; chunk < n_chunks; chunk += nsub) {
+            for (int chunk = c_begin; chunk < c_end; ++chunk) {
                 uint32_t raw[16];
                 if (kDbg & 8) continue;
                 ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
+                uint32_t rc[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) rc[i] = rn[i];
+                if (do_res && chunk + 1 < c_end && tc.ntile * p.BN + (chunk + 1) * 16 < p.e.cout_stride)
+                    ld_global_nc_256(res_row + (chunk + 1) * 16, rn);
                 ptx::tmem_ld_wait();
                 const int cl = tc.ntile * p.BN + chunk * 16;   // first channel of the chunk
                 if (!valid || cl >= p.e.cout_stride || (kDbg & 1)) continue;
@@ -348,11 +363,8 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     }
                 }
                 if (vec_ok) {
-                    if (p.has_res) {
-                        const uint4* rp = reinterpret_cast<const uint4*>(p.e.residual + off);
-                        const uint4 r0 = __ldg(rp), r1 = __ldg(rp + 1);
-                        const uint4 rr[2] = {r0, r1};
-                        const __half2* h = reinterpret_cast<const __half2*>(rr);
+                    if (do_res) {
+                        const __half2* h = reinterpret_cast<const __half2*>(rc);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float2 f = __half22float2(h[i]);
@@ -361,6 +373,13 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         }
                     }
                     act_vec16(v, p.e.act);
+                    if (kDbg & 32) {
+                        float acc_ = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) acc_ += v[i];
+                        if (acc_ == 123.456f) static_cast<float*>(p.e.y)[0] = acc_;   // keep the math alive
+                        continue;
+                    }
                     epi_store_vec16(p.e.y, p.e.out_dtype, off, v, p.e.out_scale, raw);
                     if (p.e.out2_dtype >= 0) epi_store_vec16(p.e.y2, p.e.out2_dtype, off, v, p.e.out2_scale, raw);
                 } else {
@@ -488,6 +507,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
     const int ctas_per_sm = two ? 2 : 1;
     const int k_iters = fold.on ? g.kh : g.kh * g.kw * p.cblks;
+    if ((int64_t)g.N * g.OH * g.OW >= (int64_t)1 << 31) return fail(EXB_ERR_UNSUPPORTED, "more than 2^31 output pixels");
     if ((int64_t)g.kh * w->kw_pack * w->cin_pad >= (1 << 28)) return fail(EXB_ERR_UNSUPPORTED, "reduction dimension too large");
     const int epi_bytes = 2 * p.n_tiles * p.BN * (int)sizeof(float) + k_iters * (int)sizeof(int4);
     // static barriers + alignment slack + tables; two resident CTAs share the SM's 228 KB
@@ -596,6 +616,9 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         case 8: kern = int8 ? (two ? conv_tc_kernel<true, 8, 8> : conv_tc_kernel<true, 8, 16>) : (two ? conv_tc_kernel<false, 8, 8> : conv_tc_kernel<false, 8, 16>); break;
         case 10: kern = int8 ? (two ? conv_tc_kernel<true, 10, 8> : conv_tc_kernel<true, 10, 16>) : (two ? conv_tc_kernel<false, 10, 8> : conv_tc_kernel<false, 10, 16>); break;
         case 12: kern = int8 ? (two ? conv_tc_kernel<true, 12, 8> : conv_tc_kernel<true, 12, 16>) : (two ? conv_tc_kernel<false, 12, 8> : conv_tc_kernel<false, 12, 16>); break;
+        case 16: kern = int8 ? (two ? conv_tc_kernel<true, 16, 8> : conv_tc_kernel<true, 16, 16>) : (two ? conv_tc_kernel<false, 16, 8> : conv_tc_kernel<false, 16, 16>); break;
+        case 32: kern = int8 ? (two ? conv_tc_kernel<true, 32, 8> : conv_tc_kernel<true, 32, 16>) : (two ? conv_tc_kernel<false, 32, 8> : conv_tc_kernel<false, 32, 16>); break;
+        case 48: kern = int8 ? (two ? conv_tc_kernel<true, 48, 8> : conv_tc_kernel<true, 48, 16>) : (two ? conv_tc_kernel<false, 48, 8> : conv_tc_kernel<false, 48, 16>); break;
         case 14: kern = int8 ? (two ? conv_tc_kernel<true, 14, 8> : conv_tc_kernel<true, 14, 16>) : (two ? conv_tc_kernel<false, 14, 8> : conv_tc_kernel<false, 14, 16>); break;
         default: break;
         }

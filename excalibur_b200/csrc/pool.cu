@@ -6,6 +6,8 @@
 
 #include <float.h>
 
+#include <type_traits>
+
 namespace exb {
 namespace {
 
@@ -167,6 +169,94 @@ __global__ void __launch_bounds__(256) global_pool_kernel(const T* __restrict__ 
     }
 }
 
+// 3x3 / stride 2 max pooling of fp16 NHWC data (the ResNet stem pool): a thread produces a 2x2
+// block of outputs for 16 channels.  The 5x5 input patch is read once with 32-byte loads (25
+// loads for 4 outputs instead of 36), maxima are taken on packed half2 values, and the optional
+// int8 copy is quantised from the same registers.
+__device__ __forceinline__ void ld256(const void* p, uint32_t (&o)[8]) {
+    asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void st256(void* p, const uint32_t (&o)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                 "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t hmax2_u32(uint32_t a, uint32_t b) {
+    __half2 r = __hmax2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+template <bool kOut2>
+__global__ void __launch_bounds__(128) maxpool3x3s2_f16_kernel(const __half* __restrict__ x, __half* __restrict__ y,
+                                                               int8_t* __restrict__ y2, PoolParams p) {
+    const int cv16 = p.cs / 16;
+    const int bw = (p.PW + 1) / 2, bh = (p.PH + 1) / 2;
+    const int64_t total = (int64_t)p.N * bh * bw * cv16;
+    const uint32_t NEG = 0xFC00FC00u;   // (-inf, -inf): max pooling ignores the padding
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int cv = (int)(idx % cv16);
+        int64_t t = idx / cv16;
+        const int bx = (int)(t % bw); t /= bw;
+        const int by = (int)(t % bh);
+        const int n = (int)(t / bh);
+        const int ph0 = by * 2, pw0 = bx * 2;
+        const int h0 = ph0 * 2 - p.pt, w0 = pw0 * 2 - p.pl;
+        uint32_t acc[2][2][8];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[a][b][k] = NEG;
+#pragma unroll
+        for (int r = 0; r < 5; ++r) {
+            const int h = h0 + r;
+            if (h < 0 || h >= p.H) continue;
+            uint32_t hm0[8], hm1[8];   // horizontal maxima of this input row for the two output columns
+#pragma unroll
+            for (int k = 0; k < 8; ++k) hm0[k] = hm1[k] = NEG;
+#pragma unroll
+            for (int c = 0; c < 5; ++c) {
+                const int w = w0 + c;
+                if (w < 0 || w >= p.W) continue;
+                uint32_t v[8];
+                ld256(x + (((int64_t)n * p.H + h) * p.W + w) * p.cs + cv * 16, v);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (c <= 2) hm0[k] = hmax2_u32(hm0[k], v[k]);
+                    if (c >= 2) hm1[k] = hmax2_u32(hm1[k], v[k]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (r <= 2) { acc[0][0][k] = hmax2_u32(acc[0][0][k], hm0[k]); acc[0][1][k] = hmax2_u32(acc[0][1][k], hm1[k]); }
+                if (r >= 2) { acc[1][0][k] = hmax2_u32(acc[1][0][k], hm0[k]); acc[1][1][k] = hmax2_u32(acc[1][1][k], hm1[k]); }
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const int ph = ph0 + a, pw = pw0 + b;
+                if (ph >= p.PH || pw >= p.PW) continue;
+                const int64_t o = (((int64_t)n * p.PH + ph) * p.PW + pw) * p.cs + cv * 16;
+                st256(y + o, acc[a][b]);
+                if (kOut2) {
+                    alignas(16) int8_t q[16];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&acc[a][b][k]));
+                        q[2 * k] = (int8_t)quant_rne(f.x * p.out2_scale);
+                        q[2 * k + 1] = (int8_t)quant_rne(f.y * p.out2_scale);
+                    }
+                    *reinterpret_cast<uint4*>(y2 + o) = *reinterpret_cast<const uint4*>(q);
+                }
+            }
+    }
+}
+
 int pool_dim(int in, int pa, int pb, int k, int s, int pad_mode) {
     // static_cast<int>(ceil|floor(static_cast<float>(in + pa + pb - k) / s)) + 1
     float q = (float)(in + pa + pb - k) / (float)s;
@@ -186,6 +276,14 @@ int launch(exb_ctx* ctx, const exb_pool_desc* d, const PoolParams& p, const void
         if (out2) global_pool_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T*>(x), static_cast<T*>(y), static_cast<int8_t*>(y2), p);
         else global_pool_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T*>(x), static_cast<T*>(y), nullptr, p);
         return after_launch("global_pool_kernel");
+    }
+    if (std::is_same<T, __half>::value && p.type == 0 && p.kh == 3 && p.kw == 3 && p.sh == 2 && p.sw == 2 &&
+        p.cs % 16 == 0 && p.pt <= 1 && p.pl <= 1) {
+        const int64_t work = (int64_t)p.N * ((p.PH + 1) / 2) * ((p.PW + 1) / 2) * (p.cs / 16);
+        const int g2 = stream_grid(ctx, work, 128, 16);
+        if (out2) maxpool3x3s2_f16_kernel<true><<<g2, 128, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), static_cast<int8_t*>(y2), p);
+        else maxpool3x3s2_f16_kernel<false><<<g2, 128, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), nullptr, p);
+        return after_launch("maxpool3x3s2_f16_kernel");
     }
     const int64_t total = (int64_t)p.N * p.PH * p.PW * (p.cs / V);
     const int grid = stream_grid(ctx, total, 256);
