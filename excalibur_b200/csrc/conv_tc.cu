@@ -60,6 +60,16 @@ struct ConvTcParams {
     int fold;         // folded K layout (see FoldPlan): one K block per kernel row
     int b_resident;   // the whole weight slice stays in shared memory for the life of the CTA
     int b_region;     // bytes of the B region in shared memory (ring or resident copy)
+    // "Patch" mode for stride-2 stems on NHWC4 rows (8-byte pixels): the A operand of kernel row r
+    // is the raw input patch itself, read through an un-swizzled descriptor whose rows are 16
+    // bytes apart (= one output column) and whose K chunks are 16 bytes apart as well, so the
+    // overlapping 8-pixel windows of neighbouring output columns are never duplicated in shared
+    // memory: one TMA load of (2*TH + kh - 2) x 24 pixels per tile instead of kh boxes of
+    // 128 x 64 bytes.
+    int patch;
+    int patch_rows;    // input rows per tile
+    int patch_pitch;   // bytes per patch row in shared memory
+    const void* w_global;   // packed weights (patch mode copies them into core-matrix layout)
 };
 
 struct TileCoord {
@@ -155,6 +165,18 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         }
         k_tab[it] = make_int4(cb * p.kb_elems, dw, dh, (tap * p.cin_pad + cb * p.kb_elems) | (view << 28));
     }
+    if (p.patch) {
+        // Weights into the un-swizzled canonical K-major layout: for kernel row r, 16-byte K
+        // chunk j, output channel n: r*(BN*64) + j*(BN*16) + (n/8)*128 + (n%8)*16.
+        const uint4* src = static_cast<const uint4*>(p.w_global);
+        const int total = p.kh * p.BN * 4;
+        for (int i = threadIdx.x; i < total; i += kThreads) {
+            const int j = i & 3, n = (i >> 2) % p.BN, r = (i >> 2) / p.BN;
+            const uint4 v = n < p.cout_pad ? src[((size_t)n * p.kh + r) * 4 + j] : make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(smem_b + r * (p.BN * 64) + j * (p.BN * 16) + (n >> 3) * 128 + (n & 7) * 16) = v;
+        }
+        ptx::fence_proxy_async();   // generic-proxy writes, read by the tensor core through the async proxy
+    }
     for (int c = threadIdx.x; c < p.n_tiles * p.BN; c += kThreads) {
         const bool in = c < p.cout_pad;
         s_scale[c] = in ? p.e.scale[c] : 0.f;
@@ -190,7 +212,35 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 ptx::tma_load_2d_u32(ptx::smem_u32(smem_b) + (uint32_t)(it * p.b_bytes), mapB, rb,
                                      k_tab[it].w & 0x0fffffff, 0);
         }
-        if (lane < G) {
+        if (p.patch) {
+            if (lane == 0) {
+                const uint32_t bytes = (uint32_t)(p.patch_rows * p.patch_pitch);
+                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                    const TileCoord tc = decode_tile(p, t);
+                    if (!ptx::mbar_wait_bounded_u32(empty0 + stage * 8, phase ^ 1u, &abort_flag, kMaxSpins)) {
+                        ok = 0;
+                        break;
+                    }
+                    const uint32_t fb = full0 + stage * 8;
+                    ptx::mbar_arrive_expect_tx_u32(fb, bytes);
+                    // x: first element of the window of output column ow0 (8 px wide, 4 left of
+                    // 2*ow0 in image coordinates = 2*ow0 in padded coordinates), y: first input row
+                    asm volatile(
+                        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                        " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(ptx::smem_u32(smem_a) + (uint32_t)(stage * p.a_bytes)),
+                        "l"(mapA0), "r"(fb), "r"(tc.ow0 * 8), "r"(tc.oh0 * 2 - p.pad_t), "r"(tc.n0)
+                        : "memory");
+                    if (++stage == p.stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) {
+                    atomicExch(p.error, 1);
+                    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+                }
+            }
+        } else if (lane < G) {
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
                 const int ncoord = tc.ntile * p.BN;
@@ -257,6 +307,40 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
                 uint32_t accumulate = 0;
+                if (p.patch) {
+                    if (!ptx::mbar_wait_bounded_u32(full0 + stage * 8, phase, &abort_flag, kMaxSpins)) {
+                        ok = false;
+                        break;
+                    }
+                    // un-swizzled descriptors: A rows 16 B apart (LBO 16 B, SBO = two patch rows),
+                    // B core matrices 128 B, K chunks BN*16 B apart
+                    const uint32_t a0 = ((ptx::smem_u32(smem_a) + (uint32_t)(stage * p.a_bytes)) >> 4) | (1u << 16);
+                    const uint32_t a_hi = ((uint32_t)(2 * p.patch_pitch) >> 4) | (1u << 14);
+                    const uint32_t b0 = (ptx::smem_u32(smem_b) >> 4) | ((uint32_t)(p.BN * 16 >> 4) << 16);
+                    const uint32_t b_hi = (128u >> 4) | (1u << 14);
+                    for (int r = 0; r < p.kh; ++r) {
+                        const uint32_t ar = a0 + (uint32_t)(r * p.patch_pitch >> 4);
+                        const uint32_t br = b0 + (uint32_t)(r * p.BN * 64 >> 4);
+#pragma unroll
+                        for (int ks = 0; ks < 2; ++ks) {
+                            asm volatile(
+                                "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+                                "mov.b64 da, {%1, %2};\n\t"
+                                "mov.b64 db, {%3, %4};\n\t"
+                                "setp.ne.b32 p, %6, 0;\n\t"
+                                "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+                                "r"(ar + ks * 2), "r"(a_hi), "r"(br + (uint32_t)(ks * 2 * (p.BN * 16 >> 4))), "r"(b_hi),
+                                "r"(idesc), "r"(accumulate)
+                                : "memory");
+                            accumulate = 1;
+                        }
+                    }
+                    ptx::tc_commit_u32(empty0 + stage * 8);
+                    if (++stage == p.stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                } else
                 for (int it0 = 0; it0 < k_iters; it0 += G) {
                     const int nb = min(G, k_iters - it0);
                     if (!ptx::mbar_wait_bounded_u32(full0 + stage * 8, phase, &abort_flag, kMaxSpins)) {
@@ -504,6 +588,20 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     }
     p.a_bytes = kTileM * p.kb_bytes;
     p.b_bytes = p.BN * p.kb_bytes;
+    // Patch mode (see ConvTcParams): stride-2 fp16 stems on 8-byte pixels with an 8-pixel window.
+    const bool patch = fold.on && !int8 && g.cin_stride * es == 8 && g.sw == 2 && fold.F == 8 && p.n_tiles == 1 &&
+                       g.kh <= 16;
+    p.patch = patch ? 1 : 0;
+    if (patch) {
+        p.TW = 8; p.TH = 16; p.TN = 1;   // 16 groups of 8 output columns, one output row each
+        p.tiles_w = (g.OW + 7) / 8;
+        p.tiles_h = (g.OH + 15) / 16;
+        p.tiles_nb = g.N;
+        p.patch_rows = 2 * p.TH + g.kh - 2;
+        p.patch_pitch = (2 * p.TW + 8) * 8;   // 2*TW + 6 pixels needed, rounded to 24
+        p.a_bytes = round_up(p.patch_rows * p.patch_pitch, 128);
+        p.w_global = w->d_w;
+    }
     p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
     const int ctas_per_sm = two ? 2 : 1;
     const int k_iters = fold.on ? g.kh : g.kh * g.kw * p.cblks;
@@ -535,9 +633,15 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     while (G > 1 && budget / (G * blk_bytes) < 3) --G;
     p.kgroup = G;
     int stages = budget / (G * blk_bytes);
+    if (patch) {   // ring of whole patches, weights in their own region
+        p.kgroup = G = 1;
+        if (p.b_resident) budget += b_all;
+        p.b_resident = 0;
+        stages = (budget - g.kh * p.BN * 64) / p.a_bytes;
+    }
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return fail(EXB_ERR_UNSUPPORTED, "conv tile does not fit shared memory (BN=%d)", p.BN);
-    p.b_region = p.b_resident ? b_all : stages * G * p.b_bytes;
+    p.b_region = patch ? g.kh * p.BN * 64 : (p.b_resident ? b_all : stages * G * p.b_bytes);
     p.stages = stages;
     p.acc_bufs = two ? 2 : (p.BN <= 128 ? 4 : 2);
     int cols = 32;
@@ -557,7 +661,19 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     const size_t px_bytes = (size_t)g.cin_stride * es;
     const size_t row_pitch = (size_t)g.w_pitch * px_bytes;
     const int nviews = g.sh == 1 ? 1 : 4;
-    for (int v = 0; v < nviews; ++v) {
+    if (patch) {
+        // One map: whole padded rows as the innermost dimension, box = 24 pixels x patch_rows.
+        cuuint64_t dims[3] = {(cuuint64_t)g.w_pitch * g.cin_stride, (cuuint64_t)g.H, (cuuint64_t)g.N};
+        cuuint64_t strides[2] = {(cuuint64_t)row_pitch, (cuuint64_t)g.H * row_pitch};
+        cuuint32_t box[3] = {(cuuint32_t)(p.patch_pitch / es), (cuuint32_t)p.patch_rows, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        void* base = const_cast<char*>(static_cast<const char*>(x)) + (size_t)(g.w_pad - fold.pl_eff) * px_bytes;
+        CUresult r = encode(&p.tmA[0], dt, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(patch) failed with %d", (int)r);
+    }
+    for (int v = 0; v < (patch ? 0 : nviews); ++v) {
         const int ph = v >> 1, pw = v & 1;
         const int st_ = g.sh;
         if (fold.on && pw) continue;   // the folded layout walks W inside the K row
