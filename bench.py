@@ -309,7 +309,7 @@ def run_gpu_arm(args, rank, world, local_rank):
         return sharding.max_over_ranks(v, dist, "cuda")
 
     g8, scales = build_int8_net_gpu(local_rank)
-    pipe = host.Pipeline(g8.phai_text(), g8.racy_bytes(), local_rank, fusion=True, cuda_graph=True)
+    pipe = host.Pipeline(g8.phai_text(), g8.racy_bytes(), local_rank, fusion=True, cuda_graph=not args.no_graph)
     x = torch.empty((BATCH, 3, IMG, IMG), dtype=torch.float32).pin_memory()
     gen = torch.Generator().manual_seed(SEED * 1000 + 100 + rank)
     x.uniform_(0, 1, generator=gen)
@@ -418,7 +418,8 @@ def run_gpu_arm(args, rank, world, local_rank):
                    "batch_per_gpu": BATCH, "global_batch": BATCH * world,
                    "parallelism": "batch-sharded replicas, one process per GPU, no collective",
                    "l2": "no flush: every step streams a 154 MB input and >1 GB of activations, larger than the 126 MB L2",
-                   "timing": "CUDA events on the plan's stream around K CUDA-graph replays, max over ranks"},
+                   "timing": "CUDA events on the plan's stream around K %s, max over ranks"
+                             % ("eager launches of the plan (--no-graph)" if args.no_graph else "CUDA-graph replays")},
         "clocks": clocks,
         "e2e": {"value": images / e2e_s, "unit": "images/s", "h2d_bytes_per_step": BATCH * 3 * IMG * IMG * 4,
                 "d2h_bytes_per_step": BATCH * 1000 * 4, "ms_per_step": e2e_s * 1000.0 / args.steps},
@@ -446,6 +447,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch the plan's kernels one by one instead of replaying a CUDA graph (profilers "
+                         "cannot attach to launches made during stream capture); not a bench configuration")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
