@@ -22,7 +22,7 @@ EXPORTED_SYMBOLS = [
     "exb_conv2d_fwd", "exb_conv2d_uses_tensor_cores", "exb_dw_weights_pack", "exb_dw_weights_destroy",
     "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_pool2d_nchw_f32_static", "exb_eltwise_fwd", "exb_binaryop_fwd",
     "exb_binaryop_scalar_fwd", "exb_relu_fwd", "exb_activation_fwd", "exb_quantize_fwd",
-    "exb_dequantize_fwd",
+    "exb_dequantize_fwd", "exb_concat_fwd", "exb_interp_nearest_fwd", "exb_channel_affine_fwd",
 ]
 
 
@@ -92,6 +92,9 @@ def lib():
         L.exb_activation_fwd.argtypes = [vp, i32, vp, vp, i64, i32, vp]
         L.exb_quantize_fwd.argtypes = [vp, vp, i32, vp, i64, f32, i32, vp]
         L.exb_dequantize_fwd.argtypes = [vp, vp, vp, i32, i64, f32, vp]
+        L.exb_concat_fwd.argtypes = [vp, i32, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), vp, i64, i64, i32, vp]
+        L.exb_interp_nearest_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+        L.exb_channel_affine_fwd.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i64, i32, i32, i32, vp]
         _LIB = L
     return _LIB
 
@@ -338,6 +341,73 @@ def activation(ctx, x, act, y=None):
     if y is None:
         y = t.empty_like(x)
     check(lib().exb_activation_fwd(ctx.handle, act, ptr(x), ptr(y), x.numel(), exb_dtype_of(x), cur_stream()))
+    return y
+
+
+def concat_channels(ctx, xs, channels=None, y_stride=None, y=None):
+    """Channel concat of NHWC tensors [N][H][W][cs_i] holding channels[i] valid channels each
+    (default: all of them); the result has y_stride physical channels (default: the sum)."""
+    t = _torch()
+    n = len(xs)
+    widths = [int(c) for c in (channels if channels is not None else [x.shape[-1] for x in xs])]
+    total = sum(widths)
+    ys = int(y_stride) if y_stride else total
+    rows = xs[0].numel() // xs[0].shape[-1]
+    if y is None:
+        y = t.zeros(tuple(xs[0].shape[:-1]) + (ys,), device=xs[0].device, dtype=xs[0].dtype)
+    px = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
+    pw = (C.c_int64 * n)(*widths)
+    ps = (C.c_int64 * n)(*[int(x.shape[-1]) for x in xs])
+    check(lib().exb_concat_fwd(ctx.handle, n, px, pw, ps, ptr(y), ys, rows, exb_dtype_of(xs[0]), cur_stream()))
+    return y
+
+
+def concat_nchw(ctx, xs, y=None):
+    """Channel concat of dense NCHW tensors."""
+    t = _torch()
+    n = len(xs)
+    N = xs[0].shape[0]
+    widths = [x.numel() // max(N, 1) for x in xs]
+    if y is None:
+        y = t.empty((N, sum(x.shape[1] for x in xs)) + tuple(xs[0].shape[2:]), device=xs[0].device, dtype=xs[0].dtype)
+    px = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
+    pw = (C.c_int64 * n)(*widths)
+    check(lib().exb_concat_fwd(ctx.handle, n, px, pw, pw, ptr(y), sum(widths), N, exb_dtype_of(xs[0]), cur_stream()))
+    return y
+
+
+def interp_nearest(ctx, x, OH, OW, channels=None, channel_last=True, y=None):
+    """Nearest resize of NHWC [N][H][W][cs] (channel_last) or NCHW fp32 [N][C][H][W]."""
+    t = _torch()
+    if channel_last:
+        N, H, W, cs = x.shape
+        Cc = channels or cs
+        if y is None:
+            y = t.empty((N, OH, OW, cs), device=x.device, dtype=x.dtype)
+    else:
+        N, Cc, H, W = x.shape
+        cs = 0
+        if y is None:
+            y = t.empty((N, Cc, OH, OW), device=x.device, dtype=x.dtype)
+    check(lib().exb_interp_nearest_fwd(ctx.handle, ptr(x), ptr(y), N, H, W, Cc, cs, OH, OW, exb_dtype_of(x),
+                                       1 if channel_last else 0, cur_stream()))
+    return y
+
+
+def channel_affine(ctx, x, mul, add, channels=None, channel_last=True, act=ACT_NONE, y=None):
+    """y = act(x * mul[c] + add[c]); mul / add: fp32 device tensors with one entry per channel."""
+    t = _torch()
+    if y is None:
+        y = t.empty_like(x)
+    if channel_last:
+        cs = x.shape[-1]
+        Cc = channels or cs
+        outer, inner = x.numel() // cs, 1
+    else:
+        Cc, cs = x.shape[1], 0
+        outer, inner = x.shape[0], x.numel() // max(x.shape[0] * x.shape[1], 1)
+    check(lib().exb_channel_affine_fwd(ctx.handle, ptr(x), ptr(y), ptr(mul), ptr(add), outer, Cc, cs, inner,
+                                       exb_dtype_of(x), 1 if channel_last else 0, act, cur_stream()))
     return y
 
 

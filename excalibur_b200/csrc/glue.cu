@@ -1,0 +1,205 @@
+// Graph-glue kernels around the convolution trunk: channel concatenation, nearest-neighbour
+// resize and the per-channel affine map (BatchNorm at inference, input normalisation).  All three
+// are single-pass, bandwidth-bound copies; 16-byte vectors where strides allow, scalars otherwise.
+#include "common.cuh"
+
+namespace exb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxConcatInputs = 8;
+
+struct ConcatArgs {
+    const void* x[kMaxConcatInputs];
+    int64_t width[kMaxConcatInputs];     // valid elements per row of input i
+    int64_t stride[kMaxConcatInputs];    // physical elements per row of input i
+    int64_t offset[kMaxConcatInputs + 1];  // first output column of input i; [n_in] = total width
+    int n_in;
+};
+
+// y[r][offset_i + k] = x_i[r][k].  Unit = 1 << unit_shift bytes moved per thread step (16 when every
+// width, stride and offset is a multiple of 16 bytes, else one element).
+template <typename U>
+__global__ void __launch_bounds__(kThreads) concat_rows_kernel(ConcatArgs a, U* y, int64_t y_stride, int64_t rows) {
+    const int64_t total = a.offset[a.n_in];
+    const int64_t work = rows * total;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < work; i += step) {
+        const int64_t r = i / total, c = i - r * total;
+        int k = 0;
+#pragma unroll
+        for (int j = 1; j < kMaxConcatInputs; ++j)
+            if (j < a.n_in && c >= a.offset[j]) k = j;
+        y[r * y_stride + c] = static_cast<const U*>(a.x[k])[r * a.stride[k] + (c - a.offset[k])];
+    }
+}
+
+// Nearest resize, channel-last: one thread per 16-byte (or one-element) slice of an output pixel.
+template <typename U>
+__global__ void __launch_bounds__(kThreads) interp_nearest_nhwc_kernel(const U* x, U* y, int N, int H, int W, int cs,
+                                                                       int OH, int OW, float hs, float ws) {
+    const int64_t work = (int64_t)N * OH * OW * cs;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < work; i += step) {
+        const int c = (int)(i % cs);
+        int64_t p = i / cs;
+        const int ox = (int)(p % OW);
+        p /= OW;
+        const int oy = (int)(p % OH);
+        const int n = (int)(p / OH);
+        const int iy = min((int)(oy * hs), H - 1), ix = min((int)(ox * ws), W - 1);
+        y[i] = x[(((int64_t)n * H + iy) * W + ix) * cs + c];
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) interp_nearest_nchw_kernel(const float* x, float* y, int planes, int H, int W,
+                                                                       int OH, int OW, float hs, float ws) {
+    const int64_t work = (int64_t)planes * OH * OW;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < work; i += step) {
+        const int ox = (int)(i % OW);
+        int64_t p = i / OW;
+        const int oy = (int)(p % OH);
+        const int64_t pl = p / OH;
+        const int iy = min((int)(oy * hs), H - 1), ix = min((int)(ox * ws), W - 1);
+        y[i] = x[(pl * H + iy) * W + ix];
+    }
+}
+
+__device__ __forceinline__ float ld1(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ float ld1(const float* p) { return *p; }
+__device__ __forceinline__ void st1(__half* p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void st1(float* p, float v) { *p = v; }
+
+// y = act(x * mul[c] + add[c]).  channel-last: c = i % cs (padding channels c >= C are written 0);
+// planar: c = (i / inner) % C.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) channel_affine_kernel(const T* x, T* y, const float* mul, const float* add,
+                                                                  int64_t count, int C, int cs, int64_t inner,
+                                                                  int channel_last, int act) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += step) {
+        const int c = channel_last ? (int)(i % cs) : (int)((i / inner) % C);
+        float v = 0.f;
+        if (c < C) v = apply_act(fmaf(ld1(x + i), mul[c], add[c]), act);
+        st1(y + i, v);
+    }
+}
+
+}  // namespace
+}  // namespace exb
+
+using namespace exb;
+
+extern "C" int exb_concat_fwd(exb_ctx* ctx, int n_in, const void* const* xs, const int64_t* widths,
+                              const int64_t* x_strides, void* y, int64_t y_stride, int64_t rows, int dtype,
+                              void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(n_in >= 1 && xs && widths && x_strides, "exb_concat_fwd: null argument or no inputs");
+    if (n_in > kMaxConcatInputs)
+        return fail(EXB_ERR_UNSUPPORTED, "concat supports at most %d inputs, got %d", kMaxConcatInputs, n_in);
+    const int64_t es = (int64_t)dtype_size(dtype);
+    if (es == 0) return fail(EXB_ERR_UNSUPPORTED, "exb_concat_fwd: dtype %d", dtype);
+    EXB_REQUIRE(rows >= 0, "exb_concat_fwd: negative row count");
+    ConcatArgs a;
+    a.n_in = n_in;
+    int64_t off = 0;
+    bool vec = aligned16(y) && (y_stride * es) % 16 == 0;
+    for (int i = 0; i < n_in; ++i) {
+        EXB_REQUIRE(widths[i] >= 0 && x_strides[i] >= widths[i], "exb_concat_fwd: input %d has stride < width", i);
+        EXB_REQUIRE(xs[i] != nullptr || widths[i] == 0 || rows == 0, "exb_concat_fwd: input %d is null", i);
+        a.x[i] = xs[i];
+        a.width[i] = widths[i];
+        a.stride[i] = x_strides[i];
+        a.offset[i] = off;
+        vec = vec && aligned16(xs[i]) && (widths[i] * es) % 16 == 0 && (x_strides[i] * es) % 16 == 0 && (off * es) % 16 == 0;
+        off += widths[i];
+    }
+    a.offset[n_in] = off;
+    for (int i = n_in + 1; i <= kMaxConcatInputs; ++i) a.offset[i] = off;
+    EXB_REQUIRE(y_stride >= off, "exb_concat_fwd: output stride %lld smaller than the summed width %lld",
+                (long long)y_stride, (long long)off);
+    if (rows == 0 || off == 0) return EXB_OK;
+    EXB_REQUIRE(y != nullptr, "exb_concat_fwd: null output");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (vec) {
+        const int64_t per = 16 / es;
+        for (int i = 0; i < n_in; ++i) { a.width[i] /= per; a.stride[i] /= per; a.offset[i] /= per; }
+        for (int i = n_in; i <= kMaxConcatInputs; ++i) a.offset[i] = off / per;
+        int grid = stream_grid(ctx, rows * (off / per), kThreads);
+        concat_rows_kernel<uint4><<<grid, kThreads, 0, st>>>(a, static_cast<uint4*>(y), y_stride / per, rows);
+    } else {
+        int grid = stream_grid(ctx, rows * off, kThreads);
+        if (es == 1) concat_rows_kernel<uint8_t><<<grid, kThreads, 0, st>>>(a, static_cast<uint8_t*>(y), y_stride, rows);
+        else if (es == 2) concat_rows_kernel<uint16_t><<<grid, kThreads, 0, st>>>(a, static_cast<uint16_t*>(y), y_stride, rows);
+        else concat_rows_kernel<uint32_t><<<grid, kThreads, 0, st>>>(a, static_cast<uint32_t*>(y), y_stride, rows);
+    }
+    return after_launch("exb_concat_fwd");
+}
+
+extern "C" int exb_interp_nearest_fwd(exb_ctx* ctx, const void* x, void* y, int N, int H, int W, int C, int c_stride,
+                                      int OH, int OW, int dtype, int channel_last, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(N >= 0 && H > 0 && W > 0 && C > 0 && OH > 0 && OW > 0, "exb_interp_nearest_fwd: bad shape");
+    if (N == 0) return EXB_OK;
+    EXB_REQUIRE(x && y, "exb_interp_nearest_fwd: null buffer");
+    // source coordinate = (int)(o * (in / (float)out)), clamped: src/Excalibur/operation_interp.cpp:247-262
+    const float hs = H / (float)OH, ws = W / (float)OW;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!channel_last) {
+        if (dtype != EXB_F32) return fail(EXB_ERR_UNSUPPORTED, "planar nearest resize is implemented for EXB_F32 only");
+        const int64_t planes = (int64_t)N * C;
+        EXB_REQUIRE(planes < (1ll << 31), "exb_interp_nearest_fwd: too many planes");
+        int grid = stream_grid(ctx, planes * OH * OW, kThreads);
+        interp_nearest_nchw_kernel<<<grid, kThreads, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y),
+                                                              (int)planes, H, W, OH, OW, hs, ws);
+        return after_launch("exb_interp_nearest_fwd");
+    }
+    const int cs = c_stride ? c_stride : C;
+    EXB_REQUIRE(cs >= C, "exb_interp_nearest_fwd: channel stride smaller than channel count");
+    const int64_t es = (int64_t)dtype_size(dtype);
+    if (es == 0 || dtype == EXB_I32) return fail(EXB_ERR_UNSUPPORTED, "exb_interp_nearest_fwd: dtype %d", dtype);
+    if ((cs * es) % 16 == 0 && aligned16(x) && aligned16(y)) {
+        const int v = (int)(cs * es / 16);
+        int grid = stream_grid(ctx, (int64_t)N * OH * OW * v, kThreads);
+        interp_nearest_nhwc_kernel<uint4><<<grid, kThreads, 0, st>>>(static_cast<const uint4*>(x), static_cast<uint4*>(y),
+                                                                     N, H, W, v, OH, OW, hs, ws);
+    } else {
+        int grid = stream_grid(ctx, (int64_t)N * OH * OW * cs, kThreads);
+        if (es == 1)
+            interp_nearest_nhwc_kernel<uint8_t><<<grid, kThreads, 0, st>>>(static_cast<const uint8_t*>(x),
+                                                                           static_cast<uint8_t*>(y), N, H, W, cs, OH, OW, hs, ws);
+        else if (es == 2)
+            interp_nearest_nhwc_kernel<uint16_t><<<grid, kThreads, 0, st>>>(static_cast<const uint16_t*>(x),
+                                                                            static_cast<uint16_t*>(y), N, H, W, cs, OH, OW, hs, ws);
+        else
+            interp_nearest_nhwc_kernel<uint32_t><<<grid, kThreads, 0, st>>>(static_cast<const uint32_t*>(x),
+                                                                            static_cast<uint32_t*>(y), N, H, W, cs, OH, OW, hs, ws);
+    }
+    return after_launch("exb_interp_nearest_fwd");
+}
+
+extern "C" int exb_channel_affine_fwd(exb_ctx* ctx, const void* x, void* y, const float* mul, const float* add,
+                                      int64_t outer, int C, int c_stride, int64_t inner, int dtype, int channel_last,
+                                      int act, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(outer >= 0 && C > 0 && inner > 0, "exb_channel_affine_fwd: bad shape");
+    if (dtype != EXB_F16 && dtype != EXB_F32)
+        return fail(EXB_ERR_UNSUPPORTED, "exb_channel_affine_fwd supports EXB_F16 and EXB_F32, got dtype %d", dtype);
+    if (!act_supported(act)) return fail(EXB_ERR_UNSUPPORTED, "activation type %d is not implemented", act);
+    const int cs = channel_last ? (c_stride ? c_stride : C) : C;
+    EXB_REQUIRE(cs >= C, "exb_channel_affine_fwd: channel stride smaller than channel count");
+    // channel-last: outer = pixels, inner ignored; planar: outer = images, inner = H*W
+    const int64_t count = channel_last ? outer * cs : outer * C * inner;
+    if (count == 0) return EXB_OK;
+    EXB_REQUIRE(x && y && mul && add, "exb_channel_affine_fwd: null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = stream_grid(ctx, count, kThreads);
+    if (dtype == EXB_F16)
+        channel_affine_kernel<__half><<<grid, kThreads, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), mul,
+                                                                 add, count, C, cs, inner, channel_last, act);
+    else
+        channel_affine_kernel<float><<<grid, kThreads, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), mul,
+                                                                add, count, C, cs, inner, channel_last, act);
+    return after_launch("exb_channel_affine_fwd");
+}

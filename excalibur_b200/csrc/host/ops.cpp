@@ -713,12 +713,13 @@ exb_conv_desc operation_innerproduct<Dtype>::fc_desc(int N, int cin_stride) cons
 }
 template <typename Dtype>
 exb_conv_weights* operation_innerproduct<Dtype>::packed(exb_ctx* ctx, const exb_conv_desc& d) {
-    if (w_ && w_cin_stride_ == d.cin_stride) return w_;
+    if (w_ && w_cin_stride_ == d.cin_stride && w_cout_stride_ == d.cout_stride) return w_;
     if (w_) exb_conv_weights_destroy(w_);
     w_ = nullptr;
     const float* bias = bias_term_ ? this->weights_f32_[1]->cpu_data() : nullptr;
     exb_check(exb_conv_weights_pack_f16(ctx, &d, this->weights_f32_[0]->cpu_data(), bias, &w_), "exb_conv_weights_pack_f16");
     w_cin_stride_ = d.cin_stride;
+    w_cout_stride_ = d.cout_stride;
     return w_;
 }
 // bottoms[0]: {N, C, H, W} fp32 NCHW, flattened to N x (C*H*W) like the reference.
@@ -743,6 +744,150 @@ void operation_innerproduct<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list&
 }
 INSTANCE_CLASS(operation_innerproduct);
 REGISTE(operation_innerproduct);
+
+// ---------------------------------------------------------------------------------------------
+// graph glue: concat, nearest resize, batch norm
+// ---------------------------------------------------------------------------------------------
+template <typename Dtype>
+operation_concat<Dtype>::operation_concat(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        if (kv.first == 0) axis_ = (int)std::atof(kv.second.c_str());
+        else if (kv.first != -23330) LOG(FATAL) << "Un-supported Concat Attribution " << kv.first;
+    }
+}
+template <typename Dtype>
+void operation_concat<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_GE(bottoms.size(), 2u);
+    CHECK_EQ(tops.size(), 1u);
+    if (!is_channel_concat()) NOT_IMPLEMENTED << " (Concat is implemented along the channel axis, key 0=-1)";
+    CHECK(bottoms[0]->order() == memory::NCHW) << "Concat expects NCHW tensors";
+    const int N = bottoms[0]->num(), H = bottoms[0]->height(), W = bottoms[0]->width();
+    int C = 0;
+    std::vector<const void*> xs;
+    std::vector<int64_t> widths;
+    for (const auto& b : bottoms) {
+        CHECK_EQ(b->num(), N);
+        CHECK_EQ(b->height(), H);
+        CHECK_EQ(b->width(), W);
+        C += b->channels();
+        xs.push_back(b->gpu_data());
+        widths.push_back((int64_t)b->channels() * H * W);
+    }
+    tops[0] = make_tensor<float>({N, C, H, W}, bottoms[0]->device(), memory::NCHW, bottoms[0]->allocator());
+    if (tops[0]->count() == 0) return;
+    exb_check(exb_concat_fwd(h, (int)xs.size(), xs.data(), widths.data(), widths.data(), tops[0]->mutable_gpu_data(),
+                             (int64_t)C * H * W, N, EXB_F32, nullptr), "exb_concat_fwd");
+}
+INSTANCE_CLASS(operation_concat);
+REGISTE(operation_concat);
+
+template <typename Dtype>
+operation_interp<Dtype>::operation_interp(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        switch (kv.first) {
+        case 0: resize_type_ = std::atoi(kv.second.c_str()); break;
+        case 1: width_scale_ = std::stof(kv.second); break;
+        case 2: height_scale_ = std::stof(kv.second); break;
+        case 3: output_width_ = std::atoi(kv.second.c_str()); break;
+        case 4: output_height_ = std::atoi(kv.second.c_str()); break;
+        case 6: align_corner_ = std::atoi(kv.second.c_str()); break;
+        default: LOG(FATAL) << "Un-supported Interp Attribution " << kv.first;
+        }
+    }
+}
+template <typename Dtype>
+void operation_interp<Dtype>::out_dims(int H, int W, int* OH, int* OW) const {
+    if (output_width_ == 0 || output_height_ == 0) {
+        *OH = static_cast<int>(H * height_scale_);
+        *OW = static_cast<int>(W * width_scale_);
+    } else {
+        *OH = output_height_;
+        *OW = output_width_;
+    }
+}
+template <typename Dtype>
+void operation_interp<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(tops.size(), 1u);
+    if (bottoms.size() != 1) NOT_IMPLEMENTED << " (Interp with a size tensor as second input)";
+    if (resize_type_ != 1 || align_corner_ != 0) NOT_IMPLEMENTED << " (Interp is implemented for nearest mode, keys 0=1 6=0)";
+    CHECK(bottoms[0]->order() == memory::NCHW) << "Interp expects an NCHW tensor";
+    const int N = bottoms[0]->num(), C = bottoms[0]->channels(), H = bottoms[0]->height(), W = bottoms[0]->width();
+    int OH = 0, OW = 0;
+    out_dims(H, W, &OH, &OW);
+    CHECK_GT(OH, 0);
+    CHECK_GT(OW, 0);
+    tops[0] = make_tensor<float>({N, C, OH, OW}, bottoms[0]->device(), memory::NCHW, bottoms[0]->allocator());
+    if (tops[0]->count() == 0) return;
+    exb_check(exb_interp_nearest_fwd(h, bottoms[0]->gpu_data(), tops[0]->mutable_gpu_data(), N, H, W, C, 0, OH, OW, EXB_F32,
+                                     0, nullptr), "exb_interp_nearest_fwd");
+}
+INSTANCE_CLASS(operation_interp);
+REGISTE(operation_interp);
+
+template <typename Dtype>
+operation_batchnorm<Dtype>::operation_batchnorm(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        if (kv.first == 0) channels_ = std::atoi(kv.second.c_str());
+        else if (kv.first == 1) eps_ = (float)std::atof(kv.second.c_str());
+        else LOG(FATAL) << "Un-supported Batchnorm Attribution " << kv.first;
+    }
+    this->params_.inplace_ = true;
+}
+template <typename Dtype>
+void operation_batchnorm<Dtype>::derive() {
+    const int dev = this->params_.device_;
+    const float* slope = this->weights_f32_[0]->cpu_data();
+    const float* mean = this->weights_f32_[1]->cpu_data();
+    const float* var = this->weights_f32_[2]->cpu_data();
+    const float* bias = this->weights_f32_[3]->cpu_data();
+    a_ = make_tensor<float>({channels_}, dev, memory::NCHW);
+    b_ = make_tensor<float>({channels_}, dev, memory::NCHW);
+    float* a = a_->mutable_cpu_data();
+    float* b = b_->mutable_cpu_data();
+    for (int i = 0; i < channels_; ++i) {
+        const float sqrt_var = static_cast<float>(std::sqrt(var[i] + eps_));
+        a[i] = bias[i] - slope[i] * mean[i] / sqrt_var;
+        b[i] = slope[i] / sqrt_var;
+    }
+}
+template <typename Dtype>
+int operation_batchnorm<Dtype>::init_weights(FILE* fp) {
+    const int dev = this->params_.device_;
+    static const char* const what[4] = {"slope", "mean", "var", "bias"};
+    for (int k = 0; k < 4; ++k) {
+        this->weights_f32_.push_back(make_tensor<float>({channels_}, dev, memory::NCHW));
+        read_or_die(this->weights_f32_[k]->mutable_cpu_data(), sizeof(float) * channels_, fp, what[k]);
+    }
+    derive();
+    return channels_ * (int)sizeof(float) * 4;
+}
+template <typename Dtype>
+int operation_batchnorm<Dtype>::init_weights() {
+    std::default_random_engine e;
+    std::normal_distribution<float> n(0, 0.3);
+    const int dev = this->params_.device_;
+    for (int k = 0; k < 4; ++k) {
+        this->weights_f32_.push_back(make_tensor<float>({channels_}, dev, memory::NCHW));
+        float* w = this->weights_f32_[k]->mutable_cpu_data();
+        for (int i = 0; i < channels_; ++i) w[i] = n(e);
+    }
+    derive();
+    return channels_ * (int)sizeof(float) * 4;
+}
+template <typename Dtype>
+void operation_batchnorm<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), 1u);
+    CHECK_EQ(tops.size(), 1u);
+    CHECK(bottoms[0]->order() == memory::NCHW) << "BatchNorm expects an NCHW tensor";
+    CHECK_EQ(bottoms[0]->channels(), channels_);
+    tops[0] = make_tensor<float>(bottoms[0]->data_shape(), bottoms[0]->device(), memory::NCHW, bottoms[0]->allocator());
+    if (tops[0]->count() == 0) return;
+    exb_check(exb_channel_affine_fwd(h, bottoms[0]->gpu_data(), tops[0]->mutable_gpu_data(), b_->gpu_data(), a_->gpu_data(),
+                                     bottoms[0]->num(), channels_, 0, (int64_t)bottoms[0]->height() * bottoms[0]->width(),
+                                     EXB_F32, 0, EXB_ACT_NONE, nullptr), "exb_channel_affine_fwd");
+}
+INSTANCE_CLASS(operation_batchnorm);
+REGISTE(operation_batchnorm);
 
 }  // namespace excalibur
 }  // namespace glasssix

@@ -220,8 +220,59 @@ public:
 protected:
     virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
     exb_conv_weights* w_ = nullptr;
-    int w_cin_stride_ = 0;
+    int w_cin_stride_ = 0, w_cout_stride_ = 0;
     device_scratch scratch_in_, scratch_out_;
+};
+
+// Channel concatenation: key 0 = axis in the reference's ncnn-derived convention (axis + 2 indexes
+// {N, C, H, W}, so -1 is the channel axis; reference src/Excalibur/operation_concat.cpp:10-46).
+template <typename Dtype>
+class operation_concat : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_concat(const operation_param& param);
+    virtual const char* type() const { return "Concat"; }
+    int axis_ = 0;
+    bool is_channel_concat() const { return axis_ + 2 == 1; }
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
+// Resize: keys 0 type (1 nearest, 2 bilinear), 1 / 2 width / height scale, 3 / 4 output width /
+// height, 6 align_corner (reference src/Excalibur/operation_interp.cpp:185-217).  Only the nearest
+// mode without corner alignment is implemented.
+template <typename Dtype>
+class operation_interp : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_interp(const operation_param& param);
+    virtual const char* type() const { return "Interp"; }
+    int resize_type_ = 0, output_width_ = 0, output_height_ = 0, align_corner_ = 0;
+    float width_scale_ = 1.f, height_scale_ = 1.f;
+    void out_dims(int H, int W, int* OH, int* OW) const;
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
+// Inference batch norm: keys 0 channels, 1 eps; weights in file order slope, mean, var, bias with
+// no quantize tag (reference src/Excalibur/operation_batchnorm.cpp:10-69).  y = b * x + a with
+// b = slope / sqrt(var + eps), a = bias - slope * mean / sqrt(var + eps).
+template <typename Dtype>
+class operation_batchnorm : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_batchnorm(const operation_param& param);
+    virtual const char* type() const { return "BatchNorm"; }
+    virtual int init_weights();
+    virtual int init_weights(FILE* fp);
+    int channels_ = 0;
+    float eps_ = 0.f;
+    const std::shared_ptr<memory::tensor<float>>& mul() const { return b_; }
+    const std::shared_ptr<memory::tensor<float>>& add() const { return a_; }
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    void derive();
+    std::shared_ptr<memory::tensor<float>> a_, b_;
 };
 
 }  // namespace excalibur

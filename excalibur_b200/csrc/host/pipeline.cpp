@@ -60,6 +60,7 @@ struct fmap_info {
     int N = 0, C = 0, H = 0, W = 0;
     int cs = 0;                    // physical channels of the NHWC device forms
     int w_pitch = 0, w_pad = 0;    // physically zero-padded rows (network input feeding a stem conv); 0 = dense
+    int f32_pitch = 0;             // floats per image of the fp32 form when it is a padded [N][pitch] matrix; 0 = dense
     bool need_f16 = false, need_i8 = false, need_f32 = false;
     float i8_scale = 0.f;          // multiplier of the int8 form
     std::vector<float> extra_i8_scales;   // further int8 consumers with other scales
@@ -91,7 +92,8 @@ public:
     // Why the graph cannot be fused, or "" when it can.
     std::string unsupported_reason() const {
         static const std::set<std::string> ok = {"convolution", "convolutiondepthwise", "pooling", "eltwise", "binaryop",
-                                                  "relu", "split", "innerproduct", "clip", "sigmoid"};
+                                                  "relu", "split", "innerproduct", "clip", "sigmoid", "concat", "interp",
+                                                 "batchnorm"};
         for (const auto& p : params_) {
             std::string t = p.type_;
             std::transform(t.begin(), t.end(), t.begin(), ::tolower);
@@ -143,7 +145,7 @@ private:
     }
     void* form_f32(fmap_info& f) {
         if (!f.f32) f.f32 = std::make_shared<dev_buf>();
-        return f.f32->ensure((size_t)f.N * f.H * f.W * f.C * 4, device_);
+        return f.f32->ensure((size_t)f.N * (f.f32_pitch ? f.f32_pitch : f.H * f.W * f.C) * 4, device_);
     }
     void set_shape(fmap_info& f, int N, int C, int H, int W) {
         f.N = N; f.C = C; f.H = H; f.W = W;
@@ -282,6 +284,25 @@ void fused_plan::build(int N, int C, int H, int W) {
         }
         return false;
     };
+    // x * sigmoid(x) spelled as Sigmoid + BinaryOp(mul) on the two aliases of one feature map
+    auto silu_pattern = [&](int f, int* sig, int* mul) -> bool {
+        if (output_roots.count(f) || consumers[f].size() != 2) return false;
+        for (int a = 0; a < 2; ++a) {
+            const int j = consumers[f][a], k = consumers[f][1 - a];
+            if (absorbed[j] || absorbed[k] || j == k) continue;
+            if (lower_type(params_[j]) != "sigmoid" || lower_type(params_[k]) != "binaryop") continue;
+            auto* b = dynamic_cast<operation_binaryop<float>*>(ops_[k].get());
+            if (!b || b->op_type_ != 2 || b->with_scalar_ || in_ids[k].size() != 2) continue;
+            const int so = root(out_ids[j][0]);
+            if (output_roots.count(so) || consumers[so].size() != 1 || consumers[so][0] != k) continue;
+            const int a0 = root(in_ids[k][0]), a1 = root(in_ids[k][1]);
+            if (!((a0 == so && a1 == f) || (a0 == f && a1 == so))) continue;
+            *sig = j;
+            *mul = k;
+            return true;
+        }
+        return false;
+    };
     for (size_t i = 0; i < n_ops; ++i) {
         const std::string t = lower_type(params_[i]);
         if (absorbed[i] || (t != "convolution" && t != "convolutiondepthwise")) continue;
@@ -291,8 +312,13 @@ void fused_plan::build(int N, int C, int H, int W) {
         g.act = conv->exb_activation();
         g.out = root(out_ids[i][0]);
         g.exec_at = (int)i;
-        int j;
-        if (g.act == EXB_ACT_NONE && (j = sole_consumer(g.out)) >= 0 && !absorbed[j] && act_of_op(j) > 0) {
+        int j, sj = -1, mk = -1;
+        if (g.act == EXB_ACT_NONE && silu_pattern(g.out, &sj, &mk)) {
+            g.act = EXB_ACT_SILU;
+            absorbed[sj] = absorbed[mk] = 1;
+            g.out = root(out_ids[mk][0]);
+            g.exec_at = std::max(sj, mk);
+        } else if (g.act == EXB_ACT_NONE && (j = sole_consumer(g.out)) >= 0 && !absorbed[j] && act_of_op(j) > 0) {
             g.act = act_of_op(j);
             absorbed[j] = 1;
             g.out = root(out_ids[j][0]);
@@ -514,6 +540,10 @@ void fused_plan::build(int N, int C, int H, int W) {
             exb_conv_desc d = fc->fc_desc(x.N, x.cs);
             y.N = x.N; y.C = fc->num_output_; y.H = 1; y.W = 1; y.cs = y.C;
             y.need_f32 = true;
+            // rows padded to 16 floats so the conv epilogue keeps its vector stores; the pad is dropped by the
+            // pitched device-to-host copy
+            y.f32_pitch = round_up(y.C, 16);
+            d.cout_stride = y.f32_pitch;
             const void* xin = form_f16(x);
             void* yo = form_f32(y);
             exb_conv_weights* w = fc->packed(ctx, d);
@@ -523,6 +553,67 @@ void fused_plan::build(int N, int C, int H, int W) {
             y.produced = true;
             if (!output_roots.count(root(out_ids[i][0])) || consumers[root(out_ids[i][0])].size())
                 NOT_IMPLEMENTED << " (fused plan: InnerProduct must be a pipeline output)";
+        } else if (t == "concat") {
+            auto* cc = dynamic_cast<operation_concat<float>*>(ops_[i].get());
+            if (!cc->is_channel_concat()) NOT_IMPLEMENTED << " (Concat is implemented along the channel axis, key 0=-1)";
+            auto xs = std::make_shared<std::vector<const void*>>();
+            auto widths = std::make_shared<std::vector<int64_t>>();
+            auto strides = std::make_shared<std::vector<int64_t>>();
+            int ctot = 0;
+            for (size_t k = 0; k < in_ids[i].size(); ++k) {
+                fmap_info& xi = fmaps_[root(in_ids[i][k])];
+                CHECK(xi.produced && xi.N == x.N && xi.H == x.H && xi.W == x.W) << "Concat operands differ in shape";
+                xs->push_back(form_f16(xi));
+                widths->push_back(xi.C);
+                strides->push_back(xi.cs);
+                ctot += xi.C;
+            }
+            y.need_f16 = true;
+            set_shape(y, x.N, ctot, x.H, x.W);
+            void* yo = form_f16(y);
+            const int64_t rows = (int64_t)y.N * y.H * y.W;
+            const int64_t ys = y.cs;
+            // the padding channels are never written afterwards and must stay finite
+            CUDA_CHECK(cudaMemset(yo, 0, (size_t)rows * ys * 2));
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_concat_fwd(ctx, (int)xs->size(), xs->data(), widths->data(), strides->data(), yo, ys, rows,
+                                         EXB_F16, st), "exb_concat_fwd");
+            });
+            finish_forms(y, false);
+        } else if (t == "interp") {
+            auto* ip = dynamic_cast<operation_interp<float>*>(ops_[i].get());
+            if (in_ids[i].size() != 1) NOT_IMPLEMENTED << " (Interp with a size tensor as second input)";
+            if (ip->resize_type_ != 1 || ip->align_corner_ != 0)
+                NOT_IMPLEMENTED << " (Interp is implemented for nearest mode, keys 0=1 6=0)";
+            int OH = 0, OW = 0;
+            ip->out_dims(x.H, x.W, &OH, &OW);
+            y.need_f16 = true;
+            set_shape(y, x.N, x.C, OH, OW);
+            y.cs = x.cs;
+            const void* xin = form_f16(x);
+            void* yo = form_f16(y);
+            const int n = x.N, h = x.H, w = x.W, c = x.C, cs = x.cs;
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_interp_nearest_fwd(ctx, xin, yo, n, h, w, c, cs, OH, OW, EXB_F16, 1, st), "exb_interp_nearest_fwd");
+            });
+            finish_forms(y, false);
+        } else if (t == "batchnorm") {
+            auto* bn = dynamic_cast<operation_batchnorm<float>*>(ops_[i].get());
+            CHECK_EQ(x.C, bn->channels_);
+            y.need_f16 = true;
+            set_shape(y, x.N, x.C, x.H, x.W);
+            y.cs = x.cs;
+            const void* xin = form_f16(x);
+            void* yo = form_f16(y);
+            const float* mul = bn->mul()->gpu_data();
+            const float* add = bn->add()->gpu_data();
+            const int64_t rows = (int64_t)x.N * x.H * x.W;
+            const int c = x.C, cs = x.cs;
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_channel_affine_fwd(ctx, xin, yo, mul, add, rows, c, cs, 1, EXB_F16, 1, EXB_ACT_NONE, st),
+                          "exb_channel_affine_fwd");
+            });
+            finish_forms(y, false);
         } else {
             // element-wise ops on the fp16 form
             y.need_f16 = true;
@@ -645,8 +736,12 @@ void fused_plan::run(const float* host_input, bool use_graph, bool profile, std:
     }
     for (auto& kv : host_out_) {
         fmap_info& f = fmaps_[root(index_[kv.first])];
-        CUDA_CHECK(cudaMemcpyAsync(kv.second->mutable_cpu_data(), f.f32->p, (size_t)f.N * f.C * f.H * f.W * 4,
-                                   cudaMemcpyDeviceToHost, stream_));
+        if (f.f32_pitch)
+            CUDA_CHECK(cudaMemcpy2DAsync(kv.second->mutable_cpu_data(), (size_t)f.C * 4, f.f32->p, (size_t)f.f32_pitch * 4,
+                                         (size_t)f.C * 4, f.N, cudaMemcpyDeviceToHost, stream_));
+        else
+            CUDA_CHECK(cudaMemcpyAsync(kv.second->mutable_cpu_data(), f.f32->p, (size_t)f.N * f.C * f.H * f.W * 4,
+                                       cudaMemcpyDeviceToHost, stream_));
     }
     CUDA_CHECK(cudaStreamSynchronize(stream_));
     if (!profile) {
@@ -701,7 +796,12 @@ std::shared_ptr<memory::tensor<float>> fused_plan::fetch(const std::string& name
     auto t = std::shared_ptr<memory::tensor<float>>(
         new memory::tensor<float>(std::vector<int>{f.N, f.C, f.H, f.W}, device_, memory::NCHW, nullptr));
     if (f.f32 && f.need_f32 && !f.f16) {
-        CUDA_CHECK(cudaMemcpy(t->mutable_cpu_data(), f.f32->p, (size_t)t->count() * 4, cudaMemcpyDeviceToHost));
+        CUDA_CHECK(cudaStreamSynchronize(stream_));
+        if (f.f32_pitch)
+            CUDA_CHECK(cudaMemcpy2D(t->mutable_cpu_data(), (size_t)f.C * 4, f.f32->p, (size_t)f.f32_pitch * 4,
+                                    (size_t)f.C * 4, f.N, cudaMemcpyDeviceToHost));
+        else
+            CUDA_CHECK(cudaMemcpy(t->mutable_cpu_data(), f.f32->p, (size_t)t->count() * 4, cudaMemcpyDeviceToHost));
         return t;
     }
     const void* src = f.f16 ? f.f16->p : (f.i8 ? f.i8->p : nullptr);

@@ -126,6 +126,12 @@ class GraphBuilder:
     def interp_nearest(self, name, x, y, scale=2.0):
         return self._op("Interp", name, [x], [y], "0=1 1=%r 2=%r" % (float(scale), float(scale)))
 
+    def batchnorm(self, name, x, y, slope, mean, var, bias, eps=0.0):
+        """Weights in file order slope, mean, var, bias, no quantize tag."""
+        for v in (slope, mean, var, bias):
+            self.blob += np.ascontiguousarray(v, "<f4").tobytes()
+        return self._op("BatchNorm", name, [x], [y], "0=%d 1=%r" % (len(slope), float(eps)))
+
     def innerproduct(self, name, x, y, w, bias=None):
         """w: [out][in] fp32."""
         self.blob += struct.pack("<i", RACY_TAG_F32)

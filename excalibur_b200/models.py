@@ -94,6 +94,173 @@ def resnet18(seed=2, act_scales=None, widths=RESNET18_WIDTHS, num_classes=1000, 
     return g, {"conv_inputs": conv_inputs, "input": "data", "output": "logits"}
 
 
+MOBILENET_V2_BLOCKS = ((1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2),
+                       (6, 320, 1, 1))
+
+
+def mobilenet_v2(seed=3, act_scales=None, blocks=MOBILENET_V2_BLOCKS, num_classes=1000, in_ch=3, last=1280):
+    """MobileNetV2-style (1.0x) classifier: 3x3/2 stem with 32 channels, 17 inverted-residual blocks
+    (1x1 expand t=6, 3x3 depthwise, 1x1 linear project; residual add where stride is 1 and the widths
+    match), 1x1 conv to 1280, global average pool, FC.  ReLU6 is written as a Clip(0, 6) operation
+    after the conv so that both libraries clamp (the conv's own activation code 3 zeroes values
+    above 6 in the reference).  With act_scales the 1x1 convs become int8 convs; the stem, the
+    depthwise convs and the FC stay in floating point.  Returns (GraphBuilder, info) like resnet18."""
+    g = GraphBuilder("mobilenet_v2_style")
+    wts = _Weights(seed)
+    conv_inputs = {}
+
+    def relu6(name, x):
+        return g.clip(name + "_relu6", x, name + "_act", 0.0, 6.0)
+
+    def pw(name, x, cout, cin, act):
+        w, b = wts.conv_bn(cout, cin, 1)
+        conv_inputs[name] = x
+        int8 = None
+        if act_scales is not None:
+            wq, ws = quantize_weights(w)
+            int8 = (wq, ws, np.float32(act_scales[name]))
+        y = g.conv(name, x, name + "_out", w, b, 1, 0, act=0, int8=int8)
+        return relu6(name, y) if act else y
+
+    w, b = wts.conv_bn(32, in_ch, 3)
+    x = relu6("stem", g.conv("stem", "data", "stem_out", w, b, 2, 1, act=0))
+    cin = 32
+    bi = 0
+    for t, c, n, s in blocks:
+        for i in range(n):
+            bi += 1
+            p = "b%d" % bi
+            stride = s if i == 0 else 1
+            use_res = stride == 1 and cin == c
+            if use_res:
+                x, skip = g.split(p + "_split", x, [p + "_a", p + "_b"])
+            h = x
+            hid = cin * t
+            if t != 1:
+                h = pw(p + "_expand", h, hid, cin, True)
+            wd, bd = wts.conv_bn(hid, 1, 3)
+            h = relu6(p + "_dw", g.dwconv(p + "_dw", h, p + "_dw_out", wd, bd, stride, 1, act=0))
+            h = pw(p + "_project", h, c, hid, False)
+            if use_res:
+                h = g.eltwise(p + "_add", [h, skip], p + "_sum", 1)
+            x = h
+            cin = c
+    x = pw("head", x, last, cin, True)
+    x = g.pool("gap", x, "gap_out", 1, global_pool=True)
+    fw, fb = wts.fc(num_classes, last)
+    g.innerproduct("fc", x, "logits", fw, fb)
+    return g, {"conv_inputs": conv_inputs, "input": "data", "output": "logits"}
+
+
+class _Net:
+    """Records operations first and emits them afterwards, inserting a Split wherever a feature map
+    has more than one consumer (the graph format wants every fan-out spelled out)."""
+
+    def __init__(self, g):
+        self.g = g
+        self.ops = []
+
+    def add(self, fn, ins, out):
+        self.ops.append((fn, list(ins), out))
+        return out
+
+    def emit(self, inputs=("data",)):
+        uses = {}
+        for _, ins, _ in self.ops:
+            for t in ins:
+                uses[t] = uses.get(t, 0) + 1
+        taken = {}
+
+        def take(t):
+            if uses.get(t, 0) <= 1:
+                return t
+            k = taken.get(t, 0)
+            taken[t] = k + 1
+            return "%s__%d" % (t, k)
+
+        def fan_out(t):
+            if uses.get(t, 0) > 1:
+                self.g.split(t + "_split", t, ["%s__%d" % (t, k) for k in range(uses[t])])
+
+        for t in inputs:
+            fan_out(t)
+        for fn, ins, out in self.ops:
+            fn([take(t) for t in ins], out)
+            fan_out(out)
+
+
+def yolov5s(seed=5, num_outputs=255, in_ch=3, width=(32, 64, 128, 256, 512), depth=(1, 2, 3, 1)):
+    """YOLOv5s-style detector (depth 0.33, width 0.50): 6x6/2 stem with 32 channels, 3x3/2 convs to
+    64/128/256/512 each followed by a CSP-C3 block with 1/2/3/1 bottlenecks, SPPF (three chained
+    5x5/1 max pools and a concat), PAN neck (nearest 2x upsample + concat on the way up, 3x3/2
+    convs + concat on the way down), three 1x1 heads with `num_outputs` channels at strides
+    8/16/32.  Every conv except the heads is conv + folded BN + SiLU, with SiLU written as
+    Sigmoid + BinaryOp(mul).  Returns (GraphBuilder, info); info["outputs"] names the three heads."""
+    g = GraphBuilder("yolov5s_style")
+    wts = _Weights(seed)
+    net = _Net(g)
+
+    def conv(name, x, cout, cin, k=1, s=1, p=None, act=True):
+        w, b = wts.conv_bn(cout, cin, k)
+        pad = k // 2 if p is None else p
+        y = net.add(lambda ins, out: g.conv(name, ins[0], out, w, b, s, pad, act=0), [x], name + "_out")
+        if not act:
+            return y
+        sg = net.add(lambda ins, out: g.sigmoid(name + "_sig", ins[0], out), [y], name + "_sg")
+        return net.add(lambda ins, out: g.binaryop(name + "_mul", ins[0], ins[1], out, 2), [sg, y], name + "_act")
+
+    def concat(name, xs):
+        return net.add(lambda ins, out: g.concat(name, ins, out), xs, name + "_out")
+
+    def c3(name, x, c1, c2, n, shortcut):
+        c_ = c2 // 2
+        a = conv(name + "_cv1", x, c_, c1)
+        b = conv(name + "_cv2", x, c_, c1)
+        for i in range(n):
+            m = "%s_m%d" % (name, i)
+            h = conv(m + "_cv1", a, c_, c_)
+            h = conv(m + "_cv2", h, c_, c_, 3)
+            if shortcut:
+                h = net.add(lambda ins, out, m=m: g.binaryop(m + "_add", ins[0], ins[1], out, 0), [a, h], m + "_sum")
+            a = h
+        return conv(name + "_cv3", concat(name + "_cat", [a, b]), c2, 2 * c_)
+
+    def pool5(name, x):
+        return net.add(lambda ins, out: g.pool(name, ins[0], out, 0, 5, 1, 2), [x], name + "_out")
+
+    def up2(name, x):
+        return net.add(lambda ins, out: g.interp_nearest(name, ins[0], out, 2.0), [x], name + "_out")
+
+    w0, w1, w2, w3, w4 = width
+    x = conv("stem", "data", w0, in_ch, 6, 2, 2)
+    x = conv("down1", x, w1, w0, 3, 2)
+    x = c3("c3_1", x, w1, w1, depth[0], True)
+    x = conv("down2", x, w2, w1, 3, 2)
+    p3 = c3("c3_2", x, w2, w2, depth[1], True)
+    x = conv("down3", p3, w3, w2, 3, 2)
+    p4 = c3("c3_3", x, w3, w3, depth[2], True)
+    x = conv("down4", p4, w4, w3, 3, 2)
+    x = c3("c3_4", x, w4, w4, depth[3], True)
+    h = conv("sppf_cv1", x, w4 // 2, w4)
+    y1 = pool5("sppf_p1", h)
+    y2 = pool5("sppf_p2", y1)
+    y3 = pool5("sppf_p3", y2)
+    x = conv("sppf_cv2", concat("sppf_cat", [h, y1, y2, y3]), w4, 2 * w4)
+    t5 = conv("neck_cv1", x, w3, w4)
+    x = c3("neck_c3_1", concat("neck_cat1", [up2("neck_up1", t5), p4]), 2 * w3, w3, 1, False)
+    t4 = conv("neck_cv2", x, w2, w3)
+    o3 = c3("neck_c3_2", concat("neck_cat2", [up2("neck_up2", t4), p3]), 2 * w2, w2, 1, False)
+    x = conv("neck_down1", o3, w2, w2, 3, 2)
+    o4 = c3("neck_c3_3", concat("neck_cat3", [x, t4]), 2 * w2, w3, 1, False)
+    x = conv("neck_down2", o4, w3, w3, 3, 2)
+    o5 = c3("neck_c3_4", concat("neck_cat4", [x, t5]), 2 * w3, w4, 1, False)
+    outs = [conv("head_p3", o3, num_outputs, w2, act=False),
+            conv("head_p4", o4, num_outputs, w3, act=False),
+            conv("head_p5", o5, num_outputs, w4, act=False)]
+    net.emit()
+    return g, {"input": "data", "outputs": outs}
+
+
 def calibrate(float_pipeline, conv_inputs, images):
     """fs = 127 / max|x| over the calibration images for every conv input (max-abs calibration).
     `float_pipeline` is any object with forward(x) and get(name) -> NCHW fp32 (the reference

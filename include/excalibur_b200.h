@@ -277,6 +277,41 @@ EXB_API int exb_quantize_fwd(exb_ctx* ctx, const void* x, int in_dtype, int8_t* 
 EXB_API int exb_dequantize_fwd(exb_ctx* ctx, const int8_t* q, void* y, int out_dtype,
                                int64_t count, float scale, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Graph glue around the convolution trunk.
+ *
+ * exb_concat_fwd stands in for operation_concat::forward_* (src/Excalibur/
+ * operation_concat.cpp:30-150, src/Excalibur/cuda/operation_concat.cu) for a concatenation along
+ * one axis, written as a row-wise concatenation: y[r][off_i + k] = x_i[r][k] for k < widths[i],
+ * off_i = widths[0] + ... + widths[i-1].  Channel concat of NHWC tensors: rows = N*H*W,
+ * widths = channel counts, strides = physical channels.  Channel concat of NCHW tensors:
+ * rows = N, widths = strides = C_i*H*W.  Up to 8 inputs; dtype gives the element size only.
+ *
+ * exb_interp_nearest_fwd stands in for operation_interp's nearest mode (resize_type 1,
+ * align_corner 0: src/Excalibur/operation_interp.cpp:247-268, src/Excalibur/cuda/
+ * operation_interp.cu:9-66): source index = min((int)(o * (in / (float)out)), in - 1) per axis.
+ * channel_last 1: NHWC with c_stride physical channels (EXB_F16, EXB_I8, EXB_F32);
+ * channel_last 0: NCHW EXB_F32.
+ *
+ * exb_channel_affine_fwd computes y = act(x * mul[c] + add[c]); it stands in for
+ * operation_batchnorm::forward_* (src/Excalibur/operation_batchnorm.cpp:33-69,123-160: b = slope /
+ * sqrt(var + eps), a = bias - slope * mean / sqrt(var + eps)) and for the per-channel
+ * normalisation of operation_input (src/Excalibur/operation_input.cpp:61-151).  mul / add are
+ * DEVICE fp32 arrays of C entries.  channel_last 1: x is [outer][c_stride] (outer = N*H*W;
+ * padding channels are written as 0); channel_last 0: x is [outer][C][inner] (outer = N,
+ * inner = H*W).  EXB_F16 or EXB_F32; y may alias x.
+ * ------------------------------------------------------------------------------------- */
+EXB_API int exb_concat_fwd(exb_ctx* ctx, int n_in, const void* const* xs, const int64_t* widths,
+                           const int64_t* x_strides, void* y, int64_t y_stride, int64_t rows,
+                           int dtype, void* stream);
+EXB_API int exb_interp_nearest_fwd(exb_ctx* ctx, const void* x, void* y, int N, int H, int W, int C,
+                                   int c_stride, int OH, int OW, int dtype, int channel_last,
+                                   void* stream);
+EXB_API int exb_channel_affine_fwd(exb_ctx* ctx, const void* x, void* y, const float* mul,
+                                   const float* add, int64_t outer, int C, int c_stride,
+                                   int64_t inner, int dtype, int channel_last, int act,
+                                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -201,6 +201,38 @@ def relu_f32(x):
     return y
 
 
+# ---- graph glue (pure index arithmetic, restated in numpy) -----------------------------
+def concat_channels(xs):
+    """Channel concat of NCHW arrays: src/Excalibur/operation_concat.cpp:84-110 (axis key -1)."""
+    return np.concatenate([_f32(x) for x in xs], axis=1)
+
+
+def interp_nearest(x, out_h, out_w):
+    """Nearest resize, src/Excalibur/operation_interp.cpp:247-268: source index
+    min((int)(o * (in / (float)out)), in - 1) with the ratio and the product in fp32."""
+    x = _f32(x)
+    H, W = x.shape[2], x.shape[3]
+    hs = np.float32(H) / np.float32(out_h)
+    ws = np.float32(W) / np.float32(out_w)
+    iy = np.minimum((np.arange(out_h, dtype=np.float32) * hs).astype(np.int32), H - 1)
+    ix = np.minimum((np.arange(out_w, dtype=np.float32) * ws).astype(np.int32), W - 1)
+    return np.ascontiguousarray(x[:, :, iy][:, :, :, ix])
+
+
+def batchnorm_coeffs(slope, mean, var, bias, eps=0.0):
+    """(b, a) of y = b*x + a, src/Excalibur/operation_batchnorm.cpp:56-66: fp32 throughout,
+    sqrt of (var + eps) rounded to fp32 before the divisions."""
+    slope, mean, var, bias = (_f32(v) for v in (slope, mean, var, bias))
+    sq = np.sqrt((var + np.float32(eps)).astype(np.float64)).astype(np.float32)
+    return (slope / sq).astype(np.float32), (bias - slope * mean / sq).astype(np.float32)
+
+
+def channel_affine(x, mul, add):
+    """y[n][c] = x[n][c] * mul[c] + add[c] (src/Excalibur/operation_batchnorm.cpp:123-160)."""
+    x = _f32(x)
+    return (x * _f32(mul)[None, :, None, None] + _f32(add)[None, :, None, None]).astype(np.float32)
+
+
 # ---- layout helpers -------------------------------------------------------------------
 def nchw_to_nhwc(a):
     return np.ascontiguousarray(np.transpose(a, (0, 2, 3, 1)))

@@ -3,7 +3,9 @@
 Run in a container that has the reference tree (it cannot travel to the GPU box):
 
     make -C oracle ref            # builds oracle/_ref/libexcalibur_ref.so from the reference sources
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py             # both fixture files
+    python tests/golden/make_golden.py mobilenet   # tests/golden/mobilenet_vectors.npz only
+    python tests/golden/make_golden.py yolo        # tests/golden/yolo_vectors.npz only
 
 Every case stores its inputs, weights and the reference's output, so the fixture pins the oracle
 (oracle/exb_oracle.c) and, through it, the CUDA kernels, without the reference being present.
@@ -130,6 +132,93 @@ def main():
     path = os.path.join(ROOT, "tests", "golden", "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
+    mobilenet()
+    yolo()
+
+
+def yolo():
+    """Graph-glue operations (Concat, Interp nearest, BatchNorm) one at a time, and the YOLOv5s-style
+    net at 128x128, batch 2 -> tests/golden/yolo_vectors.npz."""
+    r = np.random.default_rng(20240608)
+    out = {}
+    # Concat of three maps with ragged channel counts
+    # (the reference driver feeds one input tensor: the three maps derive from it)
+    g = GraphBuilder()
+    g.split("s", "in", ["i0", "i1", "i2"])
+    g.relu("r0", "i0", "a")
+    g.sigmoid("r1", "i1", "b")
+    g.concat("cat", ["a", "b", "i2"], "out")
+    x = r.standard_normal((2, 19, 5, 7)).astype(np.float32)
+    out["cat_x"] = x
+    out["cat_out"], = run(g, x)
+    # nearest resize: 2x, and a non-integer ratio through explicit output sizes
+    g = GraphBuilder()
+    g.interp_nearest("up", "in", "out", 2.0)
+    x = r.standard_normal((2, 10, 6, 5)).astype(np.float32)
+    out["interp2_x"] = x
+    out["interp2_out"], = run(g, x)
+    g = GraphBuilder()
+    g._op("Interp", "up", ["in"], ["out"], "0=1 3=11 4=7")
+    out["interp_odd_x"] = x
+    out["interp_odd_out"], = run(g, x)
+    # batch norm
+    C = 13
+    bn = [r.uniform(0.5, 1.5, C), r.standard_normal(C), r.uniform(0.5, 2.0, C), r.standard_normal(C)]
+    bn = [v.astype(np.float32) for v in bn]
+    g = GraphBuilder()
+    g.batchnorm("bn", "in", "out", *bn, eps=1e-5)
+    x = r.standard_normal((2, C, 6, 5)).astype(np.float32)
+    out["bn_x"] = x
+    for k, n in enumerate(("slope", "mean", "var", "bias")):
+        out["bn_" + n] = bn[k]
+    out["bn_out"], = run(g, x)
+
+    x = np.random.default_rng(5000).uniform(0, 1, (2, 3, 128, 128)).astype(np.float32)
+    gy, info = models.yolov5s(5)
+    py = ref_lib.RefPipeline(gy.phai_text(), gy.racy_bytes())
+    res = py.forward(x)
+    out["yolo_x"] = x
+    for n in info["outputs"]:
+        out["yolo_" + n] = res[n]
+    for n in ("c3_1_cv3_act", "sppf_cat_out", "neck_up1_out"):
+        out["yolo_" + n] = py.featmap(n)
+    py.close()
+    path = os.path.join(ROOT, "tests", "golden", "yolo_vectors.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
+
+
+def mobilenet():
+    """MobileNetV2-style net at 64x64, batch 2 -> tests/golden/mobilenet_vectors.npz: fp32 logits and
+    two inner feature maps, max-abs scales of the 1x1 convs from 4 seeded images, and the int8
+    network's logits (one image per forward because of the reference's int8 batch quirk)."""
+    seed = 3
+    out = {}
+    x = np.random.default_rng(3000).uniform(0, 1, (2, 3, 64, 64)).astype(np.float32)
+    g32, info = models.mobilenet_v2(seed)
+    p32 = ref_lib.RefPipeline(g32.phai_text(), g32.racy_bytes())
+    out["x"] = x
+    out["f32_logits"] = p32.forward(x)["logits"].reshape(2, -1)
+    for n in ("b1_project_out", "b3_sum", "b14_dw_act"):
+        out["f32_" + n] = p32.featmap(n)
+    calib = np.random.default_rng(3007).uniform(0, 1, (4, 3, 64, 64)).astype(np.float32)
+    scales = models.calibrate(_RefAdapter(p32), info["conv_inputs"], calib)
+    p32.close()
+    names = sorted(scales)
+    out["scale_names"] = np.array(names)
+    out["scales"] = np.array([scales[n] for n in names], np.float32)
+    g8, _ = models.mobilenet_v2(seed, act_scales=scales)
+    p8 = ref_lib.RefPipeline(g8.phai_text(), g8.racy_bytes())
+    logits, b3 = [], []
+    for i in range(2):
+        logits.append(p8.forward(x[i:i + 1])["logits"].reshape(1, -1))
+        b3.append(p8.featmap("b3_sum"))
+    p8.close()
+    out["i8_logits"] = np.concatenate(logits)
+    out["i8_b3_sum"] = np.concatenate(b3)
+    path = os.path.join(ROOT, "tests", "golden", "mobilenet_vectors.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
 
 
 class _RefAdapter:
@@ -144,4 +233,9 @@ class _RefAdapter:
 
 
 if __name__ == "__main__":
-    main()
+    if sys.argv[1:] == ["mobilenet"]:
+        mobilenet()
+    elif sys.argv[1:] == ["yolo"]:
+        yolo()
+    else:
+        main()

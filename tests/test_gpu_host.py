@@ -158,3 +158,95 @@ def test_calibration_with_own_pipeline_matches_reference_scales():
     p.close()
     for n, s in zip(G["resnet_scale_names"], G["resnet_scales"]):
         assert abs(scales[str(n)] / s - 1.0) < 1e-2, (n, scales[str(n)], s)
+
+
+# ---- MobileNetV2-style network (1x1 expand / 3x3 depthwise / 1x1 project, ReLU6 as Clip) ----------
+M = np.load(os.path.join(os.path.dirname(__file__), "golden", "mobilenet_vectors.npz"))
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_mobilenet_v2_fp(fusion):
+    h = _host()
+    g, _ = models.mobilenet_v2(3)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    x = M["x"]
+    for _ in range(3):     # eager, capture, replay
+        out = p.forward(x)["logits"].reshape(2, -1)
+    ref = M["f32_logits"]
+    assert _rel(out, ref) < 1e-2, _rel(out, ref)
+    assert (out.argmax(1) == ref.argmax(1)).all()
+    if not fusion:         # the fused plan does not materialise maps it folds into a conv epilogue
+        for n in ("b1_project_out", "b3_sum", "b14_dw_act"):
+            assert _rel(p.get(n), M["f32_" + n]) < 1e-2, n
+    p.close()
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_mobilenet_v2_int8_pointwise(fusion):
+    h = _host()
+    scales = {str(n): np.float32(s) for n, s in zip(M["scale_names"], M["scales"])}
+    g, _ = models.mobilenet_v2(3, act_scales=scales)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    x = M["x"]
+    for _ in range(3):
+        out = p.forward(x)["logits"].reshape(2, -1)
+    ref = M["i8_logits"]
+    # 35 int8 convs deep, each re-quantising its input from an fp16 (here) or fp32 (reference)
+    # map: values on a rounding boundary flip one int8 step, so the bar is the int8 network's
+    # own noise floor rather than fp16 accuracy
+    r = _rel(out, ref)
+    assert r < 5e-2, r
+    if not fusion:
+        assert _rel(p.get("b3_sum"), M["i8_b3_sum"]) < 3e-2
+    p.close()
+
+
+# ---- graph glue and the YOLOv5s-style network -------------------------------------------------------
+Y = np.load(os.path.join(os.path.dirname(__file__), "golden", "yolo_vectors.npz"))
+
+
+def test_operation_concat_interp_batchnorm():
+    h = _host()
+    x = Y["cat_x"]
+    a = h.run_op("ReLU", "", [x])
+    b = h.run_op("Sigmoid", "", [x])
+    y = h.run_op("Concat", "0=-1", [a, b, x])
+    assert y.shape == Y["cat_out"].shape
+    np.testing.assert_allclose(y, Y["cat_out"], rtol=0, atol=1e-6)      # sigmoid via __expf
+    np.testing.assert_array_equal(y[:, 38:], x)
+    np.testing.assert_array_equal(h.run_op("Interp", "0=1 1=2.0 2=2.0", [Y["interp2_x"]]), Y["interp2_out"])
+    np.testing.assert_array_equal(h.run_op("Interp", "0=1 3=11 4=7", [Y["interp_odd_x"]]), Y["interp_odd_out"])
+    g = GraphBuilder()
+    g.batchnorm("bn", "in", "out", Y["bn_slope"], Y["bn_mean"], Y["bn_var"], Y["bn_bias"], eps=1e-5)
+    params = g.lines[0].split(" ", 6)[6]
+    y = h.run_op("BatchNorm", params, [Y["bn_x"]], g.racy_bytes())
+    np.testing.assert_allclose(y, Y["bn_out"], rtol=2e-7, atol=3e-7)
+    with pytest.raises(h.HostError):
+        h.run_op("Concat", "0=0", [x, x])          # only the channel axis is implemented
+    with pytest.raises(h.HostError):
+        h.run_op("Interp", "0=2 1=2.0 2=2.0", [x])  # bilinear is not
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_yolov5s_fp(fusion):
+    h = _host()
+    g, info = models.yolov5s(5)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    x = Y["yolo_x"]
+    for _ in range(3):     # eager, capture, replay
+        out = p.forward(x)
+    assert sorted(out) == sorted(info["outputs"])
+    for n in info["outputs"]:
+        ref = Y["yolo_" + n]
+        assert out[n].shape == ref.shape
+        r = _rel(out[n], ref)
+        assert r < 1e-2, (n, r)
+    if not fusion:
+        for n in ("c3_1_cv3_act", "sppf_cat_out", "neck_up1_out"):
+            assert _rel(p.get(n), Y["yolo_" + n]) < 1e-2, n
+    else:
+        launches, _ = p.stats()
+        # every Sigmoid + BinaryOp(mul) pair folds into its conv: 57 SiLU convs + 3 heads, 7 bottleneck
+        # adds, 3 pools, 13 concats, 2 resizes, ingest and 3 emits
+        assert launches <= 60 + 7 + 3 + 13 + 2 + 1 + 3, launches
+    p.close()

@@ -72,3 +72,29 @@ def test_float32_to_int8_rule():
 def test_dequant_scale_rule():
     s = O.dequant_scales(np.array([2.0, 1e-7, 4.0], np.float32), np.array([8.0], np.float32), 3)
     np.testing.assert_array_equal(s, np.array([1.0 / 16.0, 0.0, 1.0 / 32.0], np.float32))
+
+
+# ---- graph glue (Concat, Interp nearest, BatchNorm) against tests/golden/yolo_vectors.npz ---------
+Y = np.load(os.path.join(os.path.dirname(__file__), "golden", "yolo_vectors.npz"))
+
+
+def test_concat_channels():
+    x = Y["cat_x"]
+    relu = O.relu_f32(x)
+    sig = (1.0 / (1.0 + np.exp(-x.astype(np.float64)))).astype(np.float32)
+    y = O.concat_channels([relu, sig, x])
+    assert y.shape == Y["cat_out"].shape
+    np.testing.assert_array_equal(y[:, :19], Y["cat_out"][:, :19])
+    np.testing.assert_array_equal(y[:, 38:], Y["cat_out"][:, 38:])
+    np.testing.assert_allclose(y[:, 19:38], Y["cat_out"][:, 19:38], rtol=0, atol=2e-7)   # expf vs exp
+
+
+def test_interp_nearest():
+    np.testing.assert_array_equal(O.interp_nearest(Y["interp2_x"], 12, 10), Y["interp2_out"])
+    np.testing.assert_array_equal(O.interp_nearest(Y["interp_odd_x"], 7, 11), Y["interp_odd_out"])
+
+
+def test_batchnorm():
+    b, a = O.batchnorm_coeffs(Y["bn_slope"], Y["bn_mean"], Y["bn_var"], Y["bn_bias"], 1e-5)
+    # the reference's loop may or may not contract b*x + a into one fma
+    np.testing.assert_allclose(O.channel_affine(Y["bn_x"], b, a), Y["bn_out"], rtol=2e-7, atol=3e-7)
