@@ -1,6 +1,8 @@
 // API-edge converts between the reference's NCHW fp32 tensors and the NHWC fp16 / int8
 // buffers the kernels use.  Both directions go through a shared-memory transpose tile so
 // that global reads and writes are both coalesced (reads along W, writes along C or back).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace exb {
@@ -91,6 +93,42 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_padded_kernel(const float* _
     }
 }
 
+// The same conversion for fp16 NHWC4 when W, w_pad and w_pitch are multiples of 4: one thread per
+// four consecutive row slots, a 16-byte load from each plane and one 32-byte store; rows are
+// addressed by blockIdx.y so no division is left in the loop.
+__global__ void __launch_bounds__(256) nchw_to_nhwc4_f16_quad_kernel(const float* __restrict__ x, __half* __restrict__ y,
+                                                                     int C, int H, int W, int w_pad, int w_pitch,
+                                                                     int64_t rows) {
+    const int quads = w_pitch >> 2;
+    const int64_t plane = (int64_t)H * W;
+    for (int64_t row = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; row < rows; row += (int64_t)gridDim.x * blockDim.y) {
+        const int64_t n = row / H;
+        const int h = (int)(row - n * H);
+        const float* src = x + (n * C * H + h) * (int64_t)W;
+        for (int q = threadIdx.x; q < quads; q += blockDim.x) {
+            const int w = 4 * q - w_pad;
+            float4 v[3];
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (c < C && w >= 0 && w < W) v[c] = *reinterpret_cast<const float4*>(src + c * plane + w);
+            }
+            uint32_t o[8];
+#define EXB_PACK(j, m)                                                            \
+            {                                                                         \
+                __half2 lo = __floats2half2_rn(v[0].m, v[1].m), hi = __floats2half2_rn(v[2].m, 0.f); \
+                o[2 * j] = *reinterpret_cast<uint32_t*>(&lo);                         \
+                o[2 * j + 1] = *reinterpret_cast<uint32_t*>(&hi);                     \
+            }
+            EXB_PACK(0, x) EXB_PACK(1, y) EXB_PACK(2, z) EXB_PACK(3, w)
+#undef EXB_PACK
+            uint4* dst = reinterpret_cast<uint4*>(y + (row * w_pitch + 4 * q) * 4);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+    }
+}
+
 int check_dims(const exb_ctx* ctx, const void* a, const void* b, int N, int C, int H, int W, int c_stride) {
     EXB_REQUIRE(ctx != nullptr, "null context");
     EXB_REQUIRE(N >= 0 && C > 0 && H > 0 && W > 0, "bad tensor shape %dx%dx%dx%d", N, C, H, W);
@@ -149,6 +187,14 @@ extern "C" int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x, void* y
         return fail(EXB_ERR_UNSUPPORTED, "padded ingest supports c_stride 4 or 8, got %d", c_stride);
     if (N == 0) return EXB_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == EXB_F16 && c_stride == 4 && C <= 3 && (W & 3) == 0 && (w_pad & 3) == 0 && (w_pitch & 3) == 0 &&
+        aligned16(x) && aligned16(y)) {
+        const int64_t rows = (int64_t)N * H;
+        const dim3 block(64, 4);
+        const int grid = (int)std::min<int64_t>((rows + 3) / 4, (int64_t)ctx->sm_count * 32);
+        nchw_to_nhwc4_f16_quad_kernel<<<grid, block, 0, st>>>(x, static_cast<__half*>(y), C, H, W, w_pad, w_pitch, rows);
+        return after_launch("nchw_to_nhwc4_f16_quad_kernel");
+    }
     const int grid = stream_grid(ctx, (int64_t)N * H * w_pitch, 256, 16);
 #define EXB_LAUNCH(T, CS) nchw_to_nhwc_padded_kernel<T, CS><<<grid, 256, 0, st>>>(x, static_cast<T*>(y), N, C, H, W, w_pad, w_pitch, scale, rounding)
     if (dtype == EXB_F16) { if (c_stride == 4) EXB_LAUNCH(__half, 4); else EXB_LAUNCH(__half, 8); }
