@@ -94,6 +94,7 @@ extern "C" int exb_host_pipeline_set_option(void* p, const char* key, int value)
     if (k == "fusion") h->net->set_fusion(value != 0);
     else if (k == "cuda_graph") h->net->set_cuda_graph(value != 0);
     else if (k == "profile") value ? h->net->enable_profiler() : h->net->disable_profiler();
+    else if (k == "h2d_chunks") h->net->set_h2d_chunks(value);
     else {
         g_err = "unknown option " + k;
         return EXB_ERR_BAD_ARG;

@@ -83,6 +83,8 @@ public:
         : params_(params), ops_(ops), inputs_(inputs), outputs_(outputs), device_(device) {}
     ~fused_plan() {
         if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+        for (auto e : copied_) cudaEventDestroy(e);
+        if (copy_stream_) cudaStreamDestroy(copy_stream_);
         if (stream_) cudaStreamDestroy(stream_);
         if (ev0_) cudaEventDestroy(ev0_);
         if (ev1_) cudaEventDestroy(ev1_);
@@ -104,10 +106,13 @@ public:
     }
 
     void build(int N, int C, int H, int W);
+    bool built() const { return built_; }
     bool built_for(int N, int C, int H, int W) const { return built_ && N == N_ && C == C_ && H == H_ && W == W_; }
     void run(const float* host_input, bool use_graph, bool profile, std::vector<trace_event>* trace);
     std::shared_ptr<memory::tensor<float>> fetch(const std::string& name);
     double run_resident(int iters, bool use_graph);
+    // forward of k * N_ images: chunk c+1 is copied to the device while chunk c is computed
+    void run_chunked(const float* host_input, int k, bool use_graph);
     int launches() const { return launches_; }
     double device_ms() const { return device_ms_; }
     exb_ctx* ctx() { return ctx_; }
@@ -169,6 +174,11 @@ private:
     std::unordered_map<std::string, int> index_;
     std::vector<plan_step> steps_;
     dev_buf staging_in_;
+    dev_buf chunk_stage_;                  // k chunks of fp32 input for run_chunked
+    const float* ingest_src_ = nullptr;    // what the ingest step (steps_[0]) reads; never part of the graph
+    cudaStream_t copy_stream_ = nullptr;
+    std::vector<cudaEvent_t> copied_;
+    void launch_body(bool use_graph);
     int launches_ = 0;
     double device_ms_ = 0.0;
     bool warmed_ = false;
@@ -176,6 +186,8 @@ private:
 public:
     // results of the last run, by output feature map name
     std::unordered_map<std::string, std::shared_ptr<memory::tensor<float>>> host_out_;
+    // results of the last run_chunked (all k * N_ images)
+    std::unordered_map<std::string, std::shared_ptr<memory::tensor<float>>> chunk_out_;
 };
 
 void fused_plan::finish_forms(fmap_info& f, bool wrote_i8) {
@@ -387,7 +399,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         const int in_id = root(fid(inputs_[0]));
         fmap_info& in = fmaps_[in_id];
         set_shape(in, N, C, H, W);
-        float* stage = static_cast<float*>(staging_in_.ensure((size_t)N * C * H * W * 4, device_));
+        ingest_src_ = static_cast<float*>(staging_in_.ensure((size_t)N * C * H * W * 4, device_));
         // A few-channel image that feeds one fp16 convolution is stored as NHWC4 rows with zero
         // padding along W when that lets the tensor-core kernel fold the kw taps into K.
         bool padded = false;
@@ -414,12 +426,12 @@ void fused_plan::build(int N, int C, int H, int W) {
         const float s = in.i8_scale;
         if (padded) {
             add_step("ingest " + in.name, [=](cudaStream_t st) {
-                exb_check(exb_nchw_f32_to_nhwc_padded(ctx, stage, dst, EXB_F16, N, C, H, W, cs, w_pad, w_pitch, 1.f, 1, st),
+                exb_check(exb_nchw_f32_to_nhwc_padded(ctx, this->ingest_src_, dst, EXB_F16, N, C, H, W, cs, w_pad, w_pitch, 1.f, 1, st),
                           "exb_nchw_f32_to_nhwc_padded");
             });
         } else {
             add_step("ingest " + in.name, [=](cudaStream_t st) {
-                exb_check(exb_nchw_f32_to_nhwc(ctx, stage, dst, direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs,
+                exb_check(exb_nchw_f32_to_nhwc(ctx, this->ingest_src_, dst, direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs,
                                                direct_i8 ? s : 1.f, 1, st),
                           "exb_nchw_f32_to_nhwc");
             });
@@ -691,6 +703,7 @@ void fused_plan::run(const float* host_input, bool use_graph, bool profile, std:
     CUDA_CHECK(cudaSetDevice(device_));
     const size_t in_bytes = (size_t)N_ * C_ * H_ * W_ * 4;
     CUDA_CHECK(cudaMemcpyAsync(staging_in_.p, host_input, in_bytes, cudaMemcpyHostToDevice, stream_));
+    ingest_src_ = static_cast<const float*>(staging_in_.p);
     launches_ = 0;
     for (auto& s : steps_) launches_ += s.launches;
     if (profile) {
@@ -718,20 +731,7 @@ void fused_plan::run(const float* host_input, bool use_graph, bool profile, std:
         for (auto& e : evs) cudaEventDestroy(e);
     } else {
         CUDA_CHECK(cudaEventRecord(ev0_, stream_));
-        if (use_graph && warmed_) {   // the first forward runs eagerly, the second one captures
-            if (!graph_exec_) {
-                cudaGraph_t graph = nullptr;
-                CUDA_CHECK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
-                for (auto& s : steps_) s.run(stream_);
-                CUDA_CHECK(cudaStreamEndCapture(stream_, &graph));
-                CUDA_CHECK(cudaGraphInstantiate(&graph_exec_, graph, 0));
-                cudaGraphDestroy(graph);
-            }
-            CUDA_CHECK(cudaGraphLaunch(graph_exec_, stream_));
-        } else {
-            for (auto& s : steps_) s.run(stream_);
-            warmed_ = true;
-        }
+        launch_body(use_graph);
         CUDA_CHECK(cudaEventRecord(ev1_, stream_));
     }
     for (auto& kv : host_out_) {
@@ -752,32 +752,92 @@ void fused_plan::run(const float* host_input, bool use_graph, bool profile, std:
     exb_check(exb_ctx_sync_check(ctx_, stream_), "fused forward");
 }
 
+// The ingest step reads `ingest_src_` when it is launched and is therefore launched eagerly; the rest
+// of the plan runs eagerly the first time and as one CUDA graph afterwards.
+void fused_plan::launch_body(bool use_graph) {
+    steps_[0].run(stream_);
+    if (use_graph && warmed_ && steps_.size() > 1) {
+        if (!graph_exec_) {
+            cudaGraph_t graph = nullptr;
+            CUDA_CHECK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+            for (size_t i = 1; i < steps_.size(); ++i) steps_[i].run(stream_);
+            CUDA_CHECK(cudaStreamEndCapture(stream_, &graph));
+            CUDA_CHECK(cudaGraphInstantiate(&graph_exec_, graph, 0));
+            cudaGraphDestroy(graph);
+        }
+        CUDA_CHECK(cudaGraphLaunch(graph_exec_, stream_));
+    } else {
+        for (size_t i = 1; i < steps_.size(); ++i) steps_[i].run(stream_);
+        warmed_ = true;
+    }
+}
+
 double fused_plan::run_resident(int iters, bool use_graph) {
     if (!built_) return -1.0;
     CUDA_CHECK(cudaSetDevice(device_));
-    if (use_graph && !graph_exec_) {
-        cudaGraph_t graph = nullptr;
-        for (auto& s : steps_) s.run(stream_);   // make sure every kernel has run eagerly once
-        CUDA_CHECK(cudaStreamSynchronize(stream_));
-        CUDA_CHECK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
-        for (auto& s : steps_) s.run(stream_);
-        CUDA_CHECK(cudaStreamEndCapture(stream_, &graph));
-        CUDA_CHECK(cudaGraphInstantiate(&graph_exec_, graph, 0));
-        cudaGraphDestroy(graph);
-        warmed_ = true;
-    }
+    ingest_src_ = static_cast<const float*>(staging_in_.p);
+    if (!warmed_) launch_body(false);      // make sure every kernel has run eagerly once
     CUDA_CHECK(cudaStreamSynchronize(stream_));
     CUDA_CHECK(cudaEventRecord(ev0_, stream_));
-    for (int i = 0; i < iters; ++i) {
-        if (use_graph) CUDA_CHECK(cudaGraphLaunch(graph_exec_, stream_));
-        else for (auto& s : steps_) s.run(stream_);
-    }
+    for (int i = 0; i < iters; ++i) launch_body(use_graph);
     CUDA_CHECK(cudaEventRecord(ev1_, stream_));
     CUDA_CHECK(cudaStreamSynchronize(stream_));
     float ms = 0;
     cudaEventElapsedTime(&ms, ev0_, ev1_);
     exb_check(exb_ctx_sync_check(ctx_, stream_), "resident run");
     return ms;
+}
+
+void fused_plan::run_chunked(const float* host_input, int k, bool use_graph) {
+    CUDA_CHECK(cudaSetDevice(device_));
+    CHECK(built_ && k >= 1);
+    const size_t chunk_elems = (size_t)N_ * C_ * H_ * W_;
+    float* stage = static_cast<float*>(chunk_stage_.ensure(chunk_elems * 4 * k, device_));
+    if (!copy_stream_) CUDA_CHECK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
+    while ((int)copied_.size() < k) {
+        cudaEvent_t e;
+        CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        copied_.push_back(e);
+    }
+    for (auto& kv : host_out_) {
+        auto& t = chunk_out_[kv.first];
+        const std::vector<int> shp = kv.second->data_shape();
+        if (!t || t->num() != shp[0] * k)
+            t = std::shared_ptr<memory::tensor<float>>(
+                new memory::tensor<float>(std::vector<int>{shp[0] * k, shp[1], shp[2], shp[3]}, device_, memory::NCHW, nullptr));
+    }
+    launches_ = 0;
+    for (auto& s : steps_) launches_ += s.launches;
+    launches_ *= k;
+    // every copy is queued at once on its own stream; compute of chunk c waits for copy c only
+    for (int c = 0; c < k; ++c) {
+        CUDA_CHECK(cudaMemcpyAsync(stage + c * chunk_elems, host_input + c * chunk_elems, chunk_elems * 4,
+                                   cudaMemcpyHostToDevice, copy_stream_));
+        CUDA_CHECK(cudaEventRecord(copied_[c], copy_stream_));
+    }
+    CUDA_CHECK(cudaEventRecord(ev0_, stream_));
+    for (int c = 0; c < k; ++c) {
+        CUDA_CHECK(cudaStreamWaitEvent(stream_, copied_[c], 0));
+        ingest_src_ = stage + c * chunk_elems;
+        launch_body(use_graph);
+        for (auto& kv : host_out_) {
+            fmap_info& f = fmaps_[root(index_[kv.first])];
+            const size_t per = (size_t)f.N * f.C * f.H * f.W;
+            float* dst = chunk_out_[kv.first]->mutable_cpu_data() + c * per;
+            if (f.f32_pitch)
+                CUDA_CHECK(cudaMemcpy2DAsync(dst, (size_t)f.C * 4, f.f32->p, (size_t)f.f32_pitch * 4, (size_t)f.C * 4, f.N,
+                                             cudaMemcpyDeviceToHost, stream_));
+            else
+                CUDA_CHECK(cudaMemcpyAsync(dst, f.f32->p, per * 4, cudaMemcpyDeviceToHost, stream_));
+        }
+    }
+    CUDA_CHECK(cudaEventRecord(ev1_, stream_));
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+    CUDA_CHECK(cudaStreamSynchronize(copy_stream_));
+    float ms = 0;
+    cudaEventElapsedTime(&ms, ev0_, ev1_);
+    device_ms_ = ms;
+    exb_check(exb_ctx_sync_check(ctx_, stream_), "chunked forward");
 }
 
 std::shared_ptr<memory::tensor<float>> fused_plan::fetch(const std::string& name) {
@@ -889,6 +949,7 @@ public:
         if (input_names_.empty()) LOG(FATAL) << "the graph has no input feature map";
     }
     ~impl() {
+        chunk_plan_.reset();
         plan_.reset();
         if (ctx_) exb_ctx_destroy(ctx_);
     }
@@ -923,6 +984,9 @@ public:
     int weights_mem_cost_ = 0;
     bool profile_ = false, fusion_ = true, graph_ = true;
     bool used_fused_ = false;
+    int h2d_chunks_ = 1;
+    bool used_chunked_ = false;
+    std::unique_ptr<fused_plan> chunk_plan_;
     exb_ctx* ctx_ = nullptr;
     std::unique_ptr<fused_plan> plan_;
     std::vector<trace_event> trace_;
@@ -995,6 +1059,19 @@ pipeline<float>::result_map pipeline<float>::impl::forward_gpu(const std::shared
         if (why.empty()) {
             if (input->order() == memory::NHWC) input->convert_order();
             const int N = input->num(), C = input->channels(), H = input->height(), W = input->width();
+            used_chunked_ = false;
+            if (h2d_chunks_ > 1 && !profile_ && N % h2d_chunks_ == 0) {
+                if (!chunk_plan_)
+                    chunk_plan_.reset(new fused_plan(op_params_, operations_, input_names_, output_names_, device_));
+                const int nc = N / h2d_chunks_;
+                if (!chunk_plan_->built_for(nc, C, H, W)) chunk_plan_->build(nc, C, H, W);
+                chunk_plan_->run_chunked(input->cpu_data(), h2d_chunks_, graph_);
+                launches_ = chunk_plan_->launches();
+                device_ms_ = chunk_plan_->device_ms();
+                used_fused_ = true;
+                used_chunked_ = true;
+                return chunk_plan_->chunk_out_;
+            }
             if (!plan_->built_for(N, C, H, W)) plan_->build(N, C, H, W);
             plan_->run(input->cpu_data(), graph_, profile_, &trace_);
             launches_ = plan_->launches();
@@ -1016,6 +1093,11 @@ std::shared_ptr<memory::tensor<Dtype>> pipeline<Dtype>::impl::get_featmap(std::s
 }
 template <>
 std::shared_ptr<memory::tensor<float>> pipeline<float>::impl::get_featmap(std::string_view name) {
+    if (used_fused_ && used_chunked_ && chunk_plan_) {
+        auto o = chunk_plan_->chunk_out_.find(std::string(name));
+        if (o != chunk_plan_->chunk_out_.end()) return o->second;
+        return chunk_plan_->fetch(std::string(name));
+    }
     if (used_fused_ && plan_) return plan_->fetch(std::string(name));
     auto it = featmap_index_.find(std::string(name));
     if (it == featmap_index_.end()) return nullptr;
@@ -1048,9 +1130,10 @@ template <typename Dtype> void pipeline<Dtype>::enable_profiler() { impl_->profi
 template <typename Dtype> void pipeline<Dtype>::disable_profiler() { impl_->profile_ = false; }
 template <typename Dtype> void pipeline<Dtype>::set_fusion(bool on) { impl_->fusion_ = on; }
 template <typename Dtype> void pipeline<Dtype>::set_cuda_graph(bool on) { impl_->graph_ = on; }
+template <typename Dtype> void pipeline<Dtype>::set_h2d_chunks(int k) { impl_->h2d_chunks_ = k < 1 ? 1 : k; }
 template <typename Dtype> int pipeline<Dtype>::launches_last_forward() const { return impl_->launches_; }
 template <typename Dtype> double pipeline<Dtype>::run_resident(int iters) {
-    if (!impl_->plan_ || !impl_->used_fused_) return -1.0;
+    if (!impl_->plan_ || !impl_->used_fused_ || !impl_->plan_->built()) return -1.0;
     return impl_->plan_->run_resident(iters, impl_->graph_);
 }
 template <typename Dtype> int pipeline<Dtype>::trace_size() const { return (int)impl_->trace_.size(); }

@@ -40,6 +40,10 @@ public:
     // Extras of this implementation.
     void set_fusion(bool on);            // default on for pipeline<float> on a GPU
     void set_cuda_graph(bool on);        // replay the fused plan as a CUDA graph (default on)
+    // forward() of a batch divisible by k runs as k sub-batches: sub-batch c+1 is copied to the device
+    // while sub-batch c is computed (default 1 = whole batch at once).  Only the pipeline outputs
+    // cover the whole batch afterwards; get_featmap() of an inner map sees the last sub-batch.
+    void set_h2d_chunks(int k);
     // Re-run the fused plan `iters` times on the input already resident on the device (the last
     // forward's), no host<->device copies; returns the device time in ms between CUDA events on the
     // plan's stream, or a negative value when there is no fused plan yet.
