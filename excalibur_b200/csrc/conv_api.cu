@@ -47,6 +47,10 @@ int resolve(const exb_conv_desc* d, ConvGeom& g) {
                 "bad input row padding (x_w_pad %d, x_w_pitch %d, W %d)", d->x_w_pad, d->x_w_pitch, d->W);
     g.w_pitch = d->x_w_pitch ? d->x_w_pitch : d->W;
     g.w_pad = d->x_w_pitch ? d->x_w_pad : 0;
+    EXB_REQUIRE(d->fuse_pool == 0 || d->fuse_pool == 1, "fuse_pool must be 0 or 1");
+    g.pool = d->fuse_pool;
+    g.PH = (g.OH - 1) / 2 + 1;     // (OH + 2*1 - 3) / 2 + 1, floor mode
+    g.PW = (g.OW - 1) / 2 + 1;
     return EXB_OK;
 }
 
@@ -97,9 +101,15 @@ extern "C" int exb_conv_out_dims(const exb_conv_desc* d, int* OH, int* OW) {
     ConvGeom g;
     if (int rc = resolve(d, g)) return rc;
     EXB_REQUIRE(OH && OW, "null output pointer");
-    *OH = g.OH;
-    *OW = g.OW;
+    *OH = g.pool ? g.PH : g.OH;
+    *OW = g.pool ? g.PW : g.OW;
     return EXB_OK;
+}
+
+extern "C" int exb_conv2d_pool_fusable(const exb_conv_desc* d) {
+    ConvGeom g;
+    if (int rc = resolve(d, g)) return rc;
+    return (d->impl != 1 && conv_tc_eligible(g) && conv_tc_pool_fusable(g)) ? 1 : 0;
 }
 
 extern "C" int exb_conv2d_uses_tensor_cores(const exb_conv_desc* d) {
@@ -185,6 +195,8 @@ extern "C" int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* 
     EXB_REQUIRE(!g.has_res || (residual && aligned16(residual)), "exb_conv2d_fwd: null or misaligned residual");
     EXB_REQUIRE(g.out2_dtype == -1 || (y2 && aligned16(y2)), "exb_conv2d_fwd: null or misaligned second output");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (g.pool && !(d->impl != 1 && conv_tc_eligible(g) && conv_tc_pool_fusable(g)))
+        return fail(EXB_ERR_UNSUPPORTED, "fuse_pool is not available for this convolution (see exb_conv2d_pool_fusable)");
     if (d->impl != 1 && conv_tc_eligible(g)) return conv_tc_launch(ctx, g, x, w, residual, y, y2, st);
     return conv_direct_launch(ctx, g, x, w, residual, y, y2, st);
 }

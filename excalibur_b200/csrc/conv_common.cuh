@@ -26,6 +26,8 @@ struct ConvGeom {
     int in_dtype, out_dtype, out2_dtype, has_res, act;
     float out_scale, out2_scale;
     int w_pitch, w_pad;   // physical pixels per input row and zero pixels left of pixel 0 (dense: W, 0)
+    int pool;             // 1: 3x3/2 pad-1 max pooling fused into the epilogue; y is [N][PH][PW][cout_stride]
+    int PH, PW;
 };
 
 // "Folded" K layout for convolutions with very few input channels (a stem): one K row of an
@@ -159,5 +161,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
                    const void* residual, void* y, void* y2, cudaStream_t st);
 // True when the tcgen05 kernel can run this geometry.
 bool conv_tc_eligible(const ConvGeom& g);
+// True when the tcgen05 kernel can also apply the 3x3/2 max pooling in its epilogue.
+bool conv_tc_pool_fusable(const ConvGeom& g);
 
 }  // namespace exb

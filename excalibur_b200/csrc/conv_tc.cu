@@ -70,6 +70,13 @@ struct ConvTcParams {
     int patch_rows;    // input rows per tile
     int patch_pitch;   // bytes per patch row in shared memory
     const void* w_global;   // packed weights (patch mode copies them into core-matrix layout)
+    // Tile origins: first output column / row of tile index i is i * step + org (step = TW / TH and
+    // org = 0 unless tiles overlap).
+    int step_w, step_h, org;
+    // Fused 3x3/2 pad-1 max pooling (patch mode, BN = 64): an 8 x 16 tile of the convolution output
+    // starts at (6*tx - 1, 14*ty - 1), so it holds every input of the 3 x 7 pooled outputs that
+    // start at (3*tx, 7*ty); neighbouring tiles overlap by two rows / columns, which are recomputed.
+    int pool, PH, PW;
 };
 
 struct TileCoord {
@@ -80,9 +87,9 @@ __device__ __forceinline__ TileCoord decode_tile(const ConvTcParams& p, int t) {
     TileCoord c;
     c.ntile = t % p.n_tiles;
     int m = t / p.n_tiles;
-    c.ow0 = (m % p.tiles_w) * p.TW;
+    c.ow0 = (m % p.tiles_w) * p.step_w + p.org;
     m /= p.tiles_w;
-    c.oh0 = (m % p.tiles_h) * p.TH;
+    c.oh0 = (m % p.tiles_h) * p.step_h + p.org;
     c.n0 = (m / p.tiles_h) * p.TN;
     return c;
 }
@@ -96,7 +103,10 @@ __device__ __forceinline__ TileCoord decode_tile(const ConvTcParams& p, int t) {
 //                 the single MMA-issuing thread rather than tensor throughput: two CTAs give two
 //                 issuers (and two producers) per SM; each takes half the shared memory and at
 //                 most 256 TMEM columns.
-template <bool kInt8, int kDbg, int kEpiWarps>
+//
+// kPool: the fused max-pooling epilogue (its own instantiation so that the plain kernels keep their
+// register allocation).
+template <bool kInt8, int kDbg, int kEpiWarps, bool kPool = false>
 __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps == 8 ? 2 : 1)
     conv_tc_kernel(const __grid_constant__ ConvTcParams p) {
     constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
@@ -108,6 +118,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
     __shared__ __align__(8) uint64_t bres_bar;
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
+    __shared__ int pool_fail[kMaxAccBufs];
 
     // Operand ring, 1024-byte aligned (the widest swizzle atom).
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -118,6 +129,8 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
     float* s_bias = s_scale + p.n_tiles * p.BN;
     // Per K iteration (tap, channel block): TMA coordinates that do not depend on the tile.
     int4* k_tab = reinterpret_cast<int4*>(s_bias + p.n_tiles * p.BN);
+    // Pool mode: one 128-pixel x 64-channel fp16 staging tile per epilogue group.
+    uint8_t* pool_stage = reinterpret_cast<uint8_t*>(k_tab + (p.fold ? p.kh : p.kh * p.kw * p.cblks));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -126,6 +139,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        for (int i = 0; i < kMaxAccBufs; ++i) pool_fail[i] = 0;
         for (int s = 0; s < p.stages; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
             ptx::mbar_init(&empty_bar[s], 1);
@@ -400,6 +414,100 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         uint32_t acc_phase = 0;
         bool ok = true;
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * p.BN);
+        if constexpr (kPool) {
+            // Convolution tile -> ReLU -> fp16 -> shared memory (16-byte units of a pixel row XOR-ed
+            // with the row index so that neither phase has bank conflicts) -> 3x3/2 max -> global.
+            // The group's four warps meet at a named barrier twice per tile; a warp whose bounded
+            // wait ran out still arrives, and the whole group leaves together afterwards.
+            uint8_t* stg = pool_stage + grp * (kTileM * 128);
+            volatile int* failed = &pool_fail[grp];
+            for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles; t += p.acc_bufs * gridDim.x) {
+                const TileCoord tc = decode_tile(p, t);
+                const int ow = tc.ow0 + tw, oh = tc.oh0 + th;
+                const bool inside = ow >= 0 && ow < p.OW && oh >= 0 && oh < p.OH;
+                if (!ptx::mbar_wait_bounded_warp(&tfull_bar[grp], acc_phase, &abort_flag, kMaxSpins)) {
+                    if (lane == 0) *failed = 1;
+                } else {
+                    ptx::tc_fence_after_sync();
+#pragma unroll
+                    for (int chunk = 0; chunk < 4; ++chunk) {
+                        uint32_t raw[16];
+                        ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
+                        ptx::tmem_ld_wait();
+                        float v[16];
+                        const float4* sc = reinterpret_cast<const float4*>(s_scale + chunk * 16);
+                        const float4* bi = reinterpret_cast<const float4*>(s_bias + chunk * 16);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float4 s4 = sc[i], b4 = bi[i];
+                            v[4 * i + 0] = epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x);
+                            v[4 * i + 1] = epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y);
+                            v[4 * i + 2] = epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z);
+                            v[4 * i + 3] = epi_value<kInt8>(raw[4 * i + 3], s4.w, b4.w);
+                        }
+                        act_vec16(v, p.e.act);
+                        uint32_t h[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            // positions outside the map never win: activated values are >= 0
+                            const __half2 hv = inside ? __floats2half2_rn(v[2 * i], v[2 * i + 1]) : __floats2half2_rn(0.f, 0.f);
+                            h[i] = *reinterpret_cast<const uint32_t*>(&hv);
+                        }
+                        uint8_t* dst = stg + row * 128;
+                        *reinterpret_cast<uint4*>(dst + (((2 * chunk) ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4*>(dst + (((2 * chunk + 1) ^ (row & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                    }
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&tempty_bar[grp]);   // the accumulator is free again
+                }
+                acc_phase ^= 1u;
+                if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+                else asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (*failed) {
+                    ok = false;
+                    break;
+                }
+                const int ph0 = (tc.oh0 + 1) >> 1, pw0 = (tc.ow0 + 1) >> 1;
+                for (int item = row; item < 21 * 8; item += kTileM) {
+                    const int pp = item >> 3, u = item & 7;
+                    const int pr = pp / 3, pc = pp - 3 * pr;
+                    const int ph = ph0 + pr, pw = pw0 + pc;
+                    if (ph >= p.PH || pw >= p.PW) continue;
+                    __half2 m[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) m[i] = __floats2half2_rn(0.f, 0.f);
+#pragma unroll
+                    for (int dr = 0; dr < 3; ++dr)
+#pragma unroll
+                        for (int dc = 0; dc < 3; ++dc) {
+                            const int r = (2 * pr + dr) * 8 + 2 * pc + dc;
+                            const uint4 tv = *reinterpret_cast<const uint4*>(stg + r * 128 + ((u ^ (r & 7)) << 4));
+                            const __half2* th2 = reinterpret_cast<const __half2*>(&tv);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) m[i] = __hmax2(m[i], th2[i]);
+                        }
+                    const int64_t off = (((int64_t)tc.n0 * p.PH + ph) * p.PW + pw) * p.e.cout_stride + u * 8;
+                    uint4 o;
+                    o.x = *reinterpret_cast<const uint32_t*>(&m[0]);
+                    o.y = *reinterpret_cast<const uint32_t*>(&m[1]);
+                    o.z = *reinterpret_cast<const uint32_t*>(&m[2]);
+                    o.w = *reinterpret_cast<const uint32_t*>(&m[3]);
+                    *reinterpret_cast<uint4*>(static_cast<__half*>(p.e.y) + off) = o;
+                    if (p.e.out2_dtype == EXB_I8) {
+                        const float2 f0 = __half22float2(m[0]), f1 = __half22float2(m[1]);
+                        const float2 f2 = __half22float2(m[2]), f3 = __half22float2(m[3]);
+                        uint2 qv;
+                        qv.x = quant_pack4(f0.x, f0.y, f1.x, f1.y, p.e.out2_scale);
+                        qv.y = quant_pack4(f2.x, f2.y, f3.x, f3.y, p.e.out2_scale);
+                        *reinterpret_cast<uint2*>(static_cast<int8_t*>(p.e.y2) + off) = qv;
+                    }
+                }
+                // staging may be overwritten after this one
+                if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+                else asm volatile("bar.sync 2, 128;" ::: "memory");
+            }
+        } else
         for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles && ok; t += p.acc_bufs * gridDim.x) {
             const TileCoord tc = decode_tile(p, t);
             const int ow = tc.ow0 + tw, oh = tc.oh0 + th, n = tc.n0 + tn;
@@ -542,6 +650,14 @@ void choose_tile(int N, int OH, int OW, int& TW, int& TH, int& TN) {
 
 }  // namespace
 
+bool conv_tc_pool_fusable(const ConvGeom& g) {
+    const FoldPlan fold = conv_fold_plan(g);
+    const int cout_pad = (g.cout_stride + 15) / 16 * 16;
+    return fold.on && g.in_dtype == EXB_F16 && g.cin_stride * 2 == 8 && g.sw == 2 && g.sh == 2 && fold.F == 8 && g.kh <= 16 &&
+           cout_pad == 64 && g.cout_stride == 64 && g.out_dtype == EXB_F16 && (g.out2_dtype == -1 || g.out2_dtype == EXB_I8) &&
+           !g.has_res && (g.act == EXB_ACT_RELU || g.act == EXB_ACT_RELU6) && g.group == 1;
+}
+
 bool conv_tc_eligible(const ConvGeom& g) {
     const int es = g.in_dtype == EXB_I8 ? 1 : 2;
     if (g.group != 1) return false;
@@ -565,6 +681,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.tiles_w = (g.OW + p.TW - 1) / p.TW;
     p.tiles_h = (g.OH + p.TH - 1) / p.TH;
     p.tiles_nb = (g.N + p.TN - 1) / p.TN;
+    p.step_w = p.TW; p.step_h = p.TH; p.org = 0;
     p.n_tiles = (w->cout_pad + 255) / 256;
     p.BN = round_up((w->cout_pad + p.n_tiles - 1) / p.n_tiles, 16);
     // Two CTAs per SM when the N tile is narrow (see the kernel's comment).
@@ -601,13 +718,24 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         p.patch_pitch = (2 * p.TW + 8) * 8;   // 2*TW + 6 pixels needed, rounded to 24
         p.a_bytes = round_up(p.patch_rows * p.patch_pitch, 128);
         p.w_global = w->d_w;
+        p.step_w = p.TW; p.step_h = p.TH;
+        if (g.pool) {
+            p.pool = 1;
+            p.PH = g.PH; p.PW = g.PW;
+            p.step_w = p.TW - 2; p.step_h = p.TH - 2; p.org = -1;
+            p.tiles_w = (g.PW + 2) / 3;      // 3 x 7 pooled outputs per tile
+            p.tiles_h = (g.PH + 6) / 7;
+        }
     }
+    if (g.pool && !(patch && two && p.BN == 64 && conv_tc_pool_fusable(g)))
+        return fail(EXB_ERR_UNSUPPORTED, "fused pooling needs the patch-mode stem kernel with 64 output channels");
     p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
     const int ctas_per_sm = two ? 2 : 1;
     const int k_iters = fold.on ? g.kh : g.kh * g.kw * p.cblks;
     if ((int64_t)g.N * g.OH * g.OW >= (int64_t)1 << 31) return fail(EXB_ERR_UNSUPPORTED, "more than 2^31 output pixels");
     if ((int64_t)g.kh * w->kw_pack * w->cin_pad >= (1 << 28)) return fail(EXB_ERR_UNSUPPORTED, "reduction dimension too large");
-    const int epi_bytes = 2 * p.n_tiles * p.BN * (int)sizeof(float) + k_iters * (int)sizeof(int4);
+    const int epi_bytes = 2 * p.n_tiles * p.BN * (int)sizeof(float) + k_iters * (int)sizeof(int4) +
+                          (g.pool ? 2 * kTileM * 128 : 0);
     // static barriers + alignment slack + tables; two resident CTAs share the SM's 228 KB
     // (1 KB of which is reserved per CTA)
     int budget = (two ? (228 * 1024 / 2 - 1024) : ctx->smem_optin) - 2048 - epi_bytes;
@@ -722,6 +850,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     const size_t smem = (size_t)p.stages * p.kgroup * p.a_bytes + p.b_region + 1024 + epi_bytes;
     auto kern = int8 ? (two ? conv_tc_kernel<true, 0, 8> : conv_tc_kernel<true, 0, 16>)
                      : (two ? conv_tc_kernel<false, 0, 8> : conv_tc_kernel<false, 0, 16>);
+    if (p.pool) kern = conv_tc_kernel<false, 0, 8, true>;
 #ifdef EXB_CONV_EXPERIMENTS
     if (const char* e = getenv("EXB_CONV_DBG")) {
         switch (atoi(e)) {

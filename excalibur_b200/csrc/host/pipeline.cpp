@@ -264,6 +264,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         int conv = -1;          // leading op
         int residual = -1;      // root featmap added in the epilogue
         int act = EXB_ACT_NONE;
+        int pool = -1;          // 3x3/2 max pooling op applied in the conv epilogue
         int out = -1;           // root featmap the group finally produces
         int exec_at = -1;       // index of the last absorbed op
     };
@@ -348,6 +349,32 @@ void fused_plan::build(int N, int C, int H, int W) {
                 absorbed[k] = 1;
                 g.out = root(out_ids[k][0]);
                 g.exec_at = k;
+            }
+        }
+        // Stem conv + ReLU followed by the classic 3x3/2 pad-1 max pooling: pooled in the epilogue.
+        if (t == "convolution" && g.residual < 0 && (g.act == EXB_ACT_RELU || g.act == EXB_ACT_RELU6) &&
+            root(in_ids[i][0]) == root(fid(inputs_[0])) && C <= 4 && !conv->is_int8() && conv->group_ == 1 &&
+            conv->in_channels() == C && (j = sole_consumer(g.out)) >= 0 && !absorbed[j] &&
+            lower_type(params_[j]) == "pooling" && consumers[root(in_ids[i][0])].size() == 1) {
+            auto* pl = dynamic_cast<operation_pooling<float>*>(ops_[j].get());
+            const bool classic = pl && pl->type_ == 0 && !pl->global_pooling_ && pl->kernel_size_w_ == 3 &&
+                                 pl->kernel_size_h_ == 3 && pl->stride_w_ == 2 && pl->stride_h_ == 2 && pl->pad_left_ == 1 &&
+                                 pl->pad_right_ == 1 && pl->pad_top_ == 1 && pl->pad_bottom_ == 1 && pl->pad_mode_ == 1;
+            if (classic) {
+                exb_conv_desc d = conv->base_desc(N, H, W);
+                d.in_dtype = EXB_F16;
+                d.out_dtype = EXB_F16;
+                d.cin_stride = 4;
+                d.x_w_pad = 4;
+                d.x_w_pitch = round_up(W + 4 + 8, 8);
+                d.act = g.act;
+                d.cout_stride = round_up(conv->output_channel_, conv->output_channel_ > 16 ? 32 : 16);
+                if (exb_conv2d_pool_fusable(&d) == 1) {
+                    g.pool = j;
+                    absorbed[j] = 1;
+                    g.out = root(out_ids[j][0]);
+                    g.exec_at = j;
+                }
             }
         }
         groups[i] = g;
@@ -474,6 +501,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         d.x_w_pitch = x.w_pitch;
         d.x_w_pad = x.w_pad;
         d.act = g.act;
+        d.fuse_pool = g.pool >= 0 ? 1 : 0;
         int OH, OW;
         exb_check(exb_conv_out_dims(&d, &OH, &OW), "exb_conv_out_dims");
         set_shape(y, x.N, conv->output_channel_, OH, OW);

@@ -25,7 +25,7 @@ LAYERS = {
     "s4_conv1a": (256, 14, 512, 3, 2, 1, "conv1"), "s4_proj": (256, 14, 512, 1, 2, 0, "proj"),
     "s4_conv1": (512, 7, 512, 3, 1, 1, "conv1"), "s4_conv2": (512, 7, 512, 3, 1, 1, "conv2"),
 }
-EXTRA = ("stem", "pool1")
+EXTRA = ("stem", "pool1", "stem_pool")
 
 
 def _timeit(torch, fn, iters, warmup):
@@ -82,6 +82,18 @@ def main(argv=None):
             ms = _timeit(torch, lambda: capi.conv2d(ctx, d, x, wp, None, y, None), args.iters, args.warmup)
             flop = 2.0 * N * 112 * 112 * 64 * 147
             byts = x.numel() * 2 + y.numel() * 2
+        elif name == "stem_pool":     # stem + ReLU + 3x3/2 max pool in one kernel, fp16 + int8 pooled outputs
+            pitch = (224 + 4 + 8 + 7) // 8 * 8
+            d = capi.make_conv_desc(N, 224, 224, 3, 64, 7, 2, 3, capi.EXB_F16, capi.EXB_F16, capi.EXB_I8, act=capi.ACT_RELU,
+                                    out2_scale=10.0, cin_stride=4, x_w_pitch=pitch, x_w_pad=4, fuse_pool=1)
+            wp = capi.ConvWeights(ctx, d, rng.standard_normal((64, 3, 7, 7)).astype(np.float32), np.zeros(64, np.float32))
+            x = torch.zeros((N, 224, pitch, 4), device="cuda", dtype=torch.float16)
+            x[:, :, 4:228, :3] = torch.rand((N, 224, 224, 3), device="cuda").to(torch.float16)
+            y = torch.empty((N, 56, 56, 64), device="cuda", dtype=torch.float16)
+            y2 = torch.empty((N, 56, 56, 64), device="cuda", dtype=torch.int8)
+            ms = _timeit(torch, lambda: capi.conv2d(ctx, d, x, wp, None, y, y2), args.iters, args.warmup)
+            flop = 2.0 * N * 112 * 112 * 64 * 147
+            byts = x.numel() * 2 + y.numel() * 3
         elif name == "pool1":
             x = torch.randn((N, 112, 112, 64), device="cuda", dtype=torch.float16)
             d = capi.make_pool_desc(N, 112, 112, 64, 0, 3, 2, 1, dtype=capi.EXB_F16, out2_dtype=capi.EXB_I8, out2_scale=10.0)

@@ -136,10 +136,17 @@ typedef struct exb_conv_desc {
      * the tensor-core kernel take kw taps x cin channels as ONE contiguous K row per output pixel. */
     int32_t x_w_pitch;
     int32_t x_w_pad;
+    /* 1: a 3x3 stride-2 pad-1 max pooling (floor output size, padding ignored: the reference's
+     * Pooling with keys 0=0 1=3 2=2 3=1) is applied to the activated convolution output inside the
+     * convolution's epilogue; y / y2 then hold the POOLED map [N][PH][PW][cout_stride] and the
+     * convolution output itself is never written.  Only for descriptors for which
+     * exb_conv2d_pool_fusable() returns 1; 0 = plain convolution. */
+    int32_t fuse_pool;
 } exb_conv_desc;
 
 /* Output spatial size: (in + pad_a + pad_b - k) / stride + 1
  * (src/Excalibur/operation_convolution.cpp:270-273). */
+/* With fuse_pool = 1 these are the dimensions of the pooled map. */
 EXB_API int exb_conv_out_dims(const exb_conv_desc* d, int* OH, int* OW);
 
 /* Weight pre-transform, the analogue of the reference's *_tr_kernel repacks done once in
@@ -165,6 +172,10 @@ EXB_API int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* x,
 /* Which kernel exb_conv2d_fwd would run for this descriptor: 1 = tcgen05 implicit GEMM,
  * 0 = direct kernel; negative = error. */
 EXB_API int exb_conv2d_uses_tensor_cores(const exb_conv_desc* d);
+/* 1 when exb_conv2d_fwd can run this descriptor with fuse_pool = 1 (a few-channel stride-2 fp16
+ * stem on padded NHWC4 rows with 64 output channels, ReLU or ReLU6, fp16 output and an optional
+ * int8 copy, no residual), else 0; negative = error.  The descriptor's own fuse_pool is ignored. */
+EXB_API int exb_conv2d_pool_fusable(const exb_conv_desc* d);
 
 /* ---------------------------------------------------------------------------------------
  * Depthwise convolution forward.  Stands in for operation_convolutiondepthwise::forward_*

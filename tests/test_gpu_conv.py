@@ -266,3 +266,59 @@ def test_stem_conv_folded_rows(ctx, case, impl):
     y, _ = capi.conv2d(ctx, d, xp, wp)
     ctx.sync_check()
     np.testing.assert_allclose(to_nchw(host(y)), ref, rtol=1e-4, atol=1e-4)
+
+
+POOL_STEM_CASES = [
+    # N, H, W, k, pad
+    (2, 64, 64, 7, 3),
+    (3, 37, 41, 7, 3),      # odd conv output (19 x 21) -> pooled 10 x 11, ragged last tiles
+    (2, 48, 40, 6, 2),      # YOLO-style 6x6/2 stem
+    (1, 224, 224, 7, 3),
+    (2, 30, 26, 5, 2),
+]
+
+
+@pytest.mark.parametrize("case", POOL_STEM_CASES)
+@pytest.mark.parametrize("with_i8", [False, True], ids=["f16", "f16+i8"])
+def test_stem_conv_with_fused_max_pool(ctx, case, with_i8):
+    """Stem conv + ReLU + 3x3/2 pad-1 max pooling in one kernel equals conv -> fp16 -> pool of the
+    oracle (bit-exact given the conv's fp16 result: max of rounded values, then the int8 copy)."""
+    capi = _capi()
+    N, H, W, k, pad = case
+    r = rng(sum(case) + 7)
+    x = r.uniform(0, 1, (N, 3, H, W)).astype(np.float32)
+    w = f16_round(r.standard_normal((64, 3, k, k)) * np.sqrt(2.0 / (3 * k * k)))
+    b = (r.standard_normal(64) * 0.1).astype(np.float32)
+    w_pad = 4
+    w_pitch = (W + w_pad + 8 + 7) // 8 * 8
+    xp = capi.nchw_f32_to_nhwc_padded(ctx, dev(x), capi.EXB_F16, 4, w_pad, w_pitch)
+    q = 25.0
+    kw = dict(act=1, cin_stride=4, x_w_pitch=w_pitch, x_w_pad=w_pad)
+    d0 = capi.make_conv_desc(N, H, W, 3, 64, k, 2, pad, capi.EXB_F16, capi.EXB_F16, **kw)
+    d1 = capi.make_conv_desc(N, H, W, 3, 64, k, 2, pad, capi.EXB_F16, capi.EXB_F16,
+                             capi.EXB_I8 if with_i8 else -1, out2_scale=q, fuse_pool=1, **kw)
+    assert capi.lib().exb_conv2d_pool_fusable(d0) == 1
+    wp = capi.ConvWeights(ctx, d0, w, b)
+    y0, _ = capi.conv2d(ctx, d0, xp, wp)                     # the plain kernel's fp16 conv output
+    y1, y2 = capi.conv2d(ctx, d1, xp, wp)
+    ctx.sync_check()
+    conv16 = to_nchw(host(y0).astype(np.float32))
+    ref_conv = O.conv2d_f32(f16_round(x), w, b, 2, pad, act=1)
+    np.testing.assert_allclose(conv16, ref_conv, rtol=2e-3, atol=2e-3)
+    ref_pool = O.pool2d_f32(conv16, 0, 3, 2, 1)
+    got = to_nchw(host(y1).astype(np.float32))
+    assert got.shape == ref_pool.shape
+    np.testing.assert_array_equal(got, ref_pool)
+    if with_i8:
+        np.testing.assert_array_equal(to_nchw(host(y2).astype(np.float32)), O.requantize_rne(ref_pool, q))
+
+
+def test_fused_max_pool_is_refused_where_it_cannot_run(ctx):
+    capi = _capi()
+    d = capi.make_conv_desc(1, 16, 16, 32, 64, 3, 1, 1, capi.EXB_I8, capi.EXB_F16, act=1)
+    assert capi.lib().exb_conv2d_pool_fusable(d) == 0
+    d.fuse_pool = 1
+    w = capi.ConvWeights(ctx, d, np.zeros((64, 32, 3, 3), np.int8), np.zeros(64, np.float32), np.ones(64, np.float32), 1.0)
+    x = dev(np.zeros((1, 16, 16, 32), np.int8))
+    with pytest.raises(capi.ExbError):
+        capi.conv2d(ctx, d, x, w)
