@@ -51,6 +51,15 @@ int resolve(const exb_conv_desc* d, ConvGeom& g) {
     g.pool = d->fuse_pool;
     g.PH = (g.OH - 1) / 2 + 1;     // (OH + 2*1 - 3) / 2 + 1, floor mode
     g.PW = (g.OW - 1) / 2 + 1;
+    EXB_REQUIRE((d->in_planar == 0 || d->in_planar == 1) && (d->out_i8_planar == 0 || d->out_i8_planar == 1),
+                "in_planar / out_i8_planar must be 0 or 1");
+    g.in_planar = d->in_planar;
+    g.out_i8_planar = d->out_i8_planar;
+    if (g.out_i8_planar) {
+        EXB_REQUIRE(g.cout_stride % 16 == 0, "planar16 output needs cout_stride %% 16 == 0");
+        EXB_REQUIRE(g.out_dtype == EXB_I8 || g.out2_dtype == EXB_I8, "out_i8_planar without an int8 output");
+        EXB_REQUIRE(g.in_planar || g.pool, "out_i8_planar is available with in_planar = 1 or fuse_pool = 1 only");
+    }
     return EXB_OK;
 }
 
@@ -110,6 +119,12 @@ extern "C" int exb_conv2d_pool_fusable(const exb_conv_desc* d) {
     ConvGeom g;
     if (int rc = resolve(d, g)) return rc;
     return (d->impl != 1 && conv_tc_eligible(g) && conv_tc_pool_fusable(g)) ? 1 : 0;
+}
+
+extern "C" int exb_conv2d_accepts_planar_input(const exb_conv_desc* d) {
+    ConvGeom g;
+    if (int rc = resolve(d, g)) return rc;
+    return (d->impl != 1 && conv_tc_eligible(g) && conv_tc_halo_ok(nullptr, g)) ? 1 : 0;
 }
 
 extern "C" int exb_conv2d_uses_tensor_cores(const exb_conv_desc* d) {
@@ -197,6 +212,10 @@ extern "C" int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (g.pool && !(d->impl != 1 && conv_tc_eligible(g) && conv_tc_pool_fusable(g)))
         return fail(EXB_ERR_UNSUPPORTED, "fuse_pool is not available for this convolution (see exb_conv2d_pool_fusable)");
+    if ((g.in_planar || g.out_i8_planar) && !(d->impl != 1 && conv_tc_eligible(g)))
+        return fail(EXB_ERR_UNSUPPORTED, "planar16 tensors need the tensor-core kernel");
+    if (g.in_planar && !conv_tc_halo_ok(ctx, g))
+        return fail(EXB_ERR_UNSUPPORTED, "planar16 input is not available for this convolution (see exb_conv2d_accepts_planar_input)");
     if (d->impl != 1 && conv_tc_eligible(g)) return conv_tc_launch(ctx, g, x, w, residual, y, y2, st);
     return conv_direct_launch(ctx, g, x, w, residual, y, y2, st);
 }

@@ -28,6 +28,7 @@ struct ConvGeom {
     int w_pitch, w_pad;   // physical pixels per input row and zero pixels left of pixel 0 (dense: W, 0)
     int pool;             // 1: 3x3/2 pad-1 max pooling fused into the epilogue; y is [N][PH][PW][cout_stride]
     int PH, PW;
+    int in_planar, out_i8_planar;   // planar16 int8 input / int8 output (see exb_conv_desc)
 };
 
 // "Folded" K layout for convolutions with very few input channels (a stem): one K row of an
@@ -71,6 +72,7 @@ struct EpiParams {
     int out_dtype, out2_dtype, act;
     float out_scale, out2_scale;
     int cout_stride;
+    int i8_planar;   // the int8 output (y or y2) is planar16
 };
 
 // v = act(acc * scale + bias + residual)
@@ -163,5 +165,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
 bool conv_tc_eligible(const ConvGeom& g);
 // True when the tcgen05 kernel can also apply the 3x3/2 max pooling in its epilogue.
 bool conv_tc_pool_fusable(const ConvGeom& g);
+// True when the tcgen05 kernel can read a planar16 int8 input for this geometry (halo mode).
+bool conv_tc_halo_ok(const exb_ctx* ctx, const ConvGeom& g);
 
 }  // namespace exb

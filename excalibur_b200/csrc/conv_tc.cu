@@ -77,6 +77,17 @@ struct ConvTcParams {
     // starts at (6*tx - 1, 14*ty - 1), so it holds every input of the 3 x 7 pooled outputs that
     // start at (3*tx, 7*ty); neighbouring tiles overlap by two rows / columns, which are recomputed.
     int pool, PH, PW;
+    // "Halo" mode for 3x3 stride-1 pad-1 int8 convolutions on planar16 input
+    // ([N][C/16][H][W][16]): ONE 4-D TMA load brings the (TH+2) x (TW+2) halo patch of every
+    // 16-channel slice into un-swizzled shared memory as [slice][row][10 pixels x 16 bytes]; tap
+    // (r, s) of the implicit GEMM is the same patch read through a descriptor that starts
+    // (r*10 + s)*16 bytes in (8 consecutive pixels = one 128-byte core matrix, next tile row 160
+    // bytes on, next K chunk one slice plane on).  The weights stay resident in the canonical
+    // un-swizzled K-major layout.  Operand traffic from L2 falls from nine boxes to one.
+    int halo;
+    int halo_plane;   // bytes of one 16-channel slice of the patch
+    int cchunks;      // 16-channel slices of the input
+    int xflags;       // experiment switches (always 0 in the shipped build)
 };
 
 struct TileCoord {
@@ -106,7 +117,8 @@ __device__ __forceinline__ TileCoord decode_tile(const ConvTcParams& p, int t) {
 //
 // kPool: the fused max-pooling epilogue (its own instantiation so that the plain kernels keep their
 // register allocation).
-template <bool kInt8, int kDbg, int kEpiWarps, bool kPool = false>
+// kHalo: the planar16 halo-patch main loop, likewise its own instantiation.
+template <bool kInt8, int kDbg, int kEpiWarps, bool kPool = false, bool kHalo = false>
 __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps == 8 ? 2 : 1)
     conv_tc_kernel(const __grid_constant__ ConvTcParams p) {
     constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
@@ -191,6 +203,19 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         }
         ptx::fence_proxy_async();   // generic-proxy writes, read by the tensor core through the async proxy
     }
+    if constexpr (kHalo) {
+        // Weights [cout_pad][9 * cin_pad] bytes -> for 16-byte K chunk kc and output channel n:
+        // kc*(BN*16) + (n/8)*128 + (n%8)*16.
+        const uint4* src = static_cast<const uint4*>(p.w_global);
+        const int kchunks = 9 * p.cchunks;
+        const int total = p.BN * kchunks;
+        for (int i = threadIdx.x; i < total; i += kThreads) {
+            const int kc = i % kchunks, n = i / kchunks;
+            const uint4 v = n < p.cout_pad ? src[(size_t)n * kchunks + kc] : make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(smem_b + (size_t)kc * (p.BN * 16) + (n >> 3) * 128 + (n & 7) * 16) = v;
+        }
+        ptx::fence_proxy_async();
+    }
     for (int c = threadIdx.x; c < p.n_tiles * p.BN; c += kThreads) {
         const bool in = c < p.cout_pad;
         s_scale[c] = in ? p.e.scale[c] : 0.f;
@@ -226,7 +251,35 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 ptx::tma_load_2d_u32(ptx::smem_u32(smem_b) + (uint32_t)(it * p.b_bytes), mapB, rb,
                                      k_tab[it].w & 0x0fffffff, 0);
         }
-        if (p.patch) {
+        if constexpr (kHalo) {
+            if (lane == 0) {
+                const uint32_t bytes = (uint32_t)(p.cchunks * p.halo_plane);
+                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                    const TileCoord tc = decode_tile(p, t);
+                    if (!ptx::mbar_wait_bounded_u32(empty0 + stage * 8, phase ^ 1u, &abort_flag, kMaxSpins)) {
+                        ok = 0;
+                        break;
+                    }
+                    const uint32_t fb = full0 + stage * 8;
+                    if (kDbg & 2) {
+                        ptx::mbar_arrive_u32(fb);
+                    } else {
+                    ptx::mbar_arrive_expect_tx_u32(fb, bytes);
+                    // x: byte column of pixel ow0-1 in a row of W*16 bytes, y: row oh0-1, z: slice 0, w: image
+                    ptx::tma_load_4d_u32(ptx::smem_u32(smem_a) + (uint32_t)(stage * p.a_bytes), mapA0, fb,
+                                         (tc.ow0 - 1) * 16, tc.oh0 - 1, 0, tc.n0);
+                    }
+                    if (++stage == p.stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) {
+                    atomicExch(p.error, 1);
+                    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+                }
+            }
+        } else if (p.patch) {
             if (lane == 0) {
                 const uint32_t bytes = (uint32_t)(p.patch_rows * p.patch_pitch);
                 for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -321,7 +374,47 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
                 uint32_t accumulate = 0;
-                if (p.patch) {
+                if constexpr (kHalo) {
+                    if (!ptx::mbar_wait_bounded_u32(full0 + stage * 8, phase, &abort_flag, kMaxSpins)) {
+                        ok = false;
+                        break;
+                    }
+                    // un-swizzled K-major descriptors.  A: core matrix = 8 pixels x 16 B, next tile
+                    // row 160 B on (SBO), next K chunk one slice plane on (LBO).  B: core matrices
+                    // 128 B apart (SBO), next K chunk BN*16 B on (LBO).
+                    const uint32_t a0 = ((ptx::smem_u32(smem_a) + (uint32_t)(stage * p.a_bytes)) >> 4) |
+                                        ((uint32_t)(p.halo_plane >> 4) << 16);
+                    const uint32_t a_hi = (160u >> 4) | (1u << 14);
+                    const uint32_t b_lbo = (uint32_t)(p.BN * 16) >> 4;
+                    const uint32_t b0 = (ptx::smem_u32(smem_b) >> 4) | (b_lbo << 16);
+                    const uint32_t b_hi = (128u >> 4) | (1u << 14);
+                    const uint32_t plane16 = (uint32_t)p.halo_plane >> 4;
+                    const int ksn = p.cchunks >> 1;          // 32-byte K steps per tap
+                    uint32_t bk = b0;
+                    for (int tap = 0; tap < 9; ++tap) {
+                        const int r = tap / 3, sx = tap - 3 * r;
+                        uint32_t ak = a0 + (uint32_t)(r * 10 + sx);
+                        for (int ks = 0; ks < ksn; ++ks) {
+                            if (!(kDbg & 4))
+                            asm volatile(
+                                "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+                                "mov.b64 da, {%1, %2};\n\t"
+                                "mov.b64 db, {%3, %4};\n\t"
+                                "setp.ne.b32 p, %6, 0;\n\t"
+                                "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+                                "r"(ak), "r"(a_hi), "r"(bk), "r"(b_hi), "r"(idesc), "r"(accumulate)
+                                : "memory");
+                            accumulate = 1;
+                            ak += 2 * plane16;
+                            bk += 2 * b_lbo;
+                        }
+                    }
+                    ptx::tc_commit_u32(empty0 + stage * 8);
+                    if (++stage == p.stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                } else if (p.patch) {
                     if (!ptx::mbar_wait_bounded_u32(full0 + stage * 8, phase, &abort_flag, kMaxSpins)) {
                         ok = false;
                         break;
@@ -500,7 +593,10 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         uint2 qv;
                         qv.x = quant_pack4(f0.x, f0.y, f1.x, f1.y, p.e.out2_scale);
                         qv.y = quant_pack4(f2.x, f2.y, f3.x, f3.y, p.e.out2_scale);
-                        *reinterpret_cast<uint2*>(static_cast<int8_t*>(p.e.y2) + off) = qv;
+                        const int64_t off8 = p.e.i8_planar
+                                                 ? ((((int64_t)tc.n0 * (p.e.cout_stride >> 4) + (u >> 1)) * p.PH + ph) * p.PW + pw) * 16 + (u & 1) * 8
+                                                 : off;
+                        *reinterpret_cast<uint2*>(static_cast<int8_t*>(p.e.y2) + off8) = qv;
                     }
                 }
                 // staging may be overwritten after this one
@@ -523,11 +619,28 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             uint32_t rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (do_res && c_begin < c_end && tc.ntile * p.BN + c_begin * 16 < p.e.cout_stride)
                 ld_global_nc_256(res_row + c_begin * 16, rn);
+#ifdef EXB_CONV_EXPERIMENTS
+            if (p.xflags & 1) {          // every lane polls, no sleep
+                if (!ptx::mbar_wait_bounded(&tfull_bar[grp], acc_phase, &abort_flag, kMaxSpins)) {
+                    ok = false;
+                    break;
+                }
+            } else
+#endif
             if (!ptx::mbar_wait_bounded_warp(&tfull_bar[grp], acc_phase, &abort_flag, kMaxSpins)) {
                 ok = false;
                 break;
             }
             ptx::tc_fence_after_sync();
+#ifdef EXB_CONV_EXPERIMENTS
+            if (p.xflags & 2) {          // epilogue reduced to the accumulator hand-back
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&tempty_bar[grp]);
+                acc_phase ^= 1u;
+                continue;
+            }
+#endif
             for (int chunk = c_begin; chunk < c_end; ++chunk) {
                 uint32_t raw[16];
                 if (kDbg & 8) continue;
@@ -541,6 +654,12 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 const int cl = tc.ntile * p.BN + chunk * 16;   // first channel of the chunk
                 if (!valid || cl >= p.e.cout_stride || (kDbg & 1)) continue;
                 const int64_t off = pix * p.e.cout_stride + cl;
+                // planar16: [n][channel slice][oh][ow][16]
+                int64_t off8 = off;
+                if constexpr (kHalo) {   // only this instantiation (and the pooling one) can write planar16
+                    if (p.e.i8_planar)
+                        off8 = ((((int64_t)n * (p.e.cout_stride >> 4) + (cl >> 4)) * p.OH + oh) * p.OW + ow) * 16;
+                }
                 float v[16];
                 {
                     const float4* sc = reinterpret_cast<const float4*>(s_scale + cl);
@@ -572,8 +691,9 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         if (acc_ == 123.456f) static_cast<float*>(p.e.y)[0] = acc_;   // keep the math alive
                         continue;
                     }
-                    epi_store_vec16(p.e.y, p.e.out_dtype, off, v, p.e.out_scale, raw);
-                    if (p.e.out2_dtype >= 0) epi_store_vec16(p.e.y2, p.e.out2_dtype, off, v, p.e.out2_scale, raw);
+                    epi_store_vec16(p.e.y, p.e.out_dtype, p.e.out_dtype == EXB_I8 ? off8 : off, v, p.e.out_scale, raw);
+                    if (p.e.out2_dtype >= 0)
+                        epi_store_vec16(p.e.y2, p.e.out2_dtype, p.e.out2_dtype == EXB_I8 ? off8 : off, v, p.e.out2_scale, raw);
                 } else {
                     // ragged channel count: element-wise stores, statically indexed so the
                     // accumulators stay in registers
@@ -658,6 +778,42 @@ bool conv_tc_pool_fusable(const ConvGeom& g) {
            !g.has_res && (g.act == EXB_ACT_RELU || g.act == EXB_ACT_RELU6) && g.group == 1;
 }
 
+namespace {
+// Shared-memory plan of halo mode: weights resident + a ring of whole patches.
+struct HaloPlan {
+    bool ok, two;
+    int BN, a_bytes, b_bytes, stages;
+};
+HaloPlan halo_plan(const exb_ctx* ctx, const ConvGeom& g) {
+    HaloPlan h = {false, false, 0, 0, 0, 0};
+    if (g.in_dtype != EXB_I8 || g.kh != 3 || g.kw != 3 || g.sh != 1 || g.sw != 1 || g.pt != 1 || g.pl != 1 ||
+        g.OH != g.H || g.OW != g.W || g.group != 1 || g.pool || g.cin_stride % 32 != 0 || g.W < 10 || g.H < 2 ||
+        g.w_pitch != g.W)
+        return h;
+    const int cout_pad = (g.cout_stride + 15) / 16 * 16;
+    if (cout_pad > 256) return h;
+    h.BN = cout_pad;
+    h.a_bytes = round_up((g.cin_stride / 16) * 18 * 160, 128);
+    h.b_bytes = h.BN * 9 * g.cin_stride;
+    const int fixed = 2048 + 1024 + 2 * h.BN * (int)sizeof(float) + 9 * (g.cin_stride / 32 + 1) * (int)sizeof(int4);
+    const int smem_optin = ctx ? ctx->smem_optin : 227 * 1024;
+    const int budget2 = 228 * 1024 / 2 - 1024 - fixed, budget1 = smem_optin - fixed;
+    if (h.BN <= 128 && h.b_bytes + 3 * h.a_bytes <= budget2) {
+        h.two = true;
+        h.stages = (budget2 - h.b_bytes) / h.a_bytes;
+    } else if (h.b_bytes + 2 * h.a_bytes <= budget1) {
+        h.stages = (budget1 - h.b_bytes) / h.a_bytes;
+    } else {
+        return h;
+    }
+    if (h.stages > kMaxStages) h.stages = kMaxStages;
+    h.ok = true;
+    return h;
+}
+}  // namespace
+
+bool conv_tc_halo_ok(const exb_ctx* ctx, const ConvGeom& g) { return halo_plan(ctx, g).ok; }
+
 bool conv_tc_eligible(const ConvGeom& g) {
     const int es = g.in_dtype == EXB_I8 ? 1 : 2;
     if (g.group != 1) return false;
@@ -727,6 +883,22 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
             p.tiles_h = (g.PH + 6) / 7;
         }
     }
+    const HaloPlan hp = g.in_planar ? halo_plan(ctx, g) : HaloPlan{false, false, 0, 0, 0, 0};
+    if (g.in_planar) {
+        if (!hp.ok || p.n_tiles != 1 || p.BN != hp.BN || w->kw_pack != 3 || w->cin_pad != g.cin_stride)
+            return fail(EXB_ERR_UNSUPPORTED, "planar16 input is not available for this convolution");
+        p.halo = 1;
+        two = hp.two;
+        p.TW = 8; p.TH = 16; p.TN = 1;
+        p.tiles_w = (g.OW + 7) / 8;
+        p.tiles_h = (g.OH + 15) / 16;
+        p.tiles_nb = g.N;
+        p.step_w = 8; p.step_h = 16; p.org = 0;
+        p.cchunks = g.cin_stride / 16;
+        p.halo_plane = 18 * 160;
+        p.a_bytes = hp.a_bytes;
+        p.w_global = w->d_w;
+    }
     if (g.pool && !(patch && two && p.BN == 64 && conv_tc_pool_fusable(g)))
         return fail(EXB_ERR_UNSUPPORTED, "fused pooling needs the patch-mode stem kernel with 64 output channels");
     p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
@@ -767,9 +939,14 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         p.b_resident = 0;
         stages = (budget - g.kh * p.BN * 64) / p.a_bytes;
     }
+    if (p.halo) {   // ring of whole patches, weights resident in their own region
+        p.kgroup = G = 1;
+        p.b_resident = 0;
+        stages = hp.stages;
+    }
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return fail(EXB_ERR_UNSUPPORTED, "conv tile does not fit shared memory (BN=%d)", p.BN);
-    p.b_region = patch ? g.kh * p.BN * 64 : (p.b_resident ? b_all : stages * G * p.b_bytes);
+    p.b_region = p.halo ? hp.b_bytes : (patch ? g.kh * p.BN * 64 : (p.b_resident ? b_all : stages * G * p.b_bytes));
     p.stages = stages;
     p.acc_bufs = two ? 2 : (p.BN <= 128 ? 4 : 2);
     int cols = 32;
@@ -781,7 +958,11 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.residual = static_cast<const __half*>(residual);
     p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;
     p.e.out_scale = g.out_scale; p.e.out2_scale = g.out2_scale; p.e.cout_stride = g.cout_stride;
+    p.e.i8_planar = g.out_i8_planar;
     p.error = ctx->d_error;
+#ifdef EXB_CONV_EXPERIMENTS
+    if (const char* e = getenv("EXB_CONV_X")) p.xflags = atoi(e);
+#endif
 
     const CUtensorMapDataType dt = int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUtensorMapSwizzle sw = swizzle_for(p.kb_bytes);
@@ -801,7 +982,18 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(patch) failed with %d", (int)r);
     }
-    for (int v = 0; v < (patch ? 0 : nviews); ++v) {
+    if (p.halo) {
+        // planar16: rows of W*16 bytes, H rows, C/16 slices, N images; box = 10 pixels x 18 rows x all slices.
+        cuuint64_t dims[4] = {(cuuint64_t)g.W * 16, (cuuint64_t)g.H, (cuuint64_t)p.cchunks, (cuuint64_t)g.N};
+        cuuint64_t strides[3] = {(cuuint64_t)g.W * 16, (cuuint64_t)g.H * g.W * 16, (cuuint64_t)p.cchunks * g.H * g.W * 16};
+        cuuint32_t box[4] = {160, 18, (cuuint32_t)p.cchunks, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = encode(&p.tmA[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(halo) failed with %d", (int)r);
+    }
+    for (int v = 0; v < ((patch || p.halo) ? 0 : nviews); ++v) {
         const int ph = v >> 1, pw = v & 1;
         const int st_ = g.sh;
         if (fold.on && pw) continue;   // the folded layout walks W inside the K row
@@ -851,8 +1043,9 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     auto kern = int8 ? (two ? conv_tc_kernel<true, 0, 8> : conv_tc_kernel<true, 0, 16>)
                      : (two ? conv_tc_kernel<false, 0, 8> : conv_tc_kernel<false, 0, 16>);
     if (p.pool) kern = conv_tc_kernel<false, 0, 8, true>;
+    if (p.halo) kern = two ? conv_tc_kernel<true, 0, 8, false, true> : conv_tc_kernel<true, 0, 16, false, true>;
 #ifdef EXB_CONV_EXPERIMENTS
-    if (const char* e = getenv("EXB_CONV_DBG")) {
+    if (const char* e = getenv("EXB_CONV_DBG"); e && !p.halo && !p.pool) {
         switch (atoi(e)) {
         case 1: kern = int8 ? (two ? conv_tc_kernel<true, 1, 8> : conv_tc_kernel<true, 1, 16>) : (two ? conv_tc_kernel<false, 1, 8> : conv_tc_kernel<false, 1, 16>); break;
         case 2: kern = int8 ? (two ? conv_tc_kernel<true, 2, 8> : conv_tc_kernel<true, 2, 16>) : (two ? conv_tc_kernel<false, 2, 8> : conv_tc_kernel<false, 2, 16>); break;

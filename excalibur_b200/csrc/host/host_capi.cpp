@@ -107,7 +107,7 @@ extern "C" int exb_host_pipeline_forward(void* p, const float* input, int N, int
         auto* h = static_cast<host_pipeline*>(p);
         // a tensor that borrows the caller's host memory
         auto t = std::shared_ptr<memory::tensor<float>>(
-            new memory::tensor<float>(std::vector<int>{N, C, H, W}, 0, memory::NCHW, nullptr));
+            new memory::tensor<float>(std::vector<int>{N, C, H, W}, h->net->device(), memory::NCHW, nullptr));
         t->data()->set_external_cpu_data(const_cast<float*>(input));
         h->outputs = h->net->forward(t);
         h->names.clear();

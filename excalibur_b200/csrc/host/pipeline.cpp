@@ -1026,8 +1026,17 @@ public:
 template <typename Dtype>
 typename pipeline<Dtype>::result_map pipeline<Dtype>::impl::forward_unfused(
     const std::shared_ptr<memory::tensor<Dtype>>& input) {
+    CUDA_CHECK(cudaSetDevice(device_));
     if (!ctx_) exb_check(exb_ctx_create(device_, &ctx_), "exb_ctx_create");
-    featmaps_[featmap_index_[input_names_[0]]] = input;
+    std::shared_ptr<memory::tensor<Dtype>> in0 = input;
+    if (input->device() != device_) {
+        // A tensor made for another device would be uploaded there (and switch this thread's current
+        // device): work on a copy that lives on the pipeline's device.
+        in0 = std::shared_ptr<memory::tensor<Dtype>>(
+            new memory::tensor<Dtype>(input->data_shape(), device_, input->order(), input->allocator()));
+        std::memcpy(in0->mutable_cpu_data(), input->cpu_data(), (size_t)input->count() * sizeof(Dtype));
+    }
+    featmaps_[featmap_index_[input_names_[0]]] = in0;
     trace_.clear();
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     if (profile_) {
@@ -1156,6 +1165,7 @@ template <typename Dtype>
 std::shared_ptr<memory::tensor<Dtype>> pipeline<Dtype>::get_featmap(std::string_view n) { return impl_->get_featmap(n); }
 template <typename Dtype> void pipeline<Dtype>::enable_profiler() { impl_->profile_ = true; }
 template <typename Dtype> void pipeline<Dtype>::disable_profiler() { impl_->profile_ = false; }
+template <typename Dtype> int pipeline<Dtype>::device() const { return impl_->device_; }
 template <typename Dtype> void pipeline<Dtype>::set_fusion(bool on) { impl_->fusion_ = on; }
 template <typename Dtype> void pipeline<Dtype>::set_cuda_graph(bool on) { impl_->graph_ = on; }
 template <typename Dtype> void pipeline<Dtype>::set_h2d_chunks(int k) { impl_->h2d_chunks_ = k < 1 ? 1 : k; }

@@ -38,6 +38,7 @@ public:
     bool dump_profile(std::string_view path);
 
     // Extras of this implementation.
+    int device() const;                  // the device id given at construction (-1 = none)
     void set_fusion(bool on);            // default on for pipeline<float> on a GPU
     void set_cuda_graph(bool on);        // replay the fused plan as a CUDA graph (default on)
     // forward() of a batch divisible by k runs as k sub-batches: sub-batch c+1 is copied to the device

@@ -53,6 +53,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// 16-byte asynchronous copy global -> shared (bypassing L1 and registers), per-thread groups.
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Bounded wait.  `abort_flag` (shared memory) lets one role that gave up release the others.
 // Returns false when the limit ran out or another role aborted.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,

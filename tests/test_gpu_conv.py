@@ -322,3 +322,68 @@ def test_fused_max_pool_is_refused_where_it_cannot_run(ctx):
     x = dev(np.zeros((1, 16, 16, 32), np.int8))
     with pytest.raises(capi.ExbError):
         capi.conv2d(ctx, d, x, w)
+
+
+HALO_CASES = [
+    # N, Cin, H, W, Cout
+    (2, 64, 56, 56, 64),       # ResNet stage 1
+    (3, 128, 28, 28, 128),     # stage 2 (one CTA per SM: the weights take 147 KB)
+    (2, 32, 21, 13, 48),       # ragged tiles in both directions, Cout not a multiple of 32
+    (1, 64, 16, 10, 16),
+    (5, 64, 14, 14, 256),
+]
+
+
+@pytest.mark.parametrize("case", HALO_CASES)
+def test_conv_i8_planar16_halo_mode(ctx, case):
+    """3x3 stride-1 int8 conv reading planar16 input through one halo patch per tile and writing a
+    planar16 int8 output (+ NHWC fp16 output, NHWC fp16 residual): bit-identical to the NHWC path."""
+    from tests.util import to_planar16, from_planar16
+    capi = _capi()
+    N, Cin, H, W, Cout = case
+    r = rng(sum(case) + 3)
+    xq = r.integers(-128, 128, (N, Cin, H, W)).astype(np.int8)
+    wq = r.integers(-127, 128, (Cout, Cin, 3, 3)).astype(np.int8)
+    bias = r.standard_normal(Cout).astype(np.float32)
+    ws = r.uniform(20, 60, Cout).astype(np.float32)
+    fs, q = 31.0, 17.0
+    res = f16_round(r.standard_normal((N, Cout, H, W)))
+    cs = (Cout + 15) // 16 * 16
+    base = dict(res=True, act=1, out_scale=1.0, out2_scale=q, cout_stride=cs)
+    d0 = capi.make_conv_desc(N, H, W, Cin, Cout, 3, 1, 1, capi.EXB_I8, capi.EXB_F16, capi.EXB_I8, **base)
+    d1 = capi.make_conv_desc(N, H, W, Cin, Cout, 3, 1, 1, capi.EXB_I8, capi.EXB_F16, capi.EXB_I8, in_planar=1,
+                             out_i8_planar=1, **base)
+    assert capi.lib().exb_conv2d_accepts_planar_input(d0) == 1
+    wp = capi.ConvWeights(ctx, d0, wq, bias, ws, fs)
+    resd = dev(to_nhwc(res, cs).astype(np.float16))
+    y0, q0 = capi.conv2d(ctx, d0, dev(to_nhwc(xq)), wp, resd)
+    import torch
+    q1 = torch.zeros((N, cs // 16, H, W, 16), dtype=torch.int8, device="cuda")
+    y1, _ = capi.conv2d(ctx, d1, dev(to_planar16(xq)), wp, resd, None, q1)
+    ctx.sync_check()
+    np.testing.assert_array_equal(host(y1), host(y0))
+    np.testing.assert_array_equal(from_planar16(host(q1), Cout), to_nchw(host(q0), Cout))
+    # and against the oracle: dequantised accumulator + bias + residual, ReLU
+    acc = O.conv2d_i8_acc(xq, wq, 1, 1)
+    ref = np.maximum(O.dequantize(acc, O.dequant_scales(ws, fs, Cout), bias) + res, 0)
+    assert_close_f16(to_nchw(host(y1).astype(np.float32), Cout), ref, rel=2e-3, what="halo fp16 output")
+    # int8-only output, no residual
+    d2 = capi.make_conv_desc(N, H, W, Cin, Cout, 3, 1, 1, capi.EXB_I8, capi.EXB_I8, act=1, out_scale=q, cout_stride=cs,
+                             in_planar=1, out_i8_planar=1)
+    d3 = capi.make_conv_desc(N, H, W, Cin, Cout, 3, 1, 1, capi.EXB_I8, capi.EXB_I8, act=1, out_scale=q, cout_stride=cs)
+    q2 = torch.zeros((N, cs // 16, H, W, 16), dtype=torch.int8, device="cuda")
+    capi.conv2d(ctx, d2, dev(to_planar16(xq)), wp, None, q2)
+    q3, _ = capi.conv2d(ctx, d3, dev(to_nhwc(xq)), wp)
+    ctx.sync_check()
+    np.testing.assert_array_equal(from_planar16(host(q2), Cout), to_nchw(host(q3), Cout))
+    f = torch.empty((N, Cout, H, W), dtype=torch.float32, device="cuda")
+    capi.check(capi.lib().exb_planar16_i8_to_nchw_f32(ctx.handle, capi.ptr(q2), capi.ptr(f), N, Cout, H, W, cs, 0.5,
+                                                       capi.cur_stream()))
+    np.testing.assert_array_equal(host(f), from_planar16(host(q2), Cout).astype(np.float32) * 0.5)
+
+
+def test_planar_input_is_refused_where_it_cannot_run(ctx):
+    capi = _capi()
+    for args in ((1, 16, 16, 64, 64, 3, 2, 1), (1, 16, 16, 64, 64, 1, 1, 0), (1, 7, 7, 512, 512, 3, 1, 1)):
+        d = capi.make_conv_desc(*args, capi.EXB_I8, capi.EXB_I8)
+        assert capi.lib().exb_conv2d_accepts_planar_input(d) == 0, args

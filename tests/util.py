@@ -54,3 +54,19 @@ def quant_weights(w):
     ws = (127.0 / np.abs(w).reshape(cout, -1).max(axis=1)).astype(np.float32)
     wq = np.clip(np.rint(w * ws[:, None, None, None]), -127, 127).astype(np.int8)
     return wq, ws
+
+
+def to_planar16(a_nchw, c_stride=None):
+    """NCHW numpy -> planar16 [N][cs/16][H][W][16], zero-padding the channels to c_stride."""
+    n, c, h, w = a_nchw.shape
+    cs = c_stride or (c + 15) // 16 * 16
+    p = np.zeros((n, cs, h, w), a_nchw.dtype)
+    p[:, :c] = a_nchw
+    return np.ascontiguousarray(p.reshape(n, cs // 16, 16, h, w).transpose(0, 1, 3, 4, 2))
+
+
+def from_planar16(p, C=None):
+    """planar16 [N][cs/16][H][W][16] -> NCHW numpy."""
+    n, cc, h, w, _ = p.shape
+    a = np.ascontiguousarray(p.transpose(0, 1, 4, 2, 3)).reshape(n, cc * 16, h, w)
+    return a[:, :C] if C is not None else a
