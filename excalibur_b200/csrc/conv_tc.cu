@@ -51,6 +51,7 @@ struct ConvTcParams {
     int a_tx_bytes;         // bytes one A box delivers
     int tmem_cols;
     int acc_bufs;     // accumulator buffers in TMEM (2 or 4)
+    int epi_groups;   // epilogue warp groups (2 or 4); group g drains tiles g, g + epi_groups, ... of the CTA
     int cout_pad;     // entries of the scale / bias arrays
     uint32_t idesc;
     int has_res;
@@ -158,7 +159,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         }
         for (int i = 0; i < p.acc_bufs; ++i) {
             ptx::mbar_init(&tfull_bar[i], 1);
-            ptx::mbar_init(&tempty_bar[i], kEpiWarps / p.acc_bufs);
+            ptx::mbar_init(&tempty_bar[i], kEpiWarps / p.epi_groups);
         }
         ptx::mbar_init(&bres_bar, 1);
         ptx::fence_mbar_init();
@@ -494,9 +495,9 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         // in the second case splitting the 16-column chunks between them.
         const int e = warp - kFirstEpiWarp;
         const int q = e & 3;                    // TMEM lane quarter (== warp % 4)
-        const int nsub = kEpiWarps / 4 / p.acc_bufs;
-        const int grp = (e >> 2) % p.acc_bufs;
-        const int sub = (e >> 2) / p.acc_bufs;
+        const int nsub = kEpiWarps / 4 / p.epi_groups;
+        const int grp = (e >> 2) % p.epi_groups;
+        const int sub = (e >> 2) / p.epi_groups;
         const int row = q * 32 + lane;          // row of the M tile == TMEM lane
         const int tw = row % p.TW;
         const int th = (row / p.TW) % p.TH;
@@ -504,9 +505,11 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         const bool row_in_box = row < p.TW * p.TH * p.TN;
         const bool vec_ok = (p.e.cout_stride & 15) == 0;
         const int n_chunks = p.BN / 16;
-        uint32_t acc_phase = 0;
+        // The CTA's i-th tile is accumulated in buffer i % acc_bufs (use number i / acc_bufs of that
+        // buffer gives the barrier parity) and drained by group i % epi_groups.
+        int ti = grp;
         bool ok = true;
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * p.BN);
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16);
         if constexpr (kPool) {
             // Convolution tile -> ReLU -> fp16 -> shared memory (16-byte units of a pixel row XOR-ed
             // with the row index so that neither phase has bank conflicts) -> 3x3/2 max -> global.
@@ -514,11 +517,14 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             // wait ran out still arrives, and the whole group leaves together afterwards.
             uint8_t* stg = pool_stage + grp * (kTileM * 128);
             volatile int* failed = &pool_fail[grp];
-            for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles; t += p.acc_bufs * gridDim.x) {
+            for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles; t += p.epi_groups * gridDim.x, ti += p.epi_groups) {
                 const TileCoord tc = decode_tile(p, t);
                 const int ow = tc.ow0 + tw, oh = tc.oh0 + th;
                 const bool inside = ow >= 0 && ow < p.OW && oh >= 0 && oh < p.OH;
-                if (!ptx::mbar_wait_bounded_warp(&tfull_bar[grp], acc_phase, &abort_flag, kMaxSpins)) {
+                const int buf = ti % p.acc_bufs;
+                const uint32_t acc_phase = (uint32_t)(ti / p.acc_bufs) & 1u;
+                const uint32_t taddr = taddr0 + (uint32_t)(buf * p.BN);
+                if (!ptx::mbar_wait_bounded_warp(&tfull_bar[buf], acc_phase, &abort_flag, kMaxSpins)) {
                     if (lane == 0) *failed = 1;
                 } else {
                     ptx::tc_fence_after_sync();
@@ -552,9 +558,8 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     }
                     ptx::tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&tempty_bar[grp]);   // the accumulator is free again
+                    if (lane == 0) ptx::mbar_arrive(&tempty_bar[buf]);   // the accumulator is free again
                 }
-                acc_phase ^= 1u;
                 if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
                 else asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (*failed) {
@@ -604,9 +609,12 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 else asm volatile("bar.sync 2, 128;" ::: "memory");
             }
         } else
-        for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles && ok; t += p.acc_bufs * gridDim.x) {
+        for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles && ok; t += p.epi_groups * gridDim.x, ti += p.epi_groups) {
             const TileCoord tc = decode_tile(p, t);
             const int ow = tc.ow0 + tw, oh = tc.oh0 + th, n = tc.n0 + tn;
+            const int buf = ti % p.acc_bufs;
+            const uint32_t acc_phase = (uint32_t)(ti / p.acc_bufs) & 1u;
+            const uint32_t taddr = taddr0 + (uint32_t)(buf * p.BN);
             const bool valid = row_in_box && ow < p.OW && oh < p.OH && n < p.N;
             const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
             // This warp's chunks of 16 channels.  The residual of a chunk is requested one chunk
@@ -619,15 +627,28 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             uint32_t rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (do_res && c_begin < c_end && tc.ntile * p.BN + c_begin * 16 < p.e.cout_stride)
                 ld_global_nc_256(res_row + c_begin * 16, rn);
+            // The residual rows of this group's NEXT tile are asked into L2 now (no register cost):
+            // the tile after this one then finds them a few hundred cycles away instead of a DRAM
+            // round trip per chunk, which the one-chunk-ahead register prefetch cannot cover.
+            if (p.has_res && vec_ok && t + p.epi_groups * (int)gridDim.x < total_tiles) {
+                const TileCoord c2 = decode_tile(p, t + p.epi_groups * (int)gridDim.x);
+                const int ow2 = c2.ow0 + tw, oh2 = c2.oh0 + th, n2 = c2.n0 + tn;
+                if (row_in_box && ow2 < p.OW && oh2 < p.OH && n2 < p.N) {
+                    const __half* r2 = p.e.residual + (((int64_t)n2 * p.OH + oh2) * p.OW + ow2) * p.e.cout_stride +
+                                       c2.ntile * p.BN + c_begin * 16;
+                    for (int b = 0; b < (c_end - c_begin) * 32; b += 128)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(r2) + b));
+                }
+            }
 #ifdef EXB_CONV_EXPERIMENTS
             if (p.xflags & 1) {          // every lane polls, no sleep
-                if (!ptx::mbar_wait_bounded(&tfull_bar[grp], acc_phase, &abort_flag, kMaxSpins)) {
+                if (!ptx::mbar_wait_bounded(&tfull_bar[buf], acc_phase, &abort_flag, kMaxSpins)) {
                     ok = false;
                     break;
                 }
             } else
 #endif
-            if (!ptx::mbar_wait_bounded_warp(&tfull_bar[grp], acc_phase, &abort_flag, kMaxSpins)) {
+            if (!ptx::mbar_wait_bounded_warp(&tfull_bar[buf], acc_phase, &abort_flag, kMaxSpins)) {
                 ok = false;
                 break;
             }
@@ -636,8 +657,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             if (p.xflags & 2) {          // epilogue reduced to the accumulator hand-back
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&tempty_bar[grp]);
-                acc_phase ^= 1u;
+                if (lane == 0) ptx::mbar_arrive(&tempty_bar[buf]);
                 continue;
             }
 #endif
@@ -712,8 +732,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&tempty_bar[grp]);
-            acc_phase ^= 1u;
+            if (lane == 0) ptx::mbar_arrive(&tempty_bar[buf]);
         }
         if (!ok && lane == 0) atomicExch(p.error, 3);
     }
@@ -948,7 +967,12 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     if (stages < 2) return fail(EXB_ERR_UNSUPPORTED, "conv tile does not fit shared memory (BN=%d)", p.BN);
     p.b_region = p.halo ? hp.b_bytes : (patch ? g.kh * p.BN * 64 : (p.b_resident ? b_all : stages * G * p.b_bytes));
     p.stages = stages;
-    p.acc_bufs = two ? 2 : (p.BN <= 128 ? 4 : 2);
+    // As many accumulator buffers as TMEM allows (256 columns per CTA with two CTAs per SM, else
+    // 512): a buffer goes round MMA -> hand-over -> epilogue -> hand-back, and the two hand-overs
+    // alone cost a couple of microseconds, so the number of buffers in flight sets the tile rate
+    // of short layers.  Epilogue groups need four warps each (one per TMEM lane quarter).
+    p.acc_bufs = two ? (p.BN <= 64 ? 4 : 2) : (p.BN <= 128 ? 4 : 2);
+    p.epi_groups = two ? 2 : (p.acc_bufs == 4 ? 4 : 2);
     int cols = 32;
     while (cols < p.acc_bufs * p.BN) cols *= 2;
     p.tmem_cols = cols;
@@ -1058,6 +1082,9 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         case 32: kern = int8 ? (two ? conv_tc_kernel<true, 32, 8> : conv_tc_kernel<true, 32, 16>) : (two ? conv_tc_kernel<false, 32, 8> : conv_tc_kernel<false, 32, 16>); break;
         case 48: kern = int8 ? (two ? conv_tc_kernel<true, 48, 8> : conv_tc_kernel<true, 48, 16>) : (two ? conv_tc_kernel<false, 48, 8> : conv_tc_kernel<false, 48, 16>); break;
         case 14: kern = int8 ? (two ? conv_tc_kernel<true, 14, 8> : conv_tc_kernel<true, 14, 16>) : (two ? conv_tc_kernel<false, 14, 8> : conv_tc_kernel<false, 14, 16>); break;
+        case 22: kern = int8 ? (two ? conv_tc_kernel<true, 22, 8> : conv_tc_kernel<true, 22, 16>) : (two ? conv_tc_kernel<false, 22, 8> : conv_tc_kernel<false, 22, 16>); break;
+        case 38: kern = int8 ? (two ? conv_tc_kernel<true, 38, 8> : conv_tc_kernel<true, 38, 16>) : (two ? conv_tc_kernel<false, 38, 8> : conv_tc_kernel<false, 38, 16>); break;
+        case 54: kern = int8 ? (two ? conv_tc_kernel<true, 54, 8> : conv_tc_kernel<true, 54, 16>) : (two ? conv_tc_kernel<false, 54, 8> : conv_tc_kernel<false, 54, 16>); break;
         default: break;
         }
     }
