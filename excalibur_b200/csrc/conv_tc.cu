@@ -427,6 +427,9 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     const uint32_t b0 = (ptx::smem_u32(smem_b) >> 4) | ((uint32_t)(p.BN * 16 >> 4) << 16);
                     const uint32_t b_hi = (128u >> 4) | (1u << 14);
                     for (int r = 0; r < p.kh; ++r) {
+#ifdef EXB_CONV_EXPERIMENTS
+                        if (p.xflags & 32) break;
+#endif
                         const uint32_t ar = a0 + (uint32_t)(r * p.patch_pitch >> 4);
                         const uint32_t br = b0 + (uint32_t)(r * p.BN * 64 >> 4);
 #pragma unroll
@@ -531,8 +534,14 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
 #pragma unroll
                     for (int chunk = 0; chunk < 4; ++chunk) {
                         uint32_t raw[16];
+#ifdef EXB_CONV_EXPERIMENTS
+                        if (p.xflags & 16) continue;
+#endif
                         ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
                         ptx::tmem_ld_wait();
+#ifdef EXB_CONV_EXPERIMENTS
+                        if (p.xflags & 4) continue;
+#endif
                         float v[16];
                         const float4* sc = reinterpret_cast<const float4*>(s_scale + chunk * 16);
                         const float4* bi = reinterpret_cast<const float4*>(s_bias + chunk * 16);
@@ -567,6 +576,9 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     break;
                 }
                 const int ph0 = (tc.oh0 + 1) >> 1, pw0 = (tc.ow0 + 1) >> 1;
+#ifdef EXB_CONV_EXPERIMENTS
+                if (!(p.xflags & 8))
+#endif
                 for (int item = row; item < 21 * 8; item += kTileM) {
                     const int pp = item >> 3, u = item & 7;
                     const int pr = pp / 3, pc = pp - 3 * pr;
