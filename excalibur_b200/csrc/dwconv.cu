@@ -3,6 +3,8 @@
 // vector of the strip is loaded once per kernel row and reused by all taps that touch it, and
 // each weight vector is loaded once per strip.  Weights are kept tap-major [kh*kw][C] in fp32
 // so consecutive threads read consecutive channels.
+#include <type_traits>
+
 #include "common.cuh"
 
 struct exb_dw_weights {
@@ -116,6 +118,118 @@ __global__ void __launch_bounds__(128) dw_strip_kernel(const TIn* __restrict__ x
     }
 }
 
+// 3x3 fp16 -> fp16, rolling window: a thread owns 8 channels x TW output columns and walks R output
+// rows downwards, keeping the last input rows in registers (raw fp16 vectors), so every input row
+// is loaded once per thread instead of once per output row; weights and bias sit in shared memory.
+// Over-fetch is (R+2)/R vertically and ((TW-1)*S+3)/(TW*S) horizontally, all of it served by L1/L2.
+__device__ __forceinline__ void cvt8(const uint4& r, float (&v)[V]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+
+template <int S, int TW, int R>
+__global__ void __launch_bounds__(128) dw3x3_roll_f16_kernel(const __half* __restrict__ x, const float* __restrict__ w,
+                                                             const float* __restrict__ bias, __half* __restrict__ y,
+                                                             DwParams p) {
+    constexpr int IN_W = (TW - 1) * S + 3;
+    extern __shared__ float s_w[];   // [9][cs] taps, then [cs] bias
+    for (int i = threadIdx.x; i < 9 * p.cs; i += blockDim.x) s_w[i] = w[i];
+    for (int i = threadIdx.x; i < p.cs; i += blockDim.x) s_w[9 * p.cs + i] = bias[i];
+    __syncthreads();
+    const int cvecs = p.cs / V;
+    const int owb = (p.OW + TW - 1) / TW, ohb = (p.OH + R - 1) / R;
+    const int64_t total = (int64_t)p.N * ohb * owb * cvecs;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int cv = (int)(idx % cvecs);
+        int64_t t = idx / cvecs;
+        const int ob = (int)(t % owb); t /= owb;
+        const int rb = (int)(t % ohb);
+        const int n = (int)(t / ohb);
+        const int ow0 = ob * TW, oh0 = rb * R;
+        const int iw0 = ow0 * S - p.pl;
+        const __half* xin = x + (int64_t)n * p.H * p.W * p.cs + cv * V;
+        auto load_row = [&](int ih, uint4 (&row)[IN_W]) {
+            const bool rok = ih >= 0 && ih < p.H;
+#pragma unroll
+            for (int j = 0; j < IN_W; ++j) {
+                const int iw = iw0 + j;
+                row[j] = (rok && iw >= 0 && iw < p.W)
+                             ? *reinterpret_cast<const uint4*>(xin + ((int64_t)ih * p.W + iw) * p.cs)
+                             : zero;
+            }
+        };
+        uint4 r0[IN_W], r1[IN_W], r2[IN_W];
+        if (S == 1) {
+            load_row(oh0 - p.pt, r0);
+            load_row(oh0 - p.pt + 1, r1);
+        } else {
+            load_row(oh0 * 2 - p.pt, r0);
+        }
+        const float* wb = s_w + cv * V;
+#pragma unroll 1
+        for (int orow = 0; orow < R; ++orow) {
+            const int oh = oh0 + orow;
+            if (oh >= p.OH) break;
+            if (S == 1) {
+                load_row(oh - p.pt + 2, r2);
+            } else {
+                load_row(oh * 2 - p.pt + 1, r1);
+                load_row(oh * 2 - p.pt + 2, r2);
+            }
+            float acc[TW][V];
+            {
+                float b[V];
+                loadw(wb + 9 * p.cs, b);
+#pragma unroll
+                for (int j = 0; j < TW; ++j)
+#pragma unroll
+                    for (int k = 0; k < V; ++k) acc[j][k] = b[k];
+            }
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                float wv[3][V];
+#pragma unroll
+                for (int sx = 0; sx < 3; ++sx) loadw(wb + (r * 3 + sx) * p.cs, wv[sx]);
+#pragma unroll
+                for (int j = 0; j < IN_W; ++j) {
+                    float f[V];
+                    cvt8(r == 0 ? r0[j] : (r == 1 ? r1[j] : r2[j]), f);
+#pragma unroll
+                    for (int tcol = 0; tcol < TW; ++tcol) {
+                        const int sx = j - tcol * S;
+                        if (sx >= 0 && sx < 3) {
+#pragma unroll
+                            for (int k = 0; k < V; ++k) acc[tcol][k] = fmaf(f[k], wv[sx][k], acc[tcol][k]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < TW; ++j) {
+                const int ow = ow0 + j;
+                if (ow < p.OW) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) acc[j][k] = apply_act(acc[j][k], p.act);
+                    store8(y + (((int64_t)n * p.OH + oh) * p.OW + ow) * p.cs + cv * V, acc[j], 1.f);
+                }
+            }
+            // the window moves down by S rows
+#pragma unroll
+            for (int j = 0; j < IN_W; ++j) {
+                if (S == 1) {
+                    r0[j] = r1[j];
+                    r1[j] = r2[j];
+                } else {
+                    r0[j] = r2[j];
+                }
+            }
+        }
+    }
+}
+
 // Any window / stride: one output pixel x 8 channels per thread.
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(128) dw_generic_kernel(const TIn* __restrict__ x, const float* __restrict__ w,
@@ -157,6 +271,22 @@ int launch(exb_ctx* ctx, const DwParams& p, const void* x, const exb_dw_weights*
     TOut* yo = static_cast<TOut*>(y);
     const int cvecs = p.cs / V;
     constexpr int TW = 4;
+    if constexpr (std::is_same<TIn, __half>::value && std::is_same<TOut, __half>::value) {
+        const size_t smem = (size_t)10 * p.cs * sizeof(float);
+        if (p.kh == 3 && p.kw == 3 && p.sh == p.sw && (p.sh == 1 || p.sh == 2) && smem <= 48 * 1024) {
+            constexpr int R = 8;
+            if (p.sh == 1) {
+                const int64_t total = (int64_t)p.N * ((p.OH + R - 1) / R) * ((p.OW + 3) / 4) * cvecs;
+                const int grid = stream_grid(ctx, total, 128, 4);
+                dw3x3_roll_f16_kernel<1, 4, R><<<grid, 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);
+            } else {
+                const int64_t total = (int64_t)p.N * ((p.OH + R - 1) / R) * ((p.OW + 1) / 2) * cvecs;
+                const int grid = stream_grid(ctx, total, 128, 4);
+                dw3x3_roll_f16_kernel<2, 2, R><<<grid, 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);
+            }
+            return after_launch("dw3x3_roll_f16_kernel");
+        }
+    }
     if (p.kh == 3 && p.kw == 3 && p.sh == p.sw && (p.sh == 1 || p.sh == 2)) {
         const int64_t total = (int64_t)p.N * p.OH * ((p.OW + TW - 1) / TW) * cvecs;
         const int grid = stream_grid(ctx, total, 128, 16);
