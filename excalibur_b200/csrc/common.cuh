@@ -16,6 +16,7 @@ struct exb_ctx {
     int smem_optin;          // max dynamic shared memory per block (opt-in)
     int* d_error;            // device error word written by kernels whose bounded waits ran out
     int* h_error;            // pinned host mirror
+    int pdl;                 // launch the conv kernel with programmatic stream serialization (default 1; EXB_PDL=0 turns it off)
 };
 
 namespace exb {

@@ -1,4 +1,6 @@
 // Context, error reporting and version of the C ABI.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 #include <string.h>
@@ -42,6 +44,10 @@ extern "C" int exb_ctx_create(int device, exb_ctx** out) {
     c->smem_optin = (int)prop.sharedMemPerBlockOptin;
     c->d_error = nullptr;
     c->h_error = nullptr;
+    {
+        const char* e = getenv("EXB_PDL");   // EXB_PDL=0: plain stream-ordered launches of the conv kernel
+        c->pdl = (e && e[0] == '0') ? 0 : 1;
+    }
     cudaError_t e = cudaMalloc(&c->d_error, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->d_error, 0, sizeof(int));
     if (e == cudaSuccess) e = cudaMallocHost(&c->h_error, sizeof(int));

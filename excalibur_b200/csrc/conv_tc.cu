@@ -150,6 +150,9 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
     const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.n_tiles;
     const int k_iters = p.fold ? p.kh : p.kh * p.kw * p.cblks;
 
+    // Let the next kernel of the stream be scheduled as soon as SMs free up (it waits for this
+    // grid's completion at its own griddepcontrol.wait before it reads or writes global memory).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int i = 0; i < kMaxAccBufs; ++i) pool_fail[i] = 0;
@@ -222,6 +225,10 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         s_scale[c] = in ? p.e.scale[c] : 0.f;
         s_bias[c] = in ? p.e.bias[c] : 0.f;
     }
+    // Programmatic dependent launch: everything above touches only this launch's own parameters,
+    // constant weights and on-chip state, so it may run while the previous kernel of the stream is
+    // still draining; nothing below may start before that kernel's memory is complete and visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
@@ -1102,7 +1109,18 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     }
 #endif
     EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, (kFirstEpiWarp + (two ? 8 : 16)) * 32, smem, st>>>(p);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)((kFirstEpiWarp + (two ? 8 : 16)) * 32));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    EXB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
     return after_launch("conv_tc_kernel");
 }
 
