@@ -13,7 +13,7 @@ SO_PATH = os.path.join(_PKG, "lib", "libexcalibur_b200.so")
 
 EXB_OK, EXB_ERR_BAD_ARG, EXB_ERR_UNSUPPORTED, EXB_ERR_CUDA, EXB_ERR_TIMEOUT, EXB_ERR_NOMEM = 0, -1, -2, -3, -4, -5
 EXB_F16, EXB_I8, EXB_F32, EXB_I32 = 0, 1, 2, 3
-ACT_NONE, ACT_RELU, ACT_RELU6_QUIRK, ACT_SIGMOID, ACT_RELU6, ACT_SILU = 0, 1, 3, 4, 103, 104
+ACT_NONE, ACT_RELU, ACT_RELU6_QUIRK, ACT_SIGMOID, ACT_RELU6, ACT_SILU, ACT_HARDSWISH = 0, 1, 3, 4, 103, 104, 105
 
 EXPORTED_SYMBOLS = [
     "exb_ctx_create", "exb_ctx_destroy", "exb_last_error_string", "exb_version", "exb_ctx_sm_count",
@@ -23,6 +23,7 @@ EXPORTED_SYMBOLS = [
     "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_pool2d_nchw_f32_static", "exb_eltwise_fwd", "exb_binaryop_fwd",
     "exb_binaryop_scalar_fwd", "exb_relu_fwd", "exb_activation_fwd", "exb_quantize_fwd",
     "exb_dequantize_fwd", "exb_concat_fwd", "exb_interp_nearest_fwd", "exb_channel_affine_fwd",
+    "exb_hardswish_fwd", "exb_focus_fwd",
 ]
 
 
@@ -99,6 +100,8 @@ def lib():
         L.exb_concat_fwd.argtypes = [vp, i32, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), vp, i64, i64, i32, vp]
         L.exb_interp_nearest_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
         L.exb_channel_affine_fwd.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i64, i32, i32, i32, vp]
+        L.exb_hardswish_fwd.argtypes = [vp, vp, vp, i64, i32, f32, f32, vp]
+        L.exb_focus_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
         _LIB = L
     return _LIB
 
@@ -414,6 +417,33 @@ def channel_affine(ctx, x, mul, add, channels=None, channel_last=True, act=ACT_N
         outer, inner = x.shape[0], x.numel() // max(x.shape[0] * x.shape[1], 1)
     check(lib().exb_channel_affine_fwd(ctx.handle, ptr(x), ptr(y), ptr(mul), ptr(add), outer, Cc, cs, inner,
                                        exb_dtype_of(x), 1 if channel_last else 0, act, cur_stream()))
+    return y
+
+
+def hardswish(ctx, x, alpha=1.0 / 6.0, beta=0.5, y=None):
+    t = _torch()
+    if y is None:
+        y = t.empty_like(x)
+    check(lib().exb_hardswish_fwd(ctx.handle, ptr(x), ptr(y), x.numel(), exb_dtype_of(x), float(alpha), float(beta),
+                                  cur_stream()))
+    return y
+
+
+def focus(ctx, x, channels=None, out_stride=0, channel_last=True, y=None):
+    """Space-to-depth 2x2 of NHWC [N][H][W][cs] (channel_last) or fp32 NCHW."""
+    t = _torch()
+    if channel_last:
+        N, H, W, cs = x.shape
+        Cc = channels or cs
+        ocs = out_stride or 4 * Cc
+        if y is None:
+            y = t.empty((N, H // 2, W // 2, ocs), device=x.device, dtype=x.dtype)
+        check(lib().exb_focus_fwd(ctx.handle, ptr(x), ptr(y), N, Cc, H, W, cs, ocs, exb_dtype_of(x), 1, cur_stream()))
+    else:
+        N, Cc, H, W = x.shape
+        if y is None:
+            y = t.empty((N, 4 * Cc, H // 2, W // 2), device=x.device, dtype=x.dtype)
+        check(lib().exb_focus_fwd(ctx.handle, ptr(x), ptr(y), N, Cc, H, W, 0, 0, exb_dtype_of(x), 0, cur_stream()))
     return y
 
 

@@ -78,13 +78,14 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     case EXB_ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
     case EXB_ACT_RELU6: return fminf(fmaxf(v, 0.f), 6.f);
     case EXB_ACT_SILU: return v / (1.f + __expf(-v));
+    case EXB_ACT_HARDSWISH: return v * fminf(fmaxf(fmaf(v, 1.f / 6.f, 0.5f), 0.f), 1.f);
     default: return v;
     }
 }
 
 inline bool act_supported(int act) {
     return act == EXB_ACT_NONE || act == EXB_ACT_RELU || act == EXB_ACT_RELU6_QUIRK ||
-           act == EXB_ACT_SIGMOID || act == EXB_ACT_RELU6 || act == EXB_ACT_SILU;
+           act == EXB_ACT_SIGMOID || act == EXB_ACT_RELU6 || act == EXB_ACT_SILU || act == EXB_ACT_HARDSWISH;
 }
 
 // Grid for a bandwidth-bound grid-stride kernel: enough CTAs to fill every SM a few times

@@ -66,6 +66,40 @@ __global__ void __launch_bounds__(kThreads) interp_nearest_nchw_kernel(const flo
     }
 }
 
+// Space-to-depth 2x2: output channel g*C + c of pixel (i, j) is input channel c of pixel
+// (2i + g%2, 2j + g/2).  One thread per output element; the input is a few-channel image.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) focus_kernel(const T* __restrict__ x, T* __restrict__ y, int N, int C, int H,
+                                                         int W, int in_stride, int out_stride, int channel_last) {
+    const int OH = H / 2, OW = W / 2, OC = 4 * C;
+    const int ocs = channel_last ? out_stride : OC;
+    const int64_t work = (int64_t)N * OH * OW * ocs;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < work; i += step) {
+        int n, pc, oi, oj;
+        int64_t t = i;
+        if (channel_last) {
+            pc = (int)(t % ocs); t /= ocs;
+            oj = (int)(t % OW); t /= OW;
+            oi = (int)(t % OH);
+            n = (int)(t / OH);
+        } else {
+            oj = (int)(t % OW); t /= OW;
+            oi = (int)(t % OH); t /= OH;
+            pc = (int)(t % OC);
+            n = (int)(t / OC);
+        }
+        T v = T(0);
+        if (pc < OC) {
+            const int g = pc / C, c = pc - g * C;
+            const int ih = 2 * oi + (g & 1), iw = 2 * oj + (g >> 1);
+            v = channel_last ? x[(((int64_t)n * H + ih) * W + iw) * in_stride + c]
+                             : x[(((int64_t)n * C + c) * H + ih) * W + iw];
+        }
+        y[i] = v;
+    }
+}
+
 __device__ __forceinline__ float ld1(const __half* p) { return __half2float(*p); }
 __device__ __forceinline__ float ld1(const float* p) { return *p; }
 __device__ __forceinline__ void st1(__half* p, float v) { *p = __float2half_rn(v); }
@@ -177,6 +211,39 @@ extern "C" int exb_interp_nearest_fwd(exb_ctx* ctx, const void* x, void* y, int 
                                                                             static_cast<uint32_t*>(y), N, H, W, cs, OH, OW, hs, ws);
     }
     return after_launch("exb_interp_nearest_fwd");
+}
+
+extern "C" int exb_focus_fwd(exb_ctx* ctx, const void* x, void* y, int N, int C, int H, int W, int in_stride,
+                             int out_stride, int dtype, int channel_last, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(N >= 0 && C > 0 && H >= 2 && W >= 2, "exb_focus_fwd: bad shape");
+    if (N == 0) return EXB_OK;
+    EXB_REQUIRE(x && y, "exb_focus_fwd: null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!channel_last && dtype != EXB_F32) return fail(EXB_ERR_UNSUPPORTED, "planar focus is implemented for EXB_F32 only");
+    if (channel_last) {
+        if (in_stride == 0) in_stride = C;
+        if (out_stride == 0) out_stride = 4 * C;
+        EXB_REQUIRE(in_stride >= C && out_stride >= 4 * C, "exb_focus_fwd: channel stride smaller than channel count");
+    }
+    const int64_t work = (int64_t)N * (H / 2) * (W / 2) * (channel_last ? out_stride : 4 * C);
+    const int grid = stream_grid(ctx, work, kThreads);
+    switch (dtype) {
+    case EXB_F32:
+        focus_kernel<float><<<grid, kThreads, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), N, C, H, W,
+                                                       in_stride, out_stride, channel_last);
+        break;
+    case EXB_F16:
+        focus_kernel<uint16_t><<<grid, kThreads, 0, st>>>(static_cast<const uint16_t*>(x), static_cast<uint16_t*>(y), N, C, H,
+                                                          W, in_stride, out_stride, channel_last);
+        break;
+    case EXB_I8:
+        focus_kernel<uint8_t><<<grid, kThreads, 0, st>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(y), N, C, H, W,
+                                                         in_stride, out_stride, channel_last);
+        break;
+    default: return fail(EXB_ERR_UNSUPPORTED, "exb_focus_fwd: dtype %d", dtype);
+    }
+    return after_launch("exb_focus_fwd");
 }
 
 extern "C" int exb_channel_affine_fwd(exb_ctx* ctx, const void* x, void* y, const float* mul, const float* add,

@@ -889,5 +889,108 @@ void operation_batchnorm<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bo
 INSTANCE_CLASS(operation_batchnorm);
 REGISTE(operation_batchnorm);
 
+// ---------------------------------------------------------------------------------------------
+// HardSwish, Input normalisation, YoloV5Focus
+// ---------------------------------------------------------------------------------------------
+template <typename Dtype>
+operation_hardswish<Dtype>::operation_hardswish(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        if (kv.first == 0) alpha_ = std::stof(kv.second);
+        else if (kv.first == 1) beta_ = std::stof(kv.second);
+        else LOG(FATAL) << "Un-supported HardSwish Attribution " << kv.first;
+    }
+}
+template <typename Dtype>
+void operation_hardswish<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), 1u);
+    CHECK_EQ(tops.size(), 1u);
+    tops[0] = make_tensor<float>(bottoms[0]->data_shape(), bottoms[0]->device(), bottoms[0]->order(), bottoms[0]->allocator());
+    exb_check(exb_hardswish_fwd(h, bottoms[0]->gpu_data(), tops[0]->mutable_gpu_data(), tops[0]->count(), EXB_F32, alpha_,
+                                beta_, nullptr), "exb_hardswish_fwd");
+}
+INSTANCE_CLASS(operation_hardswish);
+REGISTE(operation_hardswish);
+
+template <typename Dtype>
+operation_input<Dtype>::operation_input(const operation_param& param) : operation<Dtype>(param) {
+    auto list_of = [](const std::string& v) {
+        std::vector<float> out;
+        size_t pos = 0;
+        while (pos <= v.size()) {
+            const size_t next = v.find(',', pos);
+            const std::string tok = v.substr(pos, next == std::string::npos ? std::string::npos : next - pos);
+            if (!tok.empty()) out.push_back((float)std::atof(tok.c_str()));
+            if (next == std::string::npos) break;
+            pos = next + 1;
+        }
+        return out;
+    };
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        switch (kv.first) {
+        case 0: w_ = std::atoi(kv.second.c_str()); break;
+        case 1: h_ = std::atoi(kv.second.c_str()); break;
+        case 2: c_ = std::atoi(kv.second.c_str()); break;
+        case 3: means_ = list_of(kv.second); break;
+        case 4:
+            vars_ = list_of(kv.second);
+            if (c_ != 1 && (int)vars_.size() != c_) {   // one value stands for every channel
+                if (!vars_.empty()) vars_.resize(1);
+                for (int i = 1; i < c_; ++i) vars_.push_back(vars_[0]);
+            }
+            break;
+        case -23330: break;
+        default: LOG(FATAL) << "Un-supported Input Attribution " << kv.first;
+        }
+    }
+}
+template <typename Dtype>
+void operation_input<Dtype>::coefficients(int channels, const float** mul, const float** add) {
+    if (channels != 1 && channels != 3) LOG(FATAL) << "Un-supprted channel num: " << channels;
+    CHECK_EQ((size_t)channels, means_.size());
+    CHECK_GE(vars_.size(), (size_t)channels);
+    if (!mul_ || mul_->count() != channels) {
+        const int dev = this->params_.device_;
+        mul_ = make_tensor<float>({channels}, dev, memory::NCHW);
+        add_ = make_tensor<float>({channels}, dev, memory::NCHW);
+        for (int c = 0; c < channels; ++c) {
+            mul_->mutable_cpu_data()[c] = vars_[c];
+            add_->mutable_cpu_data()[c] = -means_[c] * vars_[c];
+        }
+    }
+    *mul = mul_->gpu_data();
+    *add = add_->gpu_data();
+}
+template <typename Dtype>
+void operation_input<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), tops.size());
+    for (size_t i = 0; i < bottoms.size(); ++i) {
+        CHECK(bottoms[i]->order() == memory::NCHW) << "Input expects an NCHW tensor";
+        const float* mul = nullptr;
+        const float* add = nullptr;
+        coefficients(bottoms[i]->channels(), &mul, &add);
+        tops[i] = make_tensor<float>(bottoms[i]->data_shape(), bottoms[i]->device(), memory::NCHW, bottoms[i]->allocator());
+        if (tops[i]->count() == 0) continue;
+        exb_check(exb_channel_affine_fwd(h, bottoms[i]->gpu_data(), tops[i]->mutable_gpu_data(), mul, add, bottoms[i]->num(),
+                                         bottoms[i]->channels(), 0, (int64_t)bottoms[i]->height() * bottoms[i]->width(),
+                                         EXB_F32, 0, EXB_ACT_NONE, nullptr), "exb_channel_affine_fwd");
+    }
+}
+INSTANCE_CLASS(operation_input);
+REGISTE(operation_input);
+
+template <typename Dtype>
+void operation_yolov5focus<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), 1u);
+    CHECK_EQ(tops.size(), 1u);
+    CHECK(bottoms[0]->order() == memory::NCHW) << "YoloV5Focus expects an NCHW tensor";
+    const int N = bottoms[0]->num(), C = bottoms[0]->channels(), H = bottoms[0]->height(), W = bottoms[0]->width();
+    tops[0] = make_tensor<float>({N, 4 * C, H / 2, W / 2}, bottoms[0]->device(), memory::NCHW, bottoms[0]->allocator());
+    if (tops[0]->count() == 0) return;
+    exb_check(exb_focus_fwd(h, bottoms[0]->gpu_data(), tops[0]->mutable_gpu_data(), N, C, H, W, 0, 0, EXB_F32, 0, nullptr),
+              "exb_focus_fwd");
+}
+INSTANCE_CLASS(operation_yolov5focus);
+REGISTE(operation_yolov5focus);
+
 }  // namespace excalibur
 }  // namespace glasssix

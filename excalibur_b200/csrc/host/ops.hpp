@@ -6,6 +6,7 @@
 // ignored (reference src/Excalibur/operation_general_conv.cpp:9-124, operation_pooling.cpp:10-77,
 // operation_eltwise.cpp:11-40, operation_binaryop.cpp:369-391, operation_relu.cpp:9-28).
 #pragma once
+#include <cmath>
 #include "operation.hpp"
 
 namespace glasssix {
@@ -273,6 +274,50 @@ protected:
     virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
     void derive();
     std::shared_ptr<memory::tensor<float>> a_, b_;
+};
+
+// y = x * clamp(alpha*x + beta, 0, 1): keys 0 alpha, 1 beta (reference
+// src/Excalibur/operation_hardswish.cpp:9-28).
+template <typename Dtype>
+class operation_hardswish : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_hardswish(const operation_param& param);
+    virtual const char* type() const { return "HardSwish"; }
+    float alpha_ = 0.f, beta_ = 0.f;
+    // the constants of the activation code EXB_ACT_HARDSWISH
+    bool is_standard() const { return std::fabs(alpha_ - 1.f / 6.f) < 1e-6f && beta_ == 0.5f; }
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
+// Network input normalisation y = (x - mean[c]) * var[c]: keys 0 w, 1 h, 2 c, 3 mean list, 4 var list
+// (reference src/Excalibur/operation_input.cpp:9-58); 1 or 3 channels.
+template <typename Dtype>
+class operation_input : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_input(const operation_param& param);
+    virtual const char* type() const { return "Input"; }
+    int w_ = 0, h_ = 0, c_ = 0;
+    std::vector<float> means_, vars_;
+    // y = x * mul[c] + add[c] with mul = var, add = -mean * var; device arrays of `channels` entries
+    void coefficients(int channels, const float** mul, const float** add);
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    std::shared_ptr<memory::tensor<float>> mul_, add_;
+};
+
+// Space-to-depth 2x2 of YOLOv5's Focus layer, no parameters (reference
+// src/Excalibur/operation_yolov5focus.cpp:16-47); every image of the batch is converted.
+template <typename Dtype>
+class operation_yolov5focus : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_yolov5focus(const operation_param& param) : operation<Dtype>(param) {}
+    virtual const char* type() const { return "YoloV5Focus"; }
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
 };
 
 }  // namespace excalibur

@@ -95,7 +95,7 @@ public:
     std::string unsupported_reason() const {
         static const std::set<std::string> ok = {"convolution", "convolutiondepthwise", "pooling", "eltwise", "binaryop",
                                                   "relu", "split", "innerproduct", "clip", "sigmoid", "concat", "interp",
-                                                 "batchnorm"};
+                                                 "batchnorm", "hardswish", "input", "yolov5focus"};
         for (const auto& p : params_) {
             std::string t = p.type_;
             std::transform(t.begin(), t.end(), t.begin(), ::tolower);
@@ -174,6 +174,7 @@ private:
     std::unordered_map<std::string, int> index_;
     std::vector<plan_step> steps_;
     dev_buf staging_in_;
+    dev_buf norm_in_;                      // normalised fp32 input when the graph starts with an Input op
     dev_buf chunk_stage_;                  // k chunks of fp32 input for run_chunked
     const float* ingest_src_ = nullptr;    // what the ingest step (steps_[0]) reads; never part of the graph
     cudaStream_t copy_stream_ = nullptr;
@@ -248,12 +249,25 @@ void fused_plan::build(int N, int C, int H, int W) {
         for (const auto& n : params_[i].input_featmaps_) in_ids[i].push_back(fid(n));
         for (const auto& n : params_[i].output_featmaps_) out_ids[i].push_back(fid(n));
     }
-    for (size_t i = 0; i < n_ops; ++i)
-        if (lower_type(params_[i]) == "split")
+    // Split outputs alias their input.  So does an Input (normalisation) op that reads the network
+    // input: its arithmetic runs on the fp32 staging buffer in front of the ingest kernel.
+    std::vector<char> alias_op(n_ops, 0);
+    int input_norm_op = -1;
+    for (size_t i = 0; i < n_ops; ++i) {
+        const std::string t = lower_type(params_[i]);
+        if (t == "split") {
+            alias_op[i] = 1;
             for (int o : out_ids[i]) fmaps_[o].root = root(in_ids[i][0]);
+        } else if (t == "input" && input_norm_op < 0 && in_ids[i].size() == 1 && out_ids[i].size() == 1 &&
+                   root(in_ids[i][0]) == root(fid(inputs_[0]))) {
+            alias_op[i] = 1;
+            input_norm_op = (int)i;
+            fmaps_[out_ids[i][0]].root = root(in_ids[i][0]);
+        }
+    }
     std::vector<std::vector<int>> consumers(fmaps_.size());   // by root id -> op indices
     for (size_t i = 0; i < n_ops; ++i) {
-        if (lower_type(params_[i]) == "split") continue;
+        if (alias_op[i]) continue;
         for (int f : in_ids[i]) consumers[root(f)].push_back((int)i);
     }
     std::set<int> output_roots;
@@ -281,6 +295,10 @@ void fused_plan::build(int N, int C, int H, int W) {
         if (t == "clip") {
             auto* c = dynamic_cast<operation_clip<float>*>(ops_[j].get());
             if (c && c->is_relu6()) return EXB_ACT_RELU6;
+        }
+        if (t == "hardswish") {
+            auto* hs = dynamic_cast<operation_hardswish<float>*>(ops_[j].get());
+            if (hs && hs->is_standard()) return EXB_ACT_HARDSWISH;
         }
         return -1;
     };
@@ -398,7 +416,7 @@ void fused_plan::build(int N, int C, int H, int W) {
     };
     for (size_t i = 0; i < n_ops; ++i) {
         const std::string t = lower_type(params_[i]);
-        if (t == "split") continue;
+        if (alias_op[i]) continue;
         if (absorbed[i]) {
             // an absorbed add reads its residual operand as fp16
             continue;
@@ -447,18 +465,34 @@ void fused_plan::build(int N, int C, int H, int W) {
                 }
             }
         }
+        // Input normalisation in front of the ingest kernel: fp32 NCHW staging -> normalised copy.
+        const float* ingest_fixed = nullptr;
+        if (input_norm_op >= 0) {
+            auto* inp = dynamic_cast<operation_input<float>*>(ops_[input_norm_op].get());
+            const float* mul = nullptr;
+            const float* add = nullptr;
+            inp->coefficients(C, &mul, &add);
+            float* norm = static_cast<float*>(norm_in_.ensure((size_t)N * C * H * W * 4, device_));
+            ingest_fixed = norm;
+            add_step(params_[input_norm_op].name_, [=](cudaStream_t st) {
+                exb_check(exb_channel_affine_fwd(ctx, this->ingest_src_, norm, mul, add, N, C, 0, (int64_t)H * W, EXB_F32, 0,
+                                                 EXB_ACT_NONE, st), "exb_channel_affine_fwd");
+            });
+        }
         const bool direct_i8 = in.need_i8 && !in.need_f16;
         void* dst = direct_i8 ? form_i8(in) : form_f16(in);
         const int cs = in.cs, w_pad = in.w_pad, w_pitch = in.w_pitch;
         const float s = in.i8_scale;
         if (padded) {
             add_step("ingest " + in.name, [=](cudaStream_t st) {
-                exb_check(exb_nchw_f32_to_nhwc_padded(ctx, this->ingest_src_, dst, EXB_F16, N, C, H, W, cs, w_pad, w_pitch, 1.f, 1, st),
+                exb_check(exb_nchw_f32_to_nhwc_padded(ctx, ingest_fixed ? ingest_fixed : this->ingest_src_, dst, EXB_F16, N, C, H, W,
+                                                      cs, w_pad, w_pitch, 1.f, 1, st),
                           "exb_nchw_f32_to_nhwc_padded");
             });
         } else {
             add_step("ingest " + in.name, [=](cudaStream_t st) {
-                exb_check(exb_nchw_f32_to_nhwc(ctx, this->ingest_src_, dst, direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs,
+                exb_check(exb_nchw_f32_to_nhwc(ctx, ingest_fixed ? ingest_fixed : this->ingest_src_, dst,
+                                               direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs,
                                                direct_i8 ? s : 1.f, 1, st),
                           "exb_nchw_f32_to_nhwc");
             });
@@ -548,7 +582,7 @@ void fused_plan::build(int N, int C, int H, int W) {
             run_conv_group(groups[run_group_at[i]]);
             continue;
         }
-        if (absorbed[i] || t == "split" || t == "convolution" || t == "convolutiondepthwise") continue;
+        if (absorbed[i] || alias_op[i] || t == "convolution" || t == "convolutiondepthwise") continue;
         fmap_info& x = fmaps_[root(in_ids[i][0])];
         fmap_info& y = fmaps_[root(out_ids[i][0])];
         CHECK(x.produced) << "feature map " << x.name << " is consumed before it is produced";
@@ -637,6 +671,34 @@ void fused_plan::build(int N, int C, int H, int W) {
                 exb_check(exb_interp_nearest_fwd(ctx, xin, yo, n, h, w, c, cs, OH, OW, EXB_F16, 1, st), "exb_interp_nearest_fwd");
             });
             finish_forms(y, false);
+        } else if (t == "yolov5focus") {
+            y.need_f16 = true;
+            set_shape(y, x.N, 4 * x.C, x.H / 2, x.W / 2);
+            const void* xin = form_f16(x);
+            void* yo = form_f16(y);
+            const int n = x.N, c = x.C, h = x.H, w = x.W, ics = x.cs, ocs = y.cs;
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_focus_fwd(ctx, xin, yo, n, c, h, w, ics, ocs, EXB_F16, 1, st), "exb_focus_fwd");
+            });
+            finish_forms(y, false);
+        } else if (t == "input") {
+            // an Input op that is not at the network input: per-channel affine on the fp16 form
+            auto* inp = dynamic_cast<operation_input<float>*>(ops_[i].get());
+            y.need_f16 = true;
+            set_shape(y, x.N, x.C, x.H, x.W);
+            y.cs = x.cs;
+            const void* xin = form_f16(x);
+            void* yo = form_f16(y);
+            const float* mul = nullptr;
+            const float* add = nullptr;
+            inp->coefficients(x.C, &mul, &add);
+            const int64_t rows = (int64_t)x.N * x.H * x.W;
+            const int c = x.C, cs = x.cs;
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_channel_affine_fwd(ctx, xin, yo, mul, add, rows, c, cs, 1, EXB_F16, 1, EXB_ACT_NONE, st),
+                          "exb_channel_affine_fwd");
+            });
+            finish_forms(y, false);
         } else if (t == "batchnorm") {
             auto* bn = dynamic_cast<operation_batchnorm<float>*>(ops_[i].get());
             CHECK_EQ(x.C, bn->channels_);
@@ -661,7 +723,14 @@ void fused_plan::build(int N, int C, int H, int W) {
             y.cs = x.cs;
             const int64_t count = (int64_t)x.N * x.H * x.W * x.cs;
             void* yo = form_f16(y);
-            if (t == "relu" || t == "clip" || t == "sigmoid") {
+            if (t == "hardswish" && act_of_op((int)i) < 0) {
+                auto* hs = dynamic_cast<operation_hardswish<float>*>(ops_[i].get());
+                const float alpha = hs->alpha_, beta = hs->beta_;
+                const void* xin = form_f16(x);
+                add_step(params_[i].name_, [=](cudaStream_t st) {
+                    exb_check(exb_hardswish_fwd(ctx, xin, yo, count, EXB_F16, alpha, beta, st), "exb_hardswish_fwd");
+                });
+            } else if (t == "relu" || t == "clip" || t == "sigmoid" || t == "hardswish") {
                 const int act = act_of_op((int)i);
                 if (act < 0) NOT_IMPLEMENTED << " (" << params_[i].type_ << " parameters)";
                 const void* xin = form_f16(x);

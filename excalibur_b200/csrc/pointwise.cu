@@ -171,6 +171,10 @@ struct ActFn {
     int act;
     __device__ float operator()(float v) const { return apply_act(v, act); }
 };
+struct HardSwishFn {
+    float alpha, beta;
+    __device__ float operator()(float v) const { return v * fminf(fmaxf(fmaf(v, alpha, beta), 0.f), 1.f); }
+};
 struct ReluFn {
     __device__ float operator()(float v) const { return v >= 0.f ? v : 0.f; }
 };
@@ -227,6 +231,11 @@ extern "C" int exb_activation_fwd(exb_ctx* ctx, int act, const void* x, void* y,
                                   int dtype, void* stream) {
     if (!act_supported(act)) return fail(EXB_ERR_UNSUPPORTED, "activation type %d is not implemented", act);
     return launch_map1(ctx, x, y, count, dtype, stream, ActFn{act}, "exb_activation_fwd");
+}
+
+extern "C" int exb_hardswish_fwd(exb_ctx* ctx, const void* x, void* y, int64_t count, int dtype, float alpha,
+                                 float beta, void* stream) {
+    return launch_map1(ctx, x, y, count, dtype, stream, HardSwishFn{alpha, beta}, "exb_hardswish_fwd");
 }
 
 extern "C" int exb_binaryop_scalar_fwd(exb_ctx* ctx, int op, const void* a, float scalar, void* y,

@@ -117,6 +117,17 @@ class GraphBuilder:
     def sigmoid(self, name, x, y):
         return self._op("Sigmoid", name, [x], [y])
 
+    def hardswish(self, name, x, y, alpha=1.0 / 6.0, beta=0.5):
+        return self._op("HardSwish", name, [x], [y], "0=%r 1=%r" % (float(alpha), float(beta)))
+
+    def input_norm(self, name, x, y, w, h, means, scales):
+        """y = (x - means[c]) * scales[c] (the reference calls the multipliers 'vars')."""
+        return self._op("Input", name, [x], [y], "0=%d 1=%d 2=%d 3=%s 4=%s" % (
+            w, h, len(means), ",".join(repr(float(m)) for m in means), ",".join(repr(float(v)) for v in scales)))
+
+    def focus(self, name, x, y):
+        return self._op("YoloV5Focus", name, [x], [y])
+
     def split(self, name, x, outs):
         return self._op("Split", name, [x], list(outs))
 

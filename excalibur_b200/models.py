@@ -261,6 +261,24 @@ def yolov5s(seed=5, num_outputs=255, in_ch=3, width=(32, 64, 128, 256, 512), dep
     return g, {"input": "data", "outputs": outs}
 
 
+def focus_net(seed=7):
+    """A small YOLOv5-v5-style front end: Input normalisation -> YoloV5Focus (space-to-depth) ->
+    3x3 conv 12->32 + HardSwish -> 3x3/2 conv 32->64 + HardSwish -> 1x1 conv 64->16 ("out")."""
+    g = GraphBuilder("focus_net")
+    wts = _Weights(seed)
+    g.input_norm("inp", "data", "data_n", 32, 32, [123.675, 116.28, 103.53], [0.0171, 0.0175, 0.0174])
+    g.focus("focus", "data_n", "f0")
+    w, b = wts.conv_bn(32, 12, 3)
+    g.conv("c1", "f0", "c1_out", w, b, 1, 1)
+    g.hardswish("h1", "c1_out", "h1_out")
+    w, b = wts.conv_bn(64, 32, 3)
+    g.conv("c2", "h1_out", "c2_out", w, b, 2, 1)
+    g.hardswish("h2", "c2_out", "h2_out")
+    w, b = wts.conv_bn(16, 64, 1)
+    g.conv("c3", "h2_out", "out", w, b, 1, 0)
+    return g
+
+
 def calibrate(float_pipeline, conv_inputs, images):
     """fs = 127 / max|x| over the calibration images for every conv input (max-abs calibration).
     `float_pipeline` is any object with forward(x) and get(name) -> NCHW fp32 (the reference

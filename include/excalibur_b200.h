@@ -51,7 +51,8 @@ typedef enum exb_act {
     EXB_ACT_RELU6_QUIRK = 3, /* reference behaviour: x > 6 -> 0 */
     EXB_ACT_SIGMOID = 4,
     EXB_ACT_RELU6 = 103,
-    EXB_ACT_SILU = 104
+    EXB_ACT_SILU = 104,
+    EXB_ACT_HARDSWISH = 105   /* x * clamp(x/6 + 0.5, 0, 1): HardSwish with alpha = 1/6, beta = 0.5 */
 } exb_act;
 
 typedef struct exb_ctx exb_ctx;                   /* per-device context */
@@ -329,6 +330,17 @@ EXB_API int exb_dequantize_fwd(exb_ctx* ctx, const int8_t* q, void* y, int out_d
  * padding channels are written as 0); channel_last 0: x is [outer][C][inner] (outer = N,
  * inner = H*W).  EXB_F16 or EXB_F32; y may alias x.
  * ------------------------------------------------------------------------------------- */
+/* y = x * clamp(alpha*x + beta, 0, 1): operation_hardswish (src/Excalibur/operation_hardswish.cpp:34-71,
+ * src/Excalibur/cuda/operation_hardswish.cu:10-36).  EXB_F16 or EXB_F32. */
+EXB_API int exb_hardswish_fwd(exb_ctx* ctx, const void* x, void* y, int64_t count, int dtype, float alpha,
+                              float beta, void* stream);
+/* Space-to-depth of operation_yolov5focus (src/Excalibur/operation_yolov5focus.cpp:16-47):
+ * out[n][g*C + c][i][j] = in[n][c][2i + g%2][2j + g/2], g = 0..3, output H/2 x W/2 with 4*C channels.
+ * Every image of the batch is converted (the reference only converts image 0).
+ * channel_last 0: fp32 NCHW; channel_last 1: NHWC with in_stride / out_stride physical channels
+ * (EXB_F16, EXB_I8 or EXB_F32; padding channels of the output are written as 0). */
+EXB_API int exb_focus_fwd(exb_ctx* ctx, const void* x, void* y, int N, int C, int H, int W, int in_stride,
+                          int out_stride, int dtype, int channel_last, void* stream);
 EXB_API int exb_concat_fwd(exb_ctx* ctx, int n_in, const void* const* xs, const int64_t* widths,
                            const int64_t* x_strides, void* y, int64_t y_stride, int64_t rows,
                            int dtype, void* stream);

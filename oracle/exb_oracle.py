@@ -233,6 +233,33 @@ def channel_affine(x, mul, add):
     return (x * _f32(mul)[None, :, None, None] + _f32(add)[None, :, None, None]).astype(np.float32)
 
 
+def hardswish(x, alpha=1.0 / 6.0, beta=0.5):
+    """y = x * min(max(0, alpha*x + beta), 1): src/Excalibur/operation_hardswish.cpp:58-62 (the AVX
+    body fuses alpha*x + beta into one fma; both forms are within 1 ulp of each other)."""
+    x = _f32(x)
+    t = (np.float32(alpha) * x + np.float32(beta)).astype(np.float32)
+    return (x * np.minimum(np.maximum(t, np.float32(0)), np.float32(1))).astype(np.float32)
+
+
+def input_norm(x, means, scales):
+    """y = (x - means[c]) * scales[c]: src/Excalibur/operation_input.cpp:92-96."""
+    x = _f32(x)
+    m = _f32(means)[None, :, None, None]
+    v = _f32(scales)[None, :, None, None]
+    return ((x - m) * v).astype(np.float32)
+
+
+def focus(x):
+    """out[n][g*C + c][i][j] = in[n][c][2i + g%2][2j + g/2]: src/Excalibur/operation_yolov5focus.cpp:27-41
+    (applied to every image; the reference only fills image 0)."""
+    x = _f32(x)
+    n, c, h, w = x.shape
+    out = np.empty((n, 4 * c, h // 2, w // 2), np.float32)
+    for g in range(4):
+        out[:, g * c:(g + 1) * c] = x[:, :, (g % 2):(h // 2) * 2:2, (g // 2):(w // 2) * 2:2]
+    return out
+
+
 # ---- layout helpers -------------------------------------------------------------------
 def nchw_to_nhwc(a):
     return np.ascontiguousarray(np.transpose(a, (0, 2, 3, 1)))

@@ -173,6 +173,32 @@ def yolo():
         out["bn_" + n] = bn[k]
     out["bn_out"], = run(g, x)
 
+    # HardSwish (standard and ncnn-style constants), Input normalisation, YoloV5Focus (batch 1: the
+    # reference only fills image 0), and a small Input -> Focus -> Conv -> HardSwish -> Conv net
+    x = (r.standard_normal((2, 5, 6, 7)) * 4).astype(np.float32)
+    out["hs_x"] = x
+    g = GraphBuilder(); g.hardswish("h", "in", "out")
+    out["hs_std_out"], = run(g, x)
+    g = GraphBuilder(); g.hardswish("h", "in", "out", 0.2, 0.5)
+    out["hs_02_out"], = run(g, x)
+    x = r.uniform(0, 255, (2, 3, 8, 10)).astype(np.float32)
+    means, scales = [123.675, 116.28, 103.53], [0.0171, 0.0175, 0.0174]
+    g = GraphBuilder(); g.input_norm("inp", "in", "out", 10, 8, means, scales)
+    out["inp_x"] = x
+    out["inp_means"] = np.array(means, np.float32)
+    out["inp_scales"] = np.array(scales, np.float32)
+    out["inp_out"], = run(g, x)
+    x = r.standard_normal((1, 3, 10, 12)).astype(np.float32)
+    g = GraphBuilder(); g.focus("f", "in", "out")
+    out["focus_x"] = x
+    out["focus_out"], = run(g, x)
+    x = r.uniform(0, 255, (1, 3, 32, 32)).astype(np.float32)
+    g = models.focus_net(7)
+    pf = ref_lib.RefPipeline(g.phai_text(), g.racy_bytes())
+    out["fnet_x"] = x
+    out["fnet_out"] = pf.forward(x)["out"]
+    pf.close()
+
     x = np.random.default_rng(5000).uniform(0, 1, (2, 3, 128, 128)).astype(np.float32)
     gy, info = models.yolov5s(5)
     py = ref_lib.RefPipeline(gy.phai_text(), gy.racy_bytes())

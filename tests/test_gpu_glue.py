@@ -100,3 +100,33 @@ def test_channel_affine(ctx, shape):
     yr = host(capi.channel_affine(ctx, dev(x), dev(mul), dev(add), channel_last=False, act=capi.ACT_RELU))
     np.testing.assert_allclose(yr, np.maximum(ref, 0), rtol=2e-7, atol=3e-7)
     ctx.sync_check()
+
+
+@pytest.mark.parametrize("alpha,beta", [(1.0 / 6.0, 0.5), (0.2, 0.5)])
+def test_hardswish(ctx, alpha, beta):
+    capi = _capi()
+    x = (rng(9).standard_normal(100003) * 4).astype(np.float32)
+    y = host(capi.hardswish(ctx, dev(x), alpha, beta))
+    np.testing.assert_allclose(y, O.hardswish(x, alpha, beta), rtol=0, atol=5e-7)
+    xh = f16_round(x)
+    yh = host(capi.hardswish(ctx, dev(xh.astype(np.float16)), alpha, beta)).astype(np.float32)
+    np.testing.assert_allclose(yh, O.hardswish(xh, alpha, beta), rtol=1e-3, atol=1e-3)
+    if alpha != 0.2:    # the activation code used by fused convolutions
+        ya = host(capi.activation(ctx, dev(x), capi.ACT_HARDSWISH))
+        np.testing.assert_allclose(ya, O.hardswish(x), rtol=0, atol=5e-7)
+    ctx.sync_check()
+
+
+@pytest.mark.parametrize("shape", [(1, 3, 10, 12), (3, 3, 64, 48), (2, 5, 7, 9)])
+def test_focus(ctx, shape):
+    capi = _capi()
+    x = rng(shape[2]).standard_normal(shape).astype(np.float32)
+    ref = O.focus(x)
+    np.testing.assert_array_equal(host(capi.focus(ctx, dev(x), channel_last=False)), ref)
+    cs_in, cs_out = 8, (4 * shape[1] + 15) // 16 * 16
+    xh = _nhwc_padded(f16_round(x), cs_in, np.float16)
+    y = host(capi.focus(ctx, dev(xh), channels=shape[1], out_stride=cs_out))
+    assert y.shape == (shape[0], shape[2] // 2, shape[3] // 2, cs_out)
+    np.testing.assert_array_equal(y[..., :4 * shape[1]].astype(np.float32), O.nchw_to_nhwc(O.focus(f16_round(x))))
+    assert not y[..., 4 * shape[1]:].any()
+    ctx.sync_check()

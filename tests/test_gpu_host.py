@@ -279,3 +279,32 @@ def test_chunked_forward_equals_whole_batch_forward():
     np.testing.assert_array_equal(p.forward(x)["logits"], whole)
     assert p.run_resident(2) > 0
     p.close()
+
+
+def test_operation_hardswish_input_focus():
+    h = _host()
+    np.testing.assert_allclose(h.run_op("HardSwish", "0=%r 1=0.5" % (1.0 / 6.0), [Y["hs_x"]]), Y["hs_std_out"], rtol=0, atol=5e-7)
+    np.testing.assert_allclose(h.run_op("HardSwish", "0=0.2 1=0.5", [Y["hs_x"]]), Y["hs_02_out"], rtol=0, atol=5e-7)
+    g = GraphBuilder()
+    g.input_norm("inp", "in", "out", 10, 8, Y["inp_means"], Y["inp_scales"])
+    y = h.run_op("Input", g.lines[0].split(" ", 6)[6], [Y["inp_x"]])
+    np.testing.assert_allclose(y, Y["inp_out"], rtol=2e-6, atol=2e-6)    # x*v - m*v against (x - m)*v
+    np.testing.assert_array_equal(h.run_op("YoloV5Focus", "", [Y["focus_x"]]), Y["focus_out"])
+    both = np.concatenate([Y["focus_x"], Y["focus_x"][:, ::-1]])          # every image is converted
+    np.testing.assert_array_equal(h.run_op("YoloV5Focus", "", [both]), O.focus(both))
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_focus_net(fusion):
+    """Input normalisation -> Focus -> conv + HardSwish x 2 -> conv against the reference's output."""
+    h = _host()
+    g = models.focus_net(7)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    for _ in range(3):
+        out = p.forward(Y["fnet_x"])["out"]
+    assert out.shape == Y["fnet_out"].shape
+    assert _rel(out, Y["fnet_out"]) < 1e-2, _rel(out, Y["fnet_out"])
+    if fusion:
+        launches, _ = p.stats()
+        assert launches == 7       # normalise, ingest, focus, 3 convs (HardSwish folded into two), emit
+    p.close()

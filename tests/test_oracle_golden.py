@@ -98,3 +98,10 @@ def test_batchnorm():
     b, a = O.batchnorm_coeffs(Y["bn_slope"], Y["bn_mean"], Y["bn_var"], Y["bn_bias"], 1e-5)
     # the reference's loop may or may not contract b*x + a into one fma
     np.testing.assert_allclose(O.channel_affine(Y["bn_x"], b, a), Y["bn_out"], rtol=2e-7, atol=3e-7)
+
+
+def test_hardswish_input_focus():
+    np.testing.assert_allclose(O.hardswish(Y["hs_x"]), Y["hs_std_out"], rtol=0, atol=5e-7)
+    np.testing.assert_allclose(O.hardswish(Y["hs_x"], 0.2, 0.5), Y["hs_02_out"], rtol=0, atol=5e-7)
+    np.testing.assert_array_equal(O.input_norm(Y["inp_x"], Y["inp_means"], Y["inp_scales"]), Y["inp_out"])
+    np.testing.assert_array_equal(O.focus(Y["focus_x"]), Y["focus_out"])
