@@ -5,6 +5,7 @@
 #include "ops.hpp"
 
 #include <cmath>
+#include <limits>
 #include <random>
 
 namespace glasssix {
@@ -220,27 +221,52 @@ exb_conv_desc operation_convolution<Dtype>::base_desc(int N, int H, int W) const
 }
 
 template <typename Dtype>
-exb_conv_weights* operation_convolution<Dtype>::packed(exb_ctx* ctx, const exb_conv_desc& d) {
+exb_conv_weights* operation_convolution<Dtype>::packed(exb_ctx* ctx, const exb_conv_desc& d, const float* post_mul,
+                                                       const float* post_add, const void* tag) {
     const int cin_stride = d.cin_stride ? d.cin_stride : d.Cin;
     const int cout_stride = d.cout_stride ? d.cout_stride : d.Cout;
     for (auto& e : packed_)
         if (e.in_dtype == d.in_dtype && e.cin_stride == cin_stride && e.cout_stride == cout_stride &&
-            e.w_pitch == d.x_w_pitch && e.w_pad == d.x_w_pad)
+            e.w_pitch == d.x_w_pitch && e.w_pad == d.x_w_pad && e.tag == tag)
             return e.w;
     exb_conv_weights* w = nullptr;
+    const int Cout = this->output_channel_;
     const float* bias = this->bias_term_ ? this->weights_f32_[1]->cpu_data() : nullptr;
+    std::vector<float> fbias, fw, fscale;
+    if (post_mul) {     // (conv + bias) * mul + add
+        fbias.resize(Cout);
+        for (int c = 0; c < Cout; ++c) fbias[c] = (bias ? bias[c] : 0.f) * post_mul[c] + (post_add ? post_add[c] : 0.f);
+        bias = fbias.data();
+    }
     if (d.in_dtype == EXB_I8) {
         CHECK(is_int8()) << "int8 convolution requested but the weights are fp32";
-        exb_check(exb_conv_weights_pack_i8(ctx, &d, this->weights_i8_[0]->cpu_data(), bias,
-                                           this->weights_scaletable_i8_->cpu_data(),
-                                           this->weights_scaletable_i8_->count(), act_scale(), &w),
+        const float* ws = this->weights_scaletable_i8_->cpu_data();
+        int n_ws = this->weights_scaletable_i8_->count();
+        if (post_mul) {
+            // the dequantise multiplier is 1 / (ws * fs): dividing ws by mul multiplies the result by mul
+            fscale.resize(Cout);
+            for (int c = 0; c < Cout; ++c) {
+                const float w0 = ws[n_ws == 1 ? 0 : c];
+                fscale[c] = post_mul[c] != 0.f ? w0 / post_mul[c] : std::numeric_limits<float>::infinity();
+            }
+            ws = fscale.data();
+            n_ws = Cout;
+        }
+        exb_check(exb_conv_weights_pack_i8(ctx, &d, this->weights_i8_[0]->cpu_data(), bias, ws, n_ws, act_scale(), &w),
                   "exb_conv_weights_pack_i8");
     } else {
         CHECK(!is_int8()) << "fp16 convolution requested but the weights are int8";
-        exb_check(exb_conv_weights_pack_f16(ctx, &d, this->weights_f32_[0]->cpu_data(), bias, &w),
-                  "exb_conv_weights_pack_f16");
+        const float* wsrc = this->weights_f32_[0]->cpu_data();
+        if (post_mul) {
+            const size_t per = (size_t)this->weights_f32_[0]->count() / Cout;
+            fw.resize((size_t)Cout * per);
+            for (int c = 0; c < Cout; ++c)
+                for (size_t k = 0; k < per; ++k) fw[c * per + k] = wsrc[c * per + k] * post_mul[c];
+            wsrc = fw.data();
+        }
+        exb_check(exb_conv_weights_pack_f16(ctx, &d, wsrc, bias, &w), "exb_conv_weights_pack_f16");
     }
-    packed_.push_back({d.in_dtype, cin_stride, cout_stride, d.x_w_pitch, d.x_w_pad, w});
+    packed_.push_back({d.in_dtype, cin_stride, cout_stride, d.x_w_pitch, d.x_w_pad, w, tag});
     return w;
 }
 
@@ -355,14 +381,30 @@ exb_dwconv_desc operation_convolutiondepthwise<Dtype>::dw_desc(int N, int H, int
 }
 
 template <typename Dtype>
-exb_dw_weights* operation_convolutiondepthwise<Dtype>::dw_packed(exb_ctx* ctx, const exb_dwconv_desc& d) {
+exb_dw_weights* operation_convolutiondepthwise<Dtype>::dw_packed(exb_ctx* ctx, const exb_dwconv_desc& d, const float* post_mul,
+                                                                 const float* post_add, const void* tag) {
     const int cs = d.c_stride ? d.c_stride : d.C;
-    if (dw_w_ && dw_cs_ == cs) return dw_w_;
+    if (dw_w_ && dw_cs_ == cs && dw_tag_ == tag) return dw_w_;
     if (dw_w_) exb_dw_weights_destroy(dw_w_);
     dw_w_ = nullptr;
     const float* bias = this->bias_term_ ? this->weights_f32_[1]->cpu_data() : nullptr;
-    exb_check(exb_dw_weights_pack(ctx, &d, dw_weights_f32(), bias, &dw_w_), "exb_dw_weights_pack");
+    const float* wsrc = dw_weights_f32();
+    std::vector<float> fw, fbias;
+    if (post_mul) {
+        const int C = d.C;
+        const size_t per = (size_t)d.kh * d.kw;
+        fw.resize((size_t)C * per);
+        fbias.resize(C);
+        for (int c = 0; c < C; ++c) {
+            for (size_t k = 0; k < per; ++k) fw[c * per + k] = wsrc[c * per + k] * post_mul[c];
+            fbias[c] = (bias ? bias[c] : 0.f) * post_mul[c] + (post_add ? post_add[c] : 0.f);
+        }
+        wsrc = fw.data();
+        bias = fbias.data();
+    }
+    exb_check(exb_dw_weights_pack(ctx, &d, wsrc, bias, &dw_w_), "exb_dw_weights_pack");
     dw_cs_ = cs;
+    dw_tag_ = tag;
     return dw_w_;
 }
 

@@ -54,7 +54,11 @@ public:
     int in_channels() const { return this->input_channel_; }
     float act_scale() const;                  // the conv's input quantisation multiplier (int8)
     // Packed weights for a given input layout; cached per (in_dtype, cin_stride, cout_stride).
-    exb_conv_weights* packed(exb_ctx* ctx, const exb_conv_desc& d);
+    // post_mul / post_add (Cout entries each, or null): a per-channel affine map applied to the conv's
+    // result, folded into the packed weights / epilogue constants (an inference BatchNorm behind the
+    // conv: y = (conv + bias) * post_mul + post_add).  `tag` identifies the map in the cache.
+    exb_conv_weights* packed(exb_ctx* ctx, const exb_conv_desc& d, const float* post_mul = nullptr,
+                             const float* post_add = nullptr, const void* tag = nullptr);
     // Descriptor skeleton for an input of N x H x W (dtypes / fusion fields left to the caller).
     exb_conv_desc base_desc(int N, int H, int W) const;
     // Drop the fp32 host weights that only a CPU path would read (keeps bias and scales).
@@ -66,7 +70,7 @@ protected:
     virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
     void forward_nchw_f32(exb_ctx* h, const f32_list& bottoms, f32_list& tops, bool int8);
 
-    struct packed_entry { int in_dtype, cin_stride, cout_stride, w_pitch, w_pad; exb_conv_weights* w; };
+    struct packed_entry { int in_dtype, cin_stride, cout_stride, w_pitch, w_pad; exb_conv_weights* w; const void* tag; };
     std::vector<packed_entry> packed_;
     device_scratch scratch_in_, scratch_out_;
 };
@@ -79,7 +83,8 @@ public:
     explicit operation_convolutiondepthwise(const operation_param& param);
     virtual ~operation_convolutiondepthwise();
     exb_dwconv_desc dw_desc(int N, int H, int W, int c_stride) const;
-    exb_dw_weights* dw_packed(exb_ctx* ctx, const exb_dwconv_desc& d);
+    exb_dw_weights* dw_packed(exb_ctx* ctx, const exb_dwconv_desc& d, const float* post_mul = nullptr,
+                              const float* post_add = nullptr, const void* tag = nullptr);
     // fp32 [C][kh][kw] weights; int8 files are dequantised once, like the reference
     // (src/Excalibur/operation_convolutiondepthwise.cpp:184-222).
     const float* dw_weights_f32();
@@ -90,6 +95,7 @@ protected:
     virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
     exb_dw_weights* dw_w_ = nullptr;
     int dw_cs_ = 0;
+    const void* dw_tag_ = nullptr;
     std::vector<float> dequantized_;
 };
 

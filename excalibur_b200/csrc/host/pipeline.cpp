@@ -279,6 +279,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         int residual = -1;      // root featmap added in the epilogue
         int act = EXB_ACT_NONE;
         int pool = -1;          // 3x3/2 max pooling op applied in the conv epilogue
+        int bn = -1;            // BatchNorm op folded into the conv's weights and bias
         int out = -1;           // root featmap the group finally produces
         int exec_at = -1;       // index of the last absorbed op
     };
@@ -344,6 +345,18 @@ void fused_plan::build(int N, int C, int H, int W) {
         g.out = root(out_ids[i][0]);
         g.exec_at = (int)i;
         int j, sj = -1, mk = -1;
+        // Conv -> BatchNorm: (conv + bias) * b + a is folded into the packed weights; what follows the
+        // BatchNorm (activation, residual add) can then be fused as if it followed the conv.
+        if (g.act == EXB_ACT_NONE && (j = sole_consumer(g.out)) >= 0 && !absorbed[j] &&
+            lower_type(params_[j]) == "batchnorm") {
+            auto* bn = dynamic_cast<operation_batchnorm<float>*>(ops_[j].get());
+            if (bn && bn->channels_ == conv->output_channel_) {
+                g.bn = j;
+                absorbed[j] = 1;
+                g.out = root(out_ids[j][0]);
+                g.exec_at = j;
+            }
+        }
         if (g.act == EXB_ACT_NONE && silu_pattern(g.out, &sj, &mk)) {
             g.act = EXB_ACT_SILU;
             absorbed[sj] = absorbed[mk] = 1;
@@ -519,7 +532,10 @@ void fused_plan::build(int N, int C, int H, int W) {
             y.cs = x.cs;
             const void* xin = form_f16(x);
             void* yo = form_f16(y);
-            exb_dw_weights* w = dw->dw_packed(ctx, d);
+            const operation_batchnorm<float>* bn =
+                g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;
+            exb_dw_weights* w = bn ? dw->dw_packed(ctx, d, bn->mul()->cpu_data(), bn->add()->cpu_data(), bn)
+                                   : dw->dw_packed(ctx, d);
             add_step(params_[i].name_, [=](cudaStream_t st) {
                 exb_check(exb_dwconv2d_fwd(ctx, &d, xin, w, yo, st), "exb_dwconv2d_fwd");
             });
@@ -569,7 +585,10 @@ void fused_plan::build(int N, int C, int H, int W) {
             y1 = form_i8(y);
             wrote_i8 = true;
         }
-        exb_conv_weights* w = conv->packed(ctx, d);
+        const operation_batchnorm<float>* bn =
+            g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;
+        exb_conv_weights* w = bn ? conv->packed(ctx, d, bn->mul()->cpu_data(), bn->add()->cpu_data(), bn)
+                                 : conv->packed(ctx, d);
         add_step(params_[i].name_, [=](cudaStream_t st) {
             exb_check(exb_conv2d_fwd(ctx, &d, xin, w, res, y1, y2, st), "exb_conv2d_fwd");
         });

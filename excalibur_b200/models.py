@@ -261,6 +261,29 @@ def yolov5s(seed=5, num_outputs=255, in_ch=3, width=(32, 64, 128, 256, 512), dep
     return g, {"input": "data", "outputs": outs}
 
 
+def bn_net(seed=8):
+    """Convolutions followed by explicit BatchNorm operations (not folded by the exporter): conv 3x3
+    3->16 -> BN -> ReLU -> depthwise 3x3 -> BN -> Clip(0,6) -> conv 1x1 16->24 -> BN ("out")."""
+    g = GraphBuilder("bn_net")
+    r = _tensor_rng(seed, 0)
+
+    def bn(name, x, y, c):
+        g.batchnorm(name, x, y, r.uniform(0.5, 1.5, c).astype(np.float32), (r.standard_normal(c) * 0.2).astype(np.float32),
+                    r.uniform(0.5, 2.0, c).astype(np.float32), (r.standard_normal(c) * 0.2).astype(np.float32), eps=1e-5)
+        return y
+
+    w = (r.standard_normal((16, 3, 3, 3)) * np.sqrt(2.0 / 27)).astype(np.float32)
+    g.conv("c1", "data", "c1_out", w, (r.standard_normal(16) * 0.1).astype(np.float32), 1, 1)
+    g.relu("r1", bn("bn1", "c1_out", "bn1_out", 16), "r1_out")
+    wd = (r.standard_normal((16, 1, 3, 3)) * np.sqrt(2.0 / 9)).astype(np.float32)
+    g.dwconv("dw", "r1_out", "dw_out", wd, None, 1, 1)
+    g.clip("cl", bn("bn2", "dw_out", "bn2_out", 16), "cl_out", 0.0, 6.0)
+    w = (r.standard_normal((24, 16, 1, 1)) * np.sqrt(2.0 / 16)).astype(np.float32)
+    g.conv("c3", "cl_out", "c3_out", w, None, 1, 0)
+    bn("bn3", "c3_out", "out", 24)
+    return g
+
+
 def focus_net(seed=7):
     """A small YOLOv5-v5-style front end: Input normalisation -> YoloV5Focus (space-to-depth) ->
     3x3 conv 12->32 + HardSwish -> 3x3/2 conv 32->64 + HardSwish -> 1x1 conv 64->16 ("out")."""

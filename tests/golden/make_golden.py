@@ -199,6 +199,13 @@ def yolo():
     out["fnet_out"] = pf.forward(x)["out"]
     pf.close()
 
+    x = r.uniform(0, 1, (2, 3, 20, 24)).astype(np.float32)
+    g = models.bn_net(8)
+    pb = ref_lib.RefPipeline(g.phai_text(), g.racy_bytes())
+    out["bnnet_x"] = x
+    out["bnnet_out"] = pb.forward(x)["out"]
+    pb.close()
+
     x = np.random.default_rng(5000).uniform(0, 1, (2, 3, 128, 128)).astype(np.float32)
     gy, info = models.yolov5s(5)
     py = ref_lib.RefPipeline(gy.phai_text(), gy.racy_bytes())

@@ -308,3 +308,21 @@ def test_focus_net(fusion):
         launches, _ = p.stats()
         assert launches == 7       # normalise, ingest, focus, 3 convs (HardSwish folded into two), emit
     p.close()
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_batchnorm_after_conv_is_folded(fusion):
+    """Conv -> BatchNorm (-> ReLU / Clip) chains: the fused plan folds every BatchNorm into the packed
+    weights of the conv in front of it (5 launches: ingest, 3 convs, emit)."""
+    h = _host()
+    g = models.bn_net(8)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    for _ in range(3):
+        out = p.forward(Y["bnnet_x"])["out"]
+    assert out.shape == Y["bnnet_out"].shape
+    assert _rel(out, Y["bnnet_out"]) < 1e-2, _rel(out, Y["bnnet_out"])
+    assert_close_f16(out, Y["bnnet_out"], rel=2e-2, what="bn_net out")
+    if fusion:
+        launches, _ = p.stats()
+        assert launches == 5, launches
+    p.close()
