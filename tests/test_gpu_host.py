@@ -326,3 +326,26 @@ def test_batchnorm_after_conv_is_folded(fusion):
         launches, _ = p.stats()
         assert launches == 5, launches
     p.close()
+
+
+def test_calibration_tool_reproduces_the_builder_int8_graph():
+    """python -m excalibur_b200.calibrate on the floating-point ResNet files gives the weight blob the
+    graph builder writes for the same scales, and a pipeline that runs."""
+    from excalibur_b200 import calibrate
+    g32, info = models.resnet18(2)
+    calib = np.random.default_rng(2007).uniform(0, 1, (4, 3, 64, 64)).astype(np.float32)
+    text8, blob8, scales = calibrate.convert(g32.phai_text(), g32.racy_bytes(), calib)
+    assert sorted(scales) == sorted(info["conv_inputs"])
+    g8, _ = models.resnet18(2, act_scales=scales)
+    assert blob8 == g8.racy_bytes()
+    _, ops_a = calibrate.parse_phai(text8)
+    _, ops_b = calibrate.parse_phai(g8.phai_text())
+    assert [(o["type"], o["name"], o["ins"], o["outs"], o["params"]) for o in ops_a] == \
+           [(o["type"], o["name"], o["ins"], o["outs"], o["params"]) for o in ops_b]
+    h = _host()
+    p = h.Pipeline(text8, blob8, 0, fusion=True)
+    out = p.forward(G["resnet_x"])["logits"].reshape(2, -1)
+    p.close()
+    for n, s in zip(G["resnet_scale_names"], G["resnet_scales"]):      # the reference's own calibration
+        assert abs(scales[str(n)] / s - 1.0) < 1e-2
+    assert _rel(out, G["resnet_i8_logits"]) < 5e-2

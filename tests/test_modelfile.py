@@ -45,3 +45,21 @@ def test_resnet18_builder_counts():
     assert macs["total"] == 1814073344 and macs["conv3x3"] == 1676279808
     wq, ws = models.quantize_weights(np.array([[[[0.5]], [[-2.0]]]], np.float32))
     assert ws[0] == np.float32(63.5) and list(wq.reshape(-1)) == [32, -127]
+
+
+def test_calibrate_reader_walks_every_weight_record():
+    """The .phai / .racy reader of the calibration tool accounts for every byte of the weight blob of
+    the floating-point and int8 benchmark graphs and reproduces the op lines it parsed."""
+    from excalibur_b200 import calibrate, models
+    scales = None
+    g32, info = models.resnet18(2)
+    graphs = [g32, models.mobilenet_v2(3)[0], models.yolov5s(5)[0], models.bn_net(8), models.focus_net(7),
+              models.resnet18(2, act_scales={k: 30.0 for k in info["conv_inputs"]})[0]]
+    for g in graphs:
+        head, ops = calibrate.parse_phai(g.phai_text())
+        assert [calibrate.op_line(op) for op in ops] == g.lines
+        pos = 0
+        blob = g.racy_bytes()
+        for op in ops:
+            pos += calibrate.racy_record_size(op, blob, pos)
+        assert pos == len(blob)
