@@ -309,6 +309,11 @@ def run_gpu_arm(args, rank, world, local_rank):
         return sharding.max_over_ranks(v, dist, "cuda")
 
     g8, scales = build_int8_net_gpu(local_rank)
+    # one rank per GPU: keep this rank's pinned input and its copy submissions on the GPU's NUMA node
+    numa_cpus = None
+    if world > 1:
+        from excalibur_b200 import sharding
+        numa_cpus = sharding.bind_host_thread_to_gpu(local_rank)
     pipe = host.Pipeline(g8.phai_text(), g8.racy_bytes(), local_rank, fusion=True, cuda_graph=not args.no_graph)
     x = torch.empty((BATCH, 3, IMG, IMG), dtype=torch.float32).pin_memory()
     gen = torch.Generator().manual_seed(SEED * 1000 + 100 + rank)
@@ -429,7 +434,8 @@ def run_gpu_arm(args, rank, world, local_rank):
         "clocks": clocks,
         "e2e": {"value": images / e2e_s, "unit": "images/s", "h2d_bytes_per_step": BATCH * 3 * IMG * IMG * 4,
                 "d2h_bytes_per_step": BATCH * 1000 * 4, "ms_per_step": e2e_s * 1000.0 / args.steps,
-                "h2d_chunks": args.e2e_chunks},
+                "h2d_chunks": args.e2e_chunks,
+                "host_binding": ("rank 0 bound to %d CPUs next to its GPU" % len(numa_cpus)) if numa_cpus else "none"},
         "gpu_launches": int(launches_per_step) * args.steps,
         "roofline": roofline,
     }

@@ -63,3 +63,15 @@ def test_two_gloo_ranks_shard_a_batch(tmp_path):
     for k in range(world):
         assert np.load(tmp_path / ("t%d.npy" % k))[0] == 11.0     # the slowest rank's value everywhere
     assert sharding.aggregate_throughput(256, 2, 2.0) == 256000.0
+
+
+def test_gpu_local_cpus_reads_sysfs(tmp_path):
+    from excalibur_b200 import sharding
+    d = tmp_path / "0000:1b:00.0"
+    d.mkdir()
+    (d / "local_cpulist").write_text("0-3,8,10-11\n")
+    assert sharding.gpu_local_cpus("0000:1B:00.0", str(tmp_path)) == {0, 1, 2, 3, 8, 10, 11}
+    assert sharding.gpu_local_cpus("0000:2c:00.0", str(tmp_path)) is None
+    (d / "local_cpulist").write_text("\n")
+    assert sharding.gpu_local_cpus("0000:1b:00.0", str(tmp_path)) is None
+    assert sharding.bind_host_thread_to_gpu(0) is None or isinstance(sharding.bind_host_thread_to_gpu(0), set)
