@@ -8,15 +8,19 @@
 // [Cout][kh][kw][Cin].  Stride-2 layers read one of four "parity" views of the input (every
 // second row / column, offset by 0 or 1) so that a box is still a dense rectangle.
 //
-// One persistent CTA per SM, 20 warps:
-//   warp 0   TMA producer (one lane)           - fills a ring of shared-memory stages
-//   warp 1   MMA issuer (one lane) + TMEM owner - tcgen05.mma, fp32 / int32 accumulators in TMEM,
-//                                                 NB = 2 or 4 accumulator buffers so epilogues
-//                                                 overlap the main loops of the following tiles
-//   warps 4-19 epilogue, in NB groups           - tile i goes to group i % NB: tcgen05.ld,
-//                                                 scale/bias, residual, activation, requantise,
-//                                                 16-byte NHWC stores
+// Persistent CTAs: two per SM with 12 warps each for N tiles of up to 128 channels, one per SM with
+// 20 warps for wider ones.
+//   warp 0   TMA producer (lane g issues K block g of a stage) - fills a ring of shared-memory stages
+//   warp 1   MMA issuer (one lane) + TMEM owner                 - tcgen05.mma, fp32 / int32 accumulators
+//                                                                 in as many TMEM buffers as fit (2-4)
+//   warps 4+ epilogue, in groups of four warps (one per TMEM     - tile i uses buffer i % buffers and
+//            lane quarter)                                        group i % groups: tcgen05.ld, scale /
+//                                                                 bias, residual, activation, requantise,
+//                                                                 32-byte NHWC stores
 //   (warps 2-3 only help with set-up)
+// Variants, each its own instantiation: patch mode for few-channel stride-2 stems (the raw input
+// patch read through un-swizzled overlapping descriptors), the same with a 3x3/2 max pooling in the
+// epilogue, and halo mode for planar16 int8 input.
 // All mbarrier waits are bounded; when one runs out the kernel raises the context's error
 // word, every role leaves its loop, TMEM is freed and the launch returns normally.
 #include "conv_common.cuh"
@@ -877,6 +881,9 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.tiles_nb = (g.N + p.TN - 1) / p.TN;
     p.step_w = p.TW; p.step_h = p.TH; p.org = 0;
     p.n_tiles = (w->cout_pad + 255) / 256;
+#ifdef EXB_CONV_EXPERIMENTS
+    if (const char* e = getenv("EXB_CONV_BNMAX")) p.n_tiles = (w->cout_pad + atoi(e) - 1) / atoi(e);
+#endif
     p.BN = round_up((w->cout_pad + p.n_tiles - 1) / p.n_tiles, 16);
     // Two CTAs per SM when the N tile is narrow (see the kernel's comment).
     bool two = p.BN <= 128;
