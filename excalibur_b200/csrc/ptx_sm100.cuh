@@ -42,14 +42,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  "r"(bytes)
                  : "memory");
 }
+// A failed mbarrier.try_wait costs a shared-memory access, and the shared-memory pipe is what the
+// convolution kernel runs out of first: the waiting thread is therefore parked in hardware for up to
+// this many nanoseconds per try (it still wakes as soon as the phase completes).
+#ifndef EXB_WAIT_HINT_NS
+#define EXB_WAIT_HINT_NS 1000
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)EXB_WAIT_HINT_NS)
         : "memory");
     return ok != 0;
 }
@@ -105,10 +111,10 @@ __device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity)
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"((uint32_t)EXB_WAIT_HINT_NS)
         : "memory");
     return ok != 0;
 }
