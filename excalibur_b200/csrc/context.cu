@@ -2,6 +2,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 #include <string.h>
 
@@ -74,6 +75,30 @@ extern "C" int exb_ctx_sm_count(const exb_ctx* ctx, int* out) {
     EXB_REQUIRE(ctx && out, "exb_ctx_sm_count: null argument");
     *out = ctx->sm_count;
     return EXB_OK;
+}
+
+namespace exb {
+namespace {
+// One thread waits, with the kernels' own bounded wait, on an mbarrier nobody ever arrives at; when the
+// limit runs out it records role code 9 in the context's error word and the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(int* error, uint32_t max_polls) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(&bar, 1);
+        ptx::fence_mbar_init();
+        if (!ptx::mbar_wait_bounded(&bar, 0, &abort_flag, max_polls)) atomicExch(error, 9);
+    }
+}
+}  // namespace
+}  // namespace exb
+
+extern "C" int exb_selftest_bounded_wait(exb_ctx* ctx, int max_polls, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "exb_selftest_bounded_wait: null context");
+    EXB_REQUIRE(max_polls >= 1 && max_polls <= 4096, "exb_selftest_bounded_wait: max_polls must be 1..4096");
+    exb::bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctx->d_error, (uint32_t)max_polls);
+    return after_launch("bounded_wait_selftest_kernel");
 }
 
 extern "C" int exb_ctx_sync_check(exb_ctx* ctx, void* stream) {

@@ -709,7 +709,13 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     const float4* bi = reinterpret_cast<const float4*>(s_bias + cl);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
+#ifdef EXB_CONV_EXPERIMENTS
+                        const bool noload = (p.xflags & 64) != 0;
+                        const float4 s4 = noload ? make_float4(0.01f, 0.01f, 0.01f, 0.01f) : sc[i];
+                        const float4 b4 = noload ? make_float4(0.f, 0.f, 0.f, 0.f) : bi[i];
+#else
                         const float4 s4 = sc[i], b4 = bi[i];
+#endif
                         v[4 * i + 0] = epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x);
                         v[4 * i + 1] = epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y);
                         v[4 * i + 2] = epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z);

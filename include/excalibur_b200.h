@@ -77,6 +77,11 @@ EXB_API int exb_ctx_sm_count(const exb_ctx* ctx, int* out);
  * kernels run on the legacy stream and errors surface as CHECK failures that terminate the
  * process (include/Primitives/logger.hpp:101-118). */
 EXB_API int exb_ctx_sync_check(exb_ctx* ctx, void* stream);
+/* Failure-path self-test without a fault: launches a one-warp kernel whose bounded mbarrier wait
+ * (the same wait the convolution kernel uses, at most max_polls <= 4096 tries of about a microsecond)
+ * can never be satisfied.  The kernel gives up, records role code 9 and returns; the following
+ * exb_ctx_sync_check reports EXB_ERR_TIMEOUT and the context stays usable.  No reference counterpart. */
+EXB_API int exb_selftest_bounded_wait(exb_ctx* ctx, int max_polls, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Layout / precision converts at the API edge.  The reference keeps NCHW fp32 tensors

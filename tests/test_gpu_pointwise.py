@@ -159,3 +159,21 @@ def test_bad_arguments_are_reported_not_fatal(ctx):
     with pytest.raises(capi.ExbError) as e:
         capi.check(capi.lib().exb_relu_fwd(ctx.handle, None, capi.ptr(x), 16, capi.EXB_F32, None))
     assert e.value.code == capi.EXB_ERR_BAD_ARG
+
+
+def test_bounded_wait_gives_up_with_a_status_and_the_context_stays_usable(ctx):
+    """The failure path of the kernels' device-side waits, exercised without a fault: a wait that can
+    never be satisfied runs out after a bounded number of tries, the kernel returns, the next
+    sync-check reports EXB_ERR_TIMEOUT once, and later launches on the same context are fine."""
+    capi = _capi()
+    ctx.sync_check()
+    capi.check(capi.lib().exb_selftest_bounded_wait(ctx.handle, 64, capi.cur_stream()))
+    with pytest.raises(capi.ExbError) as e:
+        ctx.sync_check()
+    assert e.value.code == -4 and "bounded wait" in str(e.value)
+    ctx.sync_check()                                    # the error word was cleared
+    x = rng(1).standard_normal(4096).astype(np.float32)
+    np.testing.assert_array_equal(host(capi.relu(ctx, dev(x))), np.maximum(x, 0))
+    ctx.sync_check()
+    with pytest.raises(capi.ExbError):                  # the self-test itself is bounded
+        capi.check(capi.lib().exb_selftest_bounded_wait(ctx.handle, 1 << 20, capi.cur_stream()))
