@@ -55,6 +55,17 @@ int resolve(const exb_conv_desc* d, ConvGeom& g) {
                 "in_planar / out_i8_planar must be 0 or 1");
     g.in_planar = d->in_planar;
     g.out_i8_planar = d->out_i8_planar;
+    EXB_REQUIRE((d->out_f16_planar == 0 || d->out_f16_planar == 1) && (d->res_planar == 0 || d->res_planar == 1),
+                "out_f16_planar / res_planar must be 0 or 1");
+    g.out_f16_planar = d->out_f16_planar;
+    g.res_planar = d->res_planar;
+    if (g.out_f16_planar || g.res_planar) {
+        EXB_REQUIRE(g.cout_stride % 16 == 0, "planar16 fp16 tensors need cout_stride %% 16 == 0");
+        EXB_REQUIRE(!g.out_f16_planar || g.out_dtype == EXB_F16 || g.out2_dtype == EXB_F16,
+                    "out_f16_planar without an fp16 output");
+        EXB_REQUIRE(!g.res_planar || g.has_res, "res_planar without a residual");
+        EXB_REQUIRE(!g.pool, "planar16 fp16 tensors are not available with fuse_pool");
+    }
     if (g.out_i8_planar) {
         EXB_REQUIRE(g.cout_stride % 16 == 0, "planar16 output needs cout_stride %% 16 == 0");
         EXB_REQUIRE(g.out_dtype == EXB_I8 || g.out2_dtype == EXB_I8, "out_i8_planar without an int8 output");
@@ -212,7 +223,7 @@ extern "C" int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (g.pool && !(d->impl != 1 && conv_tc_eligible(g) && conv_tc_pool_fusable(g)))
         return fail(EXB_ERR_UNSUPPORTED, "fuse_pool is not available for this convolution (see exb_conv2d_pool_fusable)");
-    if ((g.in_planar || g.out_i8_planar) && !(d->impl != 1 && conv_tc_eligible(g)))
+    if ((g.in_planar || g.out_i8_planar || g.out_f16_planar || g.res_planar) && !(d->impl != 1 && conv_tc_eligible(g)))
         return fail(EXB_ERR_UNSUPPORTED, "planar16 tensors need the tensor-core kernel");
     if (g.in_planar && !conv_tc_halo_ok(ctx, g))
         return fail(EXB_ERR_UNSUPPORTED, "planar16 input is not available for this convolution (see exb_conv2d_accepts_planar_input)");

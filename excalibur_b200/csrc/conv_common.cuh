@@ -29,6 +29,7 @@ struct ConvGeom {
     int pool;             // 1: 3x3/2 pad-1 max pooling fused into the epilogue; y is [N][PH][PW][cout_stride]
     int PH, PW;
     int in_planar, out_i8_planar;   // planar16 int8 input / int8 output (see exb_conv_desc)
+    int out_f16_planar, res_planar; // planar16 fp16 output / residual
 };
 
 // "Folded" K layout for convolutions with very few input channels (a stem): one K row of an
@@ -73,6 +74,8 @@ struct EpiParams {
     float out_scale, out2_scale;
     int cout_stride;
     int i8_planar;   // the int8 output (y or y2) is planar16
+    int f16_planar;  // the fp16 output (y or y2) is planar16
+    int res_planar;  // the residual is planar16 fp16
 };
 
 // v = act(acc * scale + bias + residual)

@@ -123,7 +123,8 @@ __device__ __forceinline__ TileCoord decode_tile(const ConvTcParams& p, int t) {
 // kPool: the fused max-pooling epilogue (its own instantiation so that the plain kernels keep their
 // register allocation).
 // kHalo: the planar16 halo-patch main loop, likewise its own instantiation.
-template <bool kInt8, int kDbg, int kEpiWarps, bool kPool = false, bool kHalo = false>
+// kPlanar: planar16 fp16 output / residual addressing in the epilogue, likewise.
+template <bool kInt8, int kDbg, int kEpiWarps, bool kPool = false, bool kHalo = false, bool kPlanar = false>
 __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps == 8 ? 2 : 1)
     conv_tc_kernel(const __grid_constant__ ConvTcParams p) {
     constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
@@ -646,10 +647,20 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const int per = (n_chunks + nsub - 1) / nsub;
             const int c_begin = sub * per, c_end = min(n_chunks, (sub + 1) * per);
             const bool do_res = p.has_res && vec_ok && valid && !(kDbg & 16);
-            const __half* res_row = p.e.residual + pix * p.e.cout_stride + tc.ntile * p.BN;
+            // planar16 fp16: element offset of (n, slice 0, oh, ow); a slice is `plane` elements on
+            int64_t poff = 0, plane = 0;
+            if constexpr (kPlanar) {
+                plane = (int64_t)p.OH * p.OW * 16;
+                poff = (int64_t)n * (p.e.cout_stride >> 4) * plane + ((int64_t)oh * p.OW + ow) * 16;
+            }
+            // residual of 16-channel chunk c: res_row + c * res_step
+            const bool rpl = kPlanar && p.e.res_planar;
+            const __half* res_row = rpl ? p.e.residual + poff + (int64_t)(tc.ntile * p.BN >> 4) * plane
+                                        : p.e.residual + pix * p.e.cout_stride + tc.ntile * p.BN;
+            const int64_t res_step = rpl ? plane : 16;
             uint32_t rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (do_res && c_begin < c_end && tc.ntile * p.BN + c_begin * 16 < p.e.cout_stride)
-                ld_global_nc_256(res_row + c_begin * 16, rn);
+                ld_global_nc_256(res_row + c_begin * res_step, rn);
             // The residual rows of this group's NEXT tile are asked into L2 now (no register cost):
             // the tile after this one then finds them a few hundred cycles away instead of a DRAM
             // round trip per chunk, which the one-chunk-ahead register prefetch cannot cover.
@@ -657,10 +668,18 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 const TileCoord c2 = decode_tile(p, t + p.epi_groups * (int)gridDim.x);
                 const int ow2 = c2.ow0 + tw, oh2 = c2.oh0 + th, n2 = c2.n0 + tn;
                 if (row_in_box && ow2 < p.OW && oh2 < p.OH && n2 < p.N) {
-                    const __half* r2 = p.e.residual + (((int64_t)n2 * p.OH + oh2) * p.OW + ow2) * p.e.cout_stride +
-                                       c2.ntile * p.BN + c_begin * 16;
-                    for (int b = 0; b < (c_end - c_begin) * 32; b += 128)
-                        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(r2) + b));
+                    if (rpl) {      // one 32-byte piece per slice; the four lanes of a line ask for it together
+                        const __half* r2 = p.e.residual + (int64_t)n2 * (p.e.cout_stride >> 4) * plane +
+                                           ((int64_t)oh2 * p.OW + ow2) * 16 + (int64_t)((c2.ntile * p.BN >> 4) + c_begin) * plane;
+                        if ((tw & 3) == 0)
+                            for (int c = 0; c < c_end - c_begin; ++c)
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(r2 + c * plane));
+                    } else {
+                        const __half* r2 = p.e.residual + (((int64_t)n2 * p.OH + oh2) * p.OW + ow2) * p.e.cout_stride +
+                                           c2.ntile * p.BN + c_begin * 16;
+                        for (int b = 0; b < (c_end - c_begin) * 32; b += 128)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(r2) + b));
+                    }
                 }
             }
 #ifdef EXB_CONV_EXPERIMENTS
@@ -692,7 +711,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
 #pragma unroll
                 for (int i = 0; i < 8; ++i) rc[i] = rn[i];
                 if (do_res && chunk + 1 < c_end && tc.ntile * p.BN + (chunk + 1) * 16 < p.e.cout_stride)
-                    ld_global_nc_256(res_row + (chunk + 1) * 16, rn);
+                    ld_global_nc_256(res_row + (chunk + 1) * res_step, rn);
                 ptx::tmem_ld_wait();
                 const int cl = tc.ntile * p.BN + chunk * 16;   // first channel of the chunk
                 if (!valid || cl >= p.e.cout_stride || (kDbg & 1)) continue;
@@ -702,6 +721,10 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 if constexpr (kHalo) {   // only this instantiation (and the pooling one) can write planar16
                     if (p.e.i8_planar)
                         off8 = ((((int64_t)n * (p.e.cout_stride >> 4) + (cl >> 4)) * p.OH + oh) * p.OW + ow) * 16;
+                }
+                int64_t off16 = off;
+                if constexpr (kPlanar) {
+                    if (p.e.f16_planar) off16 = poff + (int64_t)(cl >> 4) * plane;
                 }
                 float v[16];
                 {
@@ -740,9 +763,12 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         if (acc_ == 123.456f) static_cast<float*>(p.e.y)[0] = acc_;   // keep the math alive
                         continue;
                     }
-                    epi_store_vec16(p.e.y, p.e.out_dtype, p.e.out_dtype == EXB_I8 ? off8 : off, v, p.e.out_scale, raw);
+                    epi_store_vec16(p.e.y, p.e.out_dtype,
+                                    p.e.out_dtype == EXB_I8 ? off8 : (p.e.out_dtype == EXB_F16 ? off16 : off), v, p.e.out_scale, raw);
                     if (p.e.out2_dtype >= 0)
-                        epi_store_vec16(p.e.y2, p.e.out2_dtype, p.e.out2_dtype == EXB_I8 ? off8 : off, v, p.e.out2_scale, raw);
+                        epi_store_vec16(p.e.y2, p.e.out2_dtype,
+                                        p.e.out2_dtype == EXB_I8 ? off8 : (p.e.out2_dtype == EXB_F16 ? off16 : off), v,
+                                        p.e.out2_scale, raw);
                 } else {
                     // ragged channel count: element-wise stores, statically indexed so the
                     // accumulators stay in registers
@@ -1015,6 +1041,11 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;
     p.e.out_scale = g.out_scale; p.e.out2_scale = g.out2_scale; p.e.cout_stride = g.cout_stride;
     p.e.i8_planar = g.out_i8_planar;
+    p.e.f16_planar = g.out_f16_planar;
+    p.e.res_planar = g.res_planar;
+    const bool planar16 = g.out_f16_planar || g.res_planar;
+    if (planar16 && (p.halo || p.pool || (g.cout_stride & 15)))
+        return fail(EXB_ERR_UNSUPPORTED, "planar16 fp16 tensors are not available for this convolution");
     p.error = ctx->d_error;
 #ifdef EXB_CONV_EXPERIMENTS
     if (const char* e = getenv("EXB_CONV_X")) p.xflags = atoi(e);
@@ -1100,8 +1131,11 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
                      : (two ? conv_tc_kernel<false, 0, 8> : conv_tc_kernel<false, 0, 16>);
     if (p.pool) kern = conv_tc_kernel<false, 0, 8, true>;
     if (p.halo) kern = two ? conv_tc_kernel<true, 0, 8, false, true> : conv_tc_kernel<true, 0, 16, false, true>;
+    if (planar16)
+        kern = int8 ? (two ? conv_tc_kernel<true, 0, 8, false, false, true> : conv_tc_kernel<true, 0, 16, false, false, true>)
+                    : (two ? conv_tc_kernel<false, 0, 8, false, false, true> : conv_tc_kernel<false, 0, 16, false, false, true>);
 #ifdef EXB_CONV_EXPERIMENTS
-    if (const char* e = getenv("EXB_CONV_DBG"); e && !p.halo && !p.pool) {
+    if (const char* e = getenv("EXB_CONV_DBG"); e && !p.halo && !p.pool && !planar16) {
         switch (atoi(e)) {
         case 1: kern = int8 ? (two ? conv_tc_kernel<true, 1, 8> : conv_tc_kernel<true, 1, 16>) : (two ? conv_tc_kernel<false, 1, 8> : conv_tc_kernel<false, 1, 16>); break;
         case 2: kern = int8 ? (two ? conv_tc_kernel<true, 2, 8> : conv_tc_kernel<true, 2, 16>) : (two ? conv_tc_kernel<false, 2, 8> : conv_tc_kernel<false, 2, 16>); break;

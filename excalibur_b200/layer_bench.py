@@ -48,6 +48,8 @@ def main(argv=None):
     ap.add_argument("--layers", default=",".join(list(LAYERS) + list(EXTRA)))
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--planar-f16", action="store_true",
+                    help="fp16 outputs and residuals use the planar16 fp16 layout (coalesced epilogue accesses)")
     ap.add_argument("--planar", action="store_true",
                     help="3x3 stride-1 int8 layers read / write planar16 int8 tensors (halo mode) where the kernel accepts it")
     args = ap.parse_args(argv)
@@ -69,6 +71,10 @@ def main(argv=None):
                 d.in_planar = 1
                 d.out_i8_planar = 1 if kind != "proj" else 0
                 name = name + "*"
+            if args.planar_f16 and kind != "conv1":
+                d.out_f16_planar = 1
+                d.res_planar = 1 if res else 0
+                name = name + "^"
             wq = rng.integers(-127, 128, (cout, cin, k, k)).astype(np.int8)
             wp = capi.ConvWeights(ctx, d, wq, np.zeros(cout, np.float32), np.full(cout, 40.0, np.float32), 30.0)
             # (random bytes: the same buffer serves as NHWC or planar16 input)

@@ -101,9 +101,12 @@ EXB_API int exb_nchw_f32_to_nhwc(exb_ctx* ctx, const float* x_nchw, void* y_nhwc
 EXB_API int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x_nchw, void* y_nhwc, int dtype,
                                         int N, int C, int H, int W, int c_stride, int w_pad,
                                         int w_pitch, float scale, int rounding, void* stream);
-/* planar16 int8 [N][c_stride/16][H][W][16] -> fp32 NCHW, y = q * scale (inspection of planar maps). */
+/* planar16 [N][c_stride/16][H][W][16] (EXB_I8 or EXB_F16) -> fp32 NCHW, y = x * scale (inspection
+ * of planar maps, global pooling input). */
 EXB_API int exb_planar16_i8_to_nchw_f32(exb_ctx* ctx, const int8_t* x, float* y, int N, int C, int H, int W,
                                         int c_stride, float scale, void* stream);
+EXB_API int exb_planar16_to_nchw_f32(exb_ctx* ctx, const void* x, int dtype, float* y, int N, int C, int H,
+                                     int W, int c_stride, float scale, void* stream);
 EXB_API int exb_nhwc_to_nchw_f32(exb_ctx* ctx, const void* x_nhwc, int dtype, float* y_nchw,
                                  int N, int C, int H, int W, int c_stride, float scale,
                                  void* stream);
@@ -161,6 +164,13 @@ typedef struct exb_conv_desc {
      * fuse_pool = 1 (the two kernel variants that carry the planar store). */
     int32_t in_planar;
     int32_t out_i8_planar;
+    /* Planar fp16 skip tensors, layout [N][cout_stride/16][OH][OW][16] fp16 (32 bytes per pixel and
+     * slice): a warp's epilogue accesses then fall into 8 cache lines instead of 32.
+     * out_f16_planar = 1: whichever of y / y2 is EXB_F16 is written in that layout;
+     * res_planar = 1: the residual is read in that layout.  Both need cout_stride % 16 == 0 and the
+     * tensor-core kernel (exb_conv2d_uses_tensor_cores); int8 and fp32 outputs are not affected. */
+    int32_t out_f16_planar;
+    int32_t res_planar;
 } exb_conv_desc;
 
 /* Output spatial size: (in + pad_a + pad_b - k) / stride + 1

@@ -387,3 +387,49 @@ def test_planar_input_is_refused_where_it_cannot_run(ctx):
     for args in ((1, 16, 16, 64, 64, 3, 2, 1), (1, 16, 16, 64, 64, 1, 1, 0), (1, 7, 7, 512, 512, 3, 1, 1)):
         d = capi.make_conv_desc(*args, capi.EXB_I8, capi.EXB_I8)
         assert capi.lib().exb_conv2d_accepts_planar_input(d) == 0, args
+
+
+PLANAR_F16_CASES = [
+    # N, Cin, H, W, Cout, k, stride, pad
+    (2, 64, 56, 56, 64, 3, 1, 1),       # two CTAs per SM
+    (3, 128, 28, 28, 128, 3, 1, 1),
+    (5, 256, 14, 14, 256, 3, 1, 1),     # one CTA per SM, chunks split between two warps
+    (3, 64, 56, 56, 128, 1, 2, 0),      # projection shortcut (fp16 output only)
+    (2, 32, 13, 11, 48, 3, 1, 1),       # ragged tiles, 48 channels = 3 slices
+    (1, 64, 12, 12, 320, 3, 1, 1),      # two Cout tiles
+]
+
+
+@pytest.mark.parametrize("case", PLANAR_F16_CASES)
+def test_conv_planar16_fp16_output_and_residual(ctx, case):
+    """fp16 output and residual in the planar16 layout [N][C/16][H][W][16]: the same numbers as the NHWC
+    path, element for element; the int8 second output stays NHWC."""
+    from tests.util import to_planar16, from_planar16
+    import torch
+    capi = _capi()
+    N, Cin, H, W, Cout, k, stride, pad = case
+    r = rng(sum(case) + 11)
+    xq = r.integers(-128, 128, (N, Cin, H, W)).astype(np.int8)
+    wq = r.integers(-127, 128, (Cout, Cin, k, k)).astype(np.int8)
+    bias = r.standard_normal(Cout).astype(np.float32)
+    ws = r.uniform(20, 60, Cout).astype(np.float32)
+    OH, OW = (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
+    res = f16_round(r.standard_normal((N, Cout, OH, OW)))
+    cs = (Cout + 15) // 16 * 16
+    with_res = k == 3
+    kw = dict(res=with_res, act=1 if with_res else 0, out2_scale=13.0, cout_stride=cs)
+    d0 = capi.make_conv_desc(N, H, W, Cin, Cout, k, stride, pad, capi.EXB_I8, capi.EXB_F16, capi.EXB_I8, **kw)
+    d1 = capi.make_conv_desc(N, H, W, Cin, Cout, k, stride, pad, capi.EXB_I8, capi.EXB_F16, capi.EXB_I8,
+                             out_f16_planar=1, res_planar=1 if with_res else 0, **kw)
+    wp = capi.ConvWeights(ctx, d0, wq, bias, ws, 31.0)
+    x = dev(to_nhwc(xq))
+    y0, q0 = capi.conv2d(ctx, d0, x, wp, dev(to_nhwc(res, cs).astype(np.float16)) if with_res else None)
+    y1 = torch.zeros((N, cs // 16, OH, OW, 16), dtype=torch.float16, device="cuda")
+    _, q1 = capi.conv2d(ctx, d1, x, wp, dev(to_planar16(res.astype(np.float16), cs)) if with_res else None, y1)
+    ctx.sync_check()
+    np.testing.assert_array_equal(from_planar16(host(y1), Cout), to_nchw(host(y0), Cout))
+    np.testing.assert_array_equal(host(q1), host(q0))
+    f = torch.empty((N, Cout, OH, OW), dtype=torch.float32, device="cuda")
+    capi.check(capi.lib().exb_planar16_to_nchw_f32(ctx.handle, capi.ptr(y1), capi.EXB_F16, capi.ptr(f), N, Cout, OH, OW, cs,
+                                                    1.0, capi.cur_stream()))
+    np.testing.assert_array_equal(host(f), to_nchw(host(y0), Cout).astype(np.float32))
