@@ -8,16 +8,15 @@
 // [Cout][kh][kw][Cin].  Stride-2 layers read one of four "parity" views of the input (every
 // second row / column, offset by 0 or 1) so that a box is still a dense rectangle.
 //
-// Persistent CTAs: two per SM with 12 warps each for N tiles of up to 128 channels, one per SM with
-// 20 warps for wider ones.
+// Persistent CTAs: two per SM with 10 warps each for N tiles of up to 128 channels, one per SM with
+// 18 warps for wider ones (no idle warps: 320 threads leave 102 registers per thread at two CTAs per SM).
 //   warp 0   TMA producer (lane g issues K block g of a stage) - fills a ring of shared-memory stages
 //   warp 1   MMA issuer (one lane) + TMEM owner                 - tcgen05.mma, fp32 / int32 accumulators
 //                                                                 in as many TMEM buffers as fit (2-4)
-//   warps 4+ epilogue, in groups of four warps (one per TMEM     - tile i uses buffer i % buffers and
+//   warps 2+ epilogue, in groups of four warps (one per TMEM     - tile i uses buffer i % buffers and
 //            lane quarter)                                        group i % groups: tcgen05.ld, scale /
 //                                                                 bias, residual, activation, requantise,
 //                                                                 32-byte NHWC stores
-//   (warps 2-3 only help with set-up)
 // Variants, each its own instantiation: patch mode for few-channel stride-2 stems (the raw input
 // patch read through un-swizzled overlapping descriptors), the same with a 3x3/2 max pooling in the
 // epilogue, and halo mode for planar16 int8 input.
@@ -32,7 +31,7 @@ namespace exb {
 namespace {
 
 constexpr int kMaxStages = 8;
-constexpr int kFirstEpiWarp = 4;
+constexpr int kFirstEpiWarp = 2;   // warp 0 producer, warp 1 MMA issuer, epilogue warps from here on
 constexpr int kMaxAccBufs = 4;
 constexpr int kTileM = 128;
 constexpr uint32_t kMaxSpins = 1u << 21;  // tens of milliseconds at least; a legitimate wait is microseconds
@@ -93,7 +92,17 @@ struct ConvTcParams {
     int halo_plane;   // bytes of one 16-channel slice of the patch
     int cchunks;      // 16-channel slices of the input
     int xflags;       // experiment switches (always 0 in the shipped build)
+    unsigned long long* trace;   // experiments: clock64 stamps of CTA 0, [role 0..3][tile 0..63][4]
 };
+
+#ifdef EXB_CONV_EXPERIMENTS
+#define EXB_TRACE(role, tile_i, k)                                                              \
+    do {                                                                                        \
+        if (p.trace && blockIdx.x == 0 && (tile_i) < 64) p.trace[((role) * 64 + (tile_i)) * 4 + (k)] = clock64(); \
+    } while (0)
+#else
+#define EXB_TRACE(role, tile_i, k) do { } while (0)
+#endif
 
 struct TileCoord {
     int ow0, oh0, n0, ntile;
@@ -321,9 +330,11 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 }
             }
         } else if (lane < G) {
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            int ptile = 0;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++ptile) {
                 const TileCoord tc = decode_tile(p, t);
                 const int ncoord = tc.ntile * p.BN;
+                if (lane == 0) EXB_TRACE(0, ptile, 0);
                 for (int it0 = 0; it0 < k_iters; it0 += G) {
                     const int nb = min(G, k_iters - it0);
                     const bool mine = lane < nb;
@@ -349,6 +360,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         phase ^= 1u;
                     }
                 }
+                if (lane == 0) EXB_TRACE(0, ptile, 1);
             }
             if (!ok) {
                 if (lane == 0) atomicExch(p.error, 1);
@@ -379,11 +391,14 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const uint32_t a_stage = a_blk * G, b_stage = bres ? 0u : b_blk * G;
             const uint32_t idesc = p.idesc;
             if (bres && !ptx::mbar_wait_bounded(&bres_bar, 0, &abort_flag, kMaxSpins)) ok = false;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            int mtile = 0;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++mtile) {
+                EXB_TRACE(1, mtile, 0);
                 if (!ptx::mbar_wait_bounded_u32(tempty0 + acc * 8, acc_phase ^ 1u, &abort_flag, kMaxSpins)) {
                     ok = false;
                     break;
                 }
+                EXB_TRACE(1, mtile, 1);
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
                 uint32_t accumulate = 0;
@@ -495,7 +510,9 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     }
                 }
                 if (!ok) break;
+                EXB_TRACE(1, mtile, 2);
                 ptx::tc_commit_u32(tfull0 + acc * 8);   // accumulator complete
+                EXB_TRACE(1, mtile, 3);
                 if (++acc == p.acc_bufs) {
                     acc = 0;
                     acc_phase ^= 1u;
@@ -509,7 +526,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         // i % NB.  A group has 16/NB warps: one (NB = 4) or two (NB = 2) per TMEM lane quarter,
         // in the second case splitting the 16-column chunks between them.
         const int e = warp - kFirstEpiWarp;
-        const int q = e & 3;                    // TMEM lane quarter (== warp % 4)
+        const int q = warp & 3;                 // TMEM lane quarter: a warp can only reach lanes 32*(warp%4)..+31
         const int nsub = kEpiWarps / 4 / p.epi_groups;
         const int grp = (e >> 2) % p.epi_groups;
         const int sub = (e >> 2) / p.epi_groups;
@@ -690,10 +707,12 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 }
             } else
 #endif
+            if (q == 0 && sub == 0 && lane == 0) EXB_TRACE(2, ti, 0);
             if (!ptx::mbar_wait_bounded_warp(&tfull_bar[buf], acc_phase, &abort_flag, kMaxSpins)) {
                 ok = false;
                 break;
             }
+            if (q == 0 && sub == 0 && lane == 0) EXB_TRACE(2, ti, 1);
             ptx::tc_fence_after_sync();
 #ifdef EXB_CONV_EXPERIMENTS
             if (p.xflags & 2) {          // epilogue reduced to the accumulator hand-back
@@ -788,6 +807,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&tempty_bar[buf]);
+            if (q == 0 && sub == 0 && lane == 0) EXB_TRACE(2, ti, 2);
         }
         if (!ok && lane == 0) atomicExch(p.error, 3);
     }
@@ -1156,6 +1176,15 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     }
 #endif
     EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+#ifdef EXB_CONV_EXPERIMENTS
+    static unsigned long long* d_trace = nullptr;
+    const char* trace_path = getenv("EXB_CONV_TRACE");
+    if (trace_path) {
+        if (!d_trace) cudaMalloc(&d_trace, 4 * 64 * 4 * sizeof(unsigned long long));
+        cudaMemsetAsync(d_trace, 0, 4 * 64 * 4 * sizeof(unsigned long long), st);
+        p.trace = d_trace;
+    }
+#endif
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)grid);
@@ -1168,6 +1197,25 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 1 : 0;
     EXB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+#ifdef EXB_CONV_EXPERIMENTS
+    if (trace_path) {
+        static unsigned long long h[4 * 64 * 4];
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h, d_trace, sizeof(h), cudaMemcpyDeviceToHost);
+        if (FILE* f = fopen(trace_path, "w")) {
+            unsigned long long t0 = ~0ull;
+            for (unsigned long long v : h) if (v && v < t0) t0 = v;
+            for (int role = 0; role < 3; ++role)
+                for (int i = 0; i < 64; ++i) {
+                    const unsigned long long* e = h + (role * 64 + i) * 4;
+                    if (!e[0]) continue;
+                    fprintf(f, "%d %d %lld %lld %lld %lld\n", role, i, (long long)(e[0] - t0), e[1] ? (long long)(e[1] - t0) : -1,
+                            e[2] ? (long long)(e[2] - t0) : -1, e[3] ? (long long)(e[3] - t0) : -1);
+                }
+            fclose(f);
+        }
+    }
+#endif
     return after_launch("conv_tc_kernel");
 }
 
