@@ -149,12 +149,26 @@ __device__ __forceinline__ void epi_store_vec16(void* y, int dtype, int64_t off,
     }
 }
 
-// Activation over a register vector with the selector hoisted out of the element loop.
+// Activation over a register vector with the selector hoisted out of the element loop (one uniform
+// branch per chunk instead of a switch per element).
 __device__ __forceinline__ void act_vec16(float (&v)[16], int act) {
+    if (act == EXB_ACT_NONE) return;
     if (act == EXB_ACT_RELU) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
-    } else if (act != EXB_ACT_NONE) {
+    } else if (act == EXB_ACT_RELU6) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = fminf(fmaxf(v[i], 0.f), 6.f);
+    } else if (act == EXB_ACT_SILU) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + __expf(-v[i]));
+    } else if (act == EXB_ACT_HARDSWISH) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = v[i] * fminf(fmaxf(fmaf(v[i], 1.f / 6.f, 0.5f), 0.f), 1.f);
+    } else if (act == EXB_ACT_SIGMOID) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 1.f / (1.f + __expf(-v[i]));
+    } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = apply_act(v[i], act);
     }

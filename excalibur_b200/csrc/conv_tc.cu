@@ -31,7 +31,10 @@ namespace exb {
 namespace {
 
 constexpr int kMaxStages = 8;
-constexpr int kFirstEpiWarp = 2;   // warp 0 producer, warp 1 MMA issuer, epilogue warps from here on
+#ifndef EXB_FIRST_EPI_WARP
+#define EXB_FIRST_EPI_WARP 2
+#endif
+constexpr int kFirstEpiWarp = EXB_FIRST_EPI_WARP;   // warp 0 producer, warp 1 MMA issuer, epilogue warps from here on
 constexpr int kMaxAccBufs = 4;
 constexpr int kTileM = 128;
 constexpr uint32_t kMaxSpins = 1u << 21;  // tens of milliseconds at least; a legitimate wait is microseconds

@@ -135,6 +135,21 @@ extern "C" int exb_host_pipeline_get(void* p, const char* name, float* out, int6
     });
 }
 
+extern "C" int exb_host_pipeline_output_ptr(void* p, const char* name, const float** data, int* shape4) {
+    return guarded([&]() {
+        auto* h = static_cast<host_pipeline*>(p);
+        auto it = h->outputs.find(name);
+        if (it == h->outputs.end() || !it->second) {
+            g_err = std::string("not an output of the last forward: ") + name;
+            return (int)EXB_ERR_BAD_ARG;
+        }
+        auto shp = it->second->data_shape();
+        for (int i = 0; i < 4; ++i) shape4[i] = shp[i];
+        *data = it->second->cpu_data();
+        return (int)EXB_OK;
+    });
+}
+
 extern "C" int exb_host_pipeline_stats(void* p, int* launches, double* device_ms) {
     auto* h = static_cast<host_pipeline*>(p);
     if (launches) *launches = h->net->launches_last_forward();

@@ -12,7 +12,7 @@ EXB_HOST_FATAL = -100
 HOST_SYMBOLS = [
     "exb_host_last_error", "exb_host_registered", "exb_host_pipeline_create", "exb_host_pipeline_destroy",
     "exb_host_pipeline_set_option", "exb_host_pipeline_forward", "exb_host_pipeline_num_outputs",
-    "exb_host_pipeline_output_name", "exb_host_pipeline_get", "exb_host_pipeline_stats",
+    "exb_host_pipeline_output_name", "exb_host_pipeline_get", "exb_host_pipeline_output_ptr", "exb_host_pipeline_stats",
     "exb_host_pipeline_dump_profile", "exb_host_pipeline_run_resident", "exb_host_pipeline_trace_size",
     "exb_host_pipeline_trace_entry", "exb_host_op_run",
 ]
@@ -39,6 +39,7 @@ def lib():
         L.exb_host_pipeline_num_outputs.argtypes = [vp]
         L.exb_host_pipeline_output_name.argtypes = [vp, i32, C.c_char_p, i32]
         L.exb_host_pipeline_get.argtypes = [vp, C.c_char_p, vp, C.c_int64, vp]
+        L.exb_host_pipeline_output_ptr.argtypes = [vp, C.c_char_p, C.POINTER(C.POINTER(C.c_float)), vp]
         L.exb_host_pipeline_stats.argtypes = [vp, C.POINTER(i32), C.POINTER(C.c_double)]
         L.exb_host_pipeline_dump_profile.argtypes = [vp, C.c_char_p]
         L.exb_host_pipeline_run_resident.argtypes = [vp, i32, C.POINTER(C.c_double)]
@@ -107,6 +108,13 @@ class Pipeline:
             out = np.empty(tuple(shp), np.float32)
         _check(lib().exb_host_pipeline_get(self._h, name.encode(), out.ctypes.data, out.size, shp))
         return out
+
+    def output_view(self, name):
+        """Zero-copy numpy view of an output of the last forward (valid until the next forward)."""
+        shp = (C.c_int * 4)()
+        ptr = C.POINTER(C.c_float)()
+        _check(lib().exb_host_pipeline_output_ptr(self._h, name.encode(), C.byref(ptr), shp))
+        return np.ctypeslib.as_array(ptr, shape=tuple(shp))
 
     def stats(self):
         n, ms = C.c_int(), C.c_double()

@@ -48,6 +48,9 @@ EXB_API int exb_host_pipeline_output_name(void* p, int i, char* buf, int cap);
 /* Output or any feature map by name (pipeline::get_featmap, pipeline.hpp:32).  out == NULL
  * returns only the shape; the data is fp32 NCHW. */
 EXB_API int exb_host_pipeline_get(void* p, const char* name, float* out, int64_t cap, int* shape4);
+/* The host tensor an output of the last forward lives in (fp32 NCHW), without a copy: what
+ * pipeline<float>::forward returns to a C++ caller.  Valid until the next forward. */
+EXB_API int exb_host_pipeline_output_ptr(void* p, const char* name, const float** data, int* shape4);
 /* Kernels launched by the last forward (-1 when run op by op) and their device time in ms. */
 EXB_API int exb_host_pipeline_stats(void* p, int* launches, double* device_ms);
 EXB_API int exb_host_pipeline_dump_profile(void* p, const char* path);

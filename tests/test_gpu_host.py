@@ -349,3 +349,17 @@ def test_calibration_tool_reproduces_the_builder_int8_graph():
     for n, s in zip(G["resnet_scale_names"], G["resnet_scales"]):      # the reference's own calibration
         assert abs(scales[str(n)] / s - 1.0) < 1e-2
     assert _rel(out, G["resnet_i8_logits"]) < 5e-2
+
+
+def test_output_view_is_the_tensor_forward_returned():
+    h = _host()
+    g, info = models.yolov5s(5)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0)
+    out = p.forward(Y["yolo_x"])
+    for n in info["outputs"]:
+        v = p.output_view(n)
+        assert v.shape == out[n].shape
+        np.testing.assert_array_equal(v, out[n])
+    with pytest.raises(h.HostError):
+        p.output_view("stem_act")          # an inner map is not an output
+    p.close()
