@@ -83,6 +83,26 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     }
 }
 
+// The same over a small register vector, with the selector outside the element loop: one uniform
+// branch per vector instead of a switch per element.
+template <int N>
+__device__ __forceinline__ void apply_act_vec(float (&v)[N], int act) {
+    if (act == EXB_ACT_NONE) return;
+    if (act == EXB_ACT_RELU) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) v[i] = fmaxf(v[i], 0.f);
+    } else if (act == EXB_ACT_RELU6) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) v[i] = fminf(fmaxf(v[i], 0.f), 6.f);
+    } else if (act == EXB_ACT_SILU) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) v[i] = v[i] / (1.f + __expf(-v[i]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) v[i] = apply_act(v[i], act);
+    }
+}
+
 inline bool act_supported(int act) {
     return act == EXB_ACT_NONE || act == EXB_ACT_RELU || act == EXB_ACT_RELU6_QUIRK ||
            act == EXB_ACT_SIGMOID || act == EXB_ACT_RELU6 || act == EXB_ACT_SILU || act == EXB_ACT_HARDSWISH;

@@ -112,8 +112,7 @@ __global__ void __launch_bounds__(128) dw_strip_kernel(const TIn* __restrict__ x
         for (int j = 0; j < TW; ++j) {
             const int ow = ow0 + j;
             if (ow < p.OW) {
-#pragma unroll
-                for (int k = 0; k < V; ++k) acc[j][k] = apply_act(acc[j][k], p.act);
+                apply_act_vec(acc[j], p.act);
                 store8(y + (((int64_t)n * p.OH + oh) * p.OW + ow) * p.cs + cv * V, acc[j], p.out_scale);
             }
         }
@@ -213,8 +212,7 @@ __global__ void __launch_bounds__(128) dw3x3_roll_f16_kernel(const __half* __res
             for (int j = 0; j < TW; ++j) {
                 const int ow = ow0 + j;
                 if (ow < p.OW) {
-#pragma unroll
-                    for (int k = 0; k < V; ++k) acc[j][k] = apply_act(acc[j][k], p.act);
+                    apply_act_vec(acc[j], p.act);
                     store8(y + (((int64_t)n * p.OH + oh) * p.OW + ow) * p.cs + cv * V, acc[j], 1.f);
                 }
             }
@@ -261,8 +259,7 @@ __global__ void __launch_bounds__(128) dw_generic_kernel(const TIn* __restrict__
                 for (int k = 0; k < V; ++k) acc[k] = fmaf(in[k], wv[k], acc[k]);
             }
         }
-#pragma unroll
-        for (int k = 0; k < V; ++k) acc[k] = apply_act(acc[k], p.act);
+        apply_act_vec(acc, p.act);
         store8(y + (((int64_t)n * p.OH + oh) * p.OW + ow) * p.cs + cv * V, acc, p.out_scale);
     }
 }
