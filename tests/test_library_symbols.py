@@ -55,9 +55,22 @@ def test_pure_host_calls_work_without_a_gpu(so_path):
         capi.conv_out_dims(bad)
     # operation classes are registered under the reference's keys
     for key in ("operation_convolution", "operation_convolutiondepthwise", "operation_pooling", "operation_eltwise",
-                "operation_binaryop", "operation_relu", "operation_split", "operation_innerproduct"):
+                "operation_binaryop", "operation_relu", "operation_split", "operation_innerproduct", "operation_clip",
+                "operation_sigmoid", "operation_concat", "operation_interp", "operation_batchnorm", "operation_hardswish",
+                "operation_input", "operation_yolov5focus"):
         assert host.registered(key), key
     assert not host.registered("operation_nonexistent")
+    # capability queries are pure host arithmetic
+    stem = capi.make_conv_desc(8, 224, 224, 3, 64, 7, 2, 3, capi.EXB_F16, capi.EXB_F16, act=capi.ACT_RELU, cin_stride=4,
+                               x_w_pitch=240, x_w_pad=4)
+    assert capi.lib().exb_conv2d_pool_fusable(stem) == 1
+    stem.fuse_pool = 1
+    assert capi.conv_out_dims(stem) == (56, 56)
+    body = capi.make_conv_desc(8, 56, 56, 64, 64, 3, 1, 1, capi.EXB_I8, capi.EXB_I8)
+    assert capi.lib().exb_conv2d_pool_fusable(body) == 0
+    assert capi.lib().exb_conv2d_accepts_planar_input(body) == 1
+    wide = capi.make_conv_desc(8, 7, 7, 512, 512, 3, 1, 1, capi.EXB_I8, capi.EXB_I8)
+    assert capi.lib().exb_conv2d_accepts_planar_input(wide) == 0
 
 
 def test_no_cpu_fallback_in_the_product(so_path):
