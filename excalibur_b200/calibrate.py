@@ -55,7 +55,7 @@ def racy_record_size(op, blob, pos):
     """Bytes the op's init_weights(FILE*) consumes at `pos` (file order = op order)."""
     t = op["type"].lower()
     p = op["params"]
-    if t in ("convolution", "convolutiondepthwise"):
+    if t in ("convolution", "convolutiondepthwise", "deconvolution"):
         cout, wsize, bias = int(p[0]), int(p[6]), int(p.get(5, "0"))
         tag, = struct.unpack_from("<i", blob, pos)
         if tag == RACY_TAG_F32:
@@ -68,6 +68,8 @@ def racy_record_size(op, blob, pos):
         return 4 + 4 * wsize + 4 * nout * bias
     if t == "batchnorm":
         return 16 * int(p[0])
+    if t == "prelu":
+        return 4 * int(p[0])
     return 0
 
 

@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = [
     "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_pool2d_nchw_f32_static", "exb_eltwise_fwd", "exb_binaryop_fwd",
     "exb_binaryop_scalar_fwd", "exb_relu_fwd", "exb_activation_fwd", "exb_quantize_fwd",
     "exb_dequantize_fwd", "exb_concat_fwd", "exb_interp_nearest_fwd", "exb_channel_affine_fwd",
-    "exb_hardswish_fwd", "exb_focus_fwd",
+    "exb_hardswish_fwd", "exb_focus_fwd", "exb_prelu_fwd", "exb_depth_to_space_fwd", "exb_transpose_hw_f32",
 ]
 
 
@@ -105,6 +105,9 @@ def lib():
         L.exb_channel_affine_fwd.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i64, i32, i32, i32, vp]
         L.exb_hardswish_fwd.argtypes = [vp, vp, vp, i64, i32, f32, f32, vp]
         L.exb_focus_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+        L.exb_prelu_fwd.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i64, i32, i32, vp]
+        L.exb_depth_to_space_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+        L.exb_transpose_hw_f32.argtypes = [vp, vp, vp, i64, i32, i32, vp]
         _LIB = L
     return _LIB
 
@@ -447,6 +450,45 @@ def focus(ctx, x, channels=None, out_stride=0, channel_last=True, y=None):
         if y is None:
             y = t.empty((N, 4 * Cc, H // 2, W // 2), device=x.device, dtype=x.dtype)
         check(lib().exb_focus_fwd(ctx.handle, ptr(x), ptr(y), N, Cc, H, W, 0, 0, exb_dtype_of(x), 0, cur_stream()))
+    return y
+
+
+def prelu(ctx, x, slopes, channels=None, channel_last=True, y=None):
+    """y = x >= 0 ? x : x * slopes[c]; slopes: fp32 device tensor with one entry per channel, or one entry."""
+    t = _torch()
+    if y is None:
+        y = t.empty_like(x)
+    if channel_last:
+        cs = x.shape[-1]
+        Cc = channels or cs
+        outer, inner = x.numel() // cs, 1
+    else:
+        Cc, cs = x.shape[1], 0
+        outer, inner = x.shape[0], x.numel() // max(x.shape[0] * x.shape[1], 1)
+    check(lib().exb_prelu_fwd(ctx.handle, ptr(x), ptr(y), ptr(slopes), slopes.numel(), outer, Cc, cs, inner,
+                              exb_dtype_of(x), 1 if channel_last else 0, cur_stream()))
+    return y
+
+
+def depth_to_space(ctx, x, rh, rw, channels, y_stride=0, y=None):
+    """NHWC [N][H][W][xs] with channel (a*rw + b)*channels + c -> [N][H*rh][W*rw][y_stride or channels]."""
+    t = _torch()
+    N, H, W, xs = x.shape
+    ys = y_stride or channels
+    if y is None:
+        y = t.empty((N, H * rh, W * rw, ys), device=x.device, dtype=x.dtype)
+    check(lib().exb_depth_to_space_fwd(ctx.handle, ptr(x), ptr(y), N, H, W, rh, rw, channels, xs, ys,
+                                       exb_dtype_of(x), cur_stream()))
+    return y
+
+
+def transpose_hw(ctx, x, y=None):
+    """fp32 [..., H, W] -> [..., W, H]."""
+    t = _torch()
+    H, W = x.shape[-2], x.shape[-1]
+    if y is None:
+        y = t.empty(tuple(x.shape[:-2]) + (W, H), device=x.device, dtype=x.dtype)
+    check(lib().exb_transpose_hw_f32(ctx.handle, ptr(x), ptr(y), x.numel() // max(H * W, 1), H, W, cur_stream()))
     return y
 
 

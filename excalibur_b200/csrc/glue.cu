@@ -120,6 +120,86 @@ __global__ void __launch_bounds__(kThreads) channel_affine_kernel(const T* x, T*
     }
 }
 
+
+// y = x >= 0 ? x : x * slope[c] (PReLU; one shared slope when n_slope == 1, which is also LeakyReLU).
+// Indexing as channel_affine_kernel; padding channels of a channel-last tensor are written 0.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) prelu_kernel(const T* x, T* y, const float* slope, int n_slope, int64_t count,
+                                                         int C, int cs, int64_t inner, int channel_last) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += step) {
+        const int c = channel_last ? (int)(i % cs) : (int)((i / inner) % C);
+        float v = 0.f;
+        if (c < C) {
+            v = ld1(x + i);
+            v = v >= 0.f ? v : v * slope[n_slope == 1 ? 0 : c];
+        }
+        st1(y + i, v);
+    }
+}
+
+// Channel-last fp16, 8 channels (16 bytes) per thread step; cs is a multiple of 8.
+__global__ void __launch_bounds__(kThreads) prelu_nhwc_f16x8_kernel(const uint4* x, uint4* y, const float* slope,
+                                                                    int n_slope, int64_t nvec, int C, int cs8) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step) {
+        const int c0 = (int)(i % cs8) * 8;
+        uint4 raw = x[i];
+        __half2* h = reinterpret_cast<__half2*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 v = __half22float2(h[k]);
+            const int ca = c0 + 2 * k, cb = ca + 1;
+            const float sa = ca < C ? slope[n_slope == 1 ? 0 : ca] : 0.f;
+            const float sb = cb < C ? slope[n_slope == 1 ? 0 : cb] : 0.f;
+            v.x = ca < C ? (v.x >= 0.f ? v.x : v.x * sa) : 0.f;
+            v.y = cb < C ? (v.y >= 0.f ? v.y : v.y * sb) : 0.f;
+            h[k] = __floats2half2_rn(v.x, v.y);
+        }
+        y[i] = raw;
+    }
+}
+
+// Depth-to-space: y[n][h*rh + a][w*rw + b][c] = x[n][h][w][(a*rw + b)*C + c]; channels c >= C of y are 0.
+// One thread per output element (U = one element of the tensor's type).
+template <typename U>
+__global__ void __launch_bounds__(kThreads) depth_to_space_kernel(const U* __restrict__ x, U* __restrict__ y, int N, int H,
+                                                                  int W, int rh, int rw, int C, int xs, int ys) {
+    const int OH = H * rh, OW = W * rw;
+    const int64_t work = (int64_t)N * OH * OW * ys;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < work; i += step) {
+        const int c = (int)(i % ys);
+        int64_t p = i / ys;
+        const int ox = (int)(p % OW);
+        p /= OW;
+        const int oy = (int)(p % OH);
+        const int n = (int)(p / OH);
+        U v = U(0);
+        if (c < C) {
+            const int h = oy / rh, a = oy - h * rh, w = ox / rw, b = ox - w * rw;
+            v = x[(((int64_t)n * H + h) * W + w) * xs + (a * rw + b) * C + c];
+        }
+        y[i] = v;
+    }
+}
+
+// y[p][w][h] = x[p][h][w] for every plane p; 32x32 tiles through shared memory.
+__global__ void __launch_bounds__(256) transpose_planes_f32_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                                   int H, int W) {
+    __shared__ float tile[32][33];
+    const int64_t plane = blockIdx.z;
+    const float* xp = x + plane * (int64_t)H * W;
+    float* yp = y + plane * (int64_t)H * W;
+    const int w0 = blockIdx.x * 32, h0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int r = ty; r < 32; r += 8)
+        if (h0 + r < H && w0 + tx < W) tile[r][tx] = xp[(int64_t)(h0 + r) * W + w0 + tx];
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8)
+        if (w0 + r < W && h0 + tx < H) yp[(int64_t)(w0 + r) * H + h0 + tx] = tile[tx][r];
+}
+
 }  // namespace
 }  // namespace exb
 
@@ -269,4 +349,70 @@ extern "C" int exb_channel_affine_fwd(exb_ctx* ctx, const void* x, void* y, cons
         channel_affine_kernel<float><<<grid, kThreads, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), mul,
                                                                 add, count, C, cs, inner, channel_last, act);
     return after_launch("exb_channel_affine_fwd");
+}
+
+extern "C" int exb_prelu_fwd(exb_ctx* ctx, const void* x, void* y, const float* slope, int n_slope, int64_t outer, int C,
+                             int c_stride, int64_t inner, int dtype, int channel_last, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(outer >= 0 && C > 0 && inner > 0, "exb_prelu_fwd: bad shape");
+    EXB_REQUIRE(n_slope == 1 || n_slope == C, "exb_prelu_fwd: %d slopes for %d channels", n_slope, C);
+    if (dtype != EXB_F16 && dtype != EXB_F32)
+        return fail(EXB_ERR_UNSUPPORTED, "exb_prelu_fwd supports EXB_F16 and EXB_F32, got dtype %d", dtype);
+    const int cs = channel_last ? (c_stride ? c_stride : C) : C;
+    EXB_REQUIRE(cs >= C, "exb_prelu_fwd: channel stride smaller than channel count");
+    const int64_t count = channel_last ? outer * cs : outer * C * inner;
+    if (count == 0) return EXB_OK;
+    EXB_REQUIRE(x && y && slope, "exb_prelu_fwd: null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == EXB_F16 && channel_last && cs % 8 == 0 && aligned16(x) && aligned16(y)) {
+        const int64_t nvec = count / 8;
+        prelu_nhwc_f16x8_kernel<<<stream_grid(ctx, nvec, kThreads), kThreads, 0, st>>>(
+            static_cast<const uint4*>(x), static_cast<uint4*>(y), slope, n_slope, nvec, C, cs / 8);
+        return after_launch("exb_prelu_fwd");
+    }
+    int grid = stream_grid(ctx, count, kThreads);
+    if (dtype == EXB_F16)
+        prelu_kernel<__half><<<grid, kThreads, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), slope, n_slope,
+                                                        count, C, cs, inner, channel_last);
+    else
+        prelu_kernel<float><<<grid, kThreads, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), slope, n_slope,
+                                                       count, C, cs, inner, channel_last);
+    return after_launch("exb_prelu_fwd");
+}
+
+extern "C" int exb_depth_to_space_fwd(exb_ctx* ctx, const void* x, void* y, int N, int H, int W, int rh, int rw, int C,
+                                      int x_stride, int y_stride, int dtype, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(N >= 0 && H >= 0 && W >= 0 && rh > 0 && rw > 0 && C > 0, "exb_depth_to_space_fwd: bad shape");
+    const int64_t es = (int64_t)dtype_size(dtype);
+    if (es != 2 && es != 4) return fail(EXB_ERR_UNSUPPORTED, "exb_depth_to_space_fwd: dtype %d", dtype);
+    const int xs = x_stride ? x_stride : rh * rw * C, ys = y_stride ? y_stride : C;
+    EXB_REQUIRE(xs >= rh * rw * C && ys >= C, "exb_depth_to_space_fwd: stride smaller than channel count");
+    const int64_t work = (int64_t)N * H * rh * W * rw * ys;
+    if (work == 0) return EXB_OK;
+    EXB_REQUIRE(x && y, "exb_depth_to_space_fwd: null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = stream_grid(ctx, work, kThreads);
+    if (es == 2)
+        depth_to_space_kernel<uint16_t><<<grid, kThreads, 0, st>>>(static_cast<const uint16_t*>(x), static_cast<uint16_t*>(y),
+                                                                   N, H, W, rh, rw, C, xs, ys);
+    else
+        depth_to_space_kernel<uint32_t><<<grid, kThreads, 0, st>>>(static_cast<const uint32_t*>(x), static_cast<uint32_t*>(y),
+                                                                   N, H, W, rh, rw, C, xs, ys);
+    return after_launch("exb_depth_to_space_fwd");
+}
+
+extern "C" int exb_transpose_hw_f32(exb_ctx* ctx, const float* x, float* y, int64_t planes, int H, int W, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(planes >= 0 && H >= 0 && W >= 0, "exb_transpose_hw_f32: bad shape");
+    if (planes == 0 || H == 0 || W == 0) return EXB_OK;
+    EXB_REQUIRE(x && y && x != y, "exb_transpose_hw_f32: null or aliased buffer");
+    EXB_REQUIRE((H + 31) / 32 <= 65535, "exb_transpose_hw_f32: height %d too large", H);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int64_t p0 = 0; p0 < planes; p0 += 65535) {
+        const int64_t np = planes - p0 < 65535 ? planes - p0 : 65535;
+        dim3 grid((W + 31) / 32, (H + 31) / 32, (unsigned)np);
+        transpose_planes_f32_kernel<<<grid, 256, 0, st>>>(x + p0 * (int64_t)H * W, y + p0 * (int64_t)H * W, H, W);
+    }
+    return after_launch("exb_transpose_hw_f32");
 }

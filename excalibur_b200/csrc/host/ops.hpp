@@ -326,5 +326,95 @@ protected:
     virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
 };
 
+// y = x >= 0 ? x : slope[c] * x: key 0 = number of slopes (1 = shared by all channels); weights are the
+// slopes, no quantize tag (reference src/Excalibur/operation_prelu.cpp:10-56).
+template <typename Dtype>
+class operation_prelu : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_prelu(const operation_param& param);
+    virtual const char* type() const { return "PReLU"; }
+    virtual int init_weights();
+    virtual int init_weights(FILE* fp);
+    int num_slope_ = 0;
+    const float* slopes_gpu() const { return this->weights_f32_[0]->gpu_data(); }
+    const float* slopes_cpu() const { return this->weights_f32_[0]->cpu_data(); }
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
+// y = x < 0 ? alpha * x : x: key 0 = alpha (reference src/Excalibur/operation_leakyrelu.cpp:12-58).
+template <typename Dtype>
+class operation_leakyrelu : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_leakyrelu(const operation_param& param);
+    virtual const char* type() const { return "LeakyRelu"; }
+    float alpha_ = 0.f;
+    const float* slope_gpu();      // one-element device array holding alpha
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    std::shared_ptr<memory::tensor<float>> slope_;
+};
+
+// Transposed convolution, fp32 weights [Cin][Cout][kh][kw] behind a quantize tag of 0 (reference
+// src/Excalibur/operation_deconvolution.cpp:14-41): out[co][ih*s + a][iw*s + b] += sum_ci W[ci][co][a][b] *
+// in[ci][ih][iw], output (H-1)*s + k - pads (:83-150).  Implemented for kernel == stride, no padding, one
+// group - taps never overlap, so it is a 1x1 convolution to kh*kw*Cout channels (tensor cores) followed by
+// a depth-to-space copy; other shapes are refused.
+template <typename Dtype>
+class operation_deconvolution : public operation_general_conv<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_deconvolution(const operation_param& param);
+    virtual ~operation_deconvolution();
+    virtual int init_weights();
+    virtual int init_weights(FILE* fp);
+    bool supported() const;
+    int in_channels() const { return this->input_channel_; }
+    // the 1x1 convolution to kh*kw*Cout channels; cout_stride is left to the caller
+    exb_conv_desc inner_desc(int N, int H, int W, int cin_stride) const;
+    // packed weights of that convolution (output channel (a*kw + b)*Cout + co), with an optional per-output-
+    // channel affine map (Cout entries) folded in as operation_convolution::packed does
+    exb_conv_weights* packed(exb_ctx* ctx, const exb_conv_desc& d, const float* post_mul = nullptr,
+                             const float* post_add = nullptr, const void* tag = nullptr);
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    struct entry { int cin_stride, cout_stride; exb_conv_weights* w; const void* tag; };
+    std::vector<entry> packed_;
+    device_scratch scratch_in_, scratch_mid_, scratch_out_;
+};
+
+// View of the same NCHW data with another shape: keys 0 w, 1 h, 2 c (0 keeps, -1 deduces; n is kept;
+// reference src/Excalibur/operation_reshape.cpp:10-84).
+template <typename Dtype>
+class operation_reshape : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_reshape(const operation_param& param);
+    virtual const char* type() const { return "Reshape"; }
+    int w_ = 0, h_ = 0, c_ = 0, permute_ = 0;
+    // {n, c, h, w} of the result for an NCHW input of that shape
+    std::vector<int> out_shape(const std::vector<int>& in) const;
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
+// Axis permutation of the (h, w, c) axes: key 0 = list.  The identity and 1,0,2 (swap h and w in every
+// channel plane: out[n][c][w][h] = in[n][c][h][w], reference src/Excalibur/operation_transpose.cpp:39-66)
+// are implemented; the other permutations are refused.
+template <typename Dtype>
+class operation_transpose : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_transpose(const operation_param& param);
+    virtual const char* type() const { return "Transpose"; }
+    std::vector<int> perms_;
+    bool is_identity() const { return perms_.size() == 3 && perms_[0] == 0 && perms_[1] == 1 && perms_[2] == 2; }
+    bool is_swap_hw() const { return perms_.size() == 3 && perms_[0] == 1 && perms_[1] == 0 && perms_[2] == 2; }
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
 }  // namespace excalibur
 }  // namespace glasssix

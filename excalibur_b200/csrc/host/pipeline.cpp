@@ -67,6 +67,7 @@ struct fmap_info {
     std::shared_ptr<dev_buf> f16, i8, f32;
     std::vector<std::shared_ptr<dev_buf>> extra_i8;
     bool produced = false;
+    bool f32_only = false;         // result of a Reshape / Transpose at the tail of the graph: fp32 NCHW only
 };
 
 struct plan_step {
@@ -95,7 +96,8 @@ public:
     std::string unsupported_reason() const {
         static const std::set<std::string> ok = {"convolution", "convolutiondepthwise", "pooling", "eltwise", "binaryop",
                                                   "relu", "split", "innerproduct", "clip", "sigmoid", "concat", "interp",
-                                                 "batchnorm", "hardswish", "input", "yolov5focus"};
+                                                 "batchnorm", "hardswish", "input", "yolov5focus", "prelu", "leakyrelu",
+                                                 "deconvolution", "reshape", "transpose"};
         for (const auto& p : params_) {
             std::string t = p.type_;
             std::transform(t.begin(), t.end(), t.begin(), ::tolower);
@@ -337,11 +339,14 @@ void fused_plan::build(int N, int C, int H, int W) {
     };
     for (size_t i = 0; i < n_ops; ++i) {
         const std::string t = lower_type(params_[i]);
-        if (absorbed[i] || (t != "convolution" && t != "convolutiondepthwise")) continue;
+        if (absorbed[i] || (t != "convolution" && t != "convolutiondepthwise" && t != "deconvolution")) continue;
+        // null for a Deconvolution, which has no built-in activation and takes part in the BatchNorm and
+        // activation patterns only
         auto* conv = dynamic_cast<operation_convolution<float>*>(ops_[i].get());
+        auto* gconv = dynamic_cast<operation_general_conv<float>*>(ops_[i].get());
         group g;
         g.conv = (int)i;
-        g.act = conv->exb_activation();
+        g.act = conv ? conv->exb_activation() : EXB_ACT_NONE;
         g.out = root(out_ids[i][0]);
         g.exec_at = (int)i;
         int j, sj = -1, mk = -1;
@@ -350,7 +355,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         if (g.act == EXB_ACT_NONE && (j = sole_consumer(g.out)) >= 0 && !absorbed[j] &&
             lower_type(params_[j]) == "batchnorm") {
             auto* bn = dynamic_cast<operation_batchnorm<float>*>(ops_[j].get());
-            if (bn && bn->channels_ == conv->output_channel_) {
+            if (bn && bn->channels_ == gconv->output_channel_) {
                 g.bn = j;
                 absorbed[j] = 1;
                 g.out = root(out_ids[j][0]);
@@ -519,6 +524,8 @@ void fused_plan::build(int N, int C, int H, int W) {
         fmap_info& x = fmaps_[root(in_ids[i][0])];
         fmap_info& y = fmaps_[g.out];
         CHECK(x.produced) << "feature map " << x.name << " is consumed before it is produced";
+        if (x.f32_only)
+            NOT_IMPLEMENTED << " (fused plan: " << params_[i].name_ << " reads the result of a Reshape / Transpose; call set_fusion(false))";
         if (t == "convolutiondepthwise") {
             auto* dw = dynamic_cast<operation_convolutiondepthwise<float>*>(ops_[i].get());
             CHECK_EQ(dw->output_channel_, dw->group_);
@@ -539,6 +546,35 @@ void fused_plan::build(int N, int C, int H, int W) {
             add_step(params_[i].name_, [=](cudaStream_t st) {
                 exb_check(exb_dwconv2d_fwd(ctx, &d, xin, w, yo, st), "exb_dwconv2d_fwd");
             });
+            finish_forms(y, false);
+            return;
+        }
+        if (t == "deconvolution") {
+            auto* dc = dynamic_cast<operation_deconvolution<float>*>(ops_[i].get());
+            if (!dc->supported())
+                NOT_IMPLEMENTED << " (Deconvolution " << params_[i].name_
+                                << ": implemented for kernel == stride, no padding, no dilation, one group)";
+            CHECK_EQ(x.C, dc->in_channels()) << params_[i].name_ << ": input channels do not match the weights";
+            const int rh = dc->kernel_size_h_, rw = dc->kernel_size_w_, Cout = dc->output_channel_;
+            exb_conv_desc d = dc->inner_desc(x.N, x.H, x.W, x.cs);
+            d.act = g.act;       // element-wise, so it commutes with the depth-to-space copy
+            d.cout_stride = round_up(d.Cout, d.Cout > 16 ? 32 : 16);
+            y.need_f16 = true;
+            set_shape(y, x.N, Cout, x.H * rh, x.W * rw);
+            const void* xin = form_f16(x);
+            auto mid = std::make_shared<dev_buf>();
+            void* tmp = mid->ensure((size_t)x.N * x.H * x.W * d.cout_stride * 2, device_);
+            void* yo = form_f16(y);
+            const operation_batchnorm<float>* bn =
+                g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;
+            exb_conv_weights* w = bn ? dc->packed(ctx, d, bn->mul()->cpu_data(), bn->add()->cpu_data(), bn) : dc->packed(ctx, d);
+            const int n = x.N, h = x.H, wd = x.W, xs = d.cout_stride, ys = y.cs;
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                (void)mid;       // keeps the intermediate tensor alive as long as the step
+                exb_check(exb_conv2d_fwd(ctx, &d, xin, w, nullptr, tmp, nullptr, st), "exb_conv2d_fwd");
+                exb_check(exb_depth_to_space_fwd(ctx, tmp, yo, n, h, wd, rh, rw, Cout, xs, ys, EXB_F16, st),
+                          "exb_depth_to_space_fwd");
+            }, 2);
             finish_forms(y, false);
             return;
         }
@@ -601,10 +637,47 @@ void fused_plan::build(int N, int C, int H, int W) {
             run_conv_group(groups[run_group_at[i]]);
             continue;
         }
-        if (absorbed[i] || alias_op[i] || t == "convolution" || t == "convolutiondepthwise") continue;
+        if (absorbed[i] || alias_op[i] || t == "convolution" || t == "convolutiondepthwise" || t == "deconvolution") continue;
         fmap_info& x = fmaps_[root(in_ids[i][0])];
         fmap_info& y = fmaps_[root(out_ids[i][0])];
         CHECK(x.produced) << "feature map " << x.name << " is consumed before it is produced";
+        if (t == "reshape" || t == "transpose") {
+            // Shape surgery is defined on NCHW data: it runs on the fp32 NCHW copy of the tensor, and what it
+            // produces exists in that form only (the graph's tail: detection heads).
+            float* src = static_cast<float*>(form_f32(x));
+            if (!x.f32_only) {
+                const void* h16 = form_f16(x);
+                const int n = x.N, c = x.C, h = x.H, w = x.W, cs = x.cs;
+                add_step("emit " + x.name, [=](cudaStream_t st) {
+                    exb_check(exb_nhwc_to_nchw_f32(ctx, h16, EXB_F16, src, n, c, h, w, cs, 1.f, st), "exb_nhwc_to_nchw_f32");
+                });
+            }
+            y.f32_only = y.need_f32 = y.produced = true;
+            auto* tr = t == "transpose" ? dynamic_cast<operation_transpose<float>*>(ops_[i].get()) : nullptr;
+            if (t == "reshape") {
+                auto* rs = dynamic_cast<operation_reshape<float>*>(ops_[i].get());
+                const std::vector<int> shp = rs->out_shape({x.N, x.C, x.H, x.W});
+                y.N = shp[0]; y.C = shp[1]; y.H = shp[2]; y.W = shp[3]; y.cs = y.C;
+                y.f32 = x.f32;       // same bytes, new shape
+            } else if (tr->is_identity()) {
+                y.N = x.N; y.C = x.C; y.H = x.H; y.W = x.W; y.cs = y.C;
+                y.f32 = x.f32;
+            } else {
+                if (!tr->is_swap_hw()) NOT_IMPLEMENTED << " (Transpose is implemented for the permutations 0,1,2 and 1,0,2)";
+                y.N = x.N; y.C = x.C; y.H = x.W; y.W = x.H; y.cs = y.C;
+                float* dst = static_cast<float*>(form_f32(y));
+                const int64_t planes = (int64_t)x.N * x.C;
+                const int h = x.H, w = x.W;
+                add_step(params_[i].name_, [=](cudaStream_t st) {
+                    exb_check(exb_transpose_hw_f32(ctx, src, dst, planes, h, w, st), "exb_transpose_hw_f32");
+                });
+            }
+            continue;
+        }
+        for (int f : in_ids[i])
+            if (fmaps_[root(f)].f32_only)
+                NOT_IMPLEMENTED << " (fused plan: " << params_[i].type_ << " " << params_[i].name_
+                                << " reads the result of a Reshape / Transpose; call set_fusion(false))";
         if (t == "pooling") {
             auto* pool = dynamic_cast<operation_pooling<float>*>(ops_[i].get());
             exb_pool_desc d = pool->desc(x.N, x.H, x.W, x.C, x.cs, EXB_F16);
@@ -749,6 +822,23 @@ void fused_plan::build(int N, int C, int H, int W) {
                 add_step(params_[i].name_, [=](cudaStream_t st) {
                     exb_check(exb_hardswish_fwd(ctx, xin, yo, count, EXB_F16, alpha, beta, st), "exb_hardswish_fwd");
                 });
+            } else if (t == "prelu" || t == "leakyrelu") {
+                const float* slope = nullptr;
+                int n_slope = 1;
+                if (t == "prelu") {
+                    auto* pr = dynamic_cast<operation_prelu<float>*>(ops_[i].get());
+                    if (pr->num_slope_ != 1) CHECK_EQ(pr->num_slope_, x.C) << params_[i].name_ << ": slopes do not match the channels";
+                    slope = pr->slopes_gpu();
+                    n_slope = pr->num_slope_;
+                } else {
+                    slope = dynamic_cast<operation_leakyrelu<float>*>(ops_[i].get())->slope_gpu();
+                }
+                const void* xin = form_f16(x);
+                const int64_t rows = (int64_t)x.N * x.H * x.W;
+                const int c = x.C, cs = x.cs;
+                add_step(params_[i].name_, [=](cudaStream_t st) {
+                    exb_check(exb_prelu_fwd(ctx, xin, yo, slope, n_slope, rows, c, cs, 1, EXB_F16, 1, st), "exb_prelu_fwd");
+                });
             } else if (t == "relu" || t == "clip" || t == "sigmoid" || t == "hardswish") {
                 const int act = act_of_op((int)i);
                 if (act < 0) NOT_IMPLEMENTED << " (" << params_[i].type_ << " parameters)";
@@ -803,7 +893,8 @@ void fused_plan::build(int N, int C, int H, int W) {
         auto t = std::shared_ptr<memory::tensor<float>>(
             new memory::tensor<float>(std::vector<int>{f.N, f.C, f.H, f.W}, device_, memory::NCHW, nullptr));
         host_out_[name] = t;
-        if (f.need_f32 && f.f32 && f.H == 1 && f.W == 1) continue;   // already fp32 [N][C]
+        if (f.need_f32 && f.f32 && f.H == 1 && f.W == 1 && !f.f32_only) continue;   // already fp32 [N][C]
+        if (f.f32_only) continue;                                    // Reshape / Transpose results are fp32 NCHW already
         const void* src = form_f16(f);
         float* dst = static_cast<float*>(form_f32(f));
         const int n = f.N, c = f.C, h = f.H, w = f.W, cs = f.cs;

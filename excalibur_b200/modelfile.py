@@ -143,6 +143,27 @@ class GraphBuilder:
             self.blob += np.ascontiguousarray(v, "<f4").tobytes()
         return self._op("BatchNorm", name, [x], [y], "0=%d 1=%r" % (len(slope), float(eps)))
 
+    def prelu(self, name, x, y, slopes):
+        """Weights: the slopes, no quantize tag (1 slope = shared by every channel)."""
+        self.blob += np.ascontiguousarray(slopes, "<f4").tobytes()
+        return self._op("PReLU", name, [x], [y], "0=%d" % len(slopes))
+
+    def leakyrelu(self, name, x, y, alpha):
+        return self._op("LeakyRelu", name, [x], [y], "0=%r" % float(alpha))
+
+    def deconv(self, name, x, y, w, bias=None, stride=1, pad=0):
+        """w: [Cin][Cout][kh][kw] fp32 (the transposed-convolution layout of the reference)."""
+        _, cout, kh, kw = w.shape
+        self._conv_weights(w, bias, None)
+        return self._op("Deconvolution", name, [x], [y],
+                        self._conv_params(cout, kh, kw, stride, pad, bias is not None, int(w.size), 1, 0, False) + " 7=1")
+
+    def reshape(self, name, x, y, w=0, h=0, c=0):
+        return self._op("Reshape", name, [x], [y], "0=%d 1=%d 2=%d" % (w, h, c))
+
+    def transpose(self, name, x, y, perm=(1, 0, 2)):
+        return self._op("Transpose", name, [x], [y], "0=" + ",".join(str(int(v)) for v in perm))
+
     def innerproduct(self, name, x, y, w, bias=None):
         """w: [out][in] fp32."""
         self.blob += struct.pack("<i", RACY_TAG_F32)

@@ -356,6 +356,21 @@ EXB_API int exb_hardswish_fwd(exb_ctx* ctx, const void* x, void* y, int64_t coun
  * (EXB_F16, EXB_I8 or EXB_F32; padding channels of the output are written as 0). */
 EXB_API int exb_focus_fwd(exb_ctx* ctx, const void* x, void* y, int N, int C, int H, int W, int in_stride,
                           int out_stride, int dtype, int channel_last, void* stream);
+/* y = x >= 0 ? x : x * slope[c]: operation_prelu (src/Excalibur/operation_prelu.cpp:58-147; n_slope == C, or 1 for
+ * a slope shared by every channel) and operation_leakyrelu (src/Excalibur/operation_leakyrelu.cpp:31-58; n_slope
+ * == 1).  slope is a device array.  Tensor indexing as exb_channel_affine_fwd.  EXB_F16 or EXB_F32; y may alias x. */
+EXB_API int exb_prelu_fwd(exb_ctx* ctx, const void* x, void* y, const float* slope, int n_slope, int64_t outer,
+                          int C, int c_stride, int64_t inner, int dtype, int channel_last, void* stream);
+/* Channel-last depth-to-space, the scatter half of a transposed convolution whose kernel equals its stride
+ * (operation_deconvolution, src/Excalibur/operation_deconvolution.cpp:83-150: GEMM to a column buffer, then
+ * col2im): y[n][h*rh + a][w*rw + b][c] = x[n][h][w][(a*rw + b)*C + c].  x has x_stride physical channels
+ * (0 = rh*rw*C), y has y_stride (0 = C; channels c >= C are written as 0).  EXB_F16 or EXB_F32. */
+EXB_API int exb_depth_to_space_fwd(exb_ctx* ctx, const void* x, void* y, int N, int H, int W, int rh, int rw,
+                                   int C, int x_stride, int y_stride, int dtype, void* stream);
+/* y[p][w][h] = x[p][h][w] for `planes` fp32 planes: operation_transpose with permutation 1,0,2
+ * (src/Excalibur/operation_transpose.cpp:47-66). */
+EXB_API int exb_transpose_hw_f32(exb_ctx* ctx, const float* x, float* y, int64_t planes, int H, int W,
+                                 void* stream);
 EXB_API int exb_concat_fwd(exb_ctx* ctx, int n_in, const void* const* xs, const int64_t* widths,
                            const int64_t* x_strides, void* y, int64_t y_stride, int64_t rows,
                            int dtype, void* stream);

@@ -260,6 +260,65 @@ def focus(x):
     return out
 
 
+def prelu(x, slopes):
+    """y = x >= 0 ? x : slope[c] * x, one shared slope when len(slopes) == 1
+    (src/Excalibur/operation_prelu.cpp:58-147)."""
+    x = _f32(x)
+    sl = _f32(slopes).reshape(-1)
+    sl = np.float32(sl[0]) if sl.size == 1 else sl[None, :, None, None]
+    return np.where(x >= 0, x, (x * sl).astype(np.float32)).astype(np.float32)
+
+
+def leakyrelu(x, alpha):
+    """y = x < 0 ? alpha * x : x (src/Excalibur/operation_leakyrelu.cpp:31-58)."""
+    x = _f32(x)
+    return np.where(x < 0, (x * np.float32(alpha)).astype(np.float32), x).astype(np.float32)
+
+
+def deconv2d_f32(x, w, bias=None, stride=1, pad=0):
+    """Transposed convolution, weights [Cin][Cout][kh][kw], one group:
+    out[n][co][ih*s + a - pad][iw*s + b - pad] += sum_ci w[ci][co][a][b] * x[n][ci][ih][iw], output
+    (H - 1)*s + k - 2*pad (src/Excalibur/operation_deconvolution.cpp:83-150: GEMM into a column buffer, col2im
+    scatter-add, bias GEMM).  Accumulated in fp32 per tap, then scattered."""
+    x = _f32(x)
+    w = _f32(w)
+    n, cin, h, wd = x.shape
+    _, cout, kh, kw = w.shape
+    sh, sw = _pair(stride)
+    ph, pw = _pair(pad)
+    oh, ow = (h - 1) * sh + kh - 2 * ph, (wd - 1) * sw + kw - 2 * pw
+    full = np.zeros((n, cout, (h - 1) * sh + kh, (wd - 1) * sw + kw), np.float32)
+    for a in range(kh):
+        for b in range(kw):
+            col = np.einsum("nchw,cd->ndhw", x, w[:, :, a, b]).astype(np.float32)
+            full[:, :, a:a + (h - 1) * sh + 1:sh, b:b + (wd - 1) * sw + 1:sw] += col
+    out = full[:, :, ph:ph + oh, pw:pw + ow]
+    if bias is not None:
+        out = out + _f32(bias)[None, :, None, None]
+    return np.ascontiguousarray(out, np.float32)
+
+
+def reshape_nchw(x, w=0, h=0, c=0):
+    """New shape over the same NCHW bytes: a positive key replaces the axis, 0 keeps it, -1 deduces it; n is
+    kept (src/Excalibur/operation_reshape.cpp:48-84)."""
+    x = _f32(x)
+    s = list(x.shape)
+    for axis, v in ((1, c), (2, h), (3, w)):
+        if v > 0:
+            s[axis] = v
+    for axis, v in ((1, c), (2, h), (3, w)):
+        if v < 0:
+            rest = int(np.prod([s[a] for a in range(4) if a != axis]))
+            s[axis] = x.size // rest
+    return np.ascontiguousarray(x).reshape(s)
+
+
+def transpose_hw(x):
+    """out[n][c][w][h] = in[n][c][h][w]: Transpose with permutation 1,0,2
+    (src/Excalibur/operation_transpose.cpp:47-66)."""
+    return np.ascontiguousarray(np.swapaxes(_f32(x), 2, 3))
+
+
 # ---- layout helpers -------------------------------------------------------------------
 def nchw_to_nhwc(a):
     return np.ascontiguousarray(np.transpose(a, (0, 2, 3, 1)))

@@ -6,6 +6,7 @@ Run in a container that has the reference tree (it cannot travel to the GPU box)
     python tests/golden/make_golden.py             # both fixture files
     python tests/golden/make_golden.py mobilenet   # tests/golden/mobilenet_vectors.npz only
     python tests/golden/make_golden.py yolo        # tests/golden/yolo_vectors.npz only
+    python tests/golden/make_golden.py shipped     # tests/golden/shipped_model_vectors.npz only
 
 Every case stores its inputs, weights and the reference's output, so the fixture pins the oracle
 (oracle/exb_oracle.c) and, through it, the CUDA kernels, without the reference being present.
@@ -18,7 +19,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 
-from excalibur_b200 import models  # noqa: E402
+from excalibur_b200 import model_zoo, models  # noqa: E402
 from excalibur_b200.modelfile import GraphBuilder  # noqa: E402
 from oracle import ref_lib  # noqa: E402
 
@@ -134,6 +135,64 @@ def main():
     print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
     mobilenet()
     yolo()
+    shipped()
+
+
+def shipped():
+    """PReLU, LeakyRelu, Deconvolution, Reshape + Transpose one at a time, and the three networks with the
+    architecture of the reference's shipped descriptions (excalibur_b200/model_zoo.py) at small input
+    sizes -> tests/golden/shipped_model_vectors.npz."""
+    r = np.random.default_rng(20240609)
+    out = {}
+    x = r.standard_normal((2, 13, 5, 7)).astype(np.float32)
+    sl = r.uniform(0.05, 0.5, 13).astype(np.float32)
+    out["act_x"], out["prelu_slopes"] = x, sl
+    g = GraphBuilder(); g.prelu("p", "in", "out", sl)
+    out["prelu_out"], = run(g, x)
+    g = GraphBuilder(); g.prelu("p", "in", "out", sl[:1])
+    out["prelu_shared_out"], = run(g, x)
+    g = GraphBuilder(); g.leakyrelu("p", "in", "out", 0.1)
+    out["leaky_out"], = run(g, x)
+    # transposed convolutions: kernel == stride (the shipped models' shape), and two overlapping shapes that
+    # only pin the CPU restatement
+    for tag, cin, cout, k, s, p in (("deconv_k2s2", 13, 6, 2, 2, 0), ("deconv_k2s2_c1", 13, 1, 2, 2, 0),
+                                    ("deconv_k3s2p1", 13, 6, 3, 2, 1), ("deconv_k4s2p1", 13, 6, 4, 2, 1)):
+        w = (r.standard_normal((cin, cout, k, k)) * 0.2).astype(np.float32)
+        b = r.standard_normal(cout).astype(np.float32)
+        g = GraphBuilder(); g.deconv("d", "in", "out", w, b, s, p)
+        out[tag + "_w"], out[tag + "_b"] = w, b
+        out[tag + "_cfg"] = np.array([k, s, p], np.int32)
+        out[tag + "_out"], = run(g, x)
+    x = r.standard_normal((2, 12, 4, 5)).astype(np.float32)
+    g = GraphBuilder()
+    g.reshape("r", "in", "m", w=20, h=4, c=3)
+    g.transpose("t", "m", "out")
+    out["rt_x"] = x
+    out["rt_out"], = run(g, x)
+
+    def net(tag, g, info, x, inner=()):
+        p = ref_lib.RefPipeline(g.phai_text(), g.racy_bytes())
+        res = p.forward(x)
+        out[tag + "_x"] = x
+        for n in info["outputs"]:
+            out["%s_out_%s" % (tag, n)] = res[n]
+        for n in inner:
+            out["%s_map_%s" % (tag, n)] = p.featmap(n)
+        p.close()
+
+    g, info = model_zoo.det_db_resnet18()
+    net("detdb", g, info, r.uniform(0, 255, (2, 3, 64, 96)).astype(np.float32), ("s2_b2_act", "fuse_out", "head_relu_out"))
+    g, info = model_zoo.mobile_unicorn()
+    net("unicorn", g, info, r.uniform(0, 255, (2, 3, 128, 128)).astype(np.float32), ("conv2_4_res", "conv5_ex_act"))
+    # batch 1: the reference's YoloV5Focus only fills image 0
+    g, info = model_zoo.yolov5s_simp(size=128)
+    net("yolosimp", g, info, r.uniform(0, 255, (1, 3, 128, 128)).astype(np.float32), ("csp2_cv4_act", "spp_cat_out"))
+    path = os.path.join(ROOT, "tests", "golden", "shipped_model_vectors.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
+    for k, v in out.items():
+        if "_out" in k:
+            print("  %-40s %-18s |max| %.4g finite=%s" % (k, v.shape, np.abs(v).max(), np.isfinite(v).all()))
 
 
 def yolo():
@@ -270,5 +329,7 @@ if __name__ == "__main__":
         mobilenet()
     elif sys.argv[1:] == ["yolo"]:
         yolo()
+    elif sys.argv[1:] == ["shipped"]:
+        shipped()
     else:
         main()

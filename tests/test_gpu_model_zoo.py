@@ -1,0 +1,196 @@
+"""PReLU / LeakyRelu / Deconvolution / Reshape / Transpose kernels and host operations, and the three
+networks with the architecture of the reference's shipped descriptions, against outputs of the
+reference CPU library (golden vectors) and the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+
+from excalibur_b200 import model_zoo
+from excalibur_b200.modelfile import GraphBuilder
+from oracle import exb_oracle as O
+from tests.util import f16_round
+
+pytestmark = pytest.mark.gpu
+S = np.load(os.path.join(os.path.dirname(__file__), "golden", "shipped_model_vectors.npz"))
+
+
+def _host():
+    from excalibur_b200 import host
+    return host
+
+
+def _rel(a, b):
+    return float(np.abs(a.astype(np.float64) - b).max() / max(np.abs(b).max(), 1e-12))
+
+
+def _params(g, line=0):
+    return g.lines[line].split(" ", 6)[6]
+
+
+# ---- kernels through the C ABI ----------------------------------------------------------------------
+@pytest.mark.parametrize("C,cs", [(13, 16), (64, 64), (5, 5), (40, 48)])
+def test_prelu_kernel_nhwc_f16(C, cs):
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    r = np.random.default_rng(C)
+    x = f16_round(r.standard_normal((2, C, 9, 7)).astype(np.float32) * 3)
+    sl = r.uniform(0.01, 0.9, C).astype(np.float32)
+    xh = torch.full((2, 9, 7, cs), 7.0, dtype=torch.float16, device="cuda")      # garbage in the padding channels
+    xh[..., :C] = torch.from_numpy(O.nchw_to_nhwc(x)).cuda().half()
+    for slopes in (sl, sl[:1]):
+        y = capi.prelu(ctx, xh, torch.from_numpy(slopes).cuda(), channels=C)
+        torch.cuda.synchronize()
+        got = O.nhwc_to_nchw(y[..., :C].float().cpu().numpy())
+        np.testing.assert_array_equal(got, f16_round(O.prelu(x, slopes)))
+        assert float(y[..., C:].abs().sum()) == 0.0
+    ctx.close()
+
+
+def test_prelu_kernel_nchw_f32_and_refusals():
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    x = S["act_x"]
+    xd = torch.from_numpy(x).cuda()
+    y = capi.prelu(ctx, xd, torch.from_numpy(S["prelu_slopes"]).cuda(), channel_last=False)
+    np.testing.assert_array_equal(y.cpu().numpy(), S["prelu_out"])
+    empty = torch.empty((0, 13, 5, 7), device="cuda")
+    assert capi.prelu(ctx, empty, torch.from_numpy(S["prelu_slopes"]).cuda(), channel_last=False).numel() == 0
+    with pytest.raises(capi.ExbError):
+        capi.prelu(ctx, xd, torch.zeros(4, device="cuda"), channel_last=False)       # 4 slopes, 13 channels
+    ctx.close()
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_depth_to_space_kernel(dtype):
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    r = np.random.default_rng(3)
+    N, H, W, rh, rw, C, xs, ys = 2, 5, 6, 2, 3, 7, 48, 8
+    x = r.standard_normal((N, H, W, xs)).astype(np.float32)
+    td = torch.float16 if dtype == "f16" else torch.float32
+    xd = torch.from_numpy(x).cuda().to(td)
+    y = capi.depth_to_space(ctx, xd, rh, rw, C, y_stride=ys)
+    torch.cuda.synchronize()
+    src = xd.float().cpu().numpy()
+    want = np.zeros((N, H * rh, W * rw, ys), np.float32)
+    for a in range(rh):
+        for b in range(rw):
+            want[:, a::rh, b::rw, :C] = src[..., (a * rw + b) * C:(a * rw + b + 1) * C]
+    np.testing.assert_array_equal(y.float().cpu().numpy(), want)
+    ctx.close()
+
+
+@pytest.mark.parametrize("shape", [(3, 5, 33, 70), (1, 1, 1, 1), (2, 3, 64, 32), (0, 4, 5, 6)])
+def test_transpose_kernel(shape):
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    x = np.random.default_rng(4).standard_normal(shape).astype(np.float32)
+    y = capi.transpose_hw(ctx, torch.from_numpy(x).cuda())
+    np.testing.assert_array_equal(y.cpu().numpy(), O.transpose_hw(x))
+    ctx.close()
+
+
+# ---- host operations created through the reflector ----------------------------------------------------
+def test_operation_prelu_leakyrelu():
+    h = _host()
+    x = S["act_x"]
+    g = GraphBuilder(); g.prelu("p", "in", "out", S["prelu_slopes"])
+    np.testing.assert_array_equal(h.run_op("PReLU", _params(g), [x], g.racy_bytes()), S["prelu_out"])
+    g = GraphBuilder(); g.prelu("p", "in", "out", S["prelu_slopes"][:1])
+    np.testing.assert_array_equal(h.run_op("PReLU", _params(g), [x], g.racy_bytes()), S["prelu_shared_out"])
+    np.testing.assert_array_equal(h.run_op("LeakyRelu", "0=0.1", [x]), S["leaky_out"])
+    with pytest.raises(h.HostError):
+        h.run_op("LeakyRelu", "7=1", [x])
+
+
+@pytest.mark.parametrize("tag", ["deconv_k2s2", "deconv_k2s2_c1"])
+def test_operation_deconvolution(tag):
+    h = _host()
+    k, s, p = (int(v) for v in S[tag + "_cfg"])
+    g = GraphBuilder(); g.deconv("d", "in", "out", S[tag + "_w"], S[tag + "_b"], s, p)
+    y = h.run_op("Deconvolution", _params(g), [S["act_x"]], g.racy_bytes())
+    assert y.shape == S[tag + "_out"].shape
+    # fp16 operands, fp32 accumulation: exact against the oracle on fp16-rounded operands, 1e-2 against fp32
+    want = O.deconv2d_f32(f16_round(S["act_x"]), f16_round(S[tag + "_w"]), S[tag + "_b"], s, p)
+    np.testing.assert_allclose(y, want, rtol=0, atol=1e-5)
+    assert _rel(y, S[tag + "_out"]) < 1e-2
+
+
+def test_operation_deconvolution_refuses_overlapping_taps():
+    h = _host()
+    g = GraphBuilder(); g.deconv("d", "in", "out", S["deconv_k3s2p1_w"], S["deconv_k3s2p1_b"], 2, 1)
+    with pytest.raises(h.HostError):
+        h.run_op("Deconvolution", _params(g), [S["act_x"]], g.racy_bytes())
+
+
+def test_operation_reshape_transpose():
+    h = _host()
+    m = h.run_op("Reshape", "0=20 1=4 2=3", [S["rt_x"]])
+    assert m.shape == (2, 3, 4, 20)
+    np.testing.assert_array_equal(h.run_op("Transpose", "0=1,0,2", [m]), S["rt_out"])
+    np.testing.assert_array_equal(h.run_op("Transpose", "0=0,1,2", [m]), m)
+    with pytest.raises(h.HostError):
+        h.run_op("Transpose", "0=2,0,1", [m])
+
+
+# ---- the three networks -------------------------------------------------------------------------------
+def _run_net(builder, tag, fusion, tol, inner=(), **kw):
+    h = _host()
+    g, info = builder(**kw)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    x = S[tag + "_x"]
+    for _ in range(3):     # eager, capture, replay
+        out = p.forward(x)
+    assert sorted(out) == sorted(info["outputs"])
+    for n in info["outputs"]:
+        ref = S["%s_out_%s" % (tag, n)]
+        assert out[n].shape == ref.shape, (n, out[n].shape, ref.shape)
+        assert np.isfinite(out[n]).all()
+        r = _rel(out[n], ref)
+        assert r < tol, (n, r)
+    if not fusion:
+        for n in inner:
+            assert _rel(p.get(n), S["%s_map_%s" % (tag, n)]) < tol, n
+    stats = p.stats()
+    p.close()
+    return stats
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_det_db_resnet18(fusion):
+    launches, _ = _run_net(model_zoo.det_db_resnet18, "detdb", fusion, 1e-2, ("s2_b2_act", "fuse_out", "head_relu_out"))
+    if fusion:
+        # 32 convolutions (ReLU / add + ReLU folded), 2 transposed convolutions of 2 launches (BatchNorm + ReLU
+        # folded), Input, ingest, 4 poolings, 3 FPN adds not adjacent to their conv, 6 resizes, concat, sigmoid, emit
+        assert launches <= 32 + 4 + 2 + 4 + 3 + 6 + 1 + 1 + 1 + 4, launches
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_mobile_unicorn(fusion):
+    _run_net(model_zoo.mobile_unicorn, "unicorn", fusion, 2e-2, ("conv2_4_res", "conv5_ex_act"))
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_yolov5s_simp(fusion):
+    _run_net(model_zoo.yolov5s_simp, "yolosimp", fusion, 2e-2, ("csp2_cv4_act", "spp_cat_out"), size=128)
+
+
+def test_yolov5s_simp_batch_is_computed_for_every_image():
+    """The reference's Focus only fills image 0; here every image of a batch gives what it gives alone."""
+    h = _host()
+    g, info = model_zoo.yolov5s_simp(size=128)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=True)
+    x1 = S["yolosimp_x"]
+    x = np.concatenate([x1, x1[:, :, ::-1].copy(), x1], axis=0)
+    out = p.forward(x)
+    for n in info["outputs"]:
+        ref = S["yolosimp_out_" + n]
+        assert out[n].shape == (3,) + ref.shape[1:]
+        assert _rel(out[n][0:1], ref) < 2e-2
+        np.testing.assert_array_equal(out[n][2], out[n][0])
+    p.close()

@@ -1,0 +1,60 @@
+"""CPU checks for the operations and graphs added for the reference's shipped model descriptions: the
+oracle's PReLU / LeakyRelu / Deconvolution / Reshape / Transpose against outputs of the reference CPU
+library (golden vectors), and the model builders against the shipped `.phai` files themselves where the
+reference tree is present."""
+import os
+
+import numpy as np
+import pytest
+
+from excalibur_b200 import model_zoo
+from oracle import exb_oracle as O
+
+S = np.load(os.path.join(os.path.dirname(__file__), "golden", "shipped_model_vectors.npz"))
+REF_MODELS = "/root/reference/models"
+
+
+def test_oracle_prelu_leakyrelu_match_the_reference():
+    x = S["act_x"]
+    np.testing.assert_array_equal(O.prelu(x, S["prelu_slopes"]), S["prelu_out"])
+    np.testing.assert_array_equal(O.prelu(x, S["prelu_slopes"][:1]), S["prelu_shared_out"])
+    np.testing.assert_array_equal(O.leakyrelu(x, 0.1), S["leaky_out"])
+
+
+@pytest.mark.parametrize("tag", ["deconv_k2s2", "deconv_k2s2_c1", "deconv_k3s2p1", "deconv_k4s2p1"])
+def test_oracle_deconvolution_matches_the_reference(tag):
+    k, s, p = (int(v) for v in S[tag + "_cfg"])
+    y = O.deconv2d_f32(S["act_x"], S[tag + "_w"], S[tag + "_b"], s, p)
+    assert y.shape == S[tag + "_out"].shape
+    np.testing.assert_allclose(y, S[tag + "_out"], rtol=0, atol=2e-6)      # fp32 summation order differs
+
+
+def test_oracle_reshape_transpose_match_the_reference():
+    y = O.transpose_hw(O.reshape_nchw(S["rt_x"], w=20, h=4, c=3))
+    np.testing.assert_array_equal(y, S["rt_out"])
+    assert O.reshape_nchw(S["rt_x"], w=-1, h=2, c=6).shape == (2, 6, 2, 20)
+
+
+@pytest.mark.parametrize("name,ops", [("det_db_resnet18", 80), ("mobile_unicorn", 96), ("yolov5s_simp", 170)])
+def test_builders_have_the_shipped_architecture(name, ops):
+    g, info = getattr(model_zoo, name)()
+    mine = model_zoo.structure(g.phai_text())
+    assert len(mine) == ops
+    path = os.path.join(REF_MODELS, name + ".phai")
+    if not os.path.exists(path):
+        pytest.skip("reference tree not present: only the op count is checked")
+    with open(path) as f:
+        shipped = model_zoo.structure(f.read())
+    assert mine == shipped
+
+
+def test_weight_file_covers_every_record_of_the_builders():
+    from excalibur_b200.calibrate import parse_phai, racy_record_size
+    for fn in (model_zoo.det_db_resnet18, model_zoo.mobile_unicorn, model_zoo.yolov5s_simp):
+        g, _ = fn()
+        _, ops = parse_phai(g.phai_text())
+        blob = g.racy_bytes()
+        pos = 0
+        for op in ops:
+            pos += racy_record_size(op, blob, pos)
+        assert pos == len(blob), fn.__name__
