@@ -464,7 +464,7 @@ def prelu(ctx, x, slopes, channels=None, channel_last=True, y=None):
         outer, inner = x.numel() // cs, 1
     else:
         Cc, cs = x.shape[1], 0
-        outer, inner = x.shape[0], x.numel() // max(x.shape[0] * x.shape[1], 1)
+        outer, inner = x.shape[0], max(int(np.prod(x.shape[2:])), 1)
     check(lib().exb_prelu_fwd(ctx.handle, ptr(x), ptr(y), ptr(slopes), slopes.numel(), outer, Cc, cs, inner,
                               exb_dtype_of(x), 1 if channel_last else 0, cur_stream()))
     return y
