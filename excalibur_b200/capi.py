@@ -13,7 +13,7 @@ SO_PATH = os.path.join(_PKG, "lib", "libexcalibur_b200.so")
 
 EXB_OK, EXB_ERR_BAD_ARG, EXB_ERR_UNSUPPORTED, EXB_ERR_CUDA, EXB_ERR_TIMEOUT, EXB_ERR_NOMEM = 0, -1, -2, -3, -4, -5
 EXB_F16, EXB_I8, EXB_F32, EXB_I32 = 0, 1, 2, 3
-ACT_NONE, ACT_RELU, ACT_RELU6_QUIRK, ACT_SIGMOID, ACT_RELU6, ACT_SILU, ACT_HARDSWISH = 0, 1, 3, 4, 103, 104, 105
+ACT_NONE, ACT_RELU, ACT_RELU6_QUIRK, ACT_SIGMOID, ACT_RELU6, ACT_SILU, ACT_HARDSWISH, ACT_PRELU = 0, 1, 3, 4, 103, 104, 105, 106
 
 EXPORTED_SYMBOLS = [
     "exb_ctx_create", "exb_ctx_destroy", "exb_last_error_string", "exb_version", "exb_ctx_sm_count",
@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = [
     "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_pool2d_nchw_f32_static", "exb_eltwise_fwd", "exb_binaryop_fwd",
     "exb_binaryop_scalar_fwd", "exb_relu_fwd", "exb_activation_fwd", "exb_quantize_fwd",
     "exb_dequantize_fwd", "exb_concat_fwd", "exb_interp_nearest_fwd", "exb_channel_affine_fwd",
-    "exb_hardswish_fwd", "exb_focus_fwd", "exb_prelu_fwd", "exb_depth_to_space_fwd", "exb_transpose_hw_f32",
+    "exb_conv_weights_set_slopes", "exb_dw_weights_set_slopes", "exb_nchw_f32_focus_to_nhwc_f16", "exb_channel_affine_prelu_fwd", "exb_hardswish_fwd", "exb_focus_fwd", "exb_prelu_fwd", "exb_depth_to_space_fwd", "exb_transpose_hw_f32",
 ]
 
 
@@ -105,6 +105,10 @@ def lib():
         L.exb_channel_affine_fwd.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i64, i32, i32, i32, vp]
         L.exb_hardswish_fwd.argtypes = [vp, vp, vp, i64, i32, f32, f32, vp]
         L.exb_focus_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+        L.exb_conv_weights_set_slopes.argtypes = [vp, vp, vp, i32]
+        L.exb_dw_weights_set_slopes.argtypes = [vp, vp, vp, i32]
+        L.exb_channel_affine_prelu_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i32, i32, i64, i32, i32, vp]
+        L.exb_nchw_f32_focus_to_nhwc_f16.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]
         L.exb_prelu_fwd.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i64, i32, i32, vp]
         L.exb_depth_to_space_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
         L.exb_transpose_hw_f32.argtypes = [vp, vp, vp, i64, i32, i32, vp]
@@ -213,6 +217,11 @@ class ConvWeights:
     def handle(self):
         return self._h
 
+    def set_slopes(self, ctx, slopes):
+        """Per-output-channel (or one shared) PReLU slope for act == ACT_PRELU."""
+        sl = np.ascontiguousarray(np.atleast_1d(slopes), np.float32)
+        check(lib().exb_conv_weights_set_slopes(ctx.handle, self._h, _np_ptr(sl), int(sl.size)))
+
     def close(self):
         if self._h:
             lib().exb_conv_weights_destroy(self._h)
@@ -255,6 +264,10 @@ class DwWeights:
     @property
     def handle(self):
         return self._h
+
+    def set_slopes(self, ctx, slopes):
+        sl = np.ascontiguousarray(np.atleast_1d(slopes), np.float32)
+        check(lib().exb_dw_weights_set_slopes(ctx.handle, self._h, _np_ptr(sl), int(sl.size)))
 
     def close(self):
         if self._h:
@@ -467,6 +480,35 @@ def prelu(ctx, x, slopes, channels=None, channel_last=True, y=None):
         outer, inner = x.shape[0], max(int(np.prod(x.shape[2:])), 1)
     check(lib().exb_prelu_fwd(ctx.handle, ptr(x), ptr(y), ptr(slopes), slopes.numel(), outer, Cc, cs, inner,
                               exb_dtype_of(x), 1 if channel_last else 0, cur_stream()))
+    return y
+
+
+def channel_affine_prelu(ctx, x, mul, add, slopes, channels=None, channel_last=True, y=None):
+    """y = prelu(x * mul[c] + add[c], slopes); mul / add / slopes: fp32 device tensors."""
+    t = _torch()
+    if y is None:
+        y = t.empty_like(x)
+    if channel_last:
+        cs = x.shape[-1]
+        Cc = channels or cs
+        outer, inner = x.numel() // cs, 1
+    else:
+        Cc, cs = x.shape[1], 0
+        outer, inner = x.shape[0], max(int(np.prod(x.shape[2:])), 1)
+    check(lib().exb_channel_affine_prelu_fwd(ctx.handle, ptr(x), ptr(y), ptr(mul), ptr(add), ptr(slopes), slopes.numel(),
+                                             outer, Cc, cs, inner, exb_dtype_of(x), 1 if channel_last else 0, cur_stream()))
+    return y
+
+
+def focus_ingest(ctx, x, c_stride=16, mul=None, add=None, y=None):
+    """fp32 NCHW image -> optional per-channel affine -> Focus -> NHWC fp16 [N][H/2][W/2][c_stride]."""
+    t = _torch()
+    N, Cc, H, W = x.shape
+    if y is None:
+        y = t.empty((N, H // 2, W // 2, c_stride), dtype=t.float16, device=x.device)
+    check(lib().exb_nchw_f32_focus_to_nhwc_f16(ctx.handle, ptr(x), ptr(y), N, Cc, H, W, c_stride,
+                                               None if mul is None else ptr(mul), None if add is None else ptr(add),
+                                               cur_stream()))
     return y
 
 

@@ -28,7 +28,12 @@ int resolve(const exb_conv_desc* d, ConvGeom& g) {
         return fail(EXB_ERR_UNSUPPORTED, "convolution second output dtype %d", d->out2_dtype);
     if (d->res_dtype != -1 && d->res_dtype != EXB_F16)
         return fail(EXB_ERR_UNSUPPORTED, "convolution residual dtype %d (EXB_F16 expected)", d->res_dtype);
-    if (!act_supported(d->act)) return fail(EXB_ERR_UNSUPPORTED, "activation type %d is not implemented", d->act);
+    if (!act_supported(d->act) && d->act != EXB_ACT_PRELU)
+        return fail(EXB_ERR_UNSUPPORTED, "activation type %d is not implemented", d->act);
+    if (d->act == EXB_ACT_PRELU && d->fuse_pool)
+        return fail(EXB_ERR_UNSUPPORTED, "fuse_pool needs an activation with non-negative results, not EXB_ACT_PRELU");
+    if (d->act == EXB_ACT_PRELU && (d->in_planar || d->out_i8_planar || d->out_f16_planar || d->res_planar))
+        return fail(EXB_ERR_UNSUPPORTED, "EXB_ACT_PRELU is not available with planar16 tensors");
     g.N = d->N; g.H = d->H; g.W = d->W; g.Cin = d->Cin; g.Cout = d->Cout;
     g.cin_stride = d->cin_stride ? d->cin_stride : d->Cin;
     g.cout_stride = d->cout_stride ? d->cout_stride : d->Cout;
@@ -197,6 +202,7 @@ extern "C" int exb_conv_weights_destroy(exb_conv_weights* w) {
     if (w->d_w) cudaFree(w->d_w);
     if (w->d_scale) cudaFree(w->d_scale);
     if (w->d_bias) cudaFree(w->d_bias);
+    if (w->d_slope) cudaFree(w->d_slope);
     delete w;
     return EXB_OK;
 }
@@ -216,6 +222,11 @@ extern "C" int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* 
                     "exb_conv2d_fwd: weights were packed for a different input row layout");
     }
     EXB_REQUIRE(w->device == ctx->device, "exb_conv2d_fwd: weights live on device %d, context on %d", w->device, ctx->device);
+    if (g.act == EXB_ACT_PRELU) {
+        EXB_REQUIRE(w->d_slope != nullptr, "exb_conv2d_fwd: EXB_ACT_PRELU without slopes (exb_conv_weights_set_slopes)");
+        EXB_REQUIRE(g.cout_stride <= w->cout_pad + kSlopeSlack - 16, "exb_conv2d_fwd: output channel stride %d too wide for PReLU",
+                    g.cout_stride);
+    }
     if (g.N == 0) return EXB_OK;
     EXB_REQUIRE(x && y && aligned16(x) && aligned16(y), "exb_conv2d_fwd: null or misaligned x / y");
     EXB_REQUIRE(!g.has_res || (residual && aligned16(residual)), "exb_conv2d_fwd: null or misaligned residual");
@@ -229,4 +240,17 @@ extern "C" int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* 
         return fail(EXB_ERR_UNSUPPORTED, "planar16 input is not available for this convolution (see exb_conv2d_accepts_planar_input)");
     if (d->impl != 1 && conv_tc_eligible(g)) return conv_tc_launch(ctx, g, x, w, residual, y, y2, st);
     return conv_direct_launch(ctx, g, x, w, residual, y, y2, st);
+}
+
+extern "C" int exb_conv_weights_set_slopes(exb_ctx* ctx, exb_conv_weights* w, const float* slopes, int n) {
+    EXB_REQUIRE(ctx != nullptr && w != nullptr && slopes != nullptr, "exb_conv_weights_set_slopes: null argument");
+    EXB_REQUIRE(n == 1 || n == w->Cout, "exb_conv_weights_set_slopes: %d slopes for %d output channels", n, w->Cout);
+    const size_t len = (size_t)w->cout_pad + kSlopeSlack;
+    std::vector<float> h(len, 0.f);
+    for (int c = 0; c < w->Cout; ++c) h[c] = slopes[n == 1 ? 0 : c];
+    cudaError_t e = cudaSetDevice(w->device);
+    if (e == cudaSuccess && !w->d_slope) e = cudaMalloc(&w->d_slope, sizeof(float) * len);
+    if (e == cudaSuccess) e = cudaMemcpy(w->d_slope, h.data(), sizeof(float) * len, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail(EXB_ERR_CUDA, "exb_conv_weights_set_slopes: %s", cudaGetErrorString(e));
+    return EXB_OK;
 }

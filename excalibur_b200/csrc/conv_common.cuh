@@ -14,10 +14,14 @@ struct exb_conv_weights {
     void* d_w;        // [cout_pad][kh][kw_pack][cin_pad], K-major rows
     float* d_scale;   // [cout_pad] epilogue multiplier (fp16: 1; int8: 1/(wscale*act_scale))
     float* d_bias;    // [cout_pad] zeros when the layer has no bias
+    float* d_slope;   // [cout_pad + kSlopeSlack] PReLU slopes (zero beyond Cout), or null
     int device;
 };
 
 namespace exb {
+
+// The epilogue reads 16 slopes at any channel offset below the output's channel stride.
+constexpr int kSlopeSlack = 1024;
 
 // Problem geometry after validation (all strides physical).
 struct ConvGeom {
@@ -67,6 +71,7 @@ inline FoldPlan conv_fold_plan(const ConvGeom& g) {
 struct EpiParams {
     const float* scale;
     const float* bias;
+    const float* slope;   // EXB_ACT_PRELU only
     const __half* residual;
     void* y;
     void* y2;
@@ -151,6 +156,18 @@ __device__ __forceinline__ void epi_store_vec16(void* y, int dtype, int64_t off,
 
 // Activation over a register vector with the selector hoisted out of the element loop (one uniform
 // branch per chunk instead of a switch per element).
+__device__ __forceinline__ void prelu_vec16(float (&v)[16], const float* slope) {
+    const float4* s4 = reinterpret_cast<const float4*>(slope);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 s = __ldg(s4 + i);
+        v[4 * i + 0] = v[4 * i + 0] >= 0.f ? v[4 * i + 0] : v[4 * i + 0] * s.x;
+        v[4 * i + 1] = v[4 * i + 1] >= 0.f ? v[4 * i + 1] : v[4 * i + 1] * s.y;
+        v[4 * i + 2] = v[4 * i + 2] >= 0.f ? v[4 * i + 2] : v[4 * i + 2] * s.z;
+        v[4 * i + 3] = v[4 * i + 3] >= 0.f ? v[4 * i + 3] : v[4 * i + 3] * s.w;
+    }
+}
+
 __device__ __forceinline__ void act_vec16(float (&v)[16], int act) {
     if (act == EXB_ACT_NONE) return;
     if (act == EXB_ACT_RELU) {

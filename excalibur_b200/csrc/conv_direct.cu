@@ -56,7 +56,8 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const void* __restrict
         float v = epi_value<kInt8>(raw, p.e.scale[co], p.e.bias[co]);
         const int64_t off = pix * p.e.cout_stride + co;
         if (p.has_res) v += __half2float(p.e.residual[off]);
-        v = apply_act(v, p.e.act);
+        if (p.e.act == EXB_ACT_PRELU) v = v >= 0.f ? v : v * p.e.slope[co];
+        else v = apply_act(v, p.e.act);
         epi_store_scalar(p.e.y, p.e.out_dtype, off, v, p.e.out_scale, raw);
         if (p.e.out2_dtype >= 0) epi_store_scalar(p.e.y2, p.e.out2_dtype, off, v, p.e.out2_scale, raw);
     }
@@ -88,7 +89,7 @@ int conv_direct_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb
     p.kw_pack = w->kw_pack; p.s_shift = w->s_shift;
     p.w_pitch = g.w_pitch; p.w_pad = g.w_pad;
     p.has_res = g.has_res;
-    p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.residual = static_cast<const __half*>(residual);
+    p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.slope = w->d_slope; p.e.residual = static_cast<const __half*>(residual);
     p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;
     p.e.out_scale = g.out_scale; p.e.out2_scale = g.out2_scale; p.e.cout_stride = g.cout_stride;
     const int64_t total = (int64_t)g.N * g.OH * g.OW * g.Cout;

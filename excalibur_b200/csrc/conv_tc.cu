@@ -136,7 +136,10 @@ __device__ __forceinline__ TileCoord decode_tile(const ConvTcParams& p, int t) {
 // register allocation).
 // kHalo: the planar16 halo-patch main loop, likewise its own instantiation.
 // kPlanar: planar16 fp16 output / residual addressing in the epilogue, likewise.
-template <bool kInt8, int kDbg, int kEpiWarps, bool kPool = false, bool kHalo = false, bool kPlanar = false>
+// kPrelu: the epilogue's activation is the per-channel PReLU (its own instantiation, so the slope loads cost the
+// other kernels no registers).
+template <bool kInt8, int kDbg, int kEpiWarps, bool kPool = false, bool kHalo = false, bool kPlanar = false,
+          bool kPrelu = false>
 __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps == 8 ? 2 : 1)
     conv_tc_kernel(const __grid_constant__ ConvTcParams p) {
     constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
@@ -777,7 +780,8 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                             v[2 * i + 1] += f.y;
                         }
                     }
-                    act_vec16(v, p.e.act);
+                    if constexpr (kPrelu) prelu_vec16(v, p.e.slope + cl);
+                    else act_vec16(v, p.e.act);
                     if (kDbg & 32) {
                         float acc_ = 0.f;
 #pragma unroll
@@ -799,7 +803,8 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         if (cl + i < p.e.cout_stride) {
                             float u = v[i];
                             if (p.has_res) u += __half2float(p.e.residual[off + i]);
-                            u = apply_act(u, p.e.act);
+                            if constexpr (kPrelu) u = u >= 0.f ? u : u * __ldg(p.e.slope + cl + i);
+                            else u = apply_act(u, p.e.act);
                             epi_store_scalar(p.e.y, p.e.out_dtype, off + i, u, p.e.out_scale, raw[i]);
                             if (p.e.out2_dtype >= 0)
                                 epi_store_scalar(p.e.y2, p.e.out2_dtype, off + i, u, p.e.out2_scale, raw[i]);
@@ -1060,7 +1065,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.idesc = ptx::make_idesc(int8, kTileM, (uint32_t)p.BN);
     p.cout_pad = w->cout_pad;
     p.has_res = g.has_res;
-    p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.residual = static_cast<const __half*>(residual);
+    p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.slope = w->d_slope; p.e.residual = static_cast<const __half*>(residual);
     p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;
     p.e.out_scale = g.out_scale; p.e.out2_scale = g.out2_scale; p.e.cout_stride = g.cout_stride;
     p.e.i8_planar = g.out_i8_planar;
@@ -1152,6 +1157,9 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     const size_t smem = (size_t)p.stages * p.kgroup * p.a_bytes + p.b_region + 1024 + epi_bytes;
     auto kern = int8 ? (two ? conv_tc_kernel<true, 0, 8> : conv_tc_kernel<true, 0, 16>)
                      : (two ? conv_tc_kernel<false, 0, 8> : conv_tc_kernel<false, 0, 16>);
+    if (p.e.act == EXB_ACT_PRELU)
+        kern = int8 ? (two ? conv_tc_kernel<true, 0, 8, false, false, false, true> : conv_tc_kernel<true, 0, 16, false, false, false, true>)
+                    : (two ? conv_tc_kernel<false, 0, 8, false, false, false, true> : conv_tc_kernel<false, 0, 16, false, false, false, true>);
     if (p.pool) kern = conv_tc_kernel<false, 0, 8, true>;
     if (p.halo) kern = two ? conv_tc_kernel<true, 0, 8, false, true> : conv_tc_kernel<true, 0, 16, false, true>;
     if (planar16)

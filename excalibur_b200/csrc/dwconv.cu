@@ -12,6 +12,7 @@
 struct exb_dw_weights {
     float* d_w;     // [kh*kw][cs]
     float* d_bias;  // [cs] (zeros when the layer has no bias)
+    float* d_slope; // [cs] PReLU slopes, or null
     int C, cs, kh, kw;
     int device;
 };
@@ -26,6 +27,7 @@ struct DwParams {
     int kh, kw, sh, sw, pt, pl;
     int act;
     float in_scale, out_scale;
+    const float* slope;   // EXB_ACT_PRELU only: [cs]
 };
 
 __device__ __forceinline__ void load8(const __half* p, float (&v)[V], float) {
@@ -52,6 +54,18 @@ __device__ __forceinline__ void store8(int8_t* p, const float (&v)[V], float sca
 #pragma unroll
     for (int i = 0; i < 8; ++i) b[i] = (int8_t)quant_rne(v[i] * scale);
     *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(b);
+}
+__device__ __forceinline__ void loadw(const float* p, float (&v)[V]);
+// Activation of the 8 channels starting at c0.
+__device__ __forceinline__ void dw_act(float (&v)[V], const DwParams& p, int c0) {
+    if (p.act == EXB_ACT_PRELU) {
+        float s[V];
+        loadw(p.slope + c0, s);
+#pragma unroll
+        for (int k = 0; k < V; ++k) v[k] = v[k] >= 0.f ? v[k] : v[k] * s[k];
+    } else {
+        apply_act_vec(v, p.act);
+    }
 }
 __device__ __forceinline__ void loadw(const float* p, float (&v)[V]) {
     float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
@@ -112,7 +126,7 @@ __global__ void __launch_bounds__(128) dw_strip_kernel(const TIn* __restrict__ x
         for (int j = 0; j < TW; ++j) {
             const int ow = ow0 + j;
             if (ow < p.OW) {
-                apply_act_vec(acc[j], p.act);
+                dw_act(acc[j], p, cv * V);
                 store8(y + (((int64_t)n * p.OH + oh) * p.OW + ow) * p.cs + cv * V, acc[j], p.out_scale);
             }
         }
@@ -212,7 +226,7 @@ __global__ void __launch_bounds__(128) dw3x3_roll_f16_kernel(const __half* __res
             for (int j = 0; j < TW; ++j) {
                 const int ow = ow0 + j;
                 if (ow < p.OW) {
-                    apply_act_vec(acc[j], p.act);
+                    dw_act(acc[j], p, cv * V);
                     store8(y + (((int64_t)n * p.OH + oh) * p.OW + ow) * p.cs + cv * V, acc[j], 1.f);
                 }
             }
@@ -259,7 +273,7 @@ __global__ void __launch_bounds__(128) dw_generic_kernel(const TIn* __restrict__
                 for (int k = 0; k < V; ++k) acc[k] = fmaf(in[k], wv[k], acc[k]);
             }
         }
-        apply_act_vec(acc, p.act);
+        dw_act(acc, p, cv * V);
         store8(y + (((int64_t)n * p.OH + oh) * p.OW + ow) * p.cs + cv * V, acc, p.out_scale);
     }
 }
@@ -330,7 +344,8 @@ int check_desc(const exb_dwconv_desc* d, int& cs, int& OH, int& OW) {
     OH = (d->H + d->pad_t + d->pad_b - d->kh) / d->stride_h + 1;
     OW = (d->W + d->pad_l + d->pad_r - d->kw) / d->stride_w + 1;
     EXB_REQUIRE(OH > 0 && OW > 0, "depthwise window larger than the padded input");
-    if (!act_supported(d->act)) return fail(EXB_ERR_UNSUPPORTED, "activation type %d is not implemented", d->act);
+    if (!act_supported(d->act) && d->act != EXB_ACT_PRELU)
+        return fail(EXB_ERR_UNSUPPORTED, "activation type %d is not implemented", d->act);
     return EXB_OK;
 }
 
@@ -354,7 +369,7 @@ extern "C" int exb_dw_weights_pack(exb_ctx* ctx, const exb_dwconv_desc* d, const
     }
     exb_dw_weights* pw = new exb_dw_weights();
     pw->C = d->C; pw->cs = cs; pw->kh = d->kh; pw->kw = d->kw; pw->device = ctx->device;
-    pw->d_w = nullptr; pw->d_bias = nullptr;
+    pw->d_w = nullptr; pw->d_bias = nullptr; pw->d_slope = nullptr;
     cudaError_t e = cudaSetDevice(ctx->device);
     if (e == cudaSuccess) e = cudaMalloc(&pw->d_w, sizeof(float) * taps * cs);
     if (e == cudaSuccess) e = cudaMalloc(&pw->d_bias, sizeof(float) * cs);
@@ -374,6 +389,7 @@ extern "C" int exb_dw_weights_destroy(exb_dw_weights* w) {
     if (!w) return EXB_OK;
     if (w->d_w) cudaFree(w->d_w);
     if (w->d_bias) cudaFree(w->d_bias);
+    if (w->d_slope) cudaFree(w->d_slope);
     delete w;
     return EXB_OK;
 }
@@ -391,10 +407,25 @@ extern "C" int exb_dwconv2d_fwd(exb_ctx* ctx, const exb_dwconv_desc* d, const vo
     p.N = d->N; p.H = d->H; p.W = d->W; p.cs = cs; p.OH = OH; p.OW = OW;
     p.kh = d->kh; p.kw = d->kw; p.sh = d->stride_h; p.sw = d->stride_w; p.pt = d->pad_t; p.pl = d->pad_l;
     p.act = d->act; p.in_scale = d->in_scale; p.out_scale = d->out_scale;
+    p.slope = w->d_slope;
+    EXB_REQUIRE(p.act != EXB_ACT_PRELU || p.slope != nullptr, "exb_dwconv2d_fwd: EXB_ACT_PRELU without slopes (exb_dw_weights_set_slopes)");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (d->in_dtype == EXB_F16 && d->out_dtype == EXB_F16) return launch<__half, __half>(ctx, p, x, w, y, st);
     if (d->in_dtype == EXB_I8 && d->out_dtype == EXB_I8) return launch<int8_t, int8_t>(ctx, p, x, w, y, st);
     if (d->in_dtype == EXB_I8 && d->out_dtype == EXB_F16) return launch<int8_t, __half>(ctx, p, x, w, y, st);
     if (d->in_dtype == EXB_F16 && d->out_dtype == EXB_I8) return launch<__half, int8_t>(ctx, p, x, w, y, st);
     return fail(EXB_ERR_UNSUPPORTED, "depthwise conv dtypes in=%d out=%d", d->in_dtype, d->out_dtype);
+}
+
+extern "C" int exb_dw_weights_set_slopes(exb_ctx* ctx, exb_dw_weights* w, const float* slopes, int n) {
+    EXB_REQUIRE(ctx != nullptr && w != nullptr && slopes != nullptr, "exb_dw_weights_set_slopes: null argument");
+    EXB_REQUIRE(n == 1 || n == w->C, "exb_dw_weights_set_slopes: %d slopes for %d channels", n, w->C);
+    float* h = new float[w->cs]();
+    for (int c = 0; c < w->C; ++c) h[c] = slopes[n == 1 ? 0 : c];
+    cudaError_t e = cudaSetDevice(w->device);
+    if (e == cudaSuccess && !w->d_slope) e = cudaMalloc(&w->d_slope, sizeof(float) * w->cs);
+    if (e == cudaSuccess) e = cudaMemcpy(w->d_slope, h, sizeof(float) * w->cs, cudaMemcpyHostToDevice);
+    delete[] h;
+    if (e != cudaSuccess) return fail(EXB_ERR_CUDA, "exb_dw_weights_set_slopes: %s", cudaGetErrorString(e));
+    return EXB_OK;
 }

@@ -110,16 +110,63 @@ __device__ __forceinline__ void st1(float* p, float v) { *p = v; }
 template <typename T>
 __global__ void __launch_bounds__(kThreads) channel_affine_kernel(const T* x, T* y, const float* mul, const float* add,
                                                                   int64_t count, int C, int cs, int64_t inner,
-                                                                  int channel_last, int act) {
+                                                                  int channel_last, int act, const float* slope,
+                                                                  int n_slope) {
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += step) {
         const int c = channel_last ? (int)(i % cs) : (int)((i / inner) % C);
         float v = 0.f;
-        if (c < C) v = apply_act(fmaf(ld1(x + i), mul[c], add[c]), act);
+        if (c < C) {
+            v = fmaf(ld1(x + i), mul[c], add[c]);
+            if (slope) v = v >= 0.f ? v : v * slope[n_slope == 1 ? 0 : c];
+            else v = apply_act(v, act);
+        }
         st1(y + i, v);
     }
 }
 
+
+// Channel-last fp16, 8 channels (16 bytes) per thread step: y = f(x * mul[c] + add[c]) with f the activation
+// `act`, or the PReLU with `slope` when that is not null.  cs is a multiple of 8; padding channels are written 0.
+__global__ void __launch_bounds__(kThreads) channel_affine_nhwc_f16x8_kernel(const uint4* x, uint4* y, const float* mul,
+                                                                             const float* add, const float* slope,
+                                                                             int n_slope, int act, int64_t nvec, int C,
+                                                                             int cs8) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step) {
+        const int c0 = (int)(i % cs8) * 8;
+        uint4 raw = x[i];
+        __half2* h = reinterpret_cast<__half2*>(&raw);
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __half22float2(h[k]);
+            v[2 * k] = f.x;
+            v[2 * k + 1] = f.y;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int c = c0 + k;
+            v[k] = c < C ? fmaf(v[k], mul[c], add[c]) : 0.f;
+        }
+        if (slope) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int c = c0 + k;
+                const float sl = c < C ? slope[n_slope == 1 ? 0 : c] : 0.f;
+                v[k] = v[k] >= 0.f ? v[k] : v[k] * sl;
+            }
+        } else {
+            apply_act_vec(v, act);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (c0 + k >= C) v[k] = 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) h[k] = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+        y[i] = raw;
+    }
+}
 
 // y = x >= 0 ? x : x * slope[c] (PReLU; one shared slope when n_slope == 1, which is also LeakyReLU).
 // Indexing as channel_affine_kernel; padding channels of a channel-last tensor are written 0.
@@ -179,6 +226,37 @@ __global__ void __launch_bounds__(kThreads) depth_to_space_kernel(const U* __res
         if (c < C) {
             const int h = oy / rh, a = oy - h * rh, w = ox / rw, b = ox - w * rw;
             v = x[(((int64_t)n * H + h) * W + w) * xs + (a * rw + b) * C + c];
+        }
+        y[i] = v;
+    }
+}
+
+// The same with one 16-byte vector of 8 fp16 channels per thread step; C, xs and ys are multiples of 8 when
+// kGather is false (one aligned load), otherwise the 8 values are gathered one by one (C not a multiple of 8).
+template <bool kGather>
+__global__ void __launch_bounds__(kThreads) depth_to_space_f16x8_kernel(const __half* __restrict__ x, uint4* __restrict__ y,
+                                                                        int N, int H, int W, int rh, int rw, int C, int xs,
+                                                                        int ys8) {
+    const int OH = H * rh, OW = W * rw;
+    const int64_t work = (int64_t)N * OH * OW * ys8;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < work; i += step) {
+        const int c0 = (int)(i % ys8) * 8;
+        int64_t p = i / ys8;
+        const int ox = (int)(p % OW);
+        p /= OW;
+        const int oy = (int)(p % OH);
+        const int n = (int)(p / OH);
+        const int h = oy / rh, a = oy - h * rh, w = ox / rw, b = ox - w * rw;
+        const __half* src = x + (((int64_t)n * H + h) * W + w) * xs + (a * rw + b) * C;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (!kGather) {
+            if (c0 < C) v = *reinterpret_cast<const uint4*>(src + c0);
+        } else {
+            __half* e = reinterpret_cast<__half*>(&v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (c0 + k < C) e[k] = src[c0 + k];
         }
         y[i] = v;
     }
@@ -326,29 +404,51 @@ extern "C" int exb_focus_fwd(exb_ctx* ctx, const void* x, void* y, int N, int C,
     return after_launch("exb_focus_fwd");
 }
 
-extern "C" int exb_channel_affine_fwd(exb_ctx* ctx, const void* x, void* y, const float* mul, const float* add,
-                                      int64_t outer, int C, int c_stride, int64_t inner, int dtype, int channel_last,
-                                      int act, void* stream) {
+static int channel_affine_impl(exb_ctx* ctx, const void* x, void* y, const float* mul, const float* add, const float* slope,
+                               int n_slope, int64_t outer, int C, int c_stride, int64_t inner, int dtype, int channel_last,
+                               int act, void* stream, const char* what) {
     EXB_REQUIRE(ctx != nullptr, "null context");
-    EXB_REQUIRE(outer >= 0 && C > 0 && inner > 0, "exb_channel_affine_fwd: bad shape");
+    EXB_REQUIRE(outer >= 0 && C > 0 && inner > 0, "%s: bad shape", what);
     if (dtype != EXB_F16 && dtype != EXB_F32)
-        return fail(EXB_ERR_UNSUPPORTED, "exb_channel_affine_fwd supports EXB_F16 and EXB_F32, got dtype %d", dtype);
+        return fail(EXB_ERR_UNSUPPORTED, "%s supports EXB_F16 and EXB_F32, got dtype %d", what, dtype);
     if (!act_supported(act)) return fail(EXB_ERR_UNSUPPORTED, "activation type %d is not implemented", act);
     const int cs = channel_last ? (c_stride ? c_stride : C) : C;
-    EXB_REQUIRE(cs >= C, "exb_channel_affine_fwd: channel stride smaller than channel count");
+    EXB_REQUIRE(cs >= C, "%s: channel stride smaller than channel count", what);
     // channel-last: outer = pixels, inner ignored; planar: outer = images, inner = H*W
     const int64_t count = channel_last ? outer * cs : outer * C * inner;
     if (count == 0) return EXB_OK;
-    EXB_REQUIRE(x && y && mul && add, "exb_channel_affine_fwd: null buffer");
+    EXB_REQUIRE(x && y && mul && add, "%s: null buffer", what);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == EXB_F16 && channel_last && cs % 8 == 0 && aligned16(x) && aligned16(y)) {
+        const int64_t nvec = count / 8;
+        channel_affine_nhwc_f16x8_kernel<<<stream_grid(ctx, nvec, kThreads), kThreads, 0, st>>>(
+            static_cast<const uint4*>(x), static_cast<uint4*>(y), mul, add, slope, n_slope, act, nvec, C, cs / 8);
+        return after_launch(what);
+    }
     int grid = stream_grid(ctx, count, kThreads);
     if (dtype == EXB_F16)
         channel_affine_kernel<__half><<<grid, kThreads, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), mul,
-                                                                 add, count, C, cs, inner, channel_last, act);
+                                                                 add, count, C, cs, inner, channel_last, act, slope, n_slope);
     else
         channel_affine_kernel<float><<<grid, kThreads, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), mul,
-                                                                add, count, C, cs, inner, channel_last, act);
-    return after_launch("exb_channel_affine_fwd");
+                                                                add, count, C, cs, inner, channel_last, act, slope, n_slope);
+    return after_launch(what);
+}
+
+extern "C" int exb_channel_affine_fwd(exb_ctx* ctx, const void* x, void* y, const float* mul, const float* add,
+                                      int64_t outer, int C, int c_stride, int64_t inner, int dtype, int channel_last,
+                                      int act, void* stream) {
+    return channel_affine_impl(ctx, x, y, mul, add, nullptr, 0, outer, C, c_stride, inner, dtype, channel_last, act, stream,
+                               "exb_channel_affine_fwd");
+}
+
+extern "C" int exb_channel_affine_prelu_fwd(exb_ctx* ctx, const void* x, void* y, const float* mul, const float* add,
+                                            const float* slope, int n_slope, int64_t outer, int C, int c_stride,
+                                            int64_t inner, int dtype, int channel_last, void* stream) {
+    EXB_REQUIRE(slope != nullptr && (n_slope == 1 || n_slope == C), "exb_channel_affine_prelu_fwd: %d slopes for %d channels",
+                n_slope, C);
+    return channel_affine_impl(ctx, x, y, mul, add, slope, n_slope, outer, C, c_stride, inner, dtype, channel_last,
+                               EXB_ACT_NONE, stream, "exb_channel_affine_prelu_fwd");
 }
 
 extern "C" int exb_prelu_fwd(exb_ctx* ctx, const void* x, void* y, const float* slope, int n_slope, int64_t outer, int C,
@@ -392,6 +492,17 @@ extern "C" int exb_depth_to_space_fwd(exb_ctx* ctx, const void* x, void* y, int 
     if (work == 0) return EXB_OK;
     EXB_REQUIRE(x && y, "exb_depth_to_space_fwd: null buffer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (es == 2 && ys % 8 == 0 && aligned16(y)) {
+        const bool whole = C % 8 == 0 && xs % 8 == 0 && aligned16(x);
+        const int g8 = stream_grid(ctx, work / 8, kThreads);
+        if (whole)
+            depth_to_space_f16x8_kernel<false><<<g8, kThreads, 0, st>>>(static_cast<const __half*>(x), static_cast<uint4*>(y), N, H,
+                                                                        W, rh, rw, C, xs, ys / 8);
+        else
+            depth_to_space_f16x8_kernel<true><<<g8, kThreads, 0, st>>>(static_cast<const __half*>(x), static_cast<uint4*>(y), N, H,
+                                                                       W, rh, rw, C, xs, ys / 8);
+        return after_launch("exb_depth_to_space_fwd");
+    }
     int grid = stream_grid(ctx, work, kThreads);
     if (es == 2)
         depth_to_space_kernel<uint16_t><<<grid, kThreads, 0, st>>>(static_cast<const uint16_t*>(x), static_cast<uint16_t*>(y),

@@ -282,6 +282,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         int act = EXB_ACT_NONE;
         int pool = -1;          // 3x3/2 max pooling op applied in the conv epilogue
         int bn = -1;            // BatchNorm op folded into the conv's weights and bias
+        int slope_op = -1;      // PReLU / LeakyRelu op applied in the epilogue (act == EXB_ACT_PRELU)
         int out = -1;           // root featmap the group finally produces
         int exec_at = -1;       // index of the last absorbed op
     };
@@ -303,7 +304,21 @@ void fused_plan::build(int N, int C, int H, int W) {
             auto* hs = dynamic_cast<operation_hardswish<float>*>(ops_[j].get());
             if (hs && hs->is_standard()) return EXB_ACT_HARDSWISH;
         }
+        if (t == "prelu" || t == "leakyrelu") return EXB_ACT_PRELU;     // slopes: slopes_of_op(j, channels)
         return -1;
+    };
+    // host slopes of a PReLU / LeakyRelu op, one per channel
+    auto slopes_of_op = [&](int j, int channels) -> std::vector<float> {
+        std::vector<float> sl((size_t)channels);
+        if (lower_type(params_[j]) == "leakyrelu") {
+            const float a = dynamic_cast<operation_leakyrelu<float>*>(ops_[j].get())->alpha_;
+            for (auto& v : sl) v = a;
+        } else {
+            auto* pr = dynamic_cast<operation_prelu<float>*>(ops_[j].get());
+            if (pr->num_slope_ != 1) CHECK_EQ(pr->num_slope_, channels) << params_[j].name_ << ": slopes do not match the channels";
+            for (int c = 0; c < channels; ++c) sl[c] = pr->slopes_cpu()[pr->num_slope_ == 1 ? 0 : c];
+        }
+        return sl;
     };
     auto is_plain_add = [&](int j) -> bool {
         const std::string t = lower_type(params_[j]);
@@ -369,6 +384,7 @@ void fused_plan::build(int N, int C, int H, int W) {
             g.exec_at = std::max(sj, mk);
         } else if (g.act == EXB_ACT_NONE && (j = sole_consumer(g.out)) >= 0 && !absorbed[j] && act_of_op(j) > 0) {
             g.act = act_of_op(j);
+            if (g.act == EXB_ACT_PRELU) g.slope_op = j;
             absorbed[j] = 1;
             g.out = root(out_ids[j][0]);
             g.exec_at = j;
@@ -382,6 +398,7 @@ void fused_plan::build(int N, int C, int H, int W) {
             int k;
             if ((k = sole_consumer(g.out)) >= 0 && !absorbed[k] && act_of_op(k) > 0) {
                 g.act = act_of_op(k);
+                if (g.act == EXB_ACT_PRELU) g.slope_op = k;
                 absorbed[k] = 1;
                 g.out = root(out_ids[k][0]);
                 g.exec_at = k;
@@ -483,9 +500,33 @@ void fused_plan::build(int N, int C, int H, int W) {
                 }
             }
         }
+        // Network input -> (Input normalisation ->) YoloV5Focus: one kernel from the fp32 staging buffer to the
+        // Focus layer's channel-last fp16 output.
+        int focus_op = -1;
+        if (C <= 4 && H % 2 == 0 && W % 2 == 0 && !in.need_i8 && consumers[in_id].size() == 1 && !output_roots.count(in_id) &&
+            lower_type(params_[consumers[in_id][0]]) == "yolov5focus" && !absorbed[consumers[in_id][0]])
+            focus_op = consumers[in_id][0];
+        if (focus_op >= 0) {
+            const float* mul = nullptr;
+            const float* add = nullptr;
+            if (input_norm_op >= 0)
+                dynamic_cast<operation_input<float>*>(ops_[input_norm_op].get())->coefficients(C, &mul, &add);
+            fmap_info& fy = fmaps_[root(out_ids[focus_op][0])];
+            fy.need_f16 = true;
+            set_shape(fy, N, 4 * C, H / 2, W / 2);
+            void* yo = form_f16(fy);
+            const int ocs = fy.cs;
+            add_step("ingest+focus " + in.name, [=](cudaStream_t st) {
+                exb_check(exb_nchw_f32_focus_to_nhwc_f16(ctx, this->ingest_src_, yo, N, C, H, W, ocs, mul, add, st),
+                          "exb_nchw_f32_focus_to_nhwc_f16");
+            });
+            absorbed[focus_op] = 1;
+            in.produced = true;      // consumed inside the fused kernel; it has no device form of its own
+            finish_forms(fy, false);
+        }
         // Input normalisation in front of the ingest kernel: fp32 NCHW staging -> normalised copy.
         const float* ingest_fixed = nullptr;
-        if (input_norm_op >= 0) {
+        if (focus_op < 0 && input_norm_op >= 0) {
             auto* inp = dynamic_cast<operation_input<float>*>(ops_[input_norm_op].get());
             const float* mul = nullptr;
             const float* add = nullptr;
@@ -498,10 +539,12 @@ void fused_plan::build(int N, int C, int H, int W) {
             });
         }
         const bool direct_i8 = in.need_i8 && !in.need_f16;
-        void* dst = direct_i8 ? form_i8(in) : form_f16(in);
+        void* dst = focus_op >= 0 ? nullptr : (direct_i8 ? form_i8(in) : form_f16(in));
         const int cs = in.cs, w_pad = in.w_pad, w_pitch = in.w_pitch;
         const float s = in.i8_scale;
-        if (padded) {
+        if (focus_op >= 0) {
+            // nothing else to ingest
+        } else if (padded) {
             add_step("ingest " + in.name, [=](cudaStream_t st) {
                 exb_check(exb_nchw_f32_to_nhwc_padded(ctx, ingest_fixed ? ingest_fixed : this->ingest_src_, dst, EXB_F16, N, C, H, W,
                                                       cs, w_pad, w_pitch, 1.f, 1, st),
@@ -515,7 +558,7 @@ void fused_plan::build(int N, int C, int H, int W) {
                           "exb_nchw_f32_to_nhwc");
             });
         }
-        finish_forms(in, direct_i8);
+        if (focus_op < 0) finish_forms(in, direct_i8);
     }
 
     auto run_conv_group = [&](const group& g) {
@@ -543,6 +586,10 @@ void fused_plan::build(int N, int C, int H, int W) {
                 g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;
             exb_dw_weights* w = bn ? dw->dw_packed(ctx, d, bn->mul()->cpu_data(), bn->add()->cpu_data(), bn)
                                    : dw->dw_packed(ctx, d);
+            if (g.act == EXB_ACT_PRELU) {
+                const std::vector<float> sl = slopes_of_op(g.slope_op, x.C);
+                exb_check(exb_dw_weights_set_slopes(ctx, w, sl.data(), (int)sl.size()), "exb_dw_weights_set_slopes");
+            }
             add_step(params_[i].name_, [=](cudaStream_t st) {
                 exb_check(exb_dwconv2d_fwd(ctx, &d, xin, w, yo, st), "exb_dwconv2d_fwd");
             });
@@ -568,6 +615,12 @@ void fused_plan::build(int N, int C, int H, int W) {
             const operation_batchnorm<float>* bn =
                 g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;
             exb_conv_weights* w = bn ? dc->packed(ctx, d, bn->mul()->cpu_data(), bn->add()->cpu_data(), bn) : dc->packed(ctx, d);
+            if (g.act == EXB_ACT_PRELU) {       // inner output channel t*Cout + co carries the slope of co
+                const std::vector<float> sl = slopes_of_op(g.slope_op, Cout);
+                std::vector<float> rep((size_t)d.Cout);
+                for (int c = 0; c < d.Cout; ++c) rep[c] = sl[c % Cout];
+                exb_check(exb_conv_weights_set_slopes(ctx, w, rep.data(), (int)rep.size()), "exb_conv_weights_set_slopes");
+            }
             const int n = x.N, h = x.H, wd = x.W, xs = d.cout_stride, ys = y.cs;
             add_step(params_[i].name_, [=](cudaStream_t st) {
                 (void)mid;       // keeps the intermediate tensor alive as long as the step
@@ -625,6 +678,10 @@ void fused_plan::build(int N, int C, int H, int W) {
             g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;
         exb_conv_weights* w = bn ? conv->packed(ctx, d, bn->mul()->cpu_data(), bn->add()->cpu_data(), bn)
                                  : conv->packed(ctx, d);
+        if (g.act == EXB_ACT_PRELU) {
+            const std::vector<float> sl = slopes_of_op(g.slope_op, conv->output_channel_);
+            exb_check(exb_conv_weights_set_slopes(ctx, w, sl.data(), (int)sl.size()), "exb_conv_weights_set_slopes");
+        }
         add_step(params_[i].name_, [=](cudaStream_t st) {
             exb_check(exb_conv2d_fwd(ctx, &d, xin, w, res, y1, y2, st), "exb_conv2d_fwd");
         });
@@ -794,20 +851,46 @@ void fused_plan::build(int N, int C, int H, int W) {
         } else if (t == "batchnorm") {
             auto* bn = dynamic_cast<operation_batchnorm<float>*>(ops_[i].get());
             CHECK_EQ(x.C, bn->channels_);
-            y.need_f16 = true;
-            set_shape(y, x.N, x.C, x.H, x.W);
-            y.cs = x.cs;
+            // a PReLU / LeakyRelu / plain activation that alone reads the result runs in the same pass
+            fmap_info* yy = &y;
+            int act = EXB_ACT_NONE;
+            const float* slope = nullptr;
+            int n_slope = 0;
+            const int j = sole_consumer(root(out_ids[i][0]));
+            if (j > (int)i && !absorbed[j] && in_ids[j].size() == 1 && act_of_op(j) > 0) {
+                const std::string tj = lower_type(params_[j]);
+                if (tj == "prelu") {
+                    auto* pr = dynamic_cast<operation_prelu<float>*>(ops_[j].get());
+                    if (pr->num_slope_ != 1) CHECK_EQ(pr->num_slope_, x.C) << params_[j].name_ << ": slopes do not match the channels";
+                    slope = pr->slopes_gpu();
+                    n_slope = pr->num_slope_;
+                } else if (tj == "leakyrelu") {
+                    slope = dynamic_cast<operation_leakyrelu<float>*>(ops_[j].get())->slope_gpu();
+                    n_slope = 1;
+                } else {
+                    act = act_of_op(j);
+                }
+                absorbed[j] = 1;
+                yy = &fmaps_[root(out_ids[j][0])];
+            }
+            yy->need_f16 = true;
+            set_shape(*yy, x.N, x.C, x.H, x.W);
+            yy->cs = x.cs;
             const void* xin = form_f16(x);
-            void* yo = form_f16(y);
+            void* yo = form_f16(*yy);
             const float* mul = bn->mul()->gpu_data();
             const float* add = bn->add()->gpu_data();
             const int64_t rows = (int64_t)x.N * x.H * x.W;
             const int c = x.C, cs = x.cs;
             add_step(params_[i].name_, [=](cudaStream_t st) {
-                exb_check(exb_channel_affine_fwd(ctx, xin, yo, mul, add, rows, c, cs, 1, EXB_F16, 1, EXB_ACT_NONE, st),
-                          "exb_channel_affine_fwd");
+                if (slope)
+                    exb_check(exb_channel_affine_prelu_fwd(ctx, xin, yo, mul, add, slope, n_slope, rows, c, cs, 1, EXB_F16, 1, st),
+                              "exb_channel_affine_prelu_fwd");
+                else
+                    exb_check(exb_channel_affine_fwd(ctx, xin, yo, mul, add, rows, c, cs, 1, EXB_F16, 1, act, st),
+                              "exb_channel_affine_fwd");
             });
-            finish_forms(y, false);
+            finish_forms(*yy, false);
         } else {
             // element-wise ops on the fp16 form
             y.need_f16 = true;

@@ -61,6 +61,19 @@ __global__ void __launch_bounds__(256) nhwc_to_nchw_kernel(const In* __restrict_
     }
 }
 
+// Few channels (C <= 8, detection heads and masks): one thread per pixel reads its C values and writes
+// them to the C planes; consecutive threads write consecutive addresses of every plane.
+template <typename In>
+__global__ void __launch_bounds__(256) nhwc_to_nchw_fewc_kernel(const In* __restrict__ x, float* __restrict__ y, int N,
+                                                                int C, int HW, int c_stride, float scale) {
+    const int64_t total = (int64_t)N * HW;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / HW, hw = i - n * HW;
+        const In* px = x + i * c_stride;
+        for (int c = 0; c < C; ++c) y[(n * C + c) * HW + hw] = cvt_in<In>(px[c], scale);
+    }
+}
+
 // Few-channel images (C <= 8): one thread per output pixel slot.  Reads are coalesced along W in
 // each of the C planes, the write is one 8- or 16-byte vector per pixel; padding pixels and
 // channels are written as zero.
@@ -182,6 +195,16 @@ extern "C" int exb_nhwc_to_nchw_f32(exb_ctx* ctx, const void* x, int dtype, floa
     const int HW = H * W;
     dim3 grid((HW + kTile - 1) / kTile, (C + kTile - 1) / kTile, N), block(kTile, 8);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (C <= 8) {
+        const int g = stream_grid(ctx, (int64_t)N * HW, 256);
+        switch (dtype) {
+        case EXB_F16: nhwc_to_nchw_fewc_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(x), y, N, C, HW, c_stride, scale); break;
+        case EXB_I8: nhwc_to_nchw_fewc_kernel<int8_t><<<g, 256, 0, st>>>(static_cast<const int8_t*>(x), y, N, C, HW, c_stride, scale); break;
+        case EXB_F32: nhwc_to_nchw_fewc_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(x), y, N, C, HW, c_stride, scale); break;
+        default: return fail(EXB_ERR_UNSUPPORTED, "exb_nhwc_to_nchw_f32: dtype %d", dtype);
+        }
+        return after_launch("nhwc_to_nchw_fewc_kernel");
+    }
     switch (dtype) {
     case EXB_F16: nhwc_to_nchw_kernel<__half><<<grid, block, 0, st>>>(static_cast<const __half*>(x), y, C, HW, c_stride, scale); break;
     case EXB_I8: nhwc_to_nchw_kernel<int8_t><<<grid, block, 0, st>>>(static_cast<const int8_t*>(x), y, C, HW, c_stride, scale); break;
@@ -243,4 +266,62 @@ extern "C" int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x, void* y
     else return fail(EXB_ERR_UNSUPPORTED, "padded ingest supports EXB_F16 and EXB_I8 output");
 #undef EXB_LAUNCH
     return after_launch("nchw_to_nhwc_padded_kernel");
+}
+
+namespace exb {
+namespace {
+// Network input -> Focus in one pass: fp32 NCHW image, optional per-channel affine (input normalisation),
+// space-to-depth 2x2 and conversion to channel-last fp16.  One thread per output pixel: two float2 loads per
+// input plane (rows 2i and 2i+1, columns 2j and 2j+1), CS / 8 16-byte stores.  4*C <= CS.
+template <int CS>
+__global__ void __launch_bounds__(256) focus_ingest_kernel(const float* __restrict__ x, __half* __restrict__ y, int N, int C,
+                                                           int H, int W, const float* __restrict__ mul,
+                                                           const float* __restrict__ add) {
+    const int OH = H / 2, OW = W / 2;
+    const int64_t total = (int64_t)N * OH * OW;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int oj = (int)(i % OW);
+        const int64_t t = i / OW;
+        const int oi = (int)(t % OH);
+        const int n = (int)(t / OH);
+        alignas(16) __half out[CS];
+#pragma unroll
+        for (int k = 0; k < CS; ++k) out[k] = __float2half_rn(0.f);
+        for (int c = 0; c < C; ++c) {
+            const float* p0 = x + (((int64_t)n * C + c) * H + 2 * oi) * W + 2 * oj;
+            const float2 top = *reinterpret_cast<const float2*>(p0);
+            const float2 bot = *reinterpret_cast<const float2*>(p0 + W);
+            const float m = mul ? mul[c] : 1.f, a = add ? add[c] : 0.f;
+            // group g reads row 2i + g%2, column 2j + g/2
+            out[0 * C + c] = __float2half_rn(fmaf(top.x, m, a));
+            out[1 * C + c] = __float2half_rn(fmaf(bot.x, m, a));
+            out[2 * C + c] = __float2half_rn(fmaf(top.y, m, a));
+            out[3 * C + c] = __float2half_rn(fmaf(bot.y, m, a));
+        }
+        uint4* dst = reinterpret_cast<uint4*>(y + i * CS);
+#pragma unroll
+        for (int k = 0; k < CS / 8; ++k) dst[k] = reinterpret_cast<const uint4*>(out)[k];
+    }
+}
+}  // namespace
+}  // namespace exb
+
+extern "C" int exb_nchw_f32_focus_to_nhwc_f16(exb_ctx* ctx, const float* x, void* y, int N, int C, int H, int W,
+                                              int c_stride, const float* mul, const float* add, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(N >= 0 && C > 0 && H > 0 && W > 0, "exb_nchw_f32_focus_to_nhwc_f16: bad shape");
+    if (H % 2 || W % 2) return exb::fail(EXB_ERR_UNSUPPORTED, "exb_nchw_f32_focus_to_nhwc_f16 needs even H and W, got %d x %d", H, W);
+    if ((c_stride != 16 && c_stride != 32) || 4 * C > c_stride)
+        return exb::fail(EXB_ERR_UNSUPPORTED, "exb_nchw_f32_focus_to_nhwc_f16: channel stride %d for %d input channels", c_stride, C);
+    EXB_REQUIRE((mul == nullptr) == (add == nullptr), "exb_nchw_f32_focus_to_nhwc_f16: mul and add come together");
+    if (N == 0) return EXB_OK;
+    EXB_REQUIRE(x && y && exb::aligned16(y) && (reinterpret_cast<uintptr_t>(x) & 7u) == 0,
+                "exb_nchw_f32_focus_to_nhwc_f16: null or misaligned buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = exb::stream_grid(ctx, (int64_t)N * (H / 2) * (W / 2), 256);
+    if (c_stride == 16)
+        exb::focus_ingest_kernel<16><<<grid, 256, 0, st>>>(x, static_cast<__half*>(y), N, C, H, W, mul, add);
+    else
+        exb::focus_ingest_kernel<32><<<grid, 256, 0, st>>>(x, static_cast<__half*>(y), N, C, H, W, mul, add);
+    return exb::after_launch("exb_nchw_f32_focus_to_nhwc_f16");
 }

@@ -1,12 +1,15 @@
 """Whole-network throughput of the benchmark configurations other than the headline one.
 
-    python -m excalibur_b200.net_bench [--net resnet18_fp16,resnet18_int8,mobilenetv2_fp16,mobilenetv2_int8,yolov5s_fp16]
+    python -m excalibur_b200.net_bench [--net resnet18_fp16,resnet18_int8,mobilenetv2_fp16,mobilenetv2_int8,yolov5s_fp16,
+                                              det_db_resnet18_fp16,mobile_unicorn_fp16,yolov5s_simp_fp16]
                                        [--batch B] [--size S] [--iters K] [--trace]
 
 Per network: images/s with the input resident on the device (CUDA-graph replays, CUDA events on the
 plan's stream) and end to end (pinned host input, H2D and D2H inside the timed region).  Defaults
 follow the benchmark configurations: ResNet-18-style fp16 batch 64 / int8 batch 256 at 224x224,
-MobileNetV2-style batch 256 at 224x224, YOLOv5s-style batch 32 at 640x640.  Weights are seeded
+MobileNetV2-style batch 256 at 224x224, YOLOv5s-style batch 32 at 640x640; the DB text detector batch 8 at
+640x640, the MobileFaceNet-style embedding net batch 256 at 128x128 (its fixed size) and the shipped
+YOLOv5s variant batch 32 at 640x640 (--size does not apply to the last two).  Weights are seeded
 random tensors; int8 scales come from a max-abs calibration pass of 8 seeded images through this
 library's own floating-point pipeline.  --trace prints the ten slowest steps of the plan.
 """
@@ -15,7 +18,7 @@ import time
 
 import numpy as np
 
-from . import host, models
+from . import host, model_zoo, models
 
 NETS = {
     # name: (builder, int8, batch, size)
@@ -24,6 +27,10 @@ NETS = {
     "mobilenetv2_fp16": (models.mobilenet_v2, False, 256, 224),
     "mobilenetv2_int8": (models.mobilenet_v2, True, 256, 224),
     "yolov5s_fp16": (models.yolov5s, False, 32, 640),
+    # the architectures of three model descriptions the reference ships (model_zoo), seeded random weights
+    "det_db_resnet18_fp16": (model_zoo.det_db_resnet18, False, 8, 640),
+    "mobile_unicorn_fp16": (model_zoo.mobile_unicorn, False, 256, 128),
+    "yolov5s_simp_fp16": (lambda **kw: model_zoo.yolov5s_simp(size=640, **kw), False, 32, 640),
 }
 
 
@@ -56,7 +63,7 @@ def main(argv=None):
         g, info = build(name, 0, size)
         pipe = host.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=True)
         x = torch.empty((batch, 3, size, size), dtype=torch.float32).pin_memory()
-        x.uniform_(0, 1, generator=torch.Generator().manual_seed(1))
+        x.uniform_(0, 255 if "Input" in g.phai_text() else 1, generator=torch.Generator().manual_seed(1))
         outs = None
         for _ in range(3):      # eager, capture, replay
             pipe.forward_ptr(x.data_ptr(), batch, 3, size, size)

@@ -52,7 +52,9 @@ typedef enum exb_act {
     EXB_ACT_SIGMOID = 4,
     EXB_ACT_RELU6 = 103,
     EXB_ACT_SILU = 104,
-    EXB_ACT_HARDSWISH = 105   /* x * clamp(x/6 + 0.5, 0, 1): HardSwish with alpha = 1/6, beta = 0.5 */
+    EXB_ACT_HARDSWISH = 105,  /* x * clamp(x/6 + 0.5, 0, 1): HardSwish with alpha = 1/6, beta = 0.5 */
+    EXB_ACT_PRELU = 106       /* x >= 0 ? x : slope[c] * x (PReLU, LeakyRelu): convolutions only, slopes attached to
+                                 the packed weights with exb_conv_weights_set_slopes / exb_dw_weights_set_slopes */
 } exb_act;
 
 typedef struct exb_ctx exb_ctx;                   /* per-device context */
@@ -191,6 +193,10 @@ EXB_API int exb_conv_weights_pack_f16(exb_ctx* ctx, const exb_conv_desc* d, cons
 EXB_API int exb_conv_weights_pack_i8(exb_ctx* ctx, const exb_conv_desc* d, const int8_t* w_oihw,
                                      const float* bias, const float* wscale, int n_wscale,
                                      float act_scale, exb_conv_weights** out);
+/* Per-output-channel slopes for EXB_ACT_PRELU (operation_prelu / operation_leakyrelu behind a convolution,
+ * src/Excalibur/operation_prelu.cpp:58-147): HOST array of n == Cout values, or n == 1 for one shared slope.
+ * May be called again to replace them; a forward with act == EXB_ACT_PRELU fails if none were set. */
+EXB_API int exb_conv_weights_set_slopes(exb_ctx* ctx, exb_conv_weights* w, const float* slopes, int n);
 EXB_API int exb_conv_weights_destroy(exb_conv_weights* w);
 
 /* x: NHWC in_dtype [N][H][W][cin_stride]; y (and y2, residual): NHWC [N][OH][OW][cout_stride].
@@ -233,6 +239,8 @@ typedef struct exb_dwconv_desc {
 /* w: HOST fp32 [C][kh][kw] (the reference's OIHW with Cin/group == 1), bias[C] or NULL. */
 EXB_API int exb_dw_weights_pack(exb_ctx* ctx, const exb_dwconv_desc* d, const float* w,
                                 const float* bias, exb_dw_weights** out);
+/* As exb_conv_weights_set_slopes, n == C or 1. */
+EXB_API int exb_dw_weights_set_slopes(exb_ctx* ctx, exb_dw_weights* w, const float* slopes, int n);
 EXB_API int exb_dw_weights_destroy(exb_dw_weights* w);
 EXB_API int exb_dwconv2d_fwd(exb_ctx* ctx, const exb_dwconv_desc* d, const void* x,
                              const exb_dw_weights* w, void* y, void* stream);
@@ -349,6 +357,12 @@ EXB_API int exb_dequantize_fwd(exb_ctx* ctx, const int8_t* q, void* y, int out_d
  * src/Excalibur/cuda/operation_hardswish.cu:10-36).  EXB_F16 or EXB_F32. */
 EXB_API int exb_hardswish_fwd(exb_ctx* ctx, const void* x, void* y, int64_t count, int dtype, float alpha,
                               float beta, void* stream);
+/* Network input straight to the Focus layer's output: fp32 NCHW image -> optional y = x * mul[c] + add[c]
+ * (operation_input, src/Excalibur/operation_input.cpp:92-96; device arrays of C entries, both or neither)
+ * -> space-to-depth as exb_focus_fwd -> channel-last fp16 [N][H/2][W/2][c_stride], c_stride 16 or 32 and
+ * >= 4*C, padding channels 0.  Replaces three passes over the image (normalise, ingest, focus). */
+EXB_API int exb_nchw_f32_focus_to_nhwc_f16(exb_ctx* ctx, const float* x, void* y, int N, int C, int H, int W,
+                                           int c_stride, const float* mul, const float* add, void* stream);
 /* Space-to-depth of operation_yolov5focus (src/Excalibur/operation_yolov5focus.cpp:16-47):
  * out[n][g*C + c][i][j] = in[n][c][2i + g%2][2j + g/2], g = 0..3, output H/2 x W/2 with 4*C channels.
  * Every image of the batch is converted (the reference only converts image 0).
@@ -356,6 +370,11 @@ EXB_API int exb_hardswish_fwd(exb_ctx* ctx, const void* x, void* y, int64_t coun
  * (EXB_F16, EXB_I8 or EXB_F32; padding channels of the output are written as 0). */
 EXB_API int exb_focus_fwd(exb_ctx* ctx, const void* x, void* y, int N, int C, int H, int W, int in_stride,
                           int out_stride, int dtype, int channel_last, void* stream);
+/* y = prelu(x * mul[c] + add[c], slope): a BatchNorm followed by a PReLU / LeakyRelu in one pass (the
+ * BottleneckCSP tail of the shipped YOLOv5s description).  Arguments as exb_channel_affine_fwd and exb_prelu_fwd. */
+EXB_API int exb_channel_affine_prelu_fwd(exb_ctx* ctx, const void* x, void* y, const float* mul, const float* add,
+                                         const float* slope, int n_slope, int64_t outer, int C, int c_stride,
+                                         int64_t inner, int dtype, int channel_last, void* stream);
 /* y = x >= 0 ? x : x * slope[c]: operation_prelu (src/Excalibur/operation_prelu.cpp:58-147; n_slope == C, or 1 for
  * a slope shared by every channel) and operation_leakyrelu (src/Excalibur/operation_leakyrelu.cpp:31-58; n_slope
  * == 1).  slope is a device array.  Tensor indexing as exb_channel_affine_fwd.  EXB_F16 or EXB_F32; y may alias x. */

@@ -194,3 +194,170 @@ def test_yolov5s_simp_batch_is_computed_for_every_image():
         assert _rel(out[n][0:1], ref) < 2e-2
         np.testing.assert_array_equal(out[n][2], out[n][0])
     p.close()
+
+
+# ---- PReLU in convolution epilogues, fused passes -----------------------------------------------------
+@pytest.mark.parametrize("case", [
+    # N, Cin, H, W, Cout, k, stride, cin_stride, cout_stride, int8
+    (2, 64, 20, 20, 64, 3, 1, 64, 64, False),     # two CTAs per SM variant
+    (2, 24, 9, 11, 40, 1, 1, 32, 48, False),      # padded channels, ragged Cout
+    (1, 512, 7, 7, 512, 3, 1, 512, 512, False),   # one CTA per SM variant
+    (2, 64, 12, 12, 128, 3, 2, 64, 128, True),    # int8 operands
+    (2, 16, 9, 9, 24, 3, 1, 16, 24, False),       # ragged output stride: element-wise epilogue
+])
+def test_conv_prelu_epilogue(case):
+    import torch
+    from excalibur_b200 import capi
+    from tests.util import dev, host, to_nhwc, to_nchw, assert_close_f16, quant_weights
+    ctx = capi.Context(0)
+    N, Cin, H, W, Cout, k, s, cin_s, cout_s, int8 = case
+    r = np.random.default_rng(sum(case[:7]))
+    pad = k // 2
+    sl = r.uniform(0.05, 0.9, Cout).astype(np.float32)
+    b = (r.standard_normal(Cout) * 0.1).astype(np.float32)
+    if int8:
+        xq = r.integers(-128, 128, (N, Cin, H, W)).astype(np.int8)
+        w = (r.standard_normal((Cout, Cin, k, k)) * 0.05).astype(np.float32)
+        wq, ws = quant_weights(w)
+        fs = np.float32(31.0)
+        acc = O.conv2d_i8_acc(xq, wq, s, pad)
+        ref = O.prelu(O.dequantize(acc, O.dequant_scales(ws, fs, Cout), b), sl)
+        d = capi.make_conv_desc(N, H, W, Cin, Cout, k, s, pad, capi.EXB_I8, capi.EXB_F32, act=capi.ACT_PRELU,
+                                cin_stride=cin_s, cout_stride=cout_s)
+        wp = capi.ConvWeights(ctx, d, wq, b, ws, fs)
+        xin = dev(to_nhwc(xq, cin_s))
+    else:
+        x = f16_round(r.uniform(-1, 1, (N, Cin, H, W)))
+        w = f16_round(r.standard_normal((Cout, Cin, k, k)) * 0.1)
+        ref = O.prelu(O.conv2d_f32(x, w, b, s, pad), sl)
+        d = capi.make_conv_desc(N, H, W, Cin, Cout, k, s, pad, capi.EXB_F16, capi.EXB_F16, act=capi.ACT_PRELU,
+                                cin_stride=cin_s, cout_stride=cout_s)
+        wp = capi.ConvWeights(ctx, d, w, b)
+        xin = dev(to_nhwc(x, cin_s).astype(np.float16))
+    with pytest.raises(capi.ExbError):
+        capi.conv2d(ctx, d, xin, wp)                  # no slopes attached yet
+    wp.set_slopes(ctx, sl)
+    y, _ = capi.conv2d(ctx, d, xin, wp)
+    ctx.sync_check()
+    yh = host(y).astype(np.float32)
+    assert not yh[..., Cout:].any(), "padding channels must be written as zero"
+    if int8:
+        np.testing.assert_allclose(to_nchw(yh, Cout), ref, rtol=1e-6, atol=1e-6)
+    else:
+        assert_close_f16(to_nchw(yh, Cout), ref, what="prelu")
+    wp.set_slopes(ctx, sl[:1])                         # one shared slope (LeakyRelu)
+    y, _ = capi.conv2d(ctx, d, xin, wp)
+    ctx.sync_check()
+    ref1 = np.where(ref >= 0, ref, 0) + np.where(ref < 0, ref, 0) / sl[None, :, None, None] * sl[0]
+    np.testing.assert_allclose(to_nchw(host(y).astype(np.float32), Cout), ref1, rtol=2e-2, atol=2e-2)
+    with pytest.raises(capi.ExbError):
+        wp.set_slopes(ctx, sl[:3])
+    wp.close()
+    ctx.close()
+
+
+@pytest.mark.parametrize("k,s,C", [(3, 1, 64), (3, 2, 40), (5, 1, 16)])
+def test_dwconv_prelu_epilogue(k, s, C):
+    from excalibur_b200 import capi
+    from tests.util import dev, host, to_nhwc, to_nchw
+    ctx = capi.Context(0)
+    r = np.random.default_rng(k * 100 + C)
+    x = f16_round(r.standard_normal((2, C, 15, 17)))
+    w = (r.standard_normal((C, 1, k, k)) * 0.3).astype(np.float32)
+    b = (r.standard_normal(C) * 0.1).astype(np.float32)
+    sl = r.uniform(0.05, 0.9, C).astype(np.float32)
+    ref = O.prelu(O.dwconv2d_f32(x, w, b, s, k // 2, 0), sl)
+    d = capi.make_dw_desc(2, 15, 17, C, k, s, k // 2, act=capi.ACT_PRELU)
+    wp = capi.DwWeights(ctx, d, w, b)
+    with pytest.raises(capi.ExbError):
+        capi.dwconv2d(ctx, d, dev(to_nhwc(x).astype(np.float16)), wp)
+    wp.set_slopes(ctx, sl)
+    y = to_nchw(host(capi.dwconv2d(ctx, d, dev(to_nhwc(x).astype(np.float16)), wp)).astype(np.float32))
+    ctx.sync_check()
+    np.testing.assert_allclose(y, ref, rtol=2e-3, atol=2e-3)
+    wp.close()
+    ctx.close()
+
+
+@pytest.mark.parametrize("C,cs", [(13, 16), (64, 64), (5, 5)])
+def test_channel_affine_prelu_kernel(C, cs):
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    r = np.random.default_rng(C + 1)
+    x = f16_round(r.standard_normal((2, C, 6, 5)).astype(np.float32) * 2)
+    mul, add = r.uniform(0.5, 1.5, C).astype(np.float32), r.standard_normal(C).astype(np.float32)
+    sl = r.uniform(0.01, 0.9, C).astype(np.float32)
+    xh = torch.full((2, 6, 5, cs), 3.0, dtype=torch.float16, device="cuda")
+    xh[..., :C] = torch.from_numpy(O.nchw_to_nhwc(x)).cuda().half()
+    y = capi.channel_affine_prelu(ctx, xh, torch.from_numpy(mul).cuda(), torch.from_numpy(add).cuda(),
+                                  torch.from_numpy(sl).cuda(), channels=C)
+    torch.cuda.synchronize()
+    want = O.prelu(O.channel_affine(x, mul, add), sl)
+    got = O.nhwc_to_nchw(y[..., :C].float().cpu().numpy())
+    np.testing.assert_allclose(got, want, rtol=2e-3, atol=2e-3)
+    assert float(y[..., C:].abs().sum()) == 0.0
+    # the plain affine map takes the same vector kernel
+    y = capi.channel_affine(ctx, xh, torch.from_numpy(mul).cuda(), torch.from_numpy(add).cuda(), channels=C, act=capi.ACT_RELU)
+    got = O.nhwc_to_nchw(y[..., :C].float().cpu().numpy())
+    np.testing.assert_allclose(got, np.maximum(O.channel_affine(x, mul, add), 0), rtol=2e-3, atol=2e-3)
+    assert float(y[..., C:].abs().sum()) == 0.0
+    ctx.close()
+
+
+@pytest.mark.parametrize("norm", [False, True])
+def test_focus_ingest_kernel(norm):
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    r = np.random.default_rng(9)
+    x = r.uniform(0, 255, (3, 3, 10, 12)).astype(np.float32)
+    means, scales = np.array([10.0, 20.0, 30.0], np.float32), np.array([0.01, 0.02, 0.03], np.float32)
+    mul = torch.from_numpy(scales).cuda() if norm else None
+    add = torch.from_numpy(-means * scales).cuda() if norm else None
+    y = capi.focus_ingest(ctx, torch.from_numpy(x).cuda(), 16, mul, add)
+    torch.cuda.synchronize()
+    src = O.channel_affine(x, scales, -means * scales) if norm else x
+    want = O.focus(src)
+    got = O.nhwc_to_nchw(y[..., :12].float().cpu().numpy())
+    np.testing.assert_allclose(got, want, rtol=1e-3, atol=1e-3 if norm else 0.07)      # fp16 rounding of values up to 255
+    assert float(y[..., 12:].abs().sum()) == 0.0
+    with pytest.raises(capi.ExbError):
+        capi.focus_ingest(ctx, torch.zeros((1, 3, 9, 12), device="cuda"))
+    ctx.close()
+
+
+def test_depth_to_space_kernel_whole_vectors():
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    N, H, W, r_, C = 2, 4, 5, 2, 16
+    x = np.random.default_rng(5).standard_normal((N, H, W, r_ * r_ * C)).astype(np.float16)
+    y = capi.depth_to_space(ctx, torch.from_numpy(x).cuda(), r_, r_, C)
+    torch.cuda.synchronize()
+    want = np.zeros((N, H * r_, W * r_, C), np.float16)
+    for a in range(r_):
+        for b in range(r_):
+            want[:, a::r_, b::r_] = x[..., (a * r_ + b) * C:(a * r_ + b + 1) * C]
+    np.testing.assert_array_equal(y.cpu().numpy(), want)
+    ctx.close()
+
+
+def test_fused_plans_of_the_three_networks_are_short():
+    """PReLU / LeakyRelu / BatchNorm fold into their producers and the Focus layer into the ingest kernel."""
+    h = _host()
+    g, _ = model_zoo.mobile_unicorn()
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=True)
+    p.forward(S["unicorn_x"])
+    launches, _ = p.stats()
+    p.close()
+    # 32 convolutions + 17 depthwise convolutions (every PReLU and residual add folded), Input, ingest, FC
+    assert launches <= 32 + 17 + 3, launches
+    g, _ = model_zoo.yolov5s_simp(size=128)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=True)
+    p.forward(S["yolosimp_x"])
+    launches, _ = p.stats()
+    p.close()
+    # 70 convolutions, 8 BatchNorm + LeakyRelu passes, 13 concats, 3 poolings, 2 resizes, 7 adds at most,
+    # one ingest + focus kernel, 3 x (emit + transpose)
+    assert launches <= 70 + 8 + 13 + 3 + 2 + 7 + 1 + 6, launches
