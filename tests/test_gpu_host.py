@@ -306,7 +306,7 @@ def test_focus_net(fusion):
     assert _rel(out, Y["fnet_out"]) < 1e-2, _rel(out, Y["fnet_out"])
     if fusion:
         launches, _ = p.stats()
-        assert launches == 7       # normalise, ingest, focus, 3 convs (HardSwish folded into two), emit
+        assert launches == 5       # normalise + ingest + focus in one kernel, 3 convs (HardSwish folded into two), emit
     p.close()
 
 
