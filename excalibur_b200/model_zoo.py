@@ -1,4 +1,4 @@
-"""Graphs with the architecture of three model descriptions the reference ships, with seeded random weights.
+"""Graphs with the architecture of model descriptions the reference ships, with seeded random weights.
 
 The reference's `models/` folder holds `.phai` descriptions without weights.  These builders emit the
 same operation sequences (type, parameters and wiring; feature-map names are this package's own) so the
@@ -11,6 +11,8 @@ is not available:
   activations, depthwise 3x3 convs, a global 8x8 depthwise conv and a 128-way InnerProduct.
 * `yolov5s_simp()`     - models/yolov5s_simp.phai: YOLOv5s (Focus, BottleneckCSP with BatchNorm +
   LeakyRelu, HardSwish convs, SPP 5/9/13, PAN) with Reshape + Transpose detection heads.
+* `unicorn_light()`    - models/unicorn_light_*_usefulpart.phai and its `_int8` sibling, the int8 model
+  description the reference ships: every dense convolution quantised, the first one included.
 
 `structure(text)` reduces a description to a name-free canonical form; the test-suite compares the
 builders' output with the shipped files through it when the reference tree is present.
@@ -273,6 +275,76 @@ def yolov5s_simp(seed=13, size=640, num_outputs=255, anchors=3):
     return g, {"input": "data", "outputs": outs}
 
 
+def unicorn_light(seed=14, act_scales=None):
+    """models/unicorn_light_*_usefulpart.phai and its `_int8` sibling: a VGG-like residual embedding net for
+    3 x 128 x 128 images - unpadded 3x3 convs + ReLU + 2x2 max pooling between stages, residual pairs of
+    padded 3x3 convs whose second ReLU comes BEFORE the addition (Eltwise), and a global 4x4 depthwise conv
+    to a 256-value embedding.  act_scales {conv name: fs} turns every dense convolution into an int8 one
+    (key 8=2, the first convolution included, as in the shipped int8 description) and the depthwise
+    convolution into one with int8 weights (8=1; the reference dequantises those and computes in fp32).
+    Returns (GraphBuilder, info); info["conv_inputs"] maps each dense conv to the map it reads."""
+    from .models import quantize_weights
+    g = GraphBuilder("unicorn_light_int8" if act_scales else "unicorn_light")
+    net = _Net(g)
+    init = _Init(seed)
+    conv_inputs = {}
+
+    def conv(name, x, cout, cin, pad):
+        w, b = init.conv(cout, cin, 3)
+        conv_inputs[name] = x
+        text = "0=%d 1=3 2=1 3=1 4=%d 5=1 6=%d" % (cout, pad, w.size)
+
+        def emit(ins, out):
+            conv_inputs[name] = ins[0]
+            if act_scales is None:
+                g._conv_weights(w, b, None)
+                g._op("Convolution", name, ins, [out], text)
+            else:
+                wq, ws = quantize_weights(w)
+                g._conv_weights(w, b, (wq, ws, act_scales[name]))
+                g._op("Convolution", name, ins, [out], text + " 8=2")
+        y = net.add(emit, [x], name)
+        return net.add(lambda ins, out: g.relu(name + "_relu", ins[0], out), [y], name + "_act")
+
+    def pool(name, x):
+        return net.add(lambda ins, out: g._op("Pooling", name, ins, [out], "0=0 1=2 2=2 3=0 4=0"), [x], name)
+
+    def res(name, x, c, first):
+        h = conv("%s_%d" % (name, first), x, c, c, 1)
+        h = conv("%s_%d" % (name, first + 1), h, c, c, 1)
+        return net.add(lambda ins, out: g._op("Eltwise", "res%s_%d" % (name[4:], first + 1), ins, [out], "0=1 -23301=0"),
+                       [x, h], "res%s_%d" % (name[4:], first + 1))
+
+    x = net.add(lambda ins, out: g._op("Input", "data_norm", ins, [out], "0=128 1=128 2=3 3=104,117,123 4=0.0078125"),
+                ["data"], "normed")
+    x = conv("conv1a", x, 16, 3, 0)
+    x = conv("conv1b", x, 32, 16, 0)
+    x = pool("pool1b", x)
+    x = res("conv2", x, 32, 1)
+    cin = 32
+    for stage, (cout, pairs) in enumerate(((64, 2), (128, 5), (256, 3)), start=2):
+        x = conv("conv%d" % stage, x, cout, cin, 0)
+        x = pool("pool%d" % stage, x)
+        for k in range(pairs):
+            x = res("conv%d" % (stage + 1), x, cout, 2 * k + 1)
+        cin = cout
+    x = conv("conv5", x, 256, 256, 0)
+    w, b = init.conv(256, 1, 4)
+
+    def emit_dw(ins, out):
+        text = "0=256 1=4 2=1 3=1 4=0 5=1 6=4096 7=256"
+        if act_scales is None:
+            g._conv_weights(w, b, None)
+        else:
+            wq, ws = quantize_weights(w)
+            g._conv_weights(w, b, (wq, ws, 1.0))
+            text += " 8=1"
+        g._op("ConvolutionDepthWise", "conv5_dw", ins, [out], text)
+    net.add(emit_dw, [x], "conv5_dw")
+    net.emit()
+    return g, {"input": "data", "outputs": ["conv5_dw"], "conv_inputs": conv_inputs}
+
+
 # ---- canonical, name-free form of a description -----------------------------------------------------
 _CONV_TYPES = ("convolution", "convolutiondepthwise", "deconvolution")
 
@@ -287,7 +359,7 @@ def _canon_params(type_, params):
         kw, dil, sw, pl = one(1, 0), one(2, 1), one(3, 1), one(4, 0)
         return {"cout": one(0, 0), "kw": kw, "kh": one(11, kw), "dw": dil, "dh": one(12, dil), "sw": sw, "sh": one(13, sw),
                 "pl": pl, "pt": one(14, pl), "pr": one(15, pl), "pb": one(16, pl), "bias": one(5, 0), "wsize": one(6, 0),
-                "group": one(7, 1), "int8": one(8, 0), "act": one(9, 0)}
+                "group": one(7, 1), "int8": float(one(8, 0) != 0), "act": one(9, 0)}
     if type_ == "pooling":
         one = lambda k, d: p.get(k, (float(d),))[0]
         kw, sw, pl = one(1, 0), one(2, 1), one(3, 0)

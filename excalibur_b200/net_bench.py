@@ -1,7 +1,7 @@
 """Whole-network throughput of the benchmark configurations other than the headline one.
 
     python -m excalibur_b200.net_bench [--net resnet18_fp16,resnet18_int8,mobilenetv2_fp16,mobilenetv2_int8,yolov5s_fp16,
-                                              det_db_resnet18_fp16,mobile_unicorn_fp16,yolov5s_simp_fp16]
+                                              det_db_resnet18_fp16,mobile_unicorn_fp16,yolov5s_simp_fp16,unicorn_light_fp16,unicorn_light_int8]
                                        [--batch B] [--size S] [--iters K] [--trace]
 
 Per network: images/s with the input resident on the device (CUDA-graph replays, CUDA events on the
@@ -31,6 +31,8 @@ NETS = {
     "det_db_resnet18_fp16": (model_zoo.det_db_resnet18, False, 8, 640),
     "mobile_unicorn_fp16": (model_zoo.mobile_unicorn, False, 256, 128),
     "yolov5s_simp_fp16": (lambda **kw: model_zoo.yolov5s_simp(size=640, **kw), False, 32, 640),
+    "unicorn_light_fp16": (model_zoo.unicorn_light, False, 256, 128),
+    "unicorn_light_int8": (model_zoo.unicorn_light, True, 256, 128),
 }
 
 
@@ -39,7 +41,8 @@ def build(name, device, size):
     g, info = builder()
     if int8:
         p = host.Pipeline(g.phai_text(), g.racy_bytes(), device, fusion=False)
-        calib = np.random.default_rng(77).uniform(0, 1, (8, 3, size, size)).astype(np.float32)
+        hi = 255 if "Input" in g.phai_text() else 1
+        calib = np.random.default_rng(77).uniform(0, hi, (8, 3, size, size)).astype(np.float32)
         scales = models.calibrate(p, info["conv_inputs"], calib)
         p.close()
         g, info = builder(act_scales=scales)

@@ -187,6 +187,25 @@ def shipped():
     # batch 1: the reference's YoloV5Focus only fills image 0
     g, info = model_zoo.yolov5s_simp(size=128)
     net("yolosimp", g, info, r.uniform(0, 255, (1, 3, 128, 128)).astype(np.float32), ("csp2_cv4_act", "spp_cat_out"))
+    # the shipped int8 description: max-abs calibration of every dense conv's input through the reference's
+    # fp32 pipeline on 8 seeded images, then the reference's int8 forward (batch 1: its packed int8 path only
+    # computes image 0)
+    g, info = model_zoo.unicorn_light()
+    calib = r.uniform(0, 255, (8, 3, 128, 128)).astype(np.float32)
+    pf = ref_lib.RefPipeline(g.phai_text(), g.racy_bytes())
+    scales = models.calibrate(_RefAdapter(pf), info["conv_inputs"], calib)
+    x = r.uniform(0, 255, (1, 3, 128, 128)).astype(np.float32)
+    out["ulight_x"] = x
+    out["ulight_fp_out"] = pf.forward(x)["conv5_dw"]
+    pf.close()
+    names = sorted(scales)
+    out["ulight_scale_names"] = np.array(names)
+    out["ulight_scales"] = np.array([scales[n] for n in names], np.float32)
+    g8, info8 = model_zoo.unicorn_light(act_scales=scales)
+    p8 = ref_lib.RefPipeline(g8.phai_text(), g8.racy_bytes())
+    out["ulight_i8_out"] = p8.forward(x)["conv5_dw"]
+    out["ulight_i8_map_res2_2"] = p8.featmap("res2_2")
+    p8.close()
     path = os.path.join(ROOT, "tests", "golden", "shipped_model_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")

@@ -361,3 +361,46 @@ def test_fused_plans_of_the_three_networks_are_short():
     # 70 convolutions, 8 BatchNorm + LeakyRelu passes, 13 concats, 3 poolings, 2 resizes, 7 adds at most,
     # one ingest + focus kernel, 3 x (emit + transpose)
     assert launches <= 70 + 8 + 13 + 3 + 2 + 7 + 1 + 6, launches
+
+
+# ---- the shipped int8 description ------------------------------------------------------------------------
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_unicorn_light_fp(fusion):
+    h = _host()
+    g, _ = model_zoo.unicorn_light()
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    for _ in range(3):
+        out = p.forward(S["ulight_x"])["conv5_dw"]
+    assert out.shape == S["ulight_fp_out"].shape
+    assert _rel(out, S["ulight_fp_out"]) < 1e-2, _rel(out, S["ulight_fp_out"])
+    p.close()
+
+
+@pytest.mark.parametrize("fusion", [True, False], ids=["fused", "op_by_op"])
+def test_unicorn_light_int8(fusion):
+    """Every dense convolution int8 (the first one, on the 3-channel image, included), scales from the
+    reference's own calibration pass: within 3e-2 of the reference's int8 embedding and no further from
+    the fp32 embedding than 1.5 x the reference's own quantisation error."""
+    h = _host()
+    scales = {str(n): np.float32(v) for n, v in zip(S["ulight_scale_names"], S["ulight_scales"])}
+    g, _ = model_zoo.unicorn_light(act_scales=scales)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+    for _ in range(3):
+        out = p.forward(S["ulight_x"])["conv5_dw"]
+    ref8, ref32 = S["ulight_i8_out"], S["ulight_fp_out"]
+    assert out.shape == ref8.shape
+    assert _rel(out, ref8) < 3e-2, _rel(out, ref8)
+    assert _rel(out, ref32) < 1.5 * _rel(ref8, ref32), (_rel(out, ref32), _rel(ref8, ref32))
+    if not fusion:
+        # op by op the int8 convolutions reproduce the reference's arithmetic: first residual sum within fp32 noise
+        m = p.get("res2_2")
+        assert _rel(m, S["ulight_i8_map_res2_2"]) < 1e-5, _rel(m, S["ulight_i8_map_res2_2"])
+    p.close()
+    # a batch: every image is computed (the reference's packed int8 path only computes image 0)
+    p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=True)
+    x = np.concatenate([S["ulight_x"], S["ulight_x"][:, ::-1].copy(), S["ulight_x"]], axis=0)
+    out3 = p.forward(x)["conv5_dw"]
+    np.testing.assert_array_equal(out3[2], out3[0])
+    assert _rel(out3[0:1], ref8) < 3e-2
+    assert np.abs(out3[1] - out3[0]).max() > 0
+    p.close()

@@ -48,9 +48,25 @@ def test_builders_have_the_shipped_architecture(name, ops):
     assert mine == shipped
 
 
+def test_unicorn_light_builder_matches_the_shipped_fp_and_int8_descriptions():
+    g, info = model_zoo.unicorn_light()
+    fp = model_zoo.structure(g.phai_text())
+    g8, _ = model_zoo.unicorn_light(act_scales={n: 1.0 for n in info["conv_inputs"]})
+    i8 = model_zoo.structure(g8.phai_text())
+    assert len(fp) == len(i8) == 73
+    assert sum(1 for t, p, _ in i8 if t == "convolution" and p["int8"]) == 28
+    base = os.path.join(REF_MODELS, "unicorn_light_806204_m1x3x2+120k_universial_noised_usefulpart")
+    if not os.path.exists(base + ".phai"):
+        pytest.skip("reference tree not present: only the op counts are checked")
+    assert fp == model_zoo.structure(open(base + ".phai").read())
+    assert i8 == model_zoo.structure(open(base + "_int8.phai").read())
+
+
 def test_weight_file_covers_every_record_of_the_builders():
     from excalibur_b200.calibrate import parse_phai, racy_record_size
-    for fn in (model_zoo.det_db_resnet18, model_zoo.mobile_unicorn, model_zoo.yolov5s_simp):
+    int8 = lambda: model_zoo.unicorn_light(act_scales={n: 2.0 for n in model_zoo.unicorn_light()[1]["conv_inputs"]})
+    int8.__name__ = "unicorn_light_int8"
+    for fn in (model_zoo.det_db_resnet18, model_zoo.mobile_unicorn, model_zoo.yolov5s_simp, model_zoo.unicorn_light, int8):
         g, _ = fn()
         _, ops = parse_phai(g.phai_text())
         blob = g.racy_bytes()
