@@ -347,7 +347,14 @@ def run_gpu_arm(args, rank, world, local_rank):
     # ---- end-to-end: host buffers, H2D + D2H inside the timed region ---------------------------
     # pipeline<float>::forward on the whole pinned batch; the pipeline copies sub-batch c+1 to the
     # device while it computes sub-batch c (option h2d_chunks), logits come back per sub-batch
+    # (--e2e-host-threads T: after T host threads have converted it to fp16 - half the PCIe bytes, identical
+    # logits; off by default)
+    host_threads = args.e2e_host_threads
+    if host_threads < 0:
+        per_rank = (os.cpu_count() or 1) // max(world, 1)
+        host_threads = min(16, per_rank) if per_rank >= 4 else 0
     pipe.set_option("h2d_chunks", args.e2e_chunks)
+    pipe.set_option("host_f16_threads", host_threads)
     for _ in range(3):
         e2e_step()
     barrier()
@@ -358,6 +365,7 @@ def run_gpu_arm(args, rank, world, local_rank):
     e2e_s = max_over_ranks(time.perf_counter() - te0)
     barrier()
     pipe.set_option("h2d_chunks", 1)
+    pipe.set_option("host_f16_threads", 0)
 
     if rank != 0:
         if dist is not None:
@@ -432,7 +440,9 @@ def run_gpu_arm(args, rank, world, local_rank):
                    "timing": "CUDA events on the plan's stream around K %s, max over ranks"
                              % ("eager launches of the plan (--no-graph)" if args.no_graph else "CUDA-graph replays")},
         "clocks": clocks,
-        "e2e": {"value": images / e2e_s, "unit": "images/s", "h2d_bytes_per_step": BATCH * 3 * IMG * IMG * 4,
+        "e2e": {"value": images / e2e_s, "unit": "images/s",
+                "h2d_bytes_per_step": BATCH * 3 * IMG * IMG * (2 if host_threads > 0 else 4),
+                "host_convert_threads": host_threads,
                 "d2h_bytes_per_step": BATCH * 1000 * 4, "ms_per_step": e2e_s * 1000.0 / args.steps,
                 "h2d_chunks": args.e2e_chunks,
                 "host_binding": ("rank 0 bound to %d CPUs next to its GPU" % len(numa_cpus)) if numa_cpus else "none"},
@@ -464,6 +474,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-chunks", type=int, default=4,
                     help="sub-batches of one end-to-end forward (copy of c+1 overlaps compute of c)")
+    ap.add_argument("--e2e-host-threads", type=int, default=0,
+                    help="host threads converting the fp32 input to fp16 before the copy in the end-to-end measurement "
+                         "(0 = copy fp32 as it is, the default: on this pool's 16-vCPU hosts the conversion costs more "
+                         "than the PCIe bytes it saves; -1 = min(16, host CPUs per rank), off below 4)")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the plan's kernels one by one instead of replaying a CUDA graph (profilers "
                          "cannot attach to launches made during stream capture); not a bench configuration")

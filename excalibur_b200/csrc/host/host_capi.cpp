@@ -5,6 +5,7 @@
 #include <sstream>
 
 #include "ops.hpp"
+#include "host_convert.hpp"
 #include "pipeline.hpp"
 
 using namespace glasssix;
@@ -95,6 +96,7 @@ extern "C" int exb_host_pipeline_set_option(void* p, const char* key, int value)
     else if (k == "cuda_graph") h->net->set_cuda_graph(value != 0);
     else if (k == "profile") value ? h->net->enable_profiler() : h->net->disable_profiler();
     else if (k == "h2d_chunks") h->net->set_h2d_chunks(value);
+    else if (k == "host_f16_threads") h->net->set_host_f16_threads(value);
     else {
         g_err = "unknown option " + k;
         return EXB_ERR_BAD_ARG;
@@ -224,5 +226,22 @@ extern "C" int exb_host_op_run(const char* type, const char* params, const char*
         op.reset();
         exb_ctx_destroy(ctx);
         return rc;
+    });
+}
+
+// fp32 -> fp16 on the host, round to nearest even (what "host_f16_threads" runs before the copy); needs no GPU.
+extern "C" int exb_host_convert_f32_to_f16(const float* src, uint16_t* dst, int64_t n, int threads, int force_scalar) {
+    return guarded([&]() {
+        if (n < 0 || (n > 0 && (!src || !dst))) {
+            g_err = "exb_host_convert_f32_to_f16: bad argument";
+            return (int)EXB_ERR_BAD_ARG;
+        }
+        if (threads > 1 && !force_scalar) {
+            glasssix::excalibur::convert_pool pool(threads);
+            pool.run(src, dst, (size_t)n);
+        } else {
+            glasssix::excalibur::convert_f32_to_f16(src, dst, (size_t)n, force_scalar != 0);
+        }
+        return (int)EXB_OK;
     });
 }

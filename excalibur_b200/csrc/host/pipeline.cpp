@@ -9,6 +9,7 @@
 #include <functional>
 #include <set>
 
+#include "host_convert.hpp"
 #include "ops.hpp"
 
 namespace glasssix {
@@ -83,6 +84,7 @@ public:
                const std::vector<std::string>& inputs, const std::vector<std::string>& outputs, int device)
         : params_(params), ops_(ops), inputs_(inputs), outputs_(outputs), device_(device) {}
     ~fused_plan() {
+        if (host_f16_) cudaFreeHost(host_f16_);
         if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
         for (auto e : copied_) cudaEventDestroy(e);
         if (copy_stream_) cudaStreamDestroy(copy_stream_);
@@ -113,8 +115,11 @@ public:
     void run(const float* host_input, bool use_graph, bool profile, std::vector<trace_event>* trace);
     std::shared_ptr<memory::tensor<float>> fetch(const std::string& name);
     double run_resident(int iters, bool use_graph);
-    // forward of k * N_ images: chunk c+1 is copied to the device while chunk c is computed
-    void run_chunked(const float* host_input, int k, bool use_graph);
+    // forward of k * N_ images: chunk c+1 is copied to the device while chunk c is computed.  host_threads > 0:
+    // each chunk is first converted to fp16 on the host by that many threads (half the PCIe bytes), when the
+    // plan's ingest step can read fp16 planes; otherwise the fp32 input is copied as it is.
+    void run_chunked(const float* host_input, int k, bool use_graph, int host_threads = 0);
+    bool host_f16_capable() const { return ingest_f16_capable_; }
     int launches() const { return launches_; }
     double device_ms() const { return device_ms_; }
     exb_ctx* ctx() { return ctx_; }
@@ -178,7 +183,12 @@ private:
     dev_buf staging_in_;
     dev_buf norm_in_;                      // normalised fp32 input when the graph starts with an Input op
     dev_buf chunk_stage_;                  // k chunks of fp32 input for run_chunked
-    const float* ingest_src_ = nullptr;    // what the ingest step (steps_[0]) reads; never part of the graph
+    const void* ingest_src_ = nullptr;     // what the ingest step (steps_[0]) reads; never part of the graph
+    bool ingest_src_f16_ = false;          // ingest_src_ holds fp16 planes (converted on the host)
+    bool ingest_f16_capable_ = false;      // the ingest step has an fp16-source variant
+    void* host_f16_ = nullptr;             // pinned staging for the host-converted input
+    size_t host_f16_bytes_ = 0;
+    std::unique_ptr<convert_pool> pool_;
     cudaStream_t copy_stream_ = nullptr;
     std::vector<cudaEvent_t> copied_;
     void launch_body(bool use_graph);
@@ -517,7 +527,7 @@ void fused_plan::build(int N, int C, int H, int W) {
             void* yo = form_f16(fy);
             const int ocs = fy.cs;
             add_step("ingest+focus " + in.name, [=](cudaStream_t st) {
-                exb_check(exb_nchw_f32_focus_to_nhwc_f16(ctx, this->ingest_src_, yo, N, C, H, W, ocs, mul, add, st),
+                exb_check(exb_nchw_f32_focus_to_nhwc_f16(ctx, static_cast<const float*>(this->ingest_src_), yo, N, C, H, W, ocs, mul, add, st),
                           "exb_nchw_f32_focus_to_nhwc_f16");
             });
             absorbed[focus_op] = 1;
@@ -534,7 +544,7 @@ void fused_plan::build(int N, int C, int H, int W) {
             float* norm = static_cast<float*>(norm_in_.ensure((size_t)N * C * H * W * 4, device_));
             ingest_fixed = norm;
             add_step(params_[input_norm_op].name_, [=](cudaStream_t st) {
-                exb_check(exb_channel_affine_fwd(ctx, this->ingest_src_, norm, mul, add, N, C, 0, (int64_t)H * W, EXB_F32, 0,
+                exb_check(exb_channel_affine_fwd(ctx, static_cast<const float*>(this->ingest_src_), norm, mul, add, N, C, 0, (int64_t)H * W, EXB_F32, 0,
                                                  EXB_ACT_NONE, st), "exb_channel_affine_fwd");
             });
         }
@@ -545,14 +555,19 @@ void fused_plan::build(int N, int C, int H, int W) {
         if (focus_op >= 0) {
             // nothing else to ingest
         } else if (padded) {
+            ingest_f16_capable_ = !ingest_fixed && cs == 4 && C <= 3 && W % 4 == 0 && w_pad % 4 == 0 && w_pitch % 4 == 0;
             add_step("ingest " + in.name, [=](cudaStream_t st) {
-                exb_check(exb_nchw_f32_to_nhwc_padded(ctx, ingest_fixed ? ingest_fixed : this->ingest_src_, dst, EXB_F16, N, C, H, W,
-                                                      cs, w_pad, w_pitch, 1.f, 1, st),
-                          "exb_nchw_f32_to_nhwc_padded");
+                if (this->ingest_src_f16_)
+                    exb_check(exb_nchw_f16_to_nhwc4_padded(ctx, this->ingest_src_, dst, N, C, H, W, w_pad, w_pitch, st),
+                              "exb_nchw_f16_to_nhwc4_padded");
+                else
+                    exb_check(exb_nchw_f32_to_nhwc_padded(ctx, ingest_fixed ? ingest_fixed : static_cast<const float*>(this->ingest_src_),
+                                                          dst, EXB_F16, N, C, H, W, cs, w_pad, w_pitch, 1.f, 1, st),
+                              "exb_nchw_f32_to_nhwc_padded");
             });
         } else {
             add_step("ingest " + in.name, [=](cudaStream_t st) {
-                exb_check(exb_nchw_f32_to_nhwc(ctx, ingest_fixed ? ingest_fixed : this->ingest_src_, dst,
+                exb_check(exb_nchw_f32_to_nhwc(ctx, ingest_fixed ? ingest_fixed : static_cast<const float*>(this->ingest_src_), dst,
                                                direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs,
                                                direct_i8 ? s : 1.f, 1, st),
                           "exb_nchw_f32_to_nhwc");
@@ -993,7 +1008,8 @@ void fused_plan::run(const float* host_input, bool use_graph, bool profile, std:
     CUDA_CHECK(cudaSetDevice(device_));
     const size_t in_bytes = (size_t)N_ * C_ * H_ * W_ * 4;
     CUDA_CHECK(cudaMemcpyAsync(staging_in_.p, host_input, in_bytes, cudaMemcpyHostToDevice, stream_));
-    ingest_src_ = static_cast<const float*>(staging_in_.p);
+    ingest_src_ = staging_in_.p;
+    ingest_src_f16_ = false;
     launches_ = 0;
     for (auto& s : steps_) launches_ += s.launches;
     if (profile) {
@@ -1065,7 +1081,8 @@ void fused_plan::launch_body(bool use_graph) {
 double fused_plan::run_resident(int iters, bool use_graph) {
     if (!built_) return -1.0;
     CUDA_CHECK(cudaSetDevice(device_));
-    ingest_src_ = static_cast<const float*>(staging_in_.p);
+    ingest_src_ = staging_in_.p;
+    ingest_src_f16_ = false;
     if (!warmed_) launch_body(false);      // make sure every kernel has run eagerly once
     CUDA_CHECK(cudaStreamSynchronize(stream_));
     CUDA_CHECK(cudaEventRecord(ev0_, stream_));
@@ -1078,11 +1095,22 @@ double fused_plan::run_resident(int iters, bool use_graph) {
     return ms;
 }
 
-void fused_plan::run_chunked(const float* host_input, int k, bool use_graph) {
+void fused_plan::run_chunked(const float* host_input, int k, bool use_graph, int host_threads) {
     CUDA_CHECK(cudaSetDevice(device_));
     CHECK(built_ && k >= 1);
     const size_t chunk_elems = (size_t)N_ * C_ * H_ * W_;
+    const bool f16 = host_threads > 0 && ingest_f16_capable_;
     float* stage = static_cast<float*>(chunk_stage_.ensure(chunk_elems * 4 * k, device_));
+    uint16_t* stage16 = reinterpret_cast<uint16_t*>(stage);
+    if (f16) {
+        if (host_f16_bytes_ < chunk_elems * 2 * k) {
+            if (host_f16_) cudaFreeHost(host_f16_);
+            host_f16_ = nullptr;
+            CUDA_CHECK(cudaHostAlloc(&host_f16_, chunk_elems * 2 * k, cudaHostAllocDefault));
+            host_f16_bytes_ = chunk_elems * 2 * k;
+        }
+        if (!pool_ || pool_->threads() != host_threads) pool_.reset(new convert_pool(host_threads));
+    }
     if (!copy_stream_) CUDA_CHECK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
     while ((int)copied_.size() < k) {
         cudaEvent_t e;
@@ -1100,15 +1128,25 @@ void fused_plan::run_chunked(const float* host_input, int k, bool use_graph) {
     for (auto& s : steps_) launches_ += s.launches;
     launches_ *= k;
     // every copy is queued at once on its own stream; compute of chunk c waits for copy c only
-    for (int c = 0; c < k; ++c) {
-        CUDA_CHECK(cudaMemcpyAsync(stage + c * chunk_elems, host_input + c * chunk_elems, chunk_elems * 4,
-                                   cudaMemcpyHostToDevice, copy_stream_));
-        CUDA_CHECK(cudaEventRecord(copied_[c], copy_stream_));
+    if (!f16) {
+        for (int c = 0; c < k; ++c) {
+            CUDA_CHECK(cudaMemcpyAsync(stage + c * chunk_elems, host_input + c * chunk_elems, chunk_elems * 4,
+                                       cudaMemcpyHostToDevice, copy_stream_));
+            CUDA_CHECK(cudaEventRecord(copied_[c], copy_stream_));
+        }
     }
     CUDA_CHECK(cudaEventRecord(ev0_, stream_));
     for (int c = 0; c < k; ++c) {
+        if (f16) {
+            // the host converts chunk c while the copy of chunk c-1 and the kernels of chunk c-2 run
+            uint16_t* h16 = static_cast<uint16_t*>(host_f16_) + c * chunk_elems;
+            pool_->run(host_input + c * chunk_elems, h16, chunk_elems);
+            CUDA_CHECK(cudaMemcpyAsync(stage16 + c * chunk_elems, h16, chunk_elems * 2, cudaMemcpyHostToDevice, copy_stream_));
+            CUDA_CHECK(cudaEventRecord(copied_[c], copy_stream_));
+        }
         CUDA_CHECK(cudaStreamWaitEvent(stream_, copied_[c], 0));
-        ingest_src_ = stage + c * chunk_elems;
+        ingest_src_ = f16 ? static_cast<const void*>(stage16 + c * chunk_elems) : static_cast<const void*>(stage + c * chunk_elems);
+        ingest_src_f16_ = f16;
         launch_body(use_graph);
         for (auto& kv : host_out_) {
             fmap_info& f = fmaps_[root(index_[kv.first])];
@@ -1127,6 +1165,7 @@ void fused_plan::run_chunked(const float* host_input, int k, bool use_graph) {
     float ms = 0;
     cudaEventElapsedTime(&ms, ev0_, ev1_);
     device_ms_ = ms;
+    ingest_src_f16_ = false;
     exb_check(exb_ctx_sync_check(ctx_, stream_), "chunked forward");
 }
 
@@ -1275,6 +1314,7 @@ public:
     bool profile_ = false, fusion_ = true, graph_ = true;
     bool used_fused_ = false;
     int h2d_chunks_ = 1;
+    int host_f16_threads_ = 0;
     bool used_chunked_ = false;
     std::unique_ptr<fused_plan> chunk_plan_;
     exb_ctx* ctx_ = nullptr;
@@ -1359,12 +1399,12 @@ pipeline<float>::result_map pipeline<float>::impl::forward_gpu(const std::shared
             if (input->order() == memory::NHWC) input->convert_order();
             const int N = input->num(), C = input->channels(), H = input->height(), W = input->width();
             used_chunked_ = false;
-            if (h2d_chunks_ > 1 && !profile_ && N % h2d_chunks_ == 0) {
+            if ((h2d_chunks_ > 1 || host_f16_threads_ > 0) && !profile_ && N % h2d_chunks_ == 0) {
                 if (!chunk_plan_)
                     chunk_plan_.reset(new fused_plan(op_params_, operations_, input_names_, output_names_, device_));
                 const int nc = N / h2d_chunks_;
                 if (!chunk_plan_->built_for(nc, C, H, W)) chunk_plan_->build(nc, C, H, W);
-                chunk_plan_->run_chunked(input->cpu_data(), h2d_chunks_, graph_);
+                chunk_plan_->run_chunked(input->cpu_data(), h2d_chunks_, graph_, host_f16_threads_);
                 launches_ = chunk_plan_->launches();
                 device_ms_ = chunk_plan_->device_ms();
                 used_fused_ = true;
@@ -1431,6 +1471,7 @@ template <typename Dtype> int pipeline<Dtype>::device() const { return impl_->de
 template <typename Dtype> void pipeline<Dtype>::set_fusion(bool on) { impl_->fusion_ = on; }
 template <typename Dtype> void pipeline<Dtype>::set_cuda_graph(bool on) { impl_->graph_ = on; }
 template <typename Dtype> void pipeline<Dtype>::set_h2d_chunks(int k) { impl_->h2d_chunks_ = k < 1 ? 1 : k; }
+template <typename Dtype> void pipeline<Dtype>::set_host_f16_threads(int t) { impl_->host_f16_threads_ = t < 0 ? 0 : t; }
 template <typename Dtype> int pipeline<Dtype>::launches_last_forward() const { return impl_->launches_; }
 template <typename Dtype> double pipeline<Dtype>::run_resident(int iters) {
     if (!impl_->plan_ || !impl_->used_fused_ || !impl_->plan_->built()) return -1.0;

@@ -45,6 +45,11 @@ public:
     // while sub-batch c is computed (default 1 = whole batch at once).  Only the pipeline outputs
     // cover the whole batch afterwards; get_featmap() of an inner map sees the last sub-batch.
     void set_h2d_chunks(int k);
+    // t > 0: the forward converts the input to fp16 on the host with t threads before it is copied (half the
+    // PCIe bytes, the same round-to-nearest-even as the device ingest kernel, so identical results); used
+    // where the plan's ingest step can read fp16 planes (a 3-channel image feeding an fp16 stem conv, no
+    // Input normalisation), ignored elsewhere.  Default 0 = the fp32 input is copied as it is.
+    void set_host_f16_threads(int t);
     // Re-run the fused plan `iters` times on the input already resident on the device (the last
     // forward's), no host<->device copies; returns the device time in ms between CUDA events on the
     // plan's stream, or a negative value when there is no fused plan yet.

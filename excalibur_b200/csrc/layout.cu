@@ -142,6 +142,38 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc4_f16_quad_kernel(const float
     }
 }
 
+// The same from fp16 planes (an input converted to half precision on the host): 8-byte plane loads, pure
+// byte shuffles, the same 32-byte store.
+__global__ void __launch_bounds__(256) nchw_f16_to_nhwc4_f16_quad_kernel(const __half* __restrict__ x, __half* __restrict__ y,
+                                                                         int C, int H, int W, int w_pad, int w_pitch,
+                                                                         int64_t rows) {
+    const int quads = w_pitch >> 2;
+    const int64_t plane = (int64_t)H * W;
+    for (int64_t row = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; row < rows; row += (int64_t)gridDim.x * blockDim.y) {
+        const int64_t n = row / H;
+        const int h = (int)(row - n * H);
+        const __half* src = x + (n * C * H + h) * (int64_t)W;
+        for (int q = threadIdx.x; q < quads; q += blockDim.x) {
+            const int w = 4 * q - w_pad;
+            uint2 v[3];
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                v[c] = make_uint2(0u, 0u);
+                if (c < C && w >= 0 && w < W) v[c] = *reinterpret_cast<const uint2*>(src + c * plane + w);
+            }
+            // pixel j of the quad: halves (c0, c1, c2, 0); pixel 0/1 sit in .x, 2/3 in .y of each plane's load
+            uint32_t o[8];
+            o[0] = __byte_perm(v[0].x, v[1].x, 0x5410); o[1] = v[2].x & 0xffffu;
+            o[2] = __byte_perm(v[0].x, v[1].x, 0x7632); o[3] = v[2].x >> 16;
+            o[4] = __byte_perm(v[0].y, v[1].y, 0x5410); o[5] = v[2].y & 0xffffu;
+            o[6] = __byte_perm(v[0].y, v[1].y, 0x7632); o[7] = v[2].y >> 16;
+            uint4* dst = reinterpret_cast<uint4*>(y + (row * w_pitch + 4 * q) * 4);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+    }
+}
+
 // planar16 int8 [N][cs/16][HW][16] -> fp32 [N][C][HW]: a thread per (n, c, hw), reads of one channel
 // plane are 16-byte strided but each plane is small and read once.
 template <typename In>
@@ -266,6 +298,22 @@ extern "C" int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x, void* y
     else return fail(EXB_ERR_UNSUPPORTED, "padded ingest supports EXB_F16 and EXB_I8 output");
 #undef EXB_LAUNCH
     return after_launch("nchw_to_nhwc_padded_kernel");
+}
+
+extern "C" int exb_nchw_f16_to_nhwc4_padded(exb_ctx* ctx, const void* x, void* y, int N, int C, int H, int W, int w_pad,
+                                            int w_pitch, void* stream) {
+    if (int rc = check_dims(ctx, x, y, N, C, H, W, 4)) return rc;
+    EXB_REQUIRE(w_pad >= 0 && w_pitch >= W + w_pad, "bad row padding (w_pad %d, w_pitch %d, W %d)", w_pad, w_pitch, W);
+    if (C > 3 || (W & 3) || (w_pad & 3) || (w_pitch & 3))
+        return fail(EXB_ERR_UNSUPPORTED, "exb_nchw_f16_to_nhwc4_padded needs C <= 3 and W, w_pad, w_pitch multiples of 4");
+    if (N == 0) return EXB_OK;
+    EXB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 7u) == 0 && aligned16(y), "exb_nchw_f16_to_nhwc4_padded: misaligned buffer");
+    const int64_t rows = (int64_t)N * H;
+    const dim3 block(64, 4);
+    const int grid = (int)std::min<int64_t>((rows + 3) / 4, (int64_t)ctx->sm_count * 32);
+    nchw_f16_to_nhwc4_f16_quad_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<__half*>(y), C, H, W, w_pad, w_pitch, rows);
+    return after_launch("nchw_f16_to_nhwc4_f16_quad_kernel");
 }
 
 namespace exb {

@@ -14,7 +14,7 @@ HOST_SYMBOLS = [
     "exb_host_pipeline_set_option", "exb_host_pipeline_forward", "exb_host_pipeline_num_outputs",
     "exb_host_pipeline_output_name", "exb_host_pipeline_get", "exb_host_pipeline_output_ptr", "exb_host_pipeline_stats",
     "exb_host_pipeline_dump_profile", "exb_host_pipeline_run_resident", "exb_host_pipeline_trace_size",
-    "exb_host_pipeline_trace_entry", "exb_host_op_run",
+    "exb_host_pipeline_trace_entry", "exb_host_op_run", "exb_host_convert_f32_to_f16",
 ]
 _READY = False
 
@@ -48,6 +48,7 @@ def lib():
                                                     C.POINTER(C.c_double)]
         L.exb_host_op_run.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, i32, i32, C.POINTER(vp), vp, vp,
                                       C.c_int64, vp]
+        L.exb_host_convert_f32_to_f16.argtypes = [vp, vp, C.c_int64, i32, i32]
         _READY = True
     return L
 
@@ -179,3 +180,12 @@ def run_op(type_, params, inputs, racy_bytes=None, device=0):
     finally:
         if tmp is not None:
             os.unlink(tmp.name)
+
+
+def convert_f32_to_f16(x, threads=1, force_scalar=False):
+    """The host-side conversion the "host_f16_threads" option uses; returns a float16 array.  No GPU needed."""
+    src = np.ascontiguousarray(x, np.float32)
+    dst = np.empty(src.shape, np.float16)
+    _check(lib().exb_host_convert_f32_to_f16(src.ctypes.data_as(C.c_void_p), dst.ctypes.data_as(C.c_void_p),
+                                             C.c_int64(src.size), int(threads), int(bool(force_scalar))))
+    return dst

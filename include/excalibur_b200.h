@@ -103,6 +103,11 @@ EXB_API int exb_nchw_f32_to_nhwc(exb_ctx* ctx, const float* x_nchw, void* y_nhwc
 EXB_API int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x_nchw, void* y_nhwc, int dtype,
                                         int N, int C, int H, int W, int c_stride, int w_pad,
                                         int w_pitch, float scale, int rounding, void* stream);
+/* The same for an image that is already fp16 NCHW (converted on the host so that half the bytes cross
+ * PCIe; same round-to-nearest-even as the fp32 entry, so the results are identical): c_stride 4, fp16
+ * output, C <= 3, W / w_pad / w_pitch multiples of 4. */
+EXB_API int exb_nchw_f16_to_nhwc4_padded(exb_ctx* ctx, const void* x_nchw_f16, void* y_nhwc, int N, int C, int H,
+                                         int W, int w_pad, int w_pitch, void* stream);
 /* planar16 [N][c_stride/16][H][W][16] (EXB_I8 or EXB_F16) -> fp32 NCHW, y = x * scale (inspection
  * of planar maps, global pooling input). */
 EXB_API int exb_planar16_i8_to_nchw_f32(exb_ctx* ctx, const int8_t* x, float* y, int N, int C, int H, int W,

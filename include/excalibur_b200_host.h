@@ -38,8 +38,13 @@ EXB_API int exb_host_pipeline_create(const char* phai_text, const char* racy_pat
                                      void** out);
 EXB_API int exb_host_pipeline_destroy(void* p);
 /* key: "fusion" (fused NHWC plan, default 1), "cuda_graph" (default 1), "profile" (0/1 =
- * disable_profiler / enable_profiler, reference pipeline.hpp:38-39). */
+ * disable_profiler / enable_profiler, reference pipeline.hpp:38-39), "h2d_chunks" (k sub-batches whose
+ * copies overlap the previous sub-batch's kernels, default 1), "host_f16_threads" (t > 0: the input is
+ * converted to fp16 by t host threads before the copy - half the PCIe bytes, identical results; default 0). */
 EXB_API int exb_host_pipeline_set_option(void* p, const char* key, int value);
+/* The host-side fp32 -> fp16 conversion "host_f16_threads" uses (round to nearest even; F16C where the CPU
+ * has it, bit-level otherwise or when force_scalar != 0).  Needs no GPU. */
+EXB_API int exb_host_convert_f32_to_f16(const float* src, uint16_t* dst, int64_t n, int threads, int force_scalar);
 /* forward(): `input` is HOST memory, fp32 NCHW; it is wrapped, not copied (page-locked memory
  * makes the upload asynchronous).  The call returns when the outputs are back on the host. */
 EXB_API int exb_host_pipeline_forward(void* p, const float* input, int N, int C, int H, int W);

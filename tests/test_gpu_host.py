@@ -273,6 +273,14 @@ def test_chunked_forward_equals_whole_batch_forward():
             out = p.forward(x)["logits"]
         assert out.shape == whole.shape
         np.testing.assert_array_equal(out, whole)
+    # the input converted to fp16 by host threads before the copy: the same rounding as the device ingest kernel
+    for k, t in ((1, 1), (2, 3), (4, 8)):
+        p.set_option("h2d_chunks", k)
+        p.set_option("host_f16_threads", t)
+        for _ in range(3):
+            out = p.forward(x)["logits"]
+        np.testing.assert_array_equal(out, whole)
+    p.set_option("host_f16_threads", 0)
     p.set_option("h2d_chunks", 3)       # 8 is not divisible by 3: falls back to the whole batch
     np.testing.assert_array_equal(p.forward(x)["logits"], whole)
     p.set_option("h2d_chunks", 1)

@@ -63,3 +63,26 @@ def test_calibrate_reader_walks_every_weight_record():
         for op in ops:
             pos += calibrate.racy_record_size(op, blob, pos)
         assert pos == len(blob)
+
+
+def test_host_f32_to_f16_conversion_rounds_to_nearest_even():
+    """The conversion the host_f16_threads option runs before the copy: F16C, bit-level and pooled variants all
+    equal numpy's round-to-nearest-even (which is also the device's __float2half_rn)."""
+    from excalibur_b200 import host
+    r = np.random.default_rng(3)
+    x = np.concatenate([
+        r.standard_normal(100003).astype(np.float32),
+        (r.standard_normal(50000) * 1e-6).astype(np.float32),         # half subnormals and underflow
+        (r.standard_normal(50000) * 3e4).astype(np.float32),          # around the overflow threshold
+        np.array([0.0, -0.0, 65504.0, 65519.99, 65520.0, 65536.0, 1e9, -1e9, np.inf, -np.inf, 2.0 ** -24, 2.0 ** -25,
+                  1.5 * 2.0 ** -25, 2.0 ** -14, 2.0 ** -14 - 2.0 ** -26, 1.0 + 2.0 ** -11, 1.0 + 3 * 2.0 ** -11,
+                  0.1, 255.0, 1e-8], np.float32),
+    ])
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16)
+    for threads, scalar in ((1, False), (1, True), (5, False)):
+        got = host.convert_f32_to_f16(x, threads, scalar)
+        np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16), err_msg="threads %d scalar %s" % (threads, scalar))
+    nan = host.convert_f32_to_f16(np.array([np.nan], np.float32), 1, True)
+    assert np.isnan(nan[0])
+    assert host.convert_f32_to_f16(np.zeros((0,), np.float32)).size == 0
