@@ -278,6 +278,28 @@ __global__ void __launch_bounds__(256) transpose_planes_f32_kernel(const float* 
         if (w0 + r < W && h0 + tx < H) yp[(int64_t)(w0 + r) * H + h0 + tx] = tile[tx][r];
 }
 
+
+__device__ __forceinline__ float bin_apply(int op, float a, float b) {
+    return op == 0 ? a + b : (op == 1 ? a - b : (op == 2 ? a * b : a / b));
+}
+
+// y[n][c][p] = a[n][c][p] op b[n % b_batch][c]: a per-channel value of every image applied to a whole map
+// (squeeze-and-excitation gates).  Indexing as channel_affine_kernel; padding channels are written 0.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) binary_bcast_kernel(const T* a, const T* b, T* y, int64_t count, int C, int cs,
+                                                                int64_t inner, int channel_last, int op, int b_batch) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    const int64_t per_image = channel_last ? inner * cs : inner * C;
+    const int bcs = channel_last ? cs : C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += step) {
+        const int c = channel_last ? (int)(i % cs) : (int)((i / inner) % C);
+        const int64_t n = i / per_image;
+        float v = 0.f;
+        if (c < C) v = bin_apply(op, ld1(a + i), ld1(b + (n % b_batch) * bcs + c));
+        st1(y + i, v);
+    }
+}
+
 }  // namespace
 }  // namespace exb
 
@@ -526,4 +548,28 @@ extern "C" int exb_transpose_hw_f32(exb_ctx* ctx, const float* x, float* y, int6
         transpose_planes_f32_kernel<<<grid, 256, 0, st>>>(x + p0 * (int64_t)H * W, y + p0 * (int64_t)H * W, H, W);
     }
     return after_launch("exb_transpose_hw_f32");
+}
+
+extern "C" int exb_binaryop_channel_bcast_fwd(exb_ctx* ctx, int op, const void* a, const void* b, void* y, int N, int b_batch,
+                                              int C, int c_stride, int64_t inner, int dtype, int channel_last, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(N >= 0 && C > 0 && inner > 0, "exb_binaryop_channel_bcast_fwd: bad shape");
+    EXB_REQUIRE(b_batch == N || b_batch == 1, "exb_binaryop_channel_bcast_fwd: %d gate images for a batch of %d", b_batch, N);
+    if (op < 0 || op > 3) return fail(EXB_ERR_UNSUPPORTED, "binary op type %d", op);
+    if (dtype != EXB_F16 && dtype != EXB_F32)
+        return fail(EXB_ERR_UNSUPPORTED, "exb_binaryop_channel_bcast_fwd supports EXB_F16 and EXB_F32, got dtype %d", dtype);
+    const int cs = channel_last ? (c_stride ? c_stride : C) : C;
+    EXB_REQUIRE(cs >= C, "exb_binaryop_channel_bcast_fwd: channel stride smaller than channel count");
+    const int64_t count = (int64_t)N * inner * cs;
+    if (count == 0) return EXB_OK;
+    EXB_REQUIRE(a && b && y, "exb_binaryop_channel_bcast_fwd: null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = stream_grid(ctx, count, kThreads);
+    if (dtype == EXB_F16)
+        binary_bcast_kernel<__half><<<grid, kThreads, 0, st>>>(static_cast<const __half*>(a), static_cast<const __half*>(b),
+                                                               static_cast<__half*>(y), count, C, cs, inner, channel_last, op, b_batch);
+    else
+        binary_bcast_kernel<float><<<grid, kThreads, 0, st>>>(static_cast<const float*>(a), static_cast<const float*>(b),
+                                                              static_cast<float*>(y), count, C, cs, inner, channel_last, op, b_batch);
+    return after_launch("exb_binaryop_channel_bcast_fwd");
 }

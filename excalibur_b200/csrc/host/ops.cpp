@@ -612,8 +612,22 @@ static void binaryop_run(exb_ctx* h, int op, int with_scalar, float coef, const 
         return;
     }
     CHECK_GE(bottoms.size(), (size_t)2);
-    if (bottoms[0]->data_shape() != bottoms[1]->data_shape())
-        NOT_IMPLEMENTED << " (broadcasting binary op: only equal shapes are on the hot path)";
+    if (bottoms[0]->data_shape() != bottoms[1]->data_shape()) {
+        // (N,C,H,W) with (N or 1,C,1,1): the per-channel gate of a squeeze-and-excitation block.  As in the
+        // reference the larger operand comes first in the operation, whatever the order of the bottoms.
+        const bool first_big = bottoms[0]->count() >= bottoms[1]->count();
+        const auto& big = bottoms[first_big ? 0 : 1];
+        const auto& small = bottoms[first_big ? 1 : 0];
+        const bool gate = big->order() == memory::NCHW && small->channels() == big->channels() && small->height() == 1 &&
+                          small->width() == 1 && (small->num() == big->num() || small->num() == 1);
+        if (!gate) NOT_IMPLEMENTED << " (broadcasting binary op other than (N,C,H,W) with (N,C,1,1))";
+        tops[0] = make_tensor<T>(big->data_shape(), big->device(), big->order(), big->allocator());
+        exb_check(exb_binaryop_channel_bcast_fwd(h, op, big->gpu_data(), small->gpu_data(), tops[0]->mutable_gpu_data(),
+                                                 big->num(), small->num(), big->channels(), 0,
+                                                 (int64_t)big->height() * big->width(), dtype, 0, nullptr),
+                  "exb_binaryop_channel_bcast_fwd");
+        return;
+    }
     exb_check(exb_binaryop_fwd(h, op, bottoms[0]->gpu_data(), bottoms[1]->gpu_data(), tops[0]->mutable_gpu_data(),
                                tops[0]->count(), dtype, nullptr),
               "exb_binaryop_fwd");

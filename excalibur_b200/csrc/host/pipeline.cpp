@@ -36,6 +36,21 @@ struct trace_event {
     float begin_ms, end_ms;
 };
 
+// What the fused plan throws while it is built when the graph needs something only the op-by-op executor
+// can do (or nothing can): forward() then runs op by op, where an unimplemented case fails with its own message.
+struct plan_refusal : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+class refuse_line {
+public:
+    ~refuse_line() noexcept(false) { throw plan_refusal(os_.str()); }
+    std::ostringstream& stream() { return os_; }
+
+private:
+    std::ostringstream os_;
+};
+#define PLAN_REFUSE refuse_line().stream()
+
 // ------------------------------------------------------------------------------------------
 // Fused plan (float pipelines on a GPU)
 // ------------------------------------------------------------------------------------------
@@ -583,7 +598,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         fmap_info& y = fmaps_[g.out];
         CHECK(x.produced) << "feature map " << x.name << " is consumed before it is produced";
         if (x.f32_only)
-            NOT_IMPLEMENTED << " (fused plan: " << params_[i].name_ << " reads the result of a Reshape / Transpose; call set_fusion(false))";
+            PLAN_REFUSE << "(fused plan: " << params_[i].name_ << " reads the result of a Reshape / Transpose; call set_fusion(false))";
         if (t == "convolutiondepthwise") {
             auto* dw = dynamic_cast<operation_convolutiondepthwise<float>*>(ops_[i].get());
             CHECK_EQ(dw->output_channel_, dw->group_);
@@ -614,7 +629,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         if (t == "deconvolution") {
             auto* dc = dynamic_cast<operation_deconvolution<float>*>(ops_[i].get());
             if (!dc->supported())
-                NOT_IMPLEMENTED << " (Deconvolution " << params_[i].name_
+                PLAN_REFUSE << "(Deconvolution " << params_[i].name_
                                 << ": implemented for kernel == stride, no padding, no dilation, one group)";
             CHECK_EQ(x.C, dc->in_channels()) << params_[i].name_ << ": input channels do not match the weights";
             const int rh = dc->kernel_size_h_, rw = dc->kernel_size_w_, Cout = dc->output_channel_;
@@ -713,6 +728,22 @@ void fused_plan::build(int N, int C, int H, int W) {
         fmap_info& x = fmaps_[root(in_ids[i][0])];
         fmap_info& y = fmaps_[root(out_ids[i][0])];
         CHECK(x.produced) << "feature map " << x.name << " is consumed before it is produced";
+        if (t == "reshape" && !x.f32_only && !x.need_f32 &&
+            dynamic_cast<operation_reshape<float>*>(ops_[i].get())->out_shape({x.N, x.C, x.H, x.W}) ==
+                std::vector<int>{x.N, x.C, x.H, x.W}) {
+            // a Reshape that changes nothing (the (N,C,1,1) vectors around the InnerProducts of a gate): a copy
+            y.need_f16 = true;
+            set_shape(y, x.N, x.C, x.H, x.W);
+            y.cs = x.cs;
+            const void* src = form_f16(x);
+            void* dst = form_f16(y);
+            const size_t bytes = (size_t)x.N * x.H * x.W * x.cs * 2;
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st));
+            });
+            finish_forms(y, false);
+            continue;
+        }
         if (t == "reshape" || t == "transpose") {
             // Shape surgery is defined on NCHW data: it runs on the fp32 NCHW copy of the tensor, and what it
             // produces exists in that form only (the graph's tail: detection heads).
@@ -735,7 +766,7 @@ void fused_plan::build(int N, int C, int H, int W) {
                 y.N = x.N; y.C = x.C; y.H = x.H; y.W = x.W; y.cs = y.C;
                 y.f32 = x.f32;
             } else {
-                if (!tr->is_swap_hw()) NOT_IMPLEMENTED << " (Transpose is implemented for the permutations 0,1,2 and 1,0,2)";
+                if (!tr->is_swap_hw()) PLAN_REFUSE << "(Transpose is implemented for the permutations 0,1,2 and 1,0,2)";
                 y.N = x.N; y.C = x.C; y.H = x.W; y.W = x.H; y.cs = y.C;
                 float* dst = static_cast<float*>(form_f32(y));
                 const int64_t planes = (int64_t)x.N * x.C;
@@ -748,7 +779,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         }
         for (int f : in_ids[i])
             if (fmaps_[root(f)].f32_only)
-                NOT_IMPLEMENTED << " (fused plan: " << params_[i].type_ << " " << params_[i].name_
+                PLAN_REFUSE << "(fused plan: " << params_[i].type_ << " " << params_[i].name_
                                 << " reads the result of a Reshape / Transpose; call set_fusion(false))";
         if (t == "pooling") {
             auto* pool = dynamic_cast<operation_pooling<float>*>(ops_[i].get());
@@ -773,9 +804,25 @@ void fused_plan::build(int N, int C, int H, int W) {
             finish_forms(y, fuse_q);
         } else if (t == "innerproduct") {
             auto* fc = dynamic_cast<operation_innerproduct<float>*>(ops_[i].get());
-            if (x.H != 1 || x.W != 1) NOT_IMPLEMENTED << " (fused InnerProduct needs a 1x1 input map; call set_fusion(false))";
+            if (x.H != 1 || x.W != 1) PLAN_REFUSE << "(fused InnerProduct needs a 1x1 input map; call set_fusion(false))";
             CHECK_EQ(x.C, fc->in_features());
             exb_conv_desc d = fc->fc_desc(x.N, x.cs);
+            const int fy = root(out_ids[i][0]);
+            if (!output_roots.count(fy)) {
+                // feeds other operations (the bottleneck of a gate): an fp16 (N,C,1,1) map like any other
+                y.need_f16 = true;
+                set_shape(y, x.N, fc->num_output_, 1, 1);
+                d.out_dtype = EXB_F16;
+                d.cout_stride = y.cs;
+                const void* xin = form_f16(x);
+                void* yo = form_f16(y);
+                exb_conv_weights* w = fc->packed(ctx, d);
+                add_step(params_[i].name_, [=](cudaStream_t st) {
+                    exb_check(exb_conv2d_fwd(ctx, &d, xin, w, nullptr, yo, nullptr, st), "exb_conv2d_fwd");
+                });
+                finish_forms(y, false);
+                continue;
+            }
             y.N = x.N; y.C = fc->num_output_; y.H = 1; y.W = 1; y.cs = y.C;
             y.need_f32 = true;
             // rows padded to 16 floats so the conv epilogue keeps its vector stores; the pad is dropped by the
@@ -790,10 +837,10 @@ void fused_plan::build(int N, int C, int H, int W) {
             });
             y.produced = true;
             if (!output_roots.count(root(out_ids[i][0])) || consumers[root(out_ids[i][0])].size())
-                NOT_IMPLEMENTED << " (fused plan: InnerProduct must be a pipeline output)";
+                PLAN_REFUSE << "(fused plan: InnerProduct must be a pipeline output)";
         } else if (t == "concat") {
             auto* cc = dynamic_cast<operation_concat<float>*>(ops_[i].get());
-            if (!cc->is_channel_concat()) NOT_IMPLEMENTED << " (Concat is implemented along the channel axis, key 0=-1)";
+            if (!cc->is_channel_concat()) PLAN_REFUSE << "(Concat is implemented along the channel axis, key 0=-1)";
             auto xs = std::make_shared<std::vector<const void*>>();
             auto widths = std::make_shared<std::vector<int64_t>>();
             auto strides = std::make_shared<std::vector<int64_t>>();
@@ -820,9 +867,9 @@ void fused_plan::build(int N, int C, int H, int W) {
             finish_forms(y, false);
         } else if (t == "interp") {
             auto* ip = dynamic_cast<operation_interp<float>*>(ops_[i].get());
-            if (in_ids[i].size() != 1) NOT_IMPLEMENTED << " (Interp with a size tensor as second input)";
+            if (in_ids[i].size() != 1) PLAN_REFUSE << "(Interp with a size tensor as second input)";
             if (ip->resize_type_ != 1 || ip->align_corner_ != 0)
-                NOT_IMPLEMENTED << " (Interp is implemented for nearest mode, keys 0=1 6=0)";
+                PLAN_REFUSE << "(Interp is implemented for nearest mode, keys 0=1 6=0)";
             int OH = 0, OW = 0;
             ip->out_dims(x.H, x.W, &OH, &OW);
             y.need_f16 = true;
@@ -906,6 +953,29 @@ void fused_plan::build(int N, int C, int H, int W) {
                               "exb_channel_affine_fwd");
             });
             finish_forms(*yy, false);
+        } else if (t == "binaryop" && in_ids[i].size() == 2 &&
+                   !dynamic_cast<operation_binaryop<float>*>(ops_[i].get())->with_scalar_ &&
+                   (fmaps_[root(in_ids[i][1])].H != x.H || fmaps_[root(in_ids[i][1])].W != x.W)) {
+            // (N,C,H,W) with (N,C,1,1): a per-channel gate; the larger operand comes first in the operation
+            fmap_info& o = fmaps_[root(in_ids[i][1])];
+            fmap_info& big = (int64_t)x.H * x.W >= (int64_t)o.H * o.W ? x : o;
+            fmap_info& sm = &big == &x ? o : x;
+            if (!(sm.produced && big.produced && sm.H == 1 && sm.W == 1 && sm.C == big.C && sm.N == big.N && sm.cs == big.cs && !sm.f32_only))
+                PLAN_REFUSE << "BinaryOp " << params_[i].name_ << ": operands differ in shape";
+            y.need_f16 = true;
+            set_shape(y, big.N, big.C, big.H, big.W);
+            y.cs = big.cs;
+            const void* a = form_f16(big);
+            const void* g8 = form_f16(sm);
+            void* yo = form_f16(y);
+            const int op = dynamic_cast<operation_binaryop<float>*>(ops_[i].get())->op_type_;
+            const int n = big.N, c = big.C, cs = big.cs;
+            const int64_t inner = (int64_t)big.H * big.W;
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_binaryop_channel_bcast_fwd(ctx, op, a, g8, yo, n, n, c, cs, inner, EXB_F16, 1, st),
+                          "exb_binaryop_channel_bcast_fwd");
+            });
+            finish_forms(y, false);
         } else {
             // element-wise ops on the fp16 form
             y.need_f16 = true;
@@ -939,7 +1009,7 @@ void fused_plan::build(int N, int C, int H, int W) {
                 });
             } else if (t == "relu" || t == "clip" || t == "sigmoid" || t == "hardswish") {
                 const int act = act_of_op((int)i);
-                if (act < 0) NOT_IMPLEMENTED << " (" << params_[i].type_ << " parameters)";
+                if (act < 0) PLAN_REFUSE << "(" << params_[i].type_ << " parameters)";
                 const void* xin = form_f16(x);
                 add_step(params_[i].name_, [=](cudaStream_t st) {
                     exb_check(exb_activation_fwd(ctx, act, xin, yo, count, EXB_F16, st), "exb_activation_fwd");
@@ -955,7 +1025,7 @@ void fused_plan::build(int N, int C, int H, int W) {
                     });
                 } else {
                     fmap_info& x2 = fmaps_[root(in_ids[i][1])];
-                    CHECK(x2.produced && x2.N == x.N && x2.C == x.C && x2.H == x.H && x2.W == x.W) << "BinaryOp operands differ in shape";
+                    if (!(x2.produced && x2.N == x.N && x2.C == x.C && x2.H == x.H && x2.W == x.W)) PLAN_REFUSE << "BinaryOp " << params_[i].name_ << ": operands differ in shape";
                     const void* bb = form_f16(x2);
                     add_step(params_[i].name_, [=](cudaStream_t st) {
                         exb_check(exb_binaryop_fwd(ctx, op, a, bb, yo, count, EXB_F16, st), "exb_binaryop_fwd");
@@ -1315,6 +1385,7 @@ public:
     bool used_fused_ = false;
     int h2d_chunks_ = 1;
     int host_f16_threads_ = 0;
+    std::string plan_refused_;      // why this graph's fused plan could not be built (then: op by op for good)
     bool used_chunked_ = false;
     std::unique_ptr<fused_plan> chunk_plan_;
     exb_ctx* ctx_ = nullptr;
@@ -1394,8 +1465,8 @@ pipeline<float>::result_map pipeline<float>::impl::forward_gpu(const std::shared
     CHECK(input != nullptr && !input->empty()) << "empty input tensor";
     if (fusion_) {
         if (!plan_) plan_.reset(new fused_plan(op_params_, operations_, input_names_, output_names_, device_));
-        const std::string why = plan_->unsupported_reason();
-        if (why.empty()) {
+        std::string why = plan_refused_.empty() ? plan_->unsupported_reason() : plan_refused_;
+        if (why.empty()) try {
             if (input->order() == memory::NHWC) input->convert_order();
             const int N = input->num(), C = input->channels(), H = input->height(), W = input->width();
             used_chunked_ = false;
@@ -1417,6 +1488,12 @@ pipeline<float>::result_map pipeline<float>::impl::forward_gpu(const std::shared
             device_ms_ = plan_->device_ms();
             used_fused_ = true;
             return plan_->host_out_;
+        } catch (const plan_refusal& e) {
+            // nothing has run yet: the refusal comes from building the plan
+            plan_refused_ = e.what();
+            why = plan_refused_;
+            plan_.reset();
+            chunk_plan_.reset();
         }
         LOG(WARNING) << "running op by op: " << why;
     }

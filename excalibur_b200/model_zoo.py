@@ -351,7 +351,7 @@ _CONV_TYPES = ("convolution", "convolutiondepthwise", "deconvolution")
 
 def _canon_params(type_, params):
     def nums(v):
-        return tuple(round(float(t), 5) for t in v.split(",") if t != "")
+        return tuple(round(float(t), 6) for t in v.split(",") if t != "")
     p = {int(k): nums(v) for k, v in params.items()}
     p.pop(-23330, None)
     if type_ in _CONV_TYPES:
@@ -364,11 +364,11 @@ def _canon_params(type_, params):
         one = lambda k, d: p.get(k, (float(d),))[0]
         kw, sw, pl = one(1, 0), one(2, 1), one(3, 0)
         return {"type": one(0, 0), "kw": kw, "kh": one(11, kw), "sw": sw, "sh": one(12, sw), "pl": pl, "pr": one(14, pl),
-                "pt": one(13, pl), "pb": one(15, pl), "global": one(4, 0), "pad_mode": one(5, 0), "count_include_pad": one(6, -1)}
+                "pt": one(13, pl), "pb": one(15, pl), "global": one(4, 0), "pad_mode": one(5, 1), "count_include_pad": one(6, 0)}
     if type_ == "batchnorm":
         p.setdefault(1, (0.0,))
     if type_ == "input":
-        p.pop(0, None)      # nominal width / height
+        p.pop(0, None)      # nominal width / height: not part of the architecture
         p.pop(1, None)
     if type_ == "eltwise" and p.get(-23301) == (0.0,):
         p.pop(-23301)
@@ -397,3 +397,130 @@ def structure(phai_text):
             where[o] = (idx, k)
         out.append((t, _canon_params(t, op["params"]), ins))
     return out
+
+
+# ---- a graph with seeded weights from a canonical structure ------------------------------------------
+_CONV_KEYS = (("cout", 0), ("kw", 1), ("kh", 11), ("dw", 2), ("dh", 12), ("sw", 3), ("sh", 13), ("pl", 4), ("pt", 14),
+              ("pr", 15), ("pb", 16), ("bias", 5), ("wsize", 6), ("group", 7), ("act", 9))
+_POOL_KEYS = (("type", 0), ("kw", 1), ("kh", 11), ("sw", 2), ("sh", 12), ("pl", 3), ("pt", 13), ("pr", 14), ("pb", 15),
+              ("global", 4), ("pad_mode", 5), ("count_include_pad", 6))
+_TYPE_NAMES = {"convolution": "Convolution", "convolutiondepthwise": "ConvolutionDepthWise", "deconvolution": "Deconvolution",
+               "pooling": "Pooling", "innerproduct": "InnerProduct", "batchnorm": "BatchNorm", "prelu": "PReLU",
+               "leakyrelu": "LeakyRelu", "relu": "ReLU", "eltwise": "Eltwise", "binaryop": "BinaryOp", "input": "Input",
+               "concat": "Concat", "interp": "Interp", "sigmoid": "Sigmoid", "hardswish": "HardSwish", "clip": "Clip",
+               "reshape": "Reshape", "transpose": "Transpose", "yolov5focus": "YoloV5Focus"}
+
+
+def _num(v):
+    return repr(int(v)) if float(v) == int(v) else repr(float(v))
+
+
+def graph_from_structure(struct, seed=21, name="net", gain=1.6):
+    """GraphBuilder with the operation sequence of `struct` (the output of structure(), or its JSON round trip)
+    and seeded weights: Kaiming-normal convolutions, near-identity BatchNorm statistics, PReLU slopes in
+    [0.05, 0.3].  Feature maps are named t<op index>; a Split is inserted wherever a map has several readers.
+    int8 flags are dropped (the graph is the floating-point one).  `gain` scales the convolution weights'
+    variance (2 keeps the signal level through ReLU layers; residual and gated architectures need less).
+    Returns (GraphBuilder, output names)."""
+    g = GraphBuilder(name)
+    net = _Net(g)
+    init = _Init(seed)
+    names = {}
+    consumed = set()
+    for idx, (t, prm, ins) in enumerate(struct):
+        t = str(t)
+        prm = {(int(k) if str(k).lstrip("-").isdigit() else str(k)): v for k, v in dict(prm).items()}
+        srcs = ["data" if int(pi) < 0 else names[int(pi)] for pi, _ in ins]
+        consumed.update(srcs)
+        out = "t%d" % idx
+        names[idx] = out
+        opname = "%s_%d" % (t, idx)
+        tname = _TYPE_NAMES[t]
+        if t in _CONV_TYPES:
+            text = " ".join("%d=%s" % (k, _num(prm[key])) for key, k in _CONV_KEYS)
+            cout, kh, kw, group = int(prm["cout"]), int(prm["kh"]), int(prm["kw"]), int(prm["group"])
+            wsize = int(prm["wsize"])
+            per = wsize // (cout * kh * kw // group * group) * group if t != "convolutiondepthwise" else 1
+            cin_g = wsize // (cout * kh * kw)
+            if t == "deconvolution":
+                w, b = init.deconv(wsize // (cout * kh * kw), cout, kh) if kh == kw else (None, None)
+            else:
+                w, b = init.conv(cout, cin_g, kh, kw, gain=gain)
+            bias = b if int(prm["bias"]) else None
+
+            def emit(ins_, out_, tname=tname, opname=opname, text=text, w=w, bias=bias):
+                g._conv_weights(w, bias, None)
+                g._op(tname, opname, ins_, [out_], text)
+        elif t == "pooling":
+            text = " ".join("%d=%s" % (k, _num(prm[key])) for key, k in _POOL_KEYS)
+
+            def emit(ins_, out_, opname=opname, text=text):
+                g._op("Pooling", opname, ins_, [out_], text)
+        elif t == "innerproduct":
+            nout, wsize = int(prm[0][0]), int(prm[2][0])
+            r = init._r()
+            w = (r.standard_normal((nout, wsize // nout)) * np.sqrt(1.0 / (wsize // nout))).astype(np.float32)
+            bias = (r.standard_normal(nout) * 0.05).astype(np.float32) if int(prm.get(1, (0,))[0]) else None
+
+            def emit(ins_, out_, opname=opname, w=w, bias=bias):
+                g.innerproduct(opname, ins_[0], out_, w, bias)
+        elif t == "batchnorm":
+            bn = init.bn(int(prm[0][0]))
+            eps = float(prm.get(1, (0.0,))[0])
+
+            def emit(ins_, out_, opname=opname, bn=bn, eps=eps):
+                g.batchnorm(opname, ins_[0], out_, *bn, eps=eps)
+        elif t == "prelu":
+            sl = init.slopes(int(prm[0][0]))
+
+            def emit(ins_, out_, opname=opname, sl=sl):
+                g.prelu(opname, ins_[0], out_, sl)
+        else:
+            text = " ".join("%d=%s" % (k, ",".join(_num(x) for x in v)) for k, v in prm.items())
+            if t == "input":
+                text = "0=%d 1=%d %s" % (int(prm.get("w", 0)), int(prm.get("h", 0)),
+                                         " ".join("%d=%s" % (k, ",".join(_num(x) for x in v)) for k, v in prm.items()
+                                                  if not isinstance(k, str)))
+
+            def emit(ins_, out_, tname=tname, opname=opname, text=text):
+                g._op(tname, opname, ins_, [out_], text)
+        net.add(emit, srcs, out)
+    net.emit()
+    outs = [n for i, n in names.items() if n not in consumed]
+    return g, outs
+
+
+def architecture_input(arch, batch=1):
+    """The seeded image batch (values 0..255) for one entry of the shipped-architecture fixture list."""
+    h, w = arch["input_hw"]
+    return np.random.default_rng(arch["seed"] + 1000).uniform(0, 255, (batch, 3, h, w)).astype(np.float32)
+
+
+def sample(a, limit=8192):
+    """Every k-th value of a flattened array, at most `limit` values (what the fixture keeps of a large map)."""
+    flat = np.ascontiguousarray(a, np.float32).reshape(-1)
+    step = max(1, -(-flat.size // limit))
+    return flat[::step].copy()
+
+
+def unsupported_types(phai_text):
+    """Operation types of a description that this library has no implementation for (empty = every operation of
+    the file can be created; shape-dependent refusals, e.g. a transposed convolution with overlapping taps,
+    only show when the graph is built).  Needs no GPU."""
+    from . import host
+    from .calibrate import parse_phai
+    _, ops = parse_phai(phai_text)
+    return sorted({op["type"] for op in ops if not host.registered("operation_" + op["type"].lower())})
+
+
+def main(argv=None):
+    """python -m excalibur_b200.model_zoo file.phai ...: which operation types of each description are missing."""
+    import sys
+    for path in (argv if argv is not None else sys.argv[1:]):
+        with open(path) as f:
+            missing = unsupported_types(f.read())
+        print("%-70s %s" % (path, "all operation types implemented" if not missing else "missing: " + ", ".join(missing)))
+
+
+if __name__ == "__main__":
+    main()

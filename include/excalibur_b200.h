@@ -375,6 +375,14 @@ EXB_API int exb_nchw_f32_focus_to_nhwc_f16(exb_ctx* ctx, const float* x, void* y
  * (EXB_F16, EXB_I8 or EXB_F32; padding channels of the output are written as 0). */
 EXB_API int exb_focus_fwd(exb_ctx* ctx, const void* x, void* y, int N, int C, int H, int W, int in_stride,
                           int out_stride, int dtype, int channel_last, void* stream);
+/* y[n][c][p] = a[n][c][p] op b[n % b_batch][c] (op as exb_binaryop_fwd): operation_binaryop with a
+ * (N,C,H,W) and a (N,C,1,1) operand (src/Excalibur/operation_binaryop.cpp:168-190; the reference always
+ * computes op(larger operand, smaller operand) whatever their order, and so does the host operation that
+ * calls this).  a and y: [N][inner][c_stride] channel-last or [N][C][inner] planar; b: [b_batch][c_stride]
+ * or [b_batch][C]; b_batch is N or 1.  EXB_F16 or EXB_F32; y may alias a. */
+EXB_API int exb_binaryop_channel_bcast_fwd(exb_ctx* ctx, int op, const void* a, const void* b, void* y, int N,
+                                           int b_batch, int C, int c_stride, int64_t inner, int dtype,
+                                           int channel_last, void* stream);
 /* y = prelu(x * mul[c] + add[c], slope): a BatchNorm followed by a PReLU / LeakyRelu in one pass (the
  * BottleneckCSP tail of the shipped YOLOv5s description).  Arguments as exb_channel_affine_fwd and exb_prelu_fwd. */
 EXB_API int exb_channel_affine_prelu_fwd(exb_ctx* ctx, const void* x, void* y, const float* mul, const float* add,

@@ -7,10 +7,13 @@ Run in a container that has the reference tree (it cannot travel to the GPU box)
     python tests/golden/make_golden.py mobilenet   # tests/golden/mobilenet_vectors.npz only
     python tests/golden/make_golden.py yolo        # tests/golden/yolo_vectors.npz only
     python tests/golden/make_golden.py shipped     # tests/golden/shipped_model_vectors.npz only
+    python tests/golden/make_golden.py architectures   # tests/golden/shipped_architectures.{json,npz} only
 
 Every case stores its inputs, weights and the reference's output, so the fixture pins the oracle
 (oracle/exb_oracle.c) and, through it, the CUDA kernels, without the reference being present.
 """
+import glob
+import json
 import os
 import sys
 
@@ -136,6 +139,7 @@ def main():
     mobilenet()
     yolo()
     shipped()
+    architectures()
 
 
 def shipped():
@@ -332,6 +336,92 @@ def mobilenet():
     print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
 
 
+REF_MODELS = "/root/reference/models"
+
+
+def architectures():
+    """Every shipped floating-point description whose operation types are all implemented: its name-free
+    canonical structure (model_zoo.structure) -> tests/golden/shipped_architectures.json, and the reference's
+    outputs for the graph model_zoo.graph_from_structure rebuilds from it (seeded weights, seeded input) ->
+    tests/golden/shipped_architectures.npz (outputs and four inner maps, sampled down to 8192 values each).
+    Descriptions with identical structures are listed once."""
+    from excalibur_b200.calibrate import parse_phai
+    archs, out, seen = [], {}, []
+    for path in sorted(glob.glob(os.path.join(REF_MODELS, "*.phai"))):
+        text = open(path).read()
+        name = os.path.basename(path)[:-5]
+        if model_zoo.unsupported_types(text) or name.endswith("_int8"):
+            continue
+        st = model_zoo.structure(text)
+        dup = [a["name"] for a, s_ in seen if s_ == st]
+        if dup:
+            [a for a, s_ in seen if s_ == st][0]["same_as"].append(name)
+            continue
+        _, ops = parse_phai(text)
+        inp = [op for op in ops if op["type"] == "Input"][0]["params"]
+        w, h = int(inp[0]), int(inp[1])
+        types = {t for t, _, _ in st}
+        if not (types & {"innerproduct", "reshape"}):
+            h, w = min(h, 64) if h > 0 else 64, 96          # fully convolutional: a small image will do
+        elif w < 0:
+            w = 160
+        arch = {"name": name, "same_as": [], "seed": 31 + len(archs), "input_hw": [h, w], "structure": st}
+        picked = None
+        # the Input op's width / height keys are nominal (person_attri_simp says 640 x 640 but pools with the
+        # 28 x 28 window of a 224 x 224 image): fall back to 224 x 224 when the nominal size gives no finite result
+        bad_sizes = set()
+        for gain, hw in [(g_, (h, w)) for g_ in (2.0, 1.6, 1.2, 1.0, 0.8, 0.6, 0.5, 0.4, 0.3)] + [(g_, (224, 224)) for g_ in (2.0, 1.6, 1.2, 1.0, 0.8)]:
+            if hw in bad_sizes:
+                continue
+            arch["input_hw"] = list(hw)
+            x = model_zoo.architecture_input(arch)
+            g, outs = model_zoo.graph_from_structure(st, arch["seed"], gain=gain)
+            p = ref_lib.RefPipeline(g.phai_text(), g.racy_bytes())
+            try:
+                res = p.forward(x)
+            except Exception:           # an image size the graph cannot take
+                p.close()
+                bad_sizes.add(hw)
+                continue
+            if not all(np.isfinite(v).all() for v in res.values()) and gain == 2.0:
+                p.close()
+                bad_sizes.add(hw)       # not a matter of weight scale: the size does not fit the graph
+                continue
+            inner = [i for i in (len(st) // 4, len(st) // 2, 3 * len(st) // 4, len(st) - 2)]
+            maps = {i: p.featmap("t%d" % i) for i in inner}
+            peak = max(float(np.abs(p.featmap("t%d" % i)).max()) for i in range(len(st)) if st[i][0] != "input")
+            logit_peak = max([float(np.abs(p.featmap("t%d" % st[i][2][0][0])).max()) for i in range(len(st))
+                              if st[i][0] == "sigmoid" and "t%d" % i in outs] + [0.0])
+            p.close()
+            # a Sigmoid at the output turns a small relative error of a large logit into a large absolute one:
+            # such graphs get weights small enough for logits of a few units
+            finite = all(np.isfinite(v).all() for v in res.values())
+            if finite and peak < 8000.0 and logit_peak < 12.0:      # fp16 feature maps on the device: stay well below 65504
+                picked = gain
+                break
+        assert picked is not None, name
+        arch["gain"] = picked
+        arch["outputs"] = outs
+        arch["inner"] = inner
+        for n in outs:
+            out["%s:%s" % (name, n)] = model_zoo.sample(res[n])
+            out["%s:%s:shape" % (name, n)] = np.array(res[n].shape, np.int64)
+        for i, v in maps.items():
+            out["%s:t%d" % (name, i)] = model_zoo.sample(v)
+        h, w = arch["input_hw"]
+        print("%-40s gain %.1f peak %.3g input %dx%d outputs %s" % (
+            name[:40], picked, peak, h, w, " ".join("%s%s" % (n, res[n].shape) for n in outs)), flush=True)
+        archs.append(arch)
+        seen.append((arch, st))
+    jpath = os.path.join(ROOT, "tests", "golden", "shipped_architectures.json")
+    with open(jpath, "w") as f:
+        json.dump(archs, f, separators=(",", ":"))
+    npath = os.path.join(ROOT, "tests", "golden", "shipped_architectures.npz")
+    np.savez_compressed(npath, **out)
+    print("wrote", jpath, os.path.getsize(jpath) // 1024, "KiB and", npath, os.path.getsize(npath) // 1024, "KiB,", len(archs),
+          "architectures")
+
+
 class _RefAdapter:
     def __init__(self, p):
         self.p = p
@@ -350,5 +440,7 @@ if __name__ == "__main__":
         yolo()
     elif sys.argv[1:] == ["shipped"]:
         shipped()
+    elif sys.argv[1:] == ["architectures"]:
+        architectures()
     else:
         main()
