@@ -283,11 +283,12 @@ __device__ __forceinline__ float bin_apply(int op, float a, float b) {
     return op == 0 ? a + b : (op == 1 ? a - b : (op == 2 ? a * b : a / b));
 }
 
-// y[n][c][p] = a[n][c][p] op b[n % b_batch][c]: a per-channel value of every image applied to a whole map
-// (squeeze-and-excitation gates).  Indexing as channel_affine_kernel; padding channels are written 0.
+// y[n][c][p] = a[n][c][p] op b[n % b_batch][c] (or b op a when b_first): a per-channel value of every image
+// applied to a whole map (squeeze-and-excitation gates).  Indexing as channel_affine_kernel; padding channels are written 0.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) binary_bcast_kernel(const T* a, const T* b, T* y, int64_t count, int C, int cs,
-                                                                int64_t inner, int channel_last, int op, int b_batch) {
+                                                                int64_t inner, int channel_last, int op, int b_batch,
+                                                                int b_first) {
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     const int64_t per_image = channel_last ? inner * cs : inner * C;
     const int bcs = channel_last ? cs : C;
@@ -295,8 +296,34 @@ __global__ void __launch_bounds__(kThreads) binary_bcast_kernel(const T* a, cons
         const int c = channel_last ? (int)(i % cs) : (int)((i / inner) % C);
         const int64_t n = i / per_image;
         float v = 0.f;
-        if (c < C) v = bin_apply(op, ld1(a + i), ld1(b + (n % b_batch) * bcs + c));
+        if (c < C) {
+            const float av = ld1(a + i), bv = ld1(b + (n % b_batch) * bcs + c);
+            v = b_first ? bin_apply(op, bv, av) : bin_apply(op, av, bv);
+        }
         st1(y + i, v);
+    }
+}
+
+
+// Softmax over the C values of every (image, position): y[n][c][p] = exp(x - max_c) / sum_c exp(x - max_c).
+// One thread per (n, p); C is small (class scores).  x may have a padded image stride.
+__global__ void __launch_bounds__(kThreads) softmax_channels_kernel(const float* __restrict__ x, float* __restrict__ y, int N,
+                                                                    int C, int64_t inner, int64_t x_image_stride) {
+    const int64_t total = (int64_t)N * inner;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const int64_t n = i / inner, p = i - n * inner;
+        const float* xp = x + n * x_image_stride + p;
+        float* yp = y + n * C * inner + p;
+        float m = xp[0];
+        for (int c = 1; c < C; ++c) m = fmaxf(m, xp[c * inner]);
+        float sum = 0.f;
+        for (int c = 0; c < C; ++c) {
+            const float e = expf(xp[c * inner] - m);
+            yp[c * inner] = e;
+            sum += e;
+        }
+        for (int c = 0; c < C; ++c) yp[c * inner] = yp[c * inner] / sum;
     }
 }
 
@@ -550,8 +577,9 @@ extern "C" int exb_transpose_hw_f32(exb_ctx* ctx, const float* x, float* y, int6
     return after_launch("exb_transpose_hw_f32");
 }
 
-extern "C" int exb_binaryop_channel_bcast_fwd(exb_ctx* ctx, int op, const void* a, const void* b, void* y, int N, int b_batch,
-                                              int C, int c_stride, int64_t inner, int dtype, int channel_last, void* stream) {
+extern "C" int exb_binaryop_channel_bcast_fwd(exb_ctx* ctx, int op, const void* a, const void* b, int b_first, void* y, int N,
+                                              int b_batch, int C, int c_stride, int64_t inner, int dtype, int channel_last,
+                                              void* stream) {
     EXB_REQUIRE(ctx != nullptr, "null context");
     EXB_REQUIRE(N >= 0 && C > 0 && inner > 0, "exb_binaryop_channel_bcast_fwd: bad shape");
     EXB_REQUIRE(b_batch == N || b_batch == 1, "exb_binaryop_channel_bcast_fwd: %d gate images for a batch of %d", b_batch, N);
@@ -567,9 +595,24 @@ extern "C" int exb_binaryop_channel_bcast_fwd(exb_ctx* ctx, int op, const void* 
     const int grid = stream_grid(ctx, count, kThreads);
     if (dtype == EXB_F16)
         binary_bcast_kernel<__half><<<grid, kThreads, 0, st>>>(static_cast<const __half*>(a), static_cast<const __half*>(b),
-                                                               static_cast<__half*>(y), count, C, cs, inner, channel_last, op, b_batch);
+                                                               static_cast<__half*>(y), count, C, cs, inner, channel_last, op, b_batch,
+                                                               b_first);
     else
         binary_bcast_kernel<float><<<grid, kThreads, 0, st>>>(static_cast<const float*>(a), static_cast<const float*>(b),
-                                                              static_cast<float*>(y), count, C, cs, inner, channel_last, op, b_batch);
+                                                              static_cast<float*>(y), count, C, cs, inner, channel_last, op, b_batch,
+                                                              b_first);
     return after_launch("exb_binaryop_channel_bcast_fwd");
+}
+
+extern "C" int exb_softmax_channels_f32(exb_ctx* ctx, const float* x, float* y, int N, int C, int64_t inner,
+                                        int64_t x_image_stride, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(N >= 0 && C > 0 && inner > 0, "exb_softmax_channels_f32: bad shape");
+    if (x_image_stride == 0) x_image_stride = (int64_t)C * inner;
+    EXB_REQUIRE(x_image_stride >= (int64_t)C * inner, "exb_softmax_channels_f32: image stride smaller than an image");
+    if (N == 0) return EXB_OK;
+    EXB_REQUIRE(x && y && x != y, "exb_softmax_channels_f32: null or aliased buffer");
+    softmax_channels_kernel<<<stream_grid(ctx, (int64_t)N * inner, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, y, N, C, inner, x_image_stride);
+    return after_launch("exb_softmax_channels_f32");
 }

@@ -613,8 +613,7 @@ static void binaryop_run(exb_ctx* h, int op, int with_scalar, float coef, const 
     }
     CHECK_GE(bottoms.size(), (size_t)2);
     if (bottoms[0]->data_shape() != bottoms[1]->data_shape()) {
-        // (N,C,H,W) with (N or 1,C,1,1): the per-channel gate of a squeeze-and-excitation block.  As in the
-        // reference the larger operand comes first in the operation, whatever the order of the bottoms.
+        // (N,C,H,W) with (N or 1,C,1,1) in either order: the per-channel gate of a squeeze-and-excitation block
         const bool first_big = bottoms[0]->count() >= bottoms[1]->count();
         const auto& big = bottoms[first_big ? 0 : 1];
         const auto& small = bottoms[first_big ? 1 : 0];
@@ -622,7 +621,7 @@ static void binaryop_run(exb_ctx* h, int op, int with_scalar, float coef, const 
                           small->width() == 1 && (small->num() == big->num() || small->num() == 1);
         if (!gate) NOT_IMPLEMENTED << " (broadcasting binary op other than (N,C,H,W) with (N,C,1,1))";
         tops[0] = make_tensor<T>(big->data_shape(), big->device(), big->order(), big->allocator());
-        exb_check(exb_binaryop_channel_bcast_fwd(h, op, big->gpu_data(), small->gpu_data(), tops[0]->mutable_gpu_data(),
+        exb_check(exb_binaryop_channel_bcast_fwd(h, op, big->gpu_data(), small->gpu_data(), first_big ? 0 : 1, tops[0]->mutable_gpu_data(),
                                                  big->num(), small->num(), big->channels(), 0,
                                                  (int64_t)big->height() * big->width(), dtype, 0, nullptr),
                   "exb_binaryop_channel_bcast_fwd");
@@ -1320,6 +1319,83 @@ void operation_transpose<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bo
 }
 INSTANCE_CLASS(operation_transpose);
 REGISTE(operation_transpose);
+
+// ---------------------------------------------------------------------------------------------
+// HardSigmoid, Softmax, Flatten
+// ---------------------------------------------------------------------------------------------
+template <typename Dtype>
+operation_hardsigmoid<Dtype>::operation_hardsigmoid(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        if (kv.first == 0) alpha_ = std::stof(kv.second);
+        else if (kv.first == 1) beta_ = std::stof(kv.second);
+        else LOG(FATAL) << "Un-supported Hardsigmoid Attribution " << kv.first;
+    }
+}
+template <typename Dtype>
+void operation_hardsigmoid<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), 1u);
+    CHECK_EQ(tops.size(), 1u);
+    tops[0] = make_tensor<float>(bottoms[0]->data_shape(), bottoms[0]->device(), bottoms[0]->order(), bottoms[0]->allocator());
+    exb_check(exb_hardsigmoid_fwd(h, bottoms[0]->gpu_data(), tops[0]->mutable_gpu_data(), tops[0]->count(), EXB_F32, alpha_,
+                                  beta_, nullptr), "exb_hardsigmoid_fwd");
+}
+INSTANCE_CLASS(operation_hardsigmoid);
+REGISTE(operation_hardsigmoid);
+
+template <typename Dtype>
+operation_softmax<Dtype>::operation_softmax(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        if (kv.first == 0) axis_ = std::atoi(kv.second.c_str());
+        else if (kv.first != 1 && kv.first != -23330) LOG(FATAL) << "Un-supported Softmax Attribution " << kv.first;
+    }
+}
+template <typename Dtype>
+void operation_softmax<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), tops.size());
+    for (size_t i = 0; i < bottoms.size(); ++i) {
+        CHECK(bottoms[i]->order() == memory::NCHW) << "Softmax expects an NCHW tensor";
+        tops[i] = make_tensor<float>(bottoms[i]->data_shape(), bottoms[i]->device(), memory::NCHW, bottoms[i]->allocator());
+        if (tops[i]->count() == 0) continue;
+        exb_check(exb_softmax_channels_f32(h, bottoms[i]->gpu_data(), tops[i]->mutable_gpu_data(), bottoms[i]->num(),
+                                           bottoms[i]->channels(), (int64_t)bottoms[i]->height() * bottoms[i]->width(), 0,
+                                           nullptr), "exb_softmax_channels_f32");
+    }
+}
+INSTANCE_CLASS(operation_softmax);
+REGISTE(operation_softmax);
+
+template <typename Dtype>
+operation_flatten<Dtype>::operation_flatten(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv) {
+        if (kv.first == 0) axis_ = std::atoi(kv.second.c_str());
+        else LOG(FATAL) << "Un-supported flatten Attribution " << kv.first;
+    }
+}
+template <typename Dtype>
+std::vector<int> operation_flatten<Dtype>::out_shape(const std::vector<int>& in) const {
+    CHECK_EQ(in.size(), (size_t)4);
+    const int c = in[1], h = in[2], w = in[3];
+    switch (axis_) {
+    case 0: return {in[0], 1, c * h * w, 1};
+    case 1: return {in[0], 1, c * h, w};
+    case 2: return {in[0], 1, c, h * w};
+    case 3: return {in[0], 1, 1, c * h * w};
+    default: NOT_IMPLEMENTED << " (Flatten axis " << axis_ << ")";
+    }
+    return in;
+}
+template <typename Dtype>
+void operation_flatten<Dtype>::forward_gpu_f32(exb_ctx*&, const f32_list& bottoms, f32_list& tops) {
+    CHECK_EQ(bottoms.size(), 1u);
+    CHECK_EQ(tops.size(), 1u);
+    CHECK(bottoms[0]->order() == memory::NCHW) << "Flatten expects an NCHW tensor";
+    tops[0] = make_tensor<float>(out_shape(bottoms[0]->data_shape()), bottoms[0]->device(), memory::NCHW, bottoms[0]->allocator());
+    if (tops[0]->count() == 0) return;
+    CUDA_CHECK(cudaMemcpy(tops[0]->mutable_gpu_data(), bottoms[0]->gpu_data(), sizeof(float) * tops[0]->count(),
+                          cudaMemcpyDeviceToDevice));
+}
+INSTANCE_CLASS(operation_flatten);
+REGISTE(operation_flatten);
 
 }  // namespace excalibur
 }  // namespace glasssix

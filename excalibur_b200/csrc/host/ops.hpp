@@ -385,6 +385,45 @@ protected:
     device_scratch scratch_in_, scratch_mid_, scratch_out_;
 };
 
+// y = max(0, min(1, alpha*x + beta)): keys 0 alpha, 1 beta (reference src/Excalibur/operation_hardsigmoid.cpp:12-46).
+template <typename Dtype>
+class operation_hardsigmoid : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_hardsigmoid(const operation_param& param);
+    virtual const char* type() const { return "HardSigmoid"; }
+    float alpha_ = 0.f, beta_ = 0.f;
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
+// Softmax over the channel axis: key 0 = axis (0, the channels of an NCHW tensor without its batch axis, is the
+// only one implemented), key 1 ignored as in the reference (src/Excalibur/operation_softmax.cpp:10-96).
+template <typename Dtype>
+class operation_softmax : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_softmax(const operation_param& param);
+    virtual const char* type() const { return "Softmax"; }
+    int axis_ = 0;
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
+// Same values, shape {n, 1, h, w} with (h, w) = (c*h*w, 1), (c*h, w), (c, h*w) or (1, c*h*w) for key 0 = axis
+// 0..3, default 1 (reference src/Excalibur/operation_flatten.cpp:10-63).
+template <typename Dtype>
+class operation_flatten : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    explicit operation_flatten(const operation_param& param);
+    virtual const char* type() const { return "Flatten"; }
+    int axis_ = 1;
+    std::vector<int> out_shape(const std::vector<int>& in) const;
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+};
+
 // View of the same NCHW data with another shape: keys 0 w, 1 h, 2 c (0 keeps, -1 deduces; n is kept;
 // reference src/Excalibur/operation_reshape.cpp:10-84).
 template <typename Dtype>

@@ -114,7 +114,7 @@ public:
         static const std::set<std::string> ok = {"convolution", "convolutiondepthwise", "pooling", "eltwise", "binaryop",
                                                   "relu", "split", "innerproduct", "clip", "sigmoid", "concat", "interp",
                                                  "batchnorm", "hardswish", "input", "yolov5focus", "prelu", "leakyrelu",
-                                                 "deconvolution", "reshape", "transpose"};
+                                                 "deconvolution", "reshape", "transpose", "hardsigmoid", "softmax", "flatten"};
         for (const auto& p : params_) {
             std::string t = p.type_;
             std::transform(t.begin(), t.end(), t.begin(), ::tolower);
@@ -728,9 +728,17 @@ void fused_plan::build(int N, int C, int H, int W) {
         fmap_info& x = fmaps_[root(in_ids[i][0])];
         fmap_info& y = fmaps_[root(out_ids[i][0])];
         CHECK(x.produced) << "feature map " << x.name << " is consumed before it is produced";
-        if (t == "reshape" && !x.f32_only && !x.need_f32 &&
-            dynamic_cast<operation_reshape<float>*>(ops_[i].get())->out_shape({x.N, x.C, x.H, x.W}) ==
-                std::vector<int>{x.N, x.C, x.H, x.W}) {
+        bool plain_copy = false;
+        if (t == "reshape" && !x.f32_only && !x.need_f32)
+            plain_copy = dynamic_cast<operation_reshape<float>*>(ops_[i].get())->out_shape({x.N, x.C, x.H, x.W}) ==
+                         std::vector<int>{x.N, x.C, x.H, x.W};
+        if (t == "flatten" && !x.f32_only && !x.need_f32 && x.H == 1 && x.W == 1) {
+            // a feature vector on its way into InnerProducts, which read it as C values whatever its shape says
+            const int fy = root(out_ids[i][0]);
+            plain_copy = !output_roots.count(fy) && !consumers[fy].empty();
+            for (int cj : consumers[fy]) plain_copy = plain_copy && lower_type(params_[cj]) == "innerproduct";
+        }
+        if (plain_copy) {
             // a Reshape that changes nothing (the (N,C,1,1) vectors around the InnerProducts of a gate): a copy
             y.need_f16 = true;
             set_shape(y, x.N, x.C, x.H, x.W);
@@ -744,7 +752,7 @@ void fused_plan::build(int N, int C, int H, int W) {
             finish_forms(y, false);
             continue;
         }
-        if (t == "reshape" || t == "transpose") {
+        if (t == "reshape" || t == "transpose" || t == "flatten" || t == "softmax") {
             // Shape surgery is defined on NCHW data: it runs on the fp32 NCHW copy of the tensor, and what it
             // produces exists in that form only (the graph's tail: detection heads).
             float* src = static_cast<float*>(form_f32(x));
@@ -757,11 +765,21 @@ void fused_plan::build(int N, int C, int H, int W) {
             }
             y.f32_only = y.need_f32 = y.produced = true;
             auto* tr = t == "transpose" ? dynamic_cast<operation_transpose<float>*>(ops_[i].get()) : nullptr;
-            if (t == "reshape") {
-                auto* rs = dynamic_cast<operation_reshape<float>*>(ops_[i].get());
-                const std::vector<int> shp = rs->out_shape({x.N, x.C, x.H, x.W});
+            if (t == "reshape" || t == "flatten") {
+                const std::vector<int> in_shape{x.N, x.C, x.H, x.W};
+                const std::vector<int> shp = t == "reshape" ? dynamic_cast<operation_reshape<float>*>(ops_[i].get())->out_shape(in_shape)
+                                                            : dynamic_cast<operation_flatten<float>*>(ops_[i].get())->out_shape(in_shape);
                 y.N = shp[0]; y.C = shp[1]; y.H = shp[2]; y.W = shp[3]; y.cs = y.C;
                 y.f32 = x.f32;       // same bytes, new shape
+            } else if (t == "softmax") {
+                if (dynamic_cast<operation_softmax<float>*>(ops_[i].get())->axis_ != 0) PLAN_REFUSE << "(Softmax is implemented over the channel axis, key 0=0)";
+                y.N = x.N; y.C = x.C; y.H = x.H; y.W = x.W; y.cs = y.C;
+                float* dst = static_cast<float*>(form_f32(y));
+                const int n = x.N, c = x.C;
+                const int64_t inner = (int64_t)x.H * x.W;
+                add_step(params_[i].name_, [=](cudaStream_t st) {
+                    exb_check(exb_softmax_channels_f32(ctx, src, dst, n, c, inner, 0, st), "exb_softmax_channels_f32");
+                });
             } else if (tr->is_identity()) {
                 y.N = x.N; y.C = x.C; y.H = x.H; y.W = x.W; y.cs = y.C;
                 y.f32 = x.f32;
@@ -956,7 +974,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         } else if (t == "binaryop" && in_ids[i].size() == 2 &&
                    !dynamic_cast<operation_binaryop<float>*>(ops_[i].get())->with_scalar_ &&
                    (fmaps_[root(in_ids[i][1])].H != x.H || fmaps_[root(in_ids[i][1])].W != x.W)) {
-            // (N,C,H,W) with (N,C,1,1): a per-channel gate; the larger operand comes first in the operation
+            // (N,C,H,W) with (N,C,1,1) in either order: a per-channel gate
             fmap_info& o = fmaps_[root(in_ids[i][1])];
             fmap_info& big = (int64_t)x.H * x.W >= (int64_t)o.H * o.W ? x : o;
             fmap_info& sm = &big == &x ? o : x;
@@ -969,10 +987,10 @@ void fused_plan::build(int N, int C, int H, int W) {
             const void* g8 = form_f16(sm);
             void* yo = form_f16(y);
             const int op = dynamic_cast<operation_binaryop<float>*>(ops_[i].get())->op_type_;
-            const int n = big.N, c = big.C, cs = big.cs;
+            const int n = big.N, c = big.C, cs = big.cs, small_first = &big == &x ? 0 : 1;
             const int64_t inner = (int64_t)big.H * big.W;
             add_step(params_[i].name_, [=](cudaStream_t st) {
-                exb_check(exb_binaryop_channel_bcast_fwd(ctx, op, a, g8, yo, n, n, c, cs, inner, EXB_F16, 1, st),
+                exb_check(exb_binaryop_channel_bcast_fwd(ctx, op, a, g8, small_first, yo, n, n, c, cs, inner, EXB_F16, 1, st),
                           "exb_binaryop_channel_bcast_fwd");
             });
             finish_forms(y, false);
@@ -989,6 +1007,13 @@ void fused_plan::build(int N, int C, int H, int W) {
                 const void* xin = form_f16(x);
                 add_step(params_[i].name_, [=](cudaStream_t st) {
                     exb_check(exb_hardswish_fwd(ctx, xin, yo, count, EXB_F16, alpha, beta, st), "exb_hardswish_fwd");
+                });
+            } else if (t == "hardsigmoid") {
+                auto* hs = dynamic_cast<operation_hardsigmoid<float>*>(ops_[i].get());
+                const float alpha = hs->alpha_, beta = hs->beta_;
+                const void* xin = form_f16(x);
+                add_step(params_[i].name_, [=](cudaStream_t st) {
+                    exb_check(exb_hardsigmoid_fwd(ctx, xin, yo, count, EXB_F16, alpha, beta, st), "exb_hardsigmoid_fwd");
                 });
             } else if (t == "prelu" || t == "leakyrelu") {
                 const float* slope = nullptr;

@@ -213,6 +213,10 @@ struct HardSwishFn {
     float alpha, beta;
     __device__ float operator()(float v) const { return v * fminf(fmaxf(fmaf(v, alpha, beta), 0.f), 1.f); }
 };
+struct HardSigmoidFn {
+    float alpha, beta;
+    __device__ float operator()(float v) const { return fmaxf(0.f, fminf(1.f, alpha * v + beta)); }
+};
 struct ReluFn {
     __device__ float operator()(float v) const { return v >= 0.f ? v : 0.f; }
 };
@@ -274,6 +278,11 @@ extern "C" int exb_activation_fwd(exb_ctx* ctx, int act, const void* x, void* y,
 extern "C" int exb_hardswish_fwd(exb_ctx* ctx, const void* x, void* y, int64_t count, int dtype, float alpha,
                                  float beta, void* stream) {
     return launch_map1(ctx, x, y, count, dtype, stream, HardSwishFn{alpha, beta}, "exb_hardswish_fwd");
+}
+
+extern "C" int exb_hardsigmoid_fwd(exb_ctx* ctx, const void* x, void* y, int64_t count, int dtype, float alpha,
+                                   float beta, void* stream) {
+    return launch_map1(ctx, x, y, count, dtype, stream, HardSigmoidFn{alpha, beta}, "exb_hardsigmoid_fwd");
 }
 
 extern "C" int exb_binaryop_scalar_fwd(exb_ctx* ctx, int op, const void* a, float scalar, void* y,

@@ -408,7 +408,8 @@ _TYPE_NAMES = {"convolution": "Convolution", "convolutiondepthwise": "Convolutio
                "pooling": "Pooling", "innerproduct": "InnerProduct", "batchnorm": "BatchNorm", "prelu": "PReLU",
                "leakyrelu": "LeakyRelu", "relu": "ReLU", "eltwise": "Eltwise", "binaryop": "BinaryOp", "input": "Input",
                "concat": "Concat", "interp": "Interp", "sigmoid": "Sigmoid", "hardswish": "HardSwish", "clip": "Clip",
-               "reshape": "Reshape", "transpose": "Transpose", "yolov5focus": "YoloV5Focus"}
+               "reshape": "Reshape", "transpose": "Transpose", "yolov5focus": "YoloV5Focus", "hardsigmoid": "HardSigmoid",
+               "softmax": "Softmax", "flatten": "Flatten"}
 
 
 def _num(v):

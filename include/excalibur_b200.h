@@ -368,6 +368,15 @@ EXB_API int exb_hardswish_fwd(exb_ctx* ctx, const void* x, void* y, int64_t coun
  * >= 4*C, padding channels 0.  Replaces three passes over the image (normalise, ingest, focus). */
 EXB_API int exb_nchw_f32_focus_to_nhwc_f16(exb_ctx* ctx, const float* x, void* y, int N, int C, int H, int W,
                                            int c_stride, const float* mul, const float* add, void* stream);
+/* y = max(0, min(1, alpha*x + beta)): operation_hardsigmoid (src/Excalibur/operation_hardsigmoid.cpp:34-46).
+ * EXB_F16 or EXB_F32. */
+EXB_API int exb_hardsigmoid_fwd(exb_ctx* ctx, const void* x, void* y, int64_t count, int dtype, float alpha,
+                                float beta, void* stream);
+/* Softmax over the channels of every position of an fp32 NCHW tensor, inner = H*W: operation_softmax
+ * (src/Excalibur/operation_softmax.cpp:34-96).  x_image_stride: floats between images of x (0 = C*inner;
+ * larger for the padded rows an InnerProduct writes); y is dense.  x and y must differ. */
+EXB_API int exb_softmax_channels_f32(exb_ctx* ctx, const float* x, float* y, int N, int C, int64_t inner,
+                                     int64_t x_image_stride, void* stream);
 /* Space-to-depth of operation_yolov5focus (src/Excalibur/operation_yolov5focus.cpp:16-47):
  * out[n][g*C + c][i][j] = in[n][c][2i + g%2][2j + g/2], g = 0..3, output H/2 x W/2 with 4*C channels.
  * Every image of the batch is converted (the reference only converts image 0).
@@ -375,14 +384,14 @@ EXB_API int exb_nchw_f32_focus_to_nhwc_f16(exb_ctx* ctx, const float* x, void* y
  * (EXB_F16, EXB_I8 or EXB_F32; padding channels of the output are written as 0). */
 EXB_API int exb_focus_fwd(exb_ctx* ctx, const void* x, void* y, int N, int C, int H, int W, int in_stride,
                           int out_stride, int dtype, int channel_last, void* stream);
-/* y[n][c][p] = a[n][c][p] op b[n % b_batch][c] (op as exb_binaryop_fwd): operation_binaryop with a
- * (N,C,H,W) and a (N,C,1,1) operand (src/Excalibur/operation_binaryop.cpp:168-190; the reference always
- * computes op(larger operand, smaller operand) whatever their order, and so does the host operation that
- * calls this).  a and y: [N][inner][c_stride] channel-last or [N][C][inner] planar; b: [b_batch][c_stride]
- * or [b_batch][C]; b_batch is N or 1.  EXB_F16 or EXB_F32; y may alias a. */
-EXB_API int exb_binaryop_channel_bcast_fwd(exb_ctx* ctx, int op, const void* a, const void* b, void* y, int N,
-                                           int b_batch, int C, int c_stride, int64_t inner, int dtype,
-                                           int channel_last, void* stream);
+/* y[n][c][p] = a[n][c][p] op b[n % b_batch][c], or b op a when b_first != 0 (op as exb_binaryop_fwd):
+ * operation_binaryop with a (N,C,H,W) and a (N,C,1,1) operand in either order
+ * (src/Excalibur/operation_binaryop.cpp:12-44,168-190).  a and y: [N][inner][c_stride] channel-last or
+ * [N][C][inner] planar; b: [b_batch][c_stride] or [b_batch][C]; b_batch is N or 1.  EXB_F16 or EXB_F32;
+ * y may alias a. */
+EXB_API int exb_binaryop_channel_bcast_fwd(exb_ctx* ctx, int op, const void* a, const void* b, int b_first,
+                                           void* y, int N, int b_batch, int C, int c_stride, int64_t inner,
+                                           int dtype, int channel_last, void* stream);
 /* y = prelu(x * mul[c] + add[c], slope): a BatchNorm followed by a PReLU / LeakyRelu in one pass (the
  * BottleneckCSP tail of the shipped YOLOv5s description).  Arguments as exb_channel_affine_fwd and exb_prelu_fwd. */
 EXB_API int exb_channel_affine_prelu_fwd(exb_ctx* ctx, const void* x, void* y, const float* mul, const float* add,

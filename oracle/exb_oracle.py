@@ -298,6 +298,30 @@ def deconv2d_f32(x, w, bias=None, stride=1, pad=0):
     return np.ascontiguousarray(out, np.float32)
 
 
+def hardsigmoid(x, alpha, beta):
+    """y = max(0, min(1, alpha*x + beta)) (src/Excalibur/operation_hardsigmoid.cpp:42-45)."""
+    x = _f32(x)
+    t = (np.float32(alpha) * x + np.float32(beta)).astype(np.float32)
+    return np.maximum(np.float32(0), np.minimum(np.float32(1), t)).astype(np.float32)
+
+
+def softmax_channels(x):
+    """Softmax over the channels of every position of an NCHW tensor: subtract the channel maximum, exp,
+    divide by the channel sum (src/Excalibur/operation_softmax.cpp:62-96)."""
+    x = _f32(x)
+    e = np.exp((x - x.max(axis=1, keepdims=True)).astype(np.float32)).astype(np.float32)
+    return (e / e.sum(axis=1, keepdims=True, dtype=np.float32)).astype(np.float32)
+
+
+def flatten_nchw(x, axis=1):
+    """Same values, shape {n, 1, h, w} with (h, w) = (chw, 1), (ch, w), (c, hw), (1, chw) for axis 0..3
+    (src/Excalibur/operation_flatten.cpp:33-63)."""
+    x = _f32(x)
+    n, c, h, w = x.shape
+    hw = {0: (c * h * w, 1), 1: (c * h, w), 2: (c, h * w), 3: (1, c * h * w)}[axis]
+    return np.ascontiguousarray(x).reshape((n, 1) + hw)
+
+
 def reshape_nchw(x, w=0, h=0, c=0):
     """New shape over the same NCHW bytes: a positive key replaces the axis, 0 keeps it, -1 deduces it; n is
     kept (src/Excalibur/operation_reshape.cpp:48-84)."""

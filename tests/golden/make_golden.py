@@ -191,6 +191,28 @@ def shipped():
     # batch 1: the reference's YoloV5Focus only fills image 0
     g, info = model_zoo.yolov5s_simp(size=128)
     net("yolosimp", g, info, r.uniform(0, 255, (1, 3, 128, 128)).astype(np.float32), ("csp2_cv4_act", "spp_cat_out"))
+    # HardSigmoid, Softmax over channels, Flatten (default axis and axis 0), per-channel broadcast BinaryOp
+    x = (r.standard_normal((2, 7, 3, 5)) * 3).astype(np.float32)
+    out["misc_x"] = x
+    g = GraphBuilder(); g._op("HardSigmoid", "h", ["in"], ["out"], "0=0.2 1=0.5")
+    out["hardsigmoid_out"], = run(g, x)
+    g = GraphBuilder(); g._op("Softmax", "s", ["in"], ["out"], "0=0 1=1")
+    out["softmax_out"], = run(g, x)
+    g = GraphBuilder(); g._op("Flatten", "f", ["in"], ["out"], "")
+    out["flatten_out"], = run(g, x)
+    g = GraphBuilder(); g._op("Flatten", "f", ["in"], ["out"], "0=0")
+    out["flatten0_out"], = run(g, x)
+    g = GraphBuilder()
+    g.split("s", "in", ["a", "b"])
+    g.pool("gap", "b", "gate", 1, 1, 1, 0, global_pool=True)
+    g.binaryop("mul", "a", "gate", "out", 2)
+    out["bcast_mul_out"], = run(g, x)
+    g = GraphBuilder()
+    g.split("s", "in", ["a", "b"])
+    g.pool("gap", "b", "gate", 1, 1, 1, 0, global_pool=True)
+    g.binaryop("sub", "gate", "a", "out", 1)          # the reference computes op(larger, smaller) whatever the order
+    out["bcast_sub_out"], = run(g, x)
+
     # the shipped int8 description: max-abs calibration of every dense conv's input through the reference's
     # fp32 pipeline on 8 seeded images, then the reference's int8 forward (batch 1: its packed int8 path only
     # computes image 0)

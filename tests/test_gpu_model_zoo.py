@@ -408,3 +408,21 @@ def test_unicorn_light_int8(fusion):
     assert _rel(out3[0:1], ref8) < 3e-2
     assert np.abs(out3[1] - out3[0]).max() > 0
     p.close()
+
+
+def test_operation_hardsigmoid_softmax_flatten_broadcast_binaryop():
+    h = _host()
+    x = S["misc_x"]
+    np.testing.assert_allclose(h.run_op("HardSigmoid", "0=0.2 1=0.5", [x]), S["hardsigmoid_out"], rtol=0, atol=1e-6)
+    np.testing.assert_allclose(h.run_op("Softmax", "0=0 1=1", [x]), S["softmax_out"], rtol=0, atol=1e-6)
+    np.testing.assert_array_equal(h.run_op("Flatten", "", [x]), S["flatten_out"])
+    np.testing.assert_array_equal(h.run_op("Flatten", "0=0", [x]), S["flatten0_out"])
+    gate = h.run_op("Pooling", "0=1 1=1 2=1 3=0 4=1", [x])
+    assert gate.shape == (2, 7, 1, 1)
+    np.testing.assert_allclose(h.run_op("BinaryOp", "0=2", [x, gate]), S["bcast_mul_out"], rtol=0, atol=1e-6)
+    np.testing.assert_allclose(h.run_op("BinaryOp", "0=1", [gate, x]), S["bcast_sub_out"], rtol=0, atol=1e-6)
+    np.testing.assert_allclose(h.run_op("BinaryOp", "0=1", [x, gate]), -S["bcast_sub_out"], rtol=0, atol=1e-6)
+    with pytest.raises(h.HostError):
+        h.run_op("BinaryOp", "0=0", [x, x[:, :, :1]])          # other broadcast shapes are refused
+    with pytest.raises(h.HostError):
+        h.run_op("Softmax", "0=0 1=1 7=3", [x])

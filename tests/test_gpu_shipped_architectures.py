@@ -46,5 +46,6 @@ def test_shipped_architecture(arch, fusion):
         # all but two run on the fused plan; those two flatten a convolution map in front of an InnerProduct /
         # Concat (a Reshape in the middle of the graph), which the plan refuses, and run op by op instead
         launches, _ = p.stats()
+        print("%s: %d launches" % (name, launches))
         assert (launches > 0) == (name not in ("pfld11_landmark65_simp", "singel_char_classfi_simp")), launches
     p.close()

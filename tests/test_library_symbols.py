@@ -58,7 +58,7 @@ def test_pure_host_calls_work_without_a_gpu(so_path):
                 "operation_binaryop", "operation_relu", "operation_split", "operation_innerproduct", "operation_clip",
                 "operation_sigmoid", "operation_concat", "operation_interp", "operation_batchnorm", "operation_hardswish",
                 "operation_input", "operation_yolov5focus", "operation_prelu", "operation_leakyrelu", "operation_deconvolution",
-                "operation_reshape", "operation_transpose"):
+                "operation_reshape", "operation_transpose", "operation_hardsigmoid", "operation_softmax", "operation_flatten"):
         assert host.registered(key), key
     assert not host.registered("operation_nonexistent")
     # capability queries are pure host arithmetic

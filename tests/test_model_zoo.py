@@ -35,6 +35,17 @@ def test_oracle_reshape_transpose_match_the_reference():
     assert O.reshape_nchw(S["rt_x"], w=-1, h=2, c=6).shape == (2, 6, 2, 20)
 
 
+def test_oracle_hardsigmoid_softmax_flatten_match_the_reference():
+    x = S["misc_x"]
+    np.testing.assert_allclose(O.hardsigmoid(x, 0.2, 0.5), S["hardsigmoid_out"], rtol=0, atol=1e-7)
+    np.testing.assert_allclose(O.softmax_channels(x), S["softmax_out"], rtol=0, atol=2e-7)
+    np.testing.assert_array_equal(O.flatten_nchw(x), S["flatten_out"])
+    np.testing.assert_array_equal(O.flatten_nchw(x, 0), S["flatten0_out"])
+    gate = O.pool2d_f32(x, 1, global_pool=True)
+    np.testing.assert_allclose(x * gate, S["bcast_mul_out"], rtol=0, atol=1e-6)
+    np.testing.assert_allclose(gate - x, S["bcast_sub_out"], rtol=0, atol=1e-6)     # operand order is kept
+
+
 @pytest.mark.parametrize("name,ops", [("det_db_resnet18", 80), ("mobile_unicorn", 96), ("yolov5s_simp", 170)])
 def test_builders_have_the_shipped_architecture(name, ops):
     g, info = getattr(model_zoo, name)()
