@@ -109,6 +109,10 @@ def lib():
         L.exb_dw_weights_set_slopes.argtypes = [vp, vp, vp, i32]
         L.exb_channel_affine_prelu_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i32, i32, i64, i32, i32, vp]
         L.exb_nchw_f32_focus_to_nhwc_f16.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]
+        L.exb_binaryop_channel_bcast_fwd.argtypes = [vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i64, i32, i32, vp]
+        L.exb_hardsigmoid_fwd.argtypes = [vp, vp, vp, i64, i32, f32, f32, vp]
+        L.exb_softmax_channels_f32.argtypes = [vp, vp, vp, i32, i32, i64, i64, vp]
+        L.exb_nchw_f16_to_nhwc4_padded.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
         L.exb_prelu_fwd.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i64, i32, i32, vp]
         L.exb_depth_to_space_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
         L.exb_transpose_hw_f32.argtypes = [vp, vp, vp, i64, i32, i32, vp]

@@ -100,6 +100,9 @@ __global__ void __launch_bounds__(kThreads) focus_kernel(const T* __restrict__ x
     }
 }
 
+__device__ __forceinline__ float bin_apply(int op, float a, float b) {
+    return op == 0 ? a + b : (op == 1 ? a - b : (op == 2 ? a * b : a / b));
+}
 __device__ __forceinline__ float ld1(const __half* p) { return __half2float(*p); }
 __device__ __forceinline__ float ld1(const float* p) { return *p; }
 __device__ __forceinline__ void st1(__half* p, float v) { *p = __float2half_rn(v); }
@@ -127,15 +130,29 @@ __global__ void __launch_bounds__(kThreads) channel_affine_kernel(const T* x, T*
 
 
 // Channel-last fp16, 8 channels (16 bytes) per thread step: y = f(x * mul[c] + add[c]) with f the activation
-// `act`, or the PReLU with `slope` when that is not null.  cs is a multiple of 8; padding channels are written 0.
+// `act`, or the PReLU with `slope` when that is not null; mul == null means no affine map (plain PReLU).
+// cs is a multiple of 8; padding channels are written 0.  When the grid stride is a multiple of the vectors
+// per pixel (the launcher arranges that), a thread keeps its channel slice for the whole loop and the per-
+// channel parameters are loaded once.
 __global__ void __launch_bounds__(kThreads) channel_affine_nhwc_f16x8_kernel(const uint4* x, uint4* y, const float* mul,
                                                                              const float* add, const float* slope,
                                                                              int n_slope, int act, int64_t nvec, int C,
                                                                              int cs8) {
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step) {
-        const int c0 = (int)(i % cs8) * 8;
-        uint4 raw = x[i];
+    const bool fixed = step % cs8 == 0;
+    float m[8], a[8], sl[8];
+    auto load_params = [&](int c0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int c = c0 + k;
+            const bool in = c < C;
+            m[k] = in ? (mul ? mul[c] : 1.f) : 0.f;
+            a[k] = in && mul ? add[c] : 0.f;
+            sl[k] = in && slope ? slope[n_slope == 1 ? 0 : c] : 0.f;
+        }
+    };
+    const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    auto one = [&](uint4 raw, int c0) -> uint4 {
         __half2* h = reinterpret_cast<__half2*>(&raw);
         float v[8];
 #pragma unroll
@@ -145,17 +162,10 @@ __global__ void __launch_bounds__(kThreads) channel_affine_nhwc_f16x8_kernel(con
             v[2 * k + 1] = f.y;
         }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const int c = c0 + k;
-            v[k] = c < C ? fmaf(v[k], mul[c], add[c]) : 0.f;
-        }
+        for (int k = 0; k < 8; ++k) v[k] = fmaf(v[k], m[k], a[k]);       // padding channels: m = a = 0
         if (slope) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int c = c0 + k;
-                const float sl = c < C ? slope[n_slope == 1 ? 0 : c] : 0.f;
-                v[k] = v[k] >= 0.f ? v[k] : v[k] * sl;
-            }
+            for (int k = 0; k < 8; ++k) v[k] = v[k] >= 0.f ? v[k] : v[k] * sl[k];
         } else {
             apply_act_vec(v, act);
 #pragma unroll
@@ -164,7 +174,53 @@ __global__ void __launch_bounds__(kThreads) channel_affine_nhwc_f16x8_kernel(con
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) h[k] = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
-        y[i] = raw;
+        return raw;
+    };
+    int64_t i = first;
+    if (fixed) {
+        const int c0 = (int)(first % cs8) * 8;
+        load_params(c0);
+        // four independent 16-byte loads in flight per thread
+        for (; i + 3 * step < nvec; i += 4 * step) {
+            uint4 r[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) r[u] = x[i + u * step];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) y[i + u * step] = one(r[u], c0);
+        }
+        for (; i < nvec; i += step) y[i] = one(x[i], c0);
+        return;
+    }
+    for (; i < nvec; i += step) {
+        const int c0 = (int)(i % cs8) * 8;
+        load_params(c0);
+        y[i] = one(x[i], c0);
+    }
+}
+
+// The per-channel gate on channel-last fp16: y = a op b[n][c] (or b op a), 8 channels per thread step.
+__global__ void __launch_bounds__(kThreads) binary_bcast_nhwc_f16x8_kernel(const uint4* a, const uint4* b, uint4* y, int64_t nvec,
+                                                                           int C, int cs8, int64_t vec_per_image, int op,
+                                                                           int b_batch, int b_first) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step) {
+        const int cv = (int)(i % cs8);
+        const int64_t n = i / vec_per_image;
+        uint4 ra = a[i];
+        const uint4 rb = b[(n % b_batch) * cs8 + cv];
+        __half2* ha = reinterpret_cast<__half2*>(&ra);
+        const __half2* hb = reinterpret_cast<const __half2*>(&rb);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 fa = __half22float2(ha[k]), fb = __half22float2(hb[k]);
+            float2 r;
+            r.x = b_first ? bin_apply(op, fb.x, fa.x) : bin_apply(op, fa.x, fb.x);
+            r.y = b_first ? bin_apply(op, fb.y, fa.y) : bin_apply(op, fa.y, fb.y);
+            if (cv * 8 + 2 * k >= C) r.x = 0.f;
+            if (cv * 8 + 2 * k + 1 >= C) r.y = 0.f;
+            ha[k] = __floats2half2_rn(r.x, r.y);
+        }
+        y[i] = ra;
     }
 }
 
@@ -182,28 +238,6 @@ __global__ void __launch_bounds__(kThreads) prelu_kernel(const T* x, T* y, const
             v = v >= 0.f ? v : v * slope[n_slope == 1 ? 0 : c];
         }
         st1(y + i, v);
-    }
-}
-
-// Channel-last fp16, 8 channels (16 bytes) per thread step; cs is a multiple of 8.
-__global__ void __launch_bounds__(kThreads) prelu_nhwc_f16x8_kernel(const uint4* x, uint4* y, const float* slope,
-                                                                    int n_slope, int64_t nvec, int C, int cs8) {
-    const int64_t step = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step) {
-        const int c0 = (int)(i % cs8) * 8;
-        uint4 raw = x[i];
-        __half2* h = reinterpret_cast<__half2*>(&raw);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            float2 v = __half22float2(h[k]);
-            const int ca = c0 + 2 * k, cb = ca + 1;
-            const float sa = ca < C ? slope[n_slope == 1 ? 0 : ca] : 0.f;
-            const float sb = cb < C ? slope[n_slope == 1 ? 0 : cb] : 0.f;
-            v.x = ca < C ? (v.x >= 0.f ? v.x : v.x * sa) : 0.f;
-            v.y = cb < C ? (v.y >= 0.f ? v.y : v.y * sb) : 0.f;
-            h[k] = __floats2half2_rn(v.x, v.y);
-        }
-        y[i] = raw;
     }
 }
 
@@ -279,10 +313,6 @@ __global__ void __launch_bounds__(256) transpose_planes_f32_kernel(const float* 
 }
 
 
-__device__ __forceinline__ float bin_apply(int op, float a, float b) {
-    return op == 0 ? a + b : (op == 1 ? a - b : (op == 2 ? a * b : a / b));
-}
-
 // y[n][c][p] = a[n][c][p] op b[n % b_batch][c] (or b op a when b_first): a per-channel value of every image
 // applied to a whole map (squeeze-and-excitation gates).  Indexing as channel_affine_kernel; padding channels are written 0.
 template <typename T>
@@ -331,6 +361,17 @@ __global__ void __launch_bounds__(kThreads) softmax_channels_kernel(const float*
 }  // namespace exb
 
 using namespace exb;
+
+// Grid for the 8-channel vector kernels: the grid stride (grid * kThreads vectors) a multiple of the vectors per
+// pixel whenever that costs at most a few CTAs, so that a thread keeps its channel slice.
+static int slice_grid(const exb_ctx* ctx, int64_t nvec, int cs8) {
+    int grid = stream_grid(ctx, nvec, kThreads);
+    int a = cs8, b = kThreads;
+    while (b) { const int t = a % b; a = b; b = t; }
+    const int q = cs8 / a;                      // grid must be a multiple of q
+    if (q > 1 && grid >= q) grid = grid / q * q;
+    return grid;
+}
 
 extern "C" int exb_concat_fwd(exb_ctx* ctx, int n_in, const void* const* xs, const int64_t* widths,
                               const int64_t* x_strides, void* y, int64_t y_stride, int64_t rows, int dtype,
@@ -470,7 +511,7 @@ static int channel_affine_impl(exb_ctx* ctx, const void* x, void* y, const float
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == EXB_F16 && channel_last && cs % 8 == 0 && aligned16(x) && aligned16(y)) {
         const int64_t nvec = count / 8;
-        channel_affine_nhwc_f16x8_kernel<<<stream_grid(ctx, nvec, kThreads), kThreads, 0, st>>>(
+        channel_affine_nhwc_f16x8_kernel<<<slice_grid(ctx, nvec, cs / 8), kThreads, 0, st>>>(
             static_cast<const uint4*>(x), static_cast<uint4*>(y), mul, add, slope, n_slope, act, nvec, C, cs / 8);
         return after_launch(what);
     }
@@ -515,8 +556,8 @@ extern "C" int exb_prelu_fwd(exb_ctx* ctx, const void* x, void* y, const float* 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == EXB_F16 && channel_last && cs % 8 == 0 && aligned16(x) && aligned16(y)) {
         const int64_t nvec = count / 8;
-        prelu_nhwc_f16x8_kernel<<<stream_grid(ctx, nvec, kThreads), kThreads, 0, st>>>(
-            static_cast<const uint4*>(x), static_cast<uint4*>(y), slope, n_slope, nvec, C, cs / 8);
+        channel_affine_nhwc_f16x8_kernel<<<slice_grid(ctx, nvec, cs / 8), kThreads, 0, st>>>(
+            static_cast<const uint4*>(x), static_cast<uint4*>(y), nullptr, nullptr, slope, n_slope, EXB_ACT_NONE, nvec, C, cs / 8);
         return after_launch("exb_prelu_fwd");
     }
     int grid = stream_grid(ctx, count, kThreads);
@@ -592,6 +633,13 @@ extern "C" int exb_binaryop_channel_bcast_fwd(exb_ctx* ctx, int op, const void* 
     if (count == 0) return EXB_OK;
     EXB_REQUIRE(a && b && y, "exb_binaryop_channel_bcast_fwd: null buffer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == EXB_F16 && channel_last && cs % 8 == 0 && aligned16(a) && aligned16(b) && aligned16(y)) {
+        const int64_t nvec = count / 8;
+        binary_bcast_nhwc_f16x8_kernel<<<stream_grid(ctx, nvec, kThreads), kThreads, 0, st>>>(
+            static_cast<const uint4*>(a), static_cast<const uint4*>(b), static_cast<uint4*>(y), nvec, C, cs / 8, inner * (cs / 8), op,
+            b_batch, b_first);
+        return after_launch("exb_binaryop_channel_bcast_fwd");
+    }
     const int grid = stream_grid(ctx, count, kThreads);
     if (dtype == EXB_F16)
         binary_bcast_kernel<__half><<<grid, kThreads, 0, st>>>(static_cast<const __half*>(a), static_cast<const __half*>(b),

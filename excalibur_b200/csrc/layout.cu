@@ -321,8 +321,9 @@ namespace {
 // Network input -> Focus in one pass: fp32 NCHW image, optional per-channel affine (input normalisation),
 // space-to-depth 2x2 and conversion to channel-last fp16.  One thread per output pixel: two float2 loads per
 // input plane (rows 2i and 2i+1, columns 2j and 2j+1), CS / 8 16-byte stores.  4*C <= CS.
-template <int CS>
-__global__ void __launch_bounds__(256) focus_ingest_kernel(const float* __restrict__ x, __half* __restrict__ y, int N, int C,
+// C is a template parameter so that the output vector is indexed statically and stays in registers.
+template <int CS, int C>
+__global__ void __launch_bounds__(256) focus_ingest_kernel(const float* __restrict__ x, __half* __restrict__ y, int N,
                                                            int H, int W, const float* __restrict__ mul,
                                                            const float* __restrict__ add) {
     const int OH = H / 2, OW = W / 2;
@@ -335,6 +336,7 @@ __global__ void __launch_bounds__(256) focus_ingest_kernel(const float* __restri
         alignas(16) __half out[CS];
 #pragma unroll
         for (int k = 0; k < CS; ++k) out[k] = __float2half_rn(0.f);
+#pragma unroll
         for (int c = 0; c < C; ++c) {
             const float* p0 = x + (((int64_t)n * C + c) * H + 2 * oi) * W + 2 * oj;
             const float2 top = *reinterpret_cast<const float2*>(p0);
@@ -367,9 +369,19 @@ extern "C" int exb_nchw_f32_focus_to_nhwc_f16(exb_ctx* ctx, const float* x, void
                 "exb_nchw_f32_focus_to_nhwc_f16: null or misaligned buffer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = exb::stream_grid(ctx, (int64_t)N * (H / 2) * (W / 2), 256);
-    if (c_stride == 16)
-        exb::focus_ingest_kernel<16><<<grid, 256, 0, st>>>(x, static_cast<__half*>(y), N, C, H, W, mul, add);
-    else
-        exb::focus_ingest_kernel<32><<<grid, 256, 0, st>>>(x, static_cast<__half*>(y), N, C, H, W, mul, add);
+    __half* yh = static_cast<__half*>(y);
+#define EXB_FOCUS(CS, CC) exb::focus_ingest_kernel<CS, CC><<<grid, 256, 0, st>>>(x, yh, N, H, W, mul, add)
+    if (c_stride == 16) {
+        if (C == 1) EXB_FOCUS(16, 1); else if (C == 2) EXB_FOCUS(16, 2); else if (C == 3) EXB_FOCUS(16, 3); else EXB_FOCUS(16, 4);
+    } else {
+        switch (C) {
+        case 1: EXB_FOCUS(32, 1); break;
+        case 2: EXB_FOCUS(32, 2); break;
+        case 3: EXB_FOCUS(32, 3); break;
+        case 4: EXB_FOCUS(32, 4); break;
+        default: return exb::fail(EXB_ERR_UNSUPPORTED, "exb_nchw_f32_focus_to_nhwc_f16: %d input channels (1..4 are implemented)", C);
+        }
+    }
+#undef EXB_FOCUS
     return exb::after_launch("exb_nchw_f32_focus_to_nhwc_f16");
 }

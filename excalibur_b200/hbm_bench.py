@@ -108,6 +108,33 @@ def main(argv=None):
     yi = torch.empty((xi.shape[0], 40, 40, 256), device="cuda", dtype=torch.float16)
     report("nearest 2x resize 256ch @20 (batch/8)", _time(torch, lambda: capi.interp_nearest(ctx, xi, 40, 40, y=yi), args.iters),
            (xi.numel() + yi.numel()) * 2)
+    # the kernels added for the shipped model descriptions
+    a = f16(N, 64, 64, 64)
+    y = torch.empty_like(a)
+    sl = torch.rand(64, device="cuda") * 0.3
+    mul, add = torch.rand(64, device="cuda") + 0.5, torch.randn(64, device="cuda")
+    report("PReLU 64ch @64 fp16", _time(torch, lambda: capi.prelu(ctx, a, sl, y=y), args.iters), a.numel() * 4)
+    report("BatchNorm + LeakyRelu 64ch @64 fp16, one pass",
+           _time(torch, lambda: capi.channel_affine_prelu(ctx, a, mul, add, sl[:1], y=y), args.iters), a.numel() * 4)
+    gate = f16(N, 1, 1, 64)
+    check = capi.check
+    report("per-channel gate (N,C,H,W) x (N,C,1,1) 64ch @64",
+           _time(torch, lambda: check(capi.lib().exb_binaryop_channel_bcast_fwd(
+               ctx.handle, 2, capi.ptr(a), capi.ptr(gate), 0, capi.ptr(y), N, N, 64, 64, 64 * 64, capi.EXB_F16, 1,
+               capi.cur_stream())), args.iters), a.numel() * 4)
+    xd = f16(max(N // 4, 1), 80, 80, 256)
+    yd = torch.empty((xd.shape[0], 160, 160, 64), device="cuda", dtype=torch.float16)
+    report("depth-to-space 2x2 64ch @80 (batch/4)", _time(torch, lambda: capi.depth_to_space(ctx, xd, 2, 2, 64, y=yd), args.iters),
+           xd.numel() * 4)
+    x640 = torch.rand((max(N // 8, 1), 3, 640, 640), device="cuda", dtype=torch.float32)
+    yf = torch.empty((x640.shape[0], 320, 320, 16), device="cuda", dtype=torch.float16)
+    report("normalise + Focus + ingest fp32 @640 (batch/8)",
+           _time(torch, lambda: capi.focus_ingest(ctx, x640, 16, mul[:3], add[:3], y=yf), args.iters),
+           x640.numel() * 4 + yf.numel() * 2)
+    xt = torch.rand((max(N // 8, 1) * 3, 85, 6400), device="cuda", dtype=torch.float32)
+    yt = torch.empty((xt.shape[0], 6400, 85), device="cuda", dtype=torch.float32)
+    report("transpose 85 x 6400 planes fp32 (batch/8 x 3)", _time(torch, lambda: capi.transpose_hw(ctx, xt, y=yt), args.iters),
+           xt.numel() * 8)
     ctx.sync_check()
     ctx.close()
     return rows
