@@ -357,6 +357,30 @@ __global__ void __launch_bounds__(kThreads) softmax_channels_kernel(const float*
     }
 }
 
+
+// Detection-head export: y[n][a][p][k] = x[n][p][a*K + k] (channel-last fp16 in, fp32 out) - what a Reshape of the
+// (N, A*K, H, W) head to (N, A, K, H*W) followed by a Transpose of the last two axes computes on NCHW data.
+// A warp per position: the lanes read the A*K channels of the pixel (one contiguous run) and write A runs of K
+// floats; channel -> (a, k) with a float reciprocal, exact for the few hundred channels of a head.
+__global__ void __launch_bounds__(kThreads) split_heads_kernel(const __half* __restrict__ x, float* __restrict__ y, int64_t rows,
+                                                               int P, int cs, int A, int K) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const float inv_k = 1.0f / (float)K;
+    const int C = A * K;
+    for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const int64_t n = r / P;
+        const int p = (int)(r - n * P);
+        const __half* src = x + r * cs;
+        float* dst = y + (n * A * P + p) * (int64_t)K;
+        for (int c = lane; c < C; c += 32) {
+            const int a = (int)(((float)c + 0.5f) * inv_k);
+            const int k = c - a * K;
+            dst[(int64_t)a * P * K + k] = __half2float(src[c]);
+        }
+    }
+}
+
 }  // namespace
 }  // namespace exb
 
@@ -663,4 +687,18 @@ extern "C" int exb_softmax_channels_f32(exb_ctx* ctx, const float* x, float* y, 
     softmax_channels_kernel<<<stream_grid(ctx, (int64_t)N * inner, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         x, y, N, C, inner, x_image_stride);
     return after_launch("exb_softmax_channels_f32");
+}
+
+extern "C" int exb_nhwc_f16_split_heads_f32(exb_ctx* ctx, const void* x, float* y, int N, int P, int c_stride, int A, int K,
+                                            void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(N >= 0 && P > 0 && A > 0 && K > 0 && c_stride >= A * K, "exb_nhwc_f16_split_heads_f32: bad shape");
+    const int64_t total = (int64_t)N * A * P * K;
+    if (total == 0) return EXB_OK;
+    EXB_REQUIRE(x && y, "exb_nhwc_f16_split_heads_f32: null buffer");
+    EXB_REQUIRE(A * K <= 65536, "exb_nhwc_f16_split_heads_f32: %d channels", A * K);
+    const int64_t rows = (int64_t)N * P;
+    split_heads_kernel<<<stream_grid(ctx, rows * 32, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), y, rows, P, c_stride, A, K);
+    return after_launch("exb_nhwc_f16_split_heads_f32");
 }

@@ -752,6 +752,28 @@ void fused_plan::build(int N, int C, int H, int W) {
             finish_forms(y, false);
             continue;
         }
+        if (t == "reshape" && !x.f32_only && !x.need_f32) {
+            // detection head: (N, A*K, H, W) -> Reshape (N, A, K, H*W) -> Transpose of the last two axes, read by
+            // nothing else: one gather from the channel-last fp16 map straight into the fp32 result
+            const std::vector<int> shp = dynamic_cast<operation_reshape<float>*>(ops_[i].get())->out_shape({x.N, x.C, x.H, x.W});
+            const int ry = root(out_ids[i][0]);
+            const int j = sole_consumer(ry);
+            auto* tr2 = j > (int)i && !absorbed[j] && lower_type(params_[j]) == "transpose"
+                            ? dynamic_cast<operation_transpose<float>*>(ops_[j].get()) : nullptr;
+            if (tr2 && tr2->is_swap_hw() && shp[0] == x.N && shp[1] * shp[2] == x.C && shp[3] == x.H * x.W) {
+                fmap_info& out = fmaps_[root(out_ids[j][0])];
+                out.f32_only = out.need_f32 = out.produced = true;
+                out.N = x.N; out.C = shp[1]; out.H = shp[3]; out.W = shp[2]; out.cs = out.C;
+                const void* h16 = form_f16(x);
+                float* dst = static_cast<float*>(form_f32(out));
+                const int n = x.N, P = shp[3], cs = x.cs, A = shp[1], K = shp[2];
+                add_step(params_[i].name_ + "+" + params_[j].name_, [=](cudaStream_t st) {
+                    exb_check(exb_nhwc_f16_split_heads_f32(ctx, h16, dst, n, P, cs, A, K, st), "exb_nhwc_f16_split_heads_f32");
+                });
+                absorbed[j] = 1;
+                continue;
+            }
+        }
         if (t == "reshape" || t == "transpose" || t == "flatten" || t == "softmax") {
             // Shape surgery is defined on NCHW data: it runs on the fp32 NCHW copy of the tensor, and what it
             // produces exists in that form only (the graph's tail: detection heads).

@@ -408,6 +408,11 @@ EXB_API int exb_prelu_fwd(exb_ctx* ctx, const void* x, void* y, const float* slo
  * (0 = rh*rw*C), y has y_stride (0 = C; channels c >= C are written as 0).  EXB_F16 or EXB_F32. */
 EXB_API int exb_depth_to_space_fwd(exb_ctx* ctx, const void* x, void* y, int N, int H, int W, int rh, int rw,
                                    int C, int x_stride, int y_stride, int dtype, void* stream);
+/* Detection-head export in one pass: y[n][a][p][k] = x[n][p][a*K + k], channel-last fp16 x with c_stride >= A*K
+ * physical channels and P = H*W positions, fp32 y.  Equals operation_reshape of the (N, A*K, H, W) head to
+ * (N, A, K, H*W) followed by operation_transpose 1,0,2 (the tail of the shipped yolov5s_simp description). */
+EXB_API int exb_nhwc_f16_split_heads_f32(exb_ctx* ctx, const void* x, float* y, int N, int P, int c_stride, int A,
+                                         int K, void* stream);
 /* y[p][w][h] = x[p][h][w] for `planes` fp32 planes: operation_transpose with permutation 1,0,2
  * (src/Excalibur/operation_transpose.cpp:47-66). */
 EXB_API int exb_transpose_hw_f32(exb_ctx* ctx, const float* x, float* y, int64_t planes, int H, int W,
