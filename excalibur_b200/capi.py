@@ -113,6 +113,7 @@ def lib():
         L.exb_hardsigmoid_fwd.argtypes = [vp, vp, vp, i64, i32, f32, f32, vp]
         L.exb_softmax_channels_f32.argtypes = [vp, vp, vp, i32, i32, i64, i64, vp]
         L.exb_nchw_f16_to_nhwc4_padded.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+        L.exb_nhwc_f16_split_heads_f32.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.exb_prelu_fwd.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i64, i32, i32, vp]
         L.exb_depth_to_space_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
         L.exb_transpose_hw_f32.argtypes = [vp, vp, vp, i64, i32, i32, vp]
@@ -513,6 +514,16 @@ def focus_ingest(ctx, x, c_stride=16, mul=None, add=None, y=None):
     check(lib().exb_nchw_f32_focus_to_nhwc_f16(ctx.handle, ptr(x), ptr(y), N, Cc, H, W, c_stride,
                                                None if mul is None else ptr(mul), None if add is None else ptr(add),
                                                cur_stream()))
+    return y
+
+
+def split_heads(ctx, x, anchors, values, y=None):
+    """NHWC fp16 [N][H][W][cs] detection head -> fp32 [N][anchors][H*W][values] (Reshape + Transpose in one pass)."""
+    t = _torch()
+    N, H, W, cs = x.shape
+    if y is None:
+        y = t.empty((N, anchors, H * W, values), device=x.device, dtype=t.float32)
+    check(lib().exb_nhwc_f16_split_heads_f32(ctx.handle, ptr(x), ptr(y), N, H * W, cs, anchors, values, cur_stream()))
     return y
 
 

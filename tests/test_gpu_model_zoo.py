@@ -426,3 +426,20 @@ def test_operation_hardsigmoid_softmax_flatten_broadcast_binaryop():
         h.run_op("BinaryOp", "0=0", [x, x[:, :, :1]])          # other broadcast shapes are refused
     with pytest.raises(h.HostError):
         h.run_op("Softmax", "0=0 1=1 7=3", [x])
+
+
+@pytest.mark.parametrize("A,K,cs,hw", [(3, 85, 256, (5, 7)), (3, 8, 32, (9, 4)), (1, 16, 16, (3, 3))])
+def test_split_heads_kernel(A, K, cs, hw):
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    H, W = hw
+    x = np.random.default_rng(A * K).standard_normal((2, H, W, cs)).astype(np.float16)
+    y = capi.split_heads(ctx, torch.from_numpy(x).cuda(), A, K)
+    torch.cuda.synchronize()
+    nchw = O.nhwc_to_nchw(x[..., :A * K].astype(np.float32))
+    want = O.transpose_hw(O.reshape_nchw(nchw, w=H * W, h=K, c=A))
+    np.testing.assert_array_equal(y.cpu().numpy(), want)
+    with pytest.raises(capi.ExbError):
+        capi.split_heads(ctx, torch.from_numpy(x).cuda(), A + 1, cs)      # more channels than the tensor has
+    ctx.close()
