@@ -268,6 +268,7 @@ void fused_plan::build(int N, int C, int H, int W) {
     fmaps_.clear();
     index_.clear();
     warmed_ = false;
+    ingest_f16_capable_ = false;
     const size_t n_ops = ops_.size();
 
     // ---- 1. feature maps, Split aliases, consumers ------------------------------------------
