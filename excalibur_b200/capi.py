@@ -517,6 +517,17 @@ def focus_ingest(ctx, x, c_stride=16, mul=None, add=None, y=None):
     return y
 
 
+def binaryop_channel_bcast(ctx, a, gate, op=2, gate_first=False, channels=None, y=None):
+    """y = a op gate[n][c] (or gate op a): a NHWC [N][H][W][cs], gate [N or 1][1][1][cs], same dtype."""
+    t = _torch()
+    N, H, W, cs = a.shape
+    if y is None:
+        y = t.empty_like(a)
+    check(lib().exb_binaryop_channel_bcast_fwd(ctx.handle, op, ptr(a), ptr(gate), 1 if gate_first else 0, ptr(y), N, gate.shape[0],
+                                               channels or cs, cs, H * W, exb_dtype_of(a), 1, cur_stream()))
+    return y
+
+
 def split_heads(ctx, x, anchors, values, y=None):
     """NHWC fp16 [N][H][W][cs] detection head -> fp32 [N][anchors][H*W][values] (Reshape + Transpose in one pass)."""
     t = _torch()

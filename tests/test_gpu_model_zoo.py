@@ -443,3 +443,21 @@ def test_split_heads_kernel(A, K, cs, hw):
     with pytest.raises(capi.ExbError):
         capi.split_heads(ctx, torch.from_numpy(x).cuda(), A + 1, cs)      # more channels than the tensor has
     ctx.close()
+
+
+@pytest.mark.parametrize("C,cs,gate_batch", [(64, 64, 3), (13, 16, 3), (40, 48, 1), (5, 5, 3)])
+def test_channel_gate_kernel_nhwc_f16(C, cs, gate_batch):
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    r = np.random.default_rng(C)
+    a = f16_round(r.standard_normal((3, 6, 5, cs)).astype(np.float32))
+    g = f16_round(r.uniform(0.5, 1.5, (gate_batch, 1, 1, cs)).astype(np.float32))
+    ad, gd = torch.from_numpy(a).cuda().half(), torch.from_numpy(g).cuda().half()
+    for op, fn in ((2, lambda x, y: x * y), (1, lambda x, y: x - y), (3, lambda x, y: x / y)):
+        for first in (False, True):
+            y = capi.binaryop_channel_bcast(ctx, ad, gd, op, first, channels=C).float().cpu().numpy()
+            want = fn(g, a) if first else fn(a, g)
+            np.testing.assert_allclose(y[..., :C], f16_round(want[..., :C].astype(np.float32)), rtol=1e-3, atol=1e-3)
+            assert not y[..., C:].any()
+    ctx.close()
