@@ -831,6 +831,25 @@ void fused_plan::build(int N, int C, int H, int W) {
             set_shape(y, x.N, x.C, PH, PW);
             y.cs = x.cs;
             const void* xin = form_f16(x);
+            // SPP: a stride-1 "same" max pooling of window k is the window-5 pooling of the window-(k-4) pooling of
+            // the same map (clipped windows compose exactly), 25 loads per output instead of k*k
+            auto same_max = [](const exb_pool_desc& q, int k) {
+                return q.type == 0 && !q.global_pool && q.kh == k && q.kw == k && q.stride_h == 1 && q.stride_w == 1 &&
+                       q.pad_t == k / 2 && q.pad_b == k / 2 && q.pad_l == k / 2 && q.pad_r == k / 2;
+            };
+            if (d.kh >= 9 && (d.kh & 1) && same_max(d, d.kh)) {
+                for (size_t j = 0; j < i; ++j) {
+                    if (lower_type(params_[j]) != "pooling" || absorbed[j] || root(in_ids[j][0]) != root(in_ids[i][0])) continue;
+                    auto* pj = dynamic_cast<operation_pooling<float>*>(ops_[j].get());
+                    const exb_pool_desc dj = pj->desc(x.N, x.H, x.W, x.C, x.cs, EXB_F16);
+                    fmap_info& yj = fmaps_[root(out_ids[j][0])];
+                    if (!same_max(dj, d.kh - 4) || !yj.produced || !yj.f16) continue;
+                    xin = form_f16(yj);
+                    d.kh = d.kw = 5;
+                    d.pad_t = d.pad_b = d.pad_l = d.pad_r = 2;
+                    break;
+                }
+            }
             void* y1 = form_f16(y);
             void* y2 = nullptr;
             const bool fuse_q = y.need_i8 && d.type == 0;   // max commutes with the monotone quantiser
