@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = [
     "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_pool2d_nchw_f32_static", "exb_eltwise_fwd", "exb_binaryop_fwd",
     "exb_binaryop_scalar_fwd", "exb_relu_fwd", "exb_activation_fwd", "exb_quantize_fwd",
     "exb_dequantize_fwd", "exb_concat_fwd", "exb_interp_nearest_fwd", "exb_channel_affine_fwd",
-    "exb_conv_weights_set_slopes", "exb_dw_weights_set_slopes", "exb_nhwc_f16_split_heads_f32", "exb_hardsigmoid_fwd", "exb_softmax_channels_f32", "exb_binaryop_channel_bcast_fwd", "exb_nchw_f16_to_nhwc4_padded", "exb_nchw_f32_focus_to_nhwc_f16", "exb_channel_affine_prelu_fwd", "exb_hardswish_fwd", "exb_focus_fwd", "exb_prelu_fwd", "exb_depth_to_space_fwd", "exb_transpose_hw_f32",
+    "exb_conv_weights_set_slopes", "exb_dw_weights_set_slopes", "exb_image_f32_to_nhwc_norm", "exb_nchw_f32_to_nhwc4_padded_norm", "exb_nhwc_f16_split_heads_f32", "exb_hardsigmoid_fwd", "exb_softmax_channels_f32", "exb_binaryop_channel_bcast_fwd", "exb_nchw_f16_to_nhwc4_padded", "exb_nchw_f32_focus_to_nhwc_f16", "exb_channel_affine_prelu_fwd", "exb_hardswish_fwd", "exb_focus_fwd", "exb_prelu_fwd", "exb_depth_to_space_fwd", "exb_transpose_hw_f32",
 ]
 
 
@@ -114,6 +114,8 @@ def lib():
         L.exb_softmax_channels_f32.argtypes = [vp, vp, vp, i32, i32, i64, i64, vp]
         L.exb_nchw_f16_to_nhwc4_padded.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
         L.exb_nhwc_f16_split_heads_f32.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        L.exb_image_f32_to_nhwc_norm.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, f32, i32, vp]
+        L.exb_nchw_f32_to_nhwc4_padded_norm.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp]
         L.exb_prelu_fwd.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i64, i32, i32, vp]
         L.exb_depth_to_space_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
         L.exb_transpose_hw_f32.argtypes = [vp, vp, vp, i64, i32, i32, vp]
@@ -502,6 +504,30 @@ def channel_affine_prelu(ctx, x, mul, add, slopes, channels=None, channel_last=T
         outer, inner = x.shape[0], max(int(np.prod(x.shape[2:])), 1)
     check(lib().exb_channel_affine_prelu_fwd(ctx.handle, ptr(x), ptr(y), ptr(mul), ptr(add), ptr(slopes), slopes.numel(),
                                              outer, Cc, cs, inner, exb_dtype_of(x), 1 if channel_last else 0, cur_stream()))
+    return y
+
+
+def image_ingest(ctx, x, dtype=EXB_F16, c_stride=16, mul=None, add=None, scale=1.0, rounding=1, y=None):
+    """fp32 NCHW image (<= 4 channels) -> optional x * mul[c] + add[c] -> NHWC fp16 / int8 with c_stride channels."""
+    t = _torch()
+    N, Cc, H, W = x.shape
+    if y is None:
+        y = t.empty((N, H, W, c_stride), dtype=torch_dtype(dtype), device=x.device)
+    check(lib().exb_image_f32_to_nhwc_norm(ctx.handle, ptr(x), ptr(y), dtype, N, Cc, H, W, c_stride,
+                                           None if mul is None else ptr(mul), None if add is None else ptr(add),
+                                           float(scale), int(rounding), cur_stream()))
+    return y
+
+
+def padded_ingest_norm(ctx, x, mul, add, w_pad=4, w_pitch=0, y=None):
+    """fp32 NCHW image (<= 3 channels) -> x * mul[c] + add[c] -> fp16 NHWC4 rows padded along W."""
+    t = _torch()
+    N, Cc, H, W = x.shape
+    w_pitch = w_pitch or (W + w_pad + 8 + 7) // 8 * 8
+    if y is None:
+        y = t.empty((N, H, w_pitch, 4), dtype=t.float16, device=x.device)
+    check(lib().exb_nchw_f32_to_nhwc4_padded_norm(ctx.handle, ptr(x), ptr(y), N, Cc, H, W, w_pad, w_pitch, ptr(mul), ptr(add),
+                                                  cur_stream()))
     return y
 
 

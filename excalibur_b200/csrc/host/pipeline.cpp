@@ -550,36 +550,49 @@ void fused_plan::build(int N, int C, int H, int W) {
             in.produced = true;      // consumed inside the fused kernel; it has no device form of its own
             finish_forms(fy, false);
         }
-        // Input normalisation in front of the ingest kernel: fp32 NCHW staging -> normalised copy.
-        const float* ingest_fixed = nullptr;
-        if (focus_op < 0 && input_norm_op >= 0) {
-            auto* inp = dynamic_cast<operation_input<float>*>(ops_[input_norm_op].get());
-            const float* mul = nullptr;
-            const float* add = nullptr;
-            inp->coefficients(C, &mul, &add);
-            float* norm = static_cast<float*>(norm_in_.ensure((size_t)N * C * H * W * 4, device_));
-            ingest_fixed = norm;
-            add_step(params_[input_norm_op].name_, [=](cudaStream_t st) {
-                exb_check(exb_channel_affine_fwd(ctx, static_cast<const float*>(this->ingest_src_), norm, mul, add, N, C, 0, (int64_t)H * W, EXB_F32, 0,
-                                                 EXB_ACT_NONE, st), "exb_channel_affine_fwd");
-            });
-        }
+        // Input normalisation: inside the ingest kernel where that kernel has a fused form (few-channel images),
+        // else a pass of its own from the fp32 staging buffer to a normalised copy.
         const bool direct_i8 = in.need_i8 && !in.need_f16;
         void* dst = focus_op >= 0 ? nullptr : (direct_i8 ? form_i8(in) : form_f16(in));
         const int cs = in.cs, w_pad = in.w_pad, w_pitch = in.w_pitch;
         const float s = in.i8_scale;
+        const float* nmul = nullptr;
+        const float* nadd = nullptr;
+        if (focus_op < 0 && input_norm_op >= 0)
+            dynamic_cast<operation_input<float>*>(ops_[input_norm_op].get())->coefficients(C, &nmul, &nadd);
+        const bool quad = padded && cs == 4 && C <= 3 && W % 4 == 0 && w_pad % 4 == 0 && w_pitch % 4 == 0;
+        const bool image = !padded && C <= 4 && (direct_i8 ? (cs == 16 || cs == 32) : (cs == 8 || cs == 16));
+        const float* ingest_fixed = nullptr;
+        if (nmul && !quad && !image) {
+            float* norm = static_cast<float*>(norm_in_.ensure((size_t)N * C * H * W * 4, device_));
+            ingest_fixed = norm;
+            add_step(params_[input_norm_op].name_, [=](cudaStream_t st) {
+                exb_check(exb_channel_affine_fwd(ctx, static_cast<const float*>(this->ingest_src_), norm, nmul, nadd, N, C, 0,
+                                                 (int64_t)H * W, EXB_F32, 0, EXB_ACT_NONE, st), "exb_channel_affine_fwd");
+            });
+        }
         if (focus_op >= 0) {
             // nothing else to ingest
         } else if (padded) {
-            ingest_f16_capable_ = !ingest_fixed && cs == 4 && C <= 3 && W % 4 == 0 && w_pad % 4 == 0 && w_pitch % 4 == 0;
+            ingest_f16_capable_ = quad && !nmul;
             add_step("ingest " + in.name, [=](cudaStream_t st) {
                 if (this->ingest_src_f16_)
                     exb_check(exb_nchw_f16_to_nhwc4_padded(ctx, this->ingest_src_, dst, N, C, H, W, w_pad, w_pitch, st),
                               "exb_nchw_f16_to_nhwc4_padded");
+                else if (quad && nmul)
+                    exb_check(exb_nchw_f32_to_nhwc4_padded_norm(ctx, static_cast<const float*>(this->ingest_src_), dst, N, C, H, W,
+                                                                w_pad, w_pitch, nmul, nadd, st),
+                              "exb_nchw_f32_to_nhwc4_padded_norm");
                 else
                     exb_check(exb_nchw_f32_to_nhwc_padded(ctx, ingest_fixed ? ingest_fixed : static_cast<const float*>(this->ingest_src_),
                                                           dst, EXB_F16, N, C, H, W, cs, w_pad, w_pitch, 1.f, 1, st),
                               "exb_nchw_f32_to_nhwc_padded");
+            });
+        } else if (image) {
+            add_step("ingest " + in.name, [=](cudaStream_t st) {
+                exb_check(exb_image_f32_to_nhwc_norm(ctx, static_cast<const float*>(this->ingest_src_), dst, direct_i8 ? EXB_I8 : EXB_F16,
+                                                     N, C, H, W, cs, nmul, nadd, direct_i8 ? s : 1.f, 1, st),
+                          "exb_image_f32_to_nhwc_norm");
             });
         } else {
             add_step("ingest " + in.name, [=](cudaStream_t st) {

@@ -106,12 +106,42 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_padded_kernel(const float* _
     }
 }
 
+// Few-channel image (C <= 4) into a dense channel-last tensor of CS physical channels: one thread per pixel, C
+// coalesced plane loads, optional y = x * mul[c] + add[c] (input normalisation, same fma as the stand-alone
+// pass), conversion, CS * sizeof(Out) / 16 vector stores with the padding channels zero.
+template <typename Out, int CS>
+__global__ void __launch_bounds__(256) image_to_nhwc_kernel(const float* __restrict__ x, Out* __restrict__ y, int N, int C,
+                                                            int64_t HW, const float* __restrict__ mul,
+                                                            const float* __restrict__ add, float scale, int rounding) {
+    const int64_t total = (int64_t)N * HW;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / HW, hw = i - n * HW;
+        alignas(16) Out v[CS];
+#pragma unroll
+        for (int c = 0; c < CS; ++c) v[c] = cvt_out<Out>(0.f, scale, rounding);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (c < C) {
+                float f = x[(n * C + c) * HW + hw];
+                if (mul) f = fmaf(f, mul[c], add[c]);
+                v[c] = cvt_out<Out>(f, scale, rounding);
+            }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(y + i * CS);
+#pragma unroll
+        for (int k = 0; k < (int)(CS * sizeof(Out) / 16); ++k) dst[k] = reinterpret_cast<const uint4*>(v)[k];
+    }
+}
+
 // The same conversion for fp16 NHWC4 when W, w_pad and w_pitch are multiples of 4: one thread per
 // four consecutive row slots, a 16-byte load from each plane and one 32-byte store; rows are
 // addressed by blockIdx.y so no division is left in the loop.
+// kNorm: y = x * mul[c] + add[c] first (input normalisation), an instantiation of its own.
+template <bool kNorm>
 __global__ void __launch_bounds__(256) nchw_to_nhwc4_f16_quad_kernel(const float* __restrict__ x, __half* __restrict__ y,
                                                                      int C, int H, int W, int w_pad, int w_pitch,
-                                                                     int64_t rows) {
+                                                                     int64_t rows, const float* __restrict__ mul,
+                                                                     const float* __restrict__ add) {
     const int quads = w_pitch >> 2;
     const int64_t plane = (int64_t)H * W;
     for (int64_t row = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; row < rows; row += (int64_t)gridDim.x * blockDim.y) {
@@ -124,7 +154,13 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc4_f16_quad_kernel(const float
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
                 v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (c < C && w >= 0 && w < W) v[c] = *reinterpret_cast<const float4*>(src + c * plane + w);
+                if (c < C && w >= 0 && w < W) {
+                    v[c] = *reinterpret_cast<const float4*>(src + c * plane + w);
+                    if (kNorm) {
+                        const float m = mul[c], a = add[c];
+                        v[c] = make_float4(fmaf(v[c].x, m, a), fmaf(v[c].y, m, a), fmaf(v[c].z, m, a), fmaf(v[c].w, m, a));
+                    }
+                }
             }
             uint32_t o[8];
 #define EXB_PACK(j, m)                                                            \
@@ -288,7 +324,8 @@ extern "C" int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x, void* y
         const int64_t rows = (int64_t)N * H;
         const dim3 block(64, 4);
         const int grid = (int)std::min<int64_t>((rows + 3) / 4, (int64_t)ctx->sm_count * 32);
-        nchw_to_nhwc4_f16_quad_kernel<<<grid, block, 0, st>>>(x, static_cast<__half*>(y), C, H, W, w_pad, w_pitch, rows);
+        nchw_to_nhwc4_f16_quad_kernel<false><<<grid, block, 0, st>>>(x, static_cast<__half*>(y), C, H, W, w_pad, w_pitch, rows,
+                                                                     nullptr, nullptr);
         return after_launch("nchw_to_nhwc4_f16_quad_kernel");
     }
     const int grid = stream_grid(ctx, (int64_t)N * H * w_pitch, 256, 16);
@@ -298,6 +335,48 @@ extern "C" int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x, void* y
     else return fail(EXB_ERR_UNSUPPORTED, "padded ingest supports EXB_F16 and EXB_I8 output");
 #undef EXB_LAUNCH
     return after_launch("nchw_to_nhwc_padded_kernel");
+}
+
+// Input normalisation fused into the ingest: y = convert(x * mul[c] + add[c]).
+extern "C" int exb_image_f32_to_nhwc_norm(exb_ctx* ctx, const float* x, void* y, int dtype, int N, int C, int H, int W,
+                                          int c_stride, const float* mul, const float* add, float scale, int rounding,
+                                          void* stream) {
+    if (int rc = check_dims(ctx, x, y, N, C, H, W, c_stride)) return rc;
+    EXB_REQUIRE((mul == nullptr) == (add == nullptr), "exb_image_f32_to_nhwc_norm: mul and add come together");
+    if (C > 4) return fail(EXB_ERR_UNSUPPORTED, "exb_image_f32_to_nhwc_norm takes images of up to 4 channels, got %d", C);
+    if (N == 0) return EXB_OK;
+    EXB_REQUIRE(aligned16(y), "exb_image_f32_to_nhwc_norm: misaligned output");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t HW = (int64_t)H * W;
+    const int grid = stream_grid(ctx, (int64_t)N * HW, 256, 16);
+    if (dtype == EXB_F16 && c_stride == 16)
+        image_to_nhwc_kernel<__half, 16><<<grid, 256, 0, st>>>(x, static_cast<__half*>(y), N, C, HW, mul, add, scale, rounding);
+    else if (dtype == EXB_F16 && c_stride == 8)
+        image_to_nhwc_kernel<__half, 8><<<grid, 256, 0, st>>>(x, static_cast<__half*>(y), N, C, HW, mul, add, scale, rounding);
+    else if (dtype == EXB_I8 && c_stride == 32)
+        image_to_nhwc_kernel<int8_t, 32><<<grid, 256, 0, st>>>(x, static_cast<int8_t*>(y), N, C, HW, mul, add, scale, rounding);
+    else if (dtype == EXB_I8 && c_stride == 16)
+        image_to_nhwc_kernel<int8_t, 16><<<grid, 256, 0, st>>>(x, static_cast<int8_t*>(y), N, C, HW, mul, add, scale, rounding);
+    else
+        return fail(EXB_ERR_UNSUPPORTED, "exb_image_f32_to_nhwc_norm: dtype %d with channel stride %d", dtype, c_stride);
+    return after_launch("image_to_nhwc_kernel");
+}
+
+extern "C" int exb_nchw_f32_to_nhwc4_padded_norm(exb_ctx* ctx, const float* x, void* y, int N, int C, int H, int W, int w_pad,
+                                                 int w_pitch, const float* mul, const float* add, void* stream) {
+    if (int rc = check_dims(ctx, x, y, N, C, H, W, 4)) return rc;
+    EXB_REQUIRE(w_pad >= 0 && w_pitch >= W + w_pad, "bad row padding (w_pad %d, w_pitch %d, W %d)", w_pad, w_pitch, W);
+    EXB_REQUIRE(mul != nullptr && add != nullptr, "exb_nchw_f32_to_nhwc4_padded_norm: null coefficients");
+    if (C > 3 || (W & 3) || (w_pad & 3) || (w_pitch & 3))
+        return fail(EXB_ERR_UNSUPPORTED, "exb_nchw_f32_to_nhwc4_padded_norm needs C <= 3 and W, w_pad, w_pitch multiples of 4");
+    if (N == 0) return EXB_OK;
+    EXB_REQUIRE(aligned16(x) && aligned16(y), "exb_nchw_f32_to_nhwc4_padded_norm: misaligned buffer");
+    const int64_t rows = (int64_t)N * H;
+    const dim3 block(64, 4);
+    const int grid = (int)std::min<int64_t>((rows + 3) / 4, (int64_t)ctx->sm_count * 32);
+    nchw_to_nhwc4_f16_quad_kernel<true><<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(x, static_cast<__half*>(y), C, H, W,
+                                                                                                w_pad, w_pitch, rows, mul, add);
+    return after_launch("nchw_to_nhwc4_f16_quad_kernel");
 }
 
 extern "C" int exb_nchw_f16_to_nhwc4_padded(exb_ctx* ctx, const void* x, void* y, int N, int C, int H, int W, int w_pad,

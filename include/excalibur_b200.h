@@ -103,6 +103,18 @@ EXB_API int exb_nchw_f32_to_nhwc(exb_ctx* ctx, const float* x_nchw, void* y_nhwc
 EXB_API int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x_nchw, void* y_nhwc, int dtype,
                                         int N, int C, int H, int W, int c_stride, int w_pad,
                                         int w_pitch, float scale, int rounding, void* stream);
+/* The two conversions above with the input normalisation of operation_input fused in
+ * (src/Excalibur/operation_input.cpp:92-96): y = convert(x * mul[c] + add[c]), device arrays of C entries, the
+ * same fma as exb_channel_affine_fwd followed by the same conversion, so the results equal the two-pass form.
+ * exb_image_f32_to_nhwc_norm: images of up to 4 channels into a dense channel-last tensor (EXB_F16 with
+ * c_stride 8 or 16, EXB_I8 with c_stride 16 or 32; mul == add == NULL skips the normalisation).
+ * exb_nchw_f32_to_nhwc4_padded_norm: the padded-row fp16 NHWC4 form (C <= 3; W, w_pad, w_pitch multiples of 4). */
+EXB_API int exb_image_f32_to_nhwc_norm(exb_ctx* ctx, const float* x_nchw, void* y_nhwc, int dtype, int N, int C,
+                                       int H, int W, int c_stride, const float* mul, const float* add,
+                                       float scale, int rounding, void* stream);
+EXB_API int exb_nchw_f32_to_nhwc4_padded_norm(exb_ctx* ctx, const float* x_nchw, void* y_nhwc, int N, int C, int H,
+                                              int W, int w_pad, int w_pitch, const float* mul, const float* add,
+                                              void* stream);
 /* The same for an image that is already fp16 NCHW (converted on the host so that half the bytes cross
  * PCIe; same round-to-nearest-even as the fp32 entry, so the results are identical): c_stride 4, fp16
  * output, C <= 3, W / w_pad / w_pitch multiples of 4. */

@@ -461,3 +461,35 @@ def test_channel_gate_kernel_nhwc_f16(C, cs, gate_batch):
             np.testing.assert_allclose(y[..., :C], f16_round(want[..., :C].astype(np.float32)), rtol=1e-3, atol=1e-3)
             assert not y[..., C:].any()
     ctx.close()
+
+
+@pytest.mark.parametrize("C", [1, 3, 4])
+def test_image_ingest_with_normalisation(C):
+    import torch
+    from excalibur_b200 import capi
+    ctx = capi.Context(0)
+    r = np.random.default_rng(C)
+    x = r.uniform(0, 255, (2, C, 9, 11)).astype(np.float32)
+    mul, add = r.uniform(0.005, 0.02, C).astype(np.float32), r.uniform(-2, 0, C).astype(np.float32)
+    xd, md, ad = torch.from_numpy(x).cuda(), torch.from_numpy(mul).cuda(), torch.from_numpy(add).cuda()
+    norm = capi.channel_affine(ctx, xd, md, ad, channel_last=False)                  # the stand-alone pass
+    # fp16, with and without normalisation: equal to normalise + generic ingest, bit for bit
+    for cs in (8, 16):
+        got = capi.image_ingest(ctx, xd, capi.EXB_F16, cs, md, ad)
+        want = capi.nchw_f32_to_nhwc(ctx, norm, capi.EXB_F16, cs)
+        assert torch.equal(got, want)
+        assert torch.equal(capi.image_ingest(ctx, xd, capi.EXB_F16, cs), capi.nchw_f32_to_nhwc(ctx, xd, capi.EXB_F16, cs))
+    # int8 with the quantiser's scale, half-to-even
+    for cs in (16, 32):
+        got = capi.image_ingest(ctx, xd, capi.EXB_I8, cs, md, ad, scale=37.0, rounding=1)
+        want = capi.nchw_f32_to_nhwc(ctx, norm, capi.EXB_I8, cs, 37.0, 1)
+        assert torch.equal(got, want)
+    with pytest.raises(capi.ExbError):
+        capi.image_ingest(ctx, torch.zeros((1, 5, 4, 4), device="cuda"), capi.EXB_F16, 16)
+    if C <= 3:
+        x4 = r.uniform(0, 255, (2, C, 6, 12)).astype(np.float32)
+        x4d = torch.from_numpy(x4).cuda()
+        got = capi.padded_ingest_norm(ctx, x4d, md, ad, 4, 24)
+        want = capi.nchw_f32_to_nhwc_padded(ctx, capi.channel_affine(ctx, x4d, md, ad, channel_last=False), capi.EXB_F16, 4, 4, 24)
+        assert torch.equal(got, want)
+    ctx.close()
