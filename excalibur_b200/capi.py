@@ -34,7 +34,7 @@ class ConvDesc(C.Structure):
         "res_dtype", "act")] + [("out_scale", C.c_float), ("out2_scale", C.c_float), ("impl", C.c_int32),
                                       ("x_w_pitch", C.c_int32), ("x_w_pad", C.c_int32), ("fuse_pool", C.c_int32),
                                       ("in_planar", C.c_int32), ("out_i8_planar", C.c_int32),
-                                      ("out_f16_planar", C.c_int32), ("res_planar", C.c_int32)]
+                                      ("out_f16_planar", C.c_int32), ("res_planar", C.c_int32), ("y_pitch", C.c_int32)]
 
 
 class DwConvDesc(C.Structure):
@@ -195,13 +195,13 @@ class Context:
 def make_conv_desc(N, H, W, Cin, Cout, k, stride=1, pad=0, in_dtype=EXB_F16, out_dtype=EXB_F16,
                    out2_dtype=-1, res=False, act=ACT_NONE, out_scale=1.0, out2_scale=1.0,
                    cin_stride=0, cout_stride=0, group=1, impl=0, x_w_pitch=0, x_w_pad=0, fuse_pool=0,
-                   in_planar=0, out_i8_planar=0, out_f16_planar=0, res_planar=0):
+                   in_planar=0, out_i8_planar=0, out_f16_planar=0, res_planar=0, y_pitch=0):
     kh, kw = (k, k) if isinstance(k, int) else k
     sh, sw = (stride, stride) if isinstance(stride, int) else stride
     pt, pb, pl, pr = (pad,) * 4 if isinstance(pad, int) else pad
     return ConvDesc(N, H, W, Cin, Cout, cin_stride, cout_stride, kh, kw, sh, sw, pt, pb, pl, pr, 1, group,
                     in_dtype, out_dtype, out2_dtype, EXB_F16 if res else -1, act, out_scale, out2_scale, impl, x_w_pitch, x_w_pad, fuse_pool,
-                    in_planar, out_i8_planar, out_f16_planar, res_planar)
+                    in_planar, out_i8_planar, out_f16_planar, res_planar, y_pitch)
 
 
 class ConvWeights:

@@ -76,6 +76,14 @@ int resolve(const exb_conv_desc* d, ConvGeom& g) {
         EXB_REQUIRE(g.out_dtype == EXB_I8 || g.out2_dtype == EXB_I8, "out_i8_planar without an int8 output");
         EXB_REQUIRE(g.in_planar || g.pool, "out_i8_planar is available with in_planar = 1 or fuse_pool = 1 only");
     }
+    g.y_pitch = d->y_pitch ? d->y_pitch : g.cout_stride;
+    if (g.y_pitch != g.cout_stride) {
+        EXB_REQUIRE(g.y_pitch > g.cout_stride && g.y_pitch % 16 == 0 && g.cout_stride % 16 == 0,
+                    "y_pitch %d needs to be a multiple of 16 above cout_stride %d, itself a multiple of 16", g.y_pitch, g.cout_stride);
+        if (g.out_dtype != EXB_F16 || g.out2_dtype != -1 || g.has_res || g.pool || g.in_planar || g.out_i8_planar ||
+            g.out_f16_planar || g.res_planar)
+            return fail(EXB_ERR_UNSUPPORTED, "y_pitch is implemented for one fp16 output without residual, pooling or planar16 tensors");
+    }
     return EXB_OK;
 }
 
@@ -238,6 +246,8 @@ extern "C" int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* 
         return fail(EXB_ERR_UNSUPPORTED, "planar16 tensors need the tensor-core kernel");
     if (g.in_planar && !conv_tc_halo_ok(ctx, g))
         return fail(EXB_ERR_UNSUPPORTED, "planar16 input is not available for this convolution (see exb_conv2d_accepts_planar_input)");
+    if (g.y_pitch != g.cout_stride && !(d->impl != 1 && conv_tc_eligible(g)))
+        return fail(EXB_ERR_UNSUPPORTED, "y_pitch needs the tensor-core kernel");
     if (d->impl != 1 && conv_tc_eligible(g)) return conv_tc_launch(ctx, g, x, w, residual, y, y2, st);
     return conv_direct_launch(ctx, g, x, w, residual, y, y2, st);
 }

@@ -34,6 +34,7 @@ struct ConvGeom {
     int PH, PW;
     int in_planar, out_i8_planar;   // planar16 int8 input / int8 output (see exb_conv_desc)
     int out_f16_planar, res_planar; // planar16 fp16 output / residual
+    int y_pitch;                    // elements between output pixels of y (== cout_stride unless y is a slice of a wider tensor)
 };
 
 // "Folded" K layout for convolutions with very few input channels (a stem): one K row of an
@@ -78,6 +79,7 @@ struct EpiParams {
     int out_dtype, out2_dtype, act;
     float out_scale, out2_scale;
     int cout_stride;
+    int y_pitch;     // elements between output pixels of y / y2
     int i8_planar;   // the int8 output (y or y2) is planar16
     int f16_planar;  // the fp16 output (y or y2) is planar16
     int res_planar;  // the residual is planar16 fp16

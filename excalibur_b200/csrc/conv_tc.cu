@@ -740,7 +740,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 ptx::tmem_ld_wait();
                 const int cl = tc.ntile * p.BN + chunk * 16;   // first channel of the chunk
                 if (!valid || cl >= p.e.cout_stride || (kDbg & 1)) continue;
-                const int64_t off = pix * p.e.cout_stride + cl;
+                const int64_t off = pix * p.e.y_pitch + cl;
                 // planar16: [n][channel slice][oh][ow][16]
                 int64_t off8 = off;
                 if constexpr (kHalo) {   // only this instantiation (and the pooling one) can write planar16
@@ -1067,7 +1067,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.has_res = g.has_res;
     p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.slope = w->d_slope; p.e.residual = static_cast<const __half*>(residual);
     p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;
-    p.e.out_scale = g.out_scale; p.e.out2_scale = g.out2_scale; p.e.cout_stride = g.cout_stride;
+    p.e.out_scale = g.out_scale; p.e.out2_scale = g.out2_scale; p.e.cout_stride = g.cout_stride; p.e.y_pitch = g.y_pitch;
     p.e.i8_planar = g.out_i8_planar;
     p.e.f16_planar = g.out_f16_planar;
     p.e.res_planar = g.res_planar;

@@ -309,6 +309,10 @@ void fused_plan::build(int N, int C, int H, int W) {
         int pool = -1;          // 3x3/2 max pooling op applied in the conv epilogue
         int bn = -1;            // BatchNorm op folded into the conv's weights and bias
         int slope_op = -1;      // PReLU / LeakyRelu op applied in the epilogue (act == EXB_ACT_PRELU)
+        int cat = -1;           // Concat op whose output this group writes its channels into (epilogue stores at a
+        int cat_off = 0;        // channel offset instead of a copy kernel); cat_total = channels of that output
+        int cat_total = 0;
+        int cat_bn = -1;        // BatchNorm behind that Concat, folded slice-wise into the producers
         int out = -1;           // root featmap the group finally produces
         int exec_at = -1;       // index of the last absorbed op
     };
@@ -334,15 +338,15 @@ void fused_plan::build(int N, int C, int H, int W) {
         return -1;
     };
     // host slopes of a PReLU / LeakyRelu op, one per channel
-    auto slopes_of_op = [&](int j, int channels) -> std::vector<float> {
+    auto slopes_of_op = [&](int j, int channels, int first = 0) -> std::vector<float> {
         std::vector<float> sl((size_t)channels);
         if (lower_type(params_[j]) == "leakyrelu") {
             const float a = dynamic_cast<operation_leakyrelu<float>*>(ops_[j].get())->alpha_;
             for (auto& v : sl) v = a;
         } else {
             auto* pr = dynamic_cast<operation_prelu<float>*>(ops_[j].get());
-            if (pr->num_slope_ != 1) CHECK_EQ(pr->num_slope_, channels) << params_[j].name_ << ": slopes do not match the channels";
-            for (int c = 0; c < channels; ++c) sl[c] = pr->slopes_cpu()[pr->num_slope_ == 1 ? 0 : c];
+            if (pr->num_slope_ != 1) CHECK_GE(pr->num_slope_, first + channels) << params_[j].name_ << ": slopes do not match the channels";
+            for (int c = 0; c < channels; ++c) sl[c] = pr->slopes_cpu()[pr->num_slope_ == 1 ? 0 : first + c];
         }
         return sl;
     };
@@ -457,6 +461,65 @@ void fused_plan::build(int N, int C, int H, int W) {
             }
         }
         groups[i] = g;
+    }
+    // Concat as the producers' epilogue stores: every input comes from a dense convolution group (no residual,
+    // no fused pooling) that nothing else reads and whose channel count is a multiple of 16.  A BatchNorm (+
+    // activation) behind such a Concat of activation-free convolutions is folded slice by slice into them
+    // (the BottleneckCSP tail: conv, conv -> Concat -> BatchNorm -> LeakyRelu).
+    std::vector<int> cat_left(n_ops, 0);      // producers of a direct Concat still to be emitted
+    for (size_t k = 0; k < n_ops; ++k) {
+        if (absorbed[k] || lower_type(params_[k]) != "concat") continue;
+        auto* cc = dynamic_cast<operation_concat<float>*>(ops_[k].get());
+        if (!cc || !cc->is_channel_concat() || in_ids[k].size() < 2) continue;
+        std::vector<int> prod;
+        bool ok = true, plain = true;
+        int total = 0;
+        for (int f : in_ids[k]) {
+            const int rf = root(f);
+            int gi = -1;
+            for (size_t i = 0; i < k; ++i)
+                if (groups[i].conv >= 0 && groups[i].out == rf) gi = (int)i;
+            if (gi < 0 || sole_consumer(rf) != (int)k || std::find(prod.begin(), prod.end(), gi) != prod.end()) { ok = false; break; }
+            const group& g = groups[gi];
+            auto* conv = dynamic_cast<operation_convolution<float>*>(ops_[g.conv].get());
+            if (lower_type(params_[g.conv]) != "convolution" || !conv || conv->group_ != 1 || g.residual >= 0 || g.pool >= 0 ||
+                g.cat >= 0 || conv->output_channel_ % 16 != 0 || conv->stride_h_ != conv->stride_w_ ||
+                (conv->stride_h_ != 1 && conv->stride_h_ != 2)) { ok = false; break; }
+            plain = plain && g.act == EXB_ACT_NONE && g.bn < 0;
+            prod.push_back(gi);
+            total += conv->output_channel_;
+        }
+        if (!ok) continue;
+        int out = root(out_ids[k][0]), bn_op = -1, act = EXB_ACT_NONE, slope_op = -1;
+        if (plain) {
+            const int j = sole_consumer(out);
+            if (j > (int)k && !absorbed[j] && lower_type(params_[j]) == "batchnorm" &&
+                dynamic_cast<operation_batchnorm<float>*>(ops_[j].get())->channels_ == total) {
+                bn_op = j;
+                absorbed[j] = 1;
+                out = root(out_ids[j][0]);
+                const int a = sole_consumer(out);
+                if (a > j && !absorbed[a] && in_ids[a].size() == 1 && act_of_op(a) > 0) {
+                    act = act_of_op(a);
+                    if (act == EXB_ACT_PRELU) slope_op = a;
+                    absorbed[a] = 1;
+                    out = root(out_ids[a][0]);
+                }
+            }
+        }
+        absorbed[k] = 1;
+        int off = 0;
+        for (int gi : prod) {
+            group& g = groups[gi];
+            g.cat = (int)k;
+            g.cat_off = off;
+            g.cat_total = total;
+            g.cat_bn = bn_op;
+            if (bn_op >= 0) { g.act = act; g.slope_op = slope_op; }
+            g.out = out;
+            off += dynamic_cast<operation_convolution<float>*>(ops_[g.conv].get())->output_channel_;
+        }
+        cat_left[k] = (int)prod.size();
     }
     // Which op index triggers which group (a group runs where its last op stood).
     std::vector<int> run_group_at(n_ops, -1);
@@ -687,6 +750,43 @@ void fused_plan::build(int N, int C, int H, int W) {
         d.fuse_pool = g.pool >= 0 ? 1 : 0;
         int OH, OW;
         exb_check(exb_conv_out_dims(&d, &OH, &OW), "exb_conv_out_dims");
+        if (g.cat >= 0) {
+            // this group's channels are a slice of a Concat's output: stored there by the epilogue
+            const int Cout = conv->output_channel_;
+            if (y.N == 0) {
+                y.need_f16 = true;
+                set_shape(y, x.N, g.cat_total, OH, OW);
+                void* whole = form_f16(y);
+                // the padding channels are never written afterwards and must stay finite
+                if (y.cs > g.cat_total) CUDA_CHECK(cudaMemset(whole, 0, (size_t)y.N * y.H * y.W * y.cs * 2));
+            } else if (y.N != x.N || y.H != OH || y.W != OW) {
+                PLAN_REFUSE << "(Concat " << params_[g.cat].name_ << ": operands differ in shape)";
+            }
+            d.out_dtype = EXB_F16;
+            d.cout_stride = Cout;
+            d.y_pitch = y.cs;
+            const void* xin = int8 ? int8_form_for(x, conv->act_scale()) : form_f16(x);
+            void* y1 = static_cast<char*>(form_f16(y)) + (size_t)g.cat_off * 2;
+            exb_conv_weights* w = nullptr;
+            if (g.cat_bn >= 0) {
+                auto* cbn = dynamic_cast<operation_batchnorm<float>*>(ops_[g.cat_bn].get());
+                const float* m = cbn->mul()->cpu_data() + g.cat_off;
+                w = conv->packed(ctx, d, m, cbn->add()->cpu_data() + g.cat_off, m);
+            } else {
+                const operation_batchnorm<float>* own = g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;
+                w = own ? conv->packed(ctx, d, own->mul()->cpu_data(), own->add()->cpu_data(), own) : conv->packed(ctx, d);
+            }
+            if (g.act == EXB_ACT_PRELU) {
+                // slopes of an activation behind the Concat are indexed by the Concat's channels
+                const std::vector<float> sl = slopes_of_op(g.slope_op, Cout, g.cat_bn >= 0 ? g.cat_off : 0);
+                exb_check(exb_conv_weights_set_slopes(ctx, w, sl.data(), (int)sl.size()), "exb_conv_weights_set_slopes");
+            }
+            add_step(params_[i].name_, [=](cudaStream_t st) {
+                exb_check(exb_conv2d_fwd(ctx, &d, xin, w, nullptr, y1, nullptr, st), "exb_conv2d_fwd");
+            });
+            if (--cat_left[g.cat] == 0) finish_forms(y, false);
+            return;
+        }
         set_shape(y, x.N, conv->output_channel_, OH, OW);
         if (conv->group_ != 1) CHECK_EQ(x.cs, x.C) << "grouped convolution needs unpadded channels";
         d.cout_stride = y.cs;

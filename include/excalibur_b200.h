@@ -190,6 +190,12 @@ typedef struct exb_conv_desc {
      * tensor-core kernel (exb_conv2d_uses_tensor_cores); int8 and fp32 outputs are not affected. */
     int32_t out_f16_planar;
     int32_t res_planar;
+    /* Elements between consecutive output pixels of y, 0 = cout_stride.  A larger value lets the convolution
+     * write its cout_stride channels into a slice of a wider channel-last tensor (the caller passes y already
+     * offset to the slice's first channel): a Concat becomes the producers' epilogue stores
+     * (operation_concat, src/Excalibur/operation_concat.cpp:30-80).  Needs the tensor-core kernel, one fp16
+     * output, no residual, cout_stride % 16 == 0 and y_pitch % 16 == 0. */
+    int32_t y_pitch;
 } exb_conv_desc;
 
 /* Output spatial size: (in + pad_a + pad_b - k) / stride + 1

@@ -493,3 +493,75 @@ def test_image_ingest_with_normalisation(C):
         want = capi.nchw_f32_to_nhwc_padded(ctx, capi.channel_affine(ctx, x4d, md, ad, channel_last=False), capi.EXB_F16, 4, 4, 24)
         assert torch.equal(got, want)
     ctx.close()
+
+
+@pytest.mark.parametrize("int8", [False, True], ids=["fp16", "int8"])
+def test_conv_writes_a_channel_slice_of_a_wider_tensor(int8):
+    """y_pitch: two convolutions store their channels side by side in one tensor (a Concat without a copy)."""
+    import torch
+    from excalibur_b200 import capi
+    from tests.util import dev, host, to_nhwc, to_nchw, assert_close_f16, quant_weights
+    ctx = capi.Context(0)
+    r = np.random.default_rng(5)
+    N, Cin, H, W, pitch = 2, 32, 11, 9, 96
+    outs, refs = [], []
+    ybuf = torch.full((N, H, W, pitch), 9.0, dtype=torch.float16, device="cuda")
+    off = 0
+    for Cout, k in ((32, 3), (48, 1)):
+        b = (r.standard_normal(Cout) * 0.1).astype(np.float32)
+        if int8:
+            xq = r.integers(-128, 128, (N, Cin, H, W)).astype(np.int8)
+            wq, ws = quant_weights((r.standard_normal((Cout, Cin, k, k)) * 0.05).astype(np.float32))
+            fs = np.float32(25.0)
+            ref = O.dequantize(O.conv2d_i8_acc(xq, wq, 1, k // 2), O.dequant_scales(ws, fs, Cout), b)
+            d = capi.make_conv_desc(N, H, W, Cin, Cout, k, 1, k // 2, capi.EXB_I8, capi.EXB_F16, cout_stride=Cout, y_pitch=pitch)
+            wp = capi.ConvWeights(ctx, d, wq, b, ws, fs)
+            xin = dev(to_nhwc(xq))
+        else:
+            x = f16_round(r.uniform(-1, 1, (N, Cin, H, W)))
+            w = f16_round(r.standard_normal((Cout, Cin, k, k)) * 0.1)
+            ref = O.conv2d_f32(x, w, b, 1, k // 2)
+            d = capi.make_conv_desc(N, H, W, Cin, Cout, k, 1, k // 2, capi.EXB_F16, capi.EXB_F16, cout_stride=Cout, y_pitch=pitch)
+            wp = capi.ConvWeights(ctx, d, w, b)
+            xin = dev(to_nhwc(x).astype(np.float16))
+        capi.conv2d(ctx, d, xin, wp, y=ybuf[..., off:])
+        ctx.sync_check()
+        refs.append((off, Cout, ref))
+        off += Cout
+    yh = ybuf.float().cpu().numpy()
+    for o, c, ref in refs:
+        assert_close_f16(to_nchw(yh[..., o:o + c], c), ref, what="slice at %d" % o)
+    assert (yh[..., off:] == 9.0).all(), "channels beyond the slices must be left alone"
+    bad = capi.make_conv_desc(N, H, W, Cin, 32, 3, 1, 1, capi.EXB_F16, capi.EXB_F16, res=True, cout_stride=32, y_pitch=pitch)
+    with pytest.raises(capi.ExbError):
+        capi.conv2d(ctx, bad, xin, capi.ConvWeights(ctx, bad, np.zeros((32, Cin, 3, 3), np.float32), None), ybuf, y=ybuf)
+    ctx.close()
+
+
+def test_concat_of_convolutions_is_written_by_their_epilogues():
+    """BottleneckCSP tail conv, conv -> Concat -> BatchNorm -> LeakyRelu: two launches, not five."""
+    h = _host()
+    r = np.random.default_rng(2)
+    g = GraphBuilder()
+    g.split("s", "in", ["a", "b"])
+    w1 = (r.standard_normal((32, 16, 1, 1)) * 0.2).astype(np.float32)
+    w2 = (r.standard_normal((48, 16, 3, 3)) * 0.1).astype(np.float32)
+    g.conv("c1", "a", "y1", w1, None, 1, 0)
+    g.conv("c2", "b", "y2", w2, None, 1, 1)
+    g.concat("cat", ["y1", "y2"], "c")
+    bn = [r.uniform(0.5, 1.5, 80), r.standard_normal(80) * 0.1, r.uniform(0.5, 1.5, 80), r.standard_normal(80) * 0.1]
+    bn = [v.astype(np.float32) for v in bn]
+    g.batchnorm("bn", "c", "n", *bn, eps=1e-5)
+    g.leakyrelu("act", "n", "out", 0.1)
+    x = f16_round(r.uniform(-1, 1, (2, 16, 9, 10)).astype(np.float32))
+    cat = np.concatenate([O.conv2d_f32(x, f16_round(w1), None, 1, 0), O.conv2d_f32(x, f16_round(w2), None, 1, 1)], axis=1)
+    mul, add = O.batchnorm_coeffs(*bn, eps=1e-5)
+    want = O.leakyrelu(O.channel_affine(cat, mul, add), 0.1)
+    for fusion in (True, False):
+        p = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=fusion)
+        out = p.forward(x)["out"]
+        assert _rel(out, want) < 1e-2, (fusion, _rel(out, want))
+        if fusion:
+            launches, _ = p.stats()
+            assert launches == 4, launches          # ingest, two convolutions, emit
+        p.close()
