@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = [
     "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_pool2d_nchw_f32_static", "exb_eltwise_fwd", "exb_binaryop_fwd",
     "exb_binaryop_scalar_fwd", "exb_relu_fwd", "exb_activation_fwd", "exb_quantize_fwd",
     "exb_dequantize_fwd", "exb_concat_fwd", "exb_interp_nearest_fwd", "exb_channel_affine_fwd",
-    "exb_conv_weights_set_slopes", "exb_dw_weights_set_slopes", "exb_image_f32_to_nhwc_norm", "exb_nchw_f32_to_nhwc4_padded_norm", "exb_nhwc_f16_split_heads_f32", "exb_hardsigmoid_fwd", "exb_softmax_channels_f32", "exb_binaryop_channel_bcast_fwd", "exb_nchw_f16_to_nhwc4_padded", "exb_nchw_f32_focus_to_nhwc_f16", "exb_channel_affine_prelu_fwd", "exb_hardswish_fwd", "exb_focus_fwd", "exb_prelu_fwd", "exb_depth_to_space_fwd", "exb_transpose_hw_f32",
+    "exb_conv_weights_set_slopes", "exb_dw_weights_set_slopes", "exb_depth_to_space_nchw_f32", "exb_image_f32_to_nhwc_norm", "exb_nchw_f32_to_nhwc4_padded_norm", "exb_nhwc_f16_split_heads_f32", "exb_hardsigmoid_fwd", "exb_softmax_channels_f32", "exb_binaryop_channel_bcast_fwd", "exb_nchw_f16_to_nhwc4_padded", "exb_nchw_f32_focus_to_nhwc_f16", "exb_channel_affine_prelu_fwd", "exb_hardswish_fwd", "exb_focus_fwd", "exb_prelu_fwd", "exb_depth_to_space_fwd", "exb_transpose_hw_f32",
 ]
 
 

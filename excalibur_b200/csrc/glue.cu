@@ -381,6 +381,27 @@ __global__ void __launch_bounds__(kThreads) split_heads_kernel(const __half* __r
     }
 }
 
+
+// Depth-to-space of a channel-last fp16 tensor straight into an fp32 NCHW tensor (a transposed convolution whose
+// result leaves the network): y[n][c][h*rh + a][w*rw + b] = x[n][h][w][(a*rw + b)*C + c].  One thread per output
+// value, the output column fastest: writes are contiguous, reads of neighbouring threads fall into the same pixel.
+__global__ void __launch_bounds__(kThreads) depth_to_space_nchw_f32_kernel(const __half* __restrict__ x, float* __restrict__ y,
+                                                                           int N, int H, int W, int rh, int rw, int C, int xs) {
+    const int OH = H * rh, OW = W * rw;
+    const int64_t work = (int64_t)N * C * OH * OW;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < work; i += step) {
+        const int ox = (int)(i % OW);
+        int64_t p = i / OW;
+        const int oy = (int)(p % OH);
+        p /= OH;
+        const int c = (int)(p % C);
+        const int n = (int)(p / C);
+        const int h = oy / rh, a = oy - h * rh, w = ox / rw, b = ox - w * rw;
+        y[i] = __half2float(x[(((int64_t)n * H + h) * W + w) * xs + (a * rw + b) * C + c]);
+    }
+}
+
 }  // namespace
 }  // namespace exb
 
@@ -701,4 +722,18 @@ extern "C" int exb_nhwc_f16_split_heads_f32(exb_ctx* ctx, const void* x, float* 
     split_heads_kernel<<<stream_grid(ctx, rows * 32, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(x), y, rows, P, c_stride, A, K);
     return after_launch("exb_nhwc_f16_split_heads_f32");
+}
+
+extern "C" int exb_depth_to_space_nchw_f32(exb_ctx* ctx, const void* x, float* y, int N, int H, int W, int rh, int rw, int C,
+                                           int x_stride, void* stream) {
+    EXB_REQUIRE(ctx != nullptr, "null context");
+    EXB_REQUIRE(N >= 0 && H >= 0 && W >= 0 && rh > 0 && rw > 0 && C > 0, "exb_depth_to_space_nchw_f32: bad shape");
+    const int xs = x_stride ? x_stride : rh * rw * C;
+    EXB_REQUIRE(xs >= rh * rw * C, "exb_depth_to_space_nchw_f32: stride smaller than channel count");
+    const int64_t work = (int64_t)N * C * H * rh * W * rw;
+    if (work == 0) return EXB_OK;
+    EXB_REQUIRE(x && y, "exb_depth_to_space_nchw_f32: null buffer");
+    depth_to_space_nchw_f32_kernel<<<stream_grid(ctx, work, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), y, N, H, W, rh, rw, C, xs);
+    return after_launch("exb_depth_to_space_nchw_f32");
 }

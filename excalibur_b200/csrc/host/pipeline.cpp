@@ -713,11 +713,37 @@ void fused_plan::build(int N, int C, int H, int W) {
             exb_conv_desc d = dc->inner_desc(x.N, x.H, x.W, x.cs);
             d.act = g.act;       // element-wise, so it commutes with the depth-to-space copy
             d.cout_stride = round_up(d.Cout, d.Cout > 16 ? 32 : 16);
-            y.need_f16 = true;
-            set_shape(y, x.N, Cout, x.H * rh, x.W * rw);
             const void* xin = form_f16(x);
             auto mid = std::make_shared<dev_buf>();
             void* tmp = mid->ensure((size_t)x.N * x.H * x.W * d.cout_stride * 2, device_);
+            // a few-channel result that only leaves the network: scattered straight into the fp32 NCHW output
+            // instead of a 16-channel-padded fp16 map that an export kernel would read back
+            const bool to_output = Cout <= 8 && output_roots.count(g.out) && consumers[g.out].empty() && !y.need_i8;
+            if (to_output) {
+                const operation_batchnorm<float>* obn =
+                    g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;
+                exb_conv_weights* ow = obn ? dc->packed(ctx, d, obn->mul()->cpu_data(), obn->add()->cpu_data(), obn) : dc->packed(ctx, d);
+                if (g.act == EXB_ACT_PRELU) {
+                    const std::vector<float> sl = slopes_of_op(g.slope_op, Cout);
+                    std::vector<float> rep((size_t)d.Cout);
+                    for (int c = 0; c < d.Cout; ++c) rep[c] = sl[c % Cout];
+                    exb_check(exb_conv_weights_set_slopes(ctx, ow, rep.data(), (int)rep.size()), "exb_conv_weights_set_slopes");
+                }
+                y.f32_only = y.need_f32 = true;
+                y.N = x.N; y.C = Cout; y.H = x.H * rh; y.W = x.W * rw; y.cs = Cout;
+                float* dst = static_cast<float*>(form_f32(y));
+                const int n = x.N, h = x.H, wd = x.W, xs = d.cout_stride;
+                add_step(params_[i].name_, [=](cudaStream_t st) {
+                    (void)mid;
+                    exb_check(exb_conv2d_fwd(ctx, &d, xin, ow, nullptr, tmp, nullptr, st), "exb_conv2d_fwd");
+                    exb_check(exb_depth_to_space_nchw_f32(ctx, tmp, dst, n, h, wd, rh, rw, Cout, xs, st),
+                              "exb_depth_to_space_nchw_f32");
+                }, 2);
+                y.produced = true;
+                return;
+            }
+            y.need_f16 = true;
+            set_shape(y, x.N, Cout, x.H * rh, x.W * rw);
             void* yo = form_f16(y);
             const operation_batchnorm<float>* bn =
                 g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;

@@ -431,6 +431,10 @@ EXB_API int exb_depth_to_space_fwd(exb_ctx* ctx, const void* x, void* y, int N, 
  * (N, A, K, H*W) followed by operation_transpose 1,0,2 (the tail of the shipped yolov5s_simp description). */
 EXB_API int exb_nhwc_f16_split_heads_f32(exb_ctx* ctx, const void* x, float* y, int N, int P, int c_stride, int A,
                                          int K, void* stream);
+/* The same scatter from a channel-last fp16 x straight into an fp32 NCHW y (a transposed convolution whose result
+ * is a network output): y[n][c][h*rh + a][w*rw + b] = x[n][h][w][(a*rw + b)*C + c]. */
+EXB_API int exb_depth_to_space_nchw_f32(exb_ctx* ctx, const void* x, float* y, int N, int H, int W, int rh, int rw,
+                                        int C, int x_stride, void* stream);
 /* y[p][w][h] = x[p][h][w] for `planes` fp32 planes: operation_transpose with permutation 1,0,2
  * (src/Excalibur/operation_transpose.cpp:47-66). */
 EXB_API int exb_transpose_hw_f32(exb_ctx* ctx, const float* x, float* y, int64_t planes, int H, int W,
