@@ -85,3 +85,23 @@ def test_weight_file_covers_every_record_of_the_builders():
         for op in ops:
             pos += racy_record_size(op, blob, pos)
         assert pos == len(blob), fn.__name__
+
+
+def test_structure_fixture_round_trips_through_the_graph_generator():
+    """tests/golden/shipped_architectures.json -> graph_from_structure -> structure gives the fixture back, and
+    the generated weight file holds exactly the records the graph consumes."""
+    import json
+    from excalibur_b200.calibrate import parse_phai, racy_record_size
+    with open(os.path.join(os.path.dirname(__file__), "golden", "shipped_architectures.json")) as f:
+        archs = json.load(f)
+    assert len(archs) == 15
+    for a in archs:
+        g, outs = model_zoo.graph_from_structure(a["structure"], a["seed"], gain=a["gain"])
+        assert outs == a["outputs"], a["name"]
+        again = json.loads(json.dumps(model_zoo.structure(g.phai_text())))
+        assert again == json.loads(json.dumps(a["structure"])), a["name"]
+        _, ops = parse_phai(g.phai_text())
+        blob, pos = g.racy_bytes(), 0
+        for op in ops:
+            pos += racy_record_size(op, blob, pos)
+        assert pos == len(blob), a["name"]
