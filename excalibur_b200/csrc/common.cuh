@@ -24,12 +24,16 @@ namespace exb {
 // Record a message for exb_last_error_string() and return `code`.
 int fail(int code, const char* fmt, ...);
 
+// A failing runtime call is reported once and cleared (cudaGetLastError), so that it cannot be blamed on the next
+// launch's check.
 #define EXB_CUDA_TRY(expr)                                                                  \
     do {                                                                                    \
         cudaError_t e__ = (expr);                                                           \
-        if (e__ != cudaSuccess)                                                             \
+        if (e__ != cudaSuccess) {                                                           \
+            (void)cudaGetLastError();                                                       \
             return ::exb::fail(EXB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                \
                                cudaGetErrorString(e__), __FILE__, __LINE__);                \
+        }                                                                                   \
     } while (0)
 
 #define EXB_REQUIRE(cond, ...)                                                              \
@@ -37,8 +41,11 @@ int fail(int code, const char* fmt, ...);
         if (!(cond)) return ::exb::fail(EXB_ERR_BAD_ARG, __VA_ARGS__);                      \
     } while (0)
 
+// Launch check.  cudaGetLastError returns AND clears the calling thread's error: a launch that was refused (or an
+// error some other code of the process left behind) is reported by this call only and does not make every later
+// launch of the library fail.  Sticky errors (a faulted context) keep coming back from the runtime by themselves.
 inline int after_launch(const char* what) {
-    cudaError_t e = cudaPeekAtLastError();
+    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
         return fail(EXB_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
     return EXB_OK;
@@ -76,6 +83,7 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     case EXB_ACT_RELU: return v >= 0.f ? v : 0.f;
     case EXB_ACT_RELU6_QUIRK: return (v >= 0.f && v <= 6.f) ? v : 0.f;
     case EXB_ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
+    case EXB_ACT_MISH: return v * tanhf(v > 20.f ? v : log1pf(expf(v)));   // ln(1 + e^v) = v to fp32 accuracy above 20
     case EXB_ACT_RELU6: return fminf(fmaxf(v, 0.f), 6.f);
     case EXB_ACT_SILU: return v / (1.f + __expf(-v));
     case EXB_ACT_HARDSWISH: return v * fminf(fmaxf(fmaf(v, 1.f / 6.f, 0.5f), 0.f), 1.f);
@@ -105,7 +113,7 @@ __device__ __forceinline__ void apply_act_vec(float (&v)[N], int act) {
 
 inline bool act_supported(int act) {
     return act == EXB_ACT_NONE || act == EXB_ACT_RELU || act == EXB_ACT_RELU6_QUIRK ||
-           act == EXB_ACT_SIGMOID || act == EXB_ACT_RELU6 || act == EXB_ACT_SILU || act == EXB_ACT_HARDSWISH;
+           act == EXB_ACT_SIGMOID || act == EXB_ACT_MISH || act == EXB_ACT_RELU6 || act == EXB_ACT_SILU || act == EXB_ACT_HARDSWISH;
 }
 
 // Grid for a bandwidth-bound grid-stride kernel: enough CTAs to fill every SM a few times

@@ -198,6 +198,7 @@ int operation_convolution<Dtype>::exb_activation() const {
     case 1: return EXB_ACT_RELU;
     case 3: return EXB_ACT_RELU6_QUIRK;
     case 4: return EXB_ACT_SIGMOID;
+    case 5: return EXB_ACT_MISH;
     default: NOT_IMPLEMENTED << " (convolution activation type " << this->activation_type_ << ")";
     }
     return EXB_ACT_NONE;
@@ -671,6 +672,23 @@ void operation_relu<Dtype>::forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms
 }
 INSTANCE_CLASS(operation_relu);
 REGISTE(operation_relu);
+
+template <typename Dtype>
+operation_relu6<Dtype>::operation_relu6(const operation_param& param) : operation<Dtype>(param) {
+    for (const auto& kv : param_list(param.specific_params_).kv)
+        if (kv.first != 0 && kv.first != 1 && kv.first != -23330) LOG(FATAL) << "Un-supported ReLU6 Attribution " << kv.first;
+    this->params_.inplace_ = true;
+}
+template <typename Dtype>
+void operation_relu6<Dtype>::forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops) {
+    act_run<float>(h, EXB_ACT_RELU6_QUIRK, bottoms, tops, EXB_F32);
+}
+template <typename Dtype>
+void operation_relu6<Dtype>::forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops) {
+    act_run<unsigned short>(h, EXB_ACT_RELU6_QUIRK, bottoms, tops, EXB_F16);
+}
+INSTANCE_CLASS(operation_relu6);
+REGISTE(operation_relu6);
 
 INSTANCE_CLASS(operation_split);
 REGISTE(operation_split);

@@ -166,6 +166,22 @@ protected:
     virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
 };
 
+// The reference's ReLU6 operation (src/Excalibur/operation_relu6.cpp:35-105): keys 0, 1 and -23330 are accepted and
+// ignored, anything else is fatal; y = x for 0 <= x <= 6 and 0 elsewhere - values ABOVE 6 become 0, not 6 (the
+// reference masks with x <= 6 instead of taking the minimum).  True ReLU6 is Clip 0=0 1=6.
+template <typename Dtype>
+class operation_relu6 : public operation<Dtype> {
+public:
+    typedef typename operation<Dtype>::f32_list f32_list;
+    typedef typename operation<Dtype>::f16_list f16_list;
+    explicit operation_relu6(const operation_param& param);
+    virtual const char* type() const { return "ReLU6"; }
+
+protected:
+    virtual void forward_gpu_f32(exb_ctx*& h, const f32_list& bottoms, f32_list& tops);
+    virtual void forward_gpu_f16(exb_ctx*& h, const f16_list& bottoms, f16_list& tops);
+};
+
 // ---- glue ops around the hot path -----------------------------------------------------------
 template <typename Dtype>
 class operation_split : public operation<Dtype> {   // aliases its input to every output

@@ -112,7 +112,7 @@ public:
     // Why the graph cannot be fused, or "" when it can.
     std::string unsupported_reason() const {
         static const std::set<std::string> ok = {"convolution", "convolutiondepthwise", "pooling", "eltwise", "binaryop",
-                                                  "relu", "split", "innerproduct", "clip", "sigmoid", "concat", "interp",
+                                                  "relu", "relu6", "split", "innerproduct", "clip", "sigmoid", "concat", "interp",
                                                  "batchnorm", "hardswish", "input", "yolov5focus", "prelu", "leakyrelu",
                                                  "deconvolution", "reshape", "transpose", "hardsigmoid", "softmax", "flatten"};
         for (const auto& p : params_) {
@@ -325,6 +325,7 @@ void fused_plan::build(int N, int C, int H, int W) {
     auto act_of_op = [&](int j) -> int {
         const std::string t = lower_type(params_[j]);
         if (t == "relu") return EXB_ACT_RELU;
+        if (t == "relu6") return EXB_ACT_RELU6_QUIRK;   // the reference's ReLU6 operation writes 0 above 6
         if (t == "sigmoid") return EXB_ACT_SIGMOID;
         if (t == "clip") {
             auto* c = dynamic_cast<operation_clip<float>*>(ops_[j].get());
@@ -616,6 +617,7 @@ void fused_plan::build(int N, int C, int H, int W) {
         // Input normalisation: inside the ingest kernel where that kernel has a fused form (few-channel images),
         // else a pass of its own from the fp32 staging buffer to a normalised copy.
         const bool direct_i8 = in.need_i8 && !in.need_f16;
+        bool wrote_i8_from_f32 = false;
         void* dst = focus_op >= 0 ? nullptr : (direct_i8 ? form_i8(in) : form_f16(in));
         const int cs = in.cs, w_pad = in.w_pad, w_pitch = in.w_pitch;
         const float s = in.i8_scale;
@@ -658,14 +660,19 @@ void fused_plan::build(int N, int C, int H, int W) {
                           "exb_image_f32_to_nhwc_norm");
             });
         } else {
+            // Both forms of a wide network input: the int8 form is quantised from the fp32 values themselves (as the
+            // reference's first int8 convolution does), not from their fp16 rounding.  One step, two launches: the
+            // ingest step is the only one that may read `ingest_src_`.
+            void* dst8 = (in.need_i8 && in.need_f16) ? form_i8(in) : nullptr;
+            wrote_i8_from_f32 = dst8 != nullptr;
             add_step("ingest " + in.name, [=](cudaStream_t st) {
-                exb_check(exb_nchw_f32_to_nhwc(ctx, ingest_fixed ? ingest_fixed : static_cast<const float*>(this->ingest_src_), dst,
-                                               direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs,
-                                               direct_i8 ? s : 1.f, 1, st),
+                const float* src = ingest_fixed ? ingest_fixed : static_cast<const float*>(this->ingest_src_);
+                exb_check(exb_nchw_f32_to_nhwc(ctx, src, dst, direct_i8 ? EXB_I8 : EXB_F16, N, C, H, W, cs, direct_i8 ? s : 1.f, 1, st),
                           "exb_nchw_f32_to_nhwc");
-            });
+                if (dst8) exb_check(exb_nchw_f32_to_nhwc(ctx, src, dst8, EXB_I8, N, C, H, W, cs, s, 1, st), "exb_nchw_f32_to_nhwc");
+            }, dst8 ? 2 : 1);
         }
-        if (focus_op < 0) finish_forms(in, direct_i8);
+        if (focus_op < 0) finish_forms(in, direct_i8 || wrote_i8_from_f32);
     }
 
     auto run_conv_group = [&](const group& g) {
@@ -1213,7 +1220,7 @@ void fused_plan::build(int N, int C, int H, int W) {
                 add_step(params_[i].name_, [=](cudaStream_t st) {
                     exb_check(exb_prelu_fwd(ctx, xin, yo, slope, n_slope, rows, c, cs, 1, EXB_F16, 1, st), "exb_prelu_fwd");
                 });
-            } else if (t == "relu" || t == "clip" || t == "sigmoid" || t == "hardswish") {
+            } else if (t == "relu" || t == "relu6" || t == "clip" || t == "sigmoid" || t == "hardswish") {
                 const int act = act_of_op((int)i);
                 if (act < 0) PLAN_REFUSE << "(" << params_[i].type_ << " parameters)";
                 const void* xin = form_f16(x);
@@ -1445,10 +1452,27 @@ void fused_plan::run_chunked(const float* host_input, int k, bool use_graph, int
     exb_check(exb_ctx_sync_check(ctx_, stream_), "chunked forward");
 }
 
-std::shared_ptr<memory::tensor<float>> fused_plan::fetch(const std::string& name) {
+std::shared_ptr<memory::tensor<float>> fused_plan::fetch(const std::string& name_in) {
+    // "<feature map>:int8" asks for the quantised tensor the plan hands to int8 convolutions, as the raw integers
+    // (-128..127 in fp32, not dequantised): what a parity test compares with quantize(reference map, scale).
+    static const std::string kInt8Suffix = ":int8";
+    const bool want_i8 = name_in.size() > kInt8Suffix.size() &&
+                         name_in.compare(name_in.size() - kInt8Suffix.size(), kInt8Suffix.size(), kInt8Suffix) == 0;
+    const std::string name = want_i8 ? name_in.substr(0, name_in.size() - kInt8Suffix.size()) : name_in;
     auto it = index_.find(name);
     if (it == index_.end()) return nullptr;
     fmap_info& f = fmaps_[root(it->second)];
+    if (want_i8) {
+        if (!f.produced || !f.i8 || f.w_pitch) return nullptr;
+        auto t = std::shared_ptr<memory::tensor<float>>(
+            new memory::tensor<float>(std::vector<int>{f.N, f.C, f.H, f.W}, device_, memory::NCHW, nullptr));
+        CUDA_CHECK(cudaStreamSynchronize(stream_));
+        exb_check(exb_nhwc_to_nchw_f32(ctx_, f.i8->p, EXB_I8, t->mutable_gpu_data(), f.N, f.C, f.H, f.W, f.cs, 1.f, nullptr),
+                  "exb_nhwc_to_nchw_f32");
+        CUDA_CHECK(cudaDeviceSynchronize());
+        t->cpu_data();
+        return t;
+    }
     if (f.w_pitch) {
         LOG(WARNING) << "feature map " << name << " is kept in a padded row layout and is not exported";
         return nullptr;

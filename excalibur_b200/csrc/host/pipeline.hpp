@@ -31,6 +31,8 @@ public:
     result_map forward_cpu(const std::shared_ptr<memory::tensor<Dtype>>& input_tensor);
     result_map forward_gpu(const std::shared_ptr<memory::tensor<Dtype>>& input_tensor);
     std::shared_ptr<memory::tensor<Dtype>> get_featmap(std::string_view featmap_name);
+    // With the fused plan, "<name>:int8" returns the quantised form of a feature map that int8 convolutions read
+    // (raw integers -128..127 as Dtype, not dequantised), or nullptr when the plan keeps no such form.
 
     void enable_profiler();
     void disable_profiler();

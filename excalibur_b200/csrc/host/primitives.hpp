@@ -92,16 +92,25 @@ private:
 namespace glasssix {
 namespace memory {
 
-// Size-bucketed free list of host buffers.  A request is served from the free list when a
-// buffer of 75 %..100 % fit exists (ratio adjustable), else freshly allocated.
+// Recycling allocator for host buffers with the reference's interface (include/Primitives/pool_allocator.hpp:72-146):
+// fastMalloc(bytes, device_id) serves a request from the free list ("budgets") when a buffer of
+// size_compare_ratio..100 % fit exists (default 75 %), else allocates - page-locked memory bound to device_id when
+// device_id >= 0, 64-byte aligned heap memory otherwise; fastFree(ptr, device_id) moves a buffer from the handed-out
+// list ("payouts") back to the free list, and frees a pointer it never handed out after logging an error.
+// The two lists have a mutex each and no call ever holds both, so allocating and freeing threads cannot deadlock.
+// One deliberate difference: every entry remembers the kind of memory it is (the device id it was pinned for), a
+// request only reuses buffers of its own kind and clear() frees each buffer with the matching call; the reference
+// keeps one untyped list, so a pinned buffer can come back for a heap request and is then freed as heap memory.
 template <typename Object>
 class pool_allocator {
 public:
-    pool_allocator() : ratio_(192) {}
+    pool_allocator() : ratio_(192) {}   // 0.75 * 256
     ~pool_allocator() {
         clear();
-        for (auto& p : payouts_) LOG(ERROR) << p.second << " still in use at pool destruction";
+        std::lock_guard<std::mutex> g(payout_lock_);
+        for (auto& p : payouts_) LOG(ERROR) << "pool allocator destroyed too early: " << p.ptr << " still in use";
     }
+    // ratio in 0..1: how much of a free buffer a request must fill to reuse it
     void set_size_compare_ratio(float r) {
         if (r < 0.f || r > 1.f) {
             LOG(FATAL) << "invalid size compare ratio " << r;
@@ -109,50 +118,83 @@ public:
         }
         ratio_ = (unsigned)(r * 256);
     }
+    // release every free buffer now
     void clear() {
-        std::lock_guard<std::mutex> g(budget_lock_);
-        for (auto& b : budgets_) std::free(b.second);
-        budgets_.clear();
+        std::list<entry> drop;
+        {
+            std::lock_guard<std::mutex> g(budget_lock_);
+            drop.swap(budgets_);
+        }
+        for (auto& b : drop) release(b.ptr, b.device);
     }
-    Object* allocate(size_t count) {
-        const size_t bytes = count * sizeof(Object);
+    void* fastMalloc(size_t size, int device_id = -1) {
+        entry e{0, nullptr, device_id};
         {
             std::lock_guard<std::mutex> g(budget_lock_);
             for (auto it = budgets_.begin(); it != budgets_.end(); ++it) {
-                if (it->first >= bytes && ((it->first * ratio_) >> 8) <= bytes) {
-                    void* p = it->second;
-                    size_t sz = it->first;
+                if (it->device == device_id && it->size >= size && ((it->size * ratio_) >> 8) <= size) {
+                    e = *it;
                     budgets_.erase(it);
-                    std::lock_guard<std::mutex> g2(payout_lock_);
-                    payouts_.emplace_back(sz, p);
-                    return static_cast<Object*>(p);
+                    break;
                 }
             }
         }
-        void* p = nullptr;
-        if (posix_memalign(&p, 64, bytes ? bytes : 64) != 0) LOG(FATAL) << "out of host memory (" << bytes << " bytes)";
-        std::lock_guard<std::mutex> g2(payout_lock_);
-        payouts_.emplace_back(bytes, p);
-        return static_cast<Object*>(p);
-    }
-    void deallocate(Object* ptr) {
-        std::lock_guard<std::mutex> g2(payout_lock_);
-        for (auto it = payouts_.begin(); it != payouts_.end(); ++it) {
-            if (it->second == ptr) {
-                size_t sz = it->first;
-                payouts_.erase(it);
-                std::lock_guard<std::mutex> g(budget_lock_);
-                budgets_.emplace_back(sz, ptr);
-                return;
+        if (!e.ptr) {
+            e.size = size;
+            if (device_id >= 0) {
+                CUDA_CHECK(cudaSetDevice(device_id));
+                CUDA_CHECK(cudaMallocHost(&e.ptr, size ? size : 16));
+            } else if (posix_memalign(&e.ptr, 64, size ? size : 64) != 0) {
+                LOG(FATAL) << "out of host memory (" << size << " bytes)";
             }
         }
-        LOG(FATAL) << "pool allocator got a pointer it did not hand out: " << (void*)ptr;
+        std::lock_guard<std::mutex> g(payout_lock_);
+        payouts_.push_back(e);
+        return e.ptr;
+    }
+    void fastFree(void* ptr, int device_id = -1) {
+        entry e{0, nullptr, device_id};
+        {
+            std::lock_guard<std::mutex> g(payout_lock_);
+            for (auto it = payouts_.begin(); it != payouts_.end(); ++it) {
+                if (it->ptr == ptr) {
+                    e = *it;
+                    payouts_.erase(it);
+                    break;
+                }
+            }
+        }
+        if (e.ptr) {
+            std::lock_guard<std::mutex> g(budget_lock_);
+            budgets_.push_back(e);
+            return;
+        }
+        LOG(ERROR) << "pool allocator get wild " << ptr;
+        release(ptr, device_id);
+    }
+    // buffers on the free list / handed out (tests and diagnostics)
+    size_t budget_count() {
+        std::lock_guard<std::mutex> g(budget_lock_);
+        return budgets_.size();
+    }
+    size_t payout_count() {
+        std::lock_guard<std::mutex> g(payout_lock_);
+        return payouts_.size();
     }
 
 private:
-    unsigned ratio_;
+    struct entry {
+        size_t size;
+        void* ptr;
+        int device;
+    };
+    static void release(void* ptr, int device) {
+        if (device >= 0) CUDA_CHECK(cudaFreeHost(ptr));
+        else std::free(ptr);
+    }
+    unsigned ratio_;   // 0..256
     std::mutex budget_lock_, payout_lock_;
-    std::list<std::pair<size_t, void*>> budgets_, payouts_;
+    std::list<entry> budgets_, payouts_;
 };
 
 // Host + device copies of one buffer with a head state: data lives where it was last written
@@ -167,9 +209,9 @@ public:
         : cpu_ptr_(nullptr), gpu_ptr_(nullptr), allocator_(nullptr), size_(size), head_(UNINITIALIZED),
           own_cpu_(false), pinned_(false), device_(device) {}
     ~syncedmem() {
-        if (cpu_ptr_ && own_cpu_) {
-            if (pinned_) cudaFreeHost(cpu_ptr_);
-            else if (allocator_) allocator_->deallocate(cpu_ptr_);
+        if (cpu_ptr_ && own_cpu_) {   // as the reference's destructor (src/Primitives/syncedmem.cpp:57-80)
+            if (allocator_) allocator_->fastFree(cpu_ptr_, device_);
+            else if (pinned_) cudaFreeHost(cpu_ptr_);
             else std::free(cpu_ptr_);
         }
         if (gpu_ptr_) cudaFree(gpu_ptr_);
@@ -197,11 +239,12 @@ private:
     size_t bytes() const { return size_ * sizeof(Dtype); }
     void alloc_cpu() {
         if (cpu_ptr_) return;
-        if (device_ >= 0) {
+        if (allocator_) {   // the allocator hands out pinned memory itself when device_ >= 0 (syncedmem.cpp:182-201)
+            cpu_ptr_ = static_cast<Dtype*>(allocator_->fastMalloc(bytes(), device_));
+        } else if (device_ >= 0) {
+            CUDA_CHECK(cudaSetDevice(device_));
             CUDA_CHECK(cudaMallocHost(reinterpret_cast<void**>(&cpu_ptr_), bytes() ? bytes() : 16));
             pinned_ = true;
-        } else if (allocator_) {
-            cpu_ptr_ = allocator_->allocate(size_);
         } else {
             void* p = nullptr;
             if (posix_memalign(&p, 64, bytes() ? bytes() : 64) != 0) LOG(FATAL) << "out of host memory";

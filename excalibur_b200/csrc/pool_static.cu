@@ -27,6 +27,14 @@ std::mutex g_setup_mutex;
 
 size_t round256(size_t v) { return (v + 255) & ~size_t(255); }
 
+// Puts the caller's current device back on every way out of the entry point.
+struct device_restore {
+    int saved = -1;
+    ~device_restore() {
+        if (saved >= 0) cudaSetDevice(saved);
+    }
+};
+
 }  // namespace
 
 extern "C" int exb_pool2d_nchw_f32_static(int device, const exb_pool_desc* d, const float* x_nchw, float* y_nchw,
@@ -52,6 +60,8 @@ extern "C" int exb_pool2d_nchw_f32_static(int device, const exb_pool_desc* d, co
     if (d->N == 0) return EXB_OK;
     EXB_REQUIRE(x_nchw && y_nchw, "exb_pool2d_nchw_f32_static: null tensor");
 
+    device_restore restore;
+    EXB_CUDA_TRY(cudaGetDevice(&restore.saved));
     EXB_CUDA_TRY(cudaSetDevice(device));
     device_setup st;
     {
@@ -62,6 +72,7 @@ extern "C" int exb_pool2d_nchw_f32_static(int device, const exb_pool_desc* d, co
         if (!s.ready) {
             void* p = nullptr;
             cudaError_t e = cudaGetSymbolAddress(&p, g_pool_scratch);
+            if (e != cudaSuccess || p == nullptr) (void)cudaGetLastError();
             if (e != cudaSuccess || p == nullptr)
                 return fail(EXB_ERR_CUDA, "exb_pool2d_nchw_f32_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
             int sms = 0;
@@ -75,12 +86,9 @@ extern "C" int exb_pool2d_nchw_f32_static(int device, const exb_pool_desc* d, co
     }
 
     // A context value that only carries what the three kernels' launch helpers read.
-    exb_ctx local;
+    exb_ctx local{};          // every field zero: no error word, no programmatic dependent launch
     local.device = device;
     local.sm_count = st.sm_count;
-    local.smem_optin = 0;
-    local.d_error = nullptr;
-    local.h_error = nullptr;
 
     unsigned char* in_nhwc = static_cast<unsigned char*>(st.scratch);
     unsigned char* out_nhwc = in_nhwc + in_bytes;

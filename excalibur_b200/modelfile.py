@@ -111,6 +111,10 @@ class GraphBuilder:
     def relu(self, name, x, y):
         return self._op("ReLU", name, [x], [y])
 
+    def relu6(self, name, x, y):
+        """The reference's ReLU6 operation: 0 outside [0, 6] (values above 6 become 0, not 6)."""
+        return self._op("ReLU6", name, [x], [y])
+
     def clip(self, name, x, y, lo, hi):
         return self._op("Clip", name, [x], [y], "0=%r 1=%r" % (float(lo), float(hi)))
 

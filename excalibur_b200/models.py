@@ -52,10 +52,12 @@ def quantize_weights(w):
     return wq, ws
 
 
-def resnet18(seed=2, act_scales=None, widths=RESNET18_WIDTHS, num_classes=1000, in_ch=3):
+def resnet18(seed=2, act_scales=None, widths=RESNET18_WIDTHS, num_classes=1000, in_ch=3, stem=True):
     """Returns (GraphBuilder, info).  act_scales: {conv name: fs} turns the named convs into int8
     convs (every conv except the stem must be present); None builds the floating-point graph.
-    info["conv_inputs"] maps each quantisable conv to the feature map it reads (for calibration)."""
+    info["conv_inputs"] maps each quantisable conv to the feature map it reads (for calibration).
+    stem=False leaves out the stem convolution and the max pooling: the graph's input "data" is then the
+    widths[0]-channel map the first block reads (same weights as the full network's blocks)."""
     g = GraphBuilder("resnet18_style")
     wts = _Weights(seed)
     conv_inputs = {}
@@ -71,8 +73,12 @@ def resnet18(seed=2, act_scales=None, widths=RESNET18_WIDTHS, num_classes=1000, 
         g.conv(name, x, y, w, b, stride, pad, act=act, int8=int8)
         return y
 
-    x = conv("stem", "data", "stem_out", widths[0], in_ch, 7, 2, 3, 1, quant=False)
-    x = g.pool("pool1", x, "pool1_out", 0, 3, 2, 1)
+    if stem:
+        x = conv("stem", "data", "stem_out", widths[0], in_ch, 7, 2, 3, 1, quant=False)
+        x = g.pool("pool1", x, "pool1_out", 0, 3, 2, 1)
+    else:
+        wts.conv_bn(widths[0], in_ch, 7)      # keep the weight sequence of the full network
+        x = "data"
     cin = widths[0]
     for si, wd in enumerate(widths):
         for bi in range(2):

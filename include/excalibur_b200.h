@@ -50,6 +50,7 @@ typedef enum exb_act {
     EXB_ACT_RELU = 1,
     EXB_ACT_RELU6_QUIRK = 3, /* reference behaviour: x > 6 -> 0 */
     EXB_ACT_SIGMOID = 4,
+    EXB_ACT_MISH = 5,        /* x * tanh(ln(1 + e^x)) (operation_general_conv.cpp:255-266) */
     EXB_ACT_RELU6 = 103,
     EXB_ACT_SILU = 104,
     EXB_ACT_HARDSWISH = 105,  /* x * clamp(x/6 + 0.5, 0, 1): HardSwish with alpha = 1/6, beta = 0.5 */
@@ -84,6 +85,15 @@ EXB_API int exb_ctx_sync_check(exb_ctx* ctx, void* stream);
  * can never be satisfied.  The kernel gives up, records role code 9 and returns; the following
  * exb_ctx_sync_check reports EXB_ERR_TIMEOUT and the context stays usable.  No reference counterpart. */
 EXB_API int exb_selftest_bounded_wait(exb_ctx* ctx, int max_polls, void* stream);
+/* Best-case tensor-core rate of this GPU (the denominator of the convolution kernel's tensor roofline):
+ * sm_count * ctas_per_sm CTAs each issue iters * kblk * 4 tcgen05.mma instructions (M = 128, N = n, K = 32
+ * bytes; EXB_I8: s8 x s8 -> s32, EXB_F16: fp16 x fp16 -> fp32) on seeded operands that stay in shared
+ * memory - no TMA, no epilogue, no global traffic.  *ops_per_launch receives 2 * MACs of the launch;
+ * d_cycles (device pointer or NULL) receives CTA 0's SM cycles.  Time the launch with events on `stream`.
+ * n: multiple of 16 up to 256; ctas_per_sm 1 or 2; kblk 1..8 K blocks of 128 bytes per operand row.
+ * No reference counterpart (the reference quotes no tensor rate). */
+EXB_API int exb_tensor_peak_probe(exb_ctx* ctx, int dtype, int n, int ctas_per_sm, int kblk, int iters,
+                                  double* ops_per_launch, unsigned long long* d_cycles, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Layout / precision converts at the API edge.  The reference keeps NCHW fp32 tensors

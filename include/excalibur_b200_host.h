@@ -51,7 +51,8 @@ EXB_API int exb_host_pipeline_forward(void* p, const float* input, int N, int C,
 EXB_API int exb_host_pipeline_num_outputs(void* p);
 EXB_API int exb_host_pipeline_output_name(void* p, int i, char* buf, int cap);
 /* Output or any feature map by name (pipeline::get_featmap, pipeline.hpp:32).  out == NULL
- * returns only the shape; the data is fp32 NCHW. */
+ * returns only the shape; the data is fp32 NCHW.  With the fused plan, "<name>:int8" returns the quantised form
+ * that int8 convolutions read (raw integers -128..127 in fp32). */
 EXB_API int exb_host_pipeline_get(void* p, const char* name, float* out, int64_t cap, int* shape4);
 /* The host tensor an output of the last forward lives in (fp32 NCHW), without a copy: what
  * pipeline<float>::forward returns to a C++ caller.  Valid until the next forward. */

@@ -11,6 +11,13 @@ import tempfile
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def reference_tree():
+    """Where the reference project's source tree is expected: $EXB_REFERENCE_TREE, else a directory named
+    `reference` beside this repository.  The tree is only ever read (build recipe, fixture generator)."""
+    return os.environ.get("EXB_REFERENCE_TREE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
 SO_PATH = os.path.join(_HERE, "_ref", "libexcalibur_ref.so")
 _LIB = None
 

@@ -8,6 +8,8 @@ Run in a container that has the reference tree (it cannot travel to the GPU box)
     python tests/golden/make_golden.py yolo        # tests/golden/yolo_vectors.npz only
     python tests/golden/make_golden.py shipped     # tests/golden/shipped_model_vectors.npz only
     python tests/golden/make_golden.py architectures   # tests/golden/shipped_architectures.{json,npz} only
+    python tests/golden/make_golden.py fullsize    # tests/golden/fullsize_vectors.npz only (minutes of CPU time)
+    python tests/golden/make_golden.py boundary    # tests/golden/boundary_vectors.npz only
 
 Every case stores its inputs, weights and the reference's output, so the fixture pins the oracle
 (oracle/exb_oracle.c) and, through it, the CUDA kernels, without the reference being present.
@@ -25,6 +27,7 @@ sys.path.insert(0, ROOT)
 from excalibur_b200 import model_zoo, models  # noqa: E402
 from excalibur_b200.modelfile import GraphBuilder  # noqa: E402
 from oracle import ref_lib  # noqa: E402
+from tests.util import body_inputs, fullsize_inputs, quantize_half_away  # noqa: E402
 
 
 def run(g, x, names=("out",)):
@@ -358,7 +361,7 @@ def mobilenet():
     print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
 
 
-REF_MODELS = "/root/reference/models"
+REF_MODELS = os.path.join(ref_lib.reference_tree(), "models")
 
 
 def architectures():
@@ -444,6 +447,162 @@ def architectures():
           "architectures")
 
 
+def boundary():
+    """The ReLU6 operation (values above 6 become 0) alone and behind a convolution, and a convolution with the
+    Mish suffix activation (key 9=5), fp32 and int8 -> tests/golden/boundary_vectors.npz."""
+    r = np.random.default_rng(20240610)
+    out = {}
+    x = (r.standard_normal((2, 9, 7, 5)) * 4).astype(np.float32)
+    x.flat[:6] = [0.0, -0.0, 6.0, np.nextafter(np.float32(6), np.float32(7)), 5.999, -1e-30]
+    out["relu6_x"] = x
+    g = GraphBuilder(); g.relu6("r", "in", "out")
+    out["relu6_out"], = run(g, x)
+    g = GraphBuilder(); g._op("ReLU6", "r", ["in"], ["out"], "0=0.0 1=6.0")     # keys 0 / 1 are accepted and ignored
+    out["relu6_keys_out"], = run(g, x)
+    # convolution -> ReLU6 (fused into the epilogue by the plan)
+    xc = r.uniform(-1, 1, (2, 16, 9, 11)).astype(np.float32)
+    w = (r.standard_normal((32, 16, 3, 3)) * 0.35).astype(np.float32)
+    b = (r.standard_normal(32) * 0.5 + 2.0).astype(np.float32)
+    out["conv_x"], out["conv_w"], out["conv_b"] = xc, w, b
+    g = GraphBuilder()
+    g.conv("c", "in", "m", w, b, 1, 1, act=0)
+    g.relu6("r", "m", "out")
+    out["conv_relu6_out"], = run(g, xc)
+    # Mish suffix activation, fp32 and int8 (batch 2: the 3x3 stride-1 int8 path handles batches)
+    g = GraphBuilder(); g.conv("c", "in", "out", w, b, 1, 1, act=5)
+    out["conv_mish_out"], = run(g, xc)
+    wq, ws = models.quantize_weights(w)
+    fs = np.float32(127.0 / np.abs(xc).max())
+    out["conv_wq"], out["conv_ws"], out["conv_fs"] = wq, ws, fs
+    g = GraphBuilder(); g.conv("c", "in", "out", w, b, 1, 1, act=5, int8=(wq, ws, fs))
+    out["conv_mish_i8_out"], = run(g, xc)
+    path = os.path.join(ROOT, "tests", "golden", "boundary_vectors.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
+    print("relu6: %d of %d values above 6 -> 0" % (int((x > 6).sum()), x.size), float(out["relu6_out"][x > 6].max()))
+
+
+def fullsize():
+    """The benchmark configurations at the image sizes they are benchmarked at -> tests/golden/fullsize_vectors.npz.
+
+    ResNet-18-style at 3x224x224: fp32 logits and sampled block outputs for 3 seeded images; max-abs activation scales
+    from 32 seeded calibration images through the reference's fp32 pipeline; the int8 network's logits (one image per
+    forward: the reference's packed int8 path only computes image 0) and, for one block output per stage, the int8
+    tensor the NEXT int8 convolution sees in the reference: quantize(map, that convolution's scale).
+    MobileNetV2-style at 224 (2 images, 8 calibration images) and YOLOv5s-style at 640 (1 image): logits / head outputs
+    and inner maps, sampled.  Inputs are regenerated from their seeds (fullsize_inputs); a checksum pins them."""
+    out = {}
+    # ---- ResNet-18-style -----------------------------------------------------------------------
+    seed = 2
+    x = fullsize_inputs("resnet", 3, 224)
+    out["resnet_x_sum"] = np.float64(x.astype(np.float64).sum())
+    g32, info = models.resnet18(seed)
+    p32 = ref_lib.RefPipeline(g32.phai_text(), g32.racy_bytes())
+    out["resnet_f32_logits"] = p32.forward(x)["logits"].reshape(3, -1)
+    maps = ("pool1_out", "s1b1_out", "s1b2_out", "s2b1_out", "s3b1_out", "s4b1_out", "s4b2_out")
+    for n in maps:
+        out["resnet_f32_" + n] = model_zoo.sample(p32.featmap(n))
+    scales = models.calibrate(_RefAdapter(p32), info["conv_inputs"], fullsize_inputs("resnet_calib", 32, 224))
+    p32.close()
+    names = sorted(scales)
+    out["resnet_scale_names"] = np.array(names)
+    out["resnet_scales"] = np.array([scales[n] for n in names], np.float32)
+    g8, _ = models.resnet18(seed, act_scales=scales)
+    p8 = ref_lib.RefPipeline(g8.phai_text(), g8.racy_bytes())
+    logits = []
+    q = {("pool1_out", "s1b1_conv1"): [], ("s1b1_out", "s1b2_conv1"): [], ("s2b1_out", "s2b2_conv1"): [],
+         ("s3b1_out", "s3b2_conv1"): [], ("s4b1_out", "s4b2_conv1"): []}
+    smp = {n: [] for n in maps}
+    for i in range(3):
+        logits.append(p8.forward(x[i:i + 1])["logits"].reshape(1, -1))
+        for (m, conv) in q:
+            q[(m, conv)].append(quantize_half_away(p8.featmap(m), scales[conv]))
+        for n in maps:
+            smp[n].append(model_zoo.sample(p8.featmap(n), 4096))
+    p8.close()
+    out["resnet_i8_logits"] = np.concatenate(logits)
+    for (m, conv), v in q.items():
+        out["resnet_i8_q_%s_for_%s" % (m, conv)] = np.concatenate(v)
+    for n in maps:
+        out["resnet_i8_" + n] = np.stack(smp[n])
+    print("resnet done", flush=True)
+
+    # ---- the int8 residual trunk alone, from a seeded 64 x 56 x 56 map ----------------------------
+    # Both sides then quantise the SAME fp32 input, so the int8 tensors of the first blocks can be compared to the
+    # LSB: what differs is only what the plan composes differently (fp16 skip, requantisation in the producer's
+    # epilogue with round-half-even where the reference quantises in the consumer with round-half-away).
+    seed = 2
+    xb = body_inputs("resnet_body", 2)
+    out["body_x_sum"] = np.float64(xb.astype(np.float64).sum())
+    g32, info = models.resnet18(seed, in_ch=3, stem=False)
+    p32 = ref_lib.RefPipeline(g32.phai_text(), g32.racy_bytes())
+    out["body_f32_logits"] = p32.forward(xb)["logits"].reshape(2, -1)
+    bscales = models.calibrate(_RefAdapter(p32), info["conv_inputs"], body_inputs("resnet_body_calib", 8))
+    p32.close()
+    names = sorted(bscales)
+    out["body_scale_names"] = np.array(names)
+    out["body_scales"] = np.array([bscales[n] for n in names], np.float32)
+    g8, _ = models.resnet18(seed, act_scales=bscales, stem=False)
+    p8 = ref_lib.RefPipeline(g8.phai_text(), g8.racy_bytes())
+    logits = []
+    qb = {("s1b1_out", "s1b2_conv1"): [], ("s1b2_out", "s2b1_conv1"): [], ("s2b1_out", "s2b2_conv1"): [],
+          ("s3b1_out", "s3b2_conv1"): [], ("s4b1_out", "s4b2_conv1"): []}
+    for i in range(2):
+        logits.append(p8.forward(xb[i:i + 1])["logits"].reshape(1, -1))
+        for (m, conv) in qb:
+            qb[(m, conv)].append(quantize_half_away(p8.featmap(m), bscales[conv]))
+    p8.close()
+    out["body_i8_logits"] = np.concatenate(logits)
+    for (m, conv), v in qb.items():
+        out["body_i8_q_%s_for_%s" % (m, conv)] = np.concatenate(v)
+    print("resnet body done", flush=True)
+
+    # ---- MobileNetV2-style ---------------------------------------------------------------------
+    seed = 3
+    x = fullsize_inputs("mobilenet", 2, 224)
+    out["mobilenet_x_sum"] = np.float64(x.astype(np.float64).sum())
+    g32, info = models.mobilenet_v2(seed)
+    p32 = ref_lib.RefPipeline(g32.phai_text(), g32.racy_bytes())
+    out["mobilenet_f32_logits"] = p32.forward(x)["logits"].reshape(2, -1)
+    mmaps = ("b1_project_out", "b3_sum", "b7_dw_act", "b14_dw_act")
+    for n in mmaps:
+        out["mobilenet_f32_" + n] = model_zoo.sample(p32.featmap(n))
+    scales = models.calibrate(_RefAdapter(p32), info["conv_inputs"], fullsize_inputs("mobilenet_calib", 8, 224))
+    p32.close()
+    names = sorted(scales)
+    out["mobilenet_scale_names"] = np.array(names)
+    out["mobilenet_scales"] = np.array([scales[n] for n in names], np.float32)
+    g8, _ = models.mobilenet_v2(seed, act_scales=scales)
+    p8 = ref_lib.RefPipeline(g8.phai_text(), g8.racy_bytes())
+    logits, b3 = [], []
+    for i in range(2):
+        logits.append(p8.forward(x[i:i + 1])["logits"].reshape(1, -1))
+        b3.append(model_zoo.sample(p8.featmap("b3_sum")))
+    p8.close()
+    out["mobilenet_i8_logits"] = np.concatenate(logits)
+    out["mobilenet_i8_b3_sum"] = np.stack(b3)
+    print("mobilenet done", flush=True)
+
+    # ---- YOLOv5s-style -------------------------------------------------------------------------
+    x = fullsize_inputs("yolo", 1, 640)
+    out["yolo_x_sum"] = np.float64(x.astype(np.float64).sum())
+    gy, info = models.yolov5s(5)
+    py = ref_lib.RefPipeline(gy.phai_text(), gy.racy_bytes())
+    res = py.forward(x)
+    out["yolo_outputs"] = np.array(list(info["outputs"]))
+    for n in info["outputs"]:
+        out["yolo_" + n] = model_zoo.sample(res[n])
+        out["yolo_%s_shape" % n] = np.array(res[n].shape, np.int64)
+        out["yolo_%s_absmax" % n] = np.float32(np.abs(res[n]).max())
+    for n in ("c3_1_cv3_act", "sppf_cat_out", "neck_up1_out"):
+        out["yolo_" + n] = model_zoo.sample(py.featmap(n))
+        out["yolo_%s_absmax" % n] = np.float32(np.abs(py.featmap(n)).max())
+    py.close()
+    path = os.path.join(ROOT, "tests", "golden", "fullsize_vectors.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path) // 1024, "KiB,", len(out), "arrays")
+
+
 class _RefAdapter:
     def __init__(self, p):
         self.p = p
@@ -464,5 +623,9 @@ if __name__ == "__main__":
         shipped()
     elif sys.argv[1:] == ["architectures"]:
         architectures()
+    elif sys.argv[1:] == ["fullsize"]:
+        fullsize()
+    elif sys.argv[1:] == ["boundary"]:
+        boundary()
     else:
         main()

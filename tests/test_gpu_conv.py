@@ -196,8 +196,8 @@ def test_conv_grouped_direct(ctx):
 
 
 def test_conv_full_size_tc_equals_direct(ctx):
-    """Batch-256 stage-1 layer: too big for the CPU oracle, so the tensor-core kernel is checked
-    against the direct kernel (itself oracle-checked above) on the device, bit for bit."""
+    """Batch-256 stage-1 layer: the tensor-core kernel against the direct kernel on the device, bit for bit over the
+    whole batch, and two images of that same launch against the CPU oracle."""
     capi = _capi()
     import torch
     N, Cc, H, W = 256, 64, 56, 56
@@ -213,6 +213,11 @@ def test_conv_full_size_tc_equals_direct(ctx):
         ctx.sync_check()
         outs.append(y)
     assert torch.equal(outs[0], outs[1])
+    # two images of the same launch (the first and the last) against the CPU oracle's accumulators
+    for n in (0, N - 1):
+        xn = to_nchw(host(x[n:n + 1]))
+        ref = O.conv2d_i8_acc(xn, wq, 1, 1)
+        np.testing.assert_array_equal(to_nchw(host(outs[0][n:n + 1])), ref)
     # linearity: conv(2x) == 2*conv(x) on the accumulators
     d = capi.make_conv_desc(N, H, W, Cc, Cc, 3, 1, 1, capi.EXB_I8, capi.EXB_I32)
     wp = capi.ConvWeights(ctx, d, wq, None, np.ones(Cc, np.float32), 1.0)

@@ -9,9 +9,10 @@ import pytest
 
 from excalibur_b200 import model_zoo
 from oracle import exb_oracle as O
+from oracle import ref_lib
 
 S = np.load(os.path.join(os.path.dirname(__file__), "golden", "shipped_model_vectors.npz"))
-REF_MODELS = "/root/reference/models"
+REF_MODELS = os.path.join(ref_lib.reference_tree(), "models")
 
 
 def test_oracle_prelu_leakyrelu_match_the_reference():

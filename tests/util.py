@@ -70,3 +70,35 @@ def from_planar16(p, C=None):
     n, cc, h, w, _ = p.shape
     a = np.ascontiguousarray(p.transpose(0, 1, 4, 2, 3)).reshape(n, cc * 16, h, w)
     return a[:, :C] if C is not None else a
+
+
+# ---- benchmark-size fixtures (tests/golden/fullsize_vectors.npz) -----------------------------------
+FULLSIZE_SEEDS = {"resnet_body": 56001, "resnet_body_calib": 56007, "resnet": 224001, "resnet_calib": 224007, "mobilenet": 224101, "mobilenet_calib": 224107, "yolo": 640001}
+
+
+def fullsize_inputs(tag, n, size):
+    """Seeded uniform[0,1] images of one benchmark configuration; the fixture stores only their checksum."""
+    return np.random.default_rng(FULLSIZE_SEEDS[tag]).uniform(0, 1, (n, 3, size, size)).astype(np.float32)
+
+
+def body_inputs(tag, n, channels=64, size=56):
+    """Seeded stand-in for the map the first residual block reads (post-ReLU, post-pooling: non-negative, a few
+    units large): |N(0, 1.5)| values, about half of them clipped to 0."""
+    r = np.random.default_rng(FULLSIZE_SEEDS[tag])
+    v = r.standard_normal((n, channels, size, size)).astype(np.float32) * np.float32(1.5) - np.float32(0.2)
+    return np.maximum(v, 0).astype(np.float32)
+
+
+def quantize_half_away(x, scale):
+    """The reference's float32_to_int8 (src/Primitives/simd_types.cpp:140-152): x * scale, half away from zero,
+    truncate, saturate to [-128, 127]."""
+    t = np.asarray(x, np.float32) * np.float32(scale)
+    t = np.where(t >= 0, t + np.float32(0.5), t - np.float32(0.5))
+    return np.clip(t, -128, 127).astype(np.int32).astype(np.int8)
+
+
+def sample(a, limit=8192):
+    """Every k-th value of a flattened array, at most `limit` values (what a fixture keeps of a large map)."""
+    flat = np.ascontiguousarray(a, np.float32).reshape(-1)
+    step = max(1, -(-flat.size // limit))
+    return flat[::step].copy()
