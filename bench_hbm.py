@@ -1,6 +1,6 @@
 """Bandwidth-bound kernels against the HBM roofline, on the shapes the benchmark networks use.
 
-    python -m excalibur_b200.hbm_bench [--batch 256] [--iters 20]
+    python bench_hbm.py [--batch 256] [--iters 20]
 
 Per kernel: CUDA-event time of one launch, algorithmic bytes (every operand once at its storage
 width) and the resulting GB/s, as a fraction of the measured HBM copy bandwidth in
@@ -13,7 +13,12 @@ import os
 
 import numpy as np
 
-from . import capi
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from excalibur_b200 import capi  # noqa: E402
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 

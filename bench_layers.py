@@ -1,6 +1,6 @@
 """Per-layer timing of the hot-path kernels on the shapes of the ResNet-18-style network.
 
-    python -m excalibur_b200.layer_bench [--batch 256] [--layers s1_conv1,s1_conv2,...] [--iters 20]
+    python bench_layers.py [--batch 256] [--layers s1_conv1,s1_conv2,...] [--iters 20]
 
 Prints, per layer, the CUDA-event time of one launch and the algorithmic TFLOP/s and GB/s
 (FLOP = 2*N*OH*OW*Cout*Cin*kh*kw; bytes = every operand once at its storage width).  With
@@ -12,7 +12,11 @@ import sys
 
 import numpy as np
 
-from . import capi
+import os
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from excalibur_b200 import capi  # noqa: E402
 
 # name: (Cin, H=W, Cout, k, stride, pad, kind)   kind: conv1 = int8 -> int8 + ReLU,
 # conv2 = int8 + fp16 residual -> fp16 + int8 + ReLU, proj = int8 -> fp16
@@ -48,10 +52,6 @@ def main(argv=None):
     ap.add_argument("--layers", default=",".join(list(LAYERS) + list(EXTRA)))
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--planar-f16", action="store_true",
-                    help="fp16 outputs and residuals use the planar16 fp16 layout (coalesced epilogue accesses)")
-    ap.add_argument("--planar", action="store_true",
-                    help="3x3 stride-1 int8 layers read / write planar16 int8 tensors (halo mode) where the kernel accepts it")
     args = ap.parse_args(argv)
     N = args.batch
     torch.cuda.set_device(0)
@@ -66,18 +66,8 @@ def main(argv=None):
             d = capi.make_conv_desc(N, hw, hw, cin, cout, k, s, p, capi.EXB_I8, out, out2, res,
                                     capi.ACT_NONE if kind == "proj" else capi.ACT_RELU, 0.05, 0.05)
             oh, ow = capi.conv_out_dims(d)
-            planar = args.planar and capi.lib().exb_conv2d_accepts_planar_input(d) == 1
-            if planar:
-                d.in_planar = 1
-                d.out_i8_planar = 1 if kind != "proj" else 0
-                name = name + "*"
-            if args.planar_f16 and kind != "conv1":
-                d.out_f16_planar = 1
-                d.res_planar = 1 if res else 0
-                name = name + "^"
             wq = rng.integers(-127, 128, (cout, cin, k, k)).astype(np.int8)
             wp = capi.ConvWeights(ctx, d, wq, np.zeros(cout, np.float32), np.full(cout, 40.0, np.float32), 30.0)
-            # (random bytes: the same buffer serves as NHWC or planar16 input)
             x = torch.randint(-128, 128, (N, hw, hw, cin), device="cuda", dtype=torch.int32).to(torch.int8)
             r = torch.randn((N, oh, ow, cout), device="cuda", dtype=torch.float16) if res else None
             y = torch.empty((N, oh, ow, cout), device="cuda", dtype=capi.torch_dtype(out))

@@ -1,6 +1,6 @@
 """Whole-network throughput of the benchmark configurations other than the headline one.
 
-    python -m excalibur_b200.net_bench [--net resnet18_fp16,resnet18_int8,mobilenetv2_fp16,mobilenetv2_int8,yolov5s_fp16,
+    python bench_nets.py [--net resnet18_fp16,resnet18_int8,mobilenetv2_fp16,mobilenetv2_int8,yolov5s_fp16,
                                               det_db_resnet18_fp16,mobile_unicorn_fp16,yolov5s_simp_fp16,unicorn_light_fp16,unicorn_light_int8]
                                        [--batch B] [--size S] [--iters K] [--trace]
 
@@ -18,7 +18,12 @@ import time
 
 import numpy as np
 
-from . import host, model_zoo, models
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from excalibur_b200 import host, model_zoo, models  # noqa: E402
 
 NETS = {
     # name: (builder, int8, batch, size)

@@ -19,7 +19,7 @@ EXPORTED_SYMBOLS = [
     "exb_ctx_create", "exb_ctx_destroy", "exb_last_error_string", "exb_version", "exb_ctx_sm_count",
     "exb_ctx_sync_check", "exb_selftest_bounded_wait", "exb_tensor_peak_probe", "exb_nchw_f32_to_nhwc", "exb_nchw_f32_to_nhwc_padded", "exb_nhwc_to_nchw_f32", "exb_conv_out_dims",
     "exb_conv_weights_pack_f16", "exb_conv_weights_pack_i8", "exb_conv_weights_destroy",
-    "exb_conv2d_fwd", "exb_conv2d_uses_tensor_cores", "exb_conv2d_pool_fusable", "exb_conv2d_accepts_planar_input", "exb_planar16_i8_to_nchw_f32", "exb_planar16_to_nchw_f32", "exb_dw_weights_pack", "exb_dw_weights_destroy",
+    "exb_conv2d_fwd", "exb_conv2d_uses_tensor_cores", "exb_conv2d_pool_fusable", "exb_dw_weights_pack", "exb_dw_weights_destroy",
     "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_pool2d_nchw_f32_static", "exb_eltwise_fwd", "exb_binaryop_fwd",
     "exb_binaryop_scalar_fwd", "exb_relu_fwd", "exb_activation_fwd", "exb_quantize_fwd",
     "exb_dequantize_fwd", "exb_concat_fwd", "exb_interp_nearest_fwd", "exb_channel_affine_fwd",
@@ -33,8 +33,7 @@ class ConvDesc(C.Structure):
         "pad_t", "pad_b", "pad_l", "pad_r", "dilation", "group", "in_dtype", "out_dtype", "out2_dtype",
         "res_dtype", "act")] + [("out_scale", C.c_float), ("out2_scale", C.c_float), ("impl", C.c_int32),
                                       ("x_w_pitch", C.c_int32), ("x_w_pad", C.c_int32), ("fuse_pool", C.c_int32),
-                                      ("in_planar", C.c_int32), ("out_i8_planar", C.c_int32),
-                                      ("out_f16_planar", C.c_int32), ("res_planar", C.c_int32), ("y_pitch", C.c_int32)]
+                                      ("y_pitch", C.c_int32)]
 
 
 class DwConvDesc(C.Structure):
@@ -81,9 +80,6 @@ def lib():
         L.exb_conv_out_dims.argtypes = [C.POINTER(ConvDesc), C.POINTER(i32), C.POINTER(i32)]
         L.exb_conv2d_uses_tensor_cores.argtypes = [C.POINTER(ConvDesc)]
         L.exb_conv2d_pool_fusable.argtypes = [C.POINTER(ConvDesc)]
-        L.exb_conv2d_accepts_planar_input.argtypes = [C.POINTER(ConvDesc)]
-        L.exb_planar16_i8_to_nchw_f32.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, f32, vp]
-        L.exb_planar16_to_nchw_f32.argtypes = [vp, vp, i32, vp, i32, i32, i32, i32, i32, f32, vp]
         L.exb_conv_weights_pack_f16.argtypes = [vp, C.POINTER(ConvDesc), vp, vp, C.POINTER(vp)]
         L.exb_conv_weights_pack_i8.argtypes = [vp, C.POINTER(ConvDesc), vp, vp, vp, i32, f32, C.POINTER(vp)]
         L.exb_conv_weights_destroy.argtypes = [vp]
@@ -196,13 +192,13 @@ class Context:
 def make_conv_desc(N, H, W, Cin, Cout, k, stride=1, pad=0, in_dtype=EXB_F16, out_dtype=EXB_F16,
                    out2_dtype=-1, res=False, act=ACT_NONE, out_scale=1.0, out2_scale=1.0,
                    cin_stride=0, cout_stride=0, group=1, impl=0, x_w_pitch=0, x_w_pad=0, fuse_pool=0,
-                   in_planar=0, out_i8_planar=0, out_f16_planar=0, res_planar=0, y_pitch=0):
+                   y_pitch=0):
     kh, kw = (k, k) if isinstance(k, int) else k
     sh, sw = (stride, stride) if isinstance(stride, int) else stride
     pt, pb, pl, pr = (pad,) * 4 if isinstance(pad, int) else pad
     return ConvDesc(N, H, W, Cin, Cout, cin_stride, cout_stride, kh, kw, sh, sw, pt, pb, pl, pr, 1, group,
                     in_dtype, out_dtype, out2_dtype, EXB_F16 if res else -1, act, out_scale, out2_scale, impl, x_w_pitch, x_w_pad, fuse_pool,
-                    in_planar, out_i8_planar, out_f16_planar, res_planar, y_pitch)
+                    y_pitch)
 
 
 class ConvWeights:

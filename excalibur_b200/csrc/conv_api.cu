@@ -32,8 +32,6 @@ int resolve(const exb_conv_desc* d, ConvGeom& g) {
         return fail(EXB_ERR_UNSUPPORTED, "activation type %d is not implemented", d->act);
     if (d->act == EXB_ACT_PRELU && d->fuse_pool)
         return fail(EXB_ERR_UNSUPPORTED, "fuse_pool needs an activation with non-negative results, not EXB_ACT_PRELU");
-    if (d->act == EXB_ACT_PRELU && (d->in_planar || d->out_i8_planar || d->out_f16_planar || d->res_planar))
-        return fail(EXB_ERR_UNSUPPORTED, "EXB_ACT_PRELU is not available with planar16 tensors");
     g.N = d->N; g.H = d->H; g.W = d->W; g.Cin = d->Cin; g.Cout = d->Cout;
     g.cin_stride = d->cin_stride ? d->cin_stride : d->Cin;
     g.cout_stride = d->cout_stride ? d->cout_stride : d->Cout;
@@ -56,33 +54,12 @@ int resolve(const exb_conv_desc* d, ConvGeom& g) {
     g.pool = d->fuse_pool;
     g.PH = (g.OH - 1) / 2 + 1;     // (OH + 2*1 - 3) / 2 + 1, floor mode
     g.PW = (g.OW - 1) / 2 + 1;
-    EXB_REQUIRE((d->in_planar == 0 || d->in_planar == 1) && (d->out_i8_planar == 0 || d->out_i8_planar == 1),
-                "in_planar / out_i8_planar must be 0 or 1");
-    g.in_planar = d->in_planar;
-    g.out_i8_planar = d->out_i8_planar;
-    EXB_REQUIRE((d->out_f16_planar == 0 || d->out_f16_planar == 1) && (d->res_planar == 0 || d->res_planar == 1),
-                "out_f16_planar / res_planar must be 0 or 1");
-    g.out_f16_planar = d->out_f16_planar;
-    g.res_planar = d->res_planar;
-    if (g.out_f16_planar || g.res_planar) {
-        EXB_REQUIRE(g.cout_stride % 16 == 0, "planar16 fp16 tensors need cout_stride %% 16 == 0");
-        EXB_REQUIRE(!g.out_f16_planar || g.out_dtype == EXB_F16 || g.out2_dtype == EXB_F16,
-                    "out_f16_planar without an fp16 output");
-        EXB_REQUIRE(!g.res_planar || g.has_res, "res_planar without a residual");
-        EXB_REQUIRE(!g.pool, "planar16 fp16 tensors are not available with fuse_pool");
-    }
-    if (g.out_i8_planar) {
-        EXB_REQUIRE(g.cout_stride % 16 == 0, "planar16 output needs cout_stride %% 16 == 0");
-        EXB_REQUIRE(g.out_dtype == EXB_I8 || g.out2_dtype == EXB_I8, "out_i8_planar without an int8 output");
-        EXB_REQUIRE(g.in_planar || g.pool, "out_i8_planar is available with in_planar = 1 or fuse_pool = 1 only");
-    }
     g.y_pitch = d->y_pitch ? d->y_pitch : g.cout_stride;
     if (g.y_pitch != g.cout_stride) {
         EXB_REQUIRE(g.y_pitch > g.cout_stride && g.y_pitch % 16 == 0 && g.cout_stride % 16 == 0,
                     "y_pitch %d needs to be a multiple of 16 above cout_stride %d, itself a multiple of 16", g.y_pitch, g.cout_stride);
-        if (g.out_dtype != EXB_F16 || g.out2_dtype != -1 || g.has_res || g.pool || g.in_planar || g.out_i8_planar ||
-            g.out_f16_planar || g.res_planar)
-            return fail(EXB_ERR_UNSUPPORTED, "y_pitch is implemented for one fp16 output without residual, pooling or planar16 tensors");
+        if (g.out_dtype != EXB_F16 || g.out2_dtype != -1 || g.has_res || g.pool)
+            return fail(EXB_ERR_UNSUPPORTED, "y_pitch is implemented for one fp16 output without residual or pooling");
     }
     return EXB_OK;
 }
@@ -143,12 +120,6 @@ extern "C" int exb_conv2d_pool_fusable(const exb_conv_desc* d) {
     ConvGeom g;
     if (int rc = resolve(d, g)) return rc;
     return (d->impl != 1 && conv_tc_eligible(g) && conv_tc_pool_fusable(g)) ? 1 : 0;
-}
-
-extern "C" int exb_conv2d_accepts_planar_input(const exb_conv_desc* d) {
-    ConvGeom g;
-    if (int rc = resolve(d, g)) return rc;
-    return (d->impl != 1 && conv_tc_eligible(g) && conv_tc_halo_ok(nullptr, g)) ? 1 : 0;
 }
 
 extern "C" int exb_conv2d_uses_tensor_cores(const exb_conv_desc* d) {
@@ -242,10 +213,6 @@ extern "C" int exb_conv2d_fwd(exb_ctx* ctx, const exb_conv_desc* d, const void* 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (g.pool && !(d->impl != 1 && conv_tc_eligible(g) && conv_tc_pool_fusable(g)))
         return fail(EXB_ERR_UNSUPPORTED, "fuse_pool is not available for this convolution (see exb_conv2d_pool_fusable)");
-    if ((g.in_planar || g.out_i8_planar || g.out_f16_planar || g.res_planar) && !(d->impl != 1 && conv_tc_eligible(g)))
-        return fail(EXB_ERR_UNSUPPORTED, "planar16 tensors need the tensor-core kernel");
-    if (g.in_planar && !conv_tc_halo_ok(ctx, g))
-        return fail(EXB_ERR_UNSUPPORTED, "planar16 input is not available for this convolution (see exb_conv2d_accepts_planar_input)");
     if (g.y_pitch != g.cout_stride && !(d->impl != 1 && conv_tc_eligible(g)))
         return fail(EXB_ERR_UNSUPPORTED, "y_pitch needs the tensor-core kernel");
     if (d->impl != 1 && conv_tc_eligible(g)) return conv_tc_launch(ctx, g, x, w, residual, y, y2, st);

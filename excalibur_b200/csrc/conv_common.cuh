@@ -32,8 +32,6 @@ struct ConvGeom {
     int w_pitch, w_pad;   // physical pixels per input row and zero pixels left of pixel 0 (dense: W, 0)
     int pool;             // 1: 3x3/2 pad-1 max pooling fused into the epilogue; y is [N][PH][PW][cout_stride]
     int PH, PW;
-    int in_planar, out_i8_planar;   // planar16 int8 input / int8 output (see exb_conv_desc)
-    int out_f16_planar, res_planar; // planar16 fp16 output / residual
     int y_pitch;                    // elements between output pixels of y (== cout_stride unless y is a slice of a wider tensor)
 };
 
@@ -80,9 +78,6 @@ struct EpiParams {
     float out_scale, out2_scale;
     int cout_stride;
     int y_pitch;     // elements between output pixels of y / y2
-    int i8_planar;   // the int8 output (y or y2) is planar16
-    int f16_planar;  // the fp16 output (y or y2) is planar16
-    int res_planar;  // the residual is planar16 fp16
 };
 
 // v = act(acc * scale + bias + residual)
@@ -156,6 +151,26 @@ __device__ __forceinline__ void epi_store_vec16(void* y, int dtype, int64_t off,
     }
 }
 
+// 8 consecutive channels starting at element offset `off` (8-byte aligned for every dtype): fp16, int8 or fp32.
+__device__ __forceinline__ void epi_store_vec8(void* y, int dtype, int64_t off, const float (&v)[8], float qscale) {
+    if (dtype == EXB_I8) {
+        uint2 o;
+        o.x = quant_pack4(v[0], v[1], v[2], v[3], qscale);
+        o.y = quant_pack4(v[4], v[5], v[6], v[7], qscale);
+        *reinterpret_cast<uint2*>(static_cast<int8_t*>(y) + off) = o;
+    } else if (dtype == EXB_F16) {
+        uint4 o;
+        __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(static_cast<__half*>(y) + off) = o;
+    } else {
+        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(y) + off);
+        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
 // Activation over a register vector with the selector hoisted out of the element loop (one uniform
 // branch per chunk instead of a switch per element).
 __device__ __forceinline__ void prelu_vec16(float (&v)[16], const float* slope) {
@@ -201,7 +216,5 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
 bool conv_tc_eligible(const ConvGeom& g);
 // True when the tcgen05 kernel can also apply the 3x3/2 max pooling in its epilogue.
 bool conv_tc_pool_fusable(const ConvGeom& g);
-// True when the tcgen05 kernel can read a planar16 int8 input for this geometry (halo mode).
-bool conv_tc_halo_ok(const exb_ctx* ctx, const ConvGeom& g);
 
 }  // namespace exb

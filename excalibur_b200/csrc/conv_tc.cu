@@ -4,22 +4,30 @@
 // for every kernel tap (r,s) and channel block the A operand is a TMA tiled load of a shifted
 // TW x TH x TN box of NHWC pixels (out-of-bounds rows and columns are zero-filled by the TMA
 // unit, which is the convolution's zero padding), landing in shared memory as 128 K-major rows
-// in the hardware swizzle; the B operand is a 2-D TMA load of the packed weight matrix
+// in the hardware swizzle; the B operand is a TMA load of the packed weight matrix
 // [Cout][kh][kw][Cin].  Stride-2 layers read one of four "parity" views of the input (every
 // second row / column, offset by 0 or 1) so that a box is still a dense rectangle.
 //
 // Persistent CTAs: two per SM with 10 warps each for N tiles of up to 128 channels, one per SM with
-// 18 warps for wider ones (no idle warps: 320 threads leave 102 registers per thread at two CTAs per SM).
+// 18 warps for wider ones.
 //   warp 0   TMA producer (lane g issues K block g of a stage) - fills a ring of shared-memory stages
 //   warp 1   MMA issuer (one lane) + TMEM owner                 - tcgen05.mma, fp32 / int32 accumulators
 //                                                                 in as many TMEM buffers as fit (2-4)
 //   warps 2+ epilogue, in groups of four warps (one per TMEM     - tile i uses buffer i % buffers and
-//            lane quarter)                                        group i % groups: tcgen05.ld, scale /
-//                                                                 bias, residual, activation, requantise,
-//                                                                 32-byte NHWC stores
-// Variants, each its own instantiation: patch mode for few-channel stride-2 stems (the raw input
-// patch read through un-swizzled overlapping descriptors), the same with a 3x3/2 max pooling in the
-// epilogue, and halo mode for planar16 int8 input.
+//            lane quarter)                                        group i % groups
+//
+// What bounds this kernel is the SM's shared-memory data path (128 bytes per clock): tensor-core operand
+// reads, TMA writes and every load / store of the epilogue go through it.  Two epilogues exist:
+//   quad  (N tile a multiple of 32 channels): accumulators leave TMEM in the 16x256b shape, in which four
+//         neighbouring lanes hold one pixel; the B operand is loaded through a tensor map that permutes the
+//         output channels inside each 32-channel block so that those four lanes hold channels 0-7, 8-15,
+//         16-23, 24-31 of the pixel.  Residual loads and output stores of a warp then cover 8 pixels x 64
+//         contiguous bytes (whole 32-byte sectors) instead of 32 separate pieces.
+//   row   (any N tile, ragged channel counts): a thread owns one pixel (one TMEM lane) and walks its
+//         channels 16 at a time.
+// Variants with their own instantiation: patch mode for few-channel stride-2 stems (the raw input patch
+// read through un-swizzled overlapping descriptors) with a 3x3/2 max pooling in the epilogue, and the
+// per-channel PReLU activation.
 // All mbarrier waits are bounded; when one runs out the kernel raises the context's error
 // word, every role leaves its loop, TMEM is freed and the launch returns normally.
 #include "conv_common.cuh"
@@ -31,13 +39,12 @@ namespace exb {
 namespace {
 
 constexpr int kMaxStages = 8;
-#ifndef EXB_FIRST_EPI_WARP
-#define EXB_FIRST_EPI_WARP 2
-#endif
-constexpr int kFirstEpiWarp = EXB_FIRST_EPI_WARP;   // warp 0 producer, warp 1 MMA issuer, epilogue warps from here on
+constexpr int kFirstEpiWarp = 2;   // warp 0 producer, warp 1 MMA issuer, epilogue warps from here on
 constexpr int kMaxAccBufs = 4;
 constexpr int kTileM = 128;
 constexpr uint32_t kMaxSpins = 1u << 21;  // tens of milliseconds at least; a legitimate wait is microseconds
+
+enum EpiKind { kEpiRow = 0, kEpiQuad = 1, kEpiPool = 2 };
 
 struct ConvTcParams {
     CUtensorMap tmA[4];
@@ -67,6 +74,7 @@ struct ConvTcParams {
     int fold;         // folded K layout (see FoldPlan): one K block per kernel row
     int b_resident;   // the whole weight slice stays in shared memory for the life of the CTA
     int b_region;     // bytes of the B region in shared memory (ring or resident copy)
+    int b_perm;       // tmB is the 5-D channel-permuting map of the quad epilogue
     // "Patch" mode for stride-2 stems on NHWC4 rows (8-byte pixels): the A operand of kernel row r
     // is the raw input patch itself, read through an un-swizzled descriptor whose rows are 16
     // bytes apart (= one output column) and whose K chunks are 16 bytes apart as well, so the
@@ -84,28 +92,7 @@ struct ConvTcParams {
     // starts at (6*tx - 1, 14*ty - 1), so it holds every input of the 3 x 7 pooled outputs that
     // start at (3*tx, 7*ty); neighbouring tiles overlap by two rows / columns, which are recomputed.
     int pool, PH, PW;
-    // "Halo" mode for 3x3 stride-1 pad-1 int8 convolutions on planar16 input
-    // ([N][C/16][H][W][16]): ONE 4-D TMA load brings the (TH+2) x (TW+2) halo patch of every
-    // 16-channel slice into un-swizzled shared memory as [slice][row][10 pixels x 16 bytes]; tap
-    // (r, s) of the implicit GEMM is the same patch read through a descriptor that starts
-    // (r*10 + s)*16 bytes in (8 consecutive pixels = one 128-byte core matrix, next tile row 160
-    // bytes on, next K chunk one slice plane on).  The weights stay resident in the canonical
-    // un-swizzled K-major layout.  Operand traffic from L2 falls from nine boxes to one.
-    int halo;
-    int halo_plane;   // bytes of one 16-channel slice of the patch
-    int cchunks;      // 16-channel slices of the input
-    int xflags;       // experiment switches (always 0 in the shipped build)
-    unsigned long long* trace;   // experiments: clock64 stamps of CTA 0, [role 0..3][tile 0..63][4]
 };
-
-#ifdef EXB_CONV_EXPERIMENTS
-#define EXB_TRACE(role, tile_i, k)                                                              \
-    do {                                                                                        \
-        if (p.trace && blockIdx.x == 0 && (tile_i) < 64) p.trace[((role) * 64 + (tile_i)) * 4 + (k)] = clock64(); \
-    } while (0)
-#else
-#define EXB_TRACE(role, tile_i, k) do { } while (0)
-#endif
 
 struct TileCoord {
     int ow0, oh0, n0, ntile;
@@ -122,24 +109,108 @@ __device__ __forceinline__ TileCoord decode_tile(const ConvTcParams& p, int t) {
     return c;
 }
 
-// kDbg is 0 in the product; builds with -DEXB_CONV_EXPERIMENTS can switch single parts of the
-// kernel off (1: epilogue math and stores, 2: TMA loads, 4: MMAs, 8: TMEM loads) to see which
-// part bounds a layer.  The results are wrong in those modes by construction.
-//
+// One pixel's 16 consecutive channels starting at channel `cl`: v = acc * scale + bias (+ residual) -> activation ->
+// first / second output.  `pix` is the pixel's index in the output tensor.  The accumulators are raw[kStep * (i / 2) +
+// kFirst + (i & 1)], i = 0..15: (16, 2, 0) reads a plain 16-register chunk, (32, 4, 0) / (32, 4, 2) the first / second
+// pixel of a 16x256b fragment.
+template <bool kInt8, bool kPrelu, int kRegs, int kStep, int kFirst>
+__device__ __forceinline__ void epi_row16(const EpiParams& e, const float* s_scale, const float* s_bias, int cl, int64_t pix,
+                                          bool add_res, const uint32_t (&res)[8], const uint32_t (&raw)[kRegs]) {
+    float v[16];
+    const float4* sc = reinterpret_cast<const float4*>(s_scale + cl);
+    const float4* bi = reinterpret_cast<const float4*>(s_bias + cl);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 s4 = sc[i], b4 = bi[i];
+        v[4 * i + 0] = epi_value<kInt8>(raw[kStep * (2 * i) + kFirst], s4.x, b4.x);
+        v[4 * i + 1] = epi_value<kInt8>(raw[kStep * (2 * i) + kFirst + 1], s4.y, b4.y);
+        v[4 * i + 2] = epi_value<kInt8>(raw[kStep * (2 * i + 1) + kFirst], s4.z, b4.z);
+        v[4 * i + 3] = epi_value<kInt8>(raw[kStep * (2 * i + 1) + kFirst + 1], s4.w, b4.w);
+    }
+    if (add_res) {
+        const __half2* h = reinterpret_cast<const __half2*>(res);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = __half22float2(h[i]);
+            v[2 * i] += f.x;
+            v[2 * i + 1] += f.y;
+        }
+    }
+    if constexpr (kPrelu) prelu_vec16(v, e.slope + cl);
+    else act_vec16(v, e.act);
+    const int64_t off = pix * e.y_pitch + cl;
+    uint32_t acc[16];       // raw accumulators in channel order (only the int32 output reads them)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = raw[kStep * (i >> 1) + kFirst + (i & 1)];
+    epi_store_vec16(e.y, e.out_dtype, off, v, e.out_scale, acc);
+    if (e.out2_dtype >= 0) epi_store_vec16(e.y2, e.out2_dtype, off, v, e.out2_scale, acc);
+}
+
+// Two pixels' 8 consecutive channels from one 16x256b.x4 fragment (raw[4g + e] first pixel, raw[4g + 2 + e] second
+// pixel, channels cl + 2g + e).  Scale and bias are read once for both pixels, from the quad-ordered copy: the four
+// floats of channels 8*j + 4*i .. + 3 of a 32-channel block sit at 32*block + 16*i + 4*j, so that the four lanes of a
+// pixel read one contiguous 64-byte piece per load (channel order would put neighbouring lanes on the same banks).
+template <bool kInt8, bool kPrelu>
+__device__ __forceinline__ void epi_quad_rows(const EpiParams& e, const float* q_scale, const float* q_bias, int cl, int cq,
+                                              int pa, int pb, bool add_res, const uint4& ra, const uint4& rb,
+                                              const uint32_t (&raw)[16]) {
+    float va[8], vb[8];
+    const float4* sc = reinterpret_cast<const float4*>(q_scale + (cl & ~31) + 4 * cq);
+    const float4* bi = reinterpret_cast<const float4*>(q_bias + (cl & ~31) + 4 * cq);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float4 s4 = sc[4 * i], b4 = bi[4 * i];
+        va[4 * i + 0] = epi_value<kInt8>(raw[8 * i + 0], s4.x, b4.x);
+        va[4 * i + 1] = epi_value<kInt8>(raw[8 * i + 1], s4.y, b4.y);
+        va[4 * i + 2] = epi_value<kInt8>(raw[8 * i + 4], s4.z, b4.z);
+        va[4 * i + 3] = epi_value<kInt8>(raw[8 * i + 5], s4.w, b4.w);
+        vb[4 * i + 0] = epi_value<kInt8>(raw[8 * i + 2], s4.x, b4.x);
+        vb[4 * i + 1] = epi_value<kInt8>(raw[8 * i + 3], s4.y, b4.y);
+        vb[4 * i + 2] = epi_value<kInt8>(raw[8 * i + 6], s4.z, b4.z);
+        vb[4 * i + 3] = epi_value<kInt8>(raw[8 * i + 7], s4.w, b4.w);
+    }
+    if (add_res) {
+        const __half2* ha = reinterpret_cast<const __half2*>(&ra);
+        const __half2* hb = reinterpret_cast<const __half2*>(&rb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fa = __half22float2(ha[i]), fb = __half22float2(hb[i]);
+            va[2 * i] += fa.x;
+            va[2 * i + 1] += fa.y;
+            vb[2 * i] += fb.x;
+            vb[2 * i + 1] += fb.y;
+        }
+    }
+    if constexpr (kPrelu) {
+        const float4 l0 = __ldg(reinterpret_cast<const float4*>(e.slope + cl)), l1 = __ldg(reinterpret_cast<const float4*>(e.slope + cl) + 1);
+        const float sl[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            va[i] = va[i] >= 0.f ? va[i] : va[i] * sl[i];
+            vb[i] = vb[i] >= 0.f ? vb[i] : vb[i] * sl[i];
+        }
+    } else {
+        apply_act_vec(va, e.act);
+        apply_act_vec(vb, e.act);
+    }
+    if (pa >= 0) {
+        const int64_t off = (int64_t)pa * e.y_pitch + cl;
+        epi_store_vec8(e.y, e.out_dtype, off, va, e.out_scale);
+        if (e.out2_dtype >= 0) epi_store_vec8(e.y2, e.out2_dtype, off, va, e.out2_scale);
+    }
+    if (pb >= 0) {
+        const int64_t off = (int64_t)pb * e.y_pitch + cl;
+        epi_store_vec8(e.y, e.out_dtype, off, vb, e.out_scale);
+        if (e.out2_dtype >= 0) epi_store_vec8(e.y2, e.out2_dtype, off, vb, e.out2_scale);
+    }
+}
+
 // kEpiWarps = 16: one CTA per SM (all of shared memory and TMEM, 2-4 accumulator buffers).
-// kEpiWarps = 8:  two CTAs per SM for layers with narrow N tiles, whose cost is the issue rate of
-//                 the single MMA-issuing thread rather than tensor throughput: two CTAs give two
-//                 issuers (and two producers) per SM; each takes half the shared memory and at
-//                 most 256 TMEM columns.
-//
-// kPool: the fused max-pooling epilogue (its own instantiation so that the plain kernels keep their
-// register allocation).
-// kHalo: the planar16 halo-patch main loop, likewise its own instantiation.
-// kPlanar: planar16 fp16 output / residual addressing in the epilogue, likewise.
-// kPrelu: the epilogue's activation is the per-channel PReLU (its own instantiation, so the slope loads cost the
-// other kernels no registers).
-template <bool kInt8, int kDbg, int kEpiWarps, bool kPool = false, bool kHalo = false, bool kPlanar = false,
-          bool kPrelu = false>
+// kEpiWarps = 8:  two CTAs per SM for layers with narrow N tiles: two MMA issuers and two producers per SM;
+//                 each CTA takes half the shared memory and at most 256 TMEM columns.
+// kEpi: which epilogue (see the head of the file); each is its own instantiation so that the others keep
+// their register allocation.  kPrelu: the activation is the per-channel PReLU.
+template <bool kInt8, int kEpiWarps, int kEpi, bool kPrelu = false>
 __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps == 8 ? 2 : 1)
     conv_tc_kernel(const __grid_constant__ ConvTcParams p) {
     constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
@@ -227,23 +298,12 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         }
         ptx::fence_proxy_async();   // generic-proxy writes, read by the tensor core through the async proxy
     }
-    if constexpr (kHalo) {
-        // Weights [cout_pad][9 * cin_pad] bytes -> for 16-byte K chunk kc and output channel n:
-        // kc*(BN*16) + (n/8)*128 + (n%8)*16.
-        const uint4* src = static_cast<const uint4*>(p.w_global);
-        const int kchunks = 9 * p.cchunks;
-        const int total = p.BN * kchunks;
-        for (int i = threadIdx.x; i < total; i += kThreads) {
-            const int kc = i % kchunks, n = i / kchunks;
-            const uint4 v = n < p.cout_pad ? src[(size_t)n * kchunks + kc] : make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(smem_b + (size_t)kc * (p.BN * 16) + (n >> 3) * 128 + (n & 7) * 16) = v;
-        }
-        ptx::fence_proxy_async();
-    }
     for (int c = threadIdx.x; c < p.n_tiles * p.BN; c += kThreads) {
         const bool in = c < p.cout_pad;
-        s_scale[c] = in ? p.e.scale[c] : 0.f;
-        s_bias[c] = in ? p.e.bias[c] : 0.f;
+        // quad epilogue: channel 32*b + 8*j + 4*i + k is kept at 32*b + 16*i + 4*j + k (see epi_quad_rows)
+        const int at = kEpi == kEpiQuad ? ((c & ~31) | ((c & 4) << 2) | ((c & 24) >> 1) | (c & 3)) : c;
+        s_scale[at] = in ? p.e.scale[c] : 0.f;
+        s_bias[at] = in ? p.e.bias[c] : 0.f;
     }
     // Programmatic dependent launch: everything above touches only this launch's own parameters,
     // constant weights and on-chip state, so it may run while the previous kernel of the stream is
@@ -270,44 +330,19 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         const uint64_t mapA0 = reinterpret_cast<uint64_t>(&p.tmA[0]);
         const uint64_t mapB = reinterpret_cast<uint64_t>(&p.tmB);
         const bool bres = p.b_resident != 0;
+        const bool bperm = p.b_perm != 0;
         const uint32_t tx = (uint32_t)(p.a_tx_bytes + (bres ? 0 : p.b_bytes));
         if (bres && lane == 0) {
             // Weights stay resident: the slice [BN x K] is loaded once (n_tiles == 1 here).
             const uint32_t rb = ptx::smem_u32(&bres_bar);
             ptx::mbar_arrive_expect_tx_u32(rb, (uint32_t)(k_iters * p.b_bytes));
-            for (int it = 0; it < k_iters; ++it)
-                ptx::tma_load_2d_u32(ptx::smem_u32(smem_b) + (uint32_t)(it * p.b_bytes), mapB, rb,
-                                     k_tab[it].w & 0x0fffffff, 0);
-        }
-        if constexpr (kHalo) {
-            if (lane == 0) {
-                const uint32_t bytes = (uint32_t)(p.cchunks * p.halo_plane);
-                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                    const TileCoord tc = decode_tile(p, t);
-                    if (!ptx::mbar_wait_bounded_u32(empty0 + stage * 8, phase ^ 1u, &abort_flag, kMaxSpins)) {
-                        ok = 0;
-                        break;
-                    }
-                    const uint32_t fb = full0 + stage * 8;
-                    if (kDbg & 2) {
-                        ptx::mbar_arrive_u32(fb);
-                    } else {
-                    ptx::mbar_arrive_expect_tx_u32(fb, bytes);
-                    // x: byte column of pixel ow0-1 in a row of W*16 bytes, y: row oh0-1, z: slice 0, w: image
-                    ptx::tma_load_4d_u32(ptx::smem_u32(smem_a) + (uint32_t)(stage * p.a_bytes), mapA0, fb,
-                                         (tc.ow0 - 1) * 16, tc.oh0 - 1, 0, tc.n0);
-                    }
-                    if (++stage == p.stages) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
-                }
-                if (!ok) {
-                    atomicExch(p.error, 1);
-                    for (int i = 0; i < 2000; ++i) __nanosleep(100);
-                }
+            for (int it = 0; it < k_iters; ++it) {
+                const uint32_t dst = ptx::smem_u32(smem_b) + (uint32_t)(it * p.b_bytes);
+                if (bperm) ptx::tma_load_5d_u32(dst, mapB, rb, k_tab[it].w & 0x0fffffff, 0, 0, 0, 0);
+                else ptx::tma_load_2d_u32(dst, mapB, rb, k_tab[it].w & 0x0fffffff, 0);
             }
-        } else if (p.patch) {
+        }
+        if (p.patch) {
             if (lane == 0) {
                 const uint32_t bytes = (uint32_t)(p.patch_rows * p.patch_pitch);
                 for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -336,11 +371,9 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 }
             }
         } else if (lane < G) {
-            int ptile = 0;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++ptile) {
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
                 const int ncoord = tc.ntile * p.BN;
-                if (lane == 0) EXB_TRACE(0, ptile, 0);
                 for (int it0 = 0; it0 < k_iters; it0 += G) {
                     const int nb = min(G, k_iters - it0);
                     const bool mine = lane < nb;
@@ -351,22 +384,20 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         break;
                     }
                     const uint32_t fb = full0 + stage * 8;
-                    if (kDbg & 2) {
-                        if (lane == 0) ptx::mbar_arrive_u32(fb);
-                    } else {
                     if (lane == 0) ptx::mbar_arrive_expect_tx_u32(fb, tx * (uint32_t)nb);
                     if (mine) {
                         ptx::tma_load_4d_u32(a_base + stage * a_stage, mapA0 + ((uint32_t)e.w >> 28) * sizeof(CUtensorMap), fb,
                                              e.x, tc.ow0 + e.y, tc.oh0 + e.z, tc.n0);
-                        if (!bres) ptx::tma_load_2d_u32(b_base + stage * b_stage, mapB, fb, e.w & 0x0fffffff, ncoord);
-                    }
+                        if (!bres) {
+                            if (bperm) ptx::tma_load_5d_u32(b_base + stage * b_stage, mapB, fb, e.w & 0x0fffffff, 0, 0, 0, ncoord >> 5);
+                            else ptx::tma_load_2d_u32(b_base + stage * b_stage, mapB, fb, e.w & 0x0fffffff, ncoord);
+                        }
                     }
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if (lane == 0) EXB_TRACE(0, ptile, 1);
             }
             if (!ok) {
                 if (lane == 0) atomicExch(p.error, 1);
@@ -397,58 +428,15 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const uint32_t a_stage = a_blk * G, b_stage = bres ? 0u : b_blk * G;
             const uint32_t idesc = p.idesc;
             if (bres && !ptx::mbar_wait_bounded(&bres_bar, 0, &abort_flag, kMaxSpins)) ok = false;
-            int mtile = 0;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++mtile) {
-                EXB_TRACE(1, mtile, 0);
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 if (!ptx::mbar_wait_bounded_u32(tempty0 + acc * 8, acc_phase ^ 1u, &abort_flag, kMaxSpins)) {
                     ok = false;
                     break;
                 }
-                EXB_TRACE(1, mtile, 1);
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
                 uint32_t accumulate = 0;
-                if constexpr (kHalo) {
-                    if (!ptx::mbar_wait_bounded_u32(full0 + stage * 8, phase, &abort_flag, kMaxSpins)) {
-                        ok = false;
-                        break;
-                    }
-                    // un-swizzled K-major descriptors.  A: core matrix = 8 pixels x 16 B, next tile
-                    // row 160 B on (SBO), next K chunk one slice plane on (LBO).  B: core matrices
-                    // 128 B apart (SBO), next K chunk BN*16 B on (LBO).
-                    const uint32_t a0 = ((ptx::smem_u32(smem_a) + (uint32_t)(stage * p.a_bytes)) >> 4) |
-                                        ((uint32_t)(p.halo_plane >> 4) << 16);
-                    const uint32_t a_hi = (160u >> 4) | (1u << 14);
-                    const uint32_t b_lbo = (uint32_t)(p.BN * 16) >> 4;
-                    const uint32_t b0 = (ptx::smem_u32(smem_b) >> 4) | (b_lbo << 16);
-                    const uint32_t b_hi = (128u >> 4) | (1u << 14);
-                    const uint32_t plane16 = (uint32_t)p.halo_plane >> 4;
-                    const int ksn = p.cchunks >> 1;          // 32-byte K steps per tap
-                    uint32_t bk = b0;
-                    for (int tap = 0; tap < 9; ++tap) {
-                        const int r = tap / 3, sx = tap - 3 * r;
-                        uint32_t ak = a0 + (uint32_t)(r * 10 + sx);
-                        for (int ks = 0; ks < ksn; ++ks) {
-                            if (!(kDbg & 4))
-                            asm volatile(
-                                "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-                                "mov.b64 da, {%1, %2};\n\t"
-                                "mov.b64 db, {%3, %4};\n\t"
-                                "setp.ne.b32 p, %6, 0;\n\t"
-                                "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
-                                "r"(ak), "r"(a_hi), "r"(bk), "r"(b_hi), "r"(idesc), "r"(accumulate)
-                                : "memory");
-                            accumulate = 1;
-                            ak += 2 * plane16;
-                            bk += 2 * b_lbo;
-                        }
-                    }
-                    ptx::tc_commit_u32(empty0 + stage * 8);
-                    if (++stage == p.stages) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
-                } else if (p.patch) {
+                if (p.patch) {
                     if (!ptx::mbar_wait_bounded_u32(full0 + stage * 8, phase, &abort_flag, kMaxSpins)) {
                         ok = false;
                         break;
@@ -460,9 +448,6 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     const uint32_t b0 = (ptx::smem_u32(smem_b) >> 4) | ((uint32_t)(p.BN * 16 >> 4) << 16);
                     const uint32_t b_hi = (128u >> 4) | (1u << 14);
                     for (int r = 0; r < p.kh; ++r) {
-#ifdef EXB_CONV_EXPERIMENTS
-                        if (p.xflags & 32) break;
-#endif
                         const uint32_t ar = a0 + (uint32_t)(r * p.patch_pitch >> 4);
                         const uint32_t br = b0 + (uint32_t)(r * p.BN * 64 >> 4);
 #pragma unroll
@@ -493,7 +478,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     }
                     uint32_t a_lo = a_lo0 + stage * a_stage;
                     uint32_t b_lo = b_lo0 + (bres ? (uint32_t)it0 * b_blk : stage * b_stage);
-                    for (int g = 0; g < nb && !(kDbg & 4); ++g) {
+                    for (int g = 0; g < nb; ++g) {
                         if (ksteps == 4) {
                             ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
                             ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo + 2, b_lo + 2, desc_hi, idesc, 1);
@@ -516,9 +501,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     }
                 }
                 if (!ok) break;
-                EXB_TRACE(1, mtile, 2);
                 ptx::tc_commit_u32(tfull0 + acc * 8);   // accumulator complete
-                EXB_TRACE(1, mtile, 3);
                 if (++acc == p.acc_bufs) {
                     acc = 0;
                     acc_phase ^= 1u;
@@ -528,31 +511,25 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         }
     } else if (warp >= kFirstEpiWarp) {
         // ------------------------------- epilogue ------------------------------------------
-        // Tile i of this CTA's sequence is accumulated in buffer i % NB and drained by group
-        // i % NB.  A group has 16/NB warps: one (NB = 4) or two (NB = 2) per TMEM lane quarter,
-        // in the second case splitting the 16-column chunks between them.
+        // Tile i of this CTA's sequence is accumulated in buffer i % acc_bufs (use number i / acc_bufs of that
+        // buffer gives the barrier parity) and drained by group i % epi_groups.  A group has kEpiWarps /
+        // epi_groups warps: one or two per TMEM lane quarter; two share the quarter's work.
         const int e = warp - kFirstEpiWarp;
         const int q = warp & 3;                 // TMEM lane quarter: a warp can only reach lanes 32*(warp%4)..+31
         const int nsub = kEpiWarps / 4 / p.epi_groups;
         const int grp = (e >> 2) % p.epi_groups;
         const int sub = (e >> 2) / p.epi_groups;
-        const int row = q * 32 + lane;          // row of the M tile == TMEM lane
-        const int tw = row % p.TW;
-        const int th = (row / p.TW) % p.TH;
-        const int tn = row / (p.TW * p.TH);
-        const bool row_in_box = row < p.TW * p.TH * p.TN;
-        const bool vec_ok = (p.e.cout_stride & 15) == 0;
-        const int n_chunks = p.BN / 16;
-        // The CTA's i-th tile is accumulated in buffer i % acc_bufs (use number i / acc_bufs of that
-        // buffer gives the barrier parity) and drained by group i % epi_groups.
         int ti = grp;
         bool ok = true;
         const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16);
-        if constexpr (kPool) {
+        if constexpr (kEpi == kEpiPool) {
             // Convolution tile -> ReLU -> fp16 -> shared memory (16-byte units of a pixel row XOR-ed
             // with the row index so that neither phase has bank conflicts) -> 3x3/2 max -> global.
             // The group's four warps meet at a named barrier twice per tile; a warp whose bounded
             // wait ran out still arrives, and the whole group leaves together afterwards.
+            const int row = q * 32 + lane;          // row of the M tile == TMEM lane
+            const int tw = row % p.TW;
+            const int th = (row / p.TW) % p.TH;
             uint8_t* stg = pool_stage + grp * (kTileM * 128);
             volatile int* failed = &pool_fail[grp];
             for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles; t += p.epi_groups * gridDim.x, ti += p.epi_groups) {
@@ -569,14 +546,8 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
 #pragma unroll
                     for (int chunk = 0; chunk < 4; ++chunk) {
                         uint32_t raw[16];
-#ifdef EXB_CONV_EXPERIMENTS
-                        if (p.xflags & 16) continue;
-#endif
                         ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
                         ptx::tmem_ld_wait();
-#ifdef EXB_CONV_EXPERIMENTS
-                        if (p.xflags & 4) continue;
-#endif
                         float v[16];
                         const float4* sc = reinterpret_cast<const float4*>(s_scale + chunk * 16);
                         const float4* bi = reinterpret_cast<const float4*>(s_bias + chunk * 16);
@@ -611,9 +582,6 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     break;
                 }
                 const int ph0 = (tc.oh0 + 1) >> 1, pw0 = (tc.ow0 + 1) >> 1;
-#ifdef EXB_CONV_EXPERIMENTS
-                if (!(p.xflags & 8))
-#endif
                 for (int item = row; item < 21 * 8; item += kTileM) {
                     const int pp = item >> 3, u = item & 7;
                     const int pr = pp / 3, pc = pp - 3 * pr;
@@ -645,177 +613,173 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         uint2 qv;
                         qv.x = quant_pack4(f0.x, f0.y, f1.x, f1.y, p.e.out2_scale);
                         qv.y = quant_pack4(f2.x, f2.y, f3.x, f3.y, p.e.out2_scale);
-                        const int64_t off8 = p.e.i8_planar
-                                                 ? ((((int64_t)tc.n0 * (p.e.cout_stride >> 4) + (u >> 1)) * p.PH + ph) * p.PW + pw) * 16 + (u & 1) * 8
-                                                 : off;
-                        *reinterpret_cast<uint2*>(static_cast<int8_t*>(p.e.y2) + off8) = qv;
+                        *reinterpret_cast<uint2*>(static_cast<int8_t*>(p.e.y2) + off) = qv;
                     }
                 }
                 // staging may be overwritten after this one
                 if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
                 else asm volatile("bar.sync 2, 128;" ::: "memory");
             }
-        } else
-        for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles && ok; t += p.epi_groups * gridDim.x, ti += p.epi_groups) {
-            const TileCoord tc = decode_tile(p, t);
-            const int ow = tc.ow0 + tw, oh = tc.oh0 + th, n = tc.n0 + tn;
-            const int buf = ti % p.acc_bufs;
-            const uint32_t acc_phase = (uint32_t)(ti / p.acc_bufs) & 1u;
-            const uint32_t taddr = taddr0 + (uint32_t)(buf * p.BN);
-            const bool valid = row_in_box && ow < p.OW && oh < p.OH && n < p.N;
-            const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
-            // This warp's chunks of 16 channels.  The residual of a chunk is requested one chunk
-            // ahead (the first one before the accumulator is even ready), because with so few
-            // epilogue warps an exposed global-memory latency per chunk is what the epilogue costs.
-            const int per = (n_chunks + nsub - 1) / nsub;
-            const int c_begin = sub * per, c_end = min(n_chunks, (sub + 1) * per);
-            const bool do_res = p.has_res && vec_ok && valid && !(kDbg & 16);
-            // planar16 fp16: element offset of (n, slice 0, oh, ow); a slice is `plane` elements on
-            int64_t poff = 0, plane = 0;
-            if constexpr (kPlanar) {
-                plane = (int64_t)p.OH * p.OW * 16;
-                poff = (int64_t)n * (p.e.cout_stride >> 4) * plane + ((int64_t)oh * p.OW + ow) * 16;
+        } else if constexpr (kEpi == kEpiQuad) {
+            // Four neighbouring lanes hold one pixel: lane l of a 16-lane half covers tile rows r = l / 4 and
+            // r + 8 and, of every 32-channel block, channels 8 * (l % 4) .. + 7 (the B tensor map stores
+            // channel 8*j + 2*g + e of a block in accumulator column 8*g + 2*j + e, which is where the 16x256b
+            // shape puts registers 4*g + e of lane quad member j).  A warp's 16-byte accesses therefore cover
+            // 8 pixels x 64 contiguous bytes, every 32-byte sector whole.
+            const int cq = lane & 3;
+            const int nblk = p.BN >> 5;
+            const int h_begin = nsub == 2 ? sub : 0, h_end = nsub == 2 ? sub + 1 : 2;
+            // tile rows of this thread: [half][0 / +8], packed tw | th << 8 | tn << 16, bit 31 = row outside the box
+            uint32_t rowpack[2][2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int row = q * 32 + h * 16 + k * 8 + (lane >> 2);
+                    const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
+                    rowpack[h][k] = (uint32_t)tw | ((uint32_t)th << 8) | ((uint32_t)tn << 16) |
+                                    (row < p.TW * p.TH * p.TN ? 0u : 0x80000000u);
+                }
+            // pixel index of a packed row in tile `c`, or -1 when the row lies outside the output
+            auto pixel_of = [&](const TileCoord& c, uint32_t rp) -> int {
+                const int ow = c.ow0 + (int)(rp & 0xff), oh = c.oh0 + (int)((rp >> 8) & 0xff);
+                const int n = c.n0 + (int)((rp >> 16) & 0x7fff);
+                if ((rp >> 31) || ow >= p.OW || oh >= p.OH || n >= p.N) return -1;
+                return (n * p.OH + oh) * p.OW + ow;
+            };
+            const bool want_res = p.has_res != 0;
+            for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles && ok; t += p.epi_groups * gridDim.x, ti += p.epi_groups) {
+                const TileCoord tc = decode_tile(p, t);
+                const int buf = ti % p.acc_bufs;
+                const uint32_t acc_phase = (uint32_t)(ti / p.acc_bufs) & 1u;
+                const int c0 = tc.ntile * p.BN + cq * 8;       // first channel of this thread in block 0
+                // The residual lines of this group's NEXT tile are asked into L2 now (no register cost): when that
+                // tile's turn comes its residual loads find them a few hundred cycles away instead of in DRAM.
+                if (want_res && t + p.epi_groups * (int)gridDim.x < total_tiles) {
+                    const TileCoord c2 = decode_tile(p, t + p.epi_groups * (int)gridDim.x);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (h < h_begin || h >= h_end) continue;
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const int px = pixel_of(c2, rowpack[h][k]);
+                            if (px < 0) continue;
+                            const __half* r2 = p.e.residual + (int64_t)px * p.e.cout_stride + c2.ntile * p.BN;
+                            for (int l = cq; l * 64 < p.BN; l += 4)      // one 128-byte line per pixel and 64 channels
+                                if (c2.ntile * p.BN + l * 64 < p.e.cout_stride) asm volatile("prefetch.global.L2 [%0];" ::"l"(r2 + l * 64));
+                        }
+                    }
+                }
+                if (!ptx::mbar_wait_bounded_warp(&tfull_bar[buf], acc_phase, &abort_flag, kMaxSpins)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (h < h_begin || h >= h_end) continue;
+                    const uint32_t taddr = taddr0 + ((uint32_t)(h * 16) << 16) + (uint32_t)(buf * p.BN);
+                    const int pa = pixel_of(tc, rowpack[h][0]), pb = pixel_of(tc, rowpack[h][1]);
+#pragma unroll 1
+                    for (int b = 0; b < nblk; ++b) {
+                        const int cl = c0 + b * 32;
+                        const bool c_in = cl < p.e.cout_stride;
+                        // residual first: its latency overlaps the TMEM load and the scale / bias arithmetic
+                        uint4 ra = make_uint4(0, 0, 0, 0), rb = make_uint4(0, 0, 0, 0);
+                        if (want_res && c_in) {
+                            if (pa >= 0) ra = __ldg(reinterpret_cast<const uint4*>(p.e.residual + (int64_t)pa * p.e.cout_stride + cl));
+                            if (pb >= 0) rb = __ldg(reinterpret_cast<const uint4*>(p.e.residual + (int64_t)pb * p.e.cout_stride + cl));
+                        }
+                        uint32_t raw[16];
+                        ptx::tmem_ld_16x256b_x4(taddr + b * 32, raw);
+                        ptx::tmem_ld_wait();
+                        if (!c_in) continue;
+                        epi_quad_rows<kInt8, kPrelu>(p.e, s_scale, s_bias, cl, cq, pa, pb, want_res, ra, rb, raw);
+                    }
+                }
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&tempty_bar[buf]);
             }
-            // residual of 16-channel chunk c: res_row + c * res_step
-            const bool rpl = kPlanar && p.e.res_planar;
-            const __half* res_row = rpl ? p.e.residual + poff + (int64_t)(tc.ntile * p.BN >> 4) * plane
-                                        : p.e.residual + pix * p.e.cout_stride + tc.ntile * p.BN;
-            const int64_t res_step = rpl ? plane : 16;
-            uint32_t rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (do_res && c_begin < c_end && tc.ntile * p.BN + c_begin * 16 < p.e.cout_stride)
-                ld_global_nc_256(res_row + c_begin * res_step, rn);
-            // The residual rows of this group's NEXT tile are asked into L2 now (no register cost):
-            // the tile after this one then finds them a few hundred cycles away instead of a DRAM
-            // round trip per chunk, which the one-chunk-ahead register prefetch cannot cover.
-            if (p.has_res && vec_ok && t + p.epi_groups * (int)gridDim.x < total_tiles) {
-                const TileCoord c2 = decode_tile(p, t + p.epi_groups * (int)gridDim.x);
-                const int ow2 = c2.ow0 + tw, oh2 = c2.oh0 + th, n2 = c2.n0 + tn;
-                if (row_in_box && ow2 < p.OW && oh2 < p.OH && n2 < p.N) {
-                    if (rpl) {      // one 32-byte piece per slice; the four lanes of a line ask for it together
-                        const __half* r2 = p.e.residual + (int64_t)n2 * (p.e.cout_stride >> 4) * plane +
-                                           ((int64_t)oh2 * p.OW + ow2) * 16 + (int64_t)((c2.ntile * p.BN >> 4) + c_begin) * plane;
-                        if ((tw & 3) == 0)
-                            for (int c = 0; c < c_end - c_begin; ++c)
-                                asm volatile("prefetch.global.L2 [%0];" ::"l"(r2 + c * plane));
-                    } else {
+        } else {
+            const int row = q * 32 + lane;          // row of the M tile == TMEM lane
+            const int tw = row % p.TW;
+            const int th = (row / p.TW) % p.TH;
+            const int tn = row / (p.TW * p.TH);
+            const bool row_in_box = row < p.TW * p.TH * p.TN;
+            const bool vec_ok = (p.e.cout_stride & 15) == 0;
+            const int n_chunks = p.BN / 16;
+            for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles && ok; t += p.epi_groups * gridDim.x, ti += p.epi_groups) {
+                const TileCoord tc = decode_tile(p, t);
+                const int ow = tc.ow0 + tw, oh = tc.oh0 + th, n = tc.n0 + tn;
+                const int buf = ti % p.acc_bufs;
+                const uint32_t acc_phase = (uint32_t)(ti / p.acc_bufs) & 1u;
+                const uint32_t taddr = taddr0 + (uint32_t)(buf * p.BN);
+                const bool valid = row_in_box && ow < p.OW && oh < p.OH && n < p.N;
+                const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
+                // This warp's chunks of 16 channels.  The residual of a chunk is requested one chunk
+                // ahead (the first one before the accumulator is even ready), because with so few
+                // epilogue warps an exposed global-memory latency per chunk is what the epilogue costs.
+                const int per = (n_chunks + nsub - 1) / nsub;
+                const int c_begin = sub * per, c_end = min(n_chunks, (sub + 1) * per);
+                const bool do_res = p.has_res && vec_ok && valid;
+                const __half* res_row = p.e.residual + pix * p.e.cout_stride + tc.ntile * p.BN;
+                uint32_t rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (do_res && c_begin < c_end && tc.ntile * p.BN + c_begin * 16 < p.e.cout_stride)
+                    ld_global_nc_256(res_row + c_begin * 16, rn);
+                // The residual rows of this group's NEXT tile are asked into L2 now (no register cost):
+                // the tile after this one then finds them a few hundred cycles away instead of a DRAM
+                // round trip per chunk, which the one-chunk-ahead register prefetch cannot cover.
+                if (p.has_res && vec_ok && t + p.epi_groups * (int)gridDim.x < total_tiles) {
+                    const TileCoord c2 = decode_tile(p, t + p.epi_groups * (int)gridDim.x);
+                    const int ow2 = c2.ow0 + tw, oh2 = c2.oh0 + th, n2 = c2.n0 + tn;
+                    if (row_in_box && ow2 < p.OW && oh2 < p.OH && n2 < p.N) {
                         const __half* r2 = p.e.residual + (((int64_t)n2 * p.OH + oh2) * p.OW + ow2) * p.e.cout_stride +
                                            c2.ntile * p.BN + c_begin * 16;
                         for (int b = 0; b < (c_end - c_begin) * 32; b += 128)
                             asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(r2) + b));
                     }
                 }
-            }
-#ifdef EXB_CONV_EXPERIMENTS
-            if (p.xflags & 1) {          // every lane polls, no sleep
-                if (!ptx::mbar_wait_bounded(&tfull_bar[buf], acc_phase, &abort_flag, kMaxSpins)) {
+                if (!ptx::mbar_wait_bounded_warp(&tfull_bar[buf], acc_phase, &abort_flag, kMaxSpins)) {
                     ok = false;
                     break;
                 }
-            } else
-#endif
-            if (q == 0 && sub == 0 && lane == 0) EXB_TRACE(2, ti, 0);
-            if (!ptx::mbar_wait_bounded_warp(&tfull_bar[buf], acc_phase, &abort_flag, kMaxSpins)) {
-                ok = false;
-                break;
-            }
-            if (q == 0 && sub == 0 && lane == 0) EXB_TRACE(2, ti, 1);
-            ptx::tc_fence_after_sync();
-#ifdef EXB_CONV_EXPERIMENTS
-            if (p.xflags & 2) {          // epilogue reduced to the accumulator hand-back
+                ptx::tc_fence_after_sync();
+                for (int chunk = c_begin; chunk < c_end; ++chunk) {
+                    uint32_t raw[16];
+                    ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
+                    uint32_t rc[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) rc[i] = rn[i];
+                    if (do_res && chunk + 1 < c_end && tc.ntile * p.BN + (chunk + 1) * 16 < p.e.cout_stride)
+                        ld_global_nc_256(res_row + (chunk + 1) * 16, rn);
+                    ptx::tmem_ld_wait();
+                    const int cl = tc.ntile * p.BN + chunk * 16;   // first channel of the chunk
+                    if (!valid || cl >= p.e.cout_stride) continue;
+                    if (vec_ok) {
+                        epi_row16<kInt8, kPrelu, 16, 2, 0>(p.e, s_scale, s_bias, cl, pix, do_res, rc, raw);
+                    } else {
+                        // ragged channel count: element-wise stores, statically indexed so the
+                        // accumulators stay in registers
+                        const int64_t off = pix * p.e.y_pitch + cl;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            if (cl + i < p.e.cout_stride) {
+                                float u = epi_value<kInt8>(raw[i], s_scale[cl + i], s_bias[cl + i]);
+                                if (p.has_res) u += __half2float(p.e.residual[off + i]);
+                                if constexpr (kPrelu) u = u >= 0.f ? u : u * __ldg(p.e.slope + cl + i);
+                                else u = apply_act(u, p.e.act);
+                                epi_store_scalar(p.e.y, p.e.out_dtype, off + i, u, p.e.out_scale, raw[i]);
+                                if (p.e.out2_dtype >= 0)
+                                    epi_store_scalar(p.e.y2, p.e.out2_dtype, off + i, u, p.e.out2_scale, raw[i]);
+                            }
+                        }
+                    }
+                }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&tempty_bar[buf]);
-                continue;
             }
-#endif
-            for (int chunk = c_begin; chunk < c_end; ++chunk) {
-                uint32_t raw[16];
-                if (kDbg & 8) continue;
-                ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
-                uint32_t rc[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) rc[i] = rn[i];
-                if (do_res && chunk + 1 < c_end && tc.ntile * p.BN + (chunk + 1) * 16 < p.e.cout_stride)
-                    ld_global_nc_256(res_row + (chunk + 1) * res_step, rn);
-                ptx::tmem_ld_wait();
-                const int cl = tc.ntile * p.BN + chunk * 16;   // first channel of the chunk
-                if (!valid || cl >= p.e.cout_stride || (kDbg & 1)) continue;
-                const int64_t off = pix * p.e.y_pitch + cl;
-                // planar16: [n][channel slice][oh][ow][16]
-                int64_t off8 = off;
-                if constexpr (kHalo) {   // only this instantiation (and the pooling one) can write planar16
-                    if (p.e.i8_planar)
-                        off8 = ((((int64_t)n * (p.e.cout_stride >> 4) + (cl >> 4)) * p.OH + oh) * p.OW + ow) * 16;
-                }
-                int64_t off16 = off;
-                if constexpr (kPlanar) {
-                    if (p.e.f16_planar) off16 = poff + (int64_t)(cl >> 4) * plane;
-                }
-                float v[16];
-                {
-                    const float4* sc = reinterpret_cast<const float4*>(s_scale + cl);
-                    const float4* bi = reinterpret_cast<const float4*>(s_bias + cl);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-#ifdef EXB_CONV_EXPERIMENTS
-                        const bool noload = (p.xflags & 64) != 0;
-                        const float4 s4 = noload ? make_float4(0.01f, 0.01f, 0.01f, 0.01f) : sc[i];
-                        const float4 b4 = noload ? make_float4(0.f, 0.f, 0.f, 0.f) : bi[i];
-#else
-                        const float4 s4 = sc[i], b4 = bi[i];
-#endif
-                        v[4 * i + 0] = epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x);
-                        v[4 * i + 1] = epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y);
-                        v[4 * i + 2] = epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z);
-                        v[4 * i + 3] = epi_value<kInt8>(raw[4 * i + 3], s4.w, b4.w);
-                    }
-                }
-                if (vec_ok) {
-                    if (do_res) {
-                        const __half2* h = reinterpret_cast<const __half2*>(rc);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float2 f = __half22float2(h[i]);
-                            v[2 * i] += f.x;
-                            v[2 * i + 1] += f.y;
-                        }
-                    }
-                    if constexpr (kPrelu) prelu_vec16(v, p.e.slope + cl);
-                    else act_vec16(v, p.e.act);
-                    if (kDbg & 32) {
-                        float acc_ = 0.f;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) acc_ += v[i];
-                        if (acc_ == 123.456f) static_cast<float*>(p.e.y)[0] = acc_;   // keep the math alive
-                        continue;
-                    }
-                    epi_store_vec16(p.e.y, p.e.out_dtype,
-                                    p.e.out_dtype == EXB_I8 ? off8 : (p.e.out_dtype == EXB_F16 ? off16 : off), v, p.e.out_scale, raw);
-                    if (p.e.out2_dtype >= 0)
-                        epi_store_vec16(p.e.y2, p.e.out2_dtype,
-                                        p.e.out2_dtype == EXB_I8 ? off8 : (p.e.out2_dtype == EXB_F16 ? off16 : off), v,
-                                        p.e.out2_scale, raw);
-                } else {
-                    // ragged channel count: element-wise stores, statically indexed so the
-                    // accumulators stay in registers
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        if (cl + i < p.e.cout_stride) {
-                            float u = v[i];
-                            if (p.has_res) u += __half2float(p.e.residual[off + i]);
-                            if constexpr (kPrelu) u = u >= 0.f ? u : u * __ldg(p.e.slope + cl + i);
-                            else u = apply_act(u, p.e.act);
-                            epi_store_scalar(p.e.y, p.e.out_dtype, off + i, u, p.e.out_scale, raw[i]);
-                            if (p.e.out2_dtype >= 0)
-                                epi_store_scalar(p.e.y2, p.e.out2_dtype, off + i, u, p.e.out2_scale, raw[i]);
-                        }
-                    }
-                }
-            }
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&tempty_bar[buf]);
-            if (q == 0 && sub == 0 && lane == 0) EXB_TRACE(2, ti, 2);
         }
         if (!ok && lane == 0) atomicExch(p.error, 3);
     }
@@ -880,42 +844,6 @@ bool conv_tc_pool_fusable(const ConvGeom& g) {
            !g.has_res && (g.act == EXB_ACT_RELU || g.act == EXB_ACT_RELU6) && g.group == 1;
 }
 
-namespace {
-// Shared-memory plan of halo mode: weights resident + a ring of whole patches.
-struct HaloPlan {
-    bool ok, two;
-    int BN, a_bytes, b_bytes, stages;
-};
-HaloPlan halo_plan(const exb_ctx* ctx, const ConvGeom& g) {
-    HaloPlan h = {false, false, 0, 0, 0, 0};
-    if (g.in_dtype != EXB_I8 || g.kh != 3 || g.kw != 3 || g.sh != 1 || g.sw != 1 || g.pt != 1 || g.pl != 1 ||
-        g.OH != g.H || g.OW != g.W || g.group != 1 || g.pool || g.cin_stride % 32 != 0 || g.W < 10 || g.H < 2 ||
-        g.w_pitch != g.W)
-        return h;
-    const int cout_pad = (g.cout_stride + 15) / 16 * 16;
-    if (cout_pad > 256) return h;
-    h.BN = cout_pad;
-    h.a_bytes = round_up((g.cin_stride / 16) * 18 * 160, 128);
-    h.b_bytes = h.BN * 9 * g.cin_stride;
-    const int fixed = 2048 + 1024 + 2 * h.BN * (int)sizeof(float) + 9 * (g.cin_stride / 32 + 1) * (int)sizeof(int4);
-    const int smem_optin = ctx ? ctx->smem_optin : 227 * 1024;
-    const int budget2 = 228 * 1024 / 2 - 1024 - fixed, budget1 = smem_optin - fixed;
-    if (h.BN <= 128 && h.b_bytes + 3 * h.a_bytes <= budget2) {
-        h.two = true;
-        h.stages = (budget2 - h.b_bytes) / h.a_bytes;
-    } else if (h.b_bytes + 2 * h.a_bytes <= budget1) {
-        h.stages = (budget1 - h.b_bytes) / h.a_bytes;
-    } else {
-        return h;
-    }
-    if (h.stages > kMaxStages) h.stages = kMaxStages;
-    h.ok = true;
-    return h;
-}
-}  // namespace
-
-bool conv_tc_halo_ok(const exb_ctx* ctx, const ConvGeom& g) { return halo_plan(ctx, g).ok; }
-
 bool conv_tc_eligible(const ConvGeom& g) {
     const int es = g.in_dtype == EXB_I8 ? 1 : 2;
     if (g.group != 1) return false;
@@ -941,15 +869,9 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.tiles_nb = (g.N + p.TN - 1) / p.TN;
     p.step_w = p.TW; p.step_h = p.TH; p.org = 0;
     p.n_tiles = (w->cout_pad + 255) / 256;
-#ifdef EXB_CONV_EXPERIMENTS
-    if (const char* e = getenv("EXB_CONV_BNMAX")) p.n_tiles = (w->cout_pad + atoi(e) - 1) / atoi(e);
-#endif
     p.BN = round_up((w->cout_pad + p.n_tiles - 1) / p.n_tiles, 16);
     // Two CTAs per SM when the N tile is narrow (see the kernel's comment).
     bool two = p.BN <= 128;
-#ifdef EXB_CONV_EXPERIMENTS
-    if (const char* e = getenv("EXB_CONV_ONE_CTA")) two = two && atoi(e) == 0;
-#endif
     p.kh = g.kh; p.kw = g.kw; p.stride = g.sh; p.pad_t = g.pt; p.pad_l = g.pl;
     p.cin_pad = g.cin_stride;
     const int row_bytes = g.cin_stride * es;
@@ -987,22 +909,6 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
             p.tiles_w = (g.PW + 2) / 3;      // 3 x 7 pooled outputs per tile
             p.tiles_h = (g.PH + 6) / 7;
         }
-    }
-    const HaloPlan hp = g.in_planar ? halo_plan(ctx, g) : HaloPlan{false, false, 0, 0, 0, 0};
-    if (g.in_planar) {
-        if (!hp.ok || p.n_tiles != 1 || p.BN != hp.BN || w->kw_pack != 3 || w->cin_pad != g.cin_stride)
-            return fail(EXB_ERR_UNSUPPORTED, "planar16 input is not available for this convolution");
-        p.halo = 1;
-        two = hp.two;
-        p.TW = 8; p.TH = 16; p.TN = 1;
-        p.tiles_w = (g.OW + 7) / 8;
-        p.tiles_h = (g.OH + 15) / 16;
-        p.tiles_nb = g.N;
-        p.step_w = 8; p.step_h = 16; p.org = 0;
-        p.cchunks = g.cin_stride / 16;
-        p.halo_plane = 18 * 160;
-        p.a_bytes = hp.a_bytes;
-        p.w_global = w->d_w;
     }
     if (g.pool && !(patch && two && p.BN == 64 && conv_tc_pool_fusable(g)))
         return fail(EXB_ERR_UNSUPPORTED, "fused pooling needs the patch-mode stem kernel with 64 output channels");
@@ -1044,14 +950,9 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         p.b_resident = 0;
         stages = (budget - g.kh * p.BN * 64) / p.a_bytes;
     }
-    if (p.halo) {   // ring of whole patches, weights resident in their own region
-        p.kgroup = G = 1;
-        p.b_resident = 0;
-        stages = hp.stages;
-    }
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return fail(EXB_ERR_UNSUPPORTED, "conv tile does not fit shared memory (BN=%d)", p.BN);
-    p.b_region = p.halo ? hp.b_bytes : (patch ? g.kh * p.BN * 64 : (p.b_resident ? b_all : stages * G * p.b_bytes));
+    p.b_region = patch ? g.kh * p.BN * 64 : (p.b_resident ? b_all : stages * G * p.b_bytes);
     p.stages = stages;
     // As many accumulator buffers as TMEM allows (256 columns per CTA with two CTAs per SM, else
     // 512): a buffer goes round MMA -> hand-over -> epilogue -> hand-back, and the two hand-overs
@@ -1068,16 +969,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.e.scale = w->d_scale; p.e.bias = w->d_bias; p.e.slope = w->d_slope; p.e.residual = static_cast<const __half*>(residual);
     p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;
     p.e.out_scale = g.out_scale; p.e.out2_scale = g.out2_scale; p.e.cout_stride = g.cout_stride; p.e.y_pitch = g.y_pitch;
-    p.e.i8_planar = g.out_i8_planar;
-    p.e.f16_planar = g.out_f16_planar;
-    p.e.res_planar = g.res_planar;
-    const bool planar16 = g.out_f16_planar || g.res_planar;
-    if (planar16 && (p.halo || p.pool || (g.cout_stride & 15)))
-        return fail(EXB_ERR_UNSUPPORTED, "planar16 fp16 tensors are not available for this convolution");
     p.error = ctx->d_error;
-#ifdef EXB_CONV_EXPERIMENTS
-    if (const char* e = getenv("EXB_CONV_X")) p.xflags = atoi(e);
-#endif
 
     const CUtensorMapDataType dt = int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUtensorMapSwizzle sw = swizzle_for(p.kb_bytes);
@@ -1097,18 +989,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(patch) failed with %d", (int)r);
     }
-    if (p.halo) {
-        // planar16: rows of W*16 bytes, H rows, C/16 slices, N images; box = 10 pixels x 18 rows x all slices.
-        cuuint64_t dims[4] = {(cuuint64_t)g.W * 16, (cuuint64_t)g.H, (cuuint64_t)p.cchunks, (cuuint64_t)g.N};
-        cuuint64_t strides[3] = {(cuuint64_t)g.W * 16, (cuuint64_t)g.H * g.W * 16, (cuuint64_t)p.cchunks * g.H * g.W * 16};
-        cuuint32_t box[4] = {160, 18, (cuuint32_t)p.cchunks, 1};
-        cuuint32_t estr[4] = {1, 1, 1, 1};
-        CUresult r = encode(&p.tmA[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(x), dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(halo) failed with %d", (int)r);
-    }
-    for (int v = 0; v < ((patch || p.halo) ? 0 : nviews); ++v) {
+    for (int v = 0; v < (patch ? 0 : nviews); ++v) {
         const int ph = v >> 1, pw = v & 1;
         const int st_ = g.sh;
         if (fold.on && pw) continue;   // the folded layout walks W inside the K row
@@ -1140,14 +1021,37 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         }
         if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(A view %d) failed with %d", v, (int)r);
     }
+    // Quad epilogue: N tiles of whole 32-channel blocks, every channel group of 8 either fully inside the output or
+    // fully outside, weights stored in whole 32-row blocks (the permuting map walks rows 32 at a time).  Taken when
+    // the epilogue moves fp16 / fp32 data (an fp16 output or residual): there its whole-sector accesses are worth
+    // 15-20 % of the layer; a lone int8 output is as fast from the thread-per-pixel epilogue (measured on the
+    // ResNet-18-style layers at batch 256), which needs fewer TMEM loads.
+    const bool quad = !patch && !p.pool && p.BN % 32 == 0 && w->cout_pad % 32 == 0 && (g.cout_stride & 7) == 0 &&
+                      g.out_dtype != EXB_I32 && !(g.out_dtype == EXB_I8 && g.out2_dtype < 0 && !g.has_res) &&
+                      p.TW <= 255 && p.TH <= 255 && p.TN <= 32767;
+    p.b_perm = quad ? 1 : 0;
     {
         const int K = g.kh * w->kw_pack * w->cin_pad;
-        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)w->cout_pad};
-        cuuint64_t strides[1] = {(cuuint64_t)K * es};
-        cuuint32_t box[2] = {(cuuint32_t)p.kb_elems, (cuuint32_t)p.BN};
-        cuuint32_t estr[2] = {1, 1};
-        CUresult r = encode(&p.tmB, dt, 2, w->d_w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        CUresult r;
+        if (quad) {
+            // Rows of the packed matrix [cout][K] seen as (e: 2, j: 4, g: 4, block) with row = 32*block + 8*j + 2*g + e,
+            // traversed e, j, g, block: shared-memory row (= accumulator column) 8*g + 2*j + e of a block holds
+            // output channel 8*j + 2*g + e.
+            const cuuint64_t kb = (cuuint64_t)K * es;
+            cuuint64_t dims[5] = {(cuuint64_t)K, 2, 4, 4, (cuuint64_t)(w->cout_pad / 32)};
+            cuuint64_t strides[4] = {kb, 8 * kb, 2 * kb, 32 * kb};
+            cuuint32_t box[5] = {(cuuint32_t)p.kb_elems, 2, 4, 4, (cuuint32_t)(p.BN / 32)};
+            cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+            r = encode(&p.tmB, dt, 5, w->d_w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        } else {
+            cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)w->cout_pad};
+            cuuint64_t strides[1] = {(cuuint64_t)K * es};
+            cuuint32_t box[2] = {(cuuint32_t)p.kb_elems, (cuuint32_t)p.BN};
+            cuuint32_t estr[2] = {1, 1};
+            r = encode(&p.tmB, dt, 2, w->d_w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        }
         if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed with %d", (int)r);
     }
 
@@ -1155,47 +1059,22 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     const int max_ctas = ctx->sm_count * ctas_per_sm;
     const int grid = total_tiles < max_ctas ? total_tiles : max_ctas;
     const size_t smem = (size_t)p.stages * p.kgroup * p.a_bytes + p.b_region + 1024 + epi_bytes;
-    auto kern = int8 ? (two ? conv_tc_kernel<true, 0, 8> : conv_tc_kernel<true, 0, 16>)
-                     : (two ? conv_tc_kernel<false, 0, 8> : conv_tc_kernel<false, 0, 16>);
-    if (p.e.act == EXB_ACT_PRELU)
-        kern = int8 ? (two ? conv_tc_kernel<true, 0, 8, false, false, false, true> : conv_tc_kernel<true, 0, 16, false, false, false, true>)
-                    : (two ? conv_tc_kernel<false, 0, 8, false, false, false, true> : conv_tc_kernel<false, 0, 16, false, false, false, true>);
-    if (p.pool) kern = conv_tc_kernel<false, 0, 8, true>;
-    if (p.halo) kern = two ? conv_tc_kernel<true, 0, 8, false, true> : conv_tc_kernel<true, 0, 16, false, true>;
-    if (planar16)
-        kern = int8 ? (two ? conv_tc_kernel<true, 0, 8, false, false, true> : conv_tc_kernel<true, 0, 16, false, false, true>)
-                    : (two ? conv_tc_kernel<false, 0, 8, false, false, true> : conv_tc_kernel<false, 0, 16, false, false, true>);
-#ifdef EXB_CONV_EXPERIMENTS
-    if (const char* e = getenv("EXB_CONV_DBG"); e && !p.halo && !p.pool && !planar16) {
-        switch (atoi(e)) {
-        case 1: kern = int8 ? (two ? conv_tc_kernel<true, 1, 8> : conv_tc_kernel<true, 1, 16>) : (two ? conv_tc_kernel<false, 1, 8> : conv_tc_kernel<false, 1, 16>); break;
-        case 2: kern = int8 ? (two ? conv_tc_kernel<true, 2, 8> : conv_tc_kernel<true, 2, 16>) : (two ? conv_tc_kernel<false, 2, 8> : conv_tc_kernel<false, 2, 16>); break;
-        case 4: kern = int8 ? (two ? conv_tc_kernel<true, 4, 8> : conv_tc_kernel<true, 4, 16>) : (two ? conv_tc_kernel<false, 4, 8> : conv_tc_kernel<false, 4, 16>); break;
-        case 6: kern = int8 ? (two ? conv_tc_kernel<true, 6, 8> : conv_tc_kernel<true, 6, 16>) : (two ? conv_tc_kernel<false, 6, 8> : conv_tc_kernel<false, 6, 16>); break;
-        case 8: kern = int8 ? (two ? conv_tc_kernel<true, 8, 8> : conv_tc_kernel<true, 8, 16>) : (two ? conv_tc_kernel<false, 8, 8> : conv_tc_kernel<false, 8, 16>); break;
-        case 10: kern = int8 ? (two ? conv_tc_kernel<true, 10, 8> : conv_tc_kernel<true, 10, 16>) : (two ? conv_tc_kernel<false, 10, 8> : conv_tc_kernel<false, 10, 16>); break;
-        case 12: kern = int8 ? (two ? conv_tc_kernel<true, 12, 8> : conv_tc_kernel<true, 12, 16>) : (two ? conv_tc_kernel<false, 12, 8> : conv_tc_kernel<false, 12, 16>); break;
-        case 16: kern = int8 ? (two ? conv_tc_kernel<true, 16, 8> : conv_tc_kernel<true, 16, 16>) : (two ? conv_tc_kernel<false, 16, 8> : conv_tc_kernel<false, 16, 16>); break;
-        case 32: kern = int8 ? (two ? conv_tc_kernel<true, 32, 8> : conv_tc_kernel<true, 32, 16>) : (two ? conv_tc_kernel<false, 32, 8> : conv_tc_kernel<false, 32, 16>); break;
-        case 48: kern = int8 ? (two ? conv_tc_kernel<true, 48, 8> : conv_tc_kernel<true, 48, 16>) : (two ? conv_tc_kernel<false, 48, 8> : conv_tc_kernel<false, 48, 16>); break;
-        case 14: kern = int8 ? (two ? conv_tc_kernel<true, 14, 8> : conv_tc_kernel<true, 14, 16>) : (two ? conv_tc_kernel<false, 14, 8> : conv_tc_kernel<false, 14, 16>); break;
-        case 22: kern = int8 ? (two ? conv_tc_kernel<true, 22, 8> : conv_tc_kernel<true, 22, 16>) : (two ? conv_tc_kernel<false, 22, 8> : conv_tc_kernel<false, 22, 16>); break;
-        case 38: kern = int8 ? (two ? conv_tc_kernel<true, 38, 8> : conv_tc_kernel<true, 38, 16>) : (two ? conv_tc_kernel<false, 38, 8> : conv_tc_kernel<false, 38, 16>); break;
-        case 54: kern = int8 ? (two ? conv_tc_kernel<true, 54, 8> : conv_tc_kernel<true, 54, 16>) : (two ? conv_tc_kernel<false, 54, 8> : conv_tc_kernel<false, 54, 16>); break;
-        default: break;
-        }
-    }
-#endif
+    const bool prelu = p.e.act == EXB_ACT_PRELU;
+    void (*kern)(const ConvTcParams);
+    if (p.pool) kern = conv_tc_kernel<false, 8, kEpiPool>;
+    else if (quad && !prelu)
+        kern = int8 ? (two ? conv_tc_kernel<true, 8, kEpiQuad> : conv_tc_kernel<true, 16, kEpiQuad>)
+                    : (two ? conv_tc_kernel<false, 8, kEpiQuad> : conv_tc_kernel<false, 16, kEpiQuad>);
+    else if (quad)
+        kern = int8 ? (two ? conv_tc_kernel<true, 8, kEpiQuad, true> : conv_tc_kernel<true, 16, kEpiQuad, true>)
+                    : (two ? conv_tc_kernel<false, 8, kEpiQuad, true> : conv_tc_kernel<false, 16, kEpiQuad, true>);
+    else if (!prelu)
+        kern = int8 ? (two ? conv_tc_kernel<true, 8, kEpiRow> : conv_tc_kernel<true, 16, kEpiRow>)
+                    : (two ? conv_tc_kernel<false, 8, kEpiRow> : conv_tc_kernel<false, 16, kEpiRow>);
+    else
+        kern = int8 ? (two ? conv_tc_kernel<true, 8, kEpiRow, true> : conv_tc_kernel<true, 16, kEpiRow, true>)
+                    : (two ? conv_tc_kernel<false, 8, kEpiRow, true> : conv_tc_kernel<false, 16, kEpiRow, true>);
     EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-#ifdef EXB_CONV_EXPERIMENTS
-    static unsigned long long* d_trace = nullptr;
-    const char* trace_path = getenv("EXB_CONV_TRACE");
-    if (trace_path) {
-        if (!d_trace) cudaMalloc(&d_trace, 4 * 64 * 4 * sizeof(unsigned long long));
-        cudaMemsetAsync(d_trace, 0, 4 * 64 * 4 * sizeof(unsigned long long), st);
-        p.trace = d_trace;
-    }
-#endif
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)grid);
@@ -1208,25 +1087,6 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 1 : 0;
     EXB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
-#ifdef EXB_CONV_EXPERIMENTS
-    if (trace_path) {
-        static unsigned long long h[4 * 64 * 4];
-        cudaStreamSynchronize(st);
-        cudaMemcpy(h, d_trace, sizeof(h), cudaMemcpyDeviceToHost);
-        if (FILE* f = fopen(trace_path, "w")) {
-            unsigned long long t0 = ~0ull;
-            for (unsigned long long v : h) if (v && v < t0) t0 = v;
-            for (int role = 0; role < 3; ++role)
-                for (int i = 0; i < 64; ++i) {
-                    const unsigned long long* e = h + (role * 64 + i) * 4;
-                    if (!e[0]) continue;
-                    fprintf(f, "%d %d %lld %lld %lld %lld\n", role, i, (long long)(e[0] - t0), e[1] ? (long long)(e[1] - t0) : -1,
-                            e[2] ? (long long)(e[2] - t0) : -1, e[3] ? (long long)(e[3] - t0) : -1);
-                }
-            fclose(f);
-        }
-    }
-#endif
     return after_launch("conv_tc_kernel");
 }
 

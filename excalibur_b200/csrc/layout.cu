@@ -210,20 +210,6 @@ __global__ void __launch_bounds__(256) nchw_f16_to_nhwc4_f16_quad_kernel(const _
     }
 }
 
-// planar16 int8 [N][cs/16][HW][16] -> fp32 [N][C][HW]: a thread per (n, c, hw), reads of one channel
-// plane are 16-byte strided but each plane is small and read once.
-template <typename In>
-__global__ void __launch_bounds__(256) planar16_to_nchw_kernel(const In* __restrict__ x, float* __restrict__ y,
-                                                               int C, int HW, int c_stride, float scale, int64_t total) {
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int hw = (int)(i % HW);
-        const int64_t nc = i / HW;
-        const int c = (int)(nc % C);
-        const int64_t n = nc / C;
-        y[i] = cvt_in<In>(x[((n * (c_stride >> 4) + (c >> 4)) * HW + hw) * 16 + (c & 15)], 1.f) * scale;
-    }
-}
-
 int check_dims(const exb_ctx* ctx, const void* a, const void* b, int N, int C, int H, int W, int c_stride) {
     EXB_REQUIRE(ctx != nullptr, "null context");
     EXB_REQUIRE(N >= 0 && C > 0 && H > 0 && W > 0, "bad tensor shape %dx%dx%dx%d", N, C, H, W);
@@ -280,33 +266,6 @@ extern "C" int exb_nhwc_to_nchw_f32(exb_ctx* ctx, const void* x, int dtype, floa
     default: return fail(EXB_ERR_UNSUPPORTED, "exb_nhwc_to_nchw_f32: dtype %d", dtype);
     }
     return after_launch("nhwc_to_nchw_kernel");
-}
-
-extern "C" int exb_planar16_i8_to_nchw_f32(exb_ctx* ctx, const int8_t* x, float* y, int N, int C, int H, int W,
-                                           int c_stride, float scale, void* stream) {
-    if (c_stride == 0) c_stride = (C + 15) / 16 * 16;
-    if (int rc = check_dims(ctx, x, y, N, C, H, W, c_stride)) return rc;
-    EXB_REQUIRE(c_stride % 16 == 0, "planar16 needs c_stride %% 16 == 0, got %d", c_stride);
-    if (N == 0) return EXB_OK;
-    const int64_t total = (int64_t)N * C * H * W;
-    const int grid = stream_grid(ctx, total, 256, 16);
-    planar16_to_nchw_kernel<int8_t><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, C, H * W, c_stride, scale, total);
-    return after_launch("planar16_to_nchw_kernel");
-}
-
-extern "C" int exb_planar16_to_nchw_f32(exb_ctx* ctx, const void* x, int dtype, float* y, int N, int C, int H, int W,
-                                        int c_stride, float scale, void* stream) {
-    if (dtype == EXB_I8) return exb_planar16_i8_to_nchw_f32(ctx, static_cast<const int8_t*>(x), y, N, C, H, W, c_stride, scale, stream);
-    if (dtype != EXB_F16) return fail(EXB_ERR_UNSUPPORTED, "exb_planar16_to_nchw_f32: dtype %d", dtype);
-    if (c_stride == 0) c_stride = (C + 15) / 16 * 16;
-    if (int rc = check_dims(ctx, x, y, N, C, H, W, c_stride)) return rc;
-    EXB_REQUIRE(c_stride % 16 == 0, "planar16 needs c_stride %% 16 == 0, got %d", c_stride);
-    if (N == 0) return EXB_OK;
-    const int64_t total = (int64_t)N * C * H * W;
-    const int grid = stream_grid(ctx, total, 256, 16);
-    planar16_to_nchw_kernel<__half><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(x), y, C, H * W,
-                                                                                         c_stride, scale, total);
-    return after_launch("planar16_to_nchw_kernel");
 }
 
 extern "C" int exb_nchw_f32_to_nhwc_padded(exb_ctx* ctx, const float* x, void* y, int dtype, int N, int C, int H,

@@ -48,17 +48,31 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 #ifndef EXB_WAIT_HINT_NS
 #define EXB_WAIT_HINT_NS 1000
 #endif
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+#ifndef EXB_EPI_BACKOFF_NS
+#define EXB_EPI_BACKOFF_NS 100
+#endif
+__device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#if EXB_WAIT_HINT_NS > 0
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)EXB_WAIT_HINT_NS)
+        : "r"(bar), "r"(parity), "r"((uint32_t)EXB_WAIT_HINT_NS)
         : "memory");
+#else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+#endif
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) { return mbar_try_wait_u32(smem_u32(bar), parity); }
 // 16-byte asynchronous copy global -> shared (bypassing L1 and registers), per-thread groups.
 __device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
@@ -84,9 +98,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
-// Whole-warp wait in which only lane 0 polls (with a short back-off) and the other lanes park at
-// a warp barrier, so that a waiting warp does not spend issue slots and shared-memory bandwidth
-// that the producer and MMA threads need.  All 32 lanes must call it; returns the same value to all.
+// Whole-warp wait in which only lane 0 polls (with a back-off) and the other lanes park at a warp barrier, so that a
+// waiting warp does not spend issue slots and shared-memory bandwidth that the producer and MMA threads need: every
+// failed try and every look at the abort flag is a shared-memory access, and a dozen waiting warps polling flat out
+// cost the SM's shared-memory pipe as much as the epilogue's real work.  All 32 lanes must call it; returns the same
+// value to all.
 __device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t parity,
                                                        volatile int* abort_flag, uint32_t max_spins) {
     int ok = 1;
@@ -97,8 +113,8 @@ __device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t p
                 ok = 1;
                 break;
             }
-            if (*abort_flag) break;
-            __nanosleep(40);
+            if ((i & 15u) == 15u && *abort_flag) break;
+            __nanosleep(EXB_EPI_BACKOFF_NS);
         }
         if (!ok) *abort_flag = 1;
     }
@@ -107,17 +123,6 @@ __device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t p
 }
 
 // Variants taking 32-bit shared-memory addresses, for loops that keep addresses in registers.
-__device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"((uint32_t)EXB_WAIT_HINT_NS)
-        : "memory");
-    return ok != 0;
-}
 __device__ __forceinline__ bool mbar_test_wait_u32(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -168,6 +173,13 @@ __device__ __forceinline__ void tma_load_4d_u32(uint32_t dst, uint64_t map, uint
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d_u32(uint32_t dst, uint64_t map, uint32_t bar, int c0, int c1, int c2,
+                                                int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
 __device__ __forceinline__ void tc_commit_u32(uint32_t bar) {
@@ -278,6 +290,18 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
           "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
           "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+// 16 lanes x 32 consecutive 32-bit columns in the 16x256b shape (the accumulator fragment of the warp-level MMA):
+// thread i of the warp gets, for every group g of 8 columns, r[4g], r[4g+1] = lane (base_lane + i/4), columns
+// 8g + 2*(i%4), + 1 and r[4g+2], r[4g+3] = lane (base_lane + 8 + i/4), same columns.
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
 }

@@ -130,12 +130,6 @@ EXB_API int exb_nchw_f32_to_nhwc4_padded_norm(exb_ctx* ctx, const float* x_nchw,
  * output, C <= 3, W / w_pad / w_pitch multiples of 4. */
 EXB_API int exb_nchw_f16_to_nhwc4_padded(exb_ctx* ctx, const void* x_nchw_f16, void* y_nhwc, int N, int C, int H,
                                          int W, int w_pad, int w_pitch, void* stream);
-/* planar16 [N][c_stride/16][H][W][16] (EXB_I8 or EXB_F16) -> fp32 NCHW, y = x * scale (inspection
- * of planar maps, global pooling input). */
-EXB_API int exb_planar16_i8_to_nchw_f32(exb_ctx* ctx, const int8_t* x, float* y, int N, int C, int H, int W,
-                                        int c_stride, float scale, void* stream);
-EXB_API int exb_planar16_to_nchw_f32(exb_ctx* ctx, const void* x, int dtype, float* y, int N, int C, int H,
-                                     int W, int c_stride, float scale, void* stream);
 EXB_API int exb_nhwc_to_nchw_f32(exb_ctx* ctx, const void* x_nhwc, int dtype, float* y_nchw,
                                  int N, int C, int H, int W, int c_stride, float scale,
                                  void* stream);
@@ -183,23 +177,6 @@ typedef struct exb_conv_desc {
      * convolution output itself is never written.  Only for descriptors for which
      * exb_conv2d_pool_fusable() returns 1; 0 = plain convolution. */
     int32_t fuse_pool;
-    /* Planar int8 activations, layout [N][c_stride/16][H][W][16] ("planar16"): 16-channel slices of
-     * the map are stored as whole planes, so a 3x3 convolution can fetch ONE (TH+2) x (TW+2) halo
-     * patch per tile and derive all nine taps from it in shared memory, and a warp's epilogue
-     * stores are contiguous.
-     * in_planar = 1: x is planar16 int8 (only where exb_conv2d_accepts_planar_input() returns 1).
-     * out_i8_planar = 1: whichever of y / y2 is EXB_I8 is written as planar16; outputs of other
-     * dtypes and the residual stay NHWC.  Needs cout_stride % 16 == 0 and in_planar = 1 or
-     * fuse_pool = 1 (the two kernel variants that carry the planar store). */
-    int32_t in_planar;
-    int32_t out_i8_planar;
-    /* Planar fp16 skip tensors, layout [N][cout_stride/16][OH][OW][16] fp16 (32 bytes per pixel and
-     * slice): a warp's epilogue accesses then fall into 8 cache lines instead of 32.
-     * out_f16_planar = 1: whichever of y / y2 is EXB_F16 is written in that layout;
-     * res_planar = 1: the residual is read in that layout.  Both need cout_stride % 16 == 0 and the
-     * tensor-core kernel (exb_conv2d_uses_tensor_cores); int8 and fp32 outputs are not affected. */
-    int32_t out_f16_planar;
-    int32_t res_planar;
     /* Elements between consecutive output pixels of y, 0 = cout_stride.  A larger value lets the convolution
      * write its cout_stride channels into a slice of a wider channel-last tensor (the caller passes y already
      * offset to the slice's first channel): a Concat becomes the producers' epilogue stores
@@ -244,10 +221,6 @@ EXB_API int exb_conv2d_uses_tensor_cores(const exb_conv_desc* d);
  * stem on padded NHWC4 rows with 64 output channels, ReLU or ReLU6, fp16 output and an optional
  * int8 copy, no residual), else 0; negative = error.  The descriptor's own fuse_pool is ignored. */
 EXB_API int exb_conv2d_pool_fusable(const exb_conv_desc* d);
-/* 1 when exb_conv2d_fwd can read this descriptor's input as planar16 int8 (a 3x3 stride-1 pad-1
- * int8 convolution whose packed weights fit in shared memory beside the halo ring), else 0;
- * negative = error.  The descriptor's own in_planar is ignored. */
-EXB_API int exb_conv2d_accepts_planar_input(const exb_conv_desc* d);
 
 /* ---------------------------------------------------------------------------------------
  * Depthwise convolution forward.  Stands in for operation_convolutiondepthwise::forward_*

@@ -329,112 +329,47 @@ def test_fused_max_pool_is_refused_where_it_cannot_run(ctx):
         capi.conv2d(ctx, d, x, w)
 
 
-HALO_CASES = [
-    # N, Cin, H, W, Cout
-    (2, 64, 56, 56, 64),       # ResNet stage 1
-    (3, 128, 28, 28, 128),     # stage 2 (one CTA per SM: the weights take 147 KB)
-    (2, 32, 21, 13, 48),       # ragged tiles in both directions, Cout not a multiple of 32
-    (1, 64, 16, 10, 16),
-    (5, 64, 14, 14, 256),
-]
-
-
-@pytest.mark.parametrize("case", HALO_CASES)
-def test_conv_i8_planar16_halo_mode(ctx, case):
-    """3x3 stride-1 int8 conv reading planar16 input through one halo patch per tile and writing a
-    planar16 int8 output (+ NHWC fp16 output, NHWC fp16 residual): bit-identical to the NHWC path."""
-    from tests.util import to_planar16, from_planar16
-    capi = _capi()
-    N, Cin, H, W, Cout = case
-    r = rng(sum(case) + 3)
-    xq = r.integers(-128, 128, (N, Cin, H, W)).astype(np.int8)
-    wq = r.integers(-127, 128, (Cout, Cin, 3, 3)).astype(np.int8)
-    bias = r.standard_normal(Cout).astype(np.float32)
-    ws = r.uniform(20, 60, Cout).astype(np.float32)
-    fs, q = 31.0, 17.0
-    res = f16_round(r.standard_normal((N, Cout, H, W)))
-    cs = (Cout + 15) // 16 * 16
-    base = dict(res=True, act=1, out_scale=1.0, out2_scale=q, cout_stride=cs)
-    d0 = capi.make_conv_desc(N, H, W, Cin, Cout, 3, 1, 1, capi.EXB_I8, capi.EXB_F16, capi.EXB_I8, **base)
-    d1 = capi.make_conv_desc(N, H, W, Cin, Cout, 3, 1, 1, capi.EXB_I8, capi.EXB_F16, capi.EXB_I8, in_planar=1,
-                             out_i8_planar=1, **base)
-    assert capi.lib().exb_conv2d_accepts_planar_input(d0) == 1
-    wp = capi.ConvWeights(ctx, d0, wq, bias, ws, fs)
-    resd = dev(to_nhwc(res, cs).astype(np.float16))
-    y0, q0 = capi.conv2d(ctx, d0, dev(to_nhwc(xq)), wp, resd)
-    import torch
-    q1 = torch.zeros((N, cs // 16, H, W, 16), dtype=torch.int8, device="cuda")
-    y1, _ = capi.conv2d(ctx, d1, dev(to_planar16(xq)), wp, resd, None, q1)
-    ctx.sync_check()
-    np.testing.assert_array_equal(host(y1), host(y0))
-    np.testing.assert_array_equal(from_planar16(host(q1), Cout), to_nchw(host(q0), Cout))
-    # and against the oracle: dequantised accumulator + bias + residual, ReLU
-    acc = O.conv2d_i8_acc(xq, wq, 1, 1)
-    ref = np.maximum(O.dequantize(acc, O.dequant_scales(ws, fs, Cout), bias) + res, 0)
-    assert_close_f16(to_nchw(host(y1).astype(np.float32), Cout), ref, rel=2e-3, what="halo fp16 output")
-    # int8-only output, no residual
-    d2 = capi.make_conv_desc(N, H, W, Cin, Cout, 3, 1, 1, capi.EXB_I8, capi.EXB_I8, act=1, out_scale=q, cout_stride=cs,
-                             in_planar=1, out_i8_planar=1)
-    d3 = capi.make_conv_desc(N, H, W, Cin, Cout, 3, 1, 1, capi.EXB_I8, capi.EXB_I8, act=1, out_scale=q, cout_stride=cs)
-    q2 = torch.zeros((N, cs // 16, H, W, 16), dtype=torch.int8, device="cuda")
-    capi.conv2d(ctx, d2, dev(to_planar16(xq)), wp, None, q2)
-    q3, _ = capi.conv2d(ctx, d3, dev(to_nhwc(xq)), wp)
-    ctx.sync_check()
-    np.testing.assert_array_equal(from_planar16(host(q2), Cout), to_nchw(host(q3), Cout))
-    f = torch.empty((N, Cout, H, W), dtype=torch.float32, device="cuda")
-    capi.check(capi.lib().exb_planar16_i8_to_nchw_f32(ctx.handle, capi.ptr(q2), capi.ptr(f), N, Cout, H, W, cs, 0.5,
-                                                       capi.cur_stream()))
-    np.testing.assert_array_equal(host(f), from_planar16(host(q2), Cout).astype(np.float32) * 0.5)
-
-
-def test_planar_input_is_refused_where_it_cannot_run(ctx):
-    capi = _capi()
-    for args in ((1, 16, 16, 64, 64, 3, 2, 1), (1, 16, 16, 64, 64, 1, 1, 0), (1, 7, 7, 512, 512, 3, 1, 1)):
-        d = capi.make_conv_desc(*args, capi.EXB_I8, capi.EXB_I8)
-        assert capi.lib().exb_conv2d_accepts_planar_input(d) == 0, args
-
-
-PLANAR_F16_CASES = [
+RES_DUAL_CASES = [
     # N, Cin, H, W, Cout, k, stride, pad
-    (2, 64, 56, 56, 64, 3, 1, 1),       # two CTAs per SM
-    (3, 128, 28, 28, 128, 3, 1, 1),
-    (5, 256, 14, 14, 256, 3, 1, 1),     # one CTA per SM, chunks split between two warps
+    (2, 64, 56, 56, 64, 3, 1, 1),       # two CTAs per SM, one 64-channel block
+    (3, 128, 28, 28, 128, 3, 1, 1),     # two blocks
+    (5, 256, 14, 14, 256, 3, 1, 1),     # one CTA per SM, the two halves of a lane quarter on two warps
+    (20, 512, 7, 7, 512, 3, 1, 1),      # two Cout tiles of 256, 7x1x18 boxes with a ragged tail
     (3, 64, 56, 56, 128, 1, 2, 0),      # projection shortcut (fp16 output only)
-    (2, 32, 13, 11, 48, 3, 1, 1),       # ragged tiles, 48 channels = 3 slices
-    (1, 64, 12, 12, 320, 3, 1, 1),      # two Cout tiles
+    (2, 32, 13, 11, 48, 3, 1, 1),       # ragged tiles, 48 channels: the thread-per-pixel epilogue
+    (1, 64, 12, 12, 320, 3, 1, 1),      # two Cout tiles of 160 channels: thread-per-pixel epilogue
+    (2, 64, 9, 7, 192, 3, 1, 1),        # three blocks, tiles ragged in both directions
 ]
 
 
-@pytest.mark.parametrize("case", PLANAR_F16_CASES)
-def test_conv_planar16_fp16_output_and_residual(ctx, case):
-    """fp16 output and residual in the planar16 layout [N][C/16][H][W][16]: the same numbers as the NHWC
-    path, element for element; the int8 second output stays NHWC."""
-    from tests.util import to_planar16, from_planar16
-    import torch
+@pytest.mark.parametrize("case", RES_DUAL_CASES)
+def test_conv_i8_residual_dual_output_shapes(ctx, case):
+    """conv + fp16 skip + ReLU written as fp16 and int8 (the second convolution of a residual block) on every tile /
+    channel-block configuration of the tensor-core kernel's two epilogues, against the CPU oracle, bit for bit."""
     capi = _capi()
     N, Cin, H, W, Cout, k, stride, pad = case
     r = rng(sum(case) + 11)
-    xq = r.integers(-128, 128, (N, Cin, H, W)).astype(np.int8)
-    wq = r.integers(-127, 128, (Cout, Cin, k, k)).astype(np.int8)
-    bias = r.standard_normal(Cout).astype(np.float32)
-    ws = r.uniform(20, 60, Cout).astype(np.float32)
-    OH, OW = (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
-    res = f16_round(r.standard_normal((N, Cout, OH, OW)))
-    cs = (Cout + 15) // 16 * 16
+    x = r.uniform(-1, 1, (N, Cin, H, W)).astype(np.float32)
+    w = (r.standard_normal((Cout, Cin, k, k)) * np.sqrt(2.0 / (Cin * k * k))).astype(np.float32)
+    b = (r.standard_normal(Cout) * 0.01).astype(np.float32)
+    wq, ws = quant_weights(w)
+    fs = np.float32(127.0 / np.abs(x).max())
+    xq = O.quantize_f32_i8(x, [fs])
+    pre = O.conv2d_i8(x, wq, b, ws, fs, stride, pad, act=0)
     with_res = k == 3
-    kw = dict(res=with_res, act=1 if with_res else 0, out2_scale=13.0, cout_stride=cs)
-    d0 = capi.make_conv_desc(N, H, W, Cin, Cout, k, stride, pad, capi.EXB_I8, capi.EXB_F16, capi.EXB_I8, **kw)
-    d1 = capi.make_conv_desc(N, H, W, Cin, Cout, k, stride, pad, capi.EXB_I8, capi.EXB_F16, capi.EXB_I8,
-                             out_f16_planar=1, res_planar=1 if with_res else 0, **kw)
-    wp = capi.ConvWeights(ctx, d0, wq, bias, ws, 31.0)
-    x = dev(to_nhwc(xq))
-    y0, q0 = capi.conv2d(ctx, d0, x, wp, dev(to_nhwc(res, cs).astype(np.float16)) if with_res else None)
-    y1 = torch.zeros((N, cs // 16, OH, OW, 16), dtype=torch.float16, device="cuda")
-    _, q1 = capi.conv2d(ctx, d1, x, wp, dev(to_planar16(res.astype(np.float16), cs)) if with_res else None, y1)
-    ctx.sync_check()
-    np.testing.assert_array_equal(from_planar16(host(y1), Cout), to_nchw(host(y0), Cout))
-    np.testing.assert_array_equal(host(q1), host(q0))
-    f = torch.empty((N, Cout, OH, OW), dtype=torch.float32, device="cuda")
-    capi.check(capi.lib().exb_planar16_to_nchw_f32(ctx.handle, capi.ptr(y1), capi.EXB_F16, capi.ptr(f), N, Cout, OH, OW, cs,
-                                                    1.0, capi.cur_stream()))
-    np.testing.assert_array_equal(host(f), to_nchw(host(y0), Cout).astype(np.float32))
+    skip = f16_round(r.uniform(-1, 1, pre.shape)) if with_res else None
+    v = O.activation(pre + skip, 1) if with_res else pre
+    nxt = np.float32(127.0 / max(float(np.abs(v).max()), 1e-6))
+    if with_res:
+        y16, q, tc = run_conv_i8(ctx, xq, wq, b, ws, fs, stride, pad, capi.EXB_F16, act=1, res=skip,
+                                 out2_dtype=capi.EXB_I8, out2_scale=nxt)
+        np.testing.assert_array_equal(q, O.requantize_rne(v, nxt))
+    else:
+        y16, _, tc = run_conv_i8(ctx, xq, wq, b, ws, fs, stride, pad, capi.EXB_F16)
+    assert tc == 1
+    np.testing.assert_array_equal(y16.astype(np.float32), f16_round(v))
+    # int8 first, fp16 second (the order the first convolution of the next block's producer uses)
+    q2, h2, _ = run_conv_i8(ctx, xq, wq, b, ws, fs, stride, pad, capi.EXB_I8, act=1 if with_res else 0, res=skip,
+                            out_scale=nxt, out2_dtype=capi.EXB_F16)
+    np.testing.assert_array_equal(q2, O.requantize_rne(v, nxt))
+    np.testing.assert_array_equal(h2.astype(np.float32), f16_round(v))

@@ -69,9 +69,6 @@ def test_pure_host_calls_work_without_a_gpu(so_path):
     assert capi.conv_out_dims(stem) == (56, 56)
     body = capi.make_conv_desc(8, 56, 56, 64, 64, 3, 1, 1, capi.EXB_I8, capi.EXB_I8)
     assert capi.lib().exb_conv2d_pool_fusable(body) == 0
-    assert capi.lib().exb_conv2d_accepts_planar_input(body) == 1
-    wide = capi.make_conv_desc(8, 7, 7, 512, 512, 3, 1, 1, capi.EXB_I8, capi.EXB_I8)
-    assert capi.lib().exb_conv2d_accepts_planar_input(wide) == 0
 
 
 def test_no_cpu_fallback_in_the_product(so_path):

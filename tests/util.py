@@ -56,22 +56,6 @@ def quant_weights(w):
     return wq, ws
 
 
-def to_planar16(a_nchw, c_stride=None):
-    """NCHW numpy -> planar16 [N][cs/16][H][W][16], zero-padding the channels to c_stride."""
-    n, c, h, w = a_nchw.shape
-    cs = c_stride or (c + 15) // 16 * 16
-    p = np.zeros((n, cs, h, w), a_nchw.dtype)
-    p[:, :c] = a_nchw
-    return np.ascontiguousarray(p.reshape(n, cs // 16, 16, h, w).transpose(0, 1, 3, 4, 2))
-
-
-def from_planar16(p, C=None):
-    """planar16 [N][cs/16][H][W][16] -> NCHW numpy."""
-    n, cc, h, w, _ = p.shape
-    a = np.ascontiguousarray(p.transpose(0, 1, 4, 2, 3)).reshape(n, cc * 16, h, w)
-    return a[:, :C] if C is not None else a
-
-
 # ---- benchmark-size fixtures (tests/golden/fullsize_vectors.npz) -----------------------------------
 FULLSIZE_SEEDS = {"resnet_body": 56001, "resnet_body_calib": 56007, "resnet": 224001, "resnet_calib": 224007, "mobilenet": 224101, "mobilenet_calib": 224107, "yolo": 640001}
 
