@@ -82,7 +82,7 @@ def probe(ctx, dtype, n, ctas, seconds, sampler_cls=None, device=0):
     return out
 
 
-def measure(seconds=2.0, device=0, shapes=((64, 1), (64, 2), (128, 1), (128, 2), (256, 1))):
+def measure(seconds=2.0, device=0, shapes=((64, 1), (64, 2), (128, 1), (128, 2), (256, 1)), dtypes=("int8", "f16")):
     import torch
     from bench import ClockSampler
     from excalibur_b200 import capi
@@ -90,6 +90,8 @@ def measure(seconds=2.0, device=0, shapes=((64, 1), (64, 2), (128, 1), (128, 2),
     ctx = capi.Context(device)
     res = {"int8": [], "f16": []}
     for name, dt in (("int8", capi.EXB_I8), ("f16", capi.EXB_F16)):
+        if name not in dtypes:
+            continue
         for n, ctas in shapes:
             # the long loop only on the widest shape of each type: it is the one that reaches the peak
             res[name].append(probe(ctx, dt, n, ctas, seconds if (n, ctas) == (256, 1) else 0.0, ClockSampler, device))
@@ -97,10 +99,10 @@ def measure(seconds=2.0, device=0, shapes=((64, 1), (64, 2), (128, 1), (128, 2),
     out = {
         "how": "tcgen05.mma cta_group::1 M=128 K=32B back to back from one thread per CTA, operands resident in shared "
                "memory, no TMA / epilogue; burst = best ~0.3 ms launch, sustained = launches back to back for %.1f s" % seconds,
-        "int8_peak_tops": max(r["burst"] for r in res["int8"]),
-        "f16_peak_tflops": max(r["burst"] for r in res["f16"]),
-        "int8_peak_tops_sustained": max(r.get("sustained", 0.0) for r in res["int8"]),
-        "f16_peak_tflops_sustained": max(r.get("sustained", 0.0) for r in res["f16"]),
+        "int8_peak_tops": max([r["burst"] for r in res["int8"]] or [0.0]),
+        "f16_peak_tflops": max([r["burst"] for r in res["f16"]] or [0.0]),
+        "int8_peak_tops_sustained": max([r.get("sustained", 0.0) for r in res["int8"]] or [0.0]),
+        "f16_peak_tflops_sustained": max([r.get("sustained", 0.0) for r in res["f16"]] or [0.0]),
         "shapes": res,
     }
     return out

@@ -35,6 +35,10 @@
 
 #include <cudaTypedefs.h>
 
+#include <mutex>
+#include <set>
+#include <utility>
+
 namespace exb {
 namespace {
 
@@ -1074,7 +1078,23 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     else
         kern = int8 ? (two ? conv_tc_kernel<true, 8, kEpiRow, true> : conv_tc_kernel<true, 16, kEpiRow, true>)
                     : (two ? conv_tc_kernel<false, 8, kEpiRow, true> : conv_tc_kernel<false, 16, kEpiRow, true>);
-    EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // The dynamic shared-memory limit is an attribute of the kernel function on a device, shared by every thread that
+    // launches it: it is raised to the device's maximum once, never lowered, so that concurrent launches from several
+    // host threads (one pipeline replica per thread) cannot undercut each other.  Occupancy follows the bytes a launch
+    // actually asks for, not this limit.
+    {
+        static std::mutex attr_mutex;
+        static std::set<std::pair<const void*, int>> raised;
+        std::lock_guard<std::mutex> lock(attr_mutex);
+        const auto key = std::make_pair(reinterpret_cast<const void*>(kern), ctx->device);
+        if (!raised.count(key)) {
+            cudaFuncAttributes fa;
+            EXB_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));      // static + dynamic shared memory share the device limit
+            EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              ctx->smem_optin - (int)fa.sharedSizeBytes));
+            raised.insert(key);
+        }
+    }
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)grid);

@@ -133,7 +133,8 @@ public:
     // forward of k * N_ images: chunk c+1 is copied to the device while chunk c is computed.  host_threads > 0:
     // each chunk is first converted to fp16 on the host by that many threads (half the PCIe bytes), when the
     // plan's ingest step can read fp16 planes; otherwise the fp32 input is copied as it is.
-    void run_chunked(const float* host_input, int k, bool use_graph, int host_threads = 0);
+    // host_f16 != nullptr: the caller's input is already fp16 NCHW (pipeline<unsigned short>); it is copied as it is.
+    void run_chunked(const float* host_input, int k, bool use_graph, int host_threads = 0, const uint16_t* host_f16 = nullptr);
     bool host_f16_capable() const { return ingest_f16_capable_; }
     int launches() const { return launches_; }
     double device_ms() const { return device_ms_; }
@@ -1378,14 +1379,16 @@ double fused_plan::run_resident(int iters, bool use_graph) {
     return ms;
 }
 
-void fused_plan::run_chunked(const float* host_input, int k, bool use_graph, int host_threads) {
+void fused_plan::run_chunked(const float* host_input, int k, bool use_graph, int host_threads, const uint16_t* host_f16) {
     CUDA_CHECK(cudaSetDevice(device_));
     CHECK(built_ && k >= 1);
     const size_t chunk_elems = (size_t)N_ * C_ * H_ * W_;
-    const bool f16 = host_threads > 0 && ingest_f16_capable_;
+    if (host_f16) CHECK(ingest_f16_capable_) << "this plan's ingest step cannot read fp16 planes";
+    const bool convert = !host_f16 && host_threads > 0 && ingest_f16_capable_;
+    const bool f16 = host_f16 != nullptr || convert;
     float* stage = static_cast<float*>(chunk_stage_.ensure(chunk_elems * 4 * k, device_));
     uint16_t* stage16 = reinterpret_cast<uint16_t*>(stage);
-    if (f16) {
+    if (convert) {
         if (host_f16_bytes_ < chunk_elems * 2 * k) {
             if (host_f16_) cudaFreeHost(host_f16_);
             host_f16_ = nullptr;
@@ -1411,16 +1414,20 @@ void fused_plan::run_chunked(const float* host_input, int k, bool use_graph, int
     for (auto& s : steps_) launches_ += s.launches;
     launches_ *= k;
     // every copy is queued at once on its own stream; compute of chunk c waits for copy c only
-    if (!f16) {
+    if (!convert) {
         for (int c = 0; c < k; ++c) {
-            CUDA_CHECK(cudaMemcpyAsync(stage + c * chunk_elems, host_input + c * chunk_elems, chunk_elems * 4,
-                                       cudaMemcpyHostToDevice, copy_stream_));
+            if (host_f16)
+                CUDA_CHECK(cudaMemcpyAsync(stage16 + c * chunk_elems, host_f16 + c * chunk_elems, chunk_elems * 2,
+                                           cudaMemcpyHostToDevice, copy_stream_));
+            else
+                CUDA_CHECK(cudaMemcpyAsync(stage + c * chunk_elems, host_input + c * chunk_elems, chunk_elems * 4,
+                                           cudaMemcpyHostToDevice, copy_stream_));
             CUDA_CHECK(cudaEventRecord(copied_[c], copy_stream_));
         }
     }
     CUDA_CHECK(cudaEventRecord(ev0_, stream_));
     for (int c = 0; c < k; ++c) {
-        if (f16) {
+        if (convert) {
             // the host converts chunk c while the copy of chunk c-1 and the kernels of chunk c-2 run
             uint16_t* h16 = static_cast<uint16_t*>(host_f16_) + c * chunk_elems;
             pool_->run(host_input + c * chunk_elems, h16, chunk_elems);
@@ -1518,6 +1525,8 @@ public:
         : impl(read_lines(param_file), model_file, device) {}
     impl(const std::vector<std::string>& lines, std::string_view model_file, int device) {
         device_ = device;
+        lines_ = lines;
+        model_file_ = std::string(model_file);
         if (device >= 0) CUDA_CHECK(cudaSetDevice(device));   // select the device BEFORE creating any handle
         if (lines.empty()) LOG(FATAL) << "Incorrect param file.";
         auto head = split_string(lines[0], " ");
@@ -1603,8 +1612,18 @@ public:
     }
     result_map forward_unfused(const std::shared_ptr<memory::tensor<Dtype>>& input);
 
+    // fp16 input already on the host (pipeline<unsigned short>): the fused plan copies it as it is (half the bytes of
+    // the fp32 form); false when this graph's plan cannot ingest fp16 planes (nothing has run then).
+    bool forward_f16_input(const uint16_t* host_f16, int N, int C, int H, int W, result_map& out);
+
     std::string name_;
     int device_ = -1;
+    std::vector<std::string> lines_;
+    std::string model_file_;
+    // pipeline<unsigned short> runs its fused plan through a float pipeline of the same graph (the plan keeps fp16 /
+    // int8 tensors on the device whatever the host type is); built on the first forward that can use it
+    std::unique_ptr<typename pipeline<float>::impl> inner_;
+    bool inner_unusable_ = false;
     std::vector<operation_param> op_params_;
     std::vector<std::shared_ptr<operation<Dtype>>> operations_;
     std::unordered_map<std::string, int> featmap_index_;
@@ -1624,6 +1643,18 @@ public:
     int launches_ = 0;
     double device_ms_ = 0.0;
 };
+
+template <>
+std::shared_ptr<memory::tensor<float>> pipeline<float>::impl::get_featmap(std::string_view name);
+template <>
+std::shared_ptr<memory::tensor<unsigned short>> pipeline<unsigned short>::impl::get_featmap(std::string_view name);
+template <>
+bool pipeline<float>::impl::forward_f16_input(const uint16_t* host_f16, int N, int C, int H, int W, result_map& out);
+template <>
+pipeline<float>::result_map pipeline<float>::impl::forward_gpu(const std::shared_ptr<memory::tensor<float>>& input);
+template <>
+pipeline<unsigned short>::result_map pipeline<unsigned short>::impl::forward_gpu(
+    const std::shared_ptr<memory::tensor<unsigned short>>& input);
 
 // Op-by-op execution in file order with the reference's tensor semantics.
 template <typename Dtype>
@@ -1732,6 +1763,86 @@ pipeline<float>::result_map pipeline<float>::impl::forward_gpu(const std::shared
 }
 
 template <typename Dtype>
+bool pipeline<Dtype>::impl::forward_f16_input(const uint16_t*, int, int, int, int, result_map&) { return false; }
+template <>
+bool pipeline<float>::impl::forward_f16_input(const uint16_t* host_f16, int N, int C, int H, int W, result_map& out) {
+    if (!fusion_ || !plan_refused_.empty()) return false;
+    if (!chunk_plan_) chunk_plan_.reset(new fused_plan(op_params_, operations_, input_names_, output_names_, device_));
+    if (!chunk_plan_->unsupported_reason().empty()) return false;
+    const int k = (h2d_chunks_ > 1 && N % h2d_chunks_ == 0) ? h2d_chunks_ : 1;
+    try {
+        if (!chunk_plan_->built_for(N / k, C, H, W)) chunk_plan_->build(N / k, C, H, W);
+    } catch (const plan_refusal& e) {
+        plan_refused_ = e.what();
+        chunk_plan_.reset();
+        return false;
+    }
+    if (!chunk_plan_->host_f16_capable()) return false;
+    chunk_plan_->run_chunked(nullptr, k, graph_, 0, host_f16);
+    launches_ = chunk_plan_->launches();
+    device_ms_ = chunk_plan_->device_ms();
+    used_fused_ = true;
+    used_chunked_ = true;
+    out = chunk_plan_->chunk_out_;
+    return true;
+}
+
+namespace {
+std::shared_ptr<memory::tensor<unsigned short>> to_f16_tensor(const std::shared_ptr<memory::tensor<float>>& t, int device) {
+    if (!t) return nullptr;
+    auto h = std::shared_ptr<memory::tensor<unsigned short>>(
+        new memory::tensor<unsigned short>(t->data_shape(), device, memory::NCHW, nullptr));
+    convert_f32_to_f16(t->cpu_data(), h->mutable_cpu_data(), (size_t)t->count());
+    return h;
+}
+}  // namespace
+
+// pipeline<unsigned short> (the reference's fp16 Dtype: tensors of IEEE half bits, src/Excalibur/operation.cpp:74-93,
+// 124-126).  A network whose fused plan can read fp16 planes (a 3-channel image in front of an fp16 stem convolution)
+// runs that plan: the caller's fp16 input crosses PCIe as it is, results come back as fp16 tensors.  Everything else
+// runs op by op on operation<unsigned short> objects.
+template <>
+pipeline<unsigned short>::result_map pipeline<unsigned short>::impl::forward_gpu(
+    const std::shared_ptr<memory::tensor<unsigned short>>& input) {
+    if (device_ < 0) NO_GPU;
+    CHECK(input != nullptr && !input->empty()) << "empty input tensor";
+    used_fused_ = false;
+    if (fusion_ && !inner_unusable_) {
+        if (input->order() == memory::NHWC) input->convert_order();
+        if (!inner_) inner_.reset(new pipeline<float>::impl(lines_, model_file_, device_));
+        inner_->graph_ = graph_;
+        inner_->h2d_chunks_ = h2d_chunks_;
+        pipeline<float>::result_map res;
+        if (inner_->forward_f16_input(input->cpu_data(), input->num(), input->channels(), input->height(), input->width(), res)) {
+            launches_ = inner_->launches_;
+            device_ms_ = inner_->device_ms_;
+            used_fused_ = true;
+            result_map out;
+            for (auto& kv : res) out[kv.first] = to_f16_tensor(kv.second, device_);
+            return out;
+        }
+        inner_unusable_ = true;
+        inner_.reset();
+        LOG(WARNING) << "running op by op: the fused plan of this graph cannot read an fp16 input";
+    }
+    if (input->order() == memory::NCHW) {
+        // the fp16 operations work on channel-last tensors (as the reference's fp16 GPU path does): reorder on the host
+        const int n = input->num(), c = input->channels(), h = input->height(), w = input->width();
+        auto t = std::shared_ptr<memory::tensor<unsigned short>>(
+            new memory::tensor<unsigned short>(std::vector<int>{n, h, w, c}, device_, memory::NHWC, input->allocator()));
+        const unsigned short* src = input->cpu_data();
+        unsigned short* dst = t->mutable_cpu_data();
+        for (int in = 0; in < n; ++in)
+            for (int ic = 0; ic < c; ++ic)
+                for (int ih = 0; ih < h; ++ih)
+                    for (int iw = 0; iw < w; ++iw)
+                        dst[(((size_t)in * h + ih) * w + iw) * c + ic] = src[(((size_t)in * c + ic) * h + ih) * w + iw];
+        return forward_unfused(t);
+    }
+    return forward_unfused(input);
+}
+
+template <typename Dtype>
 std::shared_ptr<memory::tensor<Dtype>> pipeline<Dtype>::impl::get_featmap(std::string_view name) {
     auto it = featmap_index_.find(std::string(name));
     if (it == featmap_index_.end()) return nullptr;
@@ -1748,6 +1859,47 @@ std::shared_ptr<memory::tensor<float>> pipeline<float>::impl::get_featmap(std::s
     auto it = featmap_index_.find(std::string(name));
     if (it == featmap_index_.end()) return nullptr;
     return featmaps_[it->second];
+}
+template <>
+std::shared_ptr<memory::tensor<unsigned short>> pipeline<unsigned short>::impl::get_featmap(std::string_view name) {
+    if (used_fused_ && inner_) return to_f16_tensor(inner_->get_featmap(name), device_);
+    auto it = featmap_index_.find(std::string(name));
+    if (it == featmap_index_.end()) return nullptr;
+    return featmaps_[it->second];
+}
+
+// chrome://tracing JSON: one "B" / "E" event pair per entry, timestamps in microseconds; names are escaped.
+bool write_chrome_trace(std::string_view path, const std::vector<std::string>& names, const std::vector<double>& begin_ms,
+                        const std::vector<double>& end_ms) {
+    if (names.size() != begin_ms.size() || names.size() != end_ms.size()) return false;
+    std::ofstream out{std::string(path)};
+    if (!out) return false;
+    auto escaped = [](const std::string& s) {
+        std::string r;
+        for (char c : s) {
+            if (c == '"' || c == '\\') {
+                r += '\\';
+                r += c;
+            } else if ((unsigned char)c < 0x20) {
+                char buf[8];
+                std::snprintf(buf, sizeof(buf), "\\u%04x", (unsigned)(unsigned char)c);
+                r += buf;
+            } else {
+                r += c;
+            }
+        }
+        return r;
+    };
+    out << "{\"traceEvents\":[";
+    for (size_t i = 0; i < names.size(); ++i) {
+        for (int k = 0; k < 2; ++k) {
+            if (i || k) out << ",";
+            out << "{\"name\":\"" << escaped(names[i]) << "\",\"cat\":\"op\",\"ph\":\"" << (k ? "E" : "B")
+                << "\",\"pid\":0,\"tid\":0,\"ts\":" << (k ? end_ms[i] : begin_ms[i]) * 1000.0 << "}";
+        }
+    }
+    out << "]}";
+    return (bool)out;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1800,20 +1952,14 @@ template <typename Dtype> std::string pipeline<Dtype>::version() { return exb_ve
 
 template <typename Dtype>
 bool pipeline<Dtype>::dump_profile(std::string_view path) {
-    std::ofstream out{std::string(path)};
-    if (!out) return false;
-    out << "{\"traceEvents\":[";
-    bool first = true;
-    for (auto& e : impl_->trace_) {
-        for (int k = 0; k < 2; ++k) {
-            if (!first) out << ",";
-            first = false;
-            out << "{\"name\":\"" << e.name << "\",\"cat\":\"op\",\"ph\":\"" << (k ? "E" : "B") << "\",\"pid\":0,\"tid\":0,\"ts\":"
-                << (double)(k ? e.end_ms : e.begin_ms) * 1000.0 << "}";
-        }
+    std::vector<std::string> names;
+    std::vector<double> b, e;
+    for (auto& ev : impl_->trace_) {
+        names.push_back(ev.name);
+        b.push_back(ev.begin_ms);
+        e.push_back(ev.end_ms);
     }
-    out << "]}";
-    return true;
+    return write_chrome_trace(path, names, b, e);
 }
 
 INSTANCE_CLASS(pipeline);

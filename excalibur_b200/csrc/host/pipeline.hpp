@@ -15,6 +15,10 @@
 namespace glasssix {
 namespace excalibur {
 
+// What dump_profile writes: a chrome://tracing file with one "B" / "E" event pair per (name, begin, end) entry.
+EXB_HOST_API bool write_chrome_trace(std::string_view path, const std::vector<std::string>& names,
+                                     const std::vector<double>& begin_ms, const std::vector<double>& end_ms);
+
 template <typename Dtype>
 class EXB_HOST_API pipeline {
 public:

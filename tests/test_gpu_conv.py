@@ -110,7 +110,7 @@ def test_conv_i8_residual_relu_dual_output(ctx):
 
 
 F16_CASES = [
-    (1, 64, 56, 56, 64, 3, 1, 1),       # BASELINE config 1 shape
+    (1, 64, 56, 56, 64, 3, 1, 1),       # the single-layer benchmark configuration's shape
     (2, 16, 37, 41, 64, 7, 2, 3),       # stem-like (3 channels padded to 16)
     (2, 64, 28, 28, 128, 3, 2, 1),
     (2, 128, 14, 14, 256, 1, 1, 0),
@@ -145,7 +145,7 @@ def test_conv_f16(ctx, case, impl):
 
 
 def test_conv_f16_config1_against_unrounded_fp32(ctx):
-    """BASELINE config 1: fp32 data, fp16 kernel, 1e-2 relative of the fp32 result."""
+    """The single-layer benchmark configuration: fp32 data, fp16 kernel, 1e-2 relative of the fp32 result."""
     capi = _capi()
     r = rng(1000)
     x = r.uniform(-1, 1, (1, 64, 56, 56)).astype(np.float32)

@@ -371,3 +371,47 @@ def test_output_view_is_the_tensor_forward_returned():
     with pytest.raises(h.HostError):
         p.output_view("stem_act")          # an inner map is not an output
     p.close()
+
+
+@pytest.mark.parametrize("int8", [False, True], ids=["fp16_net", "int8_net"])
+def test_pipeline_f16_runs_the_fused_plan_on_an_fp16_input(int8):
+    """pipeline<unsigned short> (the reference's fp16 Dtype): the fp16 image is uploaded as it is and the fused plan
+    runs; the logits equal pipeline<float>'s on the same fp16 values, rounded to fp16, bit for bit."""
+    h = _host()
+    scales = {str(n): np.float32(s) for n, s in zip(G["resnet_scale_names"], G["resnet_scales"])} if int8 else None
+    g, _ = models.resnet18(2, act_scales=scales)
+    x16 = G["resnet_x"].astype(np.float16)
+    pf = h.Pipeline(g.phai_text(), g.racy_bytes(), 0, fusion=True)
+    ref = pf.forward(x16.astype(np.float32))["logits"]
+    pf.close()
+    ph = h.PipelineF16(g.phai_text(), g.racy_bytes(), 0, fusion=True)
+    for chunks in (1, 2):
+        ph.set_option("h2d_chunks", chunks)
+        for _ in range(3):
+            ph.forward(x16)
+        launches, _ = ph.stats()
+        assert launches > 0, "the fused plan did not run"
+        out = ph.get("logits")
+        assert out.dtype == np.float16 and out.shape == ref.shape
+        np.testing.assert_array_equal(out, ref.astype(np.float16))
+    ph.close()
+
+
+def test_pipeline_f16_falls_back_to_op_by_op():
+    """A graph whose input is not a 3-channel image (no fp16 ingest step) runs op by op on fp16 tensors."""
+    h = _host()
+    r = np.random.default_rng(12)
+    w = (r.standard_normal((32, 16, 3, 3)) * 0.2).astype(np.float32)
+    b = r.standard_normal(32).astype(np.float32)
+    g = GraphBuilder()
+    g.conv("c", "in", "out", w, b, 1, 1, act=1)
+    x = r.uniform(-1, 1, (2, 16, 9, 11)).astype(np.float32)
+    ph = h.PipelineF16(g.phai_text(), g.racy_bytes(), 0, fusion=True)
+    ph.forward(x.astype(np.float16))
+    launches, _ = ph.stats()
+    out = ph.get("out").astype(np.float32)
+    ph.close()
+    assert launches <= 0
+    ref = O.conv2d_f32(f16_round(x), f16_round(w), b, 1, 1, act=1)
+    assert out.shape == ref.shape
+    assert_close_f16(out, ref, what="fp16 pipeline, op by op")
