@@ -17,7 +17,7 @@ ACT_NONE, ACT_RELU, ACT_RELU6_QUIRK, ACT_SIGMOID, ACT_MISH, ACT_RELU6, ACT_SILU,
 
 EXPORTED_SYMBOLS = [
     "exb_ctx_create", "exb_ctx_destroy", "exb_last_error_string", "exb_version", "exb_ctx_sm_count",
-    "exb_ctx_sync_check", "exb_selftest_bounded_wait", "exb_tensor_peak_probe", "exb_nchw_f32_to_nhwc", "exb_nchw_f32_to_nhwc_padded", "exb_nhwc_to_nchw_f32", "exb_conv_out_dims",
+    "exb_ctx_sync_check", "exb_selftest_bounded_wait", "exb_tensor_peak_probe", "exb_tensor_peak_probe_layout", "exb_nchw_f32_to_nhwc", "exb_nchw_f32_to_nhwc_padded", "exb_nhwc_to_nchw_f32", "exb_conv_out_dims",
     "exb_conv_weights_pack_f16", "exb_conv_weights_pack_i8", "exb_conv_weights_destroy",
     "exb_conv2d_fwd", "exb_conv2d_uses_tensor_cores", "exb_conv2d_pool_fusable", "exb_dw_weights_pack", "exb_dw_weights_destroy",
     "exb_dwconv2d_fwd", "exb_pool_out_dims", "exb_pool2d_fwd", "exb_pool2d_nchw_f32_static", "exb_eltwise_fwd", "exb_binaryop_fwd",
@@ -74,6 +74,7 @@ def lib():
         L.exb_ctx_sync_check.argtypes = [vp, vp]
         L.exb_selftest_bounded_wait.argtypes = [vp, i32, vp]
         L.exb_tensor_peak_probe.argtypes = [vp, i32, i32, i32, i32, i32, C.POINTER(C.c_double), vp, vp]
+        L.exb_tensor_peak_probe_layout.argtypes = [vp, i32, i32, i32, i32, i32, i32, i32, i32, C.POINTER(C.c_double), vp, vp]
         L.exb_nchw_f32_to_nhwc.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
         L.exb_nchw_f32_to_nhwc_padded.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, i32, vp]
         L.exb_nhwc_to_nchw_f32.argtypes = [vp, vp, i32, vp, i32, i32, i32, i32, i32, f32, vp]

@@ -79,6 +79,17 @@ struct ConvTcParams {
     int b_resident;   // the whole weight slice stays in shared memory for the life of the CTA
     int b_region;     // bytes of the B region in shared memory (ring or resident copy)
     int b_perm;       // tmB is the 5-D channel-permuting map of the quad epilogue
+    int k_iters;      // K units per tile: (tap, channel block) pairs, or (kernel row, channel block) pairs in row-box mode
+    // "Row-box" mode for stride-1 convolutions (TW = 8): one K unit is the TMA box of TW + kw - 1 pixels x TH x TN of
+    // ONE kernel row and channel block; the kw taps of that row are the same box read through descriptors that start
+    // 0, 1, .. kw-1 pixels in (an 8-row group of the tile = 8 consecutive pixels of a box row, the next group one
+    // box row = a_sbo bytes on).  The hardware swizzle is a function of the shared-memory address, so a descriptor may
+    // start anywhere in a swizzle atom; the tensor pipe reads such operands at full rate (exb_tensor_peak_probe_layout).
+    // Every input byte then crosses from L2 into shared memory kh * (TW + kw - 1) / TW times instead of kh * kw times:
+    // that traffic, not the tensor pipe, is what bounds the tap-by-tap loop.
+    int rowbox;
+    int taps;         // B blocks (taps) per K unit: kw in row-box mode, else 1
+    int a_sbo;        // bytes between consecutive 8-row groups of the A operand
     // "Patch" mode for stride-2 stems on NHWC4 rows (8-byte pixels): the A operand of kernel row r
     // is the raw input patch itself, read through an un-swizzled descriptor whose rows are 16
     // bytes apart (= one output column) and whose K chunks are 16 bytes apart as well, so the
@@ -102,16 +113,48 @@ struct TileCoord {
     int ow0, oh0, n0, ntile;
 };
 
-__device__ __forceinline__ TileCoord decode_tile(const ConvTcParams& p, int t) {
-    TileCoord c;
-    c.ntile = t % p.n_tiles;
-    int m = t / p.n_tiles;
-    c.ow0 = (m % p.tiles_w) * p.step_w + p.org;
-    m /= p.tiles_w;
-    c.oh0 = (m % p.tiles_h) * p.step_h + p.org;
-    c.n0 = (m / p.tiles_h) * p.TN;
-    return c;
-}
+// Walks the tile sequence first, first + step, first + 2 * step, ... of one role without a division per tile: the
+// position is kept as mixed-radix digits (N tile, tile column, tile row, image group) and the step, split into the
+// same digits once, is added with carries.  (Every role is a single thread or a warp whose instructions depend on
+// one another; three integer divisions per tile were a visible part of the tile period of short-K layers.)
+struct TileCursor {
+    int nt, w, h, n;        // position
+    int dnt, dw, dh, dn;    // step
+    __device__ __forceinline__ TileCursor(const ConvTcParams& p, int first, int step) {
+        nt = first % p.n_tiles;
+        int m = first / p.n_tiles;
+        w = m % p.tiles_w;
+        m /= p.tiles_w;
+        h = m % p.tiles_h;
+        n = m / p.tiles_h;
+        dnt = step % p.n_tiles;
+        m = step / p.n_tiles;
+        dw = m % p.tiles_w;
+        m /= p.tiles_w;
+        dh = m % p.tiles_h;
+        dn = m / p.tiles_h;
+    }
+    __device__ __forceinline__ void advance(const ConvTcParams& p) {
+        nt += dnt;
+        int c = nt >= p.n_tiles;
+        if (c) nt -= p.n_tiles;
+        w += dw + c;
+        c = w >= p.tiles_w;
+        if (c) w -= p.tiles_w;
+        h += dh + c;
+        c = h >= p.tiles_h;
+        if (c) h -= p.tiles_h;
+        n += dn + c;
+    }
+    __device__ __forceinline__ TileCoord coord(const ConvTcParams& p) const {
+        TileCoord c;
+        c.ntile = nt;
+        c.ow0 = w * p.step_w + p.org;
+        c.oh0 = h * p.step_h + p.org;
+        c.n0 = n * p.TN;
+        return c;
+    }
+};
 
 // One pixel's 16 consecutive channels starting at channel `cl`: v = acc * scale + bias (+ residual) -> activation ->
 // first / second output.  `pix` is the pixel's index in the output tensor.  The accumulators are raw[kStep * (i / 2) +
@@ -209,6 +252,22 @@ __device__ __forceinline__ void epi_quad_rows(const EpiParams& e, const float* q
     }
 }
 
+// The MMAs of one row-box unit, fully unrolled: tap s reads the box s pixels further in (kSteps 32-byte K steps per
+// pixel) against the weight block of that tap.  The issuing thread retires one instruction every few cycles, so
+// every address computed at run time shows in the MMA rate of narrow tiles.
+template <bool kInt8, int kTaps, int kSteps>
+__device__ __forceinline__ void rowbox_unit(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                            uint32_t idesc, uint32_t b_tap, uint32_t accumulate) {
+#pragma unroll
+    for (int sx = 0; sx < kTaps; ++sx) {
+#pragma unroll
+        for (int ks = 0; ks < kSteps; ++ks)
+            ptx::tc_mma_ab<kInt8>(d_tmem, a_lo + (uint32_t)(sx * 2 * kSteps + 2 * ks), a_hi, b_lo + (uint32_t)(2 * ks), b_hi, idesc,
+                                  (sx | ks) ? 1u : accumulate);
+        b_lo += b_tap;
+    }
+}
+
 // kEpiWarps = 16: one CTA per SM (all of shared memory and TMEM, 2-4 accumulator buffers).
 // kEpiWarps = 8:  two CTAs per SM for layers with narrow N tiles: two MMA issuers and two producers per SM;
 //                 each CTA takes half the shared memory and at most 256 TMEM columns.
@@ -238,12 +297,12 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
     // Per K iteration (tap, channel block): TMA coordinates that do not depend on the tile.
     int4* k_tab = reinterpret_cast<int4*>(s_bias + p.n_tiles * p.BN);
     // Pool mode: one 128-pixel x 64-channel fp16 staging tile per epilogue group.
-    uint8_t* pool_stage = reinterpret_cast<uint8_t*>(k_tab + (p.fold ? p.kh : p.kh * p.kw * p.cblks));
+    uint8_t* pool_stage = reinterpret_cast<uint8_t*>(k_tab + p.k_iters);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.n_tiles;
-    const int k_iters = p.fold ? p.kh : p.kh * p.kw * p.cblks;
+    const int k_iters = p.k_iters;
 
     // Let the next kernel of the stream be scheduled as soon as SMs free up (it waits for this
     // grid's completion at its own griddepcontrol.wait before it reads or writes global memory).
@@ -273,6 +332,11 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const int oh_ = it - p.pad_t;
             const int ph = p.stride == 2 ? (oh_ & 1) : 0;
             k_tab[it] = make_int4(0, 0, p.stride == 2 ? ((oh_ - ph) >> 1) : oh_, (it * p.kb_elems) | ((ph * 2) << 28));
+            continue;
+        }
+        if (p.rowbox) {  // one unit per (kernel row, channel block): the box starts pad_l pixels left of the tile
+            const int r = it / p.cblks, cb = it - r * p.cblks;
+            k_tab[it] = make_int4(cb * p.kb_elems, -p.pad_l, r - p.pad_t, r * p.kw * p.cin_pad + cb * p.kb_elems);
             continue;
         }
         const int tap = it / p.cblks, cb = it - tap * p.cblks;
@@ -328,29 +392,36 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         uint32_t phase = 0;
         int ok = 1;
         const uint32_t a_base = ptx::smem_u32(smem_a) + (uint32_t)(lane * p.a_bytes);
-        const uint32_t b_base = ptx::smem_u32(smem_b) + (uint32_t)(lane * p.b_bytes);
-        const uint32_t a_stage = (uint32_t)(G * p.a_bytes), b_stage = (uint32_t)(G * p.b_bytes);
+        const uint32_t b_base = ptx::smem_u32(smem_b) + (uint32_t)(lane * p.taps * p.b_bytes);
+        const uint32_t a_stage = (uint32_t)(G * p.a_bytes), b_stage = (uint32_t)(G * p.taps * p.b_bytes);
         const uint32_t full0 = ptx::smem_u32(&full_bar[0]), empty0 = ptx::smem_u32(&empty_bar[0]);
         const uint64_t mapA0 = reinterpret_cast<uint64_t>(&p.tmA[0]);
         const uint64_t mapB = reinterpret_cast<uint64_t>(&p.tmB);
         const bool bres = p.b_resident != 0;
         const bool bperm = p.b_perm != 0;
-        const uint32_t tx = (uint32_t)(p.a_tx_bytes + (bres ? 0 : p.b_bytes));
+        const uint32_t tx = (uint32_t)(p.a_tx_bytes + (bres ? 0 : p.taps * p.b_bytes));
         if (bres && lane == 0) {
-            // Weights stay resident: the slice [BN x K] is loaded once (n_tiles == 1 here).
+            // Weights stay resident: the slice [BN x K] is loaded once (n_tiles == 1 here), one block per tap and
+            // channel block in tap-major order (row-box mode: unit (r, cb) holds taps (r, 0..kw-1)).
             const uint32_t rb = ptx::smem_u32(&bres_bar);
-            ptx::mbar_arrive_expect_tx_u32(rb, (uint32_t)(k_iters * p.b_bytes));
+            ptx::mbar_arrive_expect_tx_u32(rb, (uint32_t)(k_iters * p.taps * p.b_bytes));
             for (int it = 0; it < k_iters; ++it) {
-                const uint32_t dst = ptx::smem_u32(smem_b) + (uint32_t)(it * p.b_bytes);
-                if (bperm) ptx::tma_load_5d_u32(dst, mapB, rb, k_tab[it].w & 0x0fffffff, 0, 0, 0, 0);
-                else ptx::tma_load_2d_u32(dst, mapB, rb, k_tab[it].w & 0x0fffffff, 0);
+                const int r = it / p.cblks, cb = it - r * p.cblks;
+                for (int sx = 0; sx < p.taps; ++sx) {
+                    const int blk = p.rowbox ? (r * p.kw + sx) * p.cblks + cb : it;
+                    const uint32_t dst = ptx::smem_u32(smem_b) + (uint32_t)(blk * p.b_bytes);
+                    const int kc = (k_tab[it].w & 0x0fffffff) + sx * p.cin_pad;
+                    if (bperm) ptx::tma_load_5d_u32(dst, mapB, rb, kc, 0, 0, 0, 0);
+                    else ptx::tma_load_2d_u32(dst, mapB, rb, kc, 0);
+                }
             }
         }
         if (p.patch) {
             if (lane == 0) {
                 const uint32_t bytes = (uint32_t)(p.patch_rows * p.patch_pitch);
-                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                    const TileCoord tc = decode_tile(p, t);
+                TileCursor cur(p, blockIdx.x, gridDim.x);
+                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, cur.advance(p)) {
+                    const TileCoord tc = cur.coord(p);
                     if (!ptx::mbar_wait_bounded_u32(empty0 + stage * 8, phase ^ 1u, &abort_flag, kMaxSpins)) {
                         ok = 0;
                         break;
@@ -375,8 +446,9 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 }
             }
         } else if (lane < G) {
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const TileCoord tc = decode_tile(p, t);
+            TileCursor cur(p, blockIdx.x, gridDim.x);
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, cur.advance(p)) {
+                const TileCoord tc = cur.coord(p);
                 const int ncoord = tc.ntile * p.BN;
                 for (int it0 = 0; it0 < k_iters; it0 += G) {
                     const int nb = min(G, k_iters - it0);
@@ -393,8 +465,12 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         ptx::tma_load_4d_u32(a_base + stage * a_stage, mapA0 + ((uint32_t)e.w >> 28) * sizeof(CUtensorMap), fb,
                                              e.x, tc.ow0 + e.y, tc.oh0 + e.z, tc.n0);
                         if (!bres) {
-                            if (bperm) ptx::tma_load_5d_u32(b_base + stage * b_stage, mapB, fb, e.w & 0x0fffffff, 0, 0, 0, ncoord >> 5);
-                            else ptx::tma_load_2d_u32(b_base + stage * b_stage, mapB, fb, e.w & 0x0fffffff, ncoord);
+                            for (int sx = 0; sx < p.taps; ++sx) {
+                                const uint32_t dst = b_base + stage * b_stage + (uint32_t)(sx * p.b_bytes);
+                                const int kc = (e.w & 0x0fffffff) + sx * p.cin_pad;
+                                if (bperm) ptx::tma_load_5d_u32(dst, mapB, fb, kc, 0, 0, 0, ncoord >> 5);
+                                else ptx::tma_load_2d_u32(dst, mapB, fb, kc, ncoord);
+                            }
                         }
                     }
                     if (++stage == p.stages) {
@@ -429,7 +505,13 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const uint32_t b_lo0 = (uint32_t)ptx::make_smem_desc(ptx::smem_u32(smem_b), (uint32_t)p.kb_bytes);
             const uint32_t a_blk = (uint32_t)p.a_bytes >> 4, b_blk = (uint32_t)p.b_bytes >> 4;
             const bool bres = p.b_resident != 0;
-            const uint32_t a_stage = a_blk * G, b_stage = bres ? 0u : b_blk * G;
+            const uint32_t a_stage = a_blk * G, b_stage = bres ? 0u : b_blk * G * p.taps;
+            // row-box: A groups are a box row apart, tap s starts s pixels in; resident B blocks of one unit's taps
+            // are cblks blocks apart (tap-major order), streamed ones follow each other
+            const uint32_t a_hi = (desc_hi & ~0x3FFFu) | (((uint32_t)p.a_sbo >> 4) & 0x3FFFu);
+            const uint32_t a_tap = (uint32_t)p.kb_bytes >> 4;
+            const uint32_t b_tap = bres ? b_blk * p.cblks : b_blk;
+            const uint32_t rb_row = (uint32_t)((p.kw - 1) * p.cblks) * b_blk;   // after a row's last channel block: skip its other taps
             const uint32_t idesc = p.idesc;
             if (bres && !ptx::mbar_wait_bounded(&bres_bar, 0, &abort_flag, kMaxSpins)) ok = false;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -440,6 +522,8 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
                 uint32_t accumulate = 0;
+                uint32_t rb_b = b_lo0;
+                int rb_cb = 0;
                 if (p.patch) {
                     if (!ptx::mbar_wait_bounded_u32(full0 + stage * 8, phase, &abort_flag, kMaxSpins)) {
                         ok = false;
@@ -482,6 +566,26 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     }
                     uint32_t a_lo = a_lo0 + stage * a_stage;
                     uint32_t b_lo = b_lo0 + (bres ? (uint32_t)it0 * b_blk : stage * b_stage);
+                    if (p.rowbox) {
+                        for (int g = 0; g < nb; ++g) {
+                            // resident weights: the unit's first block (tap-major order); streamed: the stage's
+                            const uint32_t bu = bres ? rb_b : b_lo0 + stage * b_stage + (uint32_t)g * b_tap * p.taps;
+                            if (p.taps == 3 && ksteps == 4) rowbox_unit<kInt8, 3, 4>(d_tmem, a_lo, a_hi, bu, desc_hi, idesc, b_tap, accumulate);
+                            else if (p.taps == 3 && ksteps == 2) rowbox_unit<kInt8, 3, 2>(d_tmem, a_lo, a_hi, bu, desc_hi, idesc, b_tap, accumulate);
+                            else
+                                for (int sx = 0; sx < p.taps; ++sx)
+                                    for (int ks = 0; ks < ksteps; ++ks)
+                                        ptx::tc_mma_ab<kInt8>(d_tmem, a_lo + sx * a_tap + 2 * ks, a_hi, bu + sx * b_tap + 2 * ks, desc_hi,
+                                                              idesc, (sx | ks) ? 1u : accumulate);
+                            accumulate = 1;
+                            a_lo += a_blk;
+                            rb_b += b_blk;
+                            if (++rb_cb == p.cblks) {
+                                rb_cb = 0;
+                                rb_b += rb_row;
+                            }
+                        }
+                    } else
                     for (int g = 0; g < nb; ++g) {
                         if (ksteps == 4) {
                             ptx::tc_mma_lohi<kInt8>(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
@@ -536,8 +640,9 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const int th = (row / p.TW) % p.TH;
             uint8_t* stg = pool_stage + grp * (kTileM * 128);
             volatile int* failed = &pool_fail[grp];
-            for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles; t += p.epi_groups * gridDim.x, ti += p.epi_groups) {
-                const TileCoord tc = decode_tile(p, t);
+            TileCursor cur(p, blockIdx.x + grp * gridDim.x, p.epi_groups * gridDim.x);
+            for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles; t += p.epi_groups * gridDim.x, ti += p.epi_groups, cur.advance(p)) {
+                const TileCoord tc = cur.coord(p);
                 const int ow = tc.ow0 + tw, oh = tc.oh0 + th;
                 const bool inside = ow >= 0 && ow < p.OW && oh >= 0 && oh < p.OH;
                 const int buf = ti % p.acc_bufs;
@@ -652,15 +757,17 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 return (n * p.OH + oh) * p.OW + ow;
             };
             const bool want_res = p.has_res != 0;
+            TileCursor cur(p, blockIdx.x + grp * gridDim.x, p.epi_groups * gridDim.x);
             for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles && ok; t += p.epi_groups * gridDim.x, ti += p.epi_groups) {
-                const TileCoord tc = decode_tile(p, t);
+                const TileCoord tc = cur.coord(p);
+                cur.advance(p);            // from here on: this group's next tile
                 const int buf = ti % p.acc_bufs;
                 const uint32_t acc_phase = (uint32_t)(ti / p.acc_bufs) & 1u;
                 const int c0 = tc.ntile * p.BN + cq * 8;       // first channel of this thread in block 0
                 // The residual lines of this group's NEXT tile are asked into L2 now (no register cost): when that
                 // tile's turn comes its residual loads find them a few hundred cycles away instead of in DRAM.
                 if (want_res && t + p.epi_groups * (int)gridDim.x < total_tiles) {
-                    const TileCoord c2 = decode_tile(p, t + p.epi_groups * (int)gridDim.x);
+                    const TileCoord c2 = cur.coord(p);
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         if (h < h_begin || h >= h_end) continue;
@@ -674,32 +781,47 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         }
                     }
                 }
+                // This thread's fragments of the tile: tile-row halves h_begin .. h_end - 1, nblk 32-channel blocks each,
+                // fragment f = (half, block).  The residual of fragment f + 1 is requested before fragment f is
+                // worked on, and that of the first fragment before the accumulator is even complete: a fragment's
+                // arithmetic is a few hundred cycles, a residual load from L2 under load considerably more.
+                const int pa0 = pixel_of(tc, h_begin ? rowpack[1][0] : rowpack[0][0]), pb0 = pixel_of(tc, h_begin ? rowpack[1][1] : rowpack[0][1]);
+                const int pa1 = pixel_of(tc, rowpack[1][0]), pb1 = pixel_of(tc, rowpack[1][1]);
+                const int nfrag = (h_end - h_begin) * nblk;
+                auto res_load = [&](int f, uint4& a, uint4& b) {
+                    a = make_uint4(0, 0, 0, 0);
+                    b = make_uint4(0, 0, 0, 0);
+                    const bool second = f >= nblk;
+                    const int cl = c0 + (second ? f - nblk : f) * 32;
+                    if (want_res && f < nfrag && cl < p.e.cout_stride) {
+                        const int pa = second ? pa1 : pa0, pb = second ? pb1 : pb0;
+                        if (pa >= 0) a = __ldg(reinterpret_cast<const uint4*>(p.e.residual + (int64_t)pa * p.e.cout_stride + cl));
+                        if (pb >= 0) b = __ldg(reinterpret_cast<const uint4*>(p.e.residual + (int64_t)pb * p.e.cout_stride + cl));
+                    }
+                };
+                uint4 ra, rb;
+                res_load(0, ra, rb);
                 if (!ptx::mbar_wait_bounded_warp(&tfull_bar[buf], acc_phase, &abort_flag, kMaxSpins)) {
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after_sync();
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (h < h_begin || h >= h_end) continue;
-                    const uint32_t taddr = taddr0 + ((uint32_t)(h * 16) << 16) + (uint32_t)(buf * p.BN);
-                    const int pa = pixel_of(tc, rowpack[h][0]), pb = pixel_of(tc, rowpack[h][1]);
 #pragma unroll 1
-                    for (int b = 0; b < nblk; ++b) {
-                        const int cl = c0 + b * 32;
-                        const bool c_in = cl < p.e.cout_stride;
-                        // residual first: its latency overlaps the TMEM load and the scale / bias arithmetic
-                        uint4 ra = make_uint4(0, 0, 0, 0), rb = make_uint4(0, 0, 0, 0);
-                        if (want_res && c_in) {
-                            if (pa >= 0) ra = __ldg(reinterpret_cast<const uint4*>(p.e.residual + (int64_t)pa * p.e.cout_stride + cl));
-                            if (pb >= 0) rb = __ldg(reinterpret_cast<const uint4*>(p.e.residual + (int64_t)pb * p.e.cout_stride + cl));
-                        }
-                        uint32_t raw[16];
-                        ptx::tmem_ld_16x256b_x4(taddr + b * 32, raw);
-                        ptx::tmem_ld_wait();
-                        if (!c_in) continue;
-                        epi_quad_rows<kInt8, kPrelu>(p.e, s_scale, s_bias, cl, cq, pa, pb, want_res, ra, rb, raw);
-                    }
+                for (int f = 0; f < nfrag; ++f) {
+                    const bool second = f >= nblk;
+                    const int b = second ? f - nblk : f;
+                    const int h = second ? 1 : h_begin;
+                    const int cl = c0 + b * 32;
+                    uint4 na, nb;
+                    res_load(f + 1, na, nb);
+                    uint32_t raw[16];
+                    ptx::tmem_ld_16x256b_x4(taddr0 + ((uint32_t)(h * 16) << 16) + (uint32_t)(buf * p.BN + b * 32), raw);
+                    ptx::tmem_ld_wait();
+                    if (cl < p.e.cout_stride)
+                        epi_quad_rows<kInt8, kPrelu>(p.e, s_scale, s_bias, cl, cq, second ? pa1 : pa0, second ? pb1 : pb0, want_res, ra,
+                                                     rb, raw);
+                    ra = na;
+                    rb = nb;
                 }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
@@ -713,8 +835,10 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const bool row_in_box = row < p.TW * p.TH * p.TN;
             const bool vec_ok = (p.e.cout_stride & 15) == 0;
             const int n_chunks = p.BN / 16;
+            TileCursor cur(p, blockIdx.x + grp * gridDim.x, p.epi_groups * gridDim.x);
             for (int t = blockIdx.x + grp * gridDim.x; t < total_tiles && ok; t += p.epi_groups * gridDim.x, ti += p.epi_groups) {
-                const TileCoord tc = decode_tile(p, t);
+                const TileCoord tc = cur.coord(p);
+                cur.advance(p);            // from here on: this group's next tile
                 const int ow = tc.ow0 + tw, oh = tc.oh0 + th, n = tc.n0 + tn;
                 const int buf = ti % p.acc_bufs;
                 const uint32_t acc_phase = (uint32_t)(ti / p.acc_bufs) & 1u;
@@ -735,7 +859,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 // the tile after this one then finds them a few hundred cycles away instead of a DRAM
                 // round trip per chunk, which the one-chunk-ahead register prefetch cannot cover.
                 if (p.has_res && vec_ok && t + p.epi_groups * (int)gridDim.x < total_tiles) {
-                    const TileCoord c2 = decode_tile(p, t + p.epi_groups * (int)gridDim.x);
+                    const TileCoord c2 = cur.coord(p);
                     const int ow2 = c2.ow0 + tw, oh2 = c2.oh0 + th, n2 = c2.n0 + tn;
                     if (row_in_box && ow2 < p.OW && oh2 < p.OH && n2 < p.N) {
                         const __half* r2 = p.e.residual + (((int64_t)n2 * p.OH + oh2) * p.OW + ow2) * p.e.cout_stride +
@@ -917,8 +1041,68 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     if (g.pool && !(patch && two && p.BN == 64 && conv_tc_pool_fusable(g)))
         return fail(EXB_ERR_UNSUPPORTED, "fused pooling needs the patch-mode stem kernel with 64 output channels");
     p.a_tx_bytes = p.TW * p.TH * p.TN * p.kb_bytes;
+    p.taps = 1;
+    p.a_sbo = 8 * p.kb_bytes;
+    // Row-box mode (see ConvTcParams): stride 1, at least two taps per kernel row, dense input rows.  The tile is 8
+    // pixels wide; TH x TN = 16 is chosen for the fewest wasted rows.  Taken when it moves fewer operand bytes from L2
+    // into shared memory than the tap-by-tap loop does, counting the extra tiles a map whose width is not a multiple
+    // of 8 costs and the weights that stay resident.
+    struct RowBox {
+        bool on;
+        int TH, TN, one_cta;
+    } rb = {false, 0, 0, 0};
+    if (!fold.on && !patch && g.sh == 1 && g.sw == 1 && g.kw >= 2 && g.kw <= 9 && g.w_pitch == g.W && g.w_pad == 0) {
+        double best = -1.0;
+        for (int th = 16; th >= 1; th >>= 1) {
+            const int tn = 16 / th;
+            const int64_t tiles = (int64_t)((g.OH + th - 1) / th) * ((g.N + tn - 1) / tn);
+            const double eff = (double)g.OH * g.N / ((double)tiles * th * tn);
+            if (eff > best + 1e-9) {
+                best = eff;
+                rb.TH = th;
+                rb.TN = tn;
+            }
+        }
+        const int64_t tiles_rb = (int64_t)((g.OW + 7) / 8) * ((g.OH + rb.TH - 1) / rb.TH) * ((g.N + rb.TN - 1) / rb.TN);
+        const int64_t tiles_tap = (int64_t)p.tiles_w * p.tiles_h * p.tiles_nb;
+        const int64_t k_bytes_all = (int64_t)g.kh * g.kw * p.cblks * p.kb_bytes;             // K bytes of one operand row
+        const int64_t a_tap = kTileM * k_bytes_all;
+        const int64_t a_rb = (int64_t)(8 + g.kw - 1) * 16 * g.kh * p.cblks * p.kb_bytes;
+        const int64_t b_tile = (int64_t)p.BN * k_bytes_all;
+        // weights stay resident with two CTAs per SM (as before) or, in row-box mode, with one CTA per SM as well
+        const bool res_two = p.n_tiles == 1 && two && b_tile <= 48 * 1024;
+        const bool res_one = p.n_tiles == 1 && b_tile <= 150 * 1024;
+        const double cost_tap = (double)tiles_tap * (a_tap + (res_two ? 0 : b_tile));
+        const double cost_rb = (double)tiles_rb * (a_rb + (res_one ? 0 : b_tile));
+        if (cost_rb < 0.85 * cost_tap) {
+            rb.on = true;
+            rb.one_cta = (res_one && !res_two && two) ? 1 : 0;
+            // at least three units must fit beside the tables (and the resident weights)
+            const bool two_rb = two && !rb.one_cta;
+            const int64_t room = (two_rb ? 228 * 1024 / 2 - 1024 : ctx->smem_optin) - 2048 - 2 * p.n_tiles * p.BN * (int)sizeof(float) -
+                                 g.kh * p.cblks * (int)sizeof(int4);
+            const bool res = two_rb ? res_two : res_one;
+            const int64_t unit = round_up((8 + g.kw - 1) * 16 * p.kb_bytes, 1024) + (res ? 0 : (int64_t)g.kw * p.b_bytes);
+            if (room - (res ? b_tile : 0) < 3 * unit) rb.on = false;
+        }
+    }
+    if (rb.on) {
+        p.rowbox = 1;
+        p.taps = g.kw;
+        p.TW = 8; p.TH = rb.TH; p.TN = rb.TN;
+        p.tiles_w = (g.OW + 7) / 8;
+        p.tiles_h = (g.OH + p.TH - 1) / p.TH;
+        p.tiles_nb = (g.N + p.TN - 1) / p.TN;
+        p.step_w = p.TW; p.step_h = p.TH; p.org = 0;
+        p.a_sbo = (8 + g.kw - 1) * p.kb_bytes;
+        p.a_bytes = (8 + g.kw - 1) * 16 * p.kb_bytes;      // one box: a multiple of 1024 bytes for every kb_bytes >= 64
+        p.a_bytes = round_up(p.a_bytes, 1024);
+        p.a_tx_bytes = (8 + g.kw - 1) * 16 * p.kb_bytes;
+        if (rb.one_cta) two = false;
+    }
     const int ctas_per_sm = two ? 2 : 1;
-    const int k_iters = fold.on ? g.kh : g.kh * g.kw * p.cblks;
+    const int k_iters = fold.on ? g.kh : (p.rowbox ? g.kh * p.cblks : g.kh * g.kw * p.cblks);
+    p.k_iters = k_iters;
     if ((int64_t)g.N * g.OH * g.OW >= (int64_t)1 << 31) return fail(EXB_ERR_UNSUPPORTED, "more than 2^31 output pixels");
     if ((int64_t)g.kh * w->kw_pack * w->cin_pad >= (1 << 28)) return fail(EXB_ERR_UNSUPPORTED, "reduction dimension too large");
     const int epi_bytes = 2 * p.n_tiles * p.BN * (int)sizeof(float) + k_iters * (int)sizeof(int4) +
@@ -929,10 +1113,10 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     // Keep the weights in shared memory for the whole kernel when the slice fits beside a useful
     // operand ring: it removes the weight re-read per tile from the L2 -> SM traffic that bounds
     // this kernel.
-    const int b_all = k_iters * p.b_bytes;
-    p.b_resident = (p.n_tiles == 1 && b_all <= 150 * 1024 && budget - b_all >= 4 * p.a_bytes) ? 1 : 0;
+    const int b_all = k_iters * p.taps * p.b_bytes;
+    p.b_resident = (p.n_tiles == 1 && b_all <= 150 * 1024 && budget - b_all >= (p.rowbox ? 3 : 4) * p.a_bytes) ? 1 : 0;
     if (p.b_resident) budget -= b_all;
-    const int blk_bytes = p.a_bytes + (p.b_resident ? 0 : p.b_bytes);
+    const int blk_bytes = p.a_bytes + (p.b_resident ? 0 : p.taps * p.b_bytes);
     // K blocks per stage: aim at ~48 KB stages (one mbarrier round trip each), keep >= 3 stages,
     // prefer a group size that divides the K loop.
     int gmax = (48 * 1024) / blk_bytes;
@@ -946,6 +1130,12 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
             break;
         }
     while (G > 1 && budget / (G * blk_bytes) < 3) --G;
+    if (p.rowbox) {
+        // A row-box unit already carries kw taps.  One stage per tile (all its units behind one barrier and one
+        // commit) when two such stages fit - every hand-over costs the single issuing thread a few hundred
+        // cycles - else one unit per stage and as many stages as fit.
+        G = (k_iters * blk_bytes <= 48 * 1024 && budget / (k_iters * blk_bytes) >= 2) ? k_iters : 1;
+    }
     p.kgroup = G;
     int stages = budget / (G * blk_bytes);
     if (patch) {   // ring of whole patches, weights in their own region
@@ -956,7 +1146,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     }
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return fail(EXB_ERR_UNSUPPORTED, "conv tile does not fit shared memory (BN=%d)", p.BN);
-    p.b_region = patch ? g.kh * p.BN * 64 : (p.b_resident ? b_all : stages * G * p.b_bytes);
+    p.b_region = patch ? g.kh * p.BN * 64 : (p.b_resident ? b_all : stages * G * p.taps * p.b_bytes);
     p.stages = stages;
     // As many accumulator buffers as TMEM allows (256 columns per CTA with two CTAs per SM, else
     // 512): a buffer goes round MMA -> hand-over -> epilogue -> hand-back, and the two hand-overs
@@ -1016,7 +1206,8 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         } else {
             cuuint64_t dims[4] = {(cuuint64_t)g.cin_stride, (cuuint64_t)vw, (cuuint64_t)vh, (cuuint64_t)g.N};
             cuuint64_t strides[3] = {(cuuint64_t)st_ * px_bytes, (cuuint64_t)st_ * row_pitch, (cuuint64_t)g.H * row_pitch};
-            cuuint32_t box[4] = {(cuuint32_t)p.kb_elems, (cuuint32_t)p.TW, (cuuint32_t)p.TH, (cuuint32_t)p.TN};
+            cuuint32_t box[4] = {(cuuint32_t)p.kb_elems, (cuuint32_t)(p.rowbox ? p.TW + g.kw - 1 : p.TW), (cuuint32_t)p.TH,
+                                 (cuuint32_t)p.TN};
             cuuint32_t estr[4] = {1, 1, 1, 1};
             void* base = const_cast<char*>(static_cast<const char*>(x)) + (size_t)ph * row_pitch +
                          (size_t)(pw + g.w_pad) * px_bytes;

@@ -3,8 +3,6 @@
 // vector of the strip is loaded once per kernel row and reused by all taps that touch it, and
 // each weight vector is loaded once per strip.  Weights are kept tap-major [kh*kw][C] in fp32
 // so consecutive threads read consecutive channels.
-#include <stdlib.h>
-
 #include <type_traits>
 
 #include "common.cuh"
@@ -289,26 +287,6 @@ int launch(exb_ctx* ctx, const DwParams& p, const void* x, const exb_dw_weights*
         if (p.kh == 3 && p.kw == 3 && p.sh == p.sw && (p.sh == 1 || p.sh == 2) && smem <= 48 * 1024) {
             constexpr int R = 8;
             if (p.sh == 1) {
-#ifdef EXB_CONV_EXPERIMENTS
-                if (const char* e = getenv("EXB_DW_VARIANT")) {
-                    const int v = atoi(e);
-                    if (v == 1) {
-                        const int64_t total = (int64_t)p.N * ((p.OH + R - 1) / R) * ((p.OW + 1) / 2) * cvecs;
-                        dw3x3_roll_f16_kernel<1, 2, R><<<stream_grid(ctx, total, 128, 6), 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);
-                        return after_launch("dw3x3_roll_f16_kernel");
-                    }
-                    if (v == 2) {
-                        const int64_t total = (int64_t)p.N * ((p.OH + 15) / 16) * ((p.OW + 1) / 2) * cvecs;
-                        dw3x3_roll_f16_kernel<1, 2, 16><<<stream_grid(ctx, total, 128, 6), 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);
-                        return after_launch("dw3x3_roll_f16_kernel");
-                    }
-                    if (v == 3) {
-                        const int64_t total = (int64_t)p.N * ((p.OH + 3) / 4) * ((p.OW + 3) / 4) * cvecs;
-                        dw3x3_roll_f16_kernel<1, 4, 4><<<stream_grid(ctx, total, 128, 4), 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);
-                        return after_launch("dw3x3_roll_f16_kernel");
-                    }
-                }
-#endif
                 const int64_t total = (int64_t)p.N * ((p.OH + R - 1) / R) * ((p.OW + 3) / 4) * cvecs;
                 const int grid = stream_grid(ctx, total, 128, 4);
                 dw3x3_roll_f16_kernel<1, 4, R><<<grid, 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);

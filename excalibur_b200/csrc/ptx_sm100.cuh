@@ -114,7 +114,9 @@ __device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t p
                 break;
             }
             if ((i & 15u) == 15u && *abort_flag) break;
+#if EXB_EPI_BACKOFF_NS > 0
             __nanosleep(EXB_EPI_BACKOFF_NS);
+#endif
         }
         if (!ok) *abort_flag = 1;
     }
@@ -208,6 +210,31 @@ __device__ __forceinline__ void tc_mma_lohi(uint32_t d_tmem, uint32_t a_lo, uint
             "setp.ne.b32 p, %5, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
             "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// The same with separate high halves for the two descriptors (A and B tiles with different strides).
+template <bool kInt8>
+__device__ __forceinline__ void tc_mma_ab(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t idesc, uint32_t accumulate) {
+    if (kInt8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %2};\n\t"
+            "mov.b64 db, {%3, %4};\n\t"
+            "setp.ne.b32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+            "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %2};\n\t"
+            "mov.b64 db, {%3, %4};\n\t"
+            "setp.ne.b32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+            "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
             : "memory");
     }
 }

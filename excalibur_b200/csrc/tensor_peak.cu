@@ -19,13 +19,16 @@ constexpr uint32_t kProbeMaxSpins = 1u << 22;
 
 template <bool kInt8>
 __global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int n, int kblk, int iters, uint32_t idesc, int tmem_cols,
-                                                             int* error, unsigned long long* cycles) {
+                                                             int* error, unsigned long long* cycles, int kb_bytes, int a_sbo,
+                                                             int a_shift) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t done_bar;
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int a_bytes = 128 * 128, b_bytes = n * 128;
+    // a_sbo: bytes between consecutive 8-row groups of A (8 * kb_bytes = dense rows; larger = rows of a wider box),
+    // a_shift: byte offset of the first row inside its region (a descriptor that starts part-way into a swizzle atom)
+    const int a_bytes = 16 * a_sbo + 1024, b_bytes = n * kb_bytes;
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + (size_t)kblk * a_bytes;
     const int warp = threadIdx.x >> 5;
@@ -58,21 +61,22 @@ __global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int n, int kblk, in
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_smem;
     if (threadIdx.x == 0) {
-        const uint64_t d0 = ptx::make_smem_desc(ptx::smem_u32(smem_a), 128u);
+        const uint64_t d0 = ptx::make_smem_desc(ptx::smem_u32(smem_a) + (uint32_t)a_shift, (uint32_t)kb_bytes);
         const uint32_t desc_hi = (uint32_t)(d0 >> 32);
+        const uint32_t a_hi = (desc_hi & ~0x3FFFu) | (((uint32_t)a_sbo >> 4) & 0x3FFFu);
         const uint32_t a_lo0 = (uint32_t)d0;
-        const uint32_t b_lo0 = (uint32_t)ptx::make_smem_desc(ptx::smem_u32(smem_b), 128u);
+        const uint32_t b_lo0 = (uint32_t)ptx::make_smem_desc(ptx::smem_u32(smem_b), (uint32_t)kb_bytes);
+        const int ksteps = kb_bytes / 32;
         const uint32_t a_blk = (uint32_t)a_bytes >> 4, b_blk = (uint32_t)b_bytes >> 4;
         const unsigned long long t0 = clock64();
         uint32_t accumulate = 0;
         for (int it = 0; it < iters; ++it) {
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
             for (int kb = 0; kb < kblk; ++kb) {
-                ptx::tc_mma_lohi<kInt8>(tmem_base, a_lo, b_lo, desc_hi, idesc, accumulate);
-                ptx::tc_mma_lohi<kInt8>(tmem_base, a_lo + 2, b_lo + 2, desc_hi, idesc, 1);
-                ptx::tc_mma_lohi<kInt8>(tmem_base, a_lo + 4, b_lo + 4, desc_hi, idesc, 1);
-                ptx::tc_mma_lohi<kInt8>(tmem_base, a_lo + 6, b_lo + 6, desc_hi, idesc, 1);
-                accumulate = 1;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ptx::tc_mma_ab<kInt8>(tmem_base, a_lo + 2 * ks, a_hi, b_lo + 2 * ks, desc_hi, idesc, accumulate);
+                    accumulate = 1;
+                }
                 a_lo += a_blk;
                 b_lo += b_blk;
             }
@@ -94,14 +98,26 @@ __global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int n, int kblk, in
 
 using namespace exb;
 
+extern "C" int exb_tensor_peak_probe_layout(exb_ctx* ctx, int dtype, int n, int ctas_per_sm, int kblk, int iters, int kb_bytes,
+                                            int a_sbo, int a_shift, double* ops_per_launch, unsigned long long* d_cycles,
+                                            void* stream);
 extern "C" int exb_tensor_peak_probe(exb_ctx* ctx, int dtype, int n, int ctas_per_sm, int kblk, int iters,
                                      double* ops_per_launch, unsigned long long* d_cycles, void* stream) {
+    return exb_tensor_peak_probe_layout(ctx, dtype, n, ctas_per_sm, kblk, iters, 128, 1024, 0, ops_per_launch, d_cycles, stream);
+}
+
+extern "C" int exb_tensor_peak_probe_layout(exb_ctx* ctx, int dtype, int n, int ctas_per_sm, int kblk, int iters, int kb_bytes,
+                                            int a_sbo, int a_shift, double* ops_per_launch, unsigned long long* d_cycles,
+                                            void* stream) {
     EXB_REQUIRE(ctx != nullptr, "exb_tensor_peak_probe: null context");
     EXB_REQUIRE(dtype == EXB_I8 || dtype == EXB_F16, "exb_tensor_peak_probe: dtype must be EXB_I8 or EXB_F16");
     EXB_REQUIRE(n >= 16 && n <= 256 && n % 16 == 0, "exb_tensor_peak_probe: n must be a multiple of 16 in 16..256");
     EXB_REQUIRE(ctas_per_sm == 1 || ctas_per_sm == 2, "exb_tensor_peak_probe: ctas_per_sm must be 1 or 2");
     EXB_REQUIRE(kblk >= 1 && kblk <= 8 && iters >= 1 && iters <= (1 << 20), "exb_tensor_peak_probe: kblk 1..8, iters 1..2^20");
-    const size_t smem = (size_t)kblk * (128 + n) * 128 + 1024;
+    EXB_REQUIRE(kb_bytes == 32 || kb_bytes == 64 || kb_bytes == 128, "exb_tensor_peak_probe: kb_bytes must be 32, 64 or 128");
+    EXB_REQUIRE(a_sbo >= 8 * kb_bytes && a_sbo % 16 == 0 && a_sbo <= 4096 && a_shift >= 0 && a_shift % 16 == 0 && a_shift < 1024,
+                "exb_tensor_peak_probe: a_sbo must be a multiple of 16 in [8 * kb_bytes, 4096], a_shift a multiple of 16 below 1024");
+    const size_t smem = (size_t)kblk * ((size_t)16 * a_sbo + 1024 + (size_t)n * kb_bytes) + 1024;
     const size_t limit = ctas_per_sm == 2 ? (size_t)(228 * 1024 / 2 - 2048) : (size_t)ctx->smem_optin - 1024;
     EXB_REQUIRE(smem <= limit, "exb_tensor_peak_probe: %d K blocks of (128 + %d) rows do not fit shared memory", kblk, n);
     int cols = 32;
@@ -112,10 +128,10 @@ extern "C" int exb_tensor_peak_probe(exb_ctx* ctx, int dtype, int n, int ctas_pe
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto kern = int8 ? tensor_peak_kernel<true> : tensor_peak_kernel<false>;
     EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, 128, smem, st>>>(n, kblk, iters, idesc, cols, ctx->d_error, d_cycles);
+    kern<<<grid, 128, smem, st>>>(n, kblk, iters, idesc, cols, ctx->d_error, d_cycles, kb_bytes, a_sbo, a_shift);
     if (ops_per_launch) {
         const double k_per_mma = int8 ? 32.0 : 16.0;
-        *ops_per_launch = 2.0 * 128.0 * n * k_per_mma * 4.0 * kblk * (double)iters * grid;
+        *ops_per_launch = 2.0 * 128.0 * n * k_per_mma * (kb_bytes / 32) * kblk * (double)iters * grid;
     }
     return after_launch("tensor_peak_kernel");
 }
