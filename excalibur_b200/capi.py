@@ -74,7 +74,7 @@ def lib():
         L.exb_ctx_sync_check.argtypes = [vp, vp]
         L.exb_selftest_bounded_wait.argtypes = [vp, i32, vp]
         L.exb_tensor_peak_probe.argtypes = [vp, i32, i32, i32, i32, i32, C.POINTER(C.c_double), vp, vp]
-        L.exb_tensor_peak_probe_layout.argtypes = [vp, i32, i32, i32, i32, i32, i32, i32, i32, C.POINTER(C.c_double), vp, vp]
+        L.exb_tensor_peak_probe_layout.argtypes = [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, C.POINTER(C.c_double), vp, vp]
         L.exb_nchw_f32_to_nhwc.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
         L.exb_nchw_f32_to_nhwc_padded.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, i32, vp]
         L.exb_nhwc_to_nchw_f32.argtypes = [vp, vp, i32, vp, i32, i32, i32, i32, i32, f32, vp]

@@ -18,7 +18,7 @@ namespace {
 constexpr uint32_t kProbeMaxSpins = 1u << 22;
 
 template <bool kInt8>
-__global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int n, int kblk, int iters, uint32_t idesc, int tmem_cols,
+__global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int m, int n, int kblk, int iters, uint32_t idesc, int tmem_cols,
                                                              int* error, unsigned long long* cycles, int kb_bytes, int a_sbo,
                                                              int a_shift) {
     extern __shared__ uint8_t smem_raw[];
@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int n, int kblk, in
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // a_sbo: bytes between consecutive 8-row groups of A (8 * kb_bytes = dense rows; larger = rows of a wider box),
     // a_shift: byte offset of the first row inside its region (a descriptor that starts part-way into a swizzle atom)
-    const int a_bytes = 16 * a_sbo + 1024, b_bytes = n * kb_bytes;
+    const int a_bytes = (m / 8) * a_sbo + 1024, b_bytes = n * kb_bytes;
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + (size_t)kblk * a_bytes;
     const int warp = threadIdx.x >> 5;
@@ -73,10 +73,16 @@ __global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int n, int kblk, in
         for (int it = 0; it < iters; ++it) {
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
             for (int kb = 0; kb < kblk; ++kb) {
-                for (int ks = 0; ks < ksteps; ++ks) {
-                    ptx::tc_mma_ab<kInt8>(tmem_base, a_lo + 2 * ks, a_hi, b_lo + 2 * ks, desc_hi, idesc, accumulate);
-                    accumulate = 1;
+                if (ksteps == 4) {      // unrolled: the issuing thread's own loop overhead must not be what is measured
+                    ptx::tc_mma_ab<kInt8>(tmem_base, a_lo, a_hi, b_lo, desc_hi, idesc, accumulate);
+                    ptx::tc_mma_ab<kInt8>(tmem_base, a_lo + 2, a_hi, b_lo + 2, desc_hi, idesc, 1);
+                    ptx::tc_mma_ab<kInt8>(tmem_base, a_lo + 4, a_hi, b_lo + 4, desc_hi, idesc, 1);
+                    ptx::tc_mma_ab<kInt8>(tmem_base, a_lo + 6, a_hi, b_lo + 6, desc_hi, idesc, 1);
+                } else {
+                    for (int ks = 0; ks < ksteps; ++ks)
+                        ptx::tc_mma_ab<kInt8>(tmem_base, a_lo + 2 * ks, a_hi, b_lo + 2 * ks, desc_hi, idesc, ks ? 1u : accumulate);
                 }
+                accumulate = 1;
                 a_lo += a_blk;
                 b_lo += b_blk;
             }
@@ -98,40 +104,41 @@ __global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int n, int kblk, in
 
 using namespace exb;
 
-extern "C" int exb_tensor_peak_probe_layout(exb_ctx* ctx, int dtype, int n, int ctas_per_sm, int kblk, int iters, int kb_bytes,
+extern "C" int exb_tensor_peak_probe_layout(exb_ctx* ctx, int dtype, int m, int n, int ctas_per_sm, int kblk, int iters, int kb_bytes,
                                             int a_sbo, int a_shift, double* ops_per_launch, unsigned long long* d_cycles,
                                             void* stream);
 extern "C" int exb_tensor_peak_probe(exb_ctx* ctx, int dtype, int n, int ctas_per_sm, int kblk, int iters,
                                      double* ops_per_launch, unsigned long long* d_cycles, void* stream) {
-    return exb_tensor_peak_probe_layout(ctx, dtype, n, ctas_per_sm, kblk, iters, 128, 1024, 0, ops_per_launch, d_cycles, stream);
+    return exb_tensor_peak_probe_layout(ctx, dtype, 128, n, ctas_per_sm, kblk, iters, 128, 1024, 0, ops_per_launch, d_cycles, stream);
 }
 
-extern "C" int exb_tensor_peak_probe_layout(exb_ctx* ctx, int dtype, int n, int ctas_per_sm, int kblk, int iters, int kb_bytes,
+extern "C" int exb_tensor_peak_probe_layout(exb_ctx* ctx, int dtype, int m, int n, int ctas_per_sm, int kblk, int iters, int kb_bytes,
                                             int a_sbo, int a_shift, double* ops_per_launch, unsigned long long* d_cycles,
                                             void* stream) {
     EXB_REQUIRE(ctx != nullptr, "exb_tensor_peak_probe: null context");
     EXB_REQUIRE(dtype == EXB_I8 || dtype == EXB_F16, "exb_tensor_peak_probe: dtype must be EXB_I8 or EXB_F16");
+    EXB_REQUIRE(m == 64 || m == 128, "exb_tensor_peak_probe: m must be 64 or 128");
     EXB_REQUIRE(n >= 16 && n <= 256 && n % 16 == 0, "exb_tensor_peak_probe: n must be a multiple of 16 in 16..256");
     EXB_REQUIRE(ctas_per_sm == 1 || ctas_per_sm == 2, "exb_tensor_peak_probe: ctas_per_sm must be 1 or 2");
     EXB_REQUIRE(kblk >= 1 && kblk <= 8 && iters >= 1 && iters <= (1 << 20), "exb_tensor_peak_probe: kblk 1..8, iters 1..2^20");
     EXB_REQUIRE(kb_bytes == 32 || kb_bytes == 64 || kb_bytes == 128, "exb_tensor_peak_probe: kb_bytes must be 32, 64 or 128");
     EXB_REQUIRE(a_sbo >= 8 * kb_bytes && a_sbo % 16 == 0 && a_sbo <= 4096 && a_shift >= 0 && a_shift % 16 == 0 && a_shift < 1024,
                 "exb_tensor_peak_probe: a_sbo must be a multiple of 16 in [8 * kb_bytes, 4096], a_shift a multiple of 16 below 1024");
-    const size_t smem = (size_t)kblk * ((size_t)16 * a_sbo + 1024 + (size_t)n * kb_bytes) + 1024;
+    const size_t smem = (size_t)kblk * ((size_t)(m / 8) * a_sbo + 1024 + (size_t)n * kb_bytes) + 1024;
     const size_t limit = ctas_per_sm == 2 ? (size_t)(228 * 1024 / 2 - 2048) : (size_t)ctx->smem_optin - 1024;
-    EXB_REQUIRE(smem <= limit, "exb_tensor_peak_probe: %d K blocks of (128 + %d) rows do not fit shared memory", kblk, n);
+    EXB_REQUIRE(smem <= limit, "exb_tensor_peak_probe: %d K blocks of (%d + %d) rows do not fit shared memory", kblk, m, n);
     int cols = 32;
     while (cols < n) cols *= 2;
     const bool int8 = dtype == EXB_I8;
-    const uint32_t idesc = ptx::make_idesc(int8, 128, (uint32_t)n);
+    const uint32_t idesc = ptx::make_idesc(int8, (uint32_t)m, (uint32_t)n);
     const int grid = ctx->sm_count * ctas_per_sm;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto kern = int8 ? tensor_peak_kernel<true> : tensor_peak_kernel<false>;
     EXB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, 128, smem, st>>>(n, kblk, iters, idesc, cols, ctx->d_error, d_cycles, kb_bytes, a_sbo, a_shift);
+    kern<<<grid, 128, smem, st>>>(m, n, kblk, iters, idesc, cols, ctx->d_error, d_cycles, kb_bytes, a_sbo, a_shift);
     if (ops_per_launch) {
         const double k_per_mma = int8 ? 32.0 : 16.0;
-        *ops_per_launch = 2.0 * 128.0 * n * k_per_mma * (kb_bytes / 32) * kblk * (double)iters * grid;
+        *ops_per_launch = 2.0 * m * n * k_per_mma * (kb_bytes / 32) * kblk * (double)iters * grid;
     }
     return after_launch("tensor_peak_kernel");
 }

@@ -95,11 +95,12 @@ EXB_API int exb_selftest_bounded_wait(exb_ctx* ctx, int max_polls, void* stream)
 EXB_API int exb_tensor_peak_probe(exb_ctx* ctx, int dtype, int n, int ctas_per_sm, int kblk, int iters,
                                   double* ops_per_launch, unsigned long long* d_cycles, void* stream);
 /* The same probe with the A operand laid out as the convolution kernel's variants lay it out: K blocks of kb_bytes
- * (32 / 64 / 128, swizzle of the same width), a_sbo bytes between consecutive 8-row groups (8 * kb_bytes = dense
+ * (32 / 64 / 128, swizzle of the same width), m = 64 or 128 accumulator rows (64: what a GEMM with the output
+ * channels of a narrow layer on M would issue), a_sbo bytes between consecutive 8-row groups (8 * kb_bytes = dense
  * rows; more = rows of a box wider than the tile) and a descriptor that starts a_shift bytes into its region (a
  * shifted window of a wider box).  Shows what an operand layout costs the tensor pipe before a kernel is built
  * around it.  No reference counterpart. */
-EXB_API int exb_tensor_peak_probe_layout(exb_ctx* ctx, int dtype, int n, int ctas_per_sm, int kblk, int iters,
+EXB_API int exb_tensor_peak_probe_layout(exb_ctx* ctx, int dtype, int m, int n, int ctas_per_sm, int kblk, int iters,
                                          int kb_bytes, int a_sbo, int a_shift, double* ops_per_launch,
                                          unsigned long long* d_cycles, void* stream);
 
