@@ -86,6 +86,10 @@ int pack_common(exb_ctx* ctx, const ConvGeom& g, int dtype, const void* hw, size
         exb_conv_weights_destroy(w);
         return fail(EXB_ERR_CUDA, "conv weight upload: %s", cudaGetErrorString(e));
     }
+    w->h_scale = new float[cout_pad];
+    w->h_bias = new float[cout_pad];
+    memcpy(w->h_scale, scale.data(), sizeof(float) * cout_pad);
+    memcpy(w->h_bias, bias.data(), sizeof(float) * cout_pad);
     *out = w;
     return EXB_OK;
 }
@@ -182,6 +186,8 @@ extern "C" int exb_conv_weights_destroy(exb_conv_weights* w) {
     if (w->d_scale) cudaFree(w->d_scale);
     if (w->d_bias) cudaFree(w->d_bias);
     if (w->d_slope) cudaFree(w->d_slope);
+    delete[] w->h_scale;
+    delete[] w->h_bias;
     delete w;
     return EXB_OK;
 }

@@ -15,6 +15,8 @@ struct exb_conv_weights {
     float* d_scale;   // [cout_pad] epilogue multiplier (fp16: 1; int8: 1/(wscale*act_scale))
     float* d_bias;    // [cout_pad] zeros when the layer has no bias
     float* d_slope;   // [cout_pad + kSlopeSlack] PReLU slopes (zero beyond Cout), or null
+    float* h_scale;   // host copies of d_scale / d_bias: narrow layers pass them to the kernel as launch parameters
+    float* h_bias;
     int device;
 };
 

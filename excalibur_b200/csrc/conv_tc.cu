@@ -45,6 +45,7 @@ namespace {
 constexpr int kMaxStages = 8;
 constexpr int kFirstEpiWarp = 2;   // warp 0 producer, warp 1 MMA issuer, epilogue warps from here on
 constexpr int kMaxAccBufs = 4;
+constexpr int kConstCh = 64;      // output channels of the pool epilogue (scale / bias travel as launch parameters)
 constexpr int kTileM = 128;
 constexpr uint32_t kMaxSpins = 1u << 21;  // tens of milliseconds at least; a legitimate wait is microseconds
 
@@ -107,6 +108,13 @@ struct ConvTcParams {
     // starts at (6*tx - 1, 14*ty - 1), so it holds every input of the 3 x 7 pooled outputs that
     // start at (3*tx, 7*ty); neighbouring tiles overlap by two rows / columns, which are recomputed.
     int pool, PH, PW;
+    // Pool epilogue: per-channel scale and bias as launch parameters.  Its channel offsets are compile-time constants,
+    // so the values become constant-bank operands of the FMAs: no load instruction and no traffic on the load/store
+    // pipe, where a shared-memory load at an address common to the warp costs one wavefront per four bytes.  (With
+    // run-time offsets - the other epilogues - a constant-bank load per value measured slower than the shared-memory
+    // copy.)
+    alignas(16) float c_scale[kConstCh];
+    alignas(16) float c_bias[kConstCh];
 };
 
 struct TileCoord {
@@ -161,11 +169,9 @@ struct TileCursor {
 // kFirst + (i & 1)], i = 0..15: (16, 2, 0) reads a plain 16-register chunk, (32, 4, 0) / (32, 4, 2) the first / second
 // pixel of a 16x256b fragment.
 template <bool kInt8, bool kPrelu, int kRegs, int kStep, int kFirst>
-__device__ __forceinline__ void epi_row16(const EpiParams& e, const float* s_scale, const float* s_bias, int cl, int64_t pix,
+__device__ __forceinline__ void epi_row16(const EpiParams& e, const float4 (&sc)[4], const float4 (&bi)[4], int cl, int64_t pix,
                                           bool add_res, const uint32_t (&res)[8], const uint32_t (&raw)[kRegs]) {
     float v[16];
-    const float4* sc = reinterpret_cast<const float4*>(s_scale + cl);
-    const float4* bi = reinterpret_cast<const float4*>(s_bias + cl);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float4 s4 = sc[i], b4 = bi[i];
@@ -658,11 +664,12 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
                         ptx::tmem_ld_wait();
                         float v[16];
-                        const float4* sc = reinterpret_cast<const float4*>(s_scale + chunk * 16);
-                        const float4* bi = reinterpret_cast<const float4*>(s_bias + chunk * 16);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const float4 s4 = sc[i], b4 = bi[i];
+                            // compile-time offsets into the launch parameters: constant-bank operands of the FMAs
+                            const int c4 = chunk * 16 + 4 * i;
+                            const float4 s4 = make_float4(p.c_scale[c4], p.c_scale[c4 + 1], p.c_scale[c4 + 2], p.c_scale[c4 + 3]);
+                            const float4 b4 = make_float4(p.c_bias[c4], p.c_bias[c4 + 1], p.c_bias[c4 + 2], p.c_bias[c4 + 3]);
                             v[4 * i + 0] = epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x);
                             v[4 * i + 1] = epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y);
                             v[4 * i + 2] = epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z);
@@ -885,7 +892,13 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     const int cl = tc.ntile * p.BN + chunk * 16;   // first channel of the chunk
                     if (!valid || cl >= p.e.cout_stride) continue;
                     if (vec_ok) {
-                        epi_row16<kInt8, kPrelu, 16, 2, 0>(p.e, s_scale, s_bias, cl, pix, do_res, rc, raw);
+                        float4 sc[4], bi[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            sc[i] = reinterpret_cast<const float4*>(s_scale + cl)[i];
+                            bi[i] = reinterpret_cast<const float4*>(s_bias + cl)[i];
+                        }
+                        epi_row16<kInt8, kPrelu, 16, 2, 0>(p.e, sc, bi, cl, pix, do_res, rc, raw);
                     } else {
                         // ragged channel count: element-wise stores, statically indexed so the
                         // accumulators stay in registers
@@ -1164,6 +1177,12 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     p.e.y = y; p.e.y2 = y2; p.e.out_dtype = g.out_dtype; p.e.out2_dtype = g.out2_dtype; p.e.act = g.act;
     p.e.out_scale = g.out_scale; p.e.out2_scale = g.out2_scale; p.e.cout_stride = g.cout_stride; p.e.y_pitch = g.y_pitch;
     p.error = ctx->d_error;
+    if (g.pool) {       // BN == 64 (checked above)
+        for (int c = 0; c < kConstCh; ++c) {
+            p.c_scale[c] = c < w->cout_pad ? w->h_scale[c] : 0.f;
+            p.c_bias[c] = c < w->cout_pad ? w->h_bias[c] : 0.f;
+        }
+    }
 
     const CUtensorMapDataType dt = int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUtensorMapSwizzle sw = swizzle_for(p.kb_bytes);
