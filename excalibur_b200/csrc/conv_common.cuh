@@ -197,13 +197,13 @@ __device__ __forceinline__ void act_vec16(float (&v)[16], int act) {
         for (int i = 0; i < 16; ++i) v[i] = fminf(fmaxf(v[i], 0.f), 6.f);
     } else if (act == EXB_ACT_SILU) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + __expf(-v[i]));
+        for (int i = 0; i < 16; ++i) v[i] = v[i] * sigmoid_fast(v[i]);
     } else if (act == EXB_ACT_HARDSWISH) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = v[i] * fminf(fmaxf(fmaf(v[i], 1.f / 6.f, 0.5f), 0.f), 1.f);
     } else if (act == EXB_ACT_SIGMOID) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = 1.f / (1.f + __expf(-v[i]));
+        for (int i = 0; i < 16; ++i) v[i] = sigmoid_fast(v[i]);
     } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = apply_act(v[i], act);

@@ -1064,7 +1064,8 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         bool on;
         int TH, TN, one_cta;
     } rb = {false, 0, 0, 0};
-    if (!fold.on && !patch && g.sh == 1 && g.sw == 1 && g.kw >= 2 && g.kw <= 9 && g.w_pitch == g.W && g.w_pad == 0) {
+    if (!fold.on && !patch && g.sh == 1 && g.sw == 1 && g.kw >= 2 && g.kw <= 9 && g.w_pitch == g.W && g.w_pad == 0 &&
+        p.kb_bytes >= 64) {      // 32-byte K rows: measured slower than the tap loop (0.190 vs 0.162 ms, 16 -> 32 channels @320)
         double best = -1.0;
         for (int th = 16; th >= 1; th >>= 1) {
             const int tn = 16 / th;
@@ -1085,11 +1086,15 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         // weights stay resident with two CTAs per SM (as before) or, in row-box mode, with one CTA per SM as well
         const bool res_two = p.n_tiles == 1 && two && b_tile <= 48 * 1024;
         const bool res_one = p.n_tiles == 1 && b_tile <= 150 * 1024;
+        // One CTA per SM (to keep the weights resident) only for N tiles of 128 and more: a single issuing thread
+        // cannot keep the tensor pipe busy with N = 64 instructions.
+        const bool one_cta = res_one && !res_two && two && p.BN >= 128;
+        const bool res_rb = (two && !one_cta) ? res_two : res_one;
         const double cost_tap = (double)tiles_tap * (a_tap + (res_two ? 0 : b_tile));
-        const double cost_rb = (double)tiles_rb * (a_rb + (res_one ? 0 : b_tile));
+        const double cost_rb = (double)tiles_rb * (a_rb + (res_rb ? 0 : b_tile));
         if (cost_rb < 0.85 * cost_tap) {
             rb.on = true;
-            rb.one_cta = (res_one && !res_two && two) ? 1 : 0;
+            rb.one_cta = one_cta ? 1 : 0;
             // at least three units must fit beside the tables (and the resident weights)
             const bool two_rb = two && !rb.one_cta;
             const int64_t room = (two_rb ? 228 * 1024 / 2 - 1024 : ctx->smem_optin) - 2048 - 2 * p.n_tiles * p.BN * (int)sizeof(float) -
