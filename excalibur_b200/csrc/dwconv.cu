@@ -141,9 +141,9 @@ __device__ __forceinline__ void cvt8(const uint4& r, float (&v)[V]) {
     for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
 }
 
-template <int S, int TW, int R>
+template <typename TOut, int S, int TW, int R>
 __global__ void __launch_bounds__(128) dw3x3_roll_f16_kernel(const __half* __restrict__ x, const float* __restrict__ w,
-                                                             const float* __restrict__ bias, __half* __restrict__ y,
+                                                             const float* __restrict__ bias, TOut* __restrict__ y,
                                                              DwParams p) {
     constexpr int IN_W = (TW - 1) * S + 3;
     extern __shared__ float s_w[];   // [9][cs] taps, then [cs] bias
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(128) dw3x3_roll_f16_kernel(const __half* __res
                 const int ow = ow0 + j;
                 if (ow < p.OW) {
                     dw_act(acc[j], p, cv * V);
-                    store8(y + (((int64_t)n * p.OH + oh) * p.OW + ow) * p.cs + cv * V, acc[j], 1.f);
+                    store8(y + (((int64_t)n * p.OH + oh) * p.OW + ow) * p.cs + cv * V, acc[j], p.out_scale);
                 }
             }
             // the window moves down by S rows
@@ -282,18 +282,18 @@ int launch(exb_ctx* ctx, const DwParams& p, const void* x, const exb_dw_weights*
     TOut* yo = static_cast<TOut*>(y);
     const int cvecs = p.cs / V;
     constexpr int TW = 4;
-    if constexpr (std::is_same<TIn, __half>::value && std::is_same<TOut, __half>::value) {
+    if constexpr (std::is_same<TIn, __half>::value) {      // fp16 or int8 (quantised in the store) output
         const size_t smem = (size_t)10 * p.cs * sizeof(float);
         if (p.kh == 3 && p.kw == 3 && p.sh == p.sw && (p.sh == 1 || p.sh == 2) && smem <= 48 * 1024) {
             constexpr int R = 8;
             if (p.sh == 1) {
                 const int64_t total = (int64_t)p.N * ((p.OH + R - 1) / R) * ((p.OW + 3) / 4) * cvecs;
                 const int grid = stream_grid(ctx, total, 128, 4);
-                dw3x3_roll_f16_kernel<1, 4, R><<<grid, 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);
+                dw3x3_roll_f16_kernel<TOut, 1, 4, R><<<grid, 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);
             } else {
                 const int64_t total = (int64_t)p.N * ((p.OH + R - 1) / R) * ((p.OW + 1) / 2) * cvecs;
                 const int grid = stream_grid(ctx, total, 128, 4);
-                dw3x3_roll_f16_kernel<2, 2, R><<<grid, 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);
+                dw3x3_roll_f16_kernel<TOut, 2, 2, R><<<grid, 128, smem, st>>>(xi, w->d_w, w->d_bias, yo, p);
             }
             return after_launch("dw3x3_roll_f16_kernel");
         }

@@ -692,11 +692,18 @@ void fused_plan::build(int N, int C, int H, int W) {
             d.act = g.act;
             const int OH = (x.H + d.pad_t + d.pad_b - d.kh) / d.stride_h + 1;
             const int OW = (x.W + d.pad_l + d.pad_r - d.kw) / d.stride_w + 1;
-            y.need_f16 = true;
+            // A depthwise layer whose result is read only by int8 convolutions at one scale (the projection of an
+            // inverted-residual block) quantises in its own store: no fp16 copy of the map, no quantise pass.
+            const bool i8_only = y.need_i8 && !y.need_f16 && y.extra_i8_scales.empty();
+            if (!i8_only) y.need_f16 = true;
             set_shape(y, x.N, x.C, OH, OW);
             y.cs = x.cs;
             const void* xin = form_f16(x);
-            void* yo = form_f16(y);
+            void* yo = i8_only ? form_i8(y) : form_f16(y);
+            if (i8_only) {
+                d.out_dtype = EXB_I8;
+                d.out_scale = y.i8_scale;
+            }
             const operation_batchnorm<float>* bn =
                 g.bn >= 0 ? dynamic_cast<operation_batchnorm<float>*>(ops_[g.bn].get()) : nullptr;
             exb_dw_weights* w = bn ? dw->dw_packed(ctx, d, bn->mul()->cpu_data(), bn->add()->cpu_data(), bn)
@@ -708,7 +715,7 @@ void fused_plan::build(int N, int C, int H, int W) {
             add_step(params_[i].name_, [=](cudaStream_t st) {
                 exb_check(exb_dwconv2d_fwd(ctx, &d, xin, w, yo, st), "exb_dwconv2d_fwd");
             });
-            finish_forms(y, false);
+            finish_forms(y, i8_only);
             return;
         }
         if (t == "deconvolution") {
