@@ -2,7 +2,7 @@
 
     python bench_nets.py [--net resnet18_fp16,resnet18_int8,mobilenetv2_fp16,mobilenetv2_int8,yolov5s_fp16,
                                               det_db_resnet18_fp16,mobile_unicorn_fp16,yolov5s_simp_fp16,unicorn_light_fp16,unicorn_light_int8]
-                                       [--batch B] [--size S] [--iters K] [--trace]
+                                       [--batch B] [--size S] [--iters K] [--trace | --trace-all]
 
 Per network: images/s with the input resident on the device (CUDA-graph replays, CUDA events on the
 plan's stream) and end to end (pinned host input, H2D and D2H inside the timed region).  Defaults
@@ -62,6 +62,7 @@ def main(argv=None):
     ap.add_argument("--size", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--trace", action="store_true")
+    ap.add_argument("--trace-all", action="store_true", help="every step of the plan in execution order")
     args = ap.parse_args(argv)
     torch.cuda.set_device(0)
     for name in args.net.split(","):
@@ -89,10 +90,10 @@ def main(argv=None):
         finite = all(np.isfinite(v).all() for v in outs.values())
         print("%-18s batch %3d @%d  %4d launches  %8.3f ms/step  %9.0f images/s resident  %9.0f images/s end-to-end  finite=%s"
               % (name, batch, size, launches, ms, batch / ms * 1e3, batch / e2e, finite), flush=True)
-        if args.trace:
+        if args.trace or args.trace_all:
             pipe.set_option("profile", 1)
             pipe.forward_ptr(x.data_ptr(), batch, 3, size, size)
-            tr = sorted(pipe.trace(), key=lambda t: t[1] - t[2])[:10]
+            tr = pipe.trace() if args.trace_all else sorted(pipe.trace(), key=lambda t: t[1] - t[2])[:10]
             pipe.set_option("profile", 0)
             for n, b, e in tr:
                 print("    %-28s %8.3f ms" % (n, e - b))

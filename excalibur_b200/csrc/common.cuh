@@ -77,6 +77,20 @@ __device__ __forceinline__ int quant_rne(float v) {
     return (int)t;
 }
 
+// Four floats -> four int8 (round half to even, saturate), packed little-endian in 32 bits.
+__device__ __forceinline__ uint32_t quant_pack4(float a, float b, float c, float d, float qscale) {
+    const int q0 = __float2int_rn(a * qscale), q1 = __float2int_rn(b * qscale);
+    const int q2 = __float2int_rn(c * qscale), q3 = __float2int_rn(d * qscale);
+    uint32_t r;
+    // cvt.pack.sat.s8.s32.b32 d, a, b, c:  d = (c << 16) | (sat8(a) << 8) | sat8(b)
+    asm("{\n\t.reg .b32 t;\n\t"
+        "cvt.pack.sat.s8.s32.b32 t, %4, %3, 0;\n\t"
+        "cvt.pack.sat.s8.s32.b32 %0, %2, %1, t;\n\t}"
+        : "=r"(r)
+        : "r"(q0), "r"(q1), "r"(q2), "r"(q3));
+    return r;
+}
+
 // 1 / (1 + e^-v) for the sigmoid-type activations: hardware reciprocal plus one Newton step (within 1 ulp of the
 // IEEE division at a third of its instructions).  The exponent is clamped so that the denominator stays finite
 // (the Newton step of an infinite one would be NaN); e^80 already gives a sigmoid of 2e-35.

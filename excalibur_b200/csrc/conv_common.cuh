@@ -100,20 +100,6 @@ __device__ __forceinline__ void epi_store_scalar(void* y, int dtype, int64_t off
     }
 }
 
-// Four floats -> four int8 (round half to even, saturate), packed little-endian in 32 bits.
-__device__ __forceinline__ uint32_t quant_pack4(float a, float b, float c, float d, float qscale) {
-    const int q0 = __float2int_rn(a * qscale), q1 = __float2int_rn(b * qscale);
-    const int q2 = __float2int_rn(c * qscale), q3 = __float2int_rn(d * qscale);
-    uint32_t r;
-    // cvt.pack.sat.s8.s32.b32 d, a, b, c:  d = (c << 16) | (sat8(a) << 8) | sat8(b)
-    asm("{\n\t.reg .b32 t;\n\t"
-        "cvt.pack.sat.s8.s32.b32 t, %4, %3, 0;\n\t"
-        "cvt.pack.sat.s8.s32.b32 %0, %2, %1, t;\n\t}"
-        : "=r"(r)
-        : "r"(q0), "r"(q1), "r"(q2), "r"(q3));
-    return r;
-}
-
 // 256-bit global accesses (sm_100): one instruction per 32-byte pixel segment instead of two.
 __device__ __forceinline__ void st_global_256(void* p, const uint32_t (&o)[8]) {
     asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(o[0]), "r"(o[1]), "r"(o[2]),

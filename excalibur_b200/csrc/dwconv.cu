@@ -48,10 +48,10 @@ __device__ __forceinline__ void store8(__half* p, const float (&v)[V], float) {
     *reinterpret_cast<uint4*>(p) = r;
 }
 __device__ __forceinline__ void store8(int8_t* p, const float (&v)[V], float scale) {
-    alignas(8) int8_t b[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) b[i] = (int8_t)quant_rne(v[i] * scale);
-    *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(b);
+    uint2 r;
+    r.x = quant_pack4(v[0], v[1], v[2], v[3], scale);
+    r.y = quant_pack4(v[4], v[5], v[6], v[7], scale);
+    *reinterpret_cast<uint2*>(p) = r;
 }
 __device__ __forceinline__ void loadw(const float* p, float (&v)[V]);
 // Activation of the 8 channels starting at c0.
