@@ -399,11 +399,16 @@ def run_gpu_arm(args, rank, world, local_rank):
     x_b.uniform_(0, 1, generator=gen)
     logits_b = np.empty((BATCH, 1000, 1, 1), np.float32)
 
+    caller_errors = []
+
     def caller(pl, xin, out, n):
-        torch.cuda.set_device(local_rank)
-        for _ in range(n):
-            pl.forward_ptr(xin.data_ptr(), BATCH, 3, IMG, IMG)
-            pl.get("logits", out)
+        try:
+            torch.cuda.set_device(local_rank)
+            for _ in range(n):
+                pl.forward_ptr(xin.data_ptr(), BATCH, 3, IMG, IMG)
+                pl.get("logits", out)
+        except BaseException as exc:      # a failed caller must fail the run, not shorten the timed work
+            caller_errors.append(exc)
 
     def two_callers(n_total):
         ta = threading.Thread(target=caller, args=(pipe, x, logits, n_total - n_total // 2))
@@ -412,6 +417,8 @@ def run_gpu_arm(args, rank, world, local_rank):
         tb.start()
         ta.join()
         tb.join()
+        if caller_errors:
+            raise caller_errors[0]
 
     two_callers(6)
     barrier()
@@ -468,6 +475,8 @@ def run_gpu_arm(args, rank, world, local_rank):
         tb.start()
         ta.join()
         tb.join()
+        if caller_errors:
+            raise caller_errors[0]
 
     two_callers16(6)
     barrier()

@@ -46,6 +46,9 @@ I8_CASES = [
     (1, 64, 12, 12, 320, 3, 1, 1),      # two Cout tiles
     (2, 64, 10, 10, 32, 5, 1, 2),       # 5x5
     (1, 32, 9, 9, 16, 3, 2, 0),         # stride 2 without padding
+    (3, 256, 10, 13, 128, 3, 1, 1),     # row-box loop: two channel blocks per kernel row, weights streamed, ragged width
+    (5, 128, 6, 5, 64, 3, 1, 1),        # row-box loop: map narrower than the 8-pixel tile, several images per tile
+    (1, 192, 12, 12, 64, 2, 1, 0),      # row-box loop with two taps per row (2x2 kernel, no padding), three channel blocks
 ]
 
 
@@ -117,6 +120,9 @@ F16_CASES = [
     (4, 512, 7, 7, 512, 3, 1, 1),
     (1, 32, 40, 40, 255, 1, 1, 0),      # detect head width
     (2, 16, 30, 30, 32, 6, 2, 2),       # 6x6/2 stem
+    (2, 32, 21, 19, 32, 3, 1, 1),       # row-box loop on 64-byte K rows, ragged map
+    (2, 64, 11, 9, 64, 3, 1, 1),        # row-box loop, weights streamed with two CTAs per SM (73 KB slice)
+    (1, 128, 12, 12, 64, 5, 1, 2),      # row-box loop with five taps per row, two channel blocks
 ]
 
 
