@@ -439,7 +439,7 @@ def run_gpu_arm(args, rank, world, local_rank):
 
     # ---- the same through pipeline<unsigned short>: a caller that holds fp16 images moves half the bytes ------
     pipe16 = host.PipelineF16(g8.phai_text(), g8.racy_bytes(), local_rank, fusion=True)
-    pipe16.set_option("h2d_chunks", args.e2e_chunks)
+    pipe16.set_option("h2d_chunks", args.e2e_f16_chunks)
     x16 = x.to(torch.float16).pin_memory()
     logits16 = np.empty((BATCH, 1000, 1, 1), np.float16)
 
@@ -464,7 +464,7 @@ def run_gpu_arm(args, rank, world, local_rank):
     e2e16_s = _median(e16_blocks)
     # two callers, as for the fp32 call
     pipe16_b = host.PipelineF16(g8.phai_text(), g8.racy_bytes(), local_rank, fusion=True)
-    pipe16_b.set_option("h2d_chunks", args.e2e_chunks)
+    pipe16_b.set_option("h2d_chunks", args.e2e_f16_chunks)
     x16_b = x16.clone().pin_memory()
     logits16_b = np.empty((BATCH, 1000, 1, 1), np.float16)
 
@@ -626,7 +626,7 @@ def run_gpu_arm(args, rank, world, local_rank):
                           "two_callers": {"value": images_block / e2e16b_s, "ms_per_step": e2e16b_s * 1000.0 / K},
                           "one_caller": {"value": images_block / e2e16_s, "ms_per_step": e2e16_s * 1000.0 / K},
                           "h2d_bytes_per_step": BATCH * 3 * IMG * IMG * 2, "d2h_bytes_per_step": BATCH * 1000 * 2,
-                          "h2d_chunks": args.e2e_chunks, "fused_plan": bool(f16_fused),
+                          "h2d_chunks": args.e2e_f16_chunks, "fused_plan": bool(f16_fused),
                           "api": "pipeline<unsigned short>::forward on pinned fp16 NCHW host tensors (the reference's fp16 "
                                  "Dtype); a second number beside e2e, which stays the fp32 call"},
         "gpu_launches": int(launches_per_step) * K,
@@ -692,6 +692,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-chunks", type=int, default=4,
                     help="sub-batches of one end-to-end forward (copy of c+1 overlaps compute of c)")
+    ap.add_argument("--e2e-f16-chunks", type=int, default=2,
+                    help="the same for the fp16-input forward (half the bytes per image: fewer, larger sub-batches)")
     ap.add_argument("--e2e-host-threads", type=int, default=0,
                     help="host threads converting the fp32 input to fp16 before the copy in the end-to-end measurement "
                          "(0 = copy fp32 as it is, the default: with 16 host cores the conversion costs more "

@@ -1631,6 +1631,9 @@ public:
     // int8 tensors on the device whatever the host type is); built on the first forward that can use it
     std::unique_ptr<typename pipeline<float>::impl> inner_;
     bool inner_unusable_ = false;
+    // fp16 result tensors of the fused path, reused from forward to forward: allocating and freeing pinned host
+    // memory per call synchronises the whole device, which serialises two callers that share a GPU
+    std::unordered_map<std::string, std::shared_ptr<memory::tensor<Dtype>>> f16_results_;
     std::vector<operation_param> op_params_;
     std::vector<std::shared_ptr<operation<Dtype>>> operations_;
     std::unordered_map<std::string, int> featmap_index_;
@@ -1825,7 +1828,18 @@ pipeline<unsigned short>::result_map pipeline<unsigned short>::impl::forward_gpu
             device_ms_ = inner_->device_ms_;
             used_fused_ = true;
             result_map out;
-            for (auto& kv : res) out[kv.first] = to_f16_tensor(kv.second, device_);
+            for (auto& kv : res) {
+                auto& h = f16_results_[kv.first];
+                if (!kv.second) {
+                    h.reset();
+                } else {
+                    if (!h || h->data_shape() != kv.second->data_shape())
+                        h = std::shared_ptr<memory::tensor<unsigned short>>(
+                            new memory::tensor<unsigned short>(kv.second->data_shape(), device_, memory::NCHW, nullptr));
+                    convert_f32_to_f16(kv.second->cpu_data(), h->mutable_cpu_data(), (size_t)kv.second->count());
+                }
+                out[kv.first] = h;
+            }
             return out;
         }
         inner_unusable_ = true;
