@@ -41,7 +41,7 @@ def _deps_mtime():
 
 
 def _compile(src, obj, verbose):
-    extra = os.environ.get("EXB_NVCC_EXTRA", "").split()   # e.g. -DEXB_CONV_EXPERIMENTS for kernel experiments
+    extra = os.environ.get("EXB_NVCC_EXTRA", "").split()   # extra nvcc flags, e.g. -DEXB_WAIT_HINT_NS=0
     cmd = [nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
