@@ -261,15 +261,20 @@ __device__ __forceinline__ void epi_quad_rows(const EpiParams& e, const float* q
 // The MMAs of one row-box unit, fully unrolled: tap s reads the box s pixels further in (kSteps 32-byte K steps per
 // pixel) against the weight block of that tap.  The issuing thread retires one instruction every few cycles, so
 // every address computed at run time shows in the MMA rate of narrow tiles.
-template <bool kInt8, int kTaps, int kSteps>
+template <bool kInt8, int kTaps, int kSteps, bool kPair>
 __device__ __forceinline__ void rowbox_unit(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                             uint32_t idesc, uint32_t b_tap, uint32_t accumulate) {
 #pragma unroll
     for (int sx = 0; sx < kTaps; ++sx) {
 #pragma unroll
-        for (int ks = 0; ks < kSteps; ++ks)
-            ptx::tc_mma_ab<kInt8>(d_tmem, a_lo + (uint32_t)(sx * 2 * kSteps + 2 * ks), a_hi, b_lo + (uint32_t)(2 * ks), b_hi, idesc,
-                                  (sx | ks) ? 1u : accumulate);
+        for (int ks = 0; ks < kSteps; ++ks) {
+            if (kPair)
+                ptx::tc_mma_ab_pair<kInt8>(d_tmem, a_lo + (uint32_t)(sx * 2 * kSteps + 2 * ks), a_hi, b_lo + (uint32_t)(2 * ks), b_hi,
+                                           idesc, (sx | ks) ? 1u : accumulate);
+            else
+                ptx::tc_mma_ab<kInt8>(d_tmem, a_lo + (uint32_t)(sx * 2 * kSteps + 2 * ks), a_hi, b_lo + (uint32_t)(2 * ks), b_hi, idesc,
+                                      (sx | ks) ? 1u : accumulate);
+        }
         b_lo += b_tap;
     }
 }
@@ -428,16 +433,24 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
         if (bres && lane == 0) {
             // Weights stay resident: the slice [BN x K] is loaded once (n_tiles == 1 here), one block per tap and
             // channel block in tap-major order (row-box mode: unit (r, cb) holds taps (r, 0..kw-1)).
-            const uint32_t rb = ptx::smem_u32(&bres_bar);
-            ptx::mbar_arrive_expect_tx_u32(rb, (uint32_t)(k_iters * p.taps * p.b_bytes));
+            // pair mode: each CTA keeps its half of the rows; both halves complete on the rank-0 CTA's barrier
+            const uint32_t rb = kPair ? ptx::map_to_cta(ptx::smem_u32(&bres_bar), 0) : ptx::smem_u32(&bres_bar);
+            if (!kPair || cta_rank == 0)
+                ptx::mbar_arrive_expect_tx_u32(ptx::smem_u32(&bres_bar), (uint32_t)((kPair ? 2 : 1) * k_iters * p.taps * p.b_bytes));
+            const int nrow = kPair ? (int)cta_rank * (p.BN >> 1) : 0;
             for (int it = 0; it < k_iters; ++it) {
                 const int r = it / p.cblks, cb = it - r * p.cblks;
                 for (int sx = 0; sx < p.taps; ++sx) {
                     const int blk = p.rowbox ? (r * p.kw + sx) * p.cblks + cb : it;
                     const uint32_t dst = ptx::smem_u32(smem_b) + (uint32_t)(blk * p.b_bytes);
                     const int kc = (k_tab[it].w & 0x0fffffff) + sx * p.cin_pad;
-                    if (bperm) ptx::tma_load_5d_u32(dst, mapB, rb, kc, 0, 0, 0, 0);
-                    else ptx::tma_load_2d_u32(dst, mapB, rb, kc, 0);
+                    if (kPair) {
+                        if (bperm) ptx::tma_load_5d_pair(dst, mapB, rb, kc, 0, 0, 0, nrow >> 5);
+                        else ptx::tma_load_2d_pair(dst, mapB, rb, kc, nrow);
+                    } else {
+                        if (bperm) ptx::tma_load_5d_u32(dst, mapB, rb, kc, 0, 0, 0, 0);
+                        else ptx::tma_load_2d_u32(dst, mapB, rb, kc, 0);
+                    }
                 }
             }
         }
@@ -492,10 +505,14 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         if (mine) {
                             ptx::tma_load_4d_pair(a_base + stage * a_stage, mapA0 + ((uint32_t)e.w >> 28) * sizeof(CUtensorMap), fb,
                                                   e.x, tc.ow0 + e.y, tc.oh0 + e.z, tc.n0);
-                            const uint32_t dst = b_base + stage * b_stage;
-                            const int kc = e.w & 0x0fffffff;
-                            if (bperm) ptx::tma_load_5d_pair(dst, mapB, fb, kc, 0, 0, 0, ncoord >> 5);
-                            else ptx::tma_load_2d_pair(dst, mapB, fb, kc, ncoord);
+                            if (!bres) {
+                                for (int sx = 0; sx < p.taps; ++sx) {
+                                    const uint32_t dst = b_base + stage * b_stage + (uint32_t)(sx * p.b_bytes);
+                                    const int kc = (e.w & 0x0fffffff) + sx * p.cin_pad;
+                                    if (bperm) ptx::tma_load_5d_pair(dst, mapB, fb, kc, 0, 0, 0, ncoord >> 5);
+                                    else ptx::tma_load_2d_pair(dst, mapB, fb, kc, ncoord);
+                                }
+                            }
                         }
                     } else {
                     const uint32_t fb = full0 + stage * 8;
@@ -610,11 +627,15 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                         for (int g = 0; g < nb; ++g) {
                             // resident weights: the unit's first block (tap-major order); streamed: the stage's
                             const uint32_t bu = bres ? rb_b : b_lo0 + stage * b_stage + (uint32_t)g * b_tap * p.taps;
-                            if (p.taps == 3 && ksteps == 4) rowbox_unit<kInt8, 3, 4>(d_tmem, a_lo, a_hi, bu, desc_hi, idesc, b_tap, accumulate);
-                            else if (p.taps == 3 && ksteps == 2) rowbox_unit<kInt8, 3, 2>(d_tmem, a_lo, a_hi, bu, desc_hi, idesc, b_tap, accumulate);
+                            if (p.taps == 3 && ksteps == 4) rowbox_unit<kInt8, 3, 4, kPair>(d_tmem, a_lo, a_hi, bu, desc_hi, idesc, b_tap, accumulate);
+                            else if (p.taps == 3 && ksteps == 2) rowbox_unit<kInt8, 3, 2, kPair>(d_tmem, a_lo, a_hi, bu, desc_hi, idesc, b_tap, accumulate);
                             else
                                 for (int sx = 0; sx < p.taps; ++sx)
                                     for (int ks = 0; ks < ksteps; ++ks)
+                                        if (kPair)
+                                            ptx::tc_mma_ab_pair<kInt8>(d_tmem, a_lo + sx * a_tap + 2 * ks, a_hi, bu + sx * b_tap + 2 * ks,
+                                                                       desc_hi, idesc, (sx | ks) ? 1u : accumulate);
+                                        else
                                         ptx::tc_mma_ab<kInt8>(d_tmem, a_lo + sx * a_tap + 2 * ks, a_hi, bu + sx * b_tap + 2 * ks, desc_hi,
                                                               idesc, (sx | ks) ? 1u : accumulate);
                             accumulate = 1;
@@ -1175,10 +1196,11 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         if (rb.one_cta) two = false;
     }
     const int ctas_per_sm = two ? 2 : 1;
-    // CTA pairs (see the kernel's kPair): wide N tiles on one CTA per SM in the plain tap loop, at least two image
-    // groups to pair up.  Each CTA then holds half of the tile's weight rows.
-    const bool pair = !two && !patch && !fold.on && !p.rowbox && !g.pool && p.BN == 256 && p.tiles_nb >= 2 &&
-                      ctx->sm_count >= 2 && g.act != EXB_ACT_PRELU;
+    // CTA pairs (see the kernel's kPair): N tiles of 256 on one CTA per SM in the plain tap loop, and N tiles of 128
+    // in the row-box loop with resident weights (each CTA then keeps half of them and a stage can hold a whole tile);
+    // at least two image groups to pair up.  Each CTA holds half of the tile's weight rows.
+    const bool pair = !two && !patch && !fold.on && !g.pool && p.tiles_nb >= 2 && ctx->sm_count >= 2 && g.act != EXB_ACT_PRELU &&
+                      (p.rowbox ? (p.BN == 128 && p.n_tiles == 1 && rb.one_cta) : p.BN == 256);
     if (pair) p.b_bytes = (p.BN / 2) * p.kb_bytes;
     const int k_iters = fold.on ? g.kh : (p.rowbox ? g.kh * p.cblks : g.kh * g.kw * p.cblks);
     p.k_iters = k_iters;
@@ -1193,7 +1215,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     // operand ring: it removes the weight re-read per tile from the L2 -> SM traffic that bounds
     // this kernel.
     const int b_all = k_iters * p.taps * p.b_bytes;
-    p.b_resident = (!pair && p.n_tiles == 1 && b_all <= 150 * 1024 && budget - b_all >= (p.rowbox ? 3 : 4) * p.a_bytes) ? 1 : 0;
+    p.b_resident = ((!pair || p.rowbox) && p.n_tiles == 1 && b_all <= 150 * 1024 && budget - b_all >= (p.rowbox ? 3 : 4) * p.a_bytes) ? 1 : 0;
     if (p.b_resident) budget -= b_all;
     const int blk_bytes = p.a_bytes + (p.b_resident ? 0 : p.taps * p.b_bytes);
     // K blocks per stage: aim at ~48 KB stages (one mbarrier round trip each), keep >= 3 stages,
@@ -1221,7 +1243,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
         // A row-box unit already carries kw taps.  One stage per tile (all its units behind one barrier and one
         // commit) when two such stages fit - every hand-over costs the single issuing thread a few hundred
         // cycles - else one unit per stage and as many stages as fit.
-        G = (k_iters * blk_bytes <= 48 * 1024 && budget / (k_iters * blk_bytes) >= 2) ? k_iters : 1;
+        G = (k_iters * blk_bytes <= (pair ? 96 : 48) * 1024 && budget / (k_iters * blk_bytes) >= 2) ? k_iters : 1;
     }
     p.kgroup = G;
     int stages = budget / (G * blk_bytes);

@@ -49,6 +49,8 @@ I8_CASES = [
     (3, 256, 10, 13, 128, 3, 1, 1),     # row-box loop: two channel blocks per kernel row, weights streamed, ragged width
     (5, 128, 6, 5, 64, 3, 1, 1),        # row-box loop: map narrower than the 8-pixel tile, several images per tile
     (1, 192, 12, 12, 64, 2, 1, 0),      # row-box loop with two taps per row (2x2 kernel, no padding), three channel blocks
+    (9, 128, 12, 12, 128, 3, 1, 1),     # row-box loop on CTA pairs (resident weights, halves per CTA), odd number of image groups
+    (7, 256, 14, 14, 256, 3, 1, 1),     # tap loop on CTA pairs, odd number of image groups (last pair half empty)
 ]
 
 
@@ -123,6 +125,8 @@ F16_CASES = [
     (2, 32, 21, 19, 32, 3, 1, 1),       # row-box loop on 64-byte K rows, ragged map
     (2, 64, 11, 9, 64, 3, 1, 1),        # row-box loop, weights streamed with two CTAs per SM (73 KB slice)
     (1, 128, 12, 12, 64, 5, 1, 2),      # row-box loop with five taps per row, two channel blocks
+    (9, 64, 12, 12, 128, 3, 1, 1),      # row-box loop on CTA pairs, fp16
+    (3, 128, 14, 14, 256, 3, 2, 1),     # stride-2 tap loop on CTA pairs, fp16
 ]
 
 
