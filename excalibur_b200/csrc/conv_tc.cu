@@ -460,7 +460,12 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 TileCursor cur(p, first_unit, unit_step);
                 for (int t = first_unit; t < total_tiles && ok; t += unit_step, cur.advance(p)) {
                     const TileCoord tc = tile_of(cur);
-                    if (!ptx::mbar_wait_bounded_u32(empty0 + stage * 8, phase ^ 1u, &abort_flag, kMaxSpins)) {
+                    // Fused pooling: patch ring and accumulator ring have the same length and tile i uses slot i % length
+                    // of both, so the patch of a slot is free when the MMAs of the tile that used it have retired, which is
+                    // what the slot's "accumulator full" barrier says - one commit per tile serves producer and epilogue
+                    // (the issuing thread is what bounds that kernel).  The plain stem keeps its longer ring of patches.
+                    if (!ptx::mbar_wait_bounded_u32((p.pool ? ptx::smem_u32(&tfull_bar[0]) : empty0) + stage * 8, phase ^ 1u, &abort_flag,
+                                                    kMaxSpins)) {
                         ok = 0;
                         break;
                     }
@@ -609,7 +614,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                             accumulate = 1;
                         }
                     }
-                    ptx::tc_commit_u32(empty0 + stage * 8);
+                    if (!p.pool) ptx::tc_commit_u32(empty0 + stage * 8);
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1u;
@@ -1262,6 +1267,10 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     // alone cost a couple of microseconds, so the number of buffers in flight sets the tile rate
     // of short layers.  Epilogue groups need four warps each (one per TMEM lane quarter).
     p.acc_bufs = two ? (p.BN <= 64 ? 4 : 2) : (p.BN <= 128 ? 4 : 2);
+    if (patch && g.pool) {     // patch ring and accumulator ring run in lockstep (see the producer)
+        if (p.stages < p.acc_bufs) return fail(EXB_ERR_UNSUPPORTED, "patch ring does not fit shared memory (BN=%d)", p.BN);
+        p.stages = p.acc_bufs;
+    }
     p.epi_groups = two ? 2 : (p.acc_bufs == 4 ? 4 : 2);
     int cols = 32;
     while (cols < p.acc_bufs * p.BN) cols *= 2;
