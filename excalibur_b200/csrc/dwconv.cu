@@ -135,6 +135,9 @@ __global__ void __launch_bounds__(128) dw_strip_kernel(const TIn* __restrict__ x
 // rows downwards, keeping the last input rows in registers (raw fp16 vectors), so every input row
 // is loaded once per thread instead of once per output row; weights and bias sit in shared memory.
 // Over-fetch is (R+2)/R vertically and ((TW-1)*S+3)/(TW*S) horizontally, all of it served by L1/L2.
+// Four CTAs per SM (128 registers per thread, a few dozen bytes spilled): the kernel is bound by the latency of its
+// loads, and 16 warps per SM instead of the 12 that 160 registers allowed put a third more bytes in flight
+// (0.17 -> 0.13 ms on 32 channels @112, 0.20 -> 0.15 ms on 96 channels @112 stride 2); five CTAs spill too much.
 __device__ __forceinline__ void cvt8(const uint4& r, float (&v)[V]) {
     const __half2* h = reinterpret_cast<const __half2*>(&r);
 #pragma unroll
@@ -142,7 +145,7 @@ __device__ __forceinline__ void cvt8(const uint4& r, float (&v)[V]) {
 }
 
 template <typename TOut, int S, int TW, int R>
-__global__ void __launch_bounds__(128) dw3x3_roll_f16_kernel(const __half* __restrict__ x, const float* __restrict__ w,
+__global__ void __launch_bounds__(128, 4) dw3x3_roll_f16_kernel(const __half* __restrict__ x, const float* __restrict__ w,
                                                              const float* __restrict__ bias, TOut* __restrict__ y,
                                                              DwParams p) {
     constexpr int IN_W = (TW - 1) * S + 3;
