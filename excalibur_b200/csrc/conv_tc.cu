@@ -919,6 +919,10 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const bool row_in_box = row < p.TW * p.TH * p.TN;
             const bool vec_ok = (p.e.cout_stride & 15) == 0;
             const int n_chunks = p.BN / 16;
+            const bool lean = kInt8 && !kPrelu && vec_ok && !p.has_res && p.e.out_dtype == EXB_I8 && p.e.out2_dtype < 0 &&
+                              (p.e.act == EXB_ACT_NONE || p.e.act == EXB_ACT_RELU) && (p.BN & 31) == 0 && (p.e.cout_stride & 31) == 0 &&
+                              (p.e.y_pitch & 31) == 0 && ((n_chunks / nsub) & 1) == 0;
+            const float lean_lo = p.e.act == EXB_ACT_RELU ? 0.f : -INFINITY;
             TileCursor cur(p, first_unit + grp * unit_step, p.epi_groups * unit_step);
             for (int t = first_unit + grp * unit_step; t < total_tiles && ok; t += p.epi_groups * unit_step, ti += p.epi_groups) {
                 const TileCoord tc = tile_of(cur);
@@ -957,6 +961,28 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     break;
                 }
                 ptx::tc_fence_after_sync();
+                if (lean) {
+                    // int8-only output, no residual, ReLU or no activation: 32 channels per TMEM load, one 32-byte store
+                    // (a whole sector) per pixel and load, no run-time dispatch inside the loop
+                    for (int chunk = c_begin; chunk < c_end; chunk += 2) {
+                        uint32_t raw[32];
+                        ptx::tmem_ld_32x32b_x32(taddr + chunk * 16, raw);
+                        ptx::tmem_ld_wait();
+                        const int cl = tc.ntile * p.BN + chunk * 16;
+                        if (!valid || cl >= p.e.cout_stride) continue;
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 s4 = reinterpret_cast<const float4*>(s_scale + cl)[i];
+                            const float4 b4 = reinterpret_cast<const float4*>(s_bias + cl)[i];
+                            o[i] = quant_pack4(fmaxf(epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x), lean_lo),
+                                               fmaxf(epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y), lean_lo),
+                                               fmaxf(epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z), lean_lo),
+                                               fmaxf(epi_value<kInt8>(raw[4 * i + 3], s4.w, b4.w), lean_lo), p.e.out_scale);
+                        }
+                        st_global_256(static_cast<int8_t*>(p.e.y) + pix * p.e.y_pitch + cl, o);
+                    }
+                } else
                 for (int chunk = c_begin; chunk < c_end; ++chunk) {
                     uint32_t raw[16];
                     ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
