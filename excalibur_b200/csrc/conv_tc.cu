@@ -16,15 +16,19 @@
 //   warps 2+ epilogue, in groups of four warps (one per TMEM     - tile i uses buffer i % buffers and
 //            lane quarter)                                        group i % groups
 //
-// What bounds this kernel is the SM's shared-memory data path (128 bytes per clock): tensor-core operand
-// reads, TMA writes and every load / store of the epilogue go through it.  Two epilogues exist:
+// Main loops: the tap loop above; the row-box loop for stride-1 layers (one box of TW + kw - 1 pixels per kernel
+// row, the kw taps read through descriptors that start 0, 1, .. pixels into the swizzled box); CTA pairs for wide
+// tiles (two CTAs of a cluster share every MMA, tcgen05 cta_group::2, and each loads half of the weight rows).
+// What bounds this kernel are its serial roles - one producing and one issuing thread per CTA, epilogue warps
+// whose own instruction streams stall - and, for narrow N tiles, the shared-memory reads of the tensor pipe; every
+// loop of a single-thread role is therefore table-driven, unrolled and free of divisions.  Two epilogues exist:
 //   quad  (N tile a multiple of 32 channels): accumulators leave TMEM in the 16x256b shape, in which four
 //         neighbouring lanes hold one pixel; the B operand is loaded through a tensor map that permutes the
 //         output channels inside each 32-channel block so that those four lanes hold channels 0-7, 8-15,
 //         16-23, 24-31 of the pixel.  Residual loads and output stores of a warp then cover 8 pixels x 64
 //         contiguous bytes (whole 32-byte sectors) instead of 32 separate pieces.
 //   row   (any N tile, ragged channel counts): a thread owns one pixel (one TMEM lane) and walks its
-//         channels 16 at a time.
+//         channels 16 at a time (32 at a time, with whole-sector stores, when the only output is int8).
 // Variants with their own instantiation: patch mode for few-channel stride-2 stems (the raw input patch
 // read through un-swizzled overlapping descriptors) with a 3x3/2 max pooling in the epilogue, and the
 // per-channel PReLU activation.
