@@ -736,34 +736,29 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                     if (lane == 0) *failed = 1;
                 } else {
                     ptx::tc_fence_after_sync();
+                    // two loads of 32 channels; the activation (ReLU or ReLU6, checked by the host) is a clamp
+                    const float act_hi = p.e.act == EXB_ACT_RELU6 ? 6.f : INFINITY;
 #pragma unroll
-                    for (int chunk = 0; chunk < 4; ++chunk) {
-                        uint32_t raw[16];
-                        ptx::tmem_ld_32x32b_x16(taddr + chunk * 16, raw);
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t raw[32];
+                        ptx::tmem_ld_32x32b_x32(taddr + half * 32, raw);
                         ptx::tmem_ld_wait();
-                        float v[16];
+                        uint32_t h[16];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
+                        for (int i = 0; i < 16; ++i) {
                             // compile-time offsets into the launch parameters: constant-bank operands of the FMAs
-                            const int c4 = chunk * 16 + 4 * i;
-                            const float4 s4 = make_float4(p.c_scale[c4], p.c_scale[c4 + 1], p.c_scale[c4 + 2], p.c_scale[c4 + 3]);
-                            const float4 b4 = make_float4(p.c_bias[c4], p.c_bias[c4 + 1], p.c_bias[c4 + 2], p.c_bias[c4 + 3]);
-                            v[4 * i + 0] = epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x);
-                            v[4 * i + 1] = epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y);
-                            v[4 * i + 2] = epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z);
-                            v[4 * i + 3] = epi_value<kInt8>(raw[4 * i + 3], s4.w, b4.w);
-                        }
-                        act_vec16(v, p.e.act);
-                        uint32_t h[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
+                            const int c = half * 32 + 2 * i;
+                            const float v0 = fminf(fmaxf(epi_value<kInt8>(raw[2 * i], p.c_scale[c], p.c_bias[c]), 0.f), act_hi);
+                            const float v1 = fminf(fmaxf(epi_value<kInt8>(raw[2 * i + 1], p.c_scale[c + 1], p.c_bias[c + 1]), 0.f), act_hi);
                             // positions outside the map never win: activated values are >= 0
-                            const __half2 hv = inside ? __floats2half2_rn(v[2 * i], v[2 * i + 1]) : __floats2half2_rn(0.f, 0.f);
+                            const __half2 hv = inside ? __floats2half2_rn(v0, v1) : __floats2half2_rn(0.f, 0.f);
                             h[i] = *reinterpret_cast<const uint32_t*>(&hv);
                         }
                         uint8_t* dst = stg + row * 128;
-                        *reinterpret_cast<uint4*>(dst + (((2 * chunk) ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-                        *reinterpret_cast<uint4*>(dst + (((2 * chunk + 1) ^ (row & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            *reinterpret_cast<uint4*>(dst + (((4 * half + u) ^ (row & 7)) << 4)) =
+                                make_uint4(h[4 * u], h[4 * u + 1], h[4 * u + 2], h[4 * u + 3]);
                     }
                     ptx::tc_fence_before_sync();
                     __syncwarp();
