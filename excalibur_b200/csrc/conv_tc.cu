@@ -918,7 +918,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
             const bool row_in_box = row < p.TW * p.TH * p.TN;
             const bool vec_ok = (p.e.cout_stride & 15) == 0;
             const int n_chunks = p.BN / 16;
-            const bool lean = kInt8 && !kPrelu && vec_ok && !p.has_res && p.e.out_dtype == EXB_I8 && p.e.out2_dtype < 0 &&
+            const bool lean = kInt8 && !kPrelu && vec_ok && p.e.out_dtype == EXB_I8 && p.e.out2_dtype < 0 &&
                               (p.e.act == EXB_ACT_NONE || p.e.act == EXB_ACT_RELU) && (p.BN & 31) == 0 && (p.e.cout_stride & 31) == 0 &&
                               (p.e.y_pitch & 31) == 0 && ((n_chunks / nsub) & 1) == 0;
             const float lean_lo = p.e.act == EXB_ACT_RELU ? 0.f : -INFINITY;
@@ -940,7 +940,7 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 const bool do_res = p.has_res && vec_ok && valid;
                 const __half* res_row = p.e.residual + pix * p.e.cout_stride + tc.ntile * p.BN;
                 uint32_t rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                if (do_res && c_begin < c_end && tc.ntile * p.BN + c_begin * 16 < p.e.cout_stride)
+                if (!lean && do_res && c_begin < c_end && tc.ntile * p.BN + c_begin * 16 < p.e.cout_stride)
                     ld_global_nc_256(res_row + c_begin * 16, rn);
                 // The residual rows of this group's NEXT tile are asked into L2 now (no register cost):
                 // the tile after this one then finds them a few hundred cycles away instead of a DRAM
@@ -961,23 +961,32 @@ __global__ void __launch_bounds__((kFirstEpiWarp + kEpiWarps) * 32, kEpiWarps ==
                 }
                 ptx::tc_fence_after_sync();
                 if (lean) {
-                    // int8-only output, no residual, ReLU or no activation: 32 channels per TMEM load, one 32-byte store
-                    // (a whole sector) per pixel and load, no run-time dispatch inside the loop
+                    // int8-only output (with or without an fp16 residual), ReLU or no activation: 32 channels per TMEM load,
+                    // the residual as two 32-byte loads and the result as one 32-byte store (whole sectors) per pixel and
+                    // load, no run-time dispatch inside the loop
                     for (int chunk = c_begin; chunk < c_end; chunk += 2) {
+                        const int cl = tc.ntile * p.BN + chunk * 16;
+                        uint32_t r0[8] = {0, 0, 0, 0, 0, 0, 0, 0}, r1[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                        if (do_res && cl < p.e.cout_stride) {       // 32 channels of fp16 residual: two whole sectors
+                            ld_global_nc_256(res_row + chunk * 16, r0);
+                            ld_global_nc_256(res_row + chunk * 16 + 16, r1);
+                        }
                         uint32_t raw[32];
                         ptx::tmem_ld_32x32b_x32(taddr + chunk * 16, raw);
                         ptx::tmem_ld_wait();
-                        const int cl = tc.ntile * p.BN + chunk * 16;
                         if (!valid || cl >= p.e.cout_stride) continue;
                         uint32_t o[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float4 s4 = reinterpret_cast<const float4*>(s_scale + cl)[i];
                             const float4 b4 = reinterpret_cast<const float4*>(s_bias + cl)[i];
-                            o[i] = quant_pack4(fmaxf(epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x), lean_lo),
-                                               fmaxf(epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y), lean_lo),
-                                               fmaxf(epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z), lean_lo),
-                                               fmaxf(epi_value<kInt8>(raw[4 * i + 3], s4.w, b4.w), lean_lo), p.e.out_scale);
+                            const uint32_t* rr = i < 4 ? r0 : r1;
+                            const float2 ra = __half22float2(*reinterpret_cast<const __half2*>(&rr[2 * (i & 3)]));
+                            const float2 rb = __half22float2(*reinterpret_cast<const __half2*>(&rr[2 * (i & 3) + 1]));
+                            o[i] = quant_pack4(fmaxf(epi_value<kInt8>(raw[4 * i + 0], s4.x, b4.x) + ra.x, lean_lo),
+                                               fmaxf(epi_value<kInt8>(raw[4 * i + 1], s4.y, b4.y) + ra.y, lean_lo),
+                                               fmaxf(epi_value<kInt8>(raw[4 * i + 2], s4.z, b4.z) + rb.x, lean_lo),
+                                               fmaxf(epi_value<kInt8>(raw[4 * i + 3], s4.w, b4.w) + rb.y, lean_lo), p.e.out_scale);
                         }
                         st_global_256(static_cast<int8_t*>(p.e.y) + pix * p.e.y_pitch + cl, o);
                     }
@@ -1371,7 +1380,7 @@ int conv_tc_launch(exb_ctx* ctx, const ConvGeom& g, const void* x, const exb_con
     // 15-20 % of the layer; a lone int8 output is as fast from the thread-per-pixel epilogue (measured on the
     // ResNet-18-style layers at batch 256), which needs fewer TMEM loads.
     const bool quad = !patch && !p.pool && p.BN % 32 == 0 && w->cout_pad % 32 == 0 && (g.cout_stride & 7) == 0 &&
-                      g.out_dtype != EXB_I32 && !(g.out_dtype == EXB_I8 && g.out2_dtype < 0 && !g.has_res) &&
+                      g.out_dtype != EXB_I32 && !(g.out_dtype == EXB_I8 && g.out2_dtype < 0) &&
                       p.TW <= 255 && p.TH <= 255 && p.TN <= 32767;
     p.b_perm = quad ? 1 : 0;
     {
